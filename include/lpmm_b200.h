@@ -1,0 +1,120 @@
+/*
+ * lpmm_b200.h -- C ABI of the B200 (sm_100a) implementation of lpmm's 4-bit optimizer-step path.
+ *
+ * Every entry point takes plain device pointers, element counts and a CUDA stream handle
+ * (a cudaStream_t passed as void*; NULL means the legacy default stream) and returns an int
+ * status: 0 on success, a negative LPMM_B200_ERR_* otherwise.  Argument errors are detected on
+ * the host before anything is launched.  No entry point allocates or frees device memory unless
+ * its comment says otherwise, none synchronises the device, and all launches are asynchronous on
+ * the given stream.  The caller owns every buffer.
+ *
+ * Each declaration cites the interface of the reference (thu-ml/low-bit-optimizers, paths
+ * relative to that project) that it stands in for.
+ *
+ * Data formats shared by all entry points
+ *   - 4-bit codes: two per byte, element 2k in bits 0-3 and element 2k+1 in bits 4-7 of byte k
+ *     (lpmm/cpp_extension/fused_adamw_kernel.cu:119,133,157,163; quantization_kernel.cu:454,623).
+ *   - quantization map ("qmap"): 16 ascending fp32 values in device memory.
+ *   - nearest-code rule: code(x) = number of midpoints (q[i]+q[i+1])*0.5f that are < x, ties to
+ *     the lower code, NaN -> 15 (fused_adamw_kernel.cu:27-49, quantization_kernel.cu:397-427).
+ *   - group scale: one fp32 absmax per 128 consecutive elements of the flattened tensor.
+ */
+#ifndef LPMM_B200_H
+#define LPMM_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LPMM_B200_OK 0
+#define LPMM_B200_ERR_NULL_POINTER (-1)   /* a required pointer is NULL                        */
+#define LPMM_B200_ERR_BAD_SIZE (-2)       /* negative / inconsistent element count or range    */
+#define LPMM_B200_ERR_BAD_KIND (-3)       /* unknown tensor kind / option value                */
+#define LPMM_B200_ERR_CUDA (-4)           /* a CUDA runtime call failed, see last_cuda_error   */
+#define LPMM_B200_ERR_UNSUPPORTED (-5)    /* valid in the reference, not built here            */
+#define LPMM_B200_ERR_TOO_LARGE (-6)      /* size beyond a documented static limit             */
+
+#define LPMM_B200_GROUP 128               /* elements per scale group of the fused step        */
+#define LPMM_B200_PACK_GROUP 2048         /* elements per row of the pack/unpack layout        */
+
+/* Tensor kinds of the multi-tensor step. */
+#define LPMM_B200_KIND_Q4 0               /* 4-bit m and v, group-128 absmax scales            */
+#define LPMM_B200_KIND_FP32 1             /* fp32 m and v (the numel <= threshold fallback)    */
+
+/* One parameter tensor of a multi-tensor step.  All pointers are device pointers into
+ * contiguous arrays.  kind Q4: m, v are int8[(numel+1)/2] packed codes, m_scale, v_scale are
+ * float[(numel+127)/128].  kind FP32: m, v are float[numel], the scale pointers are ignored. */
+typedef struct lpmm_b200_tensor {
+  float* p;
+  const float* g;
+  void* m;
+  void* v;
+  float* m_scale;
+  float* v_scale;
+  int64_t numel;
+  int32_t kind;
+  int32_t reserved;
+} lpmm_b200_tensor;
+
+/* AdamW hyper-parameters, as the C floats the reference's bindings receive
+ * (lpmm/cpp_extension/fused_adamw.cc:44-58). */
+typedef struct lpmm_b200_hyper {
+  float beta1;
+  float beta2;
+  float lr;
+  float weight_decay;
+  float eps;
+  float step;
+} lpmm_b200_hyper;
+
+/* Human-readable text for a status code. */
+const char* lpmm_b200_strerror(int status);
+/* Text of the CUDA error behind the calling thread's last LPMM_B200_ERR_CUDA ("" if none). */
+const char* lpmm_b200_last_cuda_error(void);
+/* ABI version of this library (bumped on any signature change). */
+int lpmm_b200_abi_version(void);
+
+/* Fused 4-bit AdamW step of one tensor, in place.
+ * Replaces fused_adamw.adamw4bit_single_tensor (lpmm/cpp_extension/fused_adamw.cc:44-78 ->
+ * fused_adamw_kernel.cu:81-174, 208-243).  Unlike the reference (fused_adamw.cc:68-71) an odd
+ * numel is accepted; the unused high nibble of the last byte is written as 0. */
+int lpmm_b200_adamw4bit_single_tensor(float* p, const float* g, int8_t* exp_avg, int8_t* exp_avg_sq,
+                                      float* exp_avg_scale, float* exp_avg_sq_scale,
+                                      const float* exp_avg_qmap, const float* exp_avg_sq_qmap,
+                                      float beta1, float beta2, float lr, float weight_decay, float eps,
+                                      float step, int64_t numel, void* stream);
+
+/* Fused fp32-state AdamW step of one tensor, in place.
+ * Replaces fused_adamw.adamw_single_tensor (lpmm/cpp_extension/fused_adamw.cc:15-41 ->
+ * fused_adamw_kernel.cu:52-78, 177-205). */
+int lpmm_b200_adamw_single_tensor(float* p, const float* g, float* exp_avg, float* exp_avg_sq, float beta1,
+                                  float beta2, float lr, float weight_decay, float eps, float step,
+                                  int64_t numel, void* stream);
+
+/* Fused step over a whole parameter list in one launch per <= 400 tensors.
+ * Replaces the per-tensor Python loop of _fused_adamw4bit (lpmm/optim/adamw.py:463-561) and the
+ * per-tensor launches behind it.  `tensors` is a HOST array of n descriptors (copied into the
+ * launch parameters; nothing is read from it after return).  The flattened list defines a global
+ * index space of 128-element groups (tensor t contributes ceil(numel_t/128) groups, in list
+ * order); only groups in [group_begin, group_end) are updated, which is how a ZeRO-1 rank
+ * updates its shard.  Pass group_begin = 0, group_end = -1 for the whole list. */
+int lpmm_b200_adamw4bit_multi_tensor(const lpmm_b200_tensor* tensors, int n_tensors, const float* exp_avg_qmap,
+                                     const float* exp_avg_sq_qmap, lpmm_b200_hyper hyper, int64_t group_begin,
+                                     int64_t group_end, void* stream);
+
+/* Number of 128-element groups of a tensor list (the size of the index space above), or a
+ * negative status.  Host-only arithmetic. */
+int64_t lpmm_b200_count_groups(const lpmm_b200_tensor* tensors, int n_tensors);
+
+/* The two bias-correction terms exactly as the fused step computes them on the device:
+ * out[0] = 1 - powf(beta1, step), out[1] = sqrtf(1 - powf(beta2, step))
+ * (fused_adamw_kernel.cu:103-104).  out is a device pointer to 2 floats.  For tests that feed a
+ * CPU model the device's own powf result. */
+int lpmm_b200_bias_corrections(float beta1, float beta2, float step, float* out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LPMM_B200_H */

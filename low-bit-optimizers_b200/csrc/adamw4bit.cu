@@ -1,0 +1,418 @@
+// Fused 4-bit AdamW step for sm_100a: one pass over p, g, packed m/v codes and group scales.
+//
+// Arithmetic follows the reference kernels (lpmm/cpp_extension/fused_adamw_kernel.cu:81-174 for
+// 4-bit states, :52-78 for fp32 states) operation by operation, with every rounding spelled out
+// as an intrinsic so the compiler cannot re-associate or re-contract it:
+//   m  = fma(beta1, qmap_m[code]*scale_m, (1-beta1)*g)
+//   v  = fma(beta2, qmap_v[code]*scale_v, ((1-beta2)*g)*g)
+//   d  = (sqrt(v)/c2s + eps) * c1 ;  p = fma(-lr, fma(wd, p, m/d), p)
+//   new scale = group max of |m| (resp. v); new code = nearest-code rule on m/scale.
+// Work decomposition is new: a 128-element group is owned by a half-warp (16 lanes x 8
+// elements), each lane moves its 8 p and g values with one 256-bit access and its 8 codes per
+// moment with one 32-bit access, the group maxima are four-step shuffle reductions, and one
+// launch walks the whole parameter list (or a ZeRO-1 shard of it) through a descriptor table
+// carried in the kernel parameters.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace lpmm_b200 {
+
+constexpr int MAX_TENSORS = 400;  // descriptors per launch (28.9 KB of the 32 KB parameter space)
+constexpr int CTA_THREADS = 256;
+constexpr int HW_PER_CTA = CTA_THREADS / 16;
+
+struct TDesc {
+  float* p;
+  const float* g;
+  void* m;
+  void* v;
+  float* sm;
+  float* sv;
+  long long numel;
+  long long gstart;  // first global group index of this tensor
+  int kind;          // LPMM_B200_KIND_*
+  int aligned;       // all pointers satisfy the vector-access alignment
+};
+
+struct Table {
+  int n;
+  int pad;
+  long long gtotal;  // groups in this table
+  TDesc t[MAX_TENSORS];
+};
+
+struct Consts {
+  float beta1, beta2, omb1, omb2, lr, wd, eps, c1;
+  UDiv c2s;
+};
+
+__device__ __forceinline__ float upd_m(const Consts& c, float m0, float g) {
+  return __fmaf_rn(c.beta1, m0, __fmul_rn(c.omb1, g));
+}
+__device__ __forceinline__ float upd_v(const Consts& c, float v0, float g) {
+  return __fmaf_rn(c.beta2, v0, __fmul_rn(__fmul_rn(c.omb2, g), g));
+}
+__device__ __forceinline__ float upd_p(const Consts& c, float p, float m, float v) {
+  float d = udiv(__fsqrt_rn(v), c.c2s);
+  d = __fmul_rn(__fadd_rn(d, c.eps), c.c1);
+  const float u = __fmaf_rn(c.wd, p, __fdiv_rn(m, d));
+  return __fmaf_rn(-c.lr, u, p);
+}
+
+__device__ __forceinline__ float hw_max(float x, unsigned mask) {
+#pragma unroll
+  for (int o = 8; o; o >>= 1) x = fmaxf(x, __shfl_xor_sync(mask, x, o, 16));
+  return x;
+}
+
+template <bool USE_LUT>
+__device__ __forceinline__ int code_of(const QuantLut& L, float x) {
+  return USE_LUT ? lut_code(L.ent, x) : bsearch_code(L.qmap, x);
+}
+
+// One full, aligned 4-bit group: lane owns elements [8*l16, 8*l16+8).
+template <bool USE_LUT>
+__device__ __forceinline__ void group_q4_fast(const TDesc& t, long long gl, int l16, unsigned hmask,
+                                              const Consts& c, const QuantLut& Lm, const QuantLut& Lv) {
+  const long long e0 = gl * 128 + l16 * 8;
+  uint32_t* mcp = reinterpret_cast<uint32_t*>(t.m) + (e0 >> 3);
+  uint32_t* vcp = reinterpret_cast<uint32_t*>(t.v) + (e0 >> 3);
+  f8 p = ldg_f8(t.p + e0);
+  const f8 g = ldg_f8(t.g + e0);
+  const uint32_t mc = *mcp;
+  const uint32_t vc = *vcp;
+  const float sm = t.sm[gl];
+  const float sv = t.sv[gl];
+
+  float m[8], v[8];
+  float am = 0.0f, av = 0.0f;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const float m0 = __fmul_rn(Lm.qmap[(mc >> (4 * k)) & 15u], sm);
+    const float v0 = __fmul_rn(Lv.qmap[(vc >> (4 * k)) & 15u], sv);
+    m[k] = upd_m(c, m0, g.x[k]);
+    v[k] = upd_v(c, v0, g.x[k]);
+    p.x[k] = upd_p(c, p.x[k], m[k], v[k]);
+    am = fmaxf(am, fabsf(m[k]));
+    av = fmaxf(av, v[k]);
+  }
+  stg_f8(t.p + e0, p);
+  am = hw_max(am, hmask);
+  av = hw_max(av, hmask);
+  const UDiv dm = udiv_make(am), dv = udiv_make(av);
+  uint32_t mo = 0, vo = 0;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    mo |= (uint32_t)(code_of<USE_LUT>(Lm, udiv(m[k], dm)) & 15) << (4 * k);
+    vo |= (uint32_t)(code_of<USE_LUT>(Lv, udiv(v[k], dv)) & 15) << (4 * k);
+  }
+  *mcp = mo;
+  *vcp = vo;
+  if (l16 == 0) {
+    t.sm[gl] = am;
+    t.sv[gl] = av;
+  }
+}
+
+// A ragged (last) group or an unaligned tensor: same lane/element ownership, scalar accesses,
+// every element and code byte predicated on numel (fused_adamw_kernel.cu:114,130-143,160-165).
+template <bool USE_LUT>
+__device__ __forceinline__ void group_q4_slow(const TDesc& t, long long gl, int l16, unsigned hmask,
+                                              const Consts& c, const QuantLut& Lm, const QuantLut& Lv) {
+  const long long e0 = gl * 128 + l16 * 8;
+  const long long n = t.numel;
+  uint8_t* mb = reinterpret_cast<uint8_t*>(t.m) + (e0 >> 1);
+  uint8_t* vb = reinterpret_cast<uint8_t*>(t.v) + (e0 >> 1);
+  const float sm = t.sm[gl];
+  const float sv = t.sv[gl];
+  float m[8], v[8];
+  float am = 0.0f, av = 0.0f;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    m[k] = 0.0f;
+    v[k] = 0.0f;
+    if (e0 + k < n) {
+      const uint8_t mbyte = mb[k >> 1], vbyte = vb[k >> 1];
+      const float g = t.g[e0 + k];
+      const float m0 = __fmul_rn(Lm.qmap[(mbyte >> (4 * (k & 1))) & 15u], sm);
+      const float v0 = __fmul_rn(Lv.qmap[(vbyte >> (4 * (k & 1))) & 15u], sv);
+      m[k] = upd_m(c, m0, g);
+      v[k] = upd_v(c, v0, g);
+      t.p[e0 + k] = upd_p(c, t.p[e0 + k], m[k], v[k]);
+      am = fmaxf(am, fabsf(m[k]));
+      av = fmaxf(av, v[k]);
+    }
+  }
+  am = hw_max(am, hmask);
+  av = hw_max(av, hmask);
+  const UDiv dm = udiv_make(am), dv = udiv_make(av);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    if (e0 + 2 * j < n) {
+      uint32_t mo = code_of<USE_LUT>(Lm, udiv(m[2 * j], dm)) & 15;
+      uint32_t vo = code_of<USE_LUT>(Lv, udiv(v[2 * j], dv)) & 15;
+      if (e0 + 2 * j + 1 < n) {
+        mo |= (uint32_t)(code_of<USE_LUT>(Lm, udiv(m[2 * j + 1], dm)) & 15) << 4;
+        vo |= (uint32_t)(code_of<USE_LUT>(Lv, udiv(v[2 * j + 1], dv)) & 15) << 4;
+      }
+      mb[j] = (uint8_t)mo;
+      vb[j] = (uint8_t)vo;
+    }
+  }
+  if (l16 == 0) {
+    t.sm[gl] = am;
+    t.sv[gl] = av;
+  }
+}
+
+// fp32-state tensors (the numel <= threshold fallback), 128 elements per half-warp step.
+__device__ __forceinline__ void group_fp32(const TDesc& t, long long gl, int l16, const Consts& c) {
+  const long long e0 = gl * 128 + l16 * 8;
+  float* mp = reinterpret_cast<float*>(t.m);
+  float* vp = reinterpret_cast<float*>(t.v);
+  if (t.aligned && (gl + 1) * 128 <= t.numel) {
+    f8 p = ldg_f8(t.p + e0);
+    const f8 g = ldg_f8(t.g + e0);
+    f8 m = ldg_f8(mp + e0);
+    f8 v = ldg_f8(vp + e0);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      m.x[k] = upd_m(c, m.x[k], g.x[k]);
+      v.x[k] = upd_v(c, v.x[k], g.x[k]);
+      p.x[k] = upd_p(c, p.x[k], m.x[k], v.x[k]);
+    }
+    stg_f8(mp + e0, m);
+    stg_f8(vp + e0, v);
+    stg_f8(t.p + e0, p);
+  } else {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const long long e = e0 + k;
+      if (e < t.numel) {
+        const float g = t.g[e];
+        const float m = upd_m(c, mp[e], g);
+        const float v = upd_v(c, vp[e], g);
+        mp[e] = m;
+        vp[e] = v;
+        t.p[e] = upd_p(c, t.p[e], m, v);
+      }
+    }
+  }
+}
+
+template <bool USE_LUT>
+__device__ __forceinline__ void run_groups(const Table& tab, const Consts& c, const QuantLut& Lm,
+                                           const QuantLut& Lv, long long gbeg, long long gend) {
+  const int hw = threadIdx.x >> 4;
+  const int l16 = threadIdx.x & 15;
+  const unsigned hmask = 0xFFFFu << (threadIdx.x & 16);
+  long long gi = gbeg + (long long)blockIdx.x * HW_PER_CTA + hw;
+  const long long stride = (long long)gridDim.x * HW_PER_CTA;
+  if (gi >= gend) return;
+  // tensor holding group gi: last t with gstart <= gi
+  int lo = 0, hi = tab.n - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (tab.t[mid].gstart <= gi) lo = mid;
+    else hi = mid - 1;
+  }
+  int ti = lo;
+  long long tend = (ti + 1 < tab.n) ? tab.t[ti + 1].gstart : tab.gtotal;
+  for (; gi < gend; gi += stride) {
+    while (gi >= tend) {
+      ++ti;
+      tend = (ti + 1 < tab.n) ? tab.t[ti + 1].gstart : tab.gtotal;
+    }
+    const TDesc& t = tab.t[ti];
+    const long long gl = gi - t.gstart;
+    if (t.kind == LPMM_B200_KIND_Q4) {
+      if (t.aligned && (gl + 1) * 128 <= t.numel) group_q4_fast<USE_LUT>(t, gl, l16, hmask, c, Lm, Lv);
+      else group_q4_slow<USE_LUT>(t, gl, l16, hmask, c, Lm, Lv);
+    } else {
+      group_fp32(t, gl, l16, c);
+    }
+  }
+}
+
+template <bool HAS_Q4>
+__global__ void __launch_bounds__(CTA_THREADS, 4)
+adamw4bit_multi_kernel(const __grid_constant__ Table tab, const float* __restrict__ qmap_m,
+                       const float* __restrict__ qmap_v, const lpmm_b200_hyper h, long long gbeg, long long gend) {
+  __shared__ QuantLut Lm, Lv;
+  if (HAS_Q4) {
+    lut_build(Lm, qmap_m);
+    lut_build(Lv, qmap_v);
+  }
+  Consts c;
+  c.beta1 = h.beta1;
+  c.beta2 = h.beta2;
+  c.omb1 = __fsub_rn(1.0f, h.beta1);
+  c.omb2 = __fsub_rn(1.0f, h.beta2);
+  c.lr = h.lr;
+  c.wd = h.weight_decay;
+  c.eps = h.eps;
+  c.c1 = __fsub_rn(1.0f, powf(h.beta1, h.step));
+  c.c2s = udiv_make(__fsqrt_rn(__fsub_rn(1.0f, powf(h.beta2, h.step))));
+  if (!HAS_Q4 || (Lm.valid && Lv.valid)) run_groups<true>(tab, c, Lm, Lv, gbeg, gend);
+  else run_groups<false>(tab, c, Lm, Lv, gbeg, gend);
+}
+
+__global__ void bias_corrections_kernel(float beta1, float beta2, float step, float* out) {
+  out[0] = __fsub_rn(1.0f, powf(beta1, step));
+  out[1] = __fsqrt_rn(__fsub_rn(1.0f, powf(beta2, step)));
+}
+
+static inline int64_t groups_of(int64_t numel) { return (numel + 127) / 128; }
+
+static int launch_multi(const lpmm_b200_tensor* ts, int n, const float* qm, const float* qv,
+                        const lpmm_b200_hyper& h, int64_t gbeg, int64_t gend, cudaStream_t st) {
+  // `ts` may hold more than MAX_TENSORS entries: walk it in windows, each window one launch over
+  // the part of [gbeg, gend) that falls inside it.
+  static thread_local Table tab;  // 28.9 KB; copied into the launch parameters by the runtime
+  int64_t gcursor = 0;            // global group index of the window's first tensor
+  int i = 0;
+  while (i < n) {
+    int cnt = 0;
+    int64_t g = 0;
+    bool any_q4 = false;
+    for (; i < n && cnt < MAX_TENSORS; ++i) {
+      const lpmm_b200_tensor& s = ts[i];
+      if (s.numel == 0) continue;
+      TDesc& d = tab.t[cnt++];
+      d.p = s.p;
+      d.g = s.g;
+      d.m = s.m;
+      d.v = s.v;
+      d.sm = s.m_scale;
+      d.sv = s.v_scale;
+      d.numel = s.numel;
+      d.gstart = g;
+      d.kind = s.kind;
+      any_q4 = any_q4 || s.kind == LPMM_B200_KIND_Q4;
+      const uintptr_t a = (uintptr_t)s.p | (uintptr_t)s.g;
+      if (s.kind == LPMM_B200_KIND_Q4)
+        d.aligned = ((a & 31) == 0) && ((((uintptr_t)s.m | (uintptr_t)s.v) & 3) == 0);
+      else
+        d.aligned = (((a | (uintptr_t)s.m | (uintptr_t)s.v) & 31) == 0);
+      g += groups_of(s.numel);
+    }
+    tab.n = cnt;
+    tab.pad = 0;
+    tab.gtotal = g;
+    // intersect [gbeg, gend) with this window's [gcursor, gcursor + g)
+    const int64_t lo = (gbeg > gcursor ? gbeg : gcursor) - gcursor;
+    const int64_t hi = (gend < gcursor + g ? gend : gcursor + g) - gcursor;
+    gcursor += g;
+    if (cnt == 0 || hi <= lo) continue;
+    const int64_t work = hi - lo;
+    int64_t grid = (work + HW_PER_CTA - 1) / HW_PER_CTA;
+    const int64_t cap = (int64_t)num_sms() * 4;
+    if (grid > cap) grid = cap;
+    if (any_q4)
+      adamw4bit_multi_kernel<true><<<(unsigned)grid, CTA_THREADS, 0, st>>>(tab, qm, qv, h, (long long)lo,
+                                                                          (long long)hi);
+    else
+      adamw4bit_multi_kernel<false><<<(unsigned)grid, CTA_THREADS, 0, st>>>(tab, qm, qv, h, (long long)lo,
+                                                                           (long long)hi);
+    LPMM_CUDA_TRY(cudaGetLastError());
+  }
+  return LPMM_B200_OK;
+}
+
+static int check_list(const lpmm_b200_tensor* ts, int n, bool need_qmaps, const float* qm, const float* qv) {
+  if (n < 0) return LPMM_B200_ERR_BAD_SIZE;
+  if (n > 0 && !ts) return LPMM_B200_ERR_NULL_POINTER;
+  bool any_q4 = false;
+  for (int i = 0; i < n; ++i) {
+    const lpmm_b200_tensor& s = ts[i];
+    if (s.numel < 0) return LPMM_B200_ERR_BAD_SIZE;
+    if (s.kind != LPMM_B200_KIND_Q4 && s.kind != LPMM_B200_KIND_FP32) return LPMM_B200_ERR_BAD_KIND;
+    if (s.numel == 0) continue;
+    if (!s.p || !s.g || !s.m || !s.v) return LPMM_B200_ERR_NULL_POINTER;
+    if (s.kind == LPMM_B200_KIND_Q4) {
+      any_q4 = true;
+      if (!s.m_scale || !s.v_scale) return LPMM_B200_ERR_NULL_POINTER;
+    }
+  }
+  if ((any_q4 || need_qmaps) && (!qm || !qv)) return LPMM_B200_ERR_NULL_POINTER;
+  return LPMM_B200_OK;
+}
+
+}  // namespace lpmm_b200
+
+using namespace lpmm_b200;
+
+extern "C" int64_t lpmm_b200_count_groups(const lpmm_b200_tensor* tensors, int n_tensors) {
+  if (n_tensors < 0) return LPMM_B200_ERR_BAD_SIZE;
+  if (n_tensors > 0 && !tensors) return LPMM_B200_ERR_NULL_POINTER;
+  int64_t g = 0;
+  for (int i = 0; i < n_tensors; ++i) {
+    if (tensors[i].numel < 0) return LPMM_B200_ERR_BAD_SIZE;
+    g += groups_of(tensors[i].numel);
+  }
+  return g;
+}
+
+extern "C" int lpmm_b200_adamw4bit_multi_tensor(const lpmm_b200_tensor* tensors, int n_tensors,
+                                                const float* exp_avg_qmap, const float* exp_avg_sq_qmap,
+                                                lpmm_b200_hyper hyper, int64_t group_begin, int64_t group_end,
+                                                void* stream) {
+  int rc = check_list(tensors, n_tensors, false, exp_avg_qmap, exp_avg_sq_qmap);
+  if (rc != LPMM_B200_OK) return rc;
+  const int64_t total = lpmm_b200_count_groups(tensors, n_tensors);
+  if (group_end < 0) group_end = total;
+  if (group_begin < 0 || group_begin > group_end || group_end > total) return LPMM_B200_ERR_BAD_SIZE;
+  if (group_begin == group_end) return LPMM_B200_OK;
+  return launch_multi(tensors, n_tensors, exp_avg_qmap, exp_avg_sq_qmap, hyper, group_begin, group_end,
+                      (cudaStream_t)stream);
+}
+
+extern "C" int lpmm_b200_adamw4bit_single_tensor(float* p, const float* g, int8_t* exp_avg, int8_t* exp_avg_sq,
+                                                 float* exp_avg_scale, float* exp_avg_sq_scale,
+                                                 const float* exp_avg_qmap, const float* exp_avg_sq_qmap,
+                                                 float beta1, float beta2, float lr, float weight_decay, float eps,
+                                                 float step, int64_t numel, void* stream) {
+  lpmm_b200_tensor t;
+  t.p = p;
+  t.g = g;
+  t.m = exp_avg;
+  t.v = exp_avg_sq;
+  t.m_scale = exp_avg_scale;
+  t.v_scale = exp_avg_sq_scale;
+  t.numel = numel;
+  t.kind = LPMM_B200_KIND_Q4;
+  t.reserved = 0;
+  const lpmm_b200_hyper h = {beta1, beta2, lr, weight_decay, eps, step};
+  int rc = check_list(&t, 1, true, exp_avg_qmap, exp_avg_sq_qmap);
+  if (rc != LPMM_B200_OK) return rc;
+  if (numel == 0) return LPMM_B200_OK;
+  return launch_multi(&t, 1, exp_avg_qmap, exp_avg_sq_qmap, h, 0, groups_of(numel), (cudaStream_t)stream);
+}
+
+extern "C" int lpmm_b200_bias_corrections(float beta1, float beta2, float step, float* out, void* stream) {
+  if (!out) return LPMM_B200_ERR_NULL_POINTER;
+  bias_corrections_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(beta1, beta2, step, out);
+  LPMM_CUDA_TRY(cudaGetLastError());
+  return LPMM_B200_OK;
+}
+
+extern "C" int lpmm_b200_adamw_single_tensor(float* p, const float* g, float* exp_avg, float* exp_avg_sq,
+                                             float beta1, float beta2, float lr, float weight_decay, float eps,
+                                             float step, int64_t numel, void* stream) {
+  lpmm_b200_tensor t;
+  t.p = p;
+  t.g = g;
+  t.m = exp_avg;
+  t.v = exp_avg_sq;
+  t.m_scale = nullptr;
+  t.v_scale = nullptr;
+  t.numel = numel;
+  t.kind = LPMM_B200_KIND_FP32;
+  t.reserved = 0;
+  const lpmm_b200_hyper h = {beta1, beta2, lr, weight_decay, eps, step};
+  int rc = check_list(&t, 1, false, nullptr, nullptr);
+  if (rc != LPMM_B200_OK) return rc;
+  if (numel == 0) return LPMM_B200_OK;
+  return launch_multi(&t, 1, nullptr, nullptr, h, 0, groups_of(numel), (cudaStream_t)stream);
+}

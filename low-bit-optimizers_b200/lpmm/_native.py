@@ -1,0 +1,84 @@
+"""ctypes binding of the C-ABI CUDA library (``include/lpmm_b200.h``).
+
+The library is the only implementation of the optimizer-step arithmetic in this package: if it
+cannot be loaded, importing this module raises, and nothing falls back to torch ops or the CPU.
+"""
+import ctypes
+import os
+
+_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "_lib", "liblpmm_b200.so")
+
+c_float_p = ctypes.c_void_p
+c_void_p = ctypes.c_void_p
+
+
+class Tensor(ctypes.Structure):
+    """``lpmm_b200_tensor``"""
+    _fields_ = [
+        ("p", ctypes.c_void_p),
+        ("g", ctypes.c_void_p),
+        ("m", ctypes.c_void_p),
+        ("v", ctypes.c_void_p),
+        ("m_scale", ctypes.c_void_p),
+        ("v_scale", ctypes.c_void_p),
+        ("numel", ctypes.c_int64),
+        ("kind", ctypes.c_int32),
+        ("reserved", ctypes.c_int32),
+    ]
+
+
+class Hyper(ctypes.Structure):
+    """``lpmm_b200_hyper``"""
+    _fields_ = [(n, ctypes.c_float) for n in ("beta1", "beta2", "lr", "weight_decay", "eps", "step")]
+
+
+KIND_Q4 = 0
+KIND_FP32 = 1
+GROUP = 128
+PACK_GROUP = 2048
+
+
+class NativeError(RuntimeError):
+    pass
+
+
+def _load():
+    if not os.path.exists(_LIB_PATH):
+        raise ImportError(
+            f"{_LIB_PATH} is missing: build it with `python low-bit-optimizers_b200/build.py` "
+            "(needs nvcc; there is no non-CUDA implementation)")
+    lib = ctypes.CDLL(_LIB_PATH)
+    f, i64, i32, vp = ctypes.c_float, ctypes.c_int64, ctypes.c_int, ctypes.c_void_p
+    sigs = {
+        "lpmm_b200_strerror": (ctypes.c_char_p, [i32]),
+        "lpmm_b200_last_cuda_error": (ctypes.c_char_p, []),
+        "lpmm_b200_abi_version": (i32, []),
+        "lpmm_b200_adamw4bit_single_tensor": (i32, [vp] * 8 + [f] * 6 + [i64, vp]),
+        "lpmm_b200_adamw_single_tensor": (i32, [vp] * 4 + [f] * 6 + [i64, vp]),
+        "lpmm_b200_adamw4bit_multi_tensor": (i32, [ctypes.POINTER(Tensor), i32, vp, vp, Hyper, i64, i64, vp]),
+        "lpmm_b200_count_groups": (i64, [ctypes.POINTER(Tensor), i32]),
+        "lpmm_b200_bias_corrections": (i32, [f, f, f, vp, vp]),
+    }
+    for name, (res, args) in sigs.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    return lib, sigs
+
+
+lib, SIGNATURES = _load()
+
+
+def check(status):
+    """Raise ``NativeError`` (a RuntimeError, like the reference's TORCH_CHECK failures) on a
+    non-zero status."""
+    if status != 0:
+        msg = lib.lpmm_b200_strerror(int(status)).decode()
+        if status == -4:
+            msg += ": " + lib.lpmm_b200_last_cuda_error().decode()
+        raise NativeError(f"lpmm_b200 status {status}: {msg}")
+
+
+def current_stream_handle():
+    import torch
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
