@@ -81,6 +81,10 @@ __device__ __forceinline__ float hw_max(float x, unsigned mask) {
   return x;
 }
 
+__device__ __forceinline__ void prefetch_l2(const void* ptr) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(ptr));
+}
+
 // Any 4-bit group, any alignment, any map: scalar accesses predicated on numel
 // (fused_adamw_kernel.cu:114,130-143,160-165), IEEE sqrt and division, the reference's search.
 // The fast path falls back to this before it has stored anything.
@@ -131,22 +135,57 @@ __device__ __noinline__ void group_q4_generic(const TDesc& t, long long gl, int 
   }
 }
 
-// One full, aligned 4-bit group: lane owns elements [8*l16, 8*l16+8).
-// qm_l / qv_l: this lane's entry of the two maps (qmap[l16]).
+// Codes of one lane's 8 elements with IEEE division and the reference's search; used when a
+// group's scale lies outside the domain of the shared-reciprocal division.
+__device__ __noinline__ uint2 quant8_exact(const QMapSmem& Sm, const QMapSmem& Sv, float am, float av, float m0,
+                                           float m1, float m2, float m3, float m4, float m5, float m6, float m7,
+                                           float v0, float v1, float v2, float v3, float v4, float v5, float v6,
+                                           float v7) {
+  const float m[8] = {m0, m1, m2, m3, m4, m5, m6, m7};
+  const float v[8] = {v0, v1, v2, v3, v4, v5, v6, v7};
+  uint2 o = make_uint2(0u, 0u);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    o.x |= (uint32_t)(bsearch_code(Sm.qmap, __fdiv_rn(m[k], am)) & 15) << (4 * k);
+    o.y |= (uint32_t)(bsearch_code(Sv.qmap, __fdiv_rn(v[k], av)) & 15) << (4 * k);
+  }
+  return o;
+}
+
+// Pointers of one 4-bit tensor, already offset to this lane's first element of group 0.
+struct LanePtrs {
+  float* p;
+  const float* g;
+  uint32_t* mc;
+  uint32_t* vc;
+  float* sm;
+  float* sv;
+};
+
+// One full, aligned 4-bit group: lane owns elements [8*l16, 8*l16+8) of group gl.
+// qm_l / qv_l: this lane's entry of the two maps (qmap[l16]).  pf: how many groups ahead this
+// half-warp's next group lies (0 = none); its lines are requested into L2 now.
 template <bool FAST, bool VLIN>
-__device__ __forceinline__ void group_q4_fast(const TDesc& t, long long gl, int l16, unsigned hmask,
+__device__ __forceinline__ void group_q4_fast(const LanePtrs& t, unsigned gl, int l16, unsigned hmask,
                                               const Consts& c, const QMapSmem& Sm, const QMapSmem& Sv,
                                               const LutEnt* __restrict__ lut_m, const LutEnt* __restrict__ lut_v,
-                                              float qm_l, float qv_l) {
-  const long long e0 = gl * 128 + l16 * 8;
-  uint32_t* mcp = reinterpret_cast<uint32_t*>(t.m) + (e0 >> 3);
-  uint32_t* vcp = reinterpret_cast<uint32_t*>(t.v) + (e0 >> 3);
-  f8 p = ldg_f8(t.p + e0);
-  const f8 g = ldg_f8(t.g + e0);
+                                              float qm_l, float qv_l, unsigned pf) {
+  float* pp = t.p + (size_t)gl * 128;
+  const float* gp = t.g + (size_t)gl * 128;
+  uint32_t* mcp = t.mc + (size_t)gl * 16;
+  uint32_t* vcp = t.vc + (size_t)gl * 16;
+  f8 p = ldg_f8(pp);
+  const f8 g = ldg_f8(gp);
   const uint32_t mc = *mcp;
   const uint32_t vc = *vcp;
   const float pm = __fmul_rn(qm_l, t.sm[gl]);  // lane i: qmap_m[i] * scale
   const float pv = __fmul_rn(qv_l, t.sv[gl]);
+  if (pf) {
+    prefetch_l2(pp + (size_t)pf * 128);
+    prefetch_l2(gp + (size_t)pf * 128);
+    prefetch_l2(mcp + (size_t)pf * 16);
+    prefetch_l2(vcp + (size_t)pf * 16);
+  }
 
   float m[8], v[8];
   float am = 0.0f, av = 0.0f;
@@ -160,24 +199,28 @@ __device__ __forceinline__ void group_q4_fast(const TDesc& t, long long gl, int 
     am = fmaxf(am, fabsf(m[k]));
     av = fmaxf(av, v[k]);
   }
+  stg_f8(pp, p);
   am = hw_max(am, hmask);
   av = hw_max(av, hmask);
-  if (!(udiv_ok(am) && udiv_ok(av))) {  // scales outside the shared-reciprocal domain: redo exactly
-    group_q4_generic(t, gl, l16, hmask, c, Sm, Sv);
-    return;
-  }
-  stg_f8(t.p + e0, p);
-  const float rm = __frcp_rn(am), rv = __frcp_rn(av);
   uint32_t mo = 0, vo = 0;
+  if (udiv_ok(am) && udiv_ok(av)) {
+    const float rm = rcp_nr(am), rv = rcp_nr(av);
 #pragma unroll
-  for (int k = 7; k >= 0; --k) {
-    const float xm = udiv(m[k], am, rm);
-    const float xv = udiv(v[k], av, rv);
-    mo = (mo << 4) + (uint32_t)lut_code(lut_m, xm);
-    if (VLIN) vo = vo * 16u + linear16_code_bits(xv);
-    else vo = (vo << 4) + (uint32_t)lut_code(lut_v, xv);
+    for (int k = 7; k >= 0; --k) {
+      const float xm = udiv(m[k], am, rm);
+      const float xv = udiv(v[k], av, rv);
+      mo = (mo << 4) + (uint32_t)lut_code(lut_m, xm);
+      if (VLIN) vo = vo * 16u + linear16_code(xv);
+      else vo = (vo << 4) + (uint32_t)lut_code(lut_v, xv);
+    }
+    if (am == 0.0f) mo = 0xFFFFFFFFu;          // 0/0 = NaN -> code 15 for the whole group
+    if (av == 0.0f) vo = 0xFFFFFFFFu;
+  } else {  // scales outside the shared-reciprocal domain
+    const uint2 o = quant8_exact(Sm, Sv, am, av, m[0], m[1], m[2], m[3], m[4], m[5], m[6], m[7], v[0], v[1], v[2],
+                                 v[3], v[4], v[5], v[6], v[7]);
+    mo = o.x;
+    vo = o.y;
   }
-  if (VLIN) vo -= 0x4B000000u * 0x11111111u;  // strip the 2^23 exponent pattern of every nibble
   *mcp = mo;
   *vcp = vo;
   if (l16 == 0) {
@@ -221,40 +264,50 @@ __device__ __forceinline__ void group_fp32(const TDesc& t, long long gl, int l16
   }
 }
 
+// The tensor loop is uniform across the CTA (descriptor fields come from the launch parameters
+// through uniform loads); each half-warp walks its own arithmetic progression of global group
+// indices gi = gbeg + id, gbeg + id + stride, ... through the tensors in order.
 template <bool FAST, bool VLIN>
 __device__ __forceinline__ void run_groups(const Table& tab, const Consts& c, const QMapSmem& Sm,
                                            const QMapSmem& Sv, const LutEnt* lut_m, const LutEnt* lut_v,
                                            bool tables_ok, long long gbeg, long long gend) {
-  const int hw = threadIdx.x >> 4;
   const int l16 = threadIdx.x & 15;
   const unsigned hmask = 0xFFFFu << (threadIdx.x & 16);
-  long long gi = gbeg + (long long)blockIdx.x * HW_PER_CTA + hw;
+  long long gi = gbeg + (long long)blockIdx.x * HW_PER_CTA + (threadIdx.x >> 4);
   const long long stride = (long long)gridDim.x * HW_PER_CTA;
-  if (gi >= gend) return;
   const float qm_l = Sm.qmap[l16], qv_l = Sv.qmap[l16];
-  // tensor holding group gi: last t with gstart <= gi
-  int lo = 0, hi = tab.n - 1;
-  while (lo < hi) {
-    const int mid = (lo + hi + 1) >> 1;
-    if (tab.t[mid].gstart <= gi) lo = mid;
-    else hi = mid - 1;
-  }
-  int ti = lo;
-  long long tend = (ti + 1 < tab.n) ? tab.t[ti + 1].gstart : tab.gtotal;
-  for (; gi < gend; gi += stride) {
-    while (gi >= tend) {
-      ++ti;
-      tend = (ti + 1 < tab.n) ? tab.t[ti + 1].gstart : tab.gtotal;
-    }
+  int ti = 0;
+  while (ti + 1 < tab.n && tab.t[ti + 1].gstart <= gbeg) ++ti;
+  for (; ti < tab.n; ++ti) {
     const TDesc& t = tab.t[ti];
-    const long long gl = gi - t.gstart;
+    const long long tstart = t.gstart;
+    if (tstart >= gend) break;
+    long long tend = (ti + 1 < tab.n) ? tab.t[ti + 1].gstart : tab.gtotal;
+    if (tend > gend) tend = gend;
     if (t.kind == LPMM_B200_KIND_Q4) {
-      if (tables_ok && t.aligned && (gl + 1) * 128 <= t.numel)
-        group_q4_fast<FAST, VLIN>(t, gl, l16, hmask, c, Sm, Sv, lut_m, lut_v, qm_l, qv_l);
-      else
-        group_q4_generic(t, gl, l16, hmask, c, Sm, Sv);
+      if (tables_ok && t.aligned) {
+        long long fend = tstart + t.numel / 128;  // end of the full groups
+        if (fend > tend) fend = tend;
+        if (gi < fend) {
+          LanePtrs lp;
+          lp.p = t.p + l16 * 8;
+          lp.g = t.g + l16 * 8;
+          lp.mc = reinterpret_cast<uint32_t*>(t.m) + l16;
+          lp.vc = reinterpret_cast<uint32_t*>(t.v) + l16;
+          lp.sm = t.sm;
+          lp.sv = t.sv;
+          unsigned gl = (unsigned)(gi - tstart);           // groups per tensor fit 32 bits (host-checked)
+          const unsigned lim = (unsigned)(fend - tstart);
+          const unsigned st = (unsigned)stride;
+          for (; gl < lim; gl += st)
+            group_q4_fast<FAST, VLIN>(lp, gl, l16, hmask, c, Sm, Sv, lut_m, lut_v, qm_l, qv_l,
+                                      (gl + st < lim) ? st : 0u);
+          gi = tstart + gl;
+        }
+      }
+      for (; gi < tend; gi += stride) group_q4_generic(t, gi - tstart, l16, hmask, c, Sm, Sv);
     } else {
-      group_fp32<FAST>(t, gl, l16, c);
+      for (; gi < tend; gi += stride) group_fp32<FAST>(t, gi - tstart, l16, c);
     }
   }
 }
@@ -388,6 +441,7 @@ static int check_list(const lpmm_b200_tensor* ts, int n, bool need_qmaps, const 
   for (int i = 0; i < n; ++i) {
     const lpmm_b200_tensor& s = ts[i];
     if (s.numel < 0) return LPMM_B200_ERR_BAD_SIZE;
+    if (s.numel > (int64_t)1 << 37) return LPMM_B200_ERR_TOO_LARGE;  // 32-bit group index per tensor
     if (s.kind != LPMM_B200_KIND_Q4 && s.kind != LPMM_B200_KIND_FP32) return LPMM_B200_ERR_BAD_KIND;
     if (s.numel == 0) continue;
     if (!s.p || !s.g || !s.m || !s.v) return LPMM_B200_ERR_NULL_POINTER;

@@ -39,8 +39,7 @@ __device__ __forceinline__ f8 ldg_f8(const float* ptr) {
 
 __device__ __forceinline__ void stg_f8(float* ptr, const f8& r) {
   asm volatile("st.global.v8.f32 [%8], {%0,%1,%2,%3,%4,%5,%6,%7};" ::"f"(r.x[0]), "f"(r.x[1]), "f"(r.x[2]),
-               "f"(r.x[3]), "f"(r.x[4]), "f"(r.x[5]), "f"(r.x[6]), "f"(r.x[7]), "l"(ptr)
-               : "memory");
+               "f"(r.x[3]), "f"(r.x[4]), "f"(r.x[5]), "f"(r.x[6]), "f"(r.x[7]), "l"(ptr));
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -126,15 +125,13 @@ __device__ __forceinline__ int lut_code(const LutEnt* __restrict__ ent, float x)
 }
 
 // Closed form of the rule for the map q[i] = (i+1)/16 (midpoints (2k+1)/32, k = 1..15):
-// code = clamp(ceil(16x - 1.5), 0, 15), NaN -> 15.  16x - 1.5 is exact whenever it is positive,
-// and adding 2^23 with round-up leaves ceil() in the low mantissa bits.  Returns the float's bit
-// pattern 0x4B000000 + code; callers strip the constant.  Checked against the rule for every
-// bit pattern with |x| <= 1e30 and every positive NaN.
-__device__ __forceinline__ uint32_t linear16_code_bits(float x) {
-  float t = __fmaf_rn(x, 16.0f, -1.5f);
-  t = fminf(t, 15.0f);  // NaN -> 15
-  t = fmaxf(t, 0.0f);
-  return __float_as_uint(__fadd_ru(t, 8388608.0f));
+// code = clamp(ceil(16x - 1.5), 0, 15).  16x - 1.5 is exact whenever it is positive, and the
+// float->unsigned conversion with round-up saturates negatives to 0.  Valid for x <= 1 (always
+// true of a value divided by its group maximum); NaN gives 0 here, so the caller handles the only
+// NaN source, an all-zero group, itself.  Checked against the rule for every bit pattern in
+// [-1e30, 1].
+__device__ __forceinline__ uint32_t linear16_code(float x) {
+  return __float2uint_ru(__fmaf_rn(x, 16.0f, -1.5f));
 }
 
 // The reference's search, verbatim in behaviour, for maps the table cannot hold.
@@ -177,13 +174,19 @@ __device__ __forceinline__ float udiv(float x, float d, float r) {
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ float mufu_rsq(float x) {
   float y;
-  asm("rsqrt.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  asm("rsqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
 __device__ __forceinline__ float mufu_rcp(float x) {
   float y;
-  asm("rcp.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+// MUFU reciprocal refined once; the reciprocal both fma-corrected divisions below are built on.
+__device__ __forceinline__ float rcp_nr(float d) {
+  const float r = mufu_rcp(d);
+  return __fmaf_rn(r, __fmaf_rn(-d, r, 1.0f), r);
 }
 
 __device__ __forceinline__ float sqrt_rn_fast(float v) {
@@ -195,9 +198,7 @@ __device__ __forceinline__ float sqrt_rn_fast(float v) {
 }
 
 __device__ __forceinline__ float div_rn_fast(float m, float d) {
-  float r = mufu_rcp(d);
-  const float e = __fmaf_rn(-d, r, 1.0f);
-  r = __fmaf_rn(r, e, r);
+  const float r = rcp_nr(d);
   const float q = __fmul_rn(m, r);
   const float rem = __fmaf_rn(-d, q, m);
   return __fmaf_rn(rem, r, q);
