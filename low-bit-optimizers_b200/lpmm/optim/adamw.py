@@ -1,0 +1,194 @@
+"""4-bit AdamW (reference: lpmm/optim/adamw.py).
+
+Constructor, lazily created state, state names and layouts are those of the reference:
+
+* ``fused=True``  -- ``exp_avg`` / ``exp_avg_sq`` are ``int8[(numel + 1) // 2]`` packed codes with
+  ``float32[(numel + 127) // 128]`` scales in ``state['exp_avg_qstate']['overhead']['max1']``
+  (adamw.py:508-523).  The whole parameter list of a group is updated by ONE multi-tensor launch
+  instead of the reference's per-tensor loop (adamw.py:463-561).
+* ``fused=False`` -- codes in the padded 2048-row layout of ``vectorwise_quant`` with the
+  generated metadata (``max1`` or ``max_dims``, ``dim``, ``scaled_shape``, ``dtype``, ``stride``)
+  in ``overhead`` (adamw.py:425-434); each tensor is updated by one fused launch that reproduces
+  the reference's sequence of torch operations (adamw.py:369-422).
+* tensors with at most ``THRESHOLD`` (4096) elements, or overridden, keep fp32 moments.
+* ``factor_second_moment=True`` keeps fp32 row/column accumulators for every >=2-D tensor
+  (adamw.py:124-126, 579-627).
+"""
+from typing import Optional
+
+import torch
+
+from .. import _kernels
+from .optimizer import LowBitOptimizer
+
+__all__ = ["AdamW"]
+
+
+class AdamW(LowBitOptimizer):
+    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=1e-2, use_first_moment=True,
+                 factor_second_moment=False, qconfig=None, *, fused: Optional[bool] = False):
+        if not 0.0 <= lr:
+            raise ValueError("Invalid learning rate: {}".format(lr))
+        if not 0.0 <= eps:
+            raise ValueError("Invalid epsilon value: {}".format(eps))
+        if not 0.0 <= betas[0] < 1.0:
+            raise ValueError("Invalid beta parameter at index 0: {}".format(betas[0]))
+        if not 0.0 <= betas[1] < 1.0:
+            raise ValueError("Invalid beta parameter at index 1: {}".format(betas[1]))
+        if not 0.0 <= weight_decay:
+            raise ValueError("Invalid weight_decay value: {}".format(weight_decay))
+        defaults = dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, fused=fused,
+                        use_first_moment=use_first_moment, factor_second_moment=factor_second_moment)
+        super().__init__(params, defaults, qconfig)
+        self._lists = {}  # cached descriptor arrays of the multi-tensor step, per param group
+
+    def __setstate__(self, state):
+        super().__setstate__(state)
+        self._lists = {}
+        for group in self.param_groups:
+            group.setdefault("fused", None)
+        values = list(self.state.values())
+        if values and not torch.is_tensor(values[0]["step"]):
+            for s in values:
+                s["step"] = torch.tensor(float(s["step"]))
+
+    def get_subqconfig(self, optimizer_state_name):
+        if optimizer_state_name == "exp_avg":
+            return self.qconfig.QUANT.M
+        if optimizer_state_name == "exp_avg_sq":
+            return self.qconfig.QUANT.SQM
+        raise ValueError(f"unknown optimizer state {optimizer_state_name!r}")
+
+    @staticmethod
+    def _get_options(param_group, param_shape):
+        return len(param_shape) >= 2 and param_group["factor_second_moment"], param_group["use_first_moment"]
+
+    def _init_state(self, group, p):
+        """Lazy state of one parameter (reference adamw.py:116-129): a CPU step counter, 0-dim
+        placeholders for the moments (their first use allocates the real storage) and the qstates."""
+        state = self.state[p]
+        factored, _ = self._get_options(group, p.shape)
+        state["step"] = torch.tensor(0.0)
+        state["exp_avg"] = torch.zeros((), dtype=torch.float, device=p.device)
+        self.init_qstate(p, "exp_avg")
+        if factored:
+            state["exp_avg_sq_row"] = torch.zeros(p.shape[:-1], device=p.device)
+            state["exp_avg_sq_col"] = torch.zeros(p.shape[:-2] + p.shape[-1:], device=p.device)
+        else:
+            state["exp_avg_sq"] = torch.zeros((), dtype=torch.float, device=p.device)
+        self.init_qstate(p, "exp_avg_sq")
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        for gi, group in enumerate(self.param_groups):
+            params = []
+            for p in group["params"]:
+                if p.grad is None:
+                    continue
+                if p.grad.is_sparse:
+                    raise RuntimeError("AdamW does not support sparse gradients")
+                if len(self.state[p]) == 0:
+                    self._init_state(group, p)
+                params.append(p)
+            if not params:
+                continue
+            if group["fused"]:
+                self._step_fused(gi, group, params)
+            else:
+                self._step_single(group, params)
+        return loss
+
+    # ---- fused=True ---------------------------------------------------------------------------
+    def _step_fused(self, gi, group, params):
+        beta1, beta2 = group["betas"]
+        md_m = self.get_qmetadata_by_state_name("exp_avg")
+        md_v = self.get_qmetadata_by_state_name("exp_avg_sq")
+        by_step = {}
+        warned = False
+        for p in params:
+            state = self.state[p]
+            factored, _ = self._get_options(group, p.shape)
+            state["step"] += 1
+            if factored:  # the fused kernel does not cover factored tensors (reference adamw.py:472-495)
+                self._factored_update(group, p, state)
+                continue
+            en_m, en_v = self._q_enabled(p, "exp_avg"), self._q_enabled(p, "exp_avg_sq")
+            if en_m != en_v:
+                raise ValueError("For same tensor, exp_avg and exp_avg_sq should be both quantized or unquantized "
+                                 f"simultaneously, but get ({en_m} {en_v})")
+            if en_m:
+                if not warned and (md_m["scale_type"] != "group" or md_v["scale_type"] != "group"):
+                    print("Warning: fused_adamw4bit only support block-wise scaling, but get scale types "
+                          f"({md_m['scale_type']}, {md_v['scale_type']}).")
+                    warned = True
+                n = p.numel()
+                if state["exp_avg"].numel() <= 1:
+                    state["exp_avg"].data = torch.zeros(((n + 1) // 2,), dtype=torch.int8, device=p.device)
+                if state["exp_avg_sq"].numel() <= 1:
+                    state["exp_avg_sq"].data = torch.zeros(((n + 1) // 2,), dtype=torch.int8, device=p.device)
+                oh_m, oh_v = state["exp_avg_qstate"]["overhead"], state["exp_avg_sq_qstate"]["overhead"]
+                if "max1" not in oh_m:
+                    oh_m["max1"] = torch.zeros(((n + 127) // 128,), dtype=torch.float32, device=p.device)
+                if "max1" not in oh_v:
+                    oh_v["max1"] = torch.zeros(((n + 127) // 128,), dtype=torch.float32, device=p.device)
+                entry = (p, p.grad, state["exp_avg"], state["exp_avg_sq"], oh_m["max1"], oh_v["max1"])
+            else:
+                if state["exp_avg"].numel() <= 1:
+                    state["exp_avg"].data = torch.zeros_like(p, memory_format=torch.preserve_format)
+                if state["exp_avg_sq"].numel() <= 1:
+                    state["exp_avg_sq"].data = torch.zeros_like(p, memory_format=torch.preserve_format)
+                entry = (p, p.grad, state["exp_avg"], state["exp_avg_sq"], None, None)
+            for t, nm in zip(entry[:4], ("p", "g", "exp_avg", "exp_avg_sq")):
+                if not t.is_contiguous():
+                    raise RuntimeError(f"{nm} must be contiguous!")
+                if not t.is_cuda:
+                    raise RuntimeError(f"{nm} must be a CUDA tensor!")
+            if p.dtype != torch.float32 or p.grad.dtype != torch.float32:
+                raise RuntimeError("The type of p / g is not kFloat32!")
+            key = (float(state["step"].item()), p.device)
+            by_step.setdefault(key, []).append((entry, state))
+        for (step, device), items in by_step.items():
+            entries = [e for e, _ in items]
+            qm = items[0][1]["exp_avg_qstate"]["qmap"]
+            qv = items[0][1]["exp_avg_sq_qstate"]["qmap"]
+            tl = self._tensor_list((gi, step if len(by_step) > 1 else None, device), entries)
+            with torch.cuda.device(device):
+                _kernels.adamw4bit_multi_tensor(tl, qm, qv, beta1, beta2, group["lr"], group["weight_decay"],
+                                                group["eps"], step)
+
+    def _tensor_list(self, key, entries):
+        """Descriptor array of a parameter list, rebuilt only when a pointer changed."""
+        sig = tuple(t.data_ptr() if t is not None else 0 for e in entries for t in e)
+        cached = self._lists.get(key)
+        if cached is None or cached[0] != sig:
+            cached = (sig, _kernels.TensorList(entries))
+            self._lists[key] = cached
+        return cached[1]
+
+    # ---- fused=False --------------------------------------------------------------------------
+    def _step_single(self, group, params):
+        beta1, beta2 = group["betas"]
+        md_m = self.get_qmetadata_by_state_name("exp_avg")
+        md_v = self.get_qmetadata_by_state_name("exp_avg_sq")
+        for p in params:
+            state = self.state[p]
+            factored, _ = self._get_options(group, p.shape)
+            state["step"] += 1
+            if factored:
+                self._factored_update(group, p, state)
+                continue
+            _kernels.adamw4bit_unfused_step(
+                p, p.grad, state, self._q_enabled(p, "exp_avg"), self._q_enabled(p, "exp_avg_sq"), md_m, md_v,
+                beta1=beta1, beta2=beta2, lr=group["lr"], weight_decay=group["weight_decay"], eps=group["eps"],
+                step=state["step"].item())
+
+    def _factored_update(self, group, p, state):
+        beta1, beta2 = group["betas"]
+        _kernels.adamw4bit_factored_step(
+            p, p.grad, state, self._q_enabled(p, "exp_avg"), self.get_qmetadata_by_state_name("exp_avg"),
+            beta1=beta1, beta2=beta2, lr=group["lr"], weight_decay=group["weight_decay"], eps=group["eps"],
+            step=state["step"].item())
