@@ -114,6 +114,100 @@ int64_t lpmm_b200_count_groups(const lpmm_b200_tensor* tensors, int n_tensors);
  * CPU model the device's own powf result. */
 int lpmm_b200_bias_corrections(float beta1, float beta2, float step, float* out, void* stream);
 
+/* ------------------------------------------------------------------------------------------- */
+/* Standalone quantize / dequantize (the kernels behind lpmm.functional)                        */
+/* ------------------------------------------------------------------------------------------- */
+
+/* Bytes of the packed-code tensor the reference allocates for n_scaled normalised values:
+ * rows of 2048 values, two codes per byte, plus one trailing byte
+ * (lpmm/functional.py:362; lpmm/cpp_extension/quantization_kernel.cu:475-477). */
+int64_t lpmm_b200_packed_len(int64_t n_scaled);
+
+/* Replaces quantization.pack_nonlinear(data[G, S], qmap, 4, False)
+ * (lpmm/cpp_extension/quantization.cc:54-63 -> quantization_kernel.cu:430-513).  n = G*S values,
+ * n even; packed holds n/2 + 1 bytes, the last one (never written by the reference) is set to 0.
+ * Only the 4-bit round-to-nearest form is built. */
+int lpmm_b200_pack_nonlinear4(const float* data, int64_t n, const float* qmap, int8_t* packed, void* stream);
+
+/* Replaces quantization.unpack_nonlinear(packed, qmap, 4, G, S)
+ * (lpmm/cpp_extension/quantization.cc:65-76 -> quantization_kernel.cu:604-653): out[i] = qmap[code_i]
+ * for i < n = G*S, n even. */
+int lpmm_b200_unpack_nonlinear4(const int8_t* packed, const float* qmap, int64_t n, float* out, void* stream);
+
+/* Group-128 quantization of a flattened tensor: what vectorwise_quant does for scale_type
+ * 'group' with gp_sz 128, and for 'rank1' on 1-D tensors (lpmm/functional.py:26-59, 184-197,
+ * 359-369).  max1 receives ceil(numel/128) group maxima of |x|; codes receives
+ * lpmm_b200_packed_len(ceil(numel/128)*128) bytes (zero padding quantized as the reference's
+ * padded zeros are). */
+int lpmm_b200_quant_group4(const float* x, int64_t numel, const float* qmap, int8_t* codes, float* max1, void* stream);
+
+/* Inverse (vectorwise_dequant, lpmm/functional.py:62-151, group branch): out[i] = qmap[code_i] *
+ * max1[i / 128], i < numel. */
+int lpmm_b200_dequant_group4(const int8_t* codes, const float* qmap, const float* max1, int64_t numel, float* out,
+                             void* stream);
+
+/* Per-axis maxima of |x| of a contiguous ndim-D tensor (ndim <= 8): max_dims[i] points to
+ * shape[i] floats and receives the maximum over all other axes (get_sm3_statistics,
+ * lpmm/functional.py:512-531).  shape and max_dims are HOST arrays. */
+int lpmm_b200_axis_absmax(const float* x, const int64_t* shape, int ndim, float* const* max_dims, void* stream);
+
+/* Rank-1 quantization (vectorwise_quant, scale_type 'rank1', ndim >= 2; functional.py:190-203):
+ * fills max_dims as above, then codes = rule(x / min_i max_dims[i][idx_i]) in the packed layout
+ * of lpmm_b200_packed_len(numel) bytes. */
+int lpmm_b200_quant_rank1_4(const float* x, const int64_t* shape, int ndim, const float* qmap,
+                            float* const* max_dims, int8_t* codes, void* stream);
+
+/* Inverse (vectorwise_dequant, rank1 branch, functional.py:97-106). */
+int lpmm_b200_dequant_rank1_4(const int8_t* codes, const float* qmap, const float* const* max_dims,
+                              const int64_t* shape, int ndim, float* out, void* stream);
+
+/* ------------------------------------------------------------------------------------------- */
+/* One-launch-per-tensor steps with the arithmetic of the reference's non-fused Python path     */
+/* ------------------------------------------------------------------------------------------- */
+
+#define LPMM_B200_STATE_FP32 0    /* float[numel]                                               */
+#define LPMM_B200_STATE_GROUP4 1  /* 4-bit codes, group-128 scales, vectorwise_quant layout     */
+#define LPMM_B200_STATE_RANK1_4 2 /* 4-bit codes, per-axis maxima (ndim >= 2)                   */
+#define LPMM_B200_STATE_FACTORED 3/* fp32 row / column accumulators (ndim >= 2), no codes       */
+
+typedef struct lpmm_b200_step_tensor {
+  float* p;
+  const float* g;
+  int64_t numel;
+  int32_t ndim;                 /* <= 8; needed for RANK1_4 and FACTORED, else may be 1        */
+  int32_t first;                /* nonzero: the moments are not initialised yet, read as zero   */
+  int64_t shape[8];
+  int32_t m_mode;               /* FP32 or GROUP4                                               */
+  int32_t v_mode;               /* any LPMM_B200_STATE_*                                        */
+  void* m;                      /* float[numel] or int8[packed_len]                             */
+  float* m_max1;                /* GROUP4: float[ceil(numel/128)]                               */
+  void* v;                      /* float[numel] or int8[packed_len]; unused when FACTORED       */
+  float* v_max1;                /* GROUP4: float[ceil(numel/128)]                               */
+  const float* v_max_dims_old[8]; /* RANK1_4: maxima the current codes were normalised with     */
+  float* v_max_dims_new[8];       /* RANK1_4: receives the maxima of the updated second moment  */
+  float* row;                   /* FACTORED: float[prod(shape[:-1])]                            */
+  float* col;                   /* FACTORED: float[prod(shape[:-2]) * shape[-1]]                */
+} lpmm_b200_step_tensor;
+
+/* One AdamW step of one tensor with the arithmetic and state layout of the reference's
+ * non-fused path: _single_tensor_adamw4bit (lpmm/optim/adamw.py:332-436) for v_mode FP32 /
+ * GROUP4 / RANK1_4 and _single_quantized_factored_update (adamw.py:579-627, after the decay at
+ * :369/:478) for FACTORED.  Hyper-parameters arrive as the Python doubles the reference computes
+ * its scalar constants from.  FACTORED needs `scratch` (device memory, at least
+ * lpmm_b200_factored_scratch_bytes() bytes, contents irrelevant before and after); other modes
+ * ignore it. */
+int lpmm_b200_adamw4bit_unfused_step(const lpmm_b200_step_tensor* t, const float* qmap_m, const float* qmap_v,
+                                     double beta1, double beta2, double lr, double weight_decay, double eps,
+                                     double step, void* scratch, int64_t scratch_bytes, void* stream);
+int64_t lpmm_b200_factored_scratch_bytes(const int64_t* shape, int ndim);
+
+/* One momentum-SGD step of one tensor with the arithmetic of _single_tensor_sgd4bit
+ * (lpmm/optim/sgd.py:133-187).  buf_mode FP32 or GROUP4; first != 0: the buffer is created from
+ * the (decayed) gradient.  momentum == 0 ignores the buffer. */
+int lpmm_b200_sgd4bit_step(float* p, const float* g, int64_t numel, void* buf, float* buf_max1, int buf_mode,
+                           int first, const float* qmap, double weight_decay, double momentum, double lr,
+                           double dampening, int nesterov, int maximize, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -103,3 +103,278 @@ def adamw4bit_multi_tensor(tl, qmap_m, qmap_v, beta1, beta2, lr, weight_decay, e
     h = N.Hyper(beta1, beta2, lr, weight_decay, eps, step)
     N.check(N.lib.lpmm_b200_adamw4bit_multi_tensor(tl.array, tl.n, _ptr(qmap_m), _ptr(qmap_v), h, group_begin, group_end,
                                                    _stream()))
+
+
+# ----------------------------------------------------------------------------------------------
+# standalone quantize / dequantize
+# ----------------------------------------------------------------------------------------------
+def packed_len(n_scaled):
+    return (n_scaled + 2047) // 2048 * 1024 + 1
+
+
+def _i64_array(values):
+    return (ctypes.c_int64 * max(len(values), 1))(*values)
+
+
+def _ptr_array(tensors):
+    return (_vp * max(len(tensors), 1))(*[t.data_ptr() for t in tensors])
+
+
+def pack_nonlinear(data, qmap, bits, stochastic):
+    """``quantization.pack_nonlinear`` (reference quantization.cc:54-63)."""
+    if bits > 8:
+        raise RuntimeError("bits <= 8")
+    _check_cuda_float(data, "data")
+    _check_cuda_float(qmap, "qmap")
+    if data.dim() != 2 or qmap.dim() != 1:
+        raise RuntimeError("The dimension of data / qmap is not correct!")
+    if bits != 4 or stochastic:
+        raise NotImplementedError("only the 4-bit round-to-nearest pack is built in this implementation")
+    if data.shape[1] % 8 != 0:
+        raise RuntimeError("group_size % work_per_thread == 0")
+    n = data.numel()
+    out = torch.empty(n // 2 + 1, dtype=torch.int8, device=data.device)
+    with torch.cuda.device(data.device):
+        N.check(N.lib.lpmm_b200_pack_nonlinear4(_ptr(data), n, _ptr(qmap), _ptr(out), _stream()))
+    return out
+
+
+def unpack_nonlinear(data, qmap, bits, num_groups, group_size):
+    """``quantization.unpack_nonlinear`` (reference quantization.cc:65-76)."""
+    if bits > 8:
+        raise RuntimeError("bits <= 8")
+    _check_cuda_int8(data, "data")
+    _check_cuda_float(qmap, "qmap")
+    if data.dim() != 1 or qmap.dim() != 1:
+        raise RuntimeError("The dimension of data / qmap is not correct!")
+    if bits != 4:
+        raise NotImplementedError("only the 4-bit unpack is built in this implementation")
+    n = int(num_groups) * int(group_size)
+    if data.numel() < n // 2:
+        raise RuntimeError("packed tensor is too short for num_groups * group_size codes")
+    out = torch.empty((int(num_groups), int(group_size)), dtype=qmap.dtype, device=data.device)
+    with torch.cuda.device(data.device):
+        N.check(N.lib.lpmm_b200_unpack_nonlinear4(_ptr(data), _ptr(qmap), n, _ptr(out), _stream()))
+    return out
+
+
+def _qmap_on(qmap, device):
+    return qmap if qmap.device == device else qmap.to(device)
+
+
+def quant_group(x, qmap, gp_sz):
+    if gp_sz != 128:
+        raise NotImplementedError("only group size 128 is built in this implementation")
+    _check_cuda_float(x, "x")
+    n = x.numel()
+    groups = (n + 127) // 128
+    codes = torch.empty(packed_len(groups * 128), dtype=torch.int8, device=x.device)
+    max1 = torch.empty((groups, 1), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        N.check(N.lib.lpmm_b200_quant_group4(_ptr(x), n, _ptr(_qmap_on(qmap, x.device)), _ptr(codes), _ptr(max1), _stream()))
+    return codes, max1
+
+
+def dequant_group(codes, qmap, max1, numel, gp_sz):
+    if gp_sz != 128:
+        raise NotImplementedError("only group size 128 is built in this implementation")
+    _check_cuda_int8(codes, "qx")
+    out = torch.empty(numel, dtype=torch.float32, device=codes.device)
+    with torch.cuda.device(codes.device):
+        N.check(N.lib.lpmm_b200_dequant_group4(_ptr(codes), _ptr(_qmap_on(qmap, codes.device)), _ptr(max1), numel,
+                                               _ptr(out), _stream()))
+    return out
+
+
+def dequant_plain(codes, qmap, n):
+    _check_cuda_int8(codes, "qx")
+    n2 = (n + 1) // 2 * 2
+    out = torch.empty(n2, dtype=torch.float32, device=codes.device)
+    with torch.cuda.device(codes.device):
+        N.check(N.lib.lpmm_b200_unpack_nonlinear4(_ptr(codes), _ptr(_qmap_on(qmap, codes.device)), n2, _ptr(out), _stream()))
+    return out[:n]
+
+
+def _axis_vectors(shape, device):
+    nd = len(shape)
+    return [torch.empty([shape[i] if j == i else 1 for j in range(nd)], dtype=torch.float32, device=device)
+            for i in range(nd)]
+
+
+def axis_absmax(x):
+    _check_cuda_float(x, "x")
+    if x.dim() < 1 or x.dim() > 8:
+        raise NotImplementedError("1 to 8 dimensions")
+    vecs = _axis_vectors(tuple(x.shape), x.device)
+    with torch.cuda.device(x.device):
+        N.check(N.lib.lpmm_b200_axis_absmax(_ptr(x), _i64_array(list(x.shape)), x.dim(), _ptr_array(vecs), _stream()))
+    return vecs
+
+
+def quant_rank1(x, qmap):
+    _check_cuda_float(x, "x")
+    if x.dim() < 2 or x.dim() > 8:
+        raise NotImplementedError("2 to 8 dimensions")
+    vecs = _axis_vectors(tuple(x.shape), x.device)
+    codes = torch.empty(packed_len(x.numel()), dtype=torch.int8, device=x.device)
+    with torch.cuda.device(x.device):
+        N.check(N.lib.lpmm_b200_quant_rank1_4(_ptr(x), _i64_array(list(x.shape)), x.dim(),
+                                              _ptr(_qmap_on(qmap, x.device)), _ptr_array(vecs), _ptr(codes), _stream()))
+    return codes, vecs
+
+
+def dequant_rank1(codes, qmap, max_dims, shape):
+    _check_cuda_int8(codes, "qx")
+    out = torch.empty(tuple(shape), dtype=torch.float32, device=codes.device)
+    with torch.cuda.device(codes.device):
+        N.check(N.lib.lpmm_b200_dequant_rank1_4(_ptr(codes), _ptr(_qmap_on(qmap, codes.device)), _ptr_array(list(max_dims)),
+                                                _i64_array(list(shape)), len(shape), _ptr(out), _stream()))
+    return out
+
+
+# ----------------------------------------------------------------------------------------------
+# non-fused optimizer steps (one tensor per call)
+# ----------------------------------------------------------------------------------------------
+_scratch = {}
+
+
+def _scratch_for(device, nbytes):
+    buf = _scratch.get(device)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _scratch[device] = buf
+    return buf
+
+
+def _check_param_grad(p, g):
+    _check_cuda_float(p, "p")
+    _check_cuda_float(g, "g")
+    if g.numel() != p.numel():
+        raise RuntimeError("number of elements in g and p tensors should be equal")
+
+
+def _ensure_group_state(state, name, p, quantized):
+    """Allocate the storage of a group-scaled / fp32 state on first use; returns (tensor, max1, first)."""
+    t = state[name]
+    first = t.numel() <= 1  # the reference's test for "not initialised yet" (adamw.py:394)
+    oh = state[f"{name}_qstate"]["overhead"]
+    if quantized:
+        n = p.numel()
+        groups = (n + 127) // 128
+        if first or t.dtype != torch.int8:
+            t.data = torch.empty(packed_len(groups * 128), dtype=torch.int8, device=p.device)
+        if not isinstance(oh.get("max1"), torch.Tensor) or oh["max1"].numel() != groups:
+            oh["max1"] = torch.empty((groups, 1), dtype=torch.float32, device=p.device)
+        oh["dtype"], oh["stride"] = p.dtype, p.stride()
+        oh["scaled_shape"] = torch.Size([groups, 128])
+        return t, oh["max1"], first
+    if first:
+        t.data = torch.zeros_like(p, memory_format=torch.preserve_format)
+    return t, None, first
+
+
+def adamw4bit_unfused_step(p, g, state, m_quant, v_quant, md_m, md_v, spare, *, beta1, beta2, lr, weight_decay, eps,
+                           step):
+    """``spare`` is a dict owned by the optimizer (not part of its state) that keeps the second set
+    of per-axis maxima a rank-1 tensor alternates with."""
+    _check_param_grad(p, g)
+    for md, q in ((md_m, m_quant), (md_v, v_quant)):
+        if q and (md["b"] != 4 or md["round_type"] != "real-nearest" or md["gp_sz"] != 128):
+            raise NotImplementedError("only 4-bit, real-nearest, group size 128 is built in this implementation")
+    if m_quant and md_m["scale_type"] != "group":
+        raise NotImplementedError("first moment: only scale_type 'group' is built in this implementation")
+    if v_quant and md_v["scale_type"] not in ("group", "rank1"):
+        raise NotImplementedError("second moment: only scale_type 'group' / 'rank1' is built in this implementation")
+    t = N.StepTensor()
+    t.p, t.g, t.numel, t.ndim = p.data_ptr(), g.data_ptr(), p.numel(), max(p.dim(), 1)
+    for i, d in enumerate(p.shape):
+        t.shape[i] = d
+    m, m_max1, first_m = _ensure_group_state(state, "exp_avg", p, m_quant)
+    t.m_mode = N.STATE_GROUP4 if m_quant else N.STATE_FP32
+    t.m, t.m_max1 = m.data_ptr(), (m_max1.data_ptr() if m_max1 is not None else None)
+    rank1 = v_quant and md_v["scale_type"] == "rank1" and p.dim() >= 2
+    oh_v = state["exp_avg_sq_qstate"]["overhead"]
+    if rank1:
+        v = state["exp_avg_sq"]
+        first_v = v.numel() <= 1
+        if first_v:
+            v.data = torch.empty(packed_len(p.numel()), dtype=torch.int8, device=p.device)
+            oh_v["max_dims"] = _axis_vectors(tuple(p.shape), p.device)
+        if "max_dims" not in spare or spare["max_dims"][0].device != p.device:
+            spare["max_dims"] = _axis_vectors(tuple(p.shape), p.device)
+        old, new = oh_v["max_dims"], spare["max_dims"]
+        for i in range(p.dim()):
+            t.v_max_dims_old[i] = old[i].data_ptr()
+            t.v_max_dims_new[i] = new[i].data_ptr()
+        t.v_mode, t.v = N.STATE_RANK1_4, v.data_ptr()
+        oh_v["max_dims"], spare["max_dims"] = new, list(old)
+        oh_v.update(dim=p.dim(), max1=None, scaled_shape=p.shape, dtype=p.dtype, stride=p.stride())
+    else:
+        v, v_max1, first_v = _ensure_group_state(state, "exp_avg_sq", p, v_quant)
+        if v_quant and md_v["scale_type"] == "rank1":
+            oh_v["dim"] = p.dim()
+        t.v_mode = N.STATE_GROUP4 if v_quant else N.STATE_FP32
+        t.v, t.v_max1 = v.data_ptr(), (v_max1.data_ptr() if v_max1 is not None else None)
+    if first_m != first_v:
+        raise RuntimeError("exp_avg and exp_avg_sq must be initialised together")
+    t.first = int(first_m)
+    qm = state["exp_avg_qstate"]["qmap"]
+    qv = state["exp_avg_sq_qstate"]["qmap"]
+    with torch.cuda.device(p.device):
+        N.check(N.lib.lpmm_b200_adamw4bit_unfused_step(ctypes.byref(t), _ptr(qm), _ptr(qv), beta1, beta2, lr,
+                                                       weight_decay, eps, step, None, 0, _stream()))
+
+
+def adamw4bit_factored_step(p, g, state, m_quant, md_m, *, beta1, beta2, lr, weight_decay, eps, step):
+    _check_param_grad(p, g)
+    if m_quant and (md_m["b"] != 4 or md_m["round_type"] != "real-nearest" or md_m["gp_sz"] != 128
+                    or md_m["scale_type"] != "group"):
+        raise NotImplementedError("only 4-bit, real-nearest, group-128 first moments are built in this implementation")
+    t = N.StepTensor()
+    t.p, t.g, t.numel, t.ndim = p.data_ptr(), g.data_ptr(), p.numel(), p.dim()
+    for i, d in enumerate(p.shape):
+        t.shape[i] = d
+    m, m_max1, first = _ensure_group_state(state, "exp_avg", p, m_quant)
+    t.m_mode = N.STATE_GROUP4 if m_quant else N.STATE_FP32
+    t.m, t.m_max1 = m.data_ptr(), (m_max1.data_ptr() if m_max1 is not None else None)
+    t.v_mode = N.STATE_FACTORED
+    row, col = state["exp_avg_sq_row"], state["exp_avg_sq_col"]
+    _check_cuda_float(row, "exp_avg_sq_row")
+    _check_cuda_float(col, "exp_avg_sq_col")
+    t.row, t.col, t.first = row.data_ptr(), col.data_ptr(), int(first)
+    shape = _i64_array(list(p.shape))
+    need = int(N.lib.lpmm_b200_factored_scratch_bytes(shape, p.dim()))
+    scratch = _scratch_for(p.device, need)
+    qm = state["exp_avg_qstate"]["qmap"]
+    with torch.cuda.device(p.device):
+        N.check(N.lib.lpmm_b200_adamw4bit_unfused_step(ctypes.byref(t), _ptr(qm), None, beta1, beta2, lr, weight_decay,
+                                                       eps, step, _ptr(scratch), scratch.numel(), _stream()))
+
+
+def sgd4bit_step(p, g, state, quant, md, *, weight_decay, momentum, lr, dampening, nesterov, maximize):
+    _check_param_grad(p, g)
+    if quant and (md["b"] != 4 or md["round_type"] != "real-nearest" or md["gp_sz"] != 128
+                  or md["scale_type"] != "group"):
+        raise NotImplementedError("only 4-bit, real-nearest, group-128 momentum buffers are built in this implementation")
+    buf = buf_max1 = None
+    first = False
+    if momentum != 0:
+        b = state["momentum_buffer"]
+        first = b.numel() <= 1
+        oh = state["momentum_buffer_qstate"]["overhead"]
+        if quant:
+            groups = (p.numel() + 127) // 128
+            if first:
+                b.data = torch.empty(packed_len(groups * 128), dtype=torch.int8, device=p.device)
+                oh["max1"] = torch.empty((groups, 1), dtype=torch.float32, device=p.device)
+            oh.update(dtype=p.dtype, stride=p.stride(), scaled_shape=torch.Size([groups, 128]))
+            buf_max1 = oh["max1"]
+        elif first:
+            b.data = torch.empty_like(p, memory_format=torch.preserve_format)
+        buf = b
+    qmap = state["momentum_buffer_qstate"]["qmap"]
+    with torch.cuda.device(p.device):
+        N.check(N.lib.lpmm_b200_sgd4bit_step(_ptr(p), _ptr(g), p.numel(), _ptr(buf), _ptr(buf_max1),
+                                             N.STATE_GROUP4 if quant else N.STATE_FP32, int(first), _ptr(qmap),
+                                             weight_decay, momentum, lr, dampening, int(bool(nesterov)),
+                                             int(bool(maximize)), _stream()))

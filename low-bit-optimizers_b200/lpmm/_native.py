@@ -32,6 +32,29 @@ class Hyper(ctypes.Structure):
     _fields_ = [(n, ctypes.c_float) for n in ("beta1", "beta2", "lr", "weight_decay", "eps", "step")]
 
 
+class StepTensor(ctypes.Structure):
+    """``lpmm_b200_step_tensor``"""
+    _fields_ = [
+        ("p", ctypes.c_void_p),
+        ("g", ctypes.c_void_p),
+        ("numel", ctypes.c_int64),
+        ("ndim", ctypes.c_int32),
+        ("first", ctypes.c_int32),
+        ("shape", ctypes.c_int64 * 8),
+        ("m_mode", ctypes.c_int32),
+        ("v_mode", ctypes.c_int32),
+        ("m", ctypes.c_void_p),
+        ("m_max1", ctypes.c_void_p),
+        ("v", ctypes.c_void_p),
+        ("v_max1", ctypes.c_void_p),
+        ("v_max_dims_old", ctypes.c_void_p * 8),
+        ("v_max_dims_new", ctypes.c_void_p * 8),
+        ("row", ctypes.c_void_p),
+        ("col", ctypes.c_void_p),
+    ]
+
+
+STATE_FP32, STATE_GROUP4, STATE_RANK1_4, STATE_FACTORED = 0, 1, 2, 3
 KIND_Q4 = 0
 KIND_FP32 = 1
 GROUP = 128
@@ -48,7 +71,7 @@ def _load():
             f"{_LIB_PATH} is missing: build it with `python low-bit-optimizers_b200/build.py` "
             "(needs nvcc; there is no non-CUDA implementation)")
     lib = ctypes.CDLL(_LIB_PATH)
-    f, i64, i32, vp = ctypes.c_float, ctypes.c_int64, ctypes.c_int, ctypes.c_void_p
+    f, i64, i32, vp, d = ctypes.c_float, ctypes.c_int64, ctypes.c_int, ctypes.c_void_p, ctypes.c_double
     sigs = {
         "lpmm_b200_strerror": (ctypes.c_char_p, [i32]),
         "lpmm_b200_last_cuda_error": (ctypes.c_char_p, []),
@@ -58,6 +81,17 @@ def _load():
         "lpmm_b200_adamw4bit_multi_tensor": (i32, [ctypes.POINTER(Tensor), i32, vp, vp, Hyper, i64, i64, vp]),
         "lpmm_b200_count_groups": (i64, [ctypes.POINTER(Tensor), i32]),
         "lpmm_b200_bias_corrections": (i32, [f, f, f, vp, vp]),
+        "lpmm_b200_packed_len": (i64, [i64]),
+        "lpmm_b200_pack_nonlinear4": (i32, [vp, i64, vp, vp, vp]),
+        "lpmm_b200_unpack_nonlinear4": (i32, [vp, vp, i64, vp, vp]),
+        "lpmm_b200_quant_group4": (i32, [vp, i64, vp, vp, vp, vp]),
+        "lpmm_b200_dequant_group4": (i32, [vp, vp, vp, i64, vp, vp]),
+        "lpmm_b200_axis_absmax": (i32, [vp, ctypes.POINTER(i64), i32, ctypes.POINTER(vp), vp]),
+        "lpmm_b200_quant_rank1_4": (i32, [vp, ctypes.POINTER(i64), i32, vp, ctypes.POINTER(vp), vp, vp]),
+        "lpmm_b200_dequant_rank1_4": (i32, [vp, vp, ctypes.POINTER(vp), ctypes.POINTER(i64), i32, vp, vp]),
+        "lpmm_b200_adamw4bit_unfused_step": (i32, [ctypes.POINTER(StepTensor), vp, vp] + [d] * 6 + [vp, i64, vp]),
+        "lpmm_b200_factored_scratch_bytes": (i64, [ctypes.POINTER(i64), i32]),
+        "lpmm_b200_sgd4bit_step": (i32, [vp, vp, i64, vp, vp, i32, i32, vp, d, d, d, d, i32, i32, vp]),
     }
     for name, (res, args) in sigs.items():
         fn = getattr(lib, name)

@@ -41,10 +41,12 @@ class AdamW(LowBitOptimizer):
                         use_first_moment=use_first_moment, factor_second_moment=factor_second_moment)
         super().__init__(params, defaults, qconfig)
         self._lists = {}  # cached descriptor arrays of the multi-tensor step, per param group
+        self._spare = {}  # per-parameter buffers that are not optimizer state (alternate rank-1 maxima)
 
     def __setstate__(self, state):
         super().__setstate__(state)
         self._lists = {}
+        self._spare = {}
         for group in self.param_groups:
             group.setdefault("fused", None)
         values = list(self.state.values())
@@ -183,6 +185,7 @@ class AdamW(LowBitOptimizer):
                 continue
             _kernels.adamw4bit_unfused_step(
                 p, p.grad, state, self._q_enabled(p, "exp_avg"), self._q_enabled(p, "exp_avg_sq"), md_m, md_v,
+                self._spare.setdefault(id(p), {}),
                 beta1=beta1, beta2=beta2, lr=group["lr"], weight_decay=group["weight_decay"], eps=group["eps"],
                 step=state["step"].item())
 

@@ -1,0 +1,249 @@
+"""Fused 4-bit AdamW kernel through the C ABI, on a B200, against (a) the reference's own compiled
+kernels when ``oracle/_ref`` is present and (b) the C oracle.  Integer outputs (codes) and the
+fp32 scales and parameters are all required to be bit-identical."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from gpu_helpers import (HYPER, bits_equal, device, device_qmaps, fused_state, load_reference_extension, stream,
+                         student_t, vp)
+
+pytestmark = pytest.mark.gpu
+
+
+def _lib():
+    from lpmm import _native as N
+    return N
+
+
+def mine_step(N, p, g, st, qm, qv, step, h=HYPER):
+    N.check(N.lib.lpmm_b200_adamw4bit_single_tensor(vp(p), vp(g), vp(st[0]), vp(st[1]), vp(st[2]), vp(st[3]), vp(qm),
+                                                    vp(qv), h["beta1"], h["beta2"], h["lr"], h["weight_decay"],
+                                                    h["eps"], float(step), p.numel(), stream()))
+
+
+def ref_step(ref, p, g, st, qm, qv, step, h=HYPER):
+    ref.adamw4bit_single_tensor(p, g, st[0], st[1], st[2], st[3], qm, qv, h["beta1"], h["beta2"], h["lr"],
+                                h["weight_decay"], h["eps"], float(step))
+
+
+def assert_same(p_a, st_a, p_b, st_b, what):
+    assert torch.equal(st_a[0], st_b[0]), f"{what}: first-moment codes differ"
+    assert torch.equal(st_a[1], st_b[1]), f"{what}: second-moment codes differ"
+    assert bits_equal(st_a[2], st_b[2]), f"{what}: first-moment scales differ"
+    assert bits_equal(st_a[3], st_b[3]), f"{what}: second-moment scales differ"
+    assert bits_equal(p_a, p_b), f"{what}: parameters differ"
+
+
+def _grad_cases():
+    def zero_groups(n):
+        def f(s):
+            g = student_t((n,), 10 + s)
+            g[: 128 * 5] = 0
+            if s % 2:
+                g[128 * 7: 128 * 9] = 0
+            return g
+        return f
+
+    def mixed(n):
+        def f(s):
+            g = student_t((n,), 40 + s)
+            sc = torch.ones(n // 128, device=device())
+            sc[::3] = 1e-25
+            sc[1::7] = 1e18
+            sc[5::11] = 0
+            return (g.view(-1, 128) * sc[:, None]).reshape(-1).contiguous()
+        return f
+
+    return [
+        ("matrix_4096x4096", 4096 * 4096, 5, lambda s: student_t((4096, 4096), s).view(-1), {}),
+        ("ragged_even", 128 * 37 + 70, 5, lambda s: student_t((128 * 37 + 70,), s), {}),
+        ("tiny_6", 6, 3, lambda s: student_t((6,), s), {}),
+        ("zero_groups", 128 * 64, 6, zero_groups(128 * 64), {}),
+        ("tiny_grads", 128 * 64, 4, lambda s: student_t((128 * 64,), 20 + s, scale=1e-31), {}),
+        ("huge_grads", 128 * 64, 4, lambda s: student_t((128 * 64,), 30 + s, scale=1e19), {}),
+        ("mixed_scales", 128 * 256, 5, mixed(128 * 256), {}),
+        ("eps_tiny", 128 * 100, 4, lambda s: student_t((128 * 100,), 50 + s), dict(eps=1e-20)),
+        ("eps_zero", 128 * 100, 3, lambda s: student_t((128 * 100,), 60 + s), dict(eps=0.0)),
+        ("other_betas", 128 * 100, 4, lambda s: student_t((128 * 100,), 70 + s),
+         dict(beta1=0.5, beta2=0.9, weight_decay=0.0, lr=3e-2)),
+    ]
+
+
+@pytest.mark.parametrize("case", _grad_cases(), ids=lambda c: c[0])
+def test_fused_matches_reference_kernels(qmaps, case):
+    ref = load_reference_extension("fused_adamw")
+    if ref is None:
+        pytest.skip("oracle/_ref was not built (needs the reference checkout at build time)")
+    N = _lib()
+    name, n, steps, gfn, hov = case
+    h = dict(HYPER, **hov)
+    qm, qv, _ = device_qmaps(qmaps)
+    torch.manual_seed(n % 1000)
+    p_ref = torch.randn(n, device=device()) * 0.02
+    p_my = p_ref.clone()
+    st_ref, st_my = fused_state(n), fused_state(n)
+    for s in range(1, steps + 1):
+        g = gfn(s)
+        mine_step(N, p_my, g, st_my, qm, qv, s, h)
+        torch.cuda.synchronize()
+        ref_step(ref, p_ref, g, st_ref, qm, qv, s, h)
+        torch.cuda.synchronize()
+        assert_same(p_my, st_my, p_ref, st_ref, f"{name} step {s}")
+
+
+def test_fused_nonlinear_second_moment_map(qmaps):
+    """A second-moment map other than the linear one takes the table path instead of the closed form."""
+    ref = load_reference_extension("fused_adamw")
+    if ref is None:
+        pytest.skip("oracle/_ref was not built")
+    N = _lib()
+    qm, _, qv2 = device_qmaps(qmaps)
+    n = 128 * 100
+    torch.manual_seed(1)
+    p_ref = torch.randn(n, device=device()) * 0.02
+    p_my = p_ref.clone()
+    st_ref, st_my = fused_state(n), fused_state(n)
+    for s in range(1, 5):
+        g = student_t((n,), 80 + s)
+        mine_step(N, p_my, g, st_my, qm, qv2, s)
+        ref_step(ref, p_ref, g, st_ref, qm, qv2, s)
+        torch.cuda.synchronize()
+        assert_same(p_my, st_my, p_ref, st_ref, f"step {s}")
+
+
+def test_fused_unaligned_views_match_reference(qmaps):
+    ref = load_reference_extension("fused_adamw")
+    if ref is None:
+        pytest.skip("oracle/_ref was not built")
+    N = _lib()
+    qm, qv, _ = device_qmaps(qmaps)
+    n = 128 * 50
+    base = torch.randn(n + 8, device=device()) * 0.02
+    gb = torch.randn(n + 8, device=device()) * 1e-3
+    p_my, g_my = base[1:n + 1], gb[3:n + 3]
+    p_ref, g_ref = p_my.clone(), g_my.clone()
+    st_ref, st_my = fused_state(n), fused_state(n)
+    for s in range(1, 4):
+        mine_step(N, p_my, g_my, st_my, qm, qv, s)
+        ref_step(ref, p_ref, g_ref, st_ref, qm, qv, s)
+        torch.cuda.synchronize()
+    assert_same(p_my, st_my, p_ref, st_ref, "unaligned")
+
+
+@pytest.mark.parametrize("n", [128 * 3 + 77, 1, 127, 128, 4097, 128 * 37 + 70])
+def test_fused_matches_c_oracle(qmaps, n):
+    """Odd and ragged sizes (which the reference's binding rejects) against the C oracle, fed the
+    device's own bias corrections so that parameters can be compared bit for bit too."""
+    from oracle import cpu as O
+    N = _lib()
+    qm, qv, _ = device_qmaps(qmaps)
+    torch.manual_seed(5)
+    p = torch.randn(n, device=device()) * 0.02
+    st = fused_state(n)
+    p_o = p.cpu().numpy().copy()
+    st_o = [x.cpu().numpy().copy() for x in st]
+    st_o[0], st_o[1] = st_o[0].view(np.uint8), st_o[1].view(np.uint8)
+    cdev = torch.zeros(2, device=device())
+    for s in range(1, 5):
+        g = student_t((n,), 90 + s)
+        N.check(N.lib.lpmm_b200_bias_corrections(HYPER["beta1"], HYPER["beta2"], float(s), vp(cdev), stream()))
+        torch.cuda.synchronize()
+        c = cdev.cpu().numpy()
+        mine_step(N, p, g, st, qm, qv, s)
+        O.adamw4bit(p_o, g.cpu().numpy(), *st_o, qmaps["m"], qmaps["v"], HYPER["beta1"], HYPER["beta2"], HYPER["lr"],
+                    HYPER["weight_decay"], HYPER["eps"], float(s), c=(float(c[0]), float(c[1])))
+        torch.cuda.synchronize()
+        assert np.array_equal(st[0].cpu().numpy().view(np.uint8), st_o[0])
+        assert np.array_equal(st[1].cpu().numpy().view(np.uint8), st_o[1])
+        assert np.array_equal(st[2].cpu().numpy().view(np.int32), st_o[2].view(np.int32))
+        assert np.array_equal(st[3].cpu().numpy().view(np.int32), st_o[3].view(np.int32))
+        assert np.array_equal(p.cpu().numpy().view(np.int32), p_o.view(np.int32))
+
+
+def test_fused_fp32_state_kernel_matches_reference(qmaps):
+    ref = load_reference_extension("fused_adamw")
+    if ref is None:
+        pytest.skip("oracle/_ref was not built")
+    N = _lib()
+    for n in (4096, 127, 1000):
+        torch.manual_seed(n)
+        p_ref = torch.randn(n, device=device()) * 0.02
+        p_my = p_ref.clone()
+        m_r, v_r, m_m, v_m = (torch.zeros(n, device=device()) for _ in range(4))
+        for s in range(1, 5):
+            g = student_t((n,), 300 + s)
+            N.check(N.lib.lpmm_b200_adamw_single_tensor(vp(p_my), vp(g), vp(m_m), vp(v_m), HYPER["beta1"], HYPER["beta2"],
+                                                        HYPER["lr"], HYPER["weight_decay"], HYPER["eps"], float(s), n,
+                                                        stream()))
+            ref.adamw_single_tensor(p_ref, g, m_r, v_r, HYPER["beta1"], HYPER["beta2"], HYPER["lr"],
+                                    HYPER["weight_decay"], HYPER["eps"], float(s))
+            torch.cuda.synchronize()
+            assert bits_equal(m_m, m_r) and bits_equal(v_m, v_r) and bits_equal(p_my, p_ref)
+
+
+def test_multi_tensor_equals_single_tensor_and_shards(qmaps):
+    """One launch over a mixed list (4-bit, fp32-state, ragged) equals per-tensor launches, and
+    updating the list as two group ranges (ZeRO-1 shards) equals updating it at once."""
+    from lpmm import _kernels as K
+    N = _lib()
+    qm, qv, _ = device_qmaps(qmaps)
+    shapes = [(300, 128), (4096,), (5000,), (77, 129), (128,), (64, 64, 3)]
+
+    def build(seed):
+        torch.manual_seed(seed)
+        out = []
+        for s in shapes:
+            n = int(np.prod(s))
+            p = torch.randn(s, device=device()) * 0.02
+            if n > 4096:
+                st = fused_state(n)
+                out.append([p, None, st[0], st[1], st[2], st[3]])
+            else:
+                out.append([p, None, torch.zeros(s, device=device()), torch.zeros(s, device=device()), None, None])
+        return out
+
+    a, b, c = build(3), build(3), build(3)
+    for s in range(1, 4):
+        grads = [student_t(sh, 500 + 10 * s + i) for i, sh in enumerate(shapes)]
+        for lst in (a, b, c):
+            for e, g in zip(lst, grads):
+                e[1] = g
+        # a: one launch
+        K.adamw4bit_multi_tensor(K.TensorList([tuple(e) for e in a]), qm, qv, HYPER["beta1"], HYPER["beta2"],
+                                 HYPER["lr"], HYPER["weight_decay"], HYPER["eps"], float(s))
+        # b: per tensor
+        for e in b:
+            if e[4] is not None:
+                mine_step(N, e[0], e[1], e[2:6], qm, qv, s)
+            else:
+                K.adamw_single_tensor(e[0], e[1], e[2], e[3], HYPER["beta1"], HYPER["beta2"], HYPER["lr"],
+                                      HYPER["weight_decay"], HYPER["eps"], float(s))
+        # c: two shards
+        tl = K.TensorList([tuple(e) for e in c])
+        cut = tl.total_groups // 3
+        for lo, hi in ((0, cut), (cut, tl.total_groups)):
+            K.adamw4bit_multi_tensor(tl, qm, qv, HYPER["beta1"], HYPER["beta2"], HYPER["lr"], HYPER["weight_decay"],
+                                     HYPER["eps"], float(s), lo, hi)
+        torch.cuda.synchronize()
+        for ea, eb, ec in zip(a, b, c):
+            for i in (0, 2, 3, 4, 5):
+                if ea[i] is None:
+                    continue
+                x, y, z = ea[i], eb[i], ec[i]
+                if x.dtype == torch.float32:
+                    assert bits_equal(x, y) and bits_equal(x, z)
+                else:
+                    assert torch.equal(x, y) and torch.equal(x, z)
+
+
+def test_argument_errors_are_reported_not_launched():
+    N = _lib()
+    lib = N.lib
+    assert lib.lpmm_b200_adamw4bit_single_tensor(None, None, None, None, None, None, None, None, 0.9, 0.999, 1e-3, 0.0,
+                                                 1e-8, 1.0, 128, None) == -1
+    assert lib.lpmm_b200_adamw_single_tensor(None, None, None, None, 0.9, 0.999, 1e-3, 0.0, 1e-8, 1.0, -5, None) == -2
+    with pytest.raises(N.NativeError):
+        N.check(-2)

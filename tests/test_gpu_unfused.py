@@ -1,0 +1,231 @@
+"""The optimizers of the Python surface (``lpmm.optim.AdamW`` non-fused and factored, ``lpmm.optim.SGD``)
+on a B200 against the torch-op restatement of the reference's Python path run on the same GPU
+(``oracle/torch_ref.py``, itself pinned to the reference's Python on CPU).  Codes, scales and
+per-axis maxima must be bit-identical; parameters bit-identical except in the factored mode,
+where row/column means are summed in a different (fixed) order: 1e-6 relative there."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from golden_cases import CASES, THRESHOLD
+from gpu_helpers import bits_equal, device, nibbles, student_t
+
+pytestmark = pytest.mark.gpu
+
+
+def _golden(golden_dir, name):
+    z = np.load(os.path.join(golden_dir, f"python_{name}.npz"))
+    return {k: z[k] for k in z.files}
+
+
+def _dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(device())
+
+
+def _make_opt(kind, params, kw):
+    import lpmm
+    from lpmm.config import CONFIG_DIR
+    kw = dict(kw)
+    if isinstance(kw.get("qconfig"), str):
+        kw["qconfig"] = os.path.join(CONFIG_DIR, kw["qconfig"])
+    return getattr(lpmm.optim, kind)(params, **kw)
+
+
+def _run_pair_adamw(shapes, p0s, grads_of_step, steps, kw, qmaps, v_scale):
+    """Returns (optimizer, params, oracle states, oracle params)."""
+    from oracle import torch_ref as T
+    qm, qv = _dev(qmaps["m"]), _dev(qmaps["v"])
+    params = [torch.nn.Parameter(p.clone()) for p in p0s]
+    opt = _make_opt("AdamW", params, kw)
+    o_params = [p.clone() for p in p0s]
+    o_states = [dict() for _ in p0s]
+    factored = kw.get("factor_second_moment", False)
+    for i, sh in enumerate(shapes):
+        if factored and len(sh) >= 2:
+            o_states[i] = {"row": torch.zeros(sh[:-1], device=device()), "col": torch.zeros(sh[:-2] + sh[-1:], device=device())}
+    b1, b2 = kw["betas"]
+    for s in range(1, steps + 1):
+        grads = grads_of_step(s)
+        for p, g in zip(params, grads):
+            p.grad = g.clone()
+        opt.step()
+        for i, (op, g) in enumerate(zip(o_params, grads)):
+            quant = op.numel() > THRESHOLD
+            common = dict(beta1=b1, beta2=b2, lr=kw["lr"], weight_decay=kw["weight_decay"], eps=kw["eps"], step=float(s))
+            if factored and op.dim() >= 2:
+                T.factored_step(op, g, o_states[i], qm, m_quant=quant, **common)
+            else:
+                T.adamw_step(op, g, o_states[i], qm, qv, m_quant=quant, v_quant=quant, v_scale_type=v_scale, **common)
+    torch.cuda.synchronize()
+    return opt, params, o_states, o_params
+
+
+def _check_group_state(mine_codes, mine_max1, o_codes, o_md, n, what):
+    groups = (n + 127) // 128
+    assert mine_codes.numel() == o_codes.numel(), f"{what}: packed length"
+    assert torch.equal(mine_codes.view(torch.uint8), o_codes.view(torch.uint8)), f"{what}: codes (incl. padding) differ"
+    assert bits_equal(mine_max1.reshape(-1), o_md["max1"].reshape(-1)), f"{what}: scales differ"
+    assert mine_max1.numel() == groups
+
+
+def _check_adamw(opt, params, o_states, o_params, v_scale, factored=False, p_exact=True):
+    for i, p in enumerate(params):
+        st, os_, op = opt.state[p], o_states[i], o_params[i]
+        quant = p.numel() > THRESHOLD
+        fac = factored and p.dim() >= 2
+        if fac or not p_exact:
+            rel = ((p.detach() - op).norm() / op.norm()).item()
+            assert rel <= 1e-6, f"tensor {i}: params rel err {rel}"
+        else:
+            assert bits_equal(p.detach(), op), f"tensor {i}: params differ"
+        if quant:
+            _check_group_state(st["exp_avg"], st["exp_avg_qstate"]["overhead"]["max1"], os_["m"], os_["m_md"], p.numel(),
+                               f"tensor {i} exp_avg")
+        else:
+            assert bits_equal(st["exp_avg"], os_["m"]), f"tensor {i}: fp32 exp_avg differs"
+        if fac:
+            for mine, orc in ((st["exp_avg_sq_row"], os_["row"]), (st["exp_avg_sq_col"], os_["col"])):
+                rel = ((mine - orc).abs().max() / orc.abs().max()).item()
+                assert rel <= 1e-6, f"tensor {i}: accumulator rel err {rel}"
+            continue
+        if not quant:
+            assert bits_equal(st["exp_avg_sq"], os_["v"]), f"tensor {i}: fp32 exp_avg_sq differs"
+        elif v_scale == "rank1" and p.dim() >= 2:
+            oh = st["exp_avg_sq_qstate"]["overhead"]
+            assert st["exp_avg_sq"].numel() == os_["v"].numel()
+            assert torch.equal(st["exp_avg_sq"].view(torch.uint8), os_["v"].view(torch.uint8)), f"tensor {i}: v codes"
+            for d in range(p.dim()):
+                assert oh["max_dims"][d].shape == os_["v_md"]["max_dims"][d].shape
+                assert bits_equal(oh["max_dims"][d], os_["v_md"]["max_dims"][d]), f"tensor {i}: axis {d} maxima"
+        else:
+            _check_group_state(st["exp_avg_sq"], st["exp_avg_sq_qstate"]["overhead"]["max1"], os_["v"], os_["v_md"],
+                               p.numel(), f"tensor {i} exp_avg_sq")
+
+
+@pytest.mark.parametrize("name", ["adamw_rank1", "adamw_group", "adamw_rank1_ragged"])
+def test_adamw_unfused_on_golden_inputs(golden_dir, qmaps, name):
+    G = _golden(golden_dir, name)
+    _, kw, shapes = CASES[name]
+    v_scale = "rank1" if kw["qconfig"] == "default.yml" else "group"
+    steps = int(G["steps"])
+    p0s = [_dev(G[f"p0.{i}"]) for i in range(len(shapes))]
+    opt, params, o_states, o_params = _run_pair_adamw(
+        shapes, p0s, lambda s: [_dev(G[f"g{s}.{i}"]) for i in range(len(shapes))], steps, kw, qmaps, v_scale)
+    _check_adamw(opt, params, o_states, o_params, v_scale)
+    # and against what the reference's Python produced on CPU: same codes up to fp ties, same params to 1e-6
+    for i, p in enumerate(params):
+        ref_p = _dev(G[f"p.{i}"])
+        assert ((p.detach() - ref_p).norm() / ref_p.norm()).item() <= 1e-6
+        if p.numel() > THRESHOLD:
+            n = p.numel()
+            mism = (nibbles(opt.state[p]["exp_avg"], n) != nibbles(_dev(G[f"s.{i}.exp_avg"]), n)).float().mean().item()
+            assert mism <= 1e-3, f"tensor {i}: {mism} of first-moment codes differ from the CPU run"
+
+
+def test_adamw_unfused_larger_ragged_shapes(qmaps):
+    """The ragged shape list of the tail/fallback configuration: conv weights, matrices whose sizes
+    are not multiples of 128, vectors around the 4096 threshold, a column vector; 20 % exact zeros."""
+    from lpmm.config import CONFIG_DIR  # noqa: F401
+    shapes = [(3, 3, 64, 64), (1000, 768), (768, 3072), (4097,), (127,), (4096,), (50000, 1)]
+    kw = dict(qconfig="default.yml", lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01)
+    torch.manual_seed(0)
+    p0s = [torch.randn(s, device=device()) * 0.02 for s in shapes]
+    opt, params, o_states, o_params = _run_pair_adamw(
+        shapes, p0s, lambda s: [student_t(sh, s * 100003 + i, zero_fraction=0.2) for i, sh in enumerate(shapes)], 6, kw,
+        qmaps, "rank1")
+    _check_adamw(opt, params, o_states, o_params, "rank1")
+
+
+def test_adamw_group_config_matrix(qmaps):
+    shapes = [(4096, 512), (333, 77)]
+    kw = dict(qconfig=None, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01)
+    torch.manual_seed(1)
+    p0s = [torch.randn(s, device=device()) * 0.02 for s in shapes]
+    opt, params, o_states, o_params = _run_pair_adamw(
+        shapes, p0s, lambda s: [student_t(sh, s * 100003 + i) for i, sh in enumerate(shapes)], 5, kw, qmaps, "group")
+    _check_adamw(opt, params, o_states, o_params, "group")
+
+
+def test_adamw_factored_on_golden_inputs(golden_dir, qmaps):
+    G = _golden(golden_dir, "adamw_factored")
+    _, kw, shapes = CASES["adamw_factored"]
+    steps = int(G["steps"])
+    p0s = [_dev(G[f"p0.{i}"]) for i in range(len(shapes))]
+    opt, params, o_states, o_params = _run_pair_adamw(
+        shapes, p0s, lambda s: [_dev(G[f"g{s}.{i}"]) for i in range(len(shapes))], steps, kw, qmaps, "group")
+    _check_adamw(opt, params, o_states, o_params, "group", factored=True)
+
+
+def test_adamw_factored_gpt2_like_shapes(qmaps):
+    shapes = [(5025, 1024), (1024, 3072), (1024,)]
+    kw = dict(qconfig=None, factor_second_moment=True, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01)
+    torch.manual_seed(2)
+    p0s = [torch.randn(s, device=device()) * 0.02 for s in shapes]
+    opt, params, o_states, o_params = _run_pair_adamw(
+        shapes, p0s, lambda s: [student_t(sh, s * 100003 + i) for i, sh in enumerate(shapes)], 4, kw, qmaps, "group")
+    _check_adamw(opt, params, o_states, o_params, "group", factored=True)
+
+
+@pytest.mark.parametrize("name", ["sgd_momentum", "sgd_nesterov"])
+def test_sgd_on_golden_inputs(golden_dir, qmaps, name):
+    from oracle import torch_ref as T
+    G = _golden(golden_dir, name)
+    _, kw, shapes = CASES[name]
+    steps = int(G["steps"])
+    qm = _dev(qmaps["m"])
+    params = [torch.nn.Parameter(_dev(G[f"p0.{i}"])) for i in range(len(shapes))]
+    opt = _make_opt("SGD", params, kw)
+    o_params = [_dev(G[f"p0.{i}"]) for i in range(len(shapes))]
+    o_states = [dict() for _ in shapes]
+    for s in range(1, steps + 1):
+        for i, p in enumerate(params):
+            g = _dev(G[f"g{s}.{i}"])
+            p.grad = g.clone()
+            T.sgd_step(o_params[i], g, o_states[i], qm, quant=p.numel() > THRESHOLD, weight_decay=kw["weight_decay"],
+                       momentum=kw["momentum"], lr=kw["lr"], dampening=kw.get("dampening", 0),
+                       nesterov=kw.get("nesterov", False), maximize=False)
+        opt.step()
+    torch.cuda.synchronize()
+    for i, p in enumerate(params):
+        assert bits_equal(p.detach(), o_params[i]), f"tensor {i}: params differ"
+        st = opt.state[p]
+        if p.numel() > THRESHOLD:
+            _check_group_state(st["momentum_buffer"], st["momentum_buffer_qstate"]["overhead"]["max1"], o_states[i]["buf"],
+                               o_states[i]["buf_md"], p.numel(), f"tensor {i} buffer")
+        else:
+            assert bits_equal(st["momentum_buffer"], o_states[i]["buf"])
+        ref_p = _dev(G[f"p.{i}"])
+        assert ((p.detach() - ref_p).norm() / ref_p.norm()).item() <= 1e-6
+
+
+def test_state_dict_round_trip_keeps_codes_and_continues(qmaps):
+    """state_dict -> load_state_dict into a fresh optimizer, then one more step on both: identical."""
+    import lpmm
+    from lpmm.config import CONFIG_DIR
+    shapes = [(96, 64), (5000,), (100,)]
+    kw = dict(lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01, qconfig=os.path.join(CONFIG_DIR, "default.yml"))
+    torch.manual_seed(3)
+    pa = [torch.nn.Parameter(torch.randn(s, device=device()) * 0.02) for s in shapes]
+    oa = lpmm.optim.AdamW(pa, **kw)
+    for s in range(1, 4):
+        for i, p in enumerate(pa):
+            p.grad = student_t(p.shape, 900 + 10 * s + i)
+        oa.step()
+    sd = oa.state_dict()
+    assert "qconfig" in sd
+    assert sd["state"][0]["exp_avg"].dtype == torch.int8
+    pb = [torch.nn.Parameter(p.detach().clone()) for p in pa]
+    ob = lpmm.optim.AdamW(pb, **kw)
+    ob.load_state_dict(sd)
+    assert ob.state[pb[0]]["exp_avg"].dtype == torch.int8
+    for i, (a, b) in enumerate(zip(pa, pb)):
+        g = student_t(a.shape, 990 + i)
+        a.grad, b.grad = g.clone(), g.clone()
+    oa.step()
+    ob.step()
+    torch.cuda.synchronize()
+    for a, b in zip(pa, pb):
+        assert bits_equal(a.detach(), b.detach())
+        assert torch.equal(oa.state[a]["exp_avg"], ob.state[b]["exp_avg"])
