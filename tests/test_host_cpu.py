@@ -1,0 +1,126 @@
+"""CPU-only checks of the host side: the C-ABI library loads and exports every declared symbol,
+argument validation happens before any launch, and the Python mirror of the reference's
+interface (config tree, maps, optimizer constructors, enable rule) behaves like the reference."""
+import ctypes
+import os
+import pickle
+import re
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    from lpmm import _native as N
+    header = open(os.path.join(ROOT, "include", "lpmm_b200.h")).read()
+    declared = set(re.findall(r"\b(lpmm_b200_[a-z0-9_]+)\s*\(", header))
+    assert len(declared) >= 19
+    lib = ctypes.CDLL(N._LIB_PATH)
+    for name in sorted(declared):
+        assert hasattr(lib, name), f"{name} is declared in include/lpmm_b200.h but not exported"
+    assert declared == set(N.SIGNATURES), "the ctypes table and the header disagree"
+    assert N.lib.lpmm_b200_abi_version() == 1
+
+
+def test_argument_validation_without_a_gpu():
+    from lpmm import _native as N
+    lib = N.lib
+    assert lib.lpmm_b200_strerror(0) == b"ok"
+    assert lib.lpmm_b200_packed_len(1) == 1025 and lib.lpmm_b200_packed_len(2048) == 1025
+    assert lib.lpmm_b200_packed_len(2049) == 2049 and lib.lpmm_b200_packed_len(0) == 1
+    assert lib.lpmm_b200_packed_len(-1) == -2
+    assert lib.lpmm_b200_pack_nonlinear4(None, 7, None, None, None) == -2      # odd count
+    assert lib.lpmm_b200_pack_nonlinear4(None, 8, None, None, None) == -1      # null pointers
+    assert lib.lpmm_b200_adamw4bit_multi_tensor(None, -1, None, None, N.Hyper(), 0, -1, None) == -2
+    arr = (N.Tensor * 2)()
+    arr[0] = N.Tensor(0, 0, 0, 0, 0, 0, 300, N.KIND_Q4, 0)
+    arr[1] = N.Tensor(0, 0, 0, 0, 0, 0, 4096, N.KIND_FP32, 0)
+    assert lib.lpmm_b200_count_groups(arr, 2) == 3 + 32
+    assert lib.lpmm_b200_adamw4bit_multi_tensor(arr, 2, None, None, N.Hyper(), 0, -1, None) == -1  # null data
+    arr[0].kind = 7
+    assert lib.lpmm_b200_adamw4bit_multi_tensor(arr, 2, None, None, N.Hyper(), 0, -1, None) == -3
+    shape = (ctypes.c_int64 * 3)(2, 100, 64)
+    tiles = (100 + 63) // 64
+    assert lib.lpmm_b200_factored_scratch_bytes(shape, 3) == 4 * (2 * tiles * 64 + 2)
+    assert lib.lpmm_b200_factored_scratch_bytes(shape, 1) == -2
+
+
+def test_maps_are_the_reference_maps(qmaps):
+    from lpmm.functional import create_general_qmap
+    assert np.array_equal(create_general_qmap("nonlinear", 4, True).numpy(), qmaps["m"])
+    assert np.array_equal(create_general_qmap("power-1", 4, False).numpy(), qmaps["v"])
+    assert np.array_equal(create_general_qmap("nonlinear", 4, False).numpy(), qmaps["nonlinear_unsigned"])
+    assert np.array_equal(create_general_qmap("power-2", 4, False).numpy(), qmaps["power2"])
+    assert np.array_equal(create_general_qmap("power-1", 4, True).numpy(), qmaps["power1_signed"])
+    assert create_general_qmap("linear", 4, True) is None
+    with pytest.raises(ValueError):
+        create_general_qmap("no-such-map", 4, True)
+
+
+def test_config_defaults_files_and_pickle(tmp_path):
+    from lpmm.config import CONFIG_DIR, get_config
+    c = get_config(None)
+    assert (c.QUANT.M.BITS, c.QUANT.M.SCALE_TYPE.DEFAULT, c.QUANT.M.QUANT_TYPE.DEFAULT, c.QUANT.M.SIGNED) == (4, "group", "nonlinear", True)
+    assert (c.QUANT.SQM.SCALE_TYPE.DEFAULT, c.QUANT.SQM.QUANT_TYPE.DEFAULT, c.QUANT.SQM.SIGNED) == ("group", "power-1", False)
+    assert c.QUANT.M.THRESHOLD == 4096 and c.QUANT.M.ROUND_TYPE == "real-nearest" and c.QUANT.M.GROUP_SIZE == 128
+    d = get_config(os.path.join(CONFIG_DIR, "default.yml"))
+    assert d.QUANT.SQM.SCALE_TYPE.DEFAULT == "rank1" and d.QUANT.SQM.SIGNED is False and d.QUANT.M.ENABLE is True
+    assert pickle.loads(pickle.dumps(d)) == d
+    with pytest.raises(AttributeError):
+        d.QUANT.M.BITS = 8                                       # frozen
+    base = tmp_path / "base.yml"
+    base.write_text("QUANT:\n  M:\n    ENABLE: false\n")
+    child = tmp_path / "child.yml"
+    child.write_text("BASE: ['base.yml']\nQUANT:\n  SQM:\n    SCALE_TYPE:\n      DEFAULT: rank1\n")
+    e = get_config(str(child))
+    assert e.QUANT.M.ENABLE is False and e.QUANT.SQM.SCALE_TYPE.DEFAULT == "rank1"
+    with pytest.raises(TypeError):
+        get_config(123)
+    assert not os.path.exists("lpmm_config.txt")
+
+
+def test_optimizer_constructors_validate_like_the_reference():
+    import lpmm
+    w = torch.nn.Parameter(torch.zeros(8, 8))
+    for bad in (dict(lr=-1.0), dict(eps=-1.0), dict(betas=(1.0, 0.9)), dict(betas=(0.9, -0.1)), dict(weight_decay=-1.0)):
+        with pytest.raises(ValueError):
+            lpmm.optim.AdamW([w], **bad)
+    with pytest.raises(ValueError):
+        lpmm.optim.SGD([w], lr=0.1, fused=True)
+    with pytest.raises(ValueError):
+        lpmm.optim.SGD([w], lr=-0.1)
+    opt = lpmm.optim.AdamW([w], fused=True)
+    assert opt.defaults["fused"] is True and opt.qconfig.QUANT.M.BITS == 4
+    assert set(opt.state_dict()) >= {"state", "param_groups", "qconfig"}
+
+
+def test_enable_rule_and_override():
+    import lpmm
+    from lpmm.optim.optimizer import quantize_enabled
+    assert quantize_enabled(torch.zeros(4097), True, 4096) is True
+    assert quantize_enabled(torch.zeros(4096), True, 4096) is False          # exactly the threshold stays fp32
+    assert quantize_enabled(torch.zeros(10 ** 5), False, 4096) is False
+    lin = torch.nn.Linear(128, 64)
+    opt = lpmm.optim.AdamW(lin.parameters())
+    opt.override_quantize_enable(lin, "weight", False)
+    assert opt.override_q_enable[id(lin.weight)] is False
+    opt.state[lin.weight]["step"] = torch.tensor(1.0)
+    with pytest.raises(ValueError):
+        opt.override_quantize_enable(lin, "weight", True)
+
+
+def test_cpu_tensors_are_rejected_not_silently_computed():
+    """There is no CPU implementation: a step on CPU tensors raises like the reference's bindings do."""
+    import lpmm
+    w = torch.nn.Parameter(torch.randn(100, 50))
+    w.grad = torch.randn(100, 50)
+    for kw in (dict(fused=True), dict(fused=False), dict(factor_second_moment=True)):
+        opt = lpmm.optim.AdamW([w], **kw)
+        with pytest.raises(RuntimeError):
+            opt.step()
+    opt = lpmm.optim.SGD([w], lr=0.1, momentum=0.9)
+    with pytest.raises(RuntimeError):
+        opt.step()
