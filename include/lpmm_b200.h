@@ -208,6 +208,36 @@ int lpmm_b200_sgd4bit_step(float* p, const float* g, int64_t numel, void* buf, f
                            int first, const float* qmap, double weight_decay, double momentum, double lr,
                            double dampening, int nesterov, int maximize, void* stream);
 
+/* Allocation-free variant of the factored step, for callers that cannot allocate device memory.
+ * It has no counterpart in the reference.
+ *
+ * Who needs it: code that runs where cudaMalloc is off limits -- a training loop whose memory is
+ * entirely owned by a framework allocator or fixed up front, a process running under a memory
+ * budget that forbids growth after start-up, or a caller that simply has no handle on a device
+ * allocator and therefore cannot provide the scratch buffer that
+ * lpmm_b200_adamw4bit_unfused_step wants for v_mode == LPMM_B200_STATE_FACTORED.
+ *
+ * What it does: exactly that step (same kernels, same results), with the column partial sums and
+ * row means kept in a fixed array of LPMM_B200_STATIC_SCRATCH_BYTES that lives inside the library
+ * image on every GPU that loads it, from load until the process exits.  The caller passes only
+ * inputs and outputs.  Nothing is allocated or freed here, by this library or by any library it
+ * calls.
+ *
+ * Limits and rules:
+ *  - a tensor whose scratch need (lpmm_b200_factored_scratch_bytes) exceeds
+ *    LPMM_B200_STATIC_SCRATCH_BYTES is refused with LPMM_B200_ERR_TOO_LARGE and nothing is launched
+ *    (8 MiB covers a 32000 x 4096 matrix);
+ *  - t->v_mode must be LPMM_B200_STATE_FACTORED (LPMM_B200_ERR_BAD_KIND otherwise);
+ *  - the first call on each device looks up the array's device address; make that first call
+ *    with the device current and before starting any stream capture;
+ *  - all calls on a device share the one array: two calls that may overlap on the GPU (different
+ *    streams, no dependency) race on it -- order them.  The array keeps whatever the last call
+ *    left; no call relies on its previous contents. */
+#define LPMM_B200_STATIC_SCRATCH_BYTES (8 * 1024 * 1024)
+int lpmm_b200_adamw4bit_factored_step_noalloc(const lpmm_b200_step_tensor* t, const float* qmap_m, double beta1,
+                                              double beta2, double lr, double weight_decay, double eps, double step,
+                                              void* stream);
+
 #ifdef __cplusplus
 }
 #endif

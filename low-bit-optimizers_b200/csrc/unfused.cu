@@ -806,3 +806,44 @@ extern "C" int lpmm_b200_sgd4bit_step(float* p, const float* g, int64_t numel, v
   LPMM_CUDA_TRY(cudaGetLastError());
   return LPMM_B200_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Factored step without any allocation: the scratch lives in the library image.
+// ---------------------------------------------------------------------------------------------
+// Device-resident scratch of the allocation-free entry point.  In host code this name is only a
+// handle for cudaGetSymbolAddress; it is not itself a device address.
+static __device__ __align__(256) unsigned char g_static_scratch[LPMM_B200_STATIC_SCRATCH_BYTES];
+
+// Device address of g_static_scratch on the current device, looked up once per device.
+static int static_scratch_address(void** out) {
+  static void* addr[64] = {};
+  int dev = -1;
+  LPMM_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return LPMM_B200_ERR_UNSUPPORTED;
+  if (addr[dev] == nullptr) {
+    void* p = nullptr;
+    LPMM_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_scratch));
+    addr[dev] = p;  // concurrent first calls store the same value
+  }
+  *out = addr[dev];
+  return LPMM_B200_OK;
+}
+
+// For callers that may not allocate: same launches as the FACTORED branch of
+// lpmm_b200_adamw4bit_unfused_step, scratch taken from g_static_scratch.  Every partial sum and
+// row mean the kernels read is written earlier in the same call, so stale contents are harmless;
+// calls that overlap on the GPU would overwrite each other's partial sums.
+extern "C" int lpmm_b200_adamw4bit_factored_step_noalloc(const lpmm_b200_step_tensor* t, const float* qmap_m,
+                                                         double beta1, double beta2, double lr, double weight_decay,
+                                                         double eps, double step, void* stream) {
+  if (!t) return LPMM_B200_ERR_NULL_POINTER;
+  if (t->v_mode != LPMM_B200_STATE_FACTORED) return LPMM_B200_ERR_BAD_KIND;
+  const int64_t need = lpmm_b200_factored_scratch_bytes(t->shape, t->ndim);
+  if (need < 0) return (int)need;
+  if (need > (int64_t)LPMM_B200_STATIC_SCRATCH_BYTES) return LPMM_B200_ERR_TOO_LARGE;
+  void* scratch = nullptr;
+  const int rc = static_scratch_address(&scratch);
+  if (rc != LPMM_B200_OK) return rc;
+  return lpmm_b200_adamw4bit_unfused_step(t, qmap_m, nullptr, beta1, beta2, lr, weight_decay, eps, step, scratch,
+                                          (int64_t)LPMM_B200_STATIC_SCRATCH_BYTES, stream);
+}

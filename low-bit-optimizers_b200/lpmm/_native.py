@@ -59,6 +59,7 @@ KIND_Q4 = 0
 KIND_FP32 = 1
 GROUP = 128
 PACK_GROUP = 2048
+STATIC_SCRATCH_BYTES = 8 * 1024 * 1024
 
 
 class NativeError(RuntimeError):
@@ -91,6 +92,7 @@ def _load():
         "lpmm_b200_dequant_rank1_4": (i32, [vp, vp, ctypes.POINTER(vp), ctypes.POINTER(i64), i32, vp, vp]),
         "lpmm_b200_adamw4bit_unfused_step": (i32, [ctypes.POINTER(StepTensor), vp, vp] + [d] * 6 + [vp, i64, vp]),
         "lpmm_b200_factored_scratch_bytes": (i64, [ctypes.POINTER(i64), i32]),
+        "lpmm_b200_adamw4bit_factored_step_noalloc": (i32, [ctypes.POINTER(StepTensor), vp] + [d] * 6 + [vp]),
         "lpmm_b200_sgd4bit_step": (i32, [vp, vp, i64, vp, vp, i32, i32, vp, d, d, d, d, i32, i32, vp]),
     }
     for name, (res, args) in sigs.items():
