@@ -1,0 +1,207 @@
+"""ZeRO-1 sharding of the fused 4-bit AdamW step (no counterpart in the reference, which has no
+distributed code beyond a seed broadcast, lpmm/optim/optimizer.py:19-22).
+
+The parameter list defines a global sequence of 128-element groups (tensor t contributes
+ceil(numel_t / 128) groups, in list order).  Every group is independent in the fused step -- its
+codes, its two scales, its slice of p and g -- so the sequence is cut into ``world`` contiguous
+ranges of equal length S = ceil(G / world) and rank r
+
+* keeps 4-bit codes, scales, fp32 moments of small tensors and gradients ONLY for its range,
+* updates its range of the (replicated, flat) fp32 parameter buffer with the same multi-tensor
+  launch as the unsharded step, restricted to ``[r*S, (r+1)*S)``,
+* takes part in one ``all_gather_into_tensor`` of the flat parameter buffer (NCCL on GPUs).
+
+The result is bit-identical to the unsharded step.  A shard may cut a tensor but never a group.
+"""
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+GROUP = 128
+THRESHOLD = 4096
+
+
+def groups_of(numel):
+    return (numel + GROUP - 1) // GROUP
+
+
+def partition(numels, world):
+    """Group layout of a parameter list.
+
+    Returns ``(gstart, total_groups, shard_groups)``: first global group of every tensor, the
+    number of groups, and S = ceil(total / world).  Rank r owns ``[r*S, min((r+1)*S, total))``."""
+    gstart, g = [], 0
+    for n in numels:
+        gstart.append(g)
+        g += groups_of(n)
+    shard = (g + world - 1) // world if world > 0 else g
+    return gstart, g, shard
+
+
+def owned_range(rank, total_groups, shard_groups):
+    lo = min(rank * shard_groups, total_groups)
+    return lo, min(lo + shard_groups, total_groups)
+
+
+def owned_pieces(numels, gstart, lo, hi):
+    """``(tensor index, first local group, one-past-last local group)`` for every tensor that
+    intersects the global group range ``[lo, hi)``."""
+    out = []
+    for i, (n, gs) in enumerate(zip(numels, gstart)):
+        a, b = max(lo, gs), min(hi, gs + groups_of(n))
+        if a < b:
+            out.append((i, a - gs, b - gs))
+    return out
+
+
+class Zero1FusedAdamW:
+    """Fused 4-bit AdamW over a flat, replicated fp32 parameter buffer with ZeRO-1 sharded states.
+
+    ``shapes``: shapes of the parameter list.  ``self.params[i]`` is a view of the flat buffer
+    (tensor i starts on a group boundary).  ``self.grad_shard`` is this rank's slice of the flat
+    gradient (what a reduce-scatter of gradients would deliver), ``shard_groups * 128`` floats.
+    """
+
+    def __init__(self, shapes, device, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=1e-2, process_group=None,
+                 rank=None, world=None):
+        from .functional import create_general_qmap
+        self.shapes = [tuple(s) for s in shapes]
+        self.numels = [int(torch.Size(s).numel()) for s in self.shapes]
+        self.device = torch.device(device)
+        self.pg = process_group
+        self.world = world if world is not None else (dist.get_world_size(process_group) if dist.is_initialized() else 1)
+        self.rank = rank if rank is not None else (dist.get_rank(process_group) if dist.is_initialized() else 0)
+        self.hyper = dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay)
+        self.step_count = 0
+        self.gstart, self.total_groups, self.shard_groups = partition(self.numels, self.world)
+        self.lo, self.hi = owned_range(self.rank, self.total_groups, self.shard_groups)
+        S = self.shard_groups
+        self.flat = torch.zeros(self.world * S * GROUP, dtype=torch.float32, device=self.device)
+        self.params = [self.flat[gs * GROUP: gs * GROUP + n].view(s)
+                       for s, n, gs in zip(self.shapes, self.numels, self.gstart)]
+        self.grad_shard = torch.zeros(S * GROUP, dtype=torch.float32, device=self.device)
+        # states of the owned range only
+        self.m_codes = torch.zeros(S * (GROUP // 2), dtype=torch.int8, device=self.device)
+        self.v_codes = torch.zeros(S * (GROUP // 2), dtype=torch.int8, device=self.device)
+        self.m_scale = torch.zeros(S, dtype=torch.float32, device=self.device)
+        self.v_scale = torch.zeros(S, dtype=torch.float32, device=self.device)
+        # fp32 moments of the tensors at or below the threshold: own "small-tensor group" index space
+        self.fstart, f = [], 0
+        for n in self.numels:
+            self.fstart.append(f)
+            if n <= THRESHOLD:
+                f += groups_of(n)
+        pieces = owned_pieces(self.numels, self.gstart, self.lo, self.hi)
+        small = [(i, a, b) for (i, a, b) in pieces if self.numels[i] <= THRESHOLD]
+        self.f_lo = self.fstart[small[0][0]] + small[0][1] if small else 0
+        f_cnt = sum(b - a for (_, a, b) in small)
+        self.m32 = torch.zeros(max(f_cnt, 1) * GROUP, dtype=torch.float32, device=self.device)
+        self.v32 = torch.zeros(max(f_cnt, 1) * GROUP, dtype=torch.float32, device=self.device)
+        self.qmap_m = create_general_qmap("nonlinear", 4, True).to(self.device)
+        self.qmap_v = create_general_qmap("power-1", 4, False).to(self.device)
+        self._tl = None
+
+    # ---- data ---------------------------------------------------------------------------------
+    def init_params_normal_(self, std, seed=0):
+        """Same values on every rank (seeded), like replicated model parameters."""
+        g = torch.Generator(device=self.device)
+        g.manual_seed(seed)
+        chunk = 1 << 26
+        for lo in range(0, self.flat.numel(), chunk):
+            hi = min(lo + chunk, self.flat.numel())
+            self.flat[lo:hi].normal_(0, std, generator=g)
+
+    def set_grad_shard_from_full(self, grads):
+        """Copy this rank's slice out of a full gradient list (tests / single-process use)."""
+        self.grad_shard.zero_()
+        for i, a, b in owned_pieces(self.numels, self.gstart, self.lo, self.hi):
+            n = self.numels[i]
+            e0, e1 = a * GROUP, min(b * GROUP, n)
+            off = (self.gstart[i] + a - self.lo) * GROUP
+            self.grad_shard[off: off + (e1 - e0)].copy_(grads[i].reshape(-1)[e0:e1])
+
+    # ---- the step -----------------------------------------------------------------------------
+    def descriptors(self):
+        """Descriptor entries (p, g, m, v, m_scale, v_scale, numel, kind) with *virtual* base addresses:
+        states and gradients exist only for the owned range, so their pointers are offset such that
+        indexing by a tensor-local group lands inside the shard buffers for owned groups.  Groups
+        outside ``[lo, hi)`` are never touched by the launch."""
+        out = []
+        for n, gs, fs in zip(self.numels, self.gstart, self.fstart):
+            d = gs - self.lo  # may be negative
+            p = self.flat.data_ptr() + gs * GROUP * 4
+            g = self.grad_shard.data_ptr() + d * GROUP * 4
+            if n > THRESHOLD:
+                out.append((p, g, self.m_codes.data_ptr() + d * (GROUP // 2), self.v_codes.data_ptr() + d * (GROUP // 2),
+                            self.m_scale.data_ptr() + d * 4, self.v_scale.data_ptr() + d * 4, n, 0))
+            else:
+                df = fs - self.f_lo
+                out.append((p, g, self.m32.data_ptr() + df * GROUP * 4, self.v32.data_ptr() + df * GROUP * 4, 0, 0, n, 1))
+        return out
+
+    def _update(self, lo, hi):
+        """Update global groups ``[lo, hi)`` (a sub-range of the owned range) on the current stream."""
+        from . import _native as N
+        if self._tl is None:
+            desc = self.descriptors()
+            arr = (N.Tensor * len(desc))()
+            for i, (p, g, m, v, sm, sv, n, kind) in enumerate(desc):
+                arr[i] = N.Tensor(p, g, m, v, sm or None, sv or None, n, kind, 0)
+            self._tl = arr
+        b1, b2 = self.hyper["betas"]
+        h = N.Hyper(b1, b2, self.hyper["lr"], self.hyper["weight_decay"], self.hyper["eps"], float(self.step_count))
+        with torch.cuda.device(self.device):
+            N.check(N.lib.lpmm_b200_adamw4bit_multi_tensor(
+                self._tl, len(self.numels), ctypes.c_void_p(self.qmap_m.data_ptr()), ctypes.c_void_p(self.qmap_v.data_ptr()),
+                h, lo, hi, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+
+    def _gather(self):
+        if self.world == 1:
+            return
+        S = self.shard_groups * GROUP
+        dist.all_gather_into_tensor(self.flat, self.flat[self.rank * S:(self.rank + 1) * S], group=self.pg)
+
+    def step(self):
+        self.step_count += 1
+        if self.hi > self.lo:
+            self._update(self.lo, self.hi)
+        self._gather()
+
+    # ---- measurement helpers (bench) -------------------------------------------------------------
+    def time_update_only(self, iters):
+        """Mean duration (ms) of the sharded update launch alone and its algorithmic bytes."""
+        ms = []
+        for _ in range(iters):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            self.step_count += 1
+            a.record()
+            self._update(self.lo, self.hi)
+            b.record()
+            torch.cuda.synchronize()
+            ms.append(a.elapsed_time(b))
+        nbytes = 0.0
+        for i, a_, b_ in owned_pieces(self.numels, self.gstart, self.lo, self.hi):
+            cnt = min(b_ * GROUP, self.numels[i]) - a_ * GROUP
+            nbytes += cnt * (14.125 if self.numels[i] > THRESHOLD else 28.0)
+        return sum(ms) / len(ms), nbytes
+
+    def breakdown(self, iters):
+        """Update-only and all-gather-only timings, max over ranks."""
+        upd, _ = self.time_update_only(iters)
+        ms = []
+        for _ in range(iters):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            dist.barrier(group=self.pg)
+            a.record()
+            self._gather()
+            b.record()
+            torch.cuda.synchronize()
+            ms.append(a.elapsed_time(b))
+        t = torch.tensor([upd, sum(ms) / len(ms)], dtype=torch.float64, device=self.device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.pg)
+        upd_ms, ag_ms = float(t[0]), float(t[1])
+        total = sum(self.numels)
+        recv = 4.0 * self.shard_groups * GROUP * (self.world - 1)
+        return {"update_only": {"ms": upd_ms, "aggregate_params_per_s": total / (upd_ms * 1e-3)},
+                "all_gather": {"ms": ag_ms, "bytes_received_per_rank": recv, "gb_per_s_per_rank": recv / (ag_ms * 1e-3) / 1e9}}

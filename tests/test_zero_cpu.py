@@ -1,0 +1,105 @@
+"""ZeRO-1 plumbing without a GPU: partition arithmetic, and two gloo ranks whose sharded steps
+(the C oracle standing in for the CUDA launch on each rank's group range) followed by the
+all-gather reproduce the unsharded result bit for bit."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+SHAPES = [(40, 128), (4096,), (5000,), (77, 129), (100,), (64, 64, 3)]
+HYPER = dict(lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01)
+
+
+def test_partition_covers_every_group_once():
+    from lpmm.zero import owned_pieces, owned_range, partition
+    numels = [int(np.prod(s)) for s in SHAPES]
+    for world in (1, 2, 3, 4, 8, 64):
+        gstart, total, shard = partition(numels, world)
+        assert total == sum((n + 127) // 128 for n in numels) and shard * world >= total
+        seen = np.zeros(total, np.int32)
+        for r in range(world):
+            lo, hi = owned_range(r, total, shard)
+            assert 0 <= lo <= hi <= total
+            for i, a, b in owned_pieces(numels, gstart, lo, hi):
+                assert 0 <= a < b <= (numels[i] + 127) // 128
+                seen[gstart[i] + a: gstart[i] + b] += 1
+        assert (seen == 1).all(), f"world {world}: groups not covered exactly once"
+
+
+def _grads(step):
+    out = []
+    for i, s in enumerate(SHAPES):
+        g = torch.Generator()
+        g.manual_seed(step * 100003 + i)
+        out.append(torch.randn(s, generator=g) * 1e-3)
+    return out
+
+
+def _oracle_update(opt, lo, hi, qm, qv):
+    """What the CUDA launch does for global groups [lo, hi), done by the C oracle on numpy views."""
+    from oracle import cpu as O
+    from lpmm.zero import GROUP, THRESHOLD, owned_pieces
+    b1, b2 = opt.hyper["betas"]
+    for i, a, b in owned_pieces(opt.numels, opt.gstart, lo, hi):
+        n = opt.numels[i]
+        e0, e1 = a * GROUP, min(b * GROUP, n)
+        cnt = e1 - e0
+        d = opt.gstart[i] + a - opt.lo
+        p = opt.params[i].reshape(-1)[e0:e1].numpy()
+        g = opt.grad_shard[d * GROUP: d * GROUP + cnt].numpy()
+        if n > THRESHOLD:
+            nb, ng = (cnt + 1) // 2, b - a
+            O.adamw4bit(p, g, opt.m_codes[d * 64: d * 64 + nb].numpy().view(np.uint8),
+                        opt.v_codes[d * 64: d * 64 + nb].numpy().view(np.uint8), opt.m_scale[d: d + ng].numpy(),
+                        opt.v_scale[d: d + ng].numpy(), qm, qv, b1, b2, opt.hyper["lr"], opt.hyper["weight_decay"],
+                        opt.hyper["eps"], float(opt.step_count))
+        else:
+            df = opt.fstart[i] + a - opt.f_lo
+            O.adamw_fp32(p, g, opt.m32[df * GROUP: df * GROUP + cnt].numpy(), opt.v32[df * GROUP: df * GROUP + cnt].numpy(),
+                         b1, b2, opt.hyper["lr"], opt.hyper["weight_decay"], opt.hyper["eps"], float(opt.step_count))
+
+
+def _make(world, rank, qm, qv):
+    from lpmm.zero import Zero1FusedAdamW
+
+    class OracleZero(Zero1FusedAdamW):
+        def _update(self, lo, hi):
+            _oracle_update(self, lo, hi, qm, qv)
+
+    opt = OracleZero(SHAPES, "cpu", rank=rank, world=world, **HYPER)
+    opt.init_params_normal_(0.02, seed=0)
+    return opt
+
+
+def _worker(rank, world, port, golden_dir, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    z = np.load(os.path.join(golden_dir, "qmaps.npz"))
+    opt = _make(world, rank, z["m"], z["v"])
+    for step in range(1, 4):
+        opt.set_grad_shard_from_full(_grads(step))
+        opt.step()
+    np.save(os.path.join(out_dir, f"flat_{rank}.npy"), opt.flat.numpy())
+    dist.destroy_process_group()
+
+
+def test_two_gloo_ranks_equal_the_unsharded_step(golden_dir, tmp_path):
+    z = np.load(os.path.join(golden_dir, "qmaps.npz"))
+    single = _make(1, 0, z["m"], z["v"])
+    for step in range(1, 4):
+        single.set_grad_shard_from_full(_grads(step))
+        single.step()
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_worker, args=(2, port, golden_dir, str(tmp_path)), nprocs=2, join=True)
+    flats = [np.load(tmp_path / f"flat_{r}.npy") for r in range(2)]
+    assert np.array_equal(flats[0].view(np.int32), flats[1].view(np.int32)), "ranks disagree after the all-gather"
+    for i, p in enumerate(single.params):
+        lo = single.gstart[i] * 128
+        got = flats[0][lo: lo + p.numel()]
+        assert np.array_equal(got.view(np.int32), p.reshape(-1).numpy().view(np.int32)), f"tensor {i} differs from unsharded"
