@@ -180,12 +180,14 @@ __device__ __forceinline__ void group_q4_fast(const LanePtrs& t, unsigned gl, in
   const uint32_t vc = *vcp;
   const float pm = __fmul_rn(qm_l, t.sm[gl]);  // lane i: qmap_m[i] * scale
   const float pv = __fmul_rn(qv_l, t.sv[gl]);
+#ifndef EXP_NO_PREFETCH
   if (pf) {
     prefetch_l2(pp + (size_t)pf * 128);
     prefetch_l2(gp + (size_t)pf * 128);
     prefetch_l2(mcp + (size_t)pf * 16);
     prefetch_l2(vcp + (size_t)pf * 16);
   }
+#endif
 
   float m[8], v[8];
   float am = 0.0f, av = 0.0f;
@@ -218,6 +220,123 @@ __device__ __forceinline__ void group_q4_fast(const LanePtrs& t, unsigned gl, in
   } else {  // scales outside the shared-reciprocal domain
     const uint2 o = quant8_exact(Sm, Sv, am, av, m[0], m[1], m[2], m[3], m[4], m[5], m[6], m[7], v[0], v[1], v[2],
                                  v[3], v[4], v[5], v[6], v[7]);
+    mo = o.x;
+    vo = o.y;
+  }
+  *mcp = mo;
+  *vcp = vo;
+  if (l16 == 0) {
+    t.sm[gl] = am;
+    t.sv[gl] = av;
+  }
+}
+
+// Packed constants of the fp32x2 path.
+struct Consts2 {
+  f2 beta1, beta2, omb1, omb2, wd, nlr, eps, nc1, nc2s, rc2s, half, mone, one, k16, km15;
+};
+
+// The same group update written with packed fp32x2 instructions: elements (2j, 2j+1) of a lane share
+// every multiply / add / fma, each half rounding exactly like the scalar instruction, so results
+// are bit-identical to group_q4_fast<true, VLIN>.  Uses the short sqrt/division sequences, so it is
+// selected only where those are (FAST).
+template <bool VLIN>
+__device__ __forceinline__ void group_q4_x2(const LanePtrs& t, unsigned gl, int l16, unsigned hmask,
+                                            const Consts2& c, const QMapSmem& Sm, const QMapSmem& Sv,
+                                            const LutEnt* __restrict__ lut_m, const LutEnt* __restrict__ lut_v,
+                                            float qm_l, float qv_l, unsigned pf) {
+  float* pp = t.p + (size_t)gl * 128;
+  const float* gp = t.g + (size_t)gl * 128;
+  uint32_t* mcp = t.mc + (size_t)gl * 16;
+  uint32_t* vcp = t.vc + (size_t)gl * 16;
+  f2x4 p = ldg_f2x4(pp);
+  const f2x4 g = ldg_f2x4(gp);
+  const uint32_t mc = *mcp;
+  const uint32_t vc = *vcp;
+  const float pm = __fmul_rn(qm_l, t.sm[gl]);  // lane i: qmap_m[i] * scale
+  const float pv = __fmul_rn(qv_l, t.sv[gl]);
+#ifndef EXP_NO_PREFETCH
+  if (pf) {
+    prefetch_l2(pp + (size_t)pf * 128);
+    prefetch_l2(gp + (size_t)pf * 128);
+    prefetch_l2(mcp + (size_t)pf * 16);
+    prefetch_l2(vcp + (size_t)pf * 16);
+  }
+#endif
+  f2 m[4], v[4];
+  float am = 0.0f, av = 0.0f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float m0a = __shfl_sync(hmask, pm, (int)(mc >> (8 * j)), 16);  // source lane = code (mod 16)
+    const float m0b = __shfl_sync(hmask, pm, (int)(mc >> (8 * j + 4)), 16);
+    const float v0a = __shfl_sync(hmask, pv, (int)(vc >> (8 * j)), 16);
+    const float v0b = __shfl_sync(hmask, pv, (int)(vc >> (8 * j + 4)), 16);
+    const f2 gj = g.v[j];
+    m[j] = f2_fma(c.beta1, f2_pack(m0a, m0b), f2_mul(c.omb1, gj));
+    v[j] = f2_fma(c.beta2, f2_pack(v0a, v0b), f2_mul(f2_mul(c.omb2, gj), gj));
+    float ma, mb, va, vb;
+    f2_unpack(m[j], ma, mb);
+    f2_unpack(v[j], va, vb);
+    am = fmaxf(am, fmaxf(fabsf(ma), fabsf(mb)));
+    av = fmaxf(av, fmaxf(va, vb));
+    // sqrt(v): y = rsqrt(max(v, FLT_MIN)); s = v*y; s += (v - s*s) * (y/2)
+    const f2 y = f2_pack(mufu_rsq(fmaxf(va, 1.17549435e-38f)), mufu_rsq(fmaxf(vb, 1.17549435e-38f)));
+    f2 s = f2_mul(v[j], y);
+    const f2 e = f2_fma(s, f2_mul(s, c.mone), v[j]);
+    s = f2_fma(e, f2_mul(c.half, y), s);
+    // nd = -(s / c2s + eps) * c1  (the negated denominator: what the division's residuals need)
+    f2 q = f2_mul(s, c.rc2s);
+    q = f2_fma(f2_fma(q, c.nc2s, s), c.rc2s, q);
+    const f2 nd = f2_mul(f2_add(q, c.eps), c.nc1);
+    // m / d: r = rcp(d) refined once, quotient corrected by its exact residual
+    float nda, ndb;
+    f2_unpack(nd, nda, ndb);
+    const f2 r0 = f2_pack(mufu_rcp(fabsf(nda)), mufu_rcp(fabsf(ndb)));
+    const f2 r = f2_fma(r0, f2_fma(nd, r0, c.one), r0);
+    const f2 qq = f2_mul(m[j], r);
+    const f2 quo = f2_fma(f2_fma(nd, qq, m[j]), r, qq);
+    // p -= lr * (quo + wd * p)
+    p.v[j] = f2_fma(c.nlr, f2_fma(c.wd, p.v[j], quo), p.v[j]);
+  }
+  stg_f2x4(pp, p);
+  am = hw_max(am, hmask);
+  av = hw_max(av, hmask);
+  uint32_t mo = 0, vo = 0;
+  if (udiv_ok(am) && udiv_ok(av)) {
+    const float rm = rcp_nr(am), rv = rcp_nr(av);
+    const f2 rm2 = f2_splat(rm), rv2 = f2_splat(rv), nam2 = f2_splat(-am), nav2 = f2_splat(-av);
+#pragma unroll
+    for (int j = 3; j >= 0; --j) {
+      f2 xm = f2_mul(m[j], rm2);
+      xm = f2_fma(f2_fma(xm, nam2, m[j]), rm2, xm);
+      f2 xv = f2_mul(v[j], rv2);
+      xv = f2_fma(f2_fma(xv, nav2, v[j]), rv2, xv);
+      float xa, xb;
+      f2_unpack(xm, xa, xb);
+      mo = (mo << 4) + (uint32_t)lut_code(lut_m, xb);
+      mo = (mo << 4) + (uint32_t)lut_code(lut_m, xa);
+      if (VLIN) {
+        float ta, tb;
+        f2_unpack(f2_fma(xv, c.k16, c.km15), ta, tb);
+        vo = vo * 16u + __float2uint_ru(tb);
+        vo = vo * 16u + __float2uint_ru(ta);
+      } else {
+        f2_unpack(xv, xa, xb);
+        vo = (vo << 4) + (uint32_t)lut_code(lut_v, xb);
+        vo = (vo << 4) + (uint32_t)lut_code(lut_v, xa);
+      }
+    }
+    if (am == 0.0f) mo = 0xFFFFFFFFu;  // 0/0 = NaN -> code 15 for the whole group
+    if (av == 0.0f) vo = 0xFFFFFFFFu;
+  } else {  // scales outside the shared-reciprocal domain
+    float mm[8], vv[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      f2_unpack(m[j], mm[2 * j], mm[2 * j + 1]);
+      f2_unpack(v[j], vv[2 * j], vv[2 * j + 1]);
+    }
+    const uint2 o = quant8_exact(Sm, Sv, am, av, mm[0], mm[1], mm[2], mm[3], mm[4], mm[5], mm[6], mm[7], vv[0],
+                                 vv[1], vv[2], vv[3], vv[4], vv[5], vv[6], vv[7]);
     mo = o.x;
     vo = o.y;
   }
@@ -299,9 +418,30 @@ __device__ __forceinline__ void run_groups(const Table& tab, const Consts& c, co
           unsigned gl = (unsigned)(gi - tstart);           // groups per tensor fit 32 bits (host-checked)
           const unsigned lim = (unsigned)(fend - tstart);
           const unsigned st = (unsigned)stride;
-          for (; gl < lim; gl += st)
-            group_q4_fast<FAST, VLIN>(lp, gl, l16, hmask, c, Sm, Sv, lut_m, lut_v, qm_l, qv_l,
-                                      (gl + st < lim) ? st : 0u);
+          if (FAST) {
+            Consts2 c2;
+            c2.beta1 = f2_splat(c.beta1);
+            c2.beta2 = f2_splat(c.beta2);
+            c2.omb1 = f2_splat(c.omb1);
+            c2.omb2 = f2_splat(c.omb2);
+            c2.wd = f2_splat(c.wd);
+            c2.nlr = f2_splat(-c.lr);
+            c2.eps = f2_splat(c.eps);
+            c2.nc1 = f2_splat(-c.c1);
+            c2.nc2s = f2_splat(-c.c2s);
+            c2.rc2s = f2_splat(c.rc2s);
+            c2.half = f2_splat(0.5f);
+            c2.mone = f2_splat(-1.0f);
+            c2.one = f2_splat(1.0f);
+            c2.k16 = f2_splat(16.0f);
+            c2.km15 = f2_splat(-1.5f);
+            for (; gl < lim; gl += st)
+              group_q4_x2<VLIN>(lp, gl, l16, hmask, c2, Sm, Sv, lut_m, lut_v, qm_l, qv_l, (gl + st < lim) ? st : 0u);
+          } else {
+            for (; gl < lim; gl += st)
+              group_q4_fast<FAST, VLIN>(lp, gl, l16, hmask, c, Sm, Sv, lut_m, lut_v, qm_l, qv_l,
+                                        (gl + st < lim) ? st : 0u);
+          }
           gi = tstart + gl;
         }
       }

@@ -204,4 +204,51 @@ __device__ __forceinline__ float div_rn_fast(float m, float d) {
   return __fmaf_rn(rem, r, q);
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Packed fp32x2 arithmetic (sm_100 add/mul/fma .f32x2): one instruction, two IEEE round-to-nearest
+// results, each bit-identical to the scalar instruction on its half.  Values live in 64-bit
+// registers (low half = element 2j, high half = element 2j+1).
+// ---------------------------------------------------------------------------------------------
+typedef unsigned long long f2;
+
+__device__ __forceinline__ f2 f2_pack(float lo, float hi) {
+  f2 r;
+  asm("mov.b64 %0, {%1,%2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ f2 f2_splat(float x) { return f2_pack(x, x); }
+__device__ __forceinline__ void f2_unpack(f2 v, float& lo, float& hi) {
+  asm("mov.b64 {%0,%1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f2 f2_mul(f2 a, f2 b) {
+  f2 r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ f2 f2_add(f2 a, f2 b) {
+  f2 r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ f2 f2_fma(f2 a, f2 b, f2 c) {
+  f2 r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+
+struct f2x4 {
+  f2 v[4];
+};
+__device__ __forceinline__ f2x4 ldg_f2x4(const float* ptr) {
+  f2x4 r;
+  asm volatile("ld.global.L1::no_allocate.v4.b64 {%0,%1,%2,%3}, [%4];"
+               : "=l"(r.v[0]), "=l"(r.v[1]), "=l"(r.v[2]), "=l"(r.v[3])
+               : "l"(ptr));
+  return r;
+}
+__device__ __forceinline__ void stg_f2x4(float* ptr, const f2x4& r) {
+  asm volatile("st.global.v4.b64 [%4], {%0,%1,%2,%3};" ::"l"(r.v[0]), "l"(r.v[1]), "l"(r.v[2]), "l"(r.v[3]), "l"(ptr));
+}
+
 }  // namespace lpmm_b200
