@@ -1,0 +1,102 @@
+"""``lpmm.functional`` and the ``lpmm.cpp_extension.quantization`` stand-ins on a B200: against the
+reference's own compiled pack/unpack kernels when ``oracle/_ref`` is present, against the torch-op
+restatement otherwise and always.  Codes and scales bit-identical; dequantized values bit-identical."""
+import numpy as np
+import pytest
+import torch
+
+from gpu_helpers import bits_equal, device, device_qmaps, load_reference_extension, student_t
+
+pytestmark = pytest.mark.gpu
+
+
+def _special_values(qmap):
+    q = qmap.cpu()
+    mids = (q[:-1] + q[1:]) * 0.5
+    up = torch.nextafter(mids, torch.full_like(mids, 2.0))
+    dn = torch.nextafter(mids, torch.full_like(mids, -2.0))
+    extra = torch.tensor([0.0, -0.0, 1.0, -1.0, 2.0, -2.0, 1e-30, -1e-30, float("inf"), float("nan"), 1.1249, 0.5, 1e-8])
+    return torch.cat([q, mids, up, dn, extra])
+
+
+@pytest.mark.parametrize("which", ["m", "v"])
+def test_pack_unpack_match_reference_kernels(qmaps, which):
+    from lpmm.cpp_extension import quantization as mine
+    ref = load_reference_extension("quantization")
+    qm, qv, _ = device_qmaps(qmaps)
+    qmap = qm if which == "m" else qv
+    torch.manual_seed(0)
+    x = torch.cat([_special_values(qmap), torch.rand(2048 * 5) * 2.2 - 1.1])
+    x = torch.cat([x, torch.zeros((-x.numel()) % 2048)]).to(device()).view(-1, 2048)
+    packed = mine.pack_nonlinear(x, qmap, 4, False)
+    assert packed.dtype == torch.int8 and packed.numel() == x.numel() // 2 + 1 and int(packed[-1]) == 0
+    from oracle import torch_ref as T
+    assert torch.equal(packed, T.pack_nonlinear(x, qmap)), "codes differ from the restated rule"
+    out = mine.unpack_nonlinear(packed, qmap, 4, x.shape[0], 2048)
+    assert out.shape == x.shape and bits_equal(out, T.unpack_nonlinear(packed, qmap, x.shape[0], 2048))
+    if ref is not None:
+        r_packed = ref.pack_nonlinear(x, qmap, 4, False)
+        torch.cuda.synchronize()
+        assert torch.equal(packed[:-1], r_packed[:-1]), "codes differ from the reference's kernel"
+        assert bits_equal(out, ref.unpack_nonlinear(r_packed, qmap, 4, x.shape[0], 2048))
+
+
+def test_pack_argument_checks(qmaps):
+    from lpmm.cpp_extension import quantization as mine
+    qm, _, _ = device_qmaps(qmaps)
+    x = torch.zeros(2, 2048, device=device())
+    with pytest.raises(RuntimeError):
+        mine.pack_nonlinear(x.cpu(), qm, 4, False)
+    with pytest.raises(RuntimeError):
+        mine.pack_nonlinear(x.view(-1), qm, 4, False)
+    with pytest.raises(RuntimeError):
+        mine.pack_nonlinear(x, qm, 9, False)
+    with pytest.raises(NotImplementedError):
+        mine.pack_nonlinear(x, qm, 4, True)
+    with pytest.raises(RuntimeError):
+        mine.unpack_nonlinear(torch.zeros(10, device=device()), qm, 4, 1, 2048)
+
+
+_META = dict(b=4, quant_type=None, round_type="real-nearest", gp_sz=128, signed=None)
+
+
+@pytest.mark.parametrize("shape", [(4096,), (4097,), (127,), (300, 130), (3, 3, 24, 24), (5000, 1), (2, 3, 4, 5, 6)])
+@pytest.mark.parametrize("scale_type,which", [("group", "m"), ("rank1", "v"), ("group", "v")])
+def test_vectorwise_quant_dequant_match_restated_reference(qmaps, shape, scale_type, which):
+    import lpmm.functional as F
+    from oracle import torch_ref as T
+    qm, qv, _ = device_qmaps(qmaps)
+    qmap = qm if which == "m" else qv
+    x = student_t(shape, 77, zero_fraction=0.1)
+    if which == "v":
+        x = x * x
+    kw = dict(_META, quant_type="nonlinear" if which == "m" else "power-1", signed=(which == "m"), scale_type=scale_type)
+    codes, md = F.vectorwise_quant(x, qmap=qmap, shape=x.shape, **kw)
+    o_codes, o_md = T.vectorwise_quant(x, qmap, scale_type)
+    assert codes.dtype == torch.int8 and codes.numel() == o_codes.numel()
+    assert torch.equal(codes.view(torch.uint8), o_codes.view(torch.uint8)), "codes differ"
+    assert md["scaled_shape"] == o_md["scaled_shape"] and md["dtype"] == x.dtype and md["stride"] == x.stride()
+    if scale_type == "rank1" and len(shape) > 1:
+        assert md["dim"] == len(shape) and md["max1"] is None
+        for a, b in zip(md["max_dims"], o_md["max_dims"]):
+            assert a.shape == b.shape and bits_equal(a, b)
+    else:
+        assert bits_equal(md["max1"], o_md["max1"]) and md["max1"].shape == o_md["max1"].shape
+    back = F.vectorwise_dequant(codes, qmap=qmap, shape=x.shape, **{**kw, **md})
+    o_back = T.vectorwise_dequant(o_codes, qmap, scale_type, x.shape, o_md)
+    assert back.shape == x.shape and bits_equal(back, o_back)
+
+
+def test_vectorwise_quant_rejects_what_is_not_built(qmaps):
+    import lpmm.functional as F
+    qm, _, _ = device_qmaps(qmaps)
+    x = torch.randn(4096, device=device())
+    base = dict(_META, quant_type="nonlinear", signed=True, scale_type="group", qmap=qm, shape=x.shape)
+    with pytest.raises(NotImplementedError):
+        F.vectorwise_quant(x, **{**base, "b": 8})
+    with pytest.raises(NotImplementedError):
+        F.vectorwise_quant(x, **{**base, "round_type": "sr"})
+    with pytest.raises(NotImplementedError):
+        F.vectorwise_quant(x, **{**base, "scale_type": "dim0"})
+    with pytest.raises(ValueError):
+        F.vectorwise_quant(x, **{**base, "quant_type": "bogus"})
