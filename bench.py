@@ -240,7 +240,7 @@ def run_own(args):
     else:
         from lpmm.zero import Zero1FusedAdamW
         torch.manual_seed(0)
-        opt = Zero1FusedAdamW(shapes, dev, **HYPER)
+        opt = Zero1FusedAdamW(shapes, dev, gather=args.gather, **HYPER)
         opt.init_params_normal_(0.02, seed=0)
         student_t_(opt.grad_shard.view(-1), 100003 + rank, rows_outliers=False)
 
@@ -294,6 +294,17 @@ def run_own(args):
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "traffic": NCU_TRAFFIC_PER_PARAM * (k_bytes / BYTES_Q4), "peak_kind": f"of {peak_kind}",
                 "kernel": "adamw4bit_multi_kernel", "algorithmic_bytes_per_launch": k_bytes, "launch_ms": k_ms}
+    if world > 1 and args.gather == "fused":
+        # fused update + peer stores: the target time is the slower of HBM and NVLink; this kernel is NVLink-bound
+        link_bytes = 4.0 * opt.shard_groups * 128 * (world - 1)      # sent (and received) per rank per launch
+        link_peak = 770.0                                            # GB/s per direction, measured peer copy on this pool
+        t_hbm, t_link = k_bytes / (peak * 1e9), link_bytes / (link_peak * 1e9)
+        roofline = {"bound": "nvlink" if t_link >= t_hbm else "hbm", "achieved": link_bytes / (k_ms * 1e-3) / 1e9,
+                    "peak": link_peak, "unit": "GB/s", "frac": max(t_hbm, t_link) / (k_ms * 1e-3), "traffic": None,
+                    "peak_kind": "measured peer-copy rate of this pool (770 GB/s per direction); HBM side of measured",
+                    "kernel": "adamw4bit_multi_kernel (update + stores to all peers)", "launch_ms": k_ms,
+                    "algorithmic_bytes_per_launch": k_bytes, "nvlink_bytes_sent_per_rank_per_launch": link_bytes,
+                    "target_ms": max(t_hbm, t_link) * 1e3}
 
     # end to end through the public API with the gradients coming from pinned host memory
     e2e = None
@@ -376,7 +387,9 @@ def run_own(args):
             "vs_baseline": None, "dtype": "f32", "data": "synthetic (seeded N(0,0.02) params, Student-t(3)*1e-3 grads with 1% outlier rows; one gradient set reused every step)",
             "config": {"workload": "llama7b_shaped_fp32_list_fused_4bit_adamw", "params": total, "tensors": len(shapes),
                        "params_4bit": nq, "params_fp32_state": nf, "layers": args.layers,
-                       "parallelism": "single GPU" if world == 1 else f"ZeRO-1 over {world} GPUs, group-aligned shards, NCCL all-gather of fp32 params",
+                       "parallelism": "single GPU" if world == 1 else (
+                           f"ZeRO-1 over {world} GPUs, group-aligned shards, fp32 params reach the peers by "
+                           + ("NVLink stores inside the update kernel" if args.gather == "fused" else "an NCCL all-gather after the update")),
                        "l2": "inputs (>= 90 GB touched per step) exceed the 126 MB L2; no explicit flush"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": n_launch, "roofline": roofline, "cpu_baseline": cpu,
         }
@@ -394,6 +407,8 @@ def main():
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
     ap.add_argument("--layers", type=int, default=32, help="transformer layers of the list (32 = the 7B workload)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
+                    help="N > 1: parameters reach the peers by stores inside the update kernel, or by an NCCL all-gather after it")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

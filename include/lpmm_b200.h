@@ -104,6 +104,18 @@ int lpmm_b200_adamw4bit_multi_tensor(const lpmm_b200_tensor* tensors, int n_tens
                                      const float* exp_avg_sq_qmap, lpmm_b200_hyper hyper, int64_t group_begin,
                                      int64_t group_end, void* stream);
 
+/* The same step for a ZeRO-1 rank, with the all-gather of the updated parameters folded into the
+ * kernel.  It has no counterpart in the reference (which has no distributed step).
+ * Every parameter this call updates is stored at its own address AND at that address plus each of
+ * the n_peers (<= 7) byte offsets, which must lead to the same element of the other ranks' copies
+ * of the parameter buffer in peer-mapped memory (offsets multiples of 32).  The transfer over
+ * NVLink thus overlaps the update group by group.  The caller orders the ranks afterwards (any
+ * stream-ordered barrier across the ranks) before parameters are read. */
+int lpmm_b200_adamw4bit_multi_tensor_peers(const lpmm_b200_tensor* tensors, int n_tensors, const float* exp_avg_qmap,
+                                           const float* exp_avg_sq_qmap, lpmm_b200_hyper hyper, int64_t group_begin,
+                                           int64_t group_end, const int64_t* peer_byte_offsets, int n_peers,
+                                           void* stream);
+
 /* Number of 128-element groups of a tensor list (the size of the index space above), or a
  * negative status.  Host-only arithmetic. */
 int64_t lpmm_b200_count_groups(const lpmm_b200_tensor* tensors, int n_tensors);

@@ -56,6 +56,18 @@ struct Consts {
   float c2s, rc2s;  // sqrt(1 - beta2^step) and its correctly rounded reciprocal
 };
 
+// Peers of a ZeRO-1 step: byte offsets from an address in this GPU's flat parameter buffer to the
+// same element in each peer's buffer (peer-mapped memory).  Every updated parameter is stored
+// locally and at each of these offsets, so the all-gather happens inside the update kernel,
+// group by group, over NVLink.
+struct PeerInfo {
+  int n;
+  long long off[7];
+};
+__device__ __forceinline__ void peer_store1(float* addr, float val, const PeerInfo& pi) {
+  for (int i = 0; i < pi.n; ++i) *reinterpret_cast<float*>(reinterpret_cast<char*>(addr) + pi.off[i]) = val;
+}
+
 __device__ __forceinline__ float upd_m(const Consts& c, float m0, float g) {
   return __fmaf_rn(c.beta1, m0, __fmul_rn(c.omb1, g));
 }
@@ -89,7 +101,8 @@ __device__ __forceinline__ void prefetch_l2(const void* ptr) {
 // (fused_adamw_kernel.cu:114,130-143,160-165), IEEE sqrt and division, the reference's search.
 // The fast path falls back to this before it has stored anything.
 __device__ __noinline__ void group_q4_generic(const TDesc& t, long long gl, int l16, unsigned hmask,
-                                              const Consts& c, const QMapSmem& Sm, const QMapSmem& Sv) {
+                                              const Consts& c, const QMapSmem& Sm, const QMapSmem& Sv,
+                                              const PeerInfo& pi) {
   const long long e0 = gl * 128 + l16 * 8;
   const long long n = t.numel;
   uint8_t* mb = reinterpret_cast<uint8_t*>(t.m) + (e0 >> 1);
@@ -109,7 +122,9 @@ __device__ __noinline__ void group_q4_generic(const TDesc& t, long long gl, int 
       const float v0 = __fmul_rn(Sv.qmap[(vbyte >> (4 * (k & 1))) & 15u], sv);
       m[k] = upd_m(c, m0, g);
       v[k] = upd_v(c, v0, g);
-      t.p[e0 + k] = upd_p<false>(c, t.p[e0 + k], m[k], v[k]);
+      const float pn = upd_p<false>(c, t.p[e0 + k], m[k], v[k]);
+      t.p[e0 + k] = pn;
+      peer_store1(t.p + e0 + k, pn, pi);
       am = fmaxf(am, fabsf(m[k]));
       av = fmaxf(av, v[k]);
     }
@@ -169,7 +184,7 @@ template <bool FAST, bool VLIN>
 __device__ __forceinline__ void group_q4_fast(const LanePtrs& t, unsigned gl, int l16, unsigned hmask,
                                               const Consts& c, const QMapSmem& Sm, const QMapSmem& Sv,
                                               const LutEnt* __restrict__ lut_m, const LutEnt* __restrict__ lut_v,
-                                              float qm_l, float qv_l, unsigned pf) {
+                                              float qm_l, float qv_l, unsigned pf, const PeerInfo& pi) {
   float* pp = t.p + (size_t)gl * 128;
   const float* gp = t.g + (size_t)gl * 128;
   uint32_t* mcp = t.mc + (size_t)gl * 16;
@@ -202,6 +217,7 @@ __device__ __forceinline__ void group_q4_fast(const LanePtrs& t, unsigned gl, in
     av = fmaxf(av, v[k]);
   }
   stg_f8(pp, p);
+  for (int i = 0; i < pi.n; ++i) stg_f8(reinterpret_cast<float*>(reinterpret_cast<char*>(pp) + pi.off[i]), p);
   am = hw_max(am, hmask);
   av = hw_max(av, hmask);
   uint32_t mo = 0, vo = 0;
@@ -240,11 +256,11 @@ struct Consts2 {
 // every multiply / add / fma, each half rounding exactly like the scalar instruction, so results
 // are bit-identical to group_q4_fast<true, VLIN>.  Uses the short sqrt/division sequences, so it is
 // selected only where those are (FAST).
-template <bool VLIN>
+template <bool VLIN, bool PEERS>
 __device__ __forceinline__ void group_q4_x2(const LanePtrs& t, unsigned gl, int l16, unsigned hmask,
                                             const Consts2& c, const QMapSmem& Sm, const QMapSmem& Sv,
                                             const LutEnt* __restrict__ lut_m, const LutEnt* __restrict__ lut_v,
-                                            float qm_l, float qv_l, unsigned pf) {
+                                            float qm_l, float qv_l, unsigned pf, const PeerInfo& pi) {
   float* pp = t.p + (size_t)gl * 128;
   const float* gp = t.g + (size_t)gl * 128;
   uint32_t* mcp = t.mc + (size_t)gl * 16;
@@ -299,6 +315,9 @@ __device__ __forceinline__ void group_q4_x2(const LanePtrs& t, unsigned gl, int 
     p.v[j] = f2_fma(c.nlr, f2_fma(c.wd, p.v[j], quo), p.v[j]);
   }
   stg_f2x4(pp, p);
+  if (PEERS) {
+    for (int i = 0; i < pi.n; ++i) stg_f2x4(reinterpret_cast<float*>(reinterpret_cast<char*>(pp) + pi.off[i]), p);
+  }
   am = hw_max(am, hmask);
   av = hw_max(av, hmask);
   uint32_t mo = 0, vo = 0;
@@ -350,7 +369,7 @@ __device__ __forceinline__ void group_q4_x2(const LanePtrs& t, unsigned gl, int 
 
 // fp32-state tensors (the numel <= threshold fallback), 128 elements per half-warp step.
 template <bool FAST>
-__device__ __forceinline__ void group_fp32(const TDesc& t, long long gl, int l16, const Consts& c) {
+__device__ __forceinline__ void group_fp32(const TDesc& t, long long gl, int l16, const Consts& c, const PeerInfo& pi) {
   const long long e0 = gl * 128 + l16 * 8;
   float* mp = reinterpret_cast<float*>(t.m);
   float* vp = reinterpret_cast<float*>(t.v);
@@ -368,6 +387,7 @@ __device__ __forceinline__ void group_fp32(const TDesc& t, long long gl, int l16
     stg_f8(mp + e0, m);
     stg_f8(vp + e0, v);
     stg_f8(t.p + e0, p);
+    for (int i = 0; i < pi.n; ++i) stg_f8(reinterpret_cast<float*>(reinterpret_cast<char*>(t.p + e0) + pi.off[i]), p);
   } else {
     for (int k = 0; k < 8; ++k) {
       const long long e = e0 + k;
@@ -377,7 +397,9 @@ __device__ __forceinline__ void group_fp32(const TDesc& t, long long gl, int l16
         const float v = upd_v(c, vp[e], g);
         mp[e] = m;
         vp[e] = v;
-        t.p[e] = upd_p<false>(c, t.p[e], m, v);
+        const float pn = upd_p<false>(c, t.p[e], m, v);
+        t.p[e] = pn;
+        peer_store1(t.p + e, pn, pi);
       }
     }
   }
@@ -386,10 +408,10 @@ __device__ __forceinline__ void group_fp32(const TDesc& t, long long gl, int l16
 // The tensor loop is uniform across the CTA (descriptor fields come from the launch parameters
 // through uniform loads); each half-warp walks its own arithmetic progression of global group
 // indices gi = gbeg + id, gbeg + id + stride, ... through the tensors in order.
-template <bool FAST, bool VLIN>
+template <bool FAST, bool VLIN, bool PEERS>
 __device__ __forceinline__ void run_groups(const Table& tab, const Consts& c, const QMapSmem& Sm,
                                            const QMapSmem& Sv, const LutEnt* lut_m, const LutEnt* lut_v,
-                                           bool tables_ok, long long gbeg, long long gend) {
+                                           bool tables_ok, long long gbeg, long long gend, const PeerInfo& pi) {
   const int l16 = threadIdx.x & 15;
   const unsigned hmask = 0xFFFFu << (threadIdx.x & 16);
   long long gi = gbeg + (long long)blockIdx.x * HW_PER_CTA + (threadIdx.x >> 4);
@@ -436,26 +458,27 @@ __device__ __forceinline__ void run_groups(const Table& tab, const Consts& c, co
             c2.k16 = f2_splat(16.0f);
             c2.km15 = f2_splat(-1.5f);
             for (; gl < lim; gl += st)
-              group_q4_x2<VLIN>(lp, gl, l16, hmask, c2, Sm, Sv, lut_m, lut_v, qm_l, qv_l, (gl + st < lim) ? st : 0u);
+              group_q4_x2<VLIN, PEERS>(lp, gl, l16, hmask, c2, Sm, Sv, lut_m, lut_v, qm_l, qv_l, (gl + st < lim) ? st : 0u, pi);
           } else {
             for (; gl < lim; gl += st)
               group_q4_fast<FAST, VLIN>(lp, gl, l16, hmask, c, Sm, Sv, lut_m, lut_v, qm_l, qv_l,
-                                        (gl + st < lim) ? st : 0u);
+                                        (gl + st < lim) ? st : 0u, pi);
           }
           gi = tstart + gl;
         }
       }
-      for (; gi < tend; gi += stride) group_q4_generic(t, gi - tstart, l16, hmask, c, Sm, Sv);
+      for (; gi < tend; gi += stride) group_q4_generic(t, gi - tstart, l16, hmask, c, Sm, Sv, pi);
     } else {
-      for (; gi < tend; gi += stride) group_fp32<FAST>(t, gi - tstart, l16, c);
+      for (; gi < tend; gi += stride) group_fp32<FAST>(t, gi - tstart, l16, c, pi);
     }
   }
 }
 
-template <bool HAS_Q4, bool FAST>
+template <bool HAS_Q4, bool FAST, bool PEERS>
 __global__ void __launch_bounds__(CTA_THREADS, CTAS_PER_SM)
 adamw4bit_multi_kernel(const __grid_constant__ Table tab, const float* __restrict__ qmap_m,
-                       const float* __restrict__ qmap_v, const lpmm_b200_hyper h, long long gbeg, long long gend) {
+                       const float* __restrict__ qmap_v, const lpmm_b200_hyper h, long long gbeg, long long gend,
+                       const PeerInfo pi) {
   extern __shared__ __align__(16) unsigned char dyn_smem[];
   __shared__ QMapSmem Sm, Sv;
   LutEnt* lut_m = reinterpret_cast<LutEnt*>(dyn_smem);
@@ -479,8 +502,8 @@ adamw4bit_multi_kernel(const __grid_constant__ Table tab, const float* __restric
   c.c1 = __fsub_rn(1.0f, powf(h.beta1, h.step));
   c.c2s = __fsqrt_rn(__fsub_rn(1.0f, powf(h.beta2, h.step)));
   c.rc2s = __frcp_rn(c.c2s);
-  if (vlin) run_groups<FAST, true>(tab, c, Sm, Sv, lut_m, lut_v, tables_ok, gbeg, gend);
-  else run_groups<FAST, false>(tab, c, Sm, Sv, lut_m, lut_v, tables_ok, gbeg, gend);
+  if (vlin) run_groups<FAST, true, PEERS>(tab, c, Sm, Sv, lut_m, lut_v, tables_ok, gbeg, gend, pi);
+  else run_groups<FAST, false, PEERS>(tab, c, Sm, Sv, lut_m, lut_v, tables_ok, gbeg, gend, pi);
 }
 
 __global__ void bias_corrections_kernel(float beta1, float beta2, float step, float* out) {
@@ -499,25 +522,35 @@ static bool fast_math_ok(const lpmm_b200_hyper& h) {
   return dmin >= 0x1p-50 && h.eps <= 0x1p30f && c2s_min >= 0x1p-20;
 }
 
-template <bool HAS_Q4, bool FAST>
+template <bool HAS_Q4, bool FAST, bool PEERS>
 static cudaError_t launch_one(const Table& tab, unsigned grid, const float* qm, const float* qv,
-                              const lpmm_b200_hyper& h, long long lo, long long hi, cudaStream_t st) {
+                              const lpmm_b200_hyper& h, long long lo, long long hi, cudaStream_t st,
+                              const PeerInfo& pi) {
   static bool attr_set[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   const size_t smem = HAS_Q4 ? DYN_SMEM : 0;
   if (HAS_Q4 && dev >= 0 && dev < 64 && !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(adamw4bit_multi_kernel<HAS_Q4, FAST>,
+    cudaError_t e = cudaFuncSetAttribute(adamw4bit_multi_kernel<HAS_Q4, FAST, PEERS>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DYN_SMEM);
     if (e != cudaSuccess) return e;
     attr_set[dev] = true;
   }
-  adamw4bit_multi_kernel<HAS_Q4, FAST><<<grid, CTA_THREADS, smem, st>>>(tab, qm, qv, h, lo, hi);
+  adamw4bit_multi_kernel<HAS_Q4, FAST, PEERS><<<grid, CTA_THREADS, smem, st>>>(tab, qm, qv, h, lo, hi, pi);
   return cudaGetLastError();
 }
 
+template <bool HAS_Q4, bool PEERS>
+static cudaError_t launch_fast_or_exact(bool fast, const Table& tab, unsigned grid, const float* qm, const float* qv,
+                                        const lpmm_b200_hyper& h, long long lo, long long hi, cudaStream_t st,
+                                        const PeerInfo& pi) {
+  return fast ? launch_one<HAS_Q4, true, PEERS>(tab, grid, qm, qv, h, lo, hi, st, pi)
+              : launch_one<HAS_Q4, false, PEERS>(tab, grid, qm, qv, h, lo, hi, st, pi);
+}
+
 static int launch_multi(const lpmm_b200_tensor* ts, int n, const float* qm, const float* qv,
-                        const lpmm_b200_hyper& h, int64_t gbeg, int64_t gend, cudaStream_t st) {
+                        const lpmm_b200_hyper& h, int64_t gbeg, int64_t gend, cudaStream_t st,
+                        const PeerInfo& pi = PeerInfo{}) {
   // `ts` may hold more than MAX_TENSORS entries: walk it in windows, each window one launch over
   // the part of [gbeg, gend) that falls inside it.
   static thread_local Table tab;  // 28.9 KB; copied into the launch parameters by the runtime
@@ -562,13 +595,12 @@ static int launch_multi(const lpmm_b200_tensor* ts, int n, const float* qm, cons
     const int64_t cap = (int64_t)num_sms() * CTAS_PER_SM;
     if (grid > cap) grid = cap;
     cudaError_t e;
-    if (any_q4) {
-      e = fast ? launch_one<true, true>(tab, (unsigned)grid, qm, qv, h, lo, hi, st)
-               : launch_one<true, false>(tab, (unsigned)grid, qm, qv, h, lo, hi, st);
-    } else {
-      e = fast ? launch_one<false, true>(tab, (unsigned)grid, qm, qv, h, lo, hi, st)
-               : launch_one<false, false>(tab, (unsigned)grid, qm, qv, h, lo, hi, st);
-    }
+    if (pi.n > 0)
+      e = any_q4 ? launch_fast_or_exact<true, true>(fast, tab, (unsigned)grid, qm, qv, h, lo, hi, st, pi)
+                 : launch_fast_or_exact<false, true>(fast, tab, (unsigned)grid, qm, qv, h, lo, hi, st, pi);
+    else
+      e = any_q4 ? launch_fast_or_exact<true, false>(fast, tab, (unsigned)grid, qm, qv, h, lo, hi, st, pi)
+                 : launch_fast_or_exact<false, false>(fast, tab, (unsigned)grid, qm, qv, h, lo, hi, st, pi);
     LPMM_CUDA_TRY(e);
   }
   return LPMM_B200_OK;
@@ -670,4 +702,26 @@ extern "C" int lpmm_b200_bias_corrections(float beta1, float beta2, float step, 
   bias_corrections_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(beta1, beta2, step, out);
   LPMM_CUDA_TRY(cudaGetLastError());
   return LPMM_B200_OK;
+}
+
+extern "C" int lpmm_b200_adamw4bit_multi_tensor_peers(const lpmm_b200_tensor* tensors, int n_tensors,
+                                                      const float* exp_avg_qmap, const float* exp_avg_sq_qmap,
+                                                      lpmm_b200_hyper hyper, int64_t group_begin, int64_t group_end,
+                                                      const int64_t* peer_byte_offsets, int n_peers, void* stream) {
+  if (n_peers < 0 || n_peers > 7) return LPMM_B200_ERR_BAD_SIZE;
+  if (n_peers > 0 && !peer_byte_offsets) return LPMM_B200_ERR_NULL_POINTER;
+  int rc = check_list(tensors, n_tensors, false, exp_avg_qmap, exp_avg_sq_qmap);
+  if (rc != LPMM_B200_OK) return rc;
+  const int64_t total = lpmm_b200_count_groups(tensors, n_tensors);
+  if (group_end < 0) group_end = total;
+  if (group_begin < 0 || group_begin > group_end || group_end > total) return LPMM_B200_ERR_BAD_SIZE;
+  if (group_begin == group_end) return LPMM_B200_OK;
+  PeerInfo pi = {};
+  pi.n = n_peers;
+  for (int i = 0; i < n_peers; ++i) {
+    if (peer_byte_offsets[i] % 32 != 0) return LPMM_B200_ERR_BAD_SIZE;  // keeps the 256-bit stores aligned
+    pi.off[i] = peer_byte_offsets[i];
+  }
+  return launch_multi(tensors, n_tensors, exp_avg_qmap, exp_avg_sq_qmap, hyper, group_begin, group_end,
+                      (cudaStream_t)stream, pi);
 }

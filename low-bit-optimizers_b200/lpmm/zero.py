@@ -9,7 +9,11 @@ ranges of equal length S = ceil(G / world) and rank r
 * keeps 4-bit codes, scales, fp32 moments of small tensors and gradients ONLY for its range,
 * updates its range of the (replicated, flat) fp32 parameter buffer with the same multi-tensor
   launch as the unsharded step, restricted to ``[r*S, (r+1)*S)``,
-* takes part in one ``all_gather_into_tensor`` of the flat parameter buffer (NCCL on GPUs).
+* makes the updated range visible to all ranks: either one NCCL ``all_gather_into_tensor`` of the
+  flat parameter buffer after the launch (``gather="nccl"``), or -- ``gather="fused"`` -- the launch
+  itself stores every updated parameter into all peers' buffers through peer-mapped symmetric
+  memory (plain vectorised stores over NVLink, no multicast), so transfer and update overlap group
+  by group and only a barrier follows.
 
 The result is bit-identical to the unsharded step.  A shard may cut a tensor but never a group.
 """
@@ -64,7 +68,7 @@ class Zero1FusedAdamW:
     """
 
     def __init__(self, shapes, device, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=1e-2, process_group=None,
-                 rank=None, world=None):
+                 rank=None, world=None, gather="nccl"):
         from .functional import create_general_qmap
         self.shapes = [tuple(s) for s in shapes]
         self.numels = [int(torch.Size(s).numel()) for s in self.shapes]
@@ -77,7 +81,21 @@ class Zero1FusedAdamW:
         self.gstart, self.total_groups, self.shard_groups = partition(self.numels, self.world)
         self.lo, self.hi = owned_range(self.rank, self.total_groups, self.shard_groups)
         S = self.shard_groups
-        self.flat = torch.zeros(self.world * S * GROUP, dtype=torch.float32, device=self.device)
+        if gather not in ("nccl", "fused"):
+            raise ValueError("gather must be 'nccl' or 'fused'")
+        self.gather = gather if self.world > 1 else "nccl"
+        self.peer_offsets = None
+        if self.gather == "fused":
+            import torch.distributed._symmetric_memory as symm_mem
+            self.flat = symm_mem.empty(self.world * S * GROUP, dtype=torch.float32, device=self.device)
+            self.flat.zero_()
+            self._symm = symm_mem.rendezvous(self.flat, process_group if process_group is not None else dist.group.WORLD)
+            ptrs = list(self._symm.buffer_ptrs)
+            mine = self.flat.data_ptr()
+            self.peer_offsets = [int(ptrs[r]) - mine for r in range(self.world) if r != self.rank]
+            self._flag = torch.zeros(1, dtype=torch.float32, device=self.device)
+        else:
+            self.flat = torch.zeros(self.world * S * GROUP, dtype=torch.float32, device=self.device)
         self.params = [self.flat[gs * GROUP: gs * GROUP + n].view(s)
                        for s, n, gs in zip(self.shapes, self.numels, self.gstart)]
         self.grad_shard = torch.zeros(S * GROUP, dtype=torch.float32, device=self.device)
@@ -152,12 +170,21 @@ class Zero1FusedAdamW:
         b1, b2 = self.hyper["betas"]
         h = N.Hyper(b1, b2, self.hyper["lr"], self.hyper["weight_decay"], self.hyper["eps"], float(self.step_count))
         with torch.cuda.device(self.device):
-            N.check(N.lib.lpmm_b200_adamw4bit_multi_tensor(
-                self._tl, len(self.numels), ctypes.c_void_p(self.qmap_m.data_ptr()), ctypes.c_void_p(self.qmap_v.data_ptr()),
-                h, lo, hi, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+            qm, qv = ctypes.c_void_p(self.qmap_m.data_ptr()), ctypes.c_void_p(self.qmap_v.data_ptr())
+            st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+            if self.peer_offsets:
+                offs = (ctypes.c_int64 * len(self.peer_offsets))(*self.peer_offsets)
+                N.check(N.lib.lpmm_b200_adamw4bit_multi_tensor_peers(self._tl, len(self.numels), qm, qv, h, lo, hi, offs,
+                                                                     len(self.peer_offsets), st))
+            else:
+                N.check(N.lib.lpmm_b200_adamw4bit_multi_tensor(self._tl, len(self.numels), qm, qv, h, lo, hi, st))
 
     def _gather(self):
         if self.world == 1:
+            return
+        if self.gather == "fused":
+            # the launch already wrote every peer's copy; order the ranks on the stream
+            dist.all_reduce(self._flag, group=self.pg)
             return
         S = self.shard_groups * GROUP
         dist.all_gather_into_tensor(self.flat, self.flat[self.rank * S:(self.rank + 1) * S], group=self.pg)
@@ -203,5 +230,10 @@ class Zero1FusedAdamW:
         upd_ms, ag_ms = float(t[0]), float(t[1])
         total = sum(self.numels)
         recv = 4.0 * self.shard_groups * GROUP * (self.world - 1)
+        if self.gather == "fused":
+            return {"update_with_peer_stores": {"ms": upd_ms, "aggregate_params_per_s": total / (upd_ms * 1e-3),
+                                                "nvlink_bytes_sent_per_rank": recv,
+                                                "nvlink_gb_per_s_per_rank": recv / (upd_ms * 1e-3) / 1e9},
+                    "rank_barrier": {"ms": ag_ms}}
         return {"update_only": {"ms": upd_ms, "aggregate_params_per_s": total / (upd_ms * 1e-3)},
                 "all_gather": {"ms": ag_ms, "bytes_received_per_rank": recv, "gb_per_s_per_rank": recv / (ag_ms * 1e-3) / 1e9}}

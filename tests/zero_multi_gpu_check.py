@@ -1,0 +1,29 @@
+"""Run under torch.distributed.run on 2 or more GPUs (tests/test_gpu_zero_multi.py does): the ZeRO-1 step
+with parameters pushed to the peers by stores inside the update kernel equals the ZeRO-1 step followed by an
+NCCL all-gather, bit for bit, and every rank ends with the same parameter buffer.  Prints one OK line per rank."""
+import os, sys, torch, torch.distributed as dist
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, os.path.join(ROOT, "low-bit-optimizers_b200"))
+from lpmm.zero import Zero1FusedAdamW
+rank = int(os.environ["RANK"]); world = int(os.environ["WORLD_SIZE"]); lr_ = int(os.environ["LOCAL_RANK"])
+torch.cuda.set_device(lr_); dev = torch.device("cuda", lr_)
+dist.init_process_group("nccl", device_id=dev)
+shapes = [(300, 128), (4096,), (5000,), (77, 129), (128,), (64, 64, 3), (2048, 1024)]
+H = dict(lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01)
+opts = {g: Zero1FusedAdamW(shapes, dev, gather=g, **H) for g in ("nccl", "fused")}
+for o in opts.values(): o.init_params_normal_(0.02, seed=0)
+for step in range(1, 5):
+    grads = []
+    for i, s in enumerate(shapes):
+        g = torch.Generator(device=dev); g.manual_seed(step * 100003 + i)
+        grads.append(torch.randn(s, generator=g, device=dev) * 1e-3)
+    for o in opts.values():
+        o.set_grad_shard_from_full(grads); o.step()
+torch.cuda.synchronize(); dist.barrier()
+a, b = opts["nccl"].flat, opts["fused"].flat
+same = bool(torch.equal(a.view(torch.int32), b.view(torch.int32)))
+chk = torch.tensor([float(b.double().sum())], device=dev, dtype=torch.float64); lst = [torch.zeros_like(chk) for _ in range(world)]
+dist.all_gather(lst, chk)
+ok = same and all(float(x) == float(lst[0]) for x in lst)
+print(f"rank {rank}: {'OK' if ok else 'MISMATCH'} (fused == nccl: {same})", flush=True)
+dist.destroy_process_group()
