@@ -40,6 +40,7 @@ struct StepArgs {
   long long n;
   long long units;  // padded length / 128
   int first;
+  int vec_ok;  // p and g are 16-byte aligned: full lanes use 128-bit accesses
   void* m;
   float* m_max1;
   void* v;
@@ -55,8 +56,35 @@ struct StepArgs {
 struct Maps {
   float qm[16];
   float qv[16];
+  float mm[16];  // midpoints of qm, padded with +inf
+  float mv[16];
   int zero_m, zero_v;  // code of 0.0f in each map (what padding quantizes to)
 };
+
+// Nearest-code rule as a branch-free four-step search over the 15 sorted midpoints:
+// code = #{midpoints < x}; a NaN gives 15 like the reference's search.
+__device__ __forceinline__ int code16(const float* __restrict__ mids, float x) {
+  int c = (mids[7] < x) ? 8 : 0;
+  c += (mids[c + 3] < x) ? 4 : 0;
+  c += (mids[c + 1] < x) ? 2 : 0;
+  c += (mids[c] < x) ? 1 : 0;
+  return (x != x) ? 15 : c;
+}
+
+// x / d for the 8 values of a lane with a divisor shared by the half-warp: the shared-reciprocal
+// division (equal to IEEE division, see common.cuh) when d is in its domain, IEEE division otherwise.
+__device__ __forceinline__ uint32_t codes_by_group_scale(const float* __restrict__ mids, const float* x, float d) {
+  uint32_t out = 0;
+  if (udiv_ok(d)) {
+    const float r = rcp_nr(d);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) out |= (uint32_t)code16(mids, udiv(x[k], d, r)) << (4 * k);
+  } else {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) out |= (uint32_t)code16(mids, __fdiv_rn(x[k], d)) << (4 * k);
+  }
+  return out;
+}
 
 __device__ __forceinline__ void load_maps(Maps& M, const float* __restrict__ qm, const float* __restrict__ qv) {
   const int tid = threadIdx.x;
@@ -65,9 +93,15 @@ __device__ __forceinline__ void load_maps(Maps& M, const float* __restrict__ qm,
     M.qv[tid] = qv ? qv[tid] : 0.0f;
   }
   __syncthreads();
+  if (tid < 16) {
+    const float inf = __int_as_float(0x7f800000);
+    M.mm[tid] = tid < 15 ? __fmul_rn(__fadd_rn(M.qm[tid], M.qm[tid + 1]), 0.5f) : inf;
+    M.mv[tid] = tid < 15 ? __fmul_rn(__fadd_rn(M.qv[tid], M.qv[tid + 1]), 0.5f) : inf;
+  }
+  __syncthreads();
   if (tid == 0) {
-    M.zero_m = bsearch_code(M.qm, 0.0f);
-    M.zero_v = bsearch_code(M.qv, 0.0f);
+    M.zero_m = code16(M.mm, 0.0f);
+    M.zero_v = code16(M.mv, 0.0f);
   }
   __syncthreads();
 }
@@ -78,32 +112,37 @@ __device__ __forceinline__ float hmax16(float x, unsigned mask) {
   return x;
 }
 
-// Row-major coordinates of a flat index, and the step to the next element.
+// Row-major coordinates of a flat index, and the step to the next element.  ND is the exact
+// number of axes for 2, 3 and 4 (loops fully unrolled, no guards) and 8 means "up to 8, see s.nd".
+template <int ND>
 __device__ __forceinline__ void decompose(long long e, const Shape& s, int* c) {
 #pragma unroll
-  for (int i = 7; i >= 0; --i) {
-    if (i < s.nd) {
-      c[i] = (int)(e % s.dim[i]);
-      e /= s.dim[i];
+  for (int i = ND - 1; i >= 0; --i) {
+    if (ND < 8 || i < s.nd) {
+      const long long q = e / s.dim[i];
+      c[i] = (int)(e - q * s.dim[i]);
+      e = q;
     } else {
       c[i] = 0;
     }
   }
 }
+template <int ND>
 __device__ __forceinline__ void advance(int* c, const Shape& s) {
 #pragma unroll
-  for (int i = 7; i >= 0; --i) {
-    if (i < s.nd) {
+  for (int i = ND - 1; i >= 0; --i) {
+    if (ND < 8 || i < s.nd) {
       if (++c[i] < s.dim[i]) return;
       c[i] = 0;
     }
   }
 }
+template <int ND>
 __device__ __forceinline__ float axis_min(const float* const* vecs, const int* c, int nd) {
   float st = __ldg(vecs[0] + c[0]);
 #pragma unroll
-  for (int i = 1; i < 8; ++i)
-    if (i < nd) st = fminf(st, __ldg(vecs[i] + c[i]));
+  for (int i = 1; i < ND; ++i)
+    if (ND < 8 || i < nd) st = fminf(st, __ldg(vecs[i] + c[i]));
   return st;
 }
 
@@ -129,7 +168,7 @@ __device__ __forceinline__ float upd_param(const UConsts& c, float p, float m, f
 // ---------------------------------------------------------------------------------------------
 // AdamW, non-fused semantics.  MM: first-moment storage, VM: second-moment storage / source.
 // ---------------------------------------------------------------------------------------------
-template <int MM, int VM>
+template <int MM, int VM, int ND>
 __global__ void __launch_bounds__(UT) unfused_adamw_kernel(const StepArgs a, const UConsts c,
                                                             const float* __restrict__ qmap_m,
                                                             const float* __restrict__ qmap_v) {
@@ -163,15 +202,28 @@ __global__ void __launch_bounds__(UT) unfused_adamw_kernel(const StepArgs a, con
       if (VM == LPMM_B200_STATE_GROUP4) sv = a.v_max1[u];
     }
     int co[8];
-    if (VM == LPMM_B200_STATE_RANK1_4) decompose(e0, a.s, co);
+    if (VM == LPMM_B200_STATE_RANK1_4) decompose<ND>(e0, a.s, co);
     long long rowi = 0, cc = 0, bi = 0;  // factored: row index in the [B*R, C] view, column, batch entry
     if (VM == LPMM_B200_STATE_FACTORED) {
       rowi = e0 / C;
       cc = e0 - rowi * C;
       bi = e0 / RC;
     }
-    float m[8], v[8], st_new[8];
+    float m[8], v[8], st_new[8], gx[8], px[8];
     float am = 0.0f, av = 0.0f;
+    const bool full = a.vec_ok && (e0 + 8 <= n);
+    if (full) {
+      const float4 g0 = *reinterpret_cast<const float4*>(a.g + e0), g1 = *reinterpret_cast<const float4*>(a.g + e0 + 4);
+      const float4 p0 = *reinterpret_cast<const float4*>(a.p + e0), p1 = *reinterpret_cast<const float4*>(a.p + e0 + 4);
+      gx[0] = g0.x; gx[1] = g0.y; gx[2] = g0.z; gx[3] = g0.w; gx[4] = g1.x; gx[5] = g1.y; gx[6] = g1.z; gx[7] = g1.w;
+      px[0] = p0.x; px[1] = p0.y; px[2] = p0.z; px[3] = p0.w; px[4] = p1.x; px[5] = p1.y; px[6] = p1.z; px[7] = p1.w;
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        gx[k] = (e0 + k < n) ? a.g[e0 + k] : 0.0f;
+        px[k] = (e0 + k < n) ? a.p[e0 + k] : 0.0f;
+      }
+    }
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
       const long long e = e0 + k;
@@ -179,14 +231,14 @@ __global__ void __launch_bounds__(UT) unfused_adamw_kernel(const StepArgs a, con
       v[k] = 0.0f;
       st_new[k] = 1.0f;
       if (e < n) {
-        const float g = a.g[e];
+        const float g = gx[k];
         float m0 = 0.0f, v0 = 0.0f;
         if (!a.first) {
           if (MM == LPMM_B200_STATE_GROUP4) m0 = __fmul_rn(M.qm[(mcodes >> (4 * k)) & 15u], sm);
           else m0 = reinterpret_cast<const float*>(a.m)[e];
           if (VM == LPMM_B200_STATE_GROUP4) v0 = __fmul_rn(M.qv[(vcodes >> (4 * k)) & 15u], sv);
           else if (VM == LPMM_B200_STATE_RANK1_4)
-            v0 = __fmul_rn(M.qv[(vcodes >> (4 * k)) & 15u], axis_min(a.v_old, co, a.s.nd));
+            v0 = __fmul_rn(M.qv[(vcodes >> (4 * k)) & 15u], axis_min<ND>(a.v_old, co, a.s.nd));
           else if (VM == LPMM_B200_STATE_FP32) v0 = reinterpret_cast<const float*>(a.v)[e];
         }
         m[k] = lerp_m(c, m0, g);
@@ -196,42 +248,44 @@ __global__ void __launch_bounds__(UT) unfused_adamw_kernel(const StepArgs a, con
         } else {
           v[k] = upd_v2(c, v0, g);
         }
-        a.p[e] = upd_param(c, a.p[e], m[k], v[k]);
+        px[k] = upd_param(c, px[k], m[k], v[k]);
         am = fmaxf(am, fabsf(m[k]));
         av = fmaxf(av, v[k]);
         if (MM == LPMM_B200_STATE_FP32) reinterpret_cast<float*>(a.m)[e] = m[k];
         if (VM == LPMM_B200_STATE_FP32) reinterpret_cast<float*>(a.v)[e] = v[k];
-        if (VM == LPMM_B200_STATE_RANK1_4) st_new[k] = axis_min(a.v_new, co, a.s.nd);
+        if (VM == LPMM_B200_STATE_RANK1_4) st_new[k] = axis_min<ND>(a.v_new, co, a.s.nd);
       }
-      if (VM == LPMM_B200_STATE_RANK1_4) advance(co, a.s);
+      if (VM == LPMM_B200_STATE_RANK1_4) advance<ND>(co, a.s);
       if (VM == LPMM_B200_STATE_FACTORED && ++cc == C) {
         cc = 0;
         ++rowi;
         bi = rowi / a.s.dim[a.s.nd - 2];
       }
     }
+    if (full) {
+      *reinterpret_cast<float4*>(a.p + e0) = make_float4(px[0], px[1], px[2], px[3]);
+      *reinterpret_cast<float4*>(a.p + e0 + 4) = make_float4(px[4], px[5], px[6], px[7]);
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        if (e0 + k < n) a.p[e0 + k] = px[k];
+    }
     if (MM == LPMM_B200_STATE_GROUP4) {
       am = hmax16(am, hmask);
-      uint32_t out = 0;
-#pragma unroll
-      for (int k = 0; k < 8; ++k)  // padding inside the last group is 0 / max
-        out |= (uint32_t)(bsearch_code(M.qm, __fdiv_rn(m[k], am)) & 15) << (4 * k);
-      *reinterpret_cast<uint32_t*>(mb) = out;
+      // padding inside the last group is 0 / max
+      *reinterpret_cast<uint32_t*>(mb) = codes_by_group_scale(M.mm, m, am);
       if (l16 == 0) a.m_max1[u] = am;
     }
     if (VM == LPMM_B200_STATE_GROUP4) {
       av = hmax16(av, hmask);
-      uint32_t out = 0;
-#pragma unroll
-      for (int k = 0; k < 8; ++k) out |= (uint32_t)(bsearch_code(M.qv, __fdiv_rn(v[k], av)) & 15) << (4 * k);
-      *reinterpret_cast<uint32_t*>(vb) = out;
+      *reinterpret_cast<uint32_t*>(vb) = codes_by_group_scale(M.mv, v, av);
       if (l16 == 0) a.v_max1[u] = av;
     }
     if (VM == LPMM_B200_STATE_RANK1_4) {
       uint32_t out = 0;
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
-        const int code = (e0 + k < n) ? bsearch_code(M.qv, __fdiv_rn(v[k], st_new[k])) : M.zero_v;
+        const int code = (e0 + k < n) ? code16(M.mv, __fdiv_rn(v[k], st_new[k])) : M.zero_v;
         out |= (uint32_t)(code & 15) << (4 * k);
       }
       *reinterpret_cast<uint32_t*>(vb) = out;
@@ -245,30 +299,78 @@ __global__ void __launch_bounds__(UT) unfused_adamw_kernel(const StepArgs a, con
 }
 
 // Statistics pass of the rank-1 second moment: recompute v exactly as the update pass will and
-// fold it into the (zeroed) per-axis maxima.
+// fold it into the (zeroed) per-axis maxima.  The innermost axis changes with every element, so
+// its maxima are first combined in shared memory (when the axis has at most STAT_LAST entries) and
+// flushed once per CTA; the outer axes change rarely along a lane's 8 consecutive elements, so a
+// lane combines runs of equal coordinates in registers before touching global memory.
+constexpr int STAT_LAST = 8192;
+template <int ND>
 __global__ void __launch_bounds__(UT) rank1_stats_kernel(const StepArgs a, const UConsts c,
                                                           const float* __restrict__ qmap_v) {
   __shared__ Maps M;
+  __shared__ int lastmax[STAT_LAST];
   load_maps(M, nullptr, qmap_v);
+  const int nd = a.s.nd;
+  const int last = nd - 1;
+  const bool use_smem = a.s.dim[last] <= STAT_LAST;
+  if (use_smem) {
+    for (int i = threadIdx.x; i < (int)a.s.dim[last]; i += UT) lastmax[i] = 0;
+    __syncthreads();
+  }
   const long long n = a.n;
   const long long nchunks = (n + 7) / 8;
   for (long long ch = (long long)blockIdx.x * UT + threadIdx.x; ch < nchunks; ch += (long long)gridDim.x * UT) {
     const long long e0 = ch * 8;
     uint32_t vcodes = 0;
     if (!a.first) vcodes = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(a.v) + (e0 >> 1));
-    int co[8];
-    decompose(e0, a.s, co);
-    for (int k = 0; k < 8; ++k) {
-      const long long e = e0 + k;
-      if (e >= n) break;
-      float v0 = 0.0f;
-      if (!a.first) v0 = __fmul_rn(M.qv[(vcodes >> (4 * k)) & 15u], axis_min(a.v_old, co, a.s.nd));
-      const float v = upd_v2(c, v0, a.g[e]);
+    float gx[8];
+    if (a.vec_ok && e0 + 8 <= n) {
+      const float4 g0 = *reinterpret_cast<const float4*>(a.g + e0), g1 = *reinterpret_cast<const float4*>(a.g + e0 + 4);
+      gx[0] = g0.x; gx[1] = g0.y; gx[2] = g0.z; gx[3] = g0.w; gx[4] = g1.x; gx[5] = g1.y; gx[6] = g1.z; gx[7] = g1.w;
+    } else {
 #pragma unroll
-      for (int i = 0; i < 8; ++i)
-        if (i < a.s.nd) atomic_max_nonneg(a.v_new[i] + co[i], v);
-      advance(co, a.s);
+      for (int k = 0; k < 8; ++k) gx[k] = (e0 + k < n) ? a.g[e0 + k] : 0.0f;
     }
+    int co[8], run_co[8];
+    float run_max[8];
+    decompose<ND>(e0, a.s, co);
+#pragma unroll
+    for (int i = 0; i < ND; ++i) {
+      run_co[i] = co[i];
+      run_max[i] = 0.0f;
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      if (e0 + k < n) {
+        float v0 = 0.0f;
+        if (!a.first) v0 = __fmul_rn(M.qv[(vcodes >> (4 * k)) & 15u], axis_min<ND>(a.v_old, co, nd));
+        const float v = upd_v2(c, v0, gx[k]);
+#pragma unroll
+        for (int i = 0; i < ND; ++i) {
+          if (ND < 8 || i < nd) {
+            if (i == last && use_smem) {
+              if (__float_as_int(v) > lastmax[co[i]]) atomicMax(&lastmax[co[i]], __float_as_int(v));
+            } else {
+              if (co[i] != run_co[i]) {
+                atomic_max_nonneg(a.v_new[i] + run_co[i], run_max[i]);
+                run_co[i] = co[i];
+                run_max[i] = 0.0f;
+              }
+              run_max[i] = fmaxf(run_max[i], v);
+            }
+          }
+        }
+        advance<ND>(co, a.s);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < ND; ++i)
+      if ((ND < 8 || i < nd) && !(i == last && use_smem)) atomic_max_nonneg(a.v_new[i] + run_co[i], run_max[i]);
+  }
+  if (use_smem) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < (int)a.s.dim[last]; i += UT)
+      atomic_max_nonneg(a.v_new[last] + i, __int_as_float(lastmax[i]));
   }
 }
 
@@ -400,10 +502,7 @@ __global__ void __launch_bounds__(UT) sgd_kernel(float* __restrict__ p, const fl
     }
     if (bb) {
       ab = hmax16(ab, hmask);
-      uint32_t out = 0;
-#pragma unroll
-      for (int k = 0; k < 8; ++k) out |= (uint32_t)(bsearch_code(M.qm, __fdiv_rn(b[k], ab)) & 15) << (4 * k);
-      *reinterpret_cast<uint32_t*>(bb) = out;
+      *reinterpret_cast<uint32_t*>(bb) = codes_by_group_scale(M.mm, b, ab);
       if (l16 == 0) buf_max1[u] = ab;
     }
   }
@@ -421,7 +520,7 @@ __global__ void __launch_bounds__(UT) pack4_kernel(const float* __restrict__ x, 
   const long long nb = n / 2;
   for (long long b = (long long)blockIdx.x * UT + threadIdx.x; b < nb; b += (long long)gridDim.x * UT) {
     const float2 xy = *reinterpret_cast<const float2*>(x + 2 * b);
-    out[b] = (uint8_t)((bsearch_code(M.qm, xy.x) & 15) | ((bsearch_code(M.qm, xy.y) & 15) << 4));
+    out[b] = (uint8_t)(code16(M.mm, xy.x) | (code16(M.mm, xy.y) << 4));
   }
   if (blockIdx.x == 0 && threadIdx.x == 0) out[nb] = 0;
 }
@@ -436,7 +535,7 @@ __global__ void __launch_bounds__(UT) unpack4_kernel(const uint8_t* __restrict__
   }
 }
 // mode 0: group-128 scales (computes max1); mode 1: rank-1 scales from given per-axis maxima.
-template <int MODE>
+template <int MODE, int ND>
 __global__ void __launch_bounds__(UT) quant_kernel(const float* __restrict__ x, long long n, long long units,
                                                     const float* __restrict__ qmap, uint8_t* __restrict__ codes,
                                                     float* __restrict__ max1, const StepArgs a) {
@@ -456,7 +555,7 @@ __global__ void __launch_bounds__(UT) quant_kernel(const float* __restrict__ x, 
     float xv[8], st[8];
     float ax = 0.0f;
     int co[8];
-    if (MODE == 1) decompose(e0, a.s, co);
+    if (MODE == 1) decompose<ND>(e0, a.s, co);
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
       xv[k] = 0.0f;
@@ -464,20 +563,19 @@ __global__ void __launch_bounds__(UT) quant_kernel(const float* __restrict__ x, 
       if (e0 + k < n) {
         xv[k] = x[e0 + k];
         ax = fmaxf(ax, fabsf(xv[k]));
-        if (MODE == 1) st[k] = axis_min(a.v_new, co, a.s.nd);
+        if (MODE == 1) st[k] = axis_min<ND>(a.v_new, co, a.s.nd);
       }
-      if (MODE == 1) advance(co, a.s);
+      if (MODE == 1) advance<ND>(co, a.s);
     }
     uint32_t out = 0;
     if (MODE == 0) {
       ax = hmax16(ax, hmask);
-#pragma unroll
-      for (int k = 0; k < 8; ++k) out |= (uint32_t)(bsearch_code(M.qm, __fdiv_rn(xv[k], ax)) & 15) << (4 * k);
+      out = codes_by_group_scale(M.mm, xv, ax);
       if (l16 == 0) max1[u] = ax;
     } else {
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
-        const int code = (e0 + k < n) ? bsearch_code(M.qm, __fdiv_rn(xv[k], st[k])) : M.zero_m;
+        const int code = (e0 + k < n) ? code16(M.mm, __fdiv_rn(xv[k], st[k])) : M.zero_m;
         out |= (uint32_t)(code & 15) << (4 * k);
       }
     }
@@ -485,7 +583,7 @@ __global__ void __launch_bounds__(UT) quant_kernel(const float* __restrict__ x, 
   }
   if (blockIdx.x == 0 && threadIdx.x == 0) codes[units * 64] = 0;
 }
-template <int MODE>
+template <int MODE, int ND>
 __global__ void __launch_bounds__(UT) dequant_kernel(const uint8_t* __restrict__ codes, long long n,
                                                       const float* __restrict__ qmap,
                                                       const float* __restrict__ max1, float* __restrict__ out,
@@ -497,30 +595,31 @@ __global__ void __launch_bounds__(UT) dequant_kernel(const uint8_t* __restrict__
     const long long e0 = ch * 8;
     const uint32_t c = *reinterpret_cast<const uint32_t*>(codes + (e0 >> 1));
     int co[8];
-    if (MODE == 1) decompose(e0, a.s, co);
+    if (MODE == 1) decompose<ND>(e0, a.s, co);
     const float s0 = (MODE == 0) ? max1[e0 >> 7] : 0.0f;
     for (int k = 0; k < 8; ++k) {
       if (e0 + k >= n) break;
-      const float sc = (MODE == 0) ? s0 : axis_min(a.v_old, co, a.s.nd);
+      const float sc = (MODE == 0) ? s0 : axis_min<ND>(a.v_old, co, a.s.nd);
       out[e0 + k] = __fmul_rn(M.qm[(c >> (4 * k)) & 15u], sc);
-      if (MODE == 1) advance(co, a.s);
+      if (MODE == 1) advance<ND>(co, a.s);
     }
   }
 }
+template <int ND>
 __global__ void __launch_bounds__(UT) axis_absmax_kernel(const float* __restrict__ x, const StepArgs a) {
   const long long n = a.n;
   const long long nchunks = (n + 7) / 8;
   for (long long ch = (long long)blockIdx.x * UT + threadIdx.x; ch < nchunks; ch += (long long)gridDim.x * UT) {
     const long long e0 = ch * 8;
     int co[8];
-    decompose(e0, a.s, co);
+    decompose<ND>(e0, a.s, co);
     for (int k = 0; k < 8; ++k) {
       if (e0 + k >= n) break;
       const float v = fabsf(x[e0 + k]);
 #pragma unroll
-      for (int i = 0; i < 8; ++i)
-        if (i < a.s.nd) atomic_max_nonneg(a.v_new[i] + co[i], v);
-      advance(co, a.s);
+      for (int i = 0; i < ND; ++i)
+        if (ND < 8 || i < a.s.nd) atomic_max_nonneg(a.v_new[i] + co[i], v);
+      advance<ND>(co, a.s);
     }
   }
 }
@@ -528,10 +627,18 @@ __global__ void __launch_bounds__(UT) axis_absmax_kernel(const float* __restrict
 // ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
+// Calls `expr` with ND bound to the instantiation that serves `nd` axes: exact for 2, 3, 4, generic for 5..8.
+#define LPMM_DISPATCH_ND(nd, ...)        \
+  do {                                   \
+    if ((nd) == 2) { constexpr int ND = 2; __VA_ARGS__; }        \
+    else if ((nd) == 3) { constexpr int ND = 3; __VA_ARGS__; }   \
+    else if ((nd) == 4) { constexpr int ND = 4; __VA_ARGS__; }   \
+    else { constexpr int ND = 8; __VA_ARGS__; }                  \
+  } while (0)
 static inline long long pad_to(long long n, long long m) { return (n + m - 1) / m * m; }
-static inline unsigned grid_for(long long work_items, int per_cta) {
+static inline unsigned grid_for(long long work_items, int per_cta, int ctas_per_sm = 8) {
   long long g = (work_items + per_cta - 1) / per_cta;
-  const long long cap = (long long)num_sms() * 8;
+  const long long cap = (long long)num_sms() * ctas_per_sm;
   if (g > cap) g = cap;
   if (g < 1) g = 1;
   return (unsigned)g;
@@ -602,7 +709,7 @@ extern "C" int lpmm_b200_quant_group4(const float* x, int64_t numel, const float
   if (!qmap || !codes || (numel > 0 && (!x || !max1))) return LPMM_B200_ERR_NULL_POINTER;
   StepArgs a = {};
   const long long units = pad_to(pad_to(numel, 128), 2048) / 128;
-  quant_kernel<0><<<grid_for(units, UT / 16), UT, 0, (cudaStream_t)stream>>>(x, numel, units, qmap, (uint8_t*)codes,
+  quant_kernel<0, 2><<<grid_for(units, UT / 16), UT, 0, (cudaStream_t)stream>>>(x, numel, units, qmap, (uint8_t*)codes,
                                                                             max1, a);
   LPMM_CUDA_TRY(cudaGetLastError());
   return LPMM_B200_OK;
@@ -614,7 +721,7 @@ extern "C" int lpmm_b200_dequant_group4(const int8_t* codes, const float* qmap, 
   if (numel == 0) return LPMM_B200_OK;
   if (!qmap || !codes || !max1 || !out) return LPMM_B200_ERR_NULL_POINTER;
   StepArgs a = {};
-  dequant_kernel<0><<<grid_for((numel + 7) / 8, UT), UT, 0, (cudaStream_t)stream>>>((const uint8_t*)codes, numel,
+  dequant_kernel<0, 2><<<grid_for((numel + 7) / 8, UT), UT, 0, (cudaStream_t)stream>>>((const uint8_t*)codes, numel,
                                                                                    qmap, max1, out, a);
   LPMM_CUDA_TRY(cudaGetLastError());
   return LPMM_B200_OK;
@@ -638,7 +745,7 @@ extern "C" int lpmm_b200_axis_absmax(const float* x, const int64_t* shape, int n
   rc = zero_axes(a.s, max_dims, (cudaStream_t)stream);
   if (rc) return rc;
   if (a.n == 0) return LPMM_B200_OK;
-  axis_absmax_kernel<<<grid_for((a.n + 7) / 8, UT), UT, 0, (cudaStream_t)stream>>>(x, a);
+  LPMM_DISPATCH_ND(ndim, (axis_absmax_kernel<ND><<<grid_for((a.n + 7) / 8, UT), UT, 0, (cudaStream_t)stream>>>(x, a)));
   LPMM_CUDA_TRY(cudaGetLastError());
   return LPMM_B200_OK;
 }
@@ -653,8 +760,8 @@ extern "C" int lpmm_b200_quant_rank1_4(const float* x, const int64_t* shape, int
   fill_shape(a.s, shape, ndim, &a.n);
   for (int i = 0; i < ndim; ++i) a.v_new[i] = max_dims[i];
   const long long units = pad_to(a.n, 2048) / 128;
-  quant_kernel<1><<<grid_for(units, UT / 16), UT, 0, (cudaStream_t)stream>>>(x, a.n, units, qmap, (uint8_t*)codes,
-                                                                            nullptr, a);
+  LPMM_DISPATCH_ND(ndim, (quant_kernel<1, ND><<<grid_for(units, UT / 16), UT, 0, (cudaStream_t)stream>>>(
+                              x, a.n, units, qmap, (uint8_t*)codes, nullptr, a)));
   LPMM_CUDA_TRY(cudaGetLastError());
   return LPMM_B200_OK;
 }
@@ -671,8 +778,8 @@ extern "C" int lpmm_b200_dequant_rank1_4(const int8_t* codes, const float* qmap,
     if (!max_dims[i]) return LPMM_B200_ERR_NULL_POINTER;
     a.v_old[i] = max_dims[i];
   }
-  dequant_kernel<1><<<grid_for((a.n + 7) / 8, UT), UT, 0, (cudaStream_t)stream>>>((const uint8_t*)codes, a.n, qmap,
-                                                                                 nullptr, out, a);
+  LPMM_DISPATCH_ND(ndim, (dequant_kernel<1, ND><<<grid_for((a.n + 7) / 8, UT), UT, 0, (cudaStream_t)stream>>>(
+                              (const uint8_t*)codes, a.n, qmap, nullptr, out, a)));
   LPMM_CUDA_TRY(cudaGetLastError());
   return LPMM_B200_OK;
 }
@@ -690,10 +797,12 @@ template <int MM>
 static cudaError_t launch_unfused(int vm, unsigned grid, cudaStream_t st, const StepArgs& a, const UConsts& c,
                                   const float* qm, const float* qv) {
   switch (vm) {
-    case LPMM_B200_STATE_FP32: unfused_adamw_kernel<MM, LPMM_B200_STATE_FP32><<<grid, UT, 0, st>>>(a, c, qm, qv); break;
-    case LPMM_B200_STATE_GROUP4: unfused_adamw_kernel<MM, LPMM_B200_STATE_GROUP4><<<grid, UT, 0, st>>>(a, c, qm, qv); break;
-    case LPMM_B200_STATE_RANK1_4: unfused_adamw_kernel<MM, LPMM_B200_STATE_RANK1_4><<<grid, UT, 0, st>>>(a, c, qm, qv); break;
-    default: unfused_adamw_kernel<MM, LPMM_B200_STATE_FACTORED><<<grid, UT, 0, st>>>(a, c, qm, qv); break;
+    case LPMM_B200_STATE_FP32: unfused_adamw_kernel<MM, LPMM_B200_STATE_FP32, 2><<<grid, UT, 0, st>>>(a, c, qm, qv); break;
+    case LPMM_B200_STATE_GROUP4: unfused_adamw_kernel<MM, LPMM_B200_STATE_GROUP4, 2><<<grid, UT, 0, st>>>(a, c, qm, qv); break;
+    case LPMM_B200_STATE_RANK1_4:
+      LPMM_DISPATCH_ND(a.s.nd, (unfused_adamw_kernel<MM, LPMM_B200_STATE_RANK1_4, ND><<<grid, UT, 0, st>>>(a, c, qm, qv)));
+      break;
+    default: unfused_adamw_kernel<MM, LPMM_B200_STATE_FACTORED, 2><<<grid, UT, 0, st>>>(a, c, qm, qv); break;
   }
   return cudaGetLastError();
 }
@@ -716,6 +825,7 @@ extern "C" int lpmm_b200_adamw4bit_unfused_step(const lpmm_b200_step_tensor* t, 
   a.g = t->g;
   a.n = t->numel;
   a.first = t->first;
+  a.vec_ok = ((((uintptr_t)t->p | (uintptr_t)t->g) & 15) == 0);
   a.m = t->m;
   a.m_max1 = t->m_max1;
   a.v = t->v;
@@ -745,7 +855,7 @@ extern "C" int lpmm_b200_adamw4bit_unfused_step(const lpmm_b200_step_tensor* t, 
     }
     int rc = zero_axes(a.s, t->v_max_dims_new, st);
     if (rc) return rc;
-    rank1_stats_kernel<<<grid_for((a.n + 7) / 8, UT), UT, 0, st>>>(a, c, qmap_v);
+    LPMM_DISPATCH_ND(t->ndim, (rank1_stats_kernel<ND><<<grid_for((a.n + 7) / 8, UT, 3), UT, 0, st>>>(a, c, qmap_v)));
     LPMM_CUDA_TRY(cudaGetLastError());
   }
   if (t->v_mode == LPMM_B200_STATE_FACTORED) {
