@@ -42,11 +42,13 @@ class AdamW(LowBitOptimizer):
         super().__init__(params, defaults, qconfig)
         self._lists = {}  # cached descriptor arrays of the multi-tensor step, per param group
         self._spare = {}  # per-parameter buffers that are not optimizer state (alternate rank-1 maxima)
+        self._plans = {}  # fused groups: everything needed to repeat the last launch
 
     def __setstate__(self, state):
         super().__setstate__(state)
         self._lists = {}
         self._spare = {}
+        self._plans = {}
         for group in self.param_groups:
             group.setdefault("fused", None)
         values = list(self.state.values())
@@ -106,6 +108,8 @@ class AdamW(LowBitOptimizer):
 
     # ---- fused=True ---------------------------------------------------------------------------
     def _step_fused(self, gi, group, params):
+        if self._step_fused_planned(gi, group, params):
+            return
         beta1, beta2 = group["betas"]
         md_m = self.get_qmetadata_by_state_name("exp_avg")
         md_v = self.get_qmetadata_by_state_name("exp_avg_sq")
@@ -161,6 +165,50 @@ class AdamW(LowBitOptimizer):
             with torch.cuda.device(device):
                 _kernels.adamw4bit_multi_tensor(tl, qm, qv, beta1, beta2, group["lr"], group["weight_decay"],
                                                 group["eps"], step)
+            if len(by_step) == 1 and len(items) == len(params):
+                # every tensor of the group took this one launch: remember it, so that the following steps
+                # only bump the counters, refresh changed gradient pointers and launch
+                self._plans[gi] = dict(
+                    params=list(params), tl=tl, step=step, device=device, qm=qm, qv=qv,
+                    states=[st for _, st in items], steps=[st["step"] for _, st in items],
+                    m=[e[2] for e in entries], v=[e[3] for e in entries],
+                    ptrs=[(e[0].data_ptr(), e[2].data_ptr(), e[3].data_ptr()) for e in entries],
+                    gptrs=[e[1].data_ptr() for e in entries])
+
+    def _step_fused_planned(self, gi, group, params):
+        """Fast path of a fused group whose tensors, states and step counters are unchanged since the
+        last step.  Returns False (after dropping the plan) whenever anything differs."""
+        plan = self._plans.get(gi)
+        if plan is None:
+            return False
+        pp = plan["params"]
+        if len(pp) != len(params):
+            del self._plans[gi]
+            return False
+        tl, gptrs = plan["tl"], plan["gptrs"]
+        for i, p in enumerate(params):
+            st = plan["states"][i]
+            m, v = plan["m"][i], plan["v"][i]
+            if (p is not pp[i] or st.get("exp_avg") is not m or st.get("exp_avg_sq") is not v
+                    or st.get("step") is not plan["steps"][i]
+                    or (p.data_ptr(), m.data_ptr(), v.data_ptr()) != plan["ptrs"][i]):
+                del self._plans[gi]
+                return False
+            g = p.grad
+            gp = g.data_ptr()
+            if gp != gptrs[i]:
+                if g.dtype != torch.float32 or not g.is_cuda or not g.is_contiguous() or g.numel() != p.numel():
+                    del self._plans[gi]
+                    return False
+                tl.array[i].g = gp
+                gptrs[i] = gp
+        torch._foreach_add_(plan["steps"], 1.0)
+        plan["step"] += 1.0
+        beta1, beta2 = group["betas"]
+        with torch.cuda.device(plan["device"]):
+            _kernels.adamw4bit_multi_tensor(tl, plan["qm"], plan["qv"], beta1, beta2, group["lr"], group["weight_decay"],
+                                            group["eps"], plan["step"])
+        return True
 
     def _tensor_list(self, key, entries):
         """Descriptor array of a parameter list, rebuilt only when a pointer changed."""
