@@ -81,6 +81,7 @@ class Zero1FusedAdamW:
         self.gstart, self.total_groups, self.shard_groups = partition(self.numels, self.world)
         self.lo, self.hi = owned_range(self.rank, self.total_groups, self.shard_groups)
         S = self.shard_groups
+        self._check_same_layout_everywhere()
         if gather not in ("nccl", "fused"):
             raise ValueError("gather must be 'nccl' or 'fused'")
         self.gather = gather if self.world > 1 else "nccl"
@@ -119,6 +120,24 @@ class Zero1FusedAdamW:
         self.qmap_m = create_general_qmap("nonlinear", 4, True).to(self.device)
         self.qmap_v = create_general_qmap("power-1", 4, False).to(self.device)
         self._tl = None
+
+    def _check_same_layout_everywhere(self):
+        """All ranks must cut the same list the same way; a rank built from a different list would
+        update the wrong ranges silently.  Compares (tensor count, group count, a hash of the sizes)."""
+        if self.world == 1 or not dist.is_initialized():
+            return
+        h = 0
+        for n in self.numels:
+            h = (h * 1000003 + n) % 2147483629
+        mine = torch.tensor([len(self.numels), self.total_groups, h], dtype=torch.int64)
+        backend = dist.get_backend(self.pg)
+        dev = self.device if backend == "nccl" else torch.device("cpu")
+        lo, hi = mine.to(dev).clone(), mine.to(dev).clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN, group=self.pg)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX, group=self.pg)
+        if not torch.equal(lo, hi):
+            raise ValueError("ZeRO-1: the ranks were given different parameter lists "
+                             f"(this rank: {len(self.numels)} tensors, {self.total_groups} groups)")
 
     # ---- data ---------------------------------------------------------------------------------
     def init_params_normal_(self, std, seed=0):

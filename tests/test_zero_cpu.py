@@ -103,3 +103,57 @@ def test_two_gloo_ranks_equal_the_unsharded_step(golden_dir, tmp_path):
         lo = single.gstart[i] * 128
         got = flats[0][lo: lo + p.numel()]
         assert np.array_equal(got.view(np.int32), p.reshape(-1).numpy().view(np.int32)), f"tensor {i} differs from unsharded"
+
+
+# ---- failures, made on the host among gloo ranks (no GPU involved) ------------------------------
+def _mismatch_worker(rank, world, port, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from lpmm.zero import Zero1FusedAdamW
+    shapes = SHAPES if rank == 0 else SHAPES[:-1] + [(64, 64, 4)]
+    try:
+        Zero1FusedAdamW(shapes, "cpu", **HYPER)
+        verdict = "constructed"
+    except ValueError as e:
+        verdict = "ValueError: " + str(e)[:40]
+    with open(os.path.join(out_dir, f"verdict_{rank}.txt"), "w") as fh:
+        fh.write(verdict)
+    dist.destroy_process_group()
+
+
+def test_ranks_with_different_lists_are_refused(tmp_path):
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_mismatch_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    for r in range(2):
+        assert (tmp_path / f"verdict_{r}.txt").read_text().startswith("ValueError"), f"rank {r} accepted a mismatched list"
+
+
+def _dropout_worker(rank, world, port, golden_dir, out_dir):
+    import datetime
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    z = np.load(os.path.join(golden_dir, "qmaps.npz"))
+    opt = _make(world, rank, z["m"], z["v"])
+    opt.set_grad_shard_from_full(_grads(1))
+    opt.step()                                    # a healthy step first
+    if rank == 1:
+        os._exit(0)                               # rank 1 leaves between steps, nothing of its in flight
+    opt.set_grad_shard_from_full(_grads(2))
+    try:
+        opt.step()                                # the all-gather cannot complete
+        verdict = "completed"
+    except Exception as e:  # gloo reports the lost peer or the timeout as a RuntimeError
+        verdict = "error: " + type(e).__name__
+    with open(os.path.join(out_dir, "verdict_0.txt"), "w") as fh:
+        fh.write(verdict)
+    os._exit(0)
+
+
+def test_a_rank_leaving_between_steps_surfaces_as_an_error(golden_dir, tmp_path):
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_dropout_worker, args=(2, port, golden_dir, str(tmp_path)), nprocs=2, join=True)
+    assert (tmp_path / "verdict_0.txt").read_text().startswith("error"), "the surviving rank did not notice"
