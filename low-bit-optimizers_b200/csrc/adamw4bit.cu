@@ -26,8 +26,9 @@
 namespace lpmm_b200 {
 
 constexpr int MAX_TENSORS = 400;  // descriptors per launch (28.9 KB of the 32 KB parameter space)
-constexpr int CTA_THREADS = 512;
-constexpr int CTAS_PER_SM = 2;
+// One 1024-thread CTA per SM: measured faster than 2 x 512 or 3 x 256 (6.2 vs 5.9 vs 5.3 TB/s in a burst).
+constexpr int CTA_THREADS = 1024;
+constexpr int CTAS_PER_SM = 1;
 constexpr int HW_PER_CTA = CTA_THREADS / 16;
 constexpr size_t DYN_SMEM = 2 * LUT_ENTRIES * sizeof(LutEnt);  // one table per moment
 
