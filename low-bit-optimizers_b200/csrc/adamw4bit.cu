@@ -27,6 +27,7 @@ namespace lpmm_b200 {
 
 constexpr int MAX_TENSORS = 400;  // descriptors per launch (28.9 KB of the 32 KB parameter space)
 // One 1024-thread CTA per SM: measured faster than 2 x 512 or 3 x 256 (6.2 vs 5.9 vs 5.3 TB/s in a burst).
+constexpr unsigned PF_DIST = 1;  // the L2 prefetch runs this many of a half-warp's iterations ahead (2: same, 3: slower)
 constexpr int CTA_THREADS = 1024;
 constexpr int CTAS_PER_SM = 1;
 constexpr int HW_PER_CTA = CTA_THREADS / 16;
@@ -196,14 +197,12 @@ __device__ __forceinline__ void group_q4_fast(const LanePtrs& t, unsigned gl, in
   const uint32_t vc = *vcp;
   const float pm = __fmul_rn(qm_l, t.sm[gl]);  // lane i: qmap_m[i] * scale
   const float pv = __fmul_rn(qv_l, t.sv[gl]);
-#ifndef EXP_NO_PREFETCH
   if (pf) {
     prefetch_l2(pp + (size_t)pf * 128);
     prefetch_l2(gp + (size_t)pf * 128);
     prefetch_l2(mcp + (size_t)pf * 16);
     prefetch_l2(vcp + (size_t)pf * 16);
   }
-#endif
 
   float m[8], v[8];
   float am = 0.0f, av = 0.0f;
@@ -272,14 +271,12 @@ __device__ __forceinline__ void group_q4_x2(const LanePtrs& t, unsigned gl, int 
   const uint32_t vc = *vcp;
   const float pm = __fmul_rn(qm_l, t.sm[gl]);  // lane i: qmap_m[i] * scale
   const float pv = __fmul_rn(qv_l, t.sv[gl]);
-#ifndef EXP_NO_PREFETCH
   if (pf) {
     prefetch_l2(pp + (size_t)pf * 128);
     prefetch_l2(gp + (size_t)pf * 128);
     prefetch_l2(mcp + (size_t)pf * 16);
     prefetch_l2(vcp + (size_t)pf * 16);
   }
-#endif
   f2 m[4], v[4];
   float am = 0.0f, av = 0.0f;
 #pragma unroll
@@ -459,7 +456,8 @@ __device__ __forceinline__ void run_groups(const Table& tab, const Consts& c, co
             c2.k16 = f2_splat(16.0f);
             c2.km15 = f2_splat(-1.5f);
             for (; gl < lim; gl += st)
-              group_q4_x2<VLIN, PEERS>(lp, gl, l16, hmask, c2, Sm, Sv, lut_m, lut_v, qm_l, qv_l, (gl + st < lim) ? st : 0u, pi);
+              group_q4_x2<VLIN, PEERS>(lp, gl, l16, hmask, c2, Sm, Sv, lut_m, lut_v, qm_l, qv_l,
+                                       (gl + PF_DIST * st < lim) ? PF_DIST * st : 0u, pi);
           } else {
             for (; gl < lim; gl += st)
               group_q4_fast<FAST, VLIN>(lp, gl, l16, hmask, c, Sm, Sv, lut_m, lut_v, qm_l, qv_l,

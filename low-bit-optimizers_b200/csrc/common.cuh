@@ -242,13 +242,13 @@ struct f2x4 {
 };
 __device__ __forceinline__ f2x4 ldg_f2x4(const float* ptr) {
   f2x4 r;
-  asm volatile("ld.global.L1::no_allocate.v4.b64 {%0,%1,%2,%3}, [%4];"
+    asm volatile("ld.global.L1::no_allocate.v4.b64 {%0,%1,%2,%3}, [%4];"
                : "=l"(r.v[0]), "=l"(r.v[1]), "=l"(r.v[2]), "=l"(r.v[3])
                : "l"(ptr));
   return r;
 }
 __device__ __forceinline__ void stg_f2x4(float* ptr, const f2x4& r) {
-  asm volatile("st.global.v4.b64 [%4], {%0,%1,%2,%3};" ::"l"(r.v[0]), "l"(r.v[1]), "l"(r.v[2]), "l"(r.v[3]), "l"(ptr));
+    asm volatile("st.global.v4.b64 [%4], {%0,%1,%2,%3};" ::"l"(r.v[0]), "l"(r.v[1]), "l"(r.v[2]), "l"(r.v[3]), "l"(ptr));
 }
 
 }  // namespace lpmm_b200
