@@ -2,7 +2,7 @@
 
 Run in a container that holds the reference checkout:
 
-    python tests/golden/make_python_golden.py [--reference /root/reference]
+    python tests/golden/make_python_golden.py [--reference PATH_TO_REFERENCE_CHECKOUT]
 
 The reference package is imported unchanged through ``oracle/ref_loader.py`` (yacs stand-in, CPU
 stand-in for its pack/unpack extension).  For every case below the script records the initial
