@@ -214,6 +214,71 @@ class Zero1FusedAdamW:
             self._update(self.lo, self.hi)
         self._gather()
 
+    # ---- checkpoints --------------------------------------------------------------------------
+    def gather_state(self):
+        """Reassemble, on every rank, the optimizer state of the whole list in the layout of the
+        unsharded fused optimizer: per tensor ``exp_avg`` / ``exp_avg_sq`` as ``int8[(numel+1)//2]``
+        codes with ``float32[groups]`` scales, or fp32 moments for the small tensors; plus ``step``.
+        Collective: every rank must call it."""
+        S = self.shard_groups
+
+        def gathered(x):
+            if self.world == 1:
+                return x.clone()
+            out = torch.empty(self.world * x.numel(), dtype=x.dtype, device=x.device)
+            dist.all_gather_into_tensor(out, x.contiguous(), group=self.pg)
+            return out
+
+        mc, vc = gathered(self.m_codes), gathered(self.v_codes)
+        ms, vs = gathered(self.m_scale), gathered(self.v_scale)
+        # small-tensor fp32 moments: every rank contributes (first small-group index, data)
+        small = [None] * self.world
+        mine = (self.f_lo, self.m32.cpu(), self.v32.cpu())
+        if self.world == 1:
+            small = [mine]
+        else:
+            dist.all_gather_object(small, mine, group=self.pg)
+        f_total = self.fstart[-1] + (groups_of(self.numels[-1]) if self.numels[-1] <= THRESHOLD else 0) if self.numels else 0
+        m32 = torch.zeros(max(f_total, 1) * GROUP, dtype=torch.float32)
+        v32 = torch.zeros(max(f_total, 1) * GROUP, dtype=torch.float32)
+        for r, (f_lo, a, b) in enumerate(small):
+            lo, hi = owned_range(r, self.total_groups, S)
+            cnt = sum(y - x for (i, x, y) in owned_pieces(self.numels, self.gstart, lo, hi) if self.numels[i] <= THRESHOLD)
+            m32[f_lo * GROUP:(f_lo + cnt) * GROUP] = a[:cnt * GROUP]
+            v32[f_lo * GROUP:(f_lo + cnt) * GROUP] = b[:cnt * GROUP]
+        out = []
+        for n, gs, fs in zip(self.numels, self.gstart, self.fstart):
+            if n > THRESHOLD:
+                nb, ng = (n + 1) // 2, groups_of(n)
+                out.append({"step": float(self.step_count), "exp_avg": mc[gs * 64: gs * 64 + nb].clone(),
+                            "exp_avg_sq": vc[gs * 64: gs * 64 + nb].clone(), "exp_avg_scale": ms[gs: gs + ng].clone(),
+                            "exp_avg_sq_scale": vs[gs: gs + ng].clone()})
+            else:
+                out.append({"step": float(self.step_count), "exp_avg": m32[fs * GROUP: fs * GROUP + n].to(self.device),
+                            "exp_avg_sq": v32[fs * GROUP: fs * GROUP + n].to(self.device)})
+        return out
+
+    def load_full_state(self, states):
+        """Inverse of ``gather_state``: every rank keeps its own range of a full (unsharded-layout)
+        state list, e.g. one taken from ``lpmm.optim.AdamW(fused=True)``."""
+        self.step_count = int(states[0]["step"]) if states else 0
+        for buf in (self.m_codes, self.v_codes, self.m_scale, self.v_scale, self.m32, self.v32):
+            buf.zero_()
+        for i, a, b in owned_pieces(self.numels, self.gstart, self.lo, self.hi):
+            n, st = self.numels[i], states[i]
+            d = self.gstart[i] + a - self.lo
+            if n > THRESHOLD:
+                b0, b1 = a * 64, min(b * 64, (n + 1) // 2)
+                self.m_codes[d * 64: d * 64 + (b1 - b0)].copy_(st["exp_avg"].reshape(-1)[b0:b1])
+                self.v_codes[d * 64: d * 64 + (b1 - b0)].copy_(st["exp_avg_sq"].reshape(-1)[b0:b1])
+                self.m_scale[d: d + (b - a)].copy_(st["exp_avg_scale"].reshape(-1)[a:b])
+                self.v_scale[d: d + (b - a)].copy_(st["exp_avg_sq_scale"].reshape(-1)[a:b])
+            else:
+                e0, e1 = a * GROUP, min(b * GROUP, n)
+                df = self.fstart[i] + a - self.f_lo
+                self.m32[df * GROUP: df * GROUP + (e1 - e0)].copy_(st["exp_avg"].reshape(-1)[e0:e1])
+                self.v32[df * GROUP: df * GROUP + (e1 - e0)].copy_(st["exp_avg_sq"].reshape(-1)[e0:e1])
+
     # ---- measurement helpers (bench) -------------------------------------------------------------
     def time_update_only(self, iters):
         """Mean duration (ms) of the sharded update launch alone and its algorithmic bytes."""

@@ -157,3 +157,48 @@ def test_a_rank_leaving_between_steps_surfaces_as_an_error(golden_dir, tmp_path)
         port = s.getsockname()[1]
     mp.spawn(_dropout_worker, args=(2, port, golden_dir, str(tmp_path)), nprocs=2, join=True)
     assert (tmp_path / "verdict_0.txt").read_text().startswith("error"), "the surviving rank did not notice"
+
+
+# ---- sharded checkpoints -------------------------------------------------------------------------
+def _state_worker(rank, world, port, golden_dir, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    z = np.load(os.path.join(golden_dir, "qmaps.npz"))
+    opt = _make(world, rank, z["m"], z["v"])
+    for step in range(1, 3):
+        opt.set_grad_shard_from_full(_grads(step))
+        opt.step()
+    full = opt.gather_state()
+    # a fresh sharded optimizer resumed from the gathered state continues identically
+    opt2 = _make(world, rank, z["m"], z["v"])
+    opt2.flat.copy_(opt.flat)
+    opt2.load_full_state(full)
+    for o in (opt, opt2):
+        o.set_grad_shard_from_full(_grads(3))
+        o.step()
+    same = bool(torch.equal(opt.flat.view(torch.int32), opt2.flat.view(torch.int32)))
+    if rank == 0:
+        torch.save({"full": full, "same": same}, os.path.join(out_dir, "state.pt"))
+    dist.destroy_process_group()
+
+
+def test_sharded_state_gathers_to_the_unsharded_layout_and_reloads(golden_dir, tmp_path):
+    z = np.load(os.path.join(golden_dir, "qmaps.npz"))
+    single = _make(1, 0, z["m"], z["v"])
+    for step in range(1, 3):
+        single.set_grad_shard_from_full(_grads(step))
+        single.step()
+    ref = single.gather_state()
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_state_worker, args=(2, port, golden_dir, str(tmp_path)), nprocs=2, join=True)
+    got = torch.load(tmp_path / "state.pt", weights_only=False)
+    assert got["same"], "resuming from the gathered state changed the next step"
+    assert len(got["full"]) == len(ref) == len(SHAPES)
+    for i, (a, b) in enumerate(zip(got["full"], ref)):
+        assert a.keys() == b.keys() and a["step"] == b["step"] == 2.0
+        for k in a:
+            if k != "step":
+                assert a[k].dtype == b[k].dtype and a[k].shape == b[k].shape, (i, k)
+                assert torch.equal(a[k].view(torch.uint8), b[k].view(torch.uint8)), f"tensor {i} {k}"
