@@ -32,6 +32,7 @@ struct Shape {
 struct UConsts {
   float wd_mul, lerp_w, lerp_omw, beta2, omb2, inv_bc2s, bc2s, eps, alpha;
   int lerp_small;
+  int fast;  // eps keeps the denominator inside the domain of the short exact sqrt / division sequences
 };
 
 struct StepArgs {
@@ -146,6 +147,34 @@ __device__ __forceinline__ float axis_min(const float* const* vecs, const int* c
   return st;
 }
 
+// min_i vecs[i][idx_i] for the 8 consecutive elements starting at flat index e0.  2-D tensors whose
+// lane stays inside one row read the row value once and the 8 column values as two 128-bit loads.
+template <int ND>
+__device__ __forceinline__ void lane_scales(const float* const* vecs, long long e0, long long n, const Shape& s,
+                                            float* out) {
+  if (ND == 2) {
+    const long long C = s.dim[1];
+    const long long r = e0 / C;
+    const long long col = e0 - r * C;
+    if (col + 8 <= C && e0 + 8 <= n && ((reinterpret_cast<uintptr_t>(vecs[1] + col) & 15) == 0)) {
+      const float rv = __ldg(vecs[0] + r);
+      const float4 c0 = __ldg(reinterpret_cast<const float4*>(vecs[1] + col));
+      const float4 c1 = __ldg(reinterpret_cast<const float4*>(vecs[1] + col + 4));
+      out[0] = fminf(rv, c0.x); out[1] = fminf(rv, c0.y); out[2] = fminf(rv, c0.z); out[3] = fminf(rv, c0.w);
+      out[4] = fminf(rv, c1.x); out[5] = fminf(rv, c1.y); out[6] = fminf(rv, c1.z); out[7] = fminf(rv, c1.w);
+      return;
+    }
+  }
+  int co[8];
+  decompose<ND>(e0, s, co);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    out[k] = 1.0f;
+    if (e0 + k < n) out[k] = axis_min<ND>(vecs, co, s.nd);
+    advance<ND>(co, s);
+  }
+}
+
 // Monotone max of a non-negative float through an integer atomic; a stale read can only be too
 // small, so skipping the atomic when the value is not larger is always safe.
 __device__ __forceinline__ void atomic_max_nonneg(float* addr, float val) {
@@ -161,6 +190,10 @@ __device__ __forceinline__ float upd_v2(const UConsts& c, float v0, float g) {
 }
 __device__ __forceinline__ float upd_param(const UConsts& c, float p, float m, float v) {
   const float p1 = __fmul_rn(p, c.wd_mul);
+  if (c.fast) {
+    const float d = __fadd_rn(__fmul_rn(sqrt_rn_fast(v), c.inv_bc2s), c.eps);
+    return __fmaf_rn(c.alpha, div_rn_fast(m, d), p1);
+  }
   const float d = __fadd_rn(__fmul_rn(__fsqrt_rn(v), c.inv_bc2s), c.eps);
   return __fmaf_rn(c.alpha, __fdiv_rn(m, d), p1);
 }
@@ -201,15 +234,18 @@ __global__ void __launch_bounds__(UT) unfused_adamw_kernel(const StepArgs a, con
       if (vb) vcodes = *reinterpret_cast<const uint32_t*>(vb);
       if (VM == LPMM_B200_STATE_GROUP4) sv = a.v_max1[u];
     }
-    int co[8];
-    if (VM == LPMM_B200_STATE_RANK1_4) decompose<ND>(e0, a.s, co);
+    float st_old[8], st_new[8];
+    if (VM == LPMM_B200_STATE_RANK1_4) {
+      if (!a.first) lane_scales<ND>(a.v_old, e0, n, a.s, st_old);
+      lane_scales<ND>(a.v_new, e0, n, a.s, st_new);
+    }
     long long rowi = 0, cc = 0, bi = 0;  // factored: row index in the [B*R, C] view, column, batch entry
     if (VM == LPMM_B200_STATE_FACTORED) {
       rowi = e0 / C;
       cc = e0 - rowi * C;
       bi = e0 / RC;
     }
-    float m[8], v[8], st_new[8], gx[8], px[8];
+    float m[8], v[8], gx[8], px[8];
     float am = 0.0f, av = 0.0f;
     const bool full = a.vec_ok && (e0 + 8 <= n);
     if (full) {
@@ -229,7 +265,6 @@ __global__ void __launch_bounds__(UT) unfused_adamw_kernel(const StepArgs a, con
       const long long e = e0 + k;
       m[k] = 0.0f;
       v[k] = 0.0f;
-      st_new[k] = 1.0f;
       if (e < n) {
         const float g = gx[k];
         float m0 = 0.0f, v0 = 0.0f;
@@ -238,7 +273,7 @@ __global__ void __launch_bounds__(UT) unfused_adamw_kernel(const StepArgs a, con
           else m0 = reinterpret_cast<const float*>(a.m)[e];
           if (VM == LPMM_B200_STATE_GROUP4) v0 = __fmul_rn(M.qv[(vcodes >> (4 * k)) & 15u], sv);
           else if (VM == LPMM_B200_STATE_RANK1_4)
-            v0 = __fmul_rn(M.qv[(vcodes >> (4 * k)) & 15u], axis_min<ND>(a.v_old, co, a.s.nd));
+            v0 = __fmul_rn(M.qv[(vcodes >> (4 * k)) & 15u], st_old[k]);
           else if (VM == LPMM_B200_STATE_FP32) v0 = reinterpret_cast<const float*>(a.v)[e];
         }
         m[k] = lerp_m(c, m0, g);
@@ -253,9 +288,7 @@ __global__ void __launch_bounds__(UT) unfused_adamw_kernel(const StepArgs a, con
         av = fmaxf(av, v[k]);
         if (MM == LPMM_B200_STATE_FP32) reinterpret_cast<float*>(a.m)[e] = m[k];
         if (VM == LPMM_B200_STATE_FP32) reinterpret_cast<float*>(a.v)[e] = v[k];
-        if (VM == LPMM_B200_STATE_RANK1_4) st_new[k] = axis_min<ND>(a.v_new, co, a.s.nd);
       }
-      if (VM == LPMM_B200_STATE_RANK1_4) advance<ND>(co, a.s);
       if (VM == LPMM_B200_STATE_FACTORED && ++cc == C) {
         cc = 0;
         ++rowi;
@@ -332,7 +365,8 @@ __global__ void __launch_bounds__(UT) rank1_stats_kernel(const StepArgs a, const
       for (int k = 0; k < 8; ++k) gx[k] = (e0 + k < n) ? a.g[e0 + k] : 0.0f;
     }
     int co[8], run_co[8];
-    float run_max[8];
+    float run_max[8], st_old[8];
+    if (!a.first) lane_scales<ND>(a.v_old, e0, n, a.s, st_old);
     decompose<ND>(e0, a.s, co);
 #pragma unroll
     for (int i = 0; i < ND; ++i) {
@@ -343,7 +377,7 @@ __global__ void __launch_bounds__(UT) rank1_stats_kernel(const StepArgs a, const
     for (int k = 0; k < 8; ++k) {
       if (e0 + k < n) {
         float v0 = 0.0f;
-        if (!a.first) v0 = __fmul_rn(M.qv[(vcodes >> (4 * k)) & 15u], axis_min<ND>(a.v_old, co, nd));
+        if (!a.first) v0 = __fmul_rn(M.qv[(vcodes >> (4 * k)) & 15u], st_old[k]);
         const float v = upd_v2(c, v0, gx[k]);
 #pragma unroll
         for (int i = 0; i < ND; ++i) {
@@ -371,6 +405,54 @@ __global__ void __launch_bounds__(UT) rank1_stats_kernel(const StepArgs a, const
     __syncthreads();
     for (int i = threadIdx.x; i < (int)a.s.dim[last]; i += UT)
       atomic_max_nonneg(a.v_new[last] + i, __int_as_float(lastmax[i]));
+  }
+}
+
+// The same statistics pass for a matrix whose row length is a multiple of 8: a thread keeps its 8
+// columns for all the rows of its CTA, so column maxima live in registers and reach global memory
+// once per CTA; a row's maximum is reduced across the warp and costs one atomic per warp and row.
+__global__ void __launch_bounds__(UT) rank1_stats2d_kernel(const StepArgs a, const UConsts c,
+                                                            const float* __restrict__ qmap_v, int rows_per_cta) {
+  __shared__ Maps M;
+  load_maps(M, nullptr, qmap_v);
+  const long long R = a.s.dim[0], C = a.s.dim[1];
+  const long long c0 = ((long long)blockIdx.x * UT + threadIdx.x) * 8;
+  const bool active = c0 < C;
+  float col_old[8], col_max[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    col_old[k] = (active && !a.first) ? __ldg(a.v_old[1] + c0 + k) : 0.0f;
+    col_max[k] = 0.0f;
+  }
+  const long long r_begin = (long long)blockIdx.y * rows_per_cta;
+  const long long r_end = (r_begin + rows_per_cta < R) ? r_begin + rows_per_cta : R;
+  for (long long r = r_begin; r < r_end; ++r) {
+    float row_max = 0.0f;
+    if (active) {
+      const long long e0 = r * C + c0;
+      const float4 g0 = *reinterpret_cast<const float4*>(a.g + e0), g1 = *reinterpret_cast<const float4*>(a.g + e0 + 4);
+      const float gx[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+      uint32_t vcodes = 0;
+      float row_old = 0.0f;
+      if (!a.first) {
+        vcodes = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(a.v) + (e0 >> 1));
+        row_old = __ldg(a.v_old[0] + r);
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float v0 = a.first ? 0.0f : __fmul_rn(M.qv[(vcodes >> (4 * k)) & 15u], fminf(row_old, col_old[k]));
+        const float v = upd_v2(c, v0, gx[k]);
+        col_max[k] = fmaxf(col_max[k], v);
+        row_max = fmaxf(row_max, v);
+      }
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) row_max = fmaxf(row_max, __shfl_xor_sync(0xffffffffu, row_max, o));
+    if ((threadIdx.x & 31) == 0) atomic_max_nonneg(a.v_new[0] + r, row_max);
+  }
+  if (active) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) atomic_max_nonneg(a.v_new[1] + c0 + k, col_max[k]);
   }
 }
 
@@ -672,6 +754,7 @@ static UConsts make_consts(double beta1, double beta2, double lr, double wd, dou
   c.inv_bc2s = (float)(1.0 / sqrt(bc2));  // torch divides by a host scalar as x * float(1.0 / s)
   c.eps = (float)eps;
   c.alpha = (float)(-step_size);
+  c.fast = (eps >= 0x1p-40 && eps <= 0x1p30 && bc2 >= 0x1p-40);
   return c;
 }
 
@@ -855,7 +938,18 @@ extern "C" int lpmm_b200_adamw4bit_unfused_step(const lpmm_b200_step_tensor* t, 
     }
     int rc = zero_axes(a.s, t->v_max_dims_new, st);
     if (rc) return rc;
-    LPMM_DISPATCH_ND(t->ndim, (rank1_stats_kernel<ND><<<grid_for((a.n + 7) / 8, UT, 3), UT, 0, st>>>(a, c, qmap_v)));
+    if (t->ndim == 2 && t->shape[1] % 8 == 0 && a.vec_ok && (((uintptr_t)t->v & 3) == 0)) {
+      const long long R = t->shape[0], C = t->shape[1];
+      const long long col_ctas = (C / 8 + UT - 1) / UT;
+      long long row_ctas = ((long long)num_sms() * 6 + col_ctas - 1) / col_ctas;
+      if (row_ctas > R) row_ctas = R;
+      if (row_ctas > 65535) row_ctas = 65535;
+      const int rows_per_cta = (int)((R + row_ctas - 1) / row_ctas);
+      row_ctas = (R + rows_per_cta - 1) / rows_per_cta;
+      rank1_stats2d_kernel<<<dim3((unsigned)col_ctas, (unsigned)row_ctas), UT, 0, st>>>(a, c, qmap_v, rows_per_cta);
+    } else {
+      LPMM_DISPATCH_ND(t->ndim, (rank1_stats_kernel<ND><<<grid_for((a.n + 7) / 8, UT, 3), UT, 0, st>>>(a, c, qmap_v)));
+    }
     LPMM_CUDA_TRY(cudaGetLastError());
   }
   if (t->v_mode == LPMM_B200_STATE_FACTORED) {
