@@ -294,3 +294,57 @@ def test_largest_tensor_of_the_7b_list_matches_reference(qmaps):
         del g
     torch.cuda.synchronize()
     assert_same(p_my, st_my, p_ref, st_ref, "embedding-sized tensor")
+
+
+def test_full_7b_list_one_launch_equals_per_tensor_launches(qmaps):
+    """The headline workload at full size (6.74e9 parameters, 290 tensors): the single multi-tensor
+    launch and 290 single-tensor launches on a second copy give identical parameters, codes and
+    scales (compared through per-tensor integer checksums), for two consecutive steps."""
+    from gpu_helpers import llama7b_shapes
+    from lpmm import _kernels as K
+    free, _ = torch.cuda.mem_get_info()
+    if free < 120 * 2 ** 30:
+        pytest.skip("needs about 110 GB of free device memory")
+    N = _lib()
+    qm, qv, _ = device_qmaps(qmaps)
+    shapes = llama7b_shapes()
+    gen = torch.Generator(device=device())
+    gen.manual_seed(0)
+
+    def build():
+        out = []
+        for s in shapes:
+            n = int(np.prod(s))
+            if n > 4096:
+                st = fused_state(n)
+                out.append([None, None, st[0], st[1], st[2], st[3]])
+            else:
+                out.append([None, None, torch.zeros(s, device=device()), torch.zeros(s, device=device()), None, None])
+        return out
+
+    a, b = build(), build()
+    for ea, eb, s in zip(a, b, shapes):
+        ea[0] = torch.empty(s, device=device()).normal_(0, 0.02, generator=gen)
+        eb[0] = ea[0].clone()
+        g = torch.empty(s, device=device()).normal_(0, 1e-3, generator=gen)
+        ea[1] = eb[1] = g
+    tl = K.TensorList([tuple(e) for e in a])
+
+    def checksum(t):
+        return int(t.contiguous().view(torch.uint8).view(-1).to(torch.int64).sum()) if t.dtype == torch.int8 else \
+            int(t.contiguous().view(torch.int32).view(-1).to(torch.int64).sum())
+
+    for step in (1, 2):
+        K.adamw4bit_multi_tensor(tl, qm, qv, HYPER["beta1"], HYPER["beta2"], HYPER["lr"], HYPER["weight_decay"], HYPER["eps"],
+                                 float(step))
+        for e in b:
+            if e[4] is not None:
+                mine_step(N, e[0].view(-1), e[1].view(-1), e[2:6], qm, qv, step)
+            else:
+                K.adamw_single_tensor(e[0], e[1], e[2], e[3], HYPER["beta1"], HYPER["beta2"], HYPER["lr"],
+                                      HYPER["weight_decay"], HYPER["eps"], float(step))
+        torch.cuda.synchronize()
+    for i, (ea, eb) in enumerate(zip(a, b)):
+        for j in (0, 2, 3, 4, 5):
+            if ea[j] is not None:
+                assert checksum(ea[j]) == checksum(eb[j]), f"tensor {i}, field {j}"
