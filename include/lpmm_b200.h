@@ -173,13 +173,37 @@ int lpmm_b200_quant_rank1_4(const float* x, const int64_t* shape, int ndim, cons
 int lpmm_b200_dequant_rank1_4(const int8_t* codes, const float* qmap, const float* const* max_dims,
                               const int64_t* shape, int ndim, float* out, void* stream);
 
+/* The same six operations for every code width and group size of the reference's configuration
+ * files (lpmm/configs/default_{5,6,7,8}b.yml, 1st_moment_group_{256,...,4096}.yml):
+ *   bits        4 ... 8.  4: two codes per byte as above.  5 ... 8: one code per byte, the map has
+ *               2^bits entries (pack_nonlinear_8bit_kernel / unpack_nonlinear_8bit_kernel,
+ *               quantization_kernel.cu:515-537, 655-672); a NaN is stored as 255 like there.
+ *               1 ... 3 bits return LPMM_B200_ERR_UNSUPPORTED.
+ *   group_size  128, 256, ..., 4096 (a power of two): x is zero-padded to a multiple of it before
+ *               normalisation, max1 holds ceil(numel/group_size) maxima
+ *               (group_tensor, lpmm/functional.py:359-369).
+ * Packed length: rows of 2048 codes, (bits == 4 ? 1/2 : 1) byte per code, plus one trailing byte.
+ * The ...4 entry points above are these with bits = 4 and group_size = 128. */
+int64_t lpmm_b200_packed_len_bits(int64_t n_scaled, int bits);
+int lpmm_b200_pack_nonlinear(const float* data, int64_t n, const float* qmap, int bits, int8_t* packed, void* stream);
+int lpmm_b200_unpack_nonlinear(const int8_t* packed, const float* qmap, int bits, int64_t n, float* out,
+                               void* stream);
+int lpmm_b200_quant_group(const float* x, int64_t numel, const float* qmap, int bits, int64_t group_size,
+                          int8_t* codes, float* max1, void* stream);
+int lpmm_b200_dequant_group(const int8_t* codes, const float* qmap, int bits, int64_t group_size, const float* max1,
+                            int64_t numel, float* out, void* stream);
+int lpmm_b200_quant_rank1(const float* x, const int64_t* shape, int ndim, const float* qmap, int bits,
+                          float* const* max_dims, int8_t* codes, void* stream);
+int lpmm_b200_dequant_rank1(const int8_t* codes, const float* qmap, int bits, const float* const* max_dims,
+                            const int64_t* shape, int ndim, float* out, void* stream);
+
 /* ------------------------------------------------------------------------------------------- */
 /* One-launch-per-tensor steps with the arithmetic of the reference's non-fused Python path     */
 /* ------------------------------------------------------------------------------------------- */
 
 #define LPMM_B200_STATE_FP32 0    /* float[numel]                                               */
-#define LPMM_B200_STATE_GROUP4 1  /* 4-bit codes, group-128 scales, vectorwise_quant layout     */
-#define LPMM_B200_STATE_RANK1_4 2 /* 4-bit codes, per-axis maxima (ndim >= 2)                   */
+#define LPMM_B200_STATE_GROUP4 1  /* codes + group scales, vectorwise_quant layout (4 bits, groups of 128 unless the bits / group fields say otherwise) */
+#define LPMM_B200_STATE_RANK1_4 2 /* codes + per-axis maxima (ndim >= 2)                        */
 #define LPMM_B200_STATE_FACTORED 3/* fp32 row / column accumulators (ndim >= 2), no codes       */
 
 typedef struct lpmm_b200_step_tensor {
@@ -199,6 +223,8 @@ typedef struct lpmm_b200_step_tensor {
   float* v_max_dims_new[8];       /* RANK1_4: receives the maxima of the updated second moment  */
   float* row;                   /* FACTORED: float[prod(shape[:-1])]                            */
   float* col;                   /* FACTORED: float[prod(shape[:-2]) * shape[-1]]                */
+  int32_t m_bits, v_bits;       /* code width of a quantized state, 4 ... 8; 0 means 4            */
+  int32_t m_group, v_group;     /* group size of a GROUP4 state: 128 ... 4096, power of two; 0 = 128 */
 } lpmm_b200_step_tensor;
 
 /* One AdamW step of one tensor with the arithmetic and state layout of the reference's
@@ -219,6 +245,11 @@ int64_t lpmm_b200_factored_scratch_bytes(const int64_t* shape, int ndim);
 int lpmm_b200_sgd4bit_step(float* p, const float* g, int64_t numel, void* buf, float* buf_max1, int buf_mode,
                            int first, const float* qmap, double weight_decay, double momentum, double lr,
                            double dampening, int nesterov, int maximize, void* stream);
+/* The same with the buffer's code width (4 ... 8) and group size (128 ... 4096) given. */
+int lpmm_b200_sgd_lowbit_step(float* p, const float* g, int64_t numel, void* buf, float* buf_max1, int buf_mode,
+                              int bits, int64_t group_size, int first, const float* qmap, double weight_decay,
+                              double momentum, double lr, double dampening, int nesterov, int maximize,
+                              void* stream);
 
 /* Allocation-free variant of the factored step, for callers that cannot allocate device memory.
  * It has no counterpart in the reference.

@@ -14,15 +14,20 @@
 // The contraction choices were settled against torch's own CUDA kernels.
 //
 // Layout: a half-warp owns a unit of 128 consecutive elements (lane = 8 elements), as in the
-// fused step.  Codes live in the reference's padded layout: ceil(n'/2048)*1024 bytes plus one
-// trailing byte, n' = numel rounded up to 128 (group scales) or numel (rank-1 scales).
+// fused step.  Codes live in the reference's padded layout: n' = numel rounded up to the group
+// size (group scales) or numel (rank-1 scales), rounded up again to rows of 2048 codes, plus one
+// trailing byte.  4-bit maps pack two codes per byte (even element in the low nibble); maps of
+// 5 to 8 bits store one code per byte ("wide", template parameter W).  A group of 128 elements is
+// one half-warp; larger groups (256 ... 4096, powers of two) are 2 ... 32 adjacent half-warps of one
+// CTA whose maxima are combined through shared memory.
 #include <math.h>
 
 #include "common.cuh"
 
 namespace lpmm_b200 {
 
-constexpr int UT = 256;  // threads per CTA
+constexpr int UT = 256;     // threads per CTA
+constexpr int UTMAX = 512;  // threads per CTA when a group spans 32 half-warps (4096 elements)
 
 struct Shape {
   int nd;
@@ -39,7 +44,8 @@ struct StepArgs {
   float* p;
   const float* g;
   long long n;
-  long long units;  // padded length / 128
+  long long units;  // loop bound: the larger of units_m and units_v
+  long long units_m, units_v;  // padded length / 128 of each quantized state (0 when not quantized)
   int first;
   int vec_ok;  // p and g are 16-byte aligned: full lanes use 128-bit accesses
   void* m;
@@ -52,18 +58,22 @@ struct StepArgs {
   float* col;
   const float* row_mean;  // per batch (factored)
   Shape s;
+  int bits_m, bits_v;  // 4 ... 8
+  int hpg_m, hpg_v;    // half-warps (128-element units) per group: group size / 128, a power of two
+  int sh_m, sh_v;      // log2 of the above
 };
 
 struct Maps {
-  float qm[16];
-  float qv[16];
-  float mm[16];  // midpoints of qm, padded with +inf
-  float mv[16];
+  float qm[256];
+  float qv[256];
+  float mm[256];  // midpoints of qm, padded with +inf
+  float mv[256];
   int zero_m, zero_v;  // code of 0.0f in each map (what padding quantizes to)
 };
 
-// Nearest-code rule as a branch-free four-step search over the 15 sorted midpoints:
-// code = #{midpoints < x}; a NaN gives 15 like the reference's search.
+// Nearest-code rule as a branch-free search over the sorted midpoints: code = #{midpoints < x}.
+// A NaN gives what the reference's search gives: 15 in the packed 4-bit kernel, (uint8_t)-1 in the
+// one-code-per-byte kernel (quantization_kernel.cu:398-427, :533).
 __device__ __forceinline__ int code16(const float* __restrict__ mids, float x) {
   int c = (mids[7] < x) ? 8 : 0;
   c += (mids[c + 3] < x) ? 4 : 0;
@@ -71,38 +81,92 @@ __device__ __forceinline__ int code16(const float* __restrict__ mids, float x) {
   c += (mids[c] < x) ? 1 : 0;
   return (x != x) ? 15 : c;
 }
+template <bool W>
+__device__ __forceinline__ int code_of(const float* __restrict__ mids, int bits, float x) {
+  if (!W) return code16(mids, x);
+  int c = 0;
+  for (int s = 1 << (bits - 1); s; s >>= 1) c += (mids[c + s - 1] < x) ? s : 0;
+  return (x != x) ? 255 : c;
+}
 
-// x / d for the 8 values of a lane with a divisor shared by the half-warp: the shared-reciprocal
+// The 8 codes of a lane.  W = false: nibbles of one 32-bit word; W = true: bytes of two words.
+template <bool W>
+struct Codes8 {
+  uint32_t lo, hi;
+  __device__ __forceinline__ static long long byte_off(long long e0) { return W ? e0 : (e0 >> 1); }
+  __device__ __forceinline__ static long long trailing(long long units) { return W ? units * 128 : units * 64; }
+  __device__ __forceinline__ void clear() { lo = hi = 0u; }
+  __device__ __forceinline__ void fill(int c) {
+    lo = hi = (W ? 0x01010101u : 0x11111111u) * (uint32_t)c;
+  }
+  __device__ __forceinline__ void load(const uint8_t* p) {
+    if (W) {
+      const uint2 w = *reinterpret_cast<const uint2*>(p);
+      lo = w.x;
+      hi = w.y;
+    } else {
+      lo = *reinterpret_cast<const uint32_t*>(p);
+      hi = 0u;
+    }
+  }
+  __device__ __forceinline__ void store(uint8_t* p) const {
+    if (W) *reinterpret_cast<uint2*>(p) = make_uint2(lo, hi);
+    else *reinterpret_cast<uint32_t*>(p) = lo;
+  }
+  __device__ __forceinline__ int get(int k) const {
+    if (W) return (int)(((k < 4 ? lo : hi) >> (8 * (k & 3))) & 255u);
+    return (int)((lo >> (4 * k)) & 15u);
+  }
+  __device__ __forceinline__ void set(int k, int c) {  // into a cleared word
+    if (W) {
+      if (k < 4) lo |= (uint32_t)(c & 255) << (8 * k);
+      else hi |= (uint32_t)(c & 255) << (8 * (k - 4));
+    } else {
+      lo |= (uint32_t)(c & 15) << (4 * k);
+    }
+  }
+};
+
+// x / d for the 8 values of a lane with a divisor shared by the group: the shared-reciprocal
 // division (equal to IEEE division, see common.cuh) when d is in its domain, IEEE division otherwise.
-__device__ __forceinline__ uint32_t codes_by_group_scale(const float* __restrict__ mids, const float* x, float d) {
-  uint32_t out = 0;
+template <bool W>
+__device__ __forceinline__ Codes8<W> codes_by_group_scale(const float* __restrict__ mids, int bits, const float* x,
+                                                          float d) {
+  Codes8<W> out;
+  out.clear();
   if (udiv_ok(d)) {
     const float r = rcp_nr(d);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) out |= (uint32_t)code16(mids, udiv(x[k], d, r)) << (4 * k);
+    for (int k = 0; k < 8; ++k) out.set(k, code_of<W>(mids, bits, udiv(x[k], d, r)));
   } else {
 #pragma unroll
-    for (int k = 0; k < 8; ++k) out |= (uint32_t)code16(mids, __fdiv_rn(x[k], d)) << (4 * k);
+    for (int k = 0; k < 8; ++k) out.set(k, code_of<W>(mids, bits, __fdiv_rn(x[k], d)));
   }
   return out;
 }
 
-__device__ __forceinline__ void load_maps(Maps& M, const float* __restrict__ qm, const float* __restrict__ qv) {
-  const int tid = threadIdx.x;
-  if (tid < 16) {
-    M.qm[tid] = qm ? qm[tid] : 0.0f;
-    M.qv[tid] = qv ? qv[tid] : 0.0f;
+// Copies both maps (2^bits entries each; a null map reads as zeros) into shared memory and derives
+// their midpoints.  Entries past the end of a map are NaN (a NaN input's code 255 of a map with
+// fewer than 8 bits decodes to NaN instead of reading past the caller's map), midpoints +inf.
+template <bool W>
+__device__ __forceinline__ void load_maps(Maps& M, const float* __restrict__ qm, const float* __restrict__ qv,
+                                          int bits_m, int bits_v) {
+  const int nm = 1 << bits_m, nv = 1 << bits_v;
+  const float inf = __int_as_float(0x7f800000), nan = __int_as_float(0x7fc00000);
+  const int cap = W ? 256 : 16;
+  for (int i = threadIdx.x; i < cap; i += blockDim.x) {
+    M.qm[i] = (i < nm) ? (qm ? qm[i] : 0.0f) : nan;
+    M.qv[i] = (i < nv) ? (qv ? qv[i] : 0.0f) : nan;
   }
   __syncthreads();
-  if (tid < 16) {
-    const float inf = __int_as_float(0x7f800000);
-    M.mm[tid] = tid < 15 ? __fmul_rn(__fadd_rn(M.qm[tid], M.qm[tid + 1]), 0.5f) : inf;
-    M.mv[tid] = tid < 15 ? __fmul_rn(__fadd_rn(M.qv[tid], M.qv[tid + 1]), 0.5f) : inf;
+  for (int i = threadIdx.x; i < cap; i += blockDim.x) {
+    M.mm[i] = (i < nm - 1) ? __fmul_rn(__fadd_rn(M.qm[i], M.qm[i + 1]), 0.5f) : inf;
+    M.mv[i] = (i < nv - 1) ? __fmul_rn(__fadd_rn(M.qv[i], M.qv[i + 1]), 0.5f) : inf;
   }
   __syncthreads();
-  if (tid == 0) {
-    M.zero_m = code16(M.mm, 0.0f);
-    M.zero_v = code16(M.mv, 0.0f);
+  if (threadIdx.x == 0) {
+    M.zero_m = code_of<W>(M.mm, bits_m, 0.0f);
+    M.zero_v = code_of<W>(M.mv, bits_v, 0.0f);
   }
   __syncthreads();
 }
@@ -111,6 +175,20 @@ __device__ __forceinline__ float hmax16(float x, unsigned mask) {
 #pragma unroll
   for (int o = 8; o; o >>= 1) x = fmaxf(x, __shfl_xor_sync(mask, x, o, 16));
   return x;
+}
+
+// Maximum over the hpg adjacent half-warps that form one group (hpg a power of two, the group
+// aligned to hpg half-warps inside the CTA).  Every thread of the CTA must call it.
+__device__ __forceinline__ float group_max(float a, int hpg, float* red) {
+  if (hpg == 1) return a;
+  const int hw = threadIdx.x >> 4;
+  __syncthreads();
+  if ((threadIdx.x & 15) == 0) red[hw] = a;
+  __syncthreads();
+  const int b = hw & ~(hpg - 1);
+  float r = red[b];
+  for (int i = 1; i < hpg; ++i) r = fmaxf(r, red[b + i]);
+  return r;
 }
 
 // Row-major coordinates of a flat index, and the step to the next element.  ND is the exact
@@ -201,41 +279,50 @@ __device__ __forceinline__ float upd_param(const UConsts& c, float p, float m, f
 // ---------------------------------------------------------------------------------------------
 // AdamW, non-fused semantics.  MM: first-moment storage, VM: second-moment storage / source.
 // ---------------------------------------------------------------------------------------------
-template <int MM, int VM, int ND>
-__global__ void __launch_bounds__(UT) unfused_adamw_kernel(const StepArgs a, const UConsts c,
-                                                            const float* __restrict__ qmap_m,
-                                                            const float* __restrict__ qmap_v) {
+// Register budget: 64 per thread (4 CTAs of 256 threads per SM) except for the rank-1 variants, whose
+// index arithmetic needs more.
+template <int MM, int VM, int ND, bool W>
+__global__ void __launch_bounds__(UTMAX, (VM == LPMM_B200_STATE_RANK1_4) ? 1 : 2) unfused_adamw_kernel(const StepArgs a, const UConsts c,
+                                                               const float* __restrict__ qmap_m,
+                                                               const float* __restrict__ qmap_v) {
   __shared__ Maps M;
-  load_maps(M, qmap_m, qmap_v);
+  __shared__ float red[UTMAX / 16];
+  load_maps<W>(M, qmap_m, qmap_v, a.bits_m, a.bits_v);
+  constexpr bool MQ = (MM == LPMM_B200_STATE_GROUP4);
+  constexpr bool VQ = (VM == LPMM_B200_STATE_GROUP4 || VM == LPMM_B200_STATE_RANK1_4);
   const int l16 = threadIdx.x & 15;
+  const int hw = threadIdx.x >> 4, hw_per_cta = blockDim.x >> 4;
   const unsigned hmask = 0xFFFFu << (threadIdx.x & 16);
   const long long n = a.n;
-  const long long real_units = (n + 127) / 128;
+  // units that hold elements or in-group padding (zeros before normalisation); later units are
+  // the zeros that fill up the last row of 2048 after normalisation
+  const long long in_m = MQ ? (n + 128LL * a.hpg_m - 1) / (128LL * a.hpg_m) * a.hpg_m : (n + 127) / 128;
+  const long long in_v = (VM == LPMM_B200_STATE_GROUP4) ? (n + 128LL * a.hpg_v - 1) / (128LL * a.hpg_v) * a.hpg_v
+                                                         : (n + 127) / 128;
   const long long C = (VM == LPMM_B200_STATE_FACTORED) ? a.s.dim[a.s.nd - 1] : 1;
   const long long RC = (VM == LPMM_B200_STATE_FACTORED) ? C * a.s.dim[a.s.nd - 2] : 1;
-  for (long long u = (long long)blockIdx.x * (UT / 16) + (threadIdx.x >> 4); u < a.units;
-       u += (long long)gridDim.x * (UT / 16)) {
+  // a.units is a multiple of the half-warps per CTA, so every half-warp of a CTA makes the same
+  // number of trips and the group reductions below may synchronise the CTA.  The two states may
+  // have different padded lengths (group padding vs none): each is stored up to its own.
+  for (long long u = (long long)blockIdx.x * hw_per_cta + hw; u < a.units; u += (long long)gridDim.x * hw_per_cta) {
     const long long e0 = u * 128 + l16 * 8;
-    uint8_t* mb = (MM == LPMM_B200_STATE_GROUP4) ? reinterpret_cast<uint8_t*>(a.m) + (e0 >> 1) : nullptr;
-    uint8_t* vb = (VM == LPMM_B200_STATE_GROUP4 || VM == LPMM_B200_STATE_RANK1_4)
-                      ? reinterpret_cast<uint8_t*>(a.v) + (e0 >> 1) : nullptr;
-    if (u >= real_units) {  // rows of 2048 are filled up with zeros after normalisation
-      if (mb) *reinterpret_cast<uint32_t*>(mb) = 0x11111111u * (uint32_t)M.zero_m;
-      if (vb) *reinterpret_cast<uint32_t*>(vb) = 0x11111111u * (uint32_t)M.zero_v;
-      continue;
-    }
-    uint32_t mcodes = 0, vcodes = 0;
+    uint8_t* mb = MQ ? reinterpret_cast<uint8_t*>(a.m) + Codes8<W>::byte_off(e0) : nullptr;
+    uint8_t* vb = VQ ? reinterpret_cast<uint8_t*>(a.v) + Codes8<W>::byte_off(e0) : nullptr;
+    const bool has_data = e0 < n;  // this lane holds at least one element
+    Codes8<W> mcodes, vcodes;
+    mcodes.clear();
+    vcodes.clear();
     float sm = 0.0f, sv = 0.0f;
-    if (!a.first) {
-      if (MM == LPMM_B200_STATE_GROUP4) {
-        mcodes = *reinterpret_cast<const uint32_t*>(mb);
-        sm = a.m_max1[u];
+    if (!a.first && has_data) {
+      if (MQ) {
+        mcodes.load(mb);
+        sm = a.m_max1[u >> a.sh_m];
       }
-      if (vb) vcodes = *reinterpret_cast<const uint32_t*>(vb);
-      if (VM == LPMM_B200_STATE_GROUP4) sv = a.v_max1[u];
+      if (VQ) vcodes.load(vb);
+      if (VM == LPMM_B200_STATE_GROUP4) sv = a.v_max1[u >> a.sh_v];
     }
     float st_old[8], st_new[8];
-    if (VM == LPMM_B200_STATE_RANK1_4) {
+    if (VM == LPMM_B200_STATE_RANK1_4 && has_data) {
       if (!a.first) lane_scales<ND>(a.v_old, e0, n, a.s, st_old);
       lane_scales<ND>(a.v_new, e0, n, a.s, st_new);
     }
@@ -269,11 +356,10 @@ __global__ void __launch_bounds__(UT) unfused_adamw_kernel(const StepArgs a, con
         const float g = gx[k];
         float m0 = 0.0f, v0 = 0.0f;
         if (!a.first) {
-          if (MM == LPMM_B200_STATE_GROUP4) m0 = __fmul_rn(M.qm[(mcodes >> (4 * k)) & 15u], sm);
+          if (MQ) m0 = __fmul_rn(M.qm[mcodes.get(k)], sm);
           else m0 = reinterpret_cast<const float*>(a.m)[e];
-          if (VM == LPMM_B200_STATE_GROUP4) v0 = __fmul_rn(M.qv[(vcodes >> (4 * k)) & 15u], sv);
-          else if (VM == LPMM_B200_STATE_RANK1_4)
-            v0 = __fmul_rn(M.qv[(vcodes >> (4 * k)) & 15u], st_old[k]);
+          if (VM == LPMM_B200_STATE_GROUP4) v0 = __fmul_rn(M.qv[vcodes.get(k)], sv);
+          else if (VM == LPMM_B200_STATE_RANK1_4) v0 = __fmul_rn(M.qv[vcodes.get(k)], st_old[k]);
           else if (VM == LPMM_B200_STATE_FP32) v0 = reinterpret_cast<const float*>(a.v)[e];
         }
         m[k] = lerp_m(c, m0, g);
@@ -303,31 +389,40 @@ __global__ void __launch_bounds__(UT) unfused_adamw_kernel(const StepArgs a, con
       for (int k = 0; k < 8; ++k)
         if (e0 + k < n) a.p[e0 + k] = px[k];
     }
-    if (MM == LPMM_B200_STATE_GROUP4) {
-      am = hmax16(am, hmask);
-      // padding inside the last group is 0 / max
-      *reinterpret_cast<uint32_t*>(mb) = codes_by_group_scale(M.mm, m, am);
-      if (l16 == 0) a.m_max1[u] = am;
+    if (MQ) {
+      am = group_max(hmax16(am, hmask), a.hpg_m, red);
+      Codes8<W> out;
+      if (u < in_m) {
+        out = codes_by_group_scale<W>(M.mm, a.bits_m, m, am);  // padding inside the last group is 0 / max
+        if (l16 == 0 && (u & (a.hpg_m - 1)) == 0) a.m_max1[u >> a.sh_m] = am;
+      } else {
+        out.fill(M.zero_m);
+      }
+      if (u < a.units_m) out.store(mb);
     }
     if (VM == LPMM_B200_STATE_GROUP4) {
-      av = hmax16(av, hmask);
-      *reinterpret_cast<uint32_t*>(vb) = codes_by_group_scale(M.mv, v, av);
-      if (l16 == 0) a.v_max1[u] = av;
+      av = group_max(hmax16(av, hmask), a.hpg_v, red);
+      Codes8<W> out;
+      if (u < in_v) {
+        out = codes_by_group_scale<W>(M.mv, a.bits_v, v, av);
+        if (l16 == 0 && (u & (a.hpg_v - 1)) == 0) a.v_max1[u >> a.sh_v] = av;
+      } else {
+        out.fill(M.zero_v);
+      }
+      if (u < a.units_v) out.store(vb);
     }
     if (VM == LPMM_B200_STATE_RANK1_4) {
-      uint32_t out = 0;
+      Codes8<W> out;
+      out.clear();
 #pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        const int code = (e0 + k < n) ? code16(M.mv, __fdiv_rn(v[k], st_new[k])) : M.zero_v;
-        out |= (uint32_t)(code & 15) << (4 * k);
-      }
-      *reinterpret_cast<uint32_t*>(vb) = out;
+      for (int k = 0; k < 8; ++k)
+        out.set(k, (e0 + k < n) ? code_of<W>(M.mv, a.bits_v, __fdiv_rn(v[k], st_new[k])) : M.zero_v);
+      if (u < a.units_v) out.store(vb);
     }
   }
   if (blockIdx.x == 0 && threadIdx.x == 0) {  // the trailing byte of the packed layout
-    if (MM == LPMM_B200_STATE_GROUP4) reinterpret_cast<uint8_t*>(a.m)[a.units * 64] = 0;
-    if (VM == LPMM_B200_STATE_GROUP4 || VM == LPMM_B200_STATE_RANK1_4)
-      reinterpret_cast<uint8_t*>(a.v)[a.units * 64] = 0;
+    if (MQ) reinterpret_cast<uint8_t*>(a.m)[Codes8<W>::trailing(a.units_m)] = 0;
+    if (VQ) reinterpret_cast<uint8_t*>(a.v)[Codes8<W>::trailing(a.units_v)] = 0;
   }
 }
 
@@ -337,12 +432,12 @@ __global__ void __launch_bounds__(UT) unfused_adamw_kernel(const StepArgs a, con
 // flushed once per CTA; the outer axes change rarely along a lane's 8 consecutive elements, so a
 // lane combines runs of equal coordinates in registers before touching global memory.
 constexpr int STAT_LAST = 8192;
-template <int ND>
+template <int ND, bool W>
 __global__ void __launch_bounds__(UT) rank1_stats_kernel(const StepArgs a, const UConsts c,
                                                           const float* __restrict__ qmap_v) {
   __shared__ Maps M;
   __shared__ int lastmax[STAT_LAST];
-  load_maps(M, nullptr, qmap_v);
+  load_maps<W>(M, nullptr, qmap_v, 4, a.bits_v);
   const int nd = a.s.nd;
   const int last = nd - 1;
   const bool use_smem = a.s.dim[last] <= STAT_LAST;
@@ -354,8 +449,9 @@ __global__ void __launch_bounds__(UT) rank1_stats_kernel(const StepArgs a, const
   const long long nchunks = (n + 7) / 8;
   for (long long ch = (long long)blockIdx.x * UT + threadIdx.x; ch < nchunks; ch += (long long)gridDim.x * UT) {
     const long long e0 = ch * 8;
-    uint32_t vcodes = 0;
-    if (!a.first) vcodes = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(a.v) + (e0 >> 1));
+    Codes8<W> vcodes;
+    vcodes.clear();
+    if (!a.first) vcodes.load(reinterpret_cast<const uint8_t*>(a.v) + Codes8<W>::byte_off(e0));
     float gx[8];
     if (a.vec_ok && e0 + 8 <= n) {
       const float4 g0 = *reinterpret_cast<const float4*>(a.g + e0), g1 = *reinterpret_cast<const float4*>(a.g + e0 + 4);
@@ -377,7 +473,7 @@ __global__ void __launch_bounds__(UT) rank1_stats_kernel(const StepArgs a, const
     for (int k = 0; k < 8; ++k) {
       if (e0 + k < n) {
         float v0 = 0.0f;
-        if (!a.first) v0 = __fmul_rn(M.qv[(vcodes >> (4 * k)) & 15u], st_old[k]);
+        if (!a.first) v0 = __fmul_rn(M.qv[vcodes.get(k)], st_old[k]);
         const float v = upd_v2(c, v0, gx[k]);
 #pragma unroll
         for (int i = 0; i < ND; ++i) {
@@ -411,10 +507,11 @@ __global__ void __launch_bounds__(UT) rank1_stats_kernel(const StepArgs a, const
 // The same statistics pass for a matrix whose row length is a multiple of 8: a thread keeps its 8
 // columns for all the rows of its CTA, so column maxima live in registers and reach global memory
 // once per CTA; a row's maximum is reduced across the warp and costs one atomic per warp and row.
+template <bool W>
 __global__ void __launch_bounds__(UT) rank1_stats2d_kernel(const StepArgs a, const UConsts c,
                                                             const float* __restrict__ qmap_v, int rows_per_cta) {
   __shared__ Maps M;
-  load_maps(M, nullptr, qmap_v);
+  load_maps<W>(M, nullptr, qmap_v, 4, a.bits_v);
   const long long R = a.s.dim[0], C = a.s.dim[1];
   const long long c0 = ((long long)blockIdx.x * UT + threadIdx.x) * 8;
   const bool active = c0 < C;
@@ -432,15 +529,16 @@ __global__ void __launch_bounds__(UT) rank1_stats2d_kernel(const StepArgs a, con
       const long long e0 = r * C + c0;
       const float4 g0 = *reinterpret_cast<const float4*>(a.g + e0), g1 = *reinterpret_cast<const float4*>(a.g + e0 + 4);
       const float gx[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
-      uint32_t vcodes = 0;
+      Codes8<W> vcodes;
+      vcodes.clear();
       float row_old = 0.0f;
       if (!a.first) {
-        vcodes = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(a.v) + (e0 >> 1));
+        vcodes.load(reinterpret_cast<const uint8_t*>(a.v) + Codes8<W>::byte_off(e0));
         row_old = __ldg(a.v_old[0] + r);
       }
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
-        const float v0 = a.first ? 0.0f : __fmul_rn(M.qv[(vcodes >> (4 * k)) & 15u], fminf(row_old, col_old[k]));
+        const float v0 = a.first ? 0.0f : __fmul_rn(M.qv[vcodes.get(k)], fminf(row_old, col_old[k]));
         const float v = upd_v2(c, v0, gx[k]);
         col_max[k] = fmaxf(col_max[k], v);
         row_max = fmaxf(row_max, v);
@@ -531,29 +629,28 @@ struct SgdConsts {
   int has_wd, has_momentum, nesterov, maximize;
 };
 
-template <int BM>
-__global__ void __launch_bounds__(UT) sgd_kernel(float* __restrict__ p, const float* __restrict__ g, long long n,
-                                                  long long units, void* buf, float* __restrict__ buf_max1,
-                                                  int first, const float* __restrict__ qmap, const SgdConsts c) {
+template <int BM, bool W>
+__global__ void __launch_bounds__(UTMAX, 2) sgd_kernel(float* __restrict__ p, const float* __restrict__ g, long long n,
+                                                     long long units, void* buf, float* __restrict__ buf_max1,
+                                                     int first, const float* __restrict__ qmap, int bits, int hpg,
+                                                     int sh, const SgdConsts c) {
   __shared__ Maps M;
-  load_maps(M, qmap, nullptr);
+  __shared__ float red[UTMAX / 16];
+  load_maps<W>(M, qmap, nullptr, bits, 4);
   const int l16 = threadIdx.x & 15;
+  const int hw = threadIdx.x >> 4, hw_per_cta = blockDim.x >> 4;
   const unsigned hmask = 0xFFFFu << (threadIdx.x & 16);
-  const long long real_units = (n + 127) / 128;
-  for (long long u = (long long)blockIdx.x * (UT / 16) + (threadIdx.x >> 4); u < units;
-       u += (long long)gridDim.x * (UT / 16)) {
+  const long long in_units = (n + 128LL * hpg - 1) / (128LL * hpg) * hpg;
+  const bool quantized = (BM == LPMM_B200_STATE_GROUP4) && c.has_momentum;
+  for (long long u = (long long)blockIdx.x * hw_per_cta + hw; u < units; u += (long long)gridDim.x * hw_per_cta) {
     const long long e0 = u * 128 + l16 * 8;
-    uint8_t* bb = (BM == LPMM_B200_STATE_GROUP4 && c.has_momentum) ? reinterpret_cast<uint8_t*>(buf) + (e0 >> 1)
-                                                                    : nullptr;
-    if (u >= real_units) {
-      if (bb) *reinterpret_cast<uint32_t*>(bb) = 0x11111111u * (uint32_t)M.zero_m;
-      continue;
-    }
-    uint32_t codes = 0;
+    uint8_t* bb = quantized ? reinterpret_cast<uint8_t*>(buf) + Codes8<W>::byte_off(e0) : nullptr;
+    Codes8<W> codes;
+    codes.clear();
     float sc = 0.0f;
-    if (bb && !first) {
-      codes = *reinterpret_cast<const uint32_t*>(bb);
-      sc = buf_max1[u];
+    if (bb && !first && e0 < n) {
+      codes.load(bb);
+      sc = buf_max1[u >> sh];
     }
     float b[8];
     float ab = 0.0f;
@@ -570,7 +667,7 @@ __global__ void __launch_bounds__(UT) sgd_kernel(float* __restrict__ p, const fl
           if (first) {
             bv = d;                                                    // clone of d_p
           } else {
-            const float b0 = (BM == LPMM_B200_STATE_GROUP4) ? __fmul_rn(M.qm[(codes >> (4 * k)) & 15u], sc)
+            const float b0 = (BM == LPMM_B200_STATE_GROUP4) ? __fmul_rn(M.qm[codes.get(k)], sc)
                                                             : reinterpret_cast<const float*>(buf)[e];
             bv = __fmaf_rn(c.omd, d, __fmul_rn(b0, c.momentum));       // mul_(momentum).add_(d_p, alpha=1-dampening)
           }
@@ -582,62 +679,75 @@ __global__ void __launch_bounds__(UT) sgd_kernel(float* __restrict__ p, const fl
         p[e] = __fmaf_rn(c.neg_lr, d, pe);                             // param.add_(d_p, alpha=-lr)
       }
     }
-    if (bb) {
-      ab = hmax16(ab, hmask);
-      *reinterpret_cast<uint32_t*>(bb) = codes_by_group_scale(M.mm, b, ab);
-      if (l16 == 0) buf_max1[u] = ab;
+    if (quantized) {
+      ab = group_max(hmax16(ab, hmask), hpg, red);
+      Codes8<W> out;
+      if (u < in_units) {
+        out = codes_by_group_scale<W>(M.mm, bits, b, ab);
+        if (l16 == 0 && (u & (hpg - 1)) == 0) buf_max1[u >> sh] = ab;
+      } else {
+        out.fill(M.zero_m);
+      }
+      out.store(bb);
     }
   }
-  if (BM == LPMM_B200_STATE_GROUP4 && c.has_momentum && blockIdx.x == 0 && threadIdx.x == 0)
-    reinterpret_cast<uint8_t*>(buf)[units * 64] = 0;
+  if (quantized && blockIdx.x == 0 && threadIdx.x == 0) reinterpret_cast<uint8_t*>(buf)[Codes8<W>::trailing(units)] = 0;
 }
 
 // ---------------------------------------------------------------------------------------------
 // Standalone quantize / dequantize
 // ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(UT) pack4_kernel(const float* __restrict__ x, long long n,
-                                                    const float* __restrict__ qmap, uint8_t* __restrict__ out) {
+// pack / unpack of already normalised values (quantization_kernel.cu:429-460, 515-537, 603-627, 655-672)
+template <bool W>
+__global__ void __launch_bounds__(UT) pack_kernel(const float* __restrict__ x, long long n,
+                                                   const float* __restrict__ qmap, int bits,
+                                                   uint8_t* __restrict__ out) {
   __shared__ Maps M;
-  load_maps(M, qmap, nullptr);
-  const long long nb = n / 2;
+  load_maps<W>(M, qmap, nullptr, bits, 4);
+  const long long nb = W ? n : n / 2;
   for (long long b = (long long)blockIdx.x * UT + threadIdx.x; b < nb; b += (long long)gridDim.x * UT) {
-    const float2 xy = *reinterpret_cast<const float2*>(x + 2 * b);
-    out[b] = (uint8_t)(code16(M.mm, xy.x) | (code16(M.mm, xy.y) << 4));
+    if (W) {
+      out[b] = (uint8_t)code_of<true>(M.mm, bits, x[b]);
+    } else {
+      const float2 xy = *reinterpret_cast<const float2*>(x + 2 * b);
+      out[b] = (uint8_t)(code16(M.mm, xy.x) | (code16(M.mm, xy.y) << 4));
+    }
   }
   if (blockIdx.x == 0 && threadIdx.x == 0) out[nb] = 0;
 }
-__global__ void __launch_bounds__(UT) unpack4_kernel(const uint8_t* __restrict__ in, long long n,
-                                                      const float* __restrict__ qmap, float* __restrict__ out) {
+template <bool W>
+__global__ void __launch_bounds__(UT) unpack_kernel(const uint8_t* __restrict__ in, long long n,
+                                                     const float* __restrict__ qmap, int bits,
+                                                     float* __restrict__ out) {
   __shared__ Maps M;
-  load_maps(M, qmap, nullptr);
-  const long long nb = n / 2;
+  load_maps<W>(M, qmap, nullptr, bits, 4);
+  const long long nb = W ? n : n / 2;
   for (long long b = (long long)blockIdx.x * UT + threadIdx.x; b < nb; b += (long long)gridDim.x * UT) {
     const uint8_t c = in[b];
-    *reinterpret_cast<float2*>(out + 2 * b) = make_float2(M.qm[c & 15], M.qm[c >> 4]);
+    if (W) out[b] = M.qm[c];
+    else *reinterpret_cast<float2*>(out + 2 * b) = make_float2(M.qm[c & 15], M.qm[c >> 4]);
   }
 }
-// mode 0: group-128 scales (computes max1); mode 1: rank-1 scales from given per-axis maxima.
-template <int MODE, int ND>
-__global__ void __launch_bounds__(UT) quant_kernel(const float* __restrict__ x, long long n, long long units,
-                                                    const float* __restrict__ qmap, uint8_t* __restrict__ codes,
-                                                    float* __restrict__ max1, const StepArgs a) {
+// mode 0: group scales (computes max1); mode 1: rank-1 scales from given per-axis maxima.
+template <int MODE, int ND, bool W>
+__global__ void __launch_bounds__(UTMAX, 2) quant_kernel(const float* __restrict__ x, long long n, long long units,
+                                                       const float* __restrict__ qmap, int bits, int hpg, int sh,
+                                                       uint8_t* __restrict__ codes, float* __restrict__ max1,
+                                                       const StepArgs a) {
   __shared__ Maps M;
-  load_maps(M, qmap, nullptr);
+  __shared__ float red[UTMAX / 16];
+  load_maps<W>(M, qmap, nullptr, bits, 4);
   const int l16 = threadIdx.x & 15;
+  const int hw = threadIdx.x >> 4, hw_per_cta = blockDim.x >> 4;
   const unsigned hmask = 0xFFFFu << (threadIdx.x & 16);
-  const long long real_units = (n + 127) / 128;
-  for (long long u = (long long)blockIdx.x * (UT / 16) + (threadIdx.x >> 4); u < units;
-       u += (long long)gridDim.x * (UT / 16)) {
+  const long long in_units = (MODE == 0) ? (n + 128LL * hpg - 1) / (128LL * hpg) * hpg : (n + 127) / 128;
+  for (long long u = (long long)blockIdx.x * hw_per_cta + hw; u < units; u += (long long)gridDim.x * hw_per_cta) {
     const long long e0 = u * 128 + l16 * 8;
-    uint32_t* cb = reinterpret_cast<uint32_t*>(codes + (e0 >> 1));
-    if (u >= real_units) {
-      *cb = 0x11111111u * (uint32_t)M.zero_m;
-      continue;
-    }
+    uint8_t* cb = codes + Codes8<W>::byte_off(e0);
     float xv[8], st[8];
     float ax = 0.0f;
     int co[8];
-    if (MODE == 1) decompose<ND>(e0, a.s, co);
+    if (MODE == 1 && e0 < n) decompose<ND>(e0, a.s, co);
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
       xv[k] = 0.0f;
@@ -647,43 +757,49 @@ __global__ void __launch_bounds__(UT) quant_kernel(const float* __restrict__ x, 
         ax = fmaxf(ax, fabsf(xv[k]));
         if (MODE == 1) st[k] = axis_min<ND>(a.v_new, co, a.s.nd);
       }
-      if (MODE == 1) advance<ND>(co, a.s);
+      if (MODE == 1 && e0 < n) advance<ND>(co, a.s);
     }
-    uint32_t out = 0;
+    Codes8<W> out;
     if (MODE == 0) {
-      ax = hmax16(ax, hmask);
-      out = codes_by_group_scale(M.mm, xv, ax);
-      if (l16 == 0) max1[u] = ax;
-    } else {
-#pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        const int code = (e0 + k < n) ? code16(M.mm, __fdiv_rn(xv[k], st[k])) : M.zero_m;
-        out |= (uint32_t)(code & 15) << (4 * k);
+      ax = group_max(hmax16(ax, hmask), hpg, red);
+      if (u < in_units) {
+        out = codes_by_group_scale<W>(M.mm, bits, xv, ax);
+        if (l16 == 0 && (u & (hpg - 1)) == 0) max1[u >> sh] = ax;
+      } else {
+        out.fill(M.zero_m);
       }
+    } else {
+      out.clear();
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        out.set(k, (e0 + k < n) ? code_of<W>(M.mm, bits, __fdiv_rn(xv[k], st[k])) : M.zero_m);
     }
-    *cb = out;
+    out.store(cb);
   }
-  if (blockIdx.x == 0 && threadIdx.x == 0) codes[units * 64] = 0;
+  if (blockIdx.x == 0 && threadIdx.x == 0) codes[Codes8<W>::trailing(units)] = 0;
 }
-template <int MODE, int ND>
+template <int MODE, int ND, bool W>
 __global__ void __launch_bounds__(UT) dequant_kernel(const uint8_t* __restrict__ codes, long long n,
-                                                      const float* __restrict__ qmap,
+                                                      const float* __restrict__ qmap, int bits, int sh,
                                                       const float* __restrict__ max1, float* __restrict__ out,
                                                       const StepArgs a) {
   __shared__ Maps M;
-  load_maps(M, qmap, nullptr);
+  load_maps<W>(M, qmap, nullptr, bits, 4);
   const long long nchunks = (n + 7) / 8;
   for (long long ch = (long long)blockIdx.x * UT + threadIdx.x; ch < nchunks; ch += (long long)gridDim.x * UT) {
     const long long e0 = ch * 8;
-    const uint32_t c = *reinterpret_cast<const uint32_t*>(codes + (e0 >> 1));
+    Codes8<W> c;
+    c.load(codes + Codes8<W>::byte_off(e0));
     int co[8];
     if (MODE == 1) decompose<ND>(e0, a.s, co);
-    const float s0 = (MODE == 0) ? max1[e0 >> 7] : 0.0f;
+    const float s0 = (MODE == 0) ? max1[(e0 >> 7) >> sh] : 0.0f;
+#pragma unroll
     for (int k = 0; k < 8; ++k) {
-      if (e0 + k >= n) break;
-      const float sc = (MODE == 0) ? s0 : axis_min<ND>(a.v_old, co, a.s.nd);
-      out[e0 + k] = __fmul_rn(M.qm[(c >> (4 * k)) & 15u], sc);
-      if (MODE == 1) advance<ND>(co, a.s);
+      if (e0 + k < n) {
+        const float sc = (MODE == 0) ? s0 : axis_min<ND>(a.v_old, co, a.s.nd);
+        out[e0 + k] = __fmul_rn(M.qm[c.get(k)], sc);
+        if (MODE == 1) advance<ND>(co, a.s);
+      }
     }
   }
 }
@@ -762,52 +878,122 @@ static UConsts make_consts(double beta1, double beta2, double lr, double wd, dou
 
 using namespace lpmm_b200;
 
-extern "C" int64_t lpmm_b200_packed_len(int64_t n_scaled) {
-  if (n_scaled < 0) return LPMM_B200_ERR_BAD_SIZE;
-  return pad_to(n_scaled, 2048) / 2 + 1;
+// Code width and group size of one quantized state as the kernels want them.
+struct Layout {
+  int bits, hpg, sh;
+  bool wide;
+};
+static int make_layout(int bits, long long group_size, Layout* out) {
+  if (bits == 0) bits = 4;
+  if (group_size == 0) group_size = 128;
+  if (bits < 1 || bits > 8) return LPMM_B200_ERR_BAD_KIND;
+  if (bits < 4) return LPMM_B200_ERR_UNSUPPORTED;  // several codes per byte other than two
+  if (group_size < 128 || group_size > 4096 || (group_size & (group_size - 1))) {
+    return (group_size > 0) ? LPMM_B200_ERR_UNSUPPORTED : LPMM_B200_ERR_BAD_SIZE;
+  }
+  out->bits = bits;
+  out->wide = bits > 4;
+  out->hpg = (int)(group_size / 128);
+  out->sh = 0;
+  while ((1 << out->sh) < out->hpg) ++out->sh;
+  return LPMM_B200_OK;
 }
+static inline long long padded_units(long long numel, long long group_size) {
+  return pad_to(pad_to(numel, group_size), 2048) / 128;
+}
+// Threads per CTA: all half-warps of a group must sit in one CTA.
+static inline int threads_for(int hpg) { return hpg > UT / 16 ? UTMAX : UT; }
+static inline bool aligned_for(const void* p, bool wide) { return ((uintptr_t)p & (wide ? 7 : 3)) == 0; }
 
+#define LPMM_DISPATCH_W(wide, ...)                     \
+  do {                                                 \
+    if (wide) { constexpr bool W = true; __VA_ARGS__; } \
+    else { constexpr bool W = false; __VA_ARGS__; }     \
+  } while (0)
+
+extern "C" int64_t lpmm_b200_packed_len_bits(int64_t n_scaled, int bits) {
+  if (n_scaled < 0) return LPMM_B200_ERR_BAD_SIZE;
+  Layout l;
+  const int rc = make_layout(bits, 128, &l);
+  if (rc) return rc;
+  return l.wide ? pad_to(n_scaled, 2048) + 1 : pad_to(n_scaled, 2048) / 2 + 1;
+}
+extern "C" int64_t lpmm_b200_packed_len(int64_t n_scaled) { return lpmm_b200_packed_len_bits(n_scaled, 4); }
+
+extern "C" int lpmm_b200_pack_nonlinear(const float* data, int64_t n, const float* qmap, int bits, int8_t* packed,
+                                        void* stream) {
+  Layout l;
+  const int rc = make_layout(bits, 128, &l);
+  if (rc) return rc;
+  if (n < 0 || (!l.wide && (n & 1))) return LPMM_B200_ERR_BAD_SIZE;
+  if (!qmap || !packed || (n > 0 && !data)) return LPMM_B200_ERR_NULL_POINTER;
+  LPMM_DISPATCH_W(l.wide, (pack_kernel<W><<<grid_for(l.wide ? n : n / 2, UT), UT, 0, (cudaStream_t)stream>>>(
+                              data, n, qmap, l.bits, (uint8_t*)packed)));
+  LPMM_CUDA_TRY(cudaGetLastError());
+  return LPMM_B200_OK;
+}
 extern "C" int lpmm_b200_pack_nonlinear4(const float* data, int64_t n, const float* qmap, int8_t* packed,
                                          void* stream) {
-  if (n < 0 || (n & 1)) return LPMM_B200_ERR_BAD_SIZE;
-  if (!qmap || !packed || (n > 0 && !data)) return LPMM_B200_ERR_NULL_POINTER;
-  pack4_kernel<<<grid_for(n / 2, UT), UT, 0, (cudaStream_t)stream>>>(data, n, qmap, (uint8_t*)packed);
-  LPMM_CUDA_TRY(cudaGetLastError());
-  return LPMM_B200_OK;
+  return lpmm_b200_pack_nonlinear(data, n, qmap, 4, packed, stream);
 }
 
-extern "C" int lpmm_b200_unpack_nonlinear4(const int8_t* packed, const float* qmap, int64_t n, float* out,
-                                           void* stream) {
-  if (n < 0 || (n & 1)) return LPMM_B200_ERR_BAD_SIZE;
+extern "C" int lpmm_b200_unpack_nonlinear(const int8_t* packed, const float* qmap, int bits, int64_t n, float* out,
+                                          void* stream) {
+  Layout l;
+  const int rc = make_layout(bits, 128, &l);
+  if (rc) return rc;
+  if (n < 0 || (!l.wide && (n & 1))) return LPMM_B200_ERR_BAD_SIZE;
   if (n == 0) return LPMM_B200_OK;
   if (!qmap || !packed || !out) return LPMM_B200_ERR_NULL_POINTER;
-  unpack4_kernel<<<grid_for(n / 2, UT), UT, 0, (cudaStream_t)stream>>>((const uint8_t*)packed, n, qmap, out);
+  LPMM_DISPATCH_W(l.wide, (unpack_kernel<W><<<grid_for(l.wide ? n : n / 2, UT), UT, 0, (cudaStream_t)stream>>>(
+                              (const uint8_t*)packed, n, qmap, l.bits, out)));
   LPMM_CUDA_TRY(cudaGetLastError());
   return LPMM_B200_OK;
 }
+extern "C" int lpmm_b200_unpack_nonlinear4(const int8_t* packed, const float* qmap, int64_t n, float* out,
+                                           void* stream) {
+  return lpmm_b200_unpack_nonlinear(packed, qmap, 4, n, out, stream);
+}
 
-extern "C" int lpmm_b200_quant_group4(const float* x, int64_t numel, const float* qmap, int8_t* codes, float* max1,
-                                      void* stream) {
+extern "C" int lpmm_b200_quant_group(const float* x, int64_t numel, const float* qmap, int bits, int64_t group_size,
+                                     int8_t* codes, float* max1, void* stream) {
+  Layout l;
+  const int rc = make_layout(bits, group_size, &l);
+  if (rc) return rc;
   if (numel < 0) return LPMM_B200_ERR_BAD_SIZE;
   if (!qmap || !codes || (numel > 0 && (!x || !max1))) return LPMM_B200_ERR_NULL_POINTER;
+  if (!aligned_for(codes, l.wide)) return LPMM_B200_ERR_BAD_SIZE;
   StepArgs a = {};
-  const long long units = pad_to(pad_to(numel, 128), 2048) / 128;
-  quant_kernel<0, 2><<<grid_for(units, UT / 16), UT, 0, (cudaStream_t)stream>>>(x, numel, units, qmap, (uint8_t*)codes,
-                                                                            max1, a);
+  const long long units = padded_units(numel, 128LL * l.hpg);
+  const int th = threads_for(l.hpg);
+  LPMM_DISPATCH_W(l.wide, (quant_kernel<0, 2, W><<<grid_for(units, th / 16), th, 0, (cudaStream_t)stream>>>(
+                              x, numel, units, qmap, l.bits, l.hpg, l.sh, (uint8_t*)codes, max1, a)));
   LPMM_CUDA_TRY(cudaGetLastError());
   return LPMM_B200_OK;
 }
+extern "C" int lpmm_b200_quant_group4(const float* x, int64_t numel, const float* qmap, int8_t* codes, float* max1,
+                                      void* stream) {
+  return lpmm_b200_quant_group(x, numel, qmap, 4, 128, codes, max1, stream);
+}
 
-extern "C" int lpmm_b200_dequant_group4(const int8_t* codes, const float* qmap, const float* max1, int64_t numel,
-                                        float* out, void* stream) {
+extern "C" int lpmm_b200_dequant_group(const int8_t* codes, const float* qmap, int bits, int64_t group_size,
+                                       const float* max1, int64_t numel, float* out, void* stream) {
+  Layout l;
+  const int rc = make_layout(bits, group_size, &l);
+  if (rc) return rc;
   if (numel < 0) return LPMM_B200_ERR_BAD_SIZE;
   if (numel == 0) return LPMM_B200_OK;
   if (!qmap || !codes || !max1 || !out) return LPMM_B200_ERR_NULL_POINTER;
+  if (!aligned_for(codes, l.wide)) return LPMM_B200_ERR_BAD_SIZE;
   StepArgs a = {};
-  dequant_kernel<0, 2><<<grid_for((numel + 7) / 8, UT), UT, 0, (cudaStream_t)stream>>>((const uint8_t*)codes, numel,
-                                                                                   qmap, max1, out, a);
+  LPMM_DISPATCH_W(l.wide, (dequant_kernel<0, 2, W><<<grid_for((numel + 7) / 8, UT), UT, 0, (cudaStream_t)stream>>>(
+                              (const uint8_t*)codes, numel, qmap, l.bits, l.sh, max1, out, a)));
   LPMM_CUDA_TRY(cudaGetLastError());
   return LPMM_B200_OK;
+}
+extern "C" int lpmm_b200_dequant_group4(const int8_t* codes, const float* qmap, const float* max1, int64_t numel,
+                                        float* out, void* stream) {
+  return lpmm_b200_dequant_group(codes, qmap, 4, 128, max1, numel, out, stream);
 }
 
 static int zero_axes(const Shape& s, float* const* vecs, cudaStream_t st) {
@@ -833,38 +1019,57 @@ extern "C" int lpmm_b200_axis_absmax(const float* x, const int64_t* shape, int n
   return LPMM_B200_OK;
 }
 
-extern "C" int lpmm_b200_quant_rank1_4(const float* x, const int64_t* shape, int ndim, const float* qmap,
-                                       float* const* max_dims, int8_t* codes, void* stream) {
+extern "C" int lpmm_b200_quant_rank1(const float* x, const int64_t* shape, int ndim, const float* qmap, int bits,
+                                     float* const* max_dims, int8_t* codes, void* stream) {
+  Layout l;
+  int rc = make_layout(bits, 128, &l);
+  if (rc) return rc;
   if (ndim < 2) return LPMM_B200_ERR_BAD_SIZE;
-  int rc = lpmm_b200_axis_absmax(x, shape, ndim, max_dims, stream);
+  rc = lpmm_b200_axis_absmax(x, shape, ndim, max_dims, stream);
   if (rc) return rc;
   if (!qmap || !codes) return LPMM_B200_ERR_NULL_POINTER;
+  if (!aligned_for(codes, l.wide)) return LPMM_B200_ERR_BAD_SIZE;
   StepArgs a = {};
   fill_shape(a.s, shape, ndim, &a.n);
   for (int i = 0; i < ndim; ++i) a.v_new[i] = max_dims[i];
   const long long units = pad_to(a.n, 2048) / 128;
-  LPMM_DISPATCH_ND(ndim, (quant_kernel<1, ND><<<grid_for(units, UT / 16), UT, 0, (cudaStream_t)stream>>>(
-                              x, a.n, units, qmap, (uint8_t*)codes, nullptr, a)));
+  LPMM_DISPATCH_W(l.wide, LPMM_DISPATCH_ND(ndim, (quant_kernel<1, ND, W><<<grid_for(units, UT / 16), UT, 0,
+                                                                            (cudaStream_t)stream>>>(
+                                                     x, a.n, units, qmap, l.bits, 1, 0, (uint8_t*)codes, nullptr, a))));
   LPMM_CUDA_TRY(cudaGetLastError());
   return LPMM_B200_OK;
 }
+extern "C" int lpmm_b200_quant_rank1_4(const float* x, const int64_t* shape, int ndim, const float* qmap,
+                                       float* const* max_dims, int8_t* codes, void* stream) {
+  return lpmm_b200_quant_rank1(x, shape, ndim, qmap, 4, max_dims, codes, stream);
+}
 
-extern "C" int lpmm_b200_dequant_rank1_4(const int8_t* codes, const float* qmap, const float* const* max_dims,
-                                         const int64_t* shape, int ndim, float* out, void* stream) {
+extern "C" int lpmm_b200_dequant_rank1(const int8_t* codes, const float* qmap, int bits,
+                                       const float* const* max_dims, const int64_t* shape, int ndim, float* out,
+                                       void* stream) {
+  Layout l;
+  int rc = make_layout(bits, 128, &l);
+  if (rc) return rc;
   if (ndim < 2) return LPMM_B200_ERR_BAD_SIZE;
   StepArgs a = {};
-  int rc = fill_shape(a.s, shape, ndim, &a.n);
+  rc = fill_shape(a.s, shape, ndim, &a.n);
   if (rc) return rc;
   if (a.n == 0) return LPMM_B200_OK;
   if (!qmap || !codes || !max_dims || !out) return LPMM_B200_ERR_NULL_POINTER;
+  if (!aligned_for(codes, l.wide)) return LPMM_B200_ERR_BAD_SIZE;
   for (int i = 0; i < ndim; ++i) {
     if (!max_dims[i]) return LPMM_B200_ERR_NULL_POINTER;
     a.v_old[i] = max_dims[i];
   }
-  LPMM_DISPATCH_ND(ndim, (dequant_kernel<1, ND><<<grid_for((a.n + 7) / 8, UT), UT, 0, (cudaStream_t)stream>>>(
-                              (const uint8_t*)codes, a.n, qmap, nullptr, out, a)));
+  LPMM_DISPATCH_W(l.wide, LPMM_DISPATCH_ND(ndim, (dequant_kernel<1, ND, W><<<grid_for((a.n + 7) / 8, UT), UT, 0,
+                                                                              (cudaStream_t)stream>>>(
+                                                     (const uint8_t*)codes, a.n, qmap, l.bits, 0, nullptr, out, a))));
   LPMM_CUDA_TRY(cudaGetLastError());
   return LPMM_B200_OK;
+}
+extern "C" int lpmm_b200_dequant_rank1_4(const int8_t* codes, const float* qmap, const float* const* max_dims,
+                                         const int64_t* shape, int ndim, float* out, void* stream) {
+  return lpmm_b200_dequant_rank1(codes, qmap, 4, max_dims, shape, ndim, out, stream);
 }
 
 extern "C" int64_t lpmm_b200_factored_scratch_bytes(const int64_t* shape, int ndim) {
@@ -876,16 +1081,22 @@ extern "C" int64_t lpmm_b200_factored_scratch_bytes(const int64_t* shape, int nd
   return (int64_t)sizeof(float) * (B * tiles * C + B);
 }
 
-template <int MM>
-static cudaError_t launch_unfused(int vm, unsigned grid, cudaStream_t st, const StepArgs& a, const UConsts& c,
-                                  const float* qm, const float* qv) {
+template <int MM, bool W>
+static cudaError_t launch_unfused(int vm, unsigned grid, int threads, cudaStream_t st, const StepArgs& a,
+                                  const UConsts& c, const float* qm, const float* qv) {
   switch (vm) {
-    case LPMM_B200_STATE_FP32: unfused_adamw_kernel<MM, LPMM_B200_STATE_FP32, 2><<<grid, UT, 0, st>>>(a, c, qm, qv); break;
-    case LPMM_B200_STATE_GROUP4: unfused_adamw_kernel<MM, LPMM_B200_STATE_GROUP4, 2><<<grid, UT, 0, st>>>(a, c, qm, qv); break;
-    case LPMM_B200_STATE_RANK1_4:
-      LPMM_DISPATCH_ND(a.s.nd, (unfused_adamw_kernel<MM, LPMM_B200_STATE_RANK1_4, ND><<<grid, UT, 0, st>>>(a, c, qm, qv)));
+    case LPMM_B200_STATE_FP32:
+      unfused_adamw_kernel<MM, LPMM_B200_STATE_FP32, 2, W><<<grid, threads, 0, st>>>(a, c, qm, qv);
       break;
-    default: unfused_adamw_kernel<MM, LPMM_B200_STATE_FACTORED, 2><<<grid, UT, 0, st>>>(a, c, qm, qv); break;
+    case LPMM_B200_STATE_GROUP4:
+      unfused_adamw_kernel<MM, LPMM_B200_STATE_GROUP4, 2, W><<<grid, threads, 0, st>>>(a, c, qm, qv);
+      break;
+    case LPMM_B200_STATE_RANK1_4:
+      LPMM_DISPATCH_ND(a.s.nd, (unfused_adamw_kernel<MM, LPMM_B200_STATE_RANK1_4, ND, W><<<grid, threads, 0, st>>>(a, c, qm, qv)));
+      break;
+    default:
+      unfused_adamw_kernel<MM, LPMM_B200_STATE_FACTORED, 2, W><<<grid, threads, 0, st>>>(a, c, qm, qv);
+      break;
   }
   return cudaGetLastError();
 }
@@ -896,12 +1107,27 @@ extern "C" int lpmm_b200_adamw4bit_unfused_step(const lpmm_b200_step_tensor* t, 
                                                 int64_t scratch_bytes, void* stream) {
   if (!t) return LPMM_B200_ERR_NULL_POINTER;
   if (t->numel < 0) return LPMM_B200_ERR_BAD_SIZE;
-  if (t->numel == 0) return LPMM_B200_OK;
-  if (!t->p || !t->g) return LPMM_B200_ERR_NULL_POINTER;
   if (t->m_mode != LPMM_B200_STATE_FP32 && t->m_mode != LPMM_B200_STATE_GROUP4) return LPMM_B200_ERR_BAD_KIND;
   if (t->v_mode < LPMM_B200_STATE_FP32 || t->v_mode > LPMM_B200_STATE_FACTORED) return LPMM_B200_ERR_BAD_KIND;
+  const bool mq = t->m_mode == LPMM_B200_STATE_GROUP4;
+  const bool vq = t->v_mode == LPMM_B200_STATE_GROUP4 || t->v_mode == LPMM_B200_STATE_RANK1_4;
+  Layout lm = {4, 1, 0, false}, lv = {4, 1, 0, false};
+  if (mq) {
+    const int rc = make_layout(t->m_bits, t->m_group, &lm);
+    if (rc) return rc;
+  }
+  if (vq) {
+    const int rc = make_layout(t->v_bits, t->v_mode == LPMM_B200_STATE_GROUP4 ? t->v_group : 128, &lv);
+    if (rc) return rc;
+  }
+  if (mq && vq && lm.wide != lv.wide) return LPMM_B200_ERR_UNSUPPORTED;  // one storage format per launch
+  const bool wide = mq ? lm.wide : (vq && lv.wide);
+  if (t->numel == 0) return LPMM_B200_OK;
+  if (!t->p || !t->g) return LPMM_B200_ERR_NULL_POINTER;
   if (!t->m) return LPMM_B200_ERR_NULL_POINTER;
-  if (t->m_mode == LPMM_B200_STATE_GROUP4 && (!t->m_max1 || !qmap_m)) return LPMM_B200_ERR_NULL_POINTER;
+  if (mq && (!t->m_max1 || !qmap_m)) return LPMM_B200_ERR_NULL_POINTER;
+  if (mq && !aligned_for(t->m, wide)) return LPMM_B200_ERR_BAD_SIZE;
+  if (vq && t->v && !aligned_for(t->v, wide)) return LPMM_B200_ERR_BAD_SIZE;
   cudaStream_t st = (cudaStream_t)stream;
   StepArgs a = {};
   a.p = t->p;
@@ -917,7 +1143,18 @@ extern "C" int lpmm_b200_adamw4bit_unfused_step(const lpmm_b200_step_tensor* t, 
   a.col = t->col;
   a.s.nd = 1;
   a.s.dim[0] = t->numel;
-  a.units = pad_to(pad_to(a.n, 128), 2048) / 128;
+  a.bits_m = lm.bits;
+  a.bits_v = lv.bits;
+  a.hpg_m = lm.hpg;
+  a.sh_m = lm.sh;
+  a.hpg_v = lv.hpg;
+  a.sh_v = lv.sh;
+  const int hpg_max = lm.hpg > lv.hpg ? lm.hpg : lv.hpg;
+  a.units_m = mq ? padded_units(a.n, 128LL * lm.hpg) : 0;
+  a.units_v = (t->v_mode == LPMM_B200_STATE_GROUP4) ? padded_units(a.n, 128LL * lv.hpg) : (vq ? pad_to(a.n, 2048) / 128 : 0);
+  a.units = pad_to(a.n, 2048) / 128;
+  if (a.units_m > a.units) a.units = a.units_m;
+  if (a.units_v > a.units) a.units = a.units_v;
   const UConsts c = make_consts(beta1, beta2, lr, weight_decay, eps, step);
   if (t->v_mode == LPMM_B200_STATE_RANK1_4 || t->v_mode == LPMM_B200_STATE_FACTORED) {
     long long n2 = 0;
@@ -925,9 +1162,9 @@ extern "C" int lpmm_b200_adamw4bit_unfused_step(const lpmm_b200_step_tensor* t, 
     if (rc) return rc;
     if (t->ndim < 2 || n2 != t->numel) return LPMM_B200_ERR_BAD_SIZE;
   }
-  if (t->v_mode == LPMM_B200_STATE_FP32 || t->v_mode == LPMM_B200_STATE_GROUP4 || t->v_mode == LPMM_B200_STATE_RANK1_4) {
+  if (t->v_mode == LPMM_B200_STATE_FP32 || vq) {
     if (!t->v) return LPMM_B200_ERR_NULL_POINTER;
-    if (t->v_mode != LPMM_B200_STATE_FP32 && !qmap_v) return LPMM_B200_ERR_NULL_POINTER;
+    if (vq && !qmap_v) return LPMM_B200_ERR_NULL_POINTER;
     if (t->v_mode == LPMM_B200_STATE_GROUP4 && !t->v_max1) return LPMM_B200_ERR_NULL_POINTER;
   }
   if (t->v_mode == LPMM_B200_STATE_RANK1_4) {
@@ -938,7 +1175,7 @@ extern "C" int lpmm_b200_adamw4bit_unfused_step(const lpmm_b200_step_tensor* t, 
     }
     int rc = zero_axes(a.s, t->v_max_dims_new, st);
     if (rc) return rc;
-    if (t->ndim == 2 && t->shape[1] % 8 == 0 && a.vec_ok && (((uintptr_t)t->v & 3) == 0)) {
+    if (t->ndim == 2 && t->shape[1] % 8 == 0 && a.vec_ok) {
       const long long R = t->shape[0], C = t->shape[1];
       const long long col_ctas = (C / 8 + UT - 1) / UT;
       long long row_ctas = ((long long)num_sms() * 6 + col_ctas - 1) / col_ctas;
@@ -946,9 +1183,11 @@ extern "C" int lpmm_b200_adamw4bit_unfused_step(const lpmm_b200_step_tensor* t, 
       if (row_ctas > 65535) row_ctas = 65535;
       const int rows_per_cta = (int)((R + row_ctas - 1) / row_ctas);
       row_ctas = (R + rows_per_cta - 1) / rows_per_cta;
-      rank1_stats2d_kernel<<<dim3((unsigned)col_ctas, (unsigned)row_ctas), UT, 0, st>>>(a, c, qmap_v, rows_per_cta);
+      LPMM_DISPATCH_W(lv.wide, (rank1_stats2d_kernel<W><<<dim3((unsigned)col_ctas, (unsigned)row_ctas), UT, 0, st>>>(
+                                   a, c, qmap_v, rows_per_cta)));
     } else {
-      LPMM_DISPATCH_ND(t->ndim, (rank1_stats_kernel<ND><<<grid_for((a.n + 7) / 8, UT, 3), UT, 0, st>>>(a, c, qmap_v)));
+      LPMM_DISPATCH_W(lv.wide, LPMM_DISPATCH_ND(t->ndim, (rank1_stats_kernel<ND, W><<<grid_for((a.n + 7) / 8, UT, 3), UT,
+                                                                                    0, st>>>(a, c, qmap_v))));
     }
     LPMM_CUDA_TRY(cudaGetLastError());
   }
@@ -973,21 +1212,28 @@ extern "C" int lpmm_b200_adamw4bit_unfused_step(const lpmm_b200_step_tensor* t, 
     LPMM_CUDA_TRY(cudaGetLastError());
     a.row_mean = row_mean;
   }
-  const unsigned grid = grid_for(a.units, UT / 16);
-  cudaError_t e = (t->m_mode == LPMM_B200_STATE_GROUP4) ? launch_unfused<LPMM_B200_STATE_GROUP4>(t->v_mode, grid, st, a, c, qmap_m, qmap_v)
-                                                       : launch_unfused<LPMM_B200_STATE_FP32>(t->v_mode, grid, st, a, c, qmap_m, qmap_v);
+  const int threads = threads_for(hpg_max);
+  const unsigned grid = grid_for(a.units, threads / 16, threads == UT ? 8 : 4);
+  cudaError_t e = cudaSuccess;
+  LPMM_DISPATCH_W(wide, (e = mq ? launch_unfused<LPMM_B200_STATE_GROUP4, W>(t->v_mode, grid, threads, st, a, c, qmap_m, qmap_v)
+                                : launch_unfused<LPMM_B200_STATE_FP32, W>(t->v_mode, grid, threads, st, a, c, qmap_m, qmap_v)));
   LPMM_CUDA_TRY(e);
   return LPMM_B200_OK;
 }
 
-extern "C" int lpmm_b200_sgd4bit_step(float* p, const float* g, int64_t numel, void* buf, float* buf_max1,
-                                      int buf_mode, int first, const float* qmap, double weight_decay,
-                                      double momentum, double lr, double dampening, int nesterov, int maximize,
-                                      void* stream) {
+extern "C" int lpmm_b200_sgd_lowbit_step(float* p, const float* g, int64_t numel, void* buf, float* buf_max1,
+                                         int buf_mode, int bits, int64_t group_size, int first, const float* qmap,
+                                         double weight_decay, double momentum, double lr, double dampening,
+                                         int nesterov, int maximize, void* stream) {
   if (numel < 0) return LPMM_B200_ERR_BAD_SIZE;
+  if (buf_mode != LPMM_B200_STATE_FP32 && buf_mode != LPMM_B200_STATE_GROUP4) return LPMM_B200_ERR_BAD_KIND;
+  Layout l = {4, 1, 0, false};
+  if (buf_mode == LPMM_B200_STATE_GROUP4) {
+    const int rc = make_layout(bits, group_size, &l);
+    if (rc) return rc;
+  }
   if (numel == 0) return LPMM_B200_OK;
   if (!p || !g) return LPMM_B200_ERR_NULL_POINTER;
-  if (buf_mode != LPMM_B200_STATE_FP32 && buf_mode != LPMM_B200_STATE_GROUP4) return LPMM_B200_ERR_BAD_KIND;
   SgdConsts c;
   c.wd = (float)weight_decay;
   c.momentum = (float)momentum;
@@ -1000,15 +1246,27 @@ extern "C" int lpmm_b200_sgd4bit_step(float* p, const float* g, int64_t numel, v
   if (c.has_momentum) {
     if (!buf) return LPMM_B200_ERR_NULL_POINTER;
     if (buf_mode == LPMM_B200_STATE_GROUP4 && (!buf_max1 || !qmap)) return LPMM_B200_ERR_NULL_POINTER;
+    if (buf_mode == LPMM_B200_STATE_GROUP4 && !aligned_for(buf, l.wide)) return LPMM_B200_ERR_BAD_SIZE;
   }
-  const long long units = pad_to(pad_to(numel, 128), 2048) / 128;
-  const unsigned grid = grid_for(units, UT / 16);
-  if (buf_mode == LPMM_B200_STATE_GROUP4)
-    sgd_kernel<LPMM_B200_STATE_GROUP4><<<grid, UT, 0, (cudaStream_t)stream>>>(p, g, numel, units, buf, buf_max1, first, qmap, c);
-  else
-    sgd_kernel<LPMM_B200_STATE_FP32><<<grid, UT, 0, (cudaStream_t)stream>>>(p, g, numel, units, buf, buf_max1, first, qmap, c);
+  const long long units = padded_units(numel, 128LL * l.hpg);
+  const int threads = threads_for(l.hpg);
+  const unsigned grid = grid_for(units, threads / 16, threads == UT ? 8 : 4);
+  if (buf_mode == LPMM_B200_STATE_GROUP4) {
+    LPMM_DISPATCH_W(l.wide, (sgd_kernel<LPMM_B200_STATE_GROUP4, W><<<grid, threads, 0, (cudaStream_t)stream>>>(
+                                p, g, numel, units, buf, buf_max1, first, qmap, l.bits, l.hpg, l.sh, c)));
+  } else {
+    sgd_kernel<LPMM_B200_STATE_FP32, false><<<grid, threads, 0, (cudaStream_t)stream>>>(p, g, numel, units, buf, buf_max1,
+                                                                                     first, qmap, 4, 1, 0, c);
+  }
   LPMM_CUDA_TRY(cudaGetLastError());
   return LPMM_B200_OK;
+}
+extern "C" int lpmm_b200_sgd4bit_step(float* p, const float* g, int64_t numel, void* buf, float* buf_max1,
+                                      int buf_mode, int first, const float* qmap, double weight_decay,
+                                      double momentum, double lr, double dampening, int nesterov, int maximize,
+                                      void* stream) {
+  return lpmm_b200_sgd_lowbit_step(p, g, numel, buf, buf_max1, buf_mode, 4, 128, first, qmap, weight_decay, momentum,
+                                   lr, dampening, nesterov, maximize, stream);
 }
 
 // ---------------------------------------------------------------------------------------------

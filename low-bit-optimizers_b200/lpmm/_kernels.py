@@ -108,8 +108,27 @@ def adamw4bit_multi_tensor(tl, qmap_m, qmap_v, beta1, beta2, lr, weight_decay, e
 # ----------------------------------------------------------------------------------------------
 # standalone quantize / dequantize
 # ----------------------------------------------------------------------------------------------
-def packed_len(n_scaled):
-    return (n_scaled + 2047) // 2048 * 1024 + 1
+SUPPORTED_BITS = (4, 5, 6, 7, 8)
+SUPPORTED_GROUPS = (128, 256, 512, 1024, 2048, 4096)
+
+
+def packed_len(n_scaled, bits=4):
+    """Bytes of the packed-code tensor for ``n_scaled`` normalised values: rows of 2048 codes, two
+    codes per byte for 4 bits and one per byte for 5 to 8, plus one trailing byte."""
+    rows = (n_scaled + 2047) // 2048
+    return rows * (1024 if bits == 4 else 2048) + 1
+
+
+def _check_layout(bits, gp_sz=128):
+    if bits not in SUPPORTED_BITS:
+        raise NotImplementedError(f"code widths {SUPPORTED_BITS} are built in this implementation, not {bits}")
+    if gp_sz not in SUPPORTED_GROUPS:
+        raise NotImplementedError(f"group sizes {SUPPORTED_GROUPS} are built in this implementation, not {gp_sz}")
+
+
+def _check_qmap(qmap, bits):
+    if qmap.numel() != (1 << bits):
+        raise RuntimeError(f"a {bits}-bit quantization map must have {1 << bits} entries, got {qmap.numel()}")
 
 
 def _i64_array(values):
@@ -128,14 +147,16 @@ def pack_nonlinear(data, qmap, bits, stochastic):
     _check_cuda_float(qmap, "qmap")
     if data.dim() != 2 or qmap.dim() != 1:
         raise RuntimeError("The dimension of data / qmap is not correct!")
-    if bits != 4 or stochastic:
-        raise NotImplementedError("only the 4-bit round-to-nearest pack is built in this implementation")
-    if data.shape[1] % 8 != 0:
+    if stochastic:
+        raise NotImplementedError("only the round-to-nearest pack is built in this implementation")
+    _check_layout(bits)
+    _check_qmap(qmap, bits)
+    if data.shape[1] % (8 if bits == 4 else 4) != 0:
         raise RuntimeError("group_size % work_per_thread == 0")
     n = data.numel()
-    out = torch.empty(n // 2 + 1, dtype=torch.int8, device=data.device)
+    out = torch.empty((n // 2 if bits == 4 else n) + 1, dtype=torch.int8, device=data.device)
     with torch.cuda.device(data.device):
-        N.check(N.lib.lpmm_b200_pack_nonlinear4(_ptr(data), n, _ptr(qmap), _ptr(out), _stream()))
+        N.check(N.lib.lpmm_b200_pack_nonlinear(_ptr(data), n, _ptr(qmap), bits, _ptr(out), _stream()))
     return out
 
 
@@ -147,14 +168,14 @@ def unpack_nonlinear(data, qmap, bits, num_groups, group_size):
     _check_cuda_float(qmap, "qmap")
     if data.dim() != 1 or qmap.dim() != 1:
         raise RuntimeError("The dimension of data / qmap is not correct!")
-    if bits != 4:
-        raise NotImplementedError("only the 4-bit unpack is built in this implementation")
+    _check_layout(bits)
+    _check_qmap(qmap, bits)
     n = int(num_groups) * int(group_size)
-    if data.numel() < n // 2:
+    if data.numel() < (n // 2 if bits == 4 else n):
         raise RuntimeError("packed tensor is too short for num_groups * group_size codes")
     out = torch.empty((int(num_groups), int(group_size)), dtype=qmap.dtype, device=data.device)
     with torch.cuda.device(data.device):
-        N.check(N.lib.lpmm_b200_unpack_nonlinear4(_ptr(data), _ptr(qmap), n, _ptr(out), _stream()))
+        N.check(N.lib.lpmm_b200_unpack_nonlinear(_ptr(data), _ptr(qmap), bits, n, _ptr(out), _stream()))
     return out
 
 
@@ -162,36 +183,44 @@ def _qmap_on(qmap, device):
     return qmap if qmap.device == device else qmap.to(device)
 
 
-def quant_group(x, qmap, gp_sz):
-    if gp_sz != 128:
-        raise NotImplementedError("only group size 128 is built in this implementation")
+def _groups(n, gp_sz):
+    return (n + gp_sz - 1) // gp_sz
+
+
+def quant_group(x, qmap, gp_sz, bits=4):
+    _check_layout(bits, gp_sz)
+    _check_qmap(qmap, bits)
     _check_cuda_float(x, "x")
     n = x.numel()
-    groups = (n + 127) // 128
-    codes = torch.empty(packed_len(groups * 128), dtype=torch.int8, device=x.device)
+    groups = _groups(n, gp_sz)
+    codes = torch.empty(packed_len(groups * gp_sz, bits), dtype=torch.int8, device=x.device)
     max1 = torch.empty((groups, 1), dtype=torch.float32, device=x.device)
     with torch.cuda.device(x.device):
-        N.check(N.lib.lpmm_b200_quant_group4(_ptr(x), n, _ptr(_qmap_on(qmap, x.device)), _ptr(codes), _ptr(max1), _stream()))
+        N.check(N.lib.lpmm_b200_quant_group(_ptr(x), n, _ptr(_qmap_on(qmap, x.device)), bits, gp_sz, _ptr(codes),
+                                            _ptr(max1), _stream()))
     return codes, max1
 
 
-def dequant_group(codes, qmap, max1, numel, gp_sz):
-    if gp_sz != 128:
-        raise NotImplementedError("only group size 128 is built in this implementation")
+def dequant_group(codes, qmap, max1, numel, gp_sz, bits=4):
+    _check_layout(bits, gp_sz)
+    _check_qmap(qmap, bits)
     _check_cuda_int8(codes, "qx")
     out = torch.empty(numel, dtype=torch.float32, device=codes.device)
     with torch.cuda.device(codes.device):
-        N.check(N.lib.lpmm_b200_dequant_group4(_ptr(codes), _ptr(_qmap_on(qmap, codes.device)), _ptr(max1), numel,
-                                               _ptr(out), _stream()))
+        N.check(N.lib.lpmm_b200_dequant_group(_ptr(codes), _ptr(_qmap_on(qmap, codes.device)), bits, gp_sz, _ptr(max1),
+                                              numel, _ptr(out), _stream()))
     return out
 
 
-def dequant_plain(codes, qmap, n):
+def dequant_plain(codes, qmap, n, bits=4):
+    _check_layout(bits)
+    _check_qmap(qmap, bits)
     _check_cuda_int8(codes, "qx")
     n2 = (n + 1) // 2 * 2
     out = torch.empty(n2, dtype=torch.float32, device=codes.device)
     with torch.cuda.device(codes.device):
-        N.check(N.lib.lpmm_b200_unpack_nonlinear4(_ptr(codes), _ptr(_qmap_on(qmap, codes.device)), n2, _ptr(out), _stream()))
+        N.check(N.lib.lpmm_b200_unpack_nonlinear(_ptr(codes), _ptr(_qmap_on(qmap, codes.device)), bits, n2, _ptr(out),
+                                                 _stream()))
     return out[:n]
 
 
@@ -211,24 +240,29 @@ def axis_absmax(x):
     return vecs
 
 
-def quant_rank1(x, qmap):
+def quant_rank1(x, qmap, bits=4):
+    _check_layout(bits)
+    _check_qmap(qmap, bits)
     _check_cuda_float(x, "x")
     if x.dim() < 2 or x.dim() > 8:
         raise NotImplementedError("2 to 8 dimensions")
     vecs = _axis_vectors(tuple(x.shape), x.device)
-    codes = torch.empty(packed_len(x.numel()), dtype=torch.int8, device=x.device)
+    codes = torch.empty(packed_len(x.numel(), bits), dtype=torch.int8, device=x.device)
     with torch.cuda.device(x.device):
-        N.check(N.lib.lpmm_b200_quant_rank1_4(_ptr(x), _i64_array(list(x.shape)), x.dim(),
-                                              _ptr(_qmap_on(qmap, x.device)), _ptr_array(vecs), _ptr(codes), _stream()))
+        N.check(N.lib.lpmm_b200_quant_rank1(_ptr(x), _i64_array(list(x.shape)), x.dim(), _ptr(_qmap_on(qmap, x.device)),
+                                            bits, _ptr_array(vecs), _ptr(codes), _stream()))
     return codes, vecs
 
 
-def dequant_rank1(codes, qmap, max_dims, shape):
+def dequant_rank1(codes, qmap, max_dims, shape, bits=4):
+    _check_layout(bits)
+    _check_qmap(qmap, bits)
     _check_cuda_int8(codes, "qx")
     out = torch.empty(tuple(shape), dtype=torch.float32, device=codes.device)
     with torch.cuda.device(codes.device):
-        N.check(N.lib.lpmm_b200_dequant_rank1_4(_ptr(codes), _ptr(_qmap_on(qmap, codes.device)), _ptr_array(list(max_dims)),
-                                                _i64_array(list(shape)), len(shape), _ptr(out), _stream()))
+        N.check(N.lib.lpmm_b200_dequant_rank1(_ptr(codes), _ptr(_qmap_on(qmap, codes.device)), bits,
+                                              _ptr_array(list(max_dims)), _i64_array(list(shape)), len(shape), _ptr(out),
+                                              _stream()))
     return out
 
 
@@ -253,20 +287,26 @@ def _check_param_grad(p, g):
         raise RuntimeError("number of elements in g and p tensors should be equal")
 
 
-def _ensure_group_state(state, name, p, quantized):
+def _check_group_md(md, what):
+    if md["round_type"] != "real-nearest":
+        raise NotImplementedError(f"{what}: only round_type 'real-nearest' is built in this implementation")
+    _check_layout(md["b"], md["gp_sz"])
+
+
+def _ensure_group_state(state, name, p, quantized, bits=4, gp_sz=128):
     """Allocate the storage of a group-scaled / fp32 state on first use; returns (tensor, max1, first)."""
     t = state[name]
     first = t.numel() <= 1  # the reference's test for "not initialised yet" (adamw.py:394)
     oh = state[f"{name}_qstate"]["overhead"]
     if quantized:
         n = p.numel()
-        groups = (n + 127) // 128
+        groups = _groups(n, gp_sz)
         if first or t.dtype != torch.int8:
-            t.data = torch.empty(packed_len(groups * 128), dtype=torch.int8, device=p.device)
+            t.data = torch.empty(packed_len(groups * gp_sz, bits), dtype=torch.int8, device=p.device)
         if not isinstance(oh.get("max1"), torch.Tensor) or oh["max1"].numel() != groups:
             oh["max1"] = torch.empty((groups, 1), dtype=torch.float32, device=p.device)
         oh["dtype"], oh["stride"] = p.dtype, p.stride()
-        oh["scaled_shape"] = torch.Size([groups, 128])
+        oh["scaled_shape"] = torch.Size([groups, gp_sz])
         return t, oh["max1"], first
     if first:
         t.data = torch.zeros_like(p, memory_format=torch.preserve_format)
@@ -278,18 +318,25 @@ def adamw4bit_unfused_step(p, g, state, m_quant, v_quant, md_m, md_v, spare, *, 
     """``spare`` is a dict owned by the optimizer (not part of its state) that keeps the second set
     of per-axis maxima a rank-1 tensor alternates with."""
     _check_param_grad(p, g)
-    for md, q in ((md_m, m_quant), (md_v, v_quant)):
-        if q and (md["b"] != 4 or md["round_type"] != "real-nearest" or md["gp_sz"] != 128):
-            raise NotImplementedError("only 4-bit, real-nearest, group size 128 is built in this implementation")
-    if m_quant and md_m["scale_type"] != "group":
-        raise NotImplementedError("first moment: only scale_type 'group' is built in this implementation")
-    if v_quant and md_v["scale_type"] not in ("group", "rank1"):
-        raise NotImplementedError("second moment: only scale_type 'group' / 'rank1' is built in this implementation")
+    if m_quant:
+        _check_group_md(md_m, "first moment")
+        if md_m["scale_type"] != "group":
+            raise NotImplementedError("first moment: only scale_type 'group' is built in this implementation")
+    if v_quant:
+        _check_group_md(md_v, "second moment")
+        if md_v["scale_type"] not in ("group", "rank1"):
+            raise NotImplementedError("second moment: only scale_type 'group' / 'rank1' is built in this implementation")
+    if m_quant and v_quant and (md_m["b"] == 4) != (md_v["b"] == 4):
+        raise NotImplementedError("4-bit and wider codes cannot be mixed within one tensor in this implementation")
     t = N.StepTensor()
     t.p, t.g, t.numel, t.ndim = p.data_ptr(), g.data_ptr(), p.numel(), max(p.dim(), 1)
     for i, d in enumerate(p.shape):
         t.shape[i] = d
-    m, m_max1, first_m = _ensure_group_state(state, "exp_avg", p, m_quant)
+    if m_quant:
+        t.m_bits, t.m_group = md_m["b"], md_m["gp_sz"]
+    if v_quant:
+        t.v_bits, t.v_group = md_v["b"], md_v["gp_sz"]
+    m, m_max1, first_m = _ensure_group_state(state, "exp_avg", p, m_quant, md_m["b"], md_m["gp_sz"])
     t.m_mode = N.STATE_GROUP4 if m_quant else N.STATE_FP32
     t.m, t.m_max1 = m.data_ptr(), (m_max1.data_ptr() if m_max1 is not None else None)
     rank1 = v_quant and md_v["scale_type"] == "rank1" and p.dim() >= 2
@@ -298,7 +345,7 @@ def adamw4bit_unfused_step(p, g, state, m_quant, v_quant, md_m, md_v, spare, *, 
         v = state["exp_avg_sq"]
         first_v = v.numel() <= 1
         if first_v:
-            v.data = torch.empty(packed_len(p.numel()), dtype=torch.int8, device=p.device)
+            v.data = torch.empty(packed_len(p.numel(), md_v["b"]), dtype=torch.int8, device=p.device)
             oh_v["max_dims"] = _axis_vectors(tuple(p.shape), p.device)
         if "max_dims" not in spare or spare["max_dims"][0].device != p.device:
             spare["max_dims"] = _axis_vectors(tuple(p.shape), p.device)
@@ -310,7 +357,7 @@ def adamw4bit_unfused_step(p, g, state, m_quant, v_quant, md_m, md_v, spare, *, 
         oh_v["max_dims"], spare["max_dims"] = new, list(old)
         oh_v.update(dim=p.dim(), max1=None, scaled_shape=p.shape, dtype=p.dtype, stride=p.stride())
     else:
-        v, v_max1, first_v = _ensure_group_state(state, "exp_avg_sq", p, v_quant)
+        v, v_max1, first_v = _ensure_group_state(state, "exp_avg_sq", p, v_quant, md_v["b"], md_v["gp_sz"])
         if v_quant and md_v["scale_type"] == "rank1":
             oh_v["dim"] = p.dim()
         t.v_mode = N.STATE_GROUP4 if v_quant else N.STATE_FP32
@@ -327,14 +374,17 @@ def adamw4bit_unfused_step(p, g, state, m_quant, v_quant, md_m, md_v, spare, *, 
 
 def adamw4bit_factored_step(p, g, state, m_quant, md_m, *, beta1, beta2, lr, weight_decay, eps, step):
     _check_param_grad(p, g)
-    if m_quant and (md_m["b"] != 4 or md_m["round_type"] != "real-nearest" or md_m["gp_sz"] != 128
-                    or md_m["scale_type"] != "group"):
-        raise NotImplementedError("only 4-bit, real-nearest, group-128 first moments are built in this implementation")
+    if m_quant:
+        _check_group_md(md_m, "first moment")
+        if md_m["scale_type"] != "group":
+            raise NotImplementedError("first moment: only scale_type 'group' is built in this implementation")
     t = N.StepTensor()
     t.p, t.g, t.numel, t.ndim = p.data_ptr(), g.data_ptr(), p.numel(), p.dim()
     for i, d in enumerate(p.shape):
         t.shape[i] = d
-    m, m_max1, first = _ensure_group_state(state, "exp_avg", p, m_quant)
+    if m_quant:
+        t.m_bits, t.m_group = md_m["b"], md_m["gp_sz"]
+    m, m_max1, first = _ensure_group_state(state, "exp_avg", p, m_quant, md_m["b"], md_m["gp_sz"])
     t.m_mode = N.STATE_GROUP4 if m_quant else N.STATE_FP32
     t.m, t.m_max1 = m.data_ptr(), (m_max1.data_ptr() if m_max1 is not None else None)
     t.v_mode = N.STATE_FACTORED
@@ -353,9 +403,12 @@ def adamw4bit_factored_step(p, g, state, m_quant, md_m, *, beta1, beta2, lr, wei
 
 def sgd4bit_step(p, g, state, quant, md, *, weight_decay, momentum, lr, dampening, nesterov, maximize):
     _check_param_grad(p, g)
-    if quant and (md["b"] != 4 or md["round_type"] != "real-nearest" or md["gp_sz"] != 128
-                  or md["scale_type"] != "group"):
-        raise NotImplementedError("only 4-bit, real-nearest, group-128 momentum buffers are built in this implementation")
+    bits, gp_sz = 4, 128
+    if quant:
+        _check_group_md(md, "momentum buffer")
+        if md["scale_type"] != "group":
+            raise NotImplementedError("momentum buffer: only scale_type 'group' is built in this implementation")
+        bits, gp_sz = md["b"], md["gp_sz"]
     buf = buf_max1 = None
     first = False
     if momentum != 0:
@@ -363,18 +416,18 @@ def sgd4bit_step(p, g, state, quant, md, *, weight_decay, momentum, lr, dampenin
         first = b.numel() <= 1
         oh = state["momentum_buffer_qstate"]["overhead"]
         if quant:
-            groups = (p.numel() + 127) // 128
+            groups = _groups(p.numel(), gp_sz)
             if first:
-                b.data = torch.empty(packed_len(groups * 128), dtype=torch.int8, device=p.device)
+                b.data = torch.empty(packed_len(groups * gp_sz, bits), dtype=torch.int8, device=p.device)
                 oh["max1"] = torch.empty((groups, 1), dtype=torch.float32, device=p.device)
-            oh.update(dtype=p.dtype, stride=p.stride(), scaled_shape=torch.Size([groups, 128]))
+            oh.update(dtype=p.dtype, stride=p.stride(), scaled_shape=torch.Size([groups, gp_sz]))
             buf_max1 = oh["max1"]
         elif first:
             b.data = torch.empty_like(p, memory_format=torch.preserve_format)
         buf = b
     qmap = state["momentum_buffer_qstate"]["qmap"]
     with torch.cuda.device(p.device):
-        N.check(N.lib.lpmm_b200_sgd4bit_step(_ptr(p), _ptr(g), p.numel(), _ptr(buf), _ptr(buf_max1),
-                                             N.STATE_GROUP4 if quant else N.STATE_FP32, int(first), _ptr(qmap),
-                                             weight_decay, momentum, lr, dampening, int(bool(nesterov)),
-                                             int(bool(maximize)), _stream()))
+        N.check(N.lib.lpmm_b200_sgd_lowbit_step(_ptr(p), _ptr(g), p.numel(), _ptr(buf), _ptr(buf_max1),
+                                                N.STATE_GROUP4 if quant else N.STATE_FP32, bits, gp_sz, int(first),
+                                                _ptr(qmap), weight_decay, momentum, lr, dampening,
+                                                int(bool(nesterov)), int(bool(maximize)), _stream()))

@@ -51,6 +51,10 @@ class StepTensor(ctypes.Structure):
         ("v_max_dims_new", ctypes.c_void_p * 8),
         ("row", ctypes.c_void_p),
         ("col", ctypes.c_void_p),
+        ("m_bits", ctypes.c_int32),
+        ("v_bits", ctypes.c_int32),
+        ("m_group", ctypes.c_int32),
+        ("v_group", ctypes.c_int32),
     ]
 
 
@@ -92,6 +96,14 @@ def _load():
         "lpmm_b200_axis_absmax": (i32, [vp, ctypes.POINTER(i64), i32, ctypes.POINTER(vp), vp]),
         "lpmm_b200_quant_rank1_4": (i32, [vp, ctypes.POINTER(i64), i32, vp, ctypes.POINTER(vp), vp, vp]),
         "lpmm_b200_dequant_rank1_4": (i32, [vp, vp, ctypes.POINTER(vp), ctypes.POINTER(i64), i32, vp, vp]),
+        "lpmm_b200_packed_len_bits": (i64, [i64, i32]),
+        "lpmm_b200_pack_nonlinear": (i32, [vp, i64, vp, i32, vp, vp]),
+        "lpmm_b200_unpack_nonlinear": (i32, [vp, vp, i32, i64, vp, vp]),
+        "lpmm_b200_quant_group": (i32, [vp, i64, vp, i32, i64, vp, vp, vp]),
+        "lpmm_b200_dequant_group": (i32, [vp, vp, i32, i64, vp, i64, vp, vp]),
+        "lpmm_b200_quant_rank1": (i32, [vp, ctypes.POINTER(i64), i32, vp, i32, ctypes.POINTER(vp), vp, vp]),
+        "lpmm_b200_dequant_rank1": (i32, [vp, vp, i32, ctypes.POINTER(vp), ctypes.POINTER(i64), i32, vp, vp]),
+        "lpmm_b200_sgd_lowbit_step": (i32, [vp, vp, i64, vp, vp, i32, i32, i64, i32, vp, d, d, d, d, i32, i32, vp]),
         "lpmm_b200_adamw4bit_unfused_step": (i32, [ctypes.POINTER(StepTensor), vp, vp] + [d] * 6 + [vp, i64, vp]),
         "lpmm_b200_factored_scratch_bytes": (i64, [ctypes.POINTER(i64), i32]),
         "lpmm_b200_adamw4bit_factored_step_noalloc": (i32, [ctypes.POINTER(StepTensor), vp] + [d] * 6 + [vp]),

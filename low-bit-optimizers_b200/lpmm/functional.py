@@ -2,9 +2,9 @@
 
 The maps are built with the same torch calls as the reference so their fp32 values are
 identical (functional.py:244-315, 644-656).  ``vectorwise_quant`` / ``vectorwise_dequant`` keep the
-reference's signature and metadata dictionaries for the configurations of the 4-bit optimizers
--- ``scale_type`` 'group' or 'rank1', ``quant_type`` 'nonlinear' or 'power-*', ``round_type``
-'real-nearest', 4 bits -- and run on the CUDA library; anything else raises.
+reference's signature and metadata dictionaries for the configurations of the low-bit optimizers
+-- ``scale_type`` 'group' (128 ... 4096) or 'rank1', ``quant_type`` 'nonlinear' or 'power-*',
+``round_type`` 'real-nearest', 4 to 8 bits -- and run on the CUDA library; anything else raises.
 """
 import torch
 
@@ -133,8 +133,8 @@ def _resolve_qmap(kwargs):
 def _check_supported(kwargs):
     if kwargs["quant_type"] not in _MAP_TYPES:
         raise ValueError(f"Not support {kwargs['quant_type']} quant type.")
-    if kwargs["b"] != 4:
-        raise NotImplementedError("only 4-bit maps are built in this implementation")
+    if kwargs["b"] not in _kernels.SUPPORTED_BITS:
+        raise NotImplementedError(f"code widths {_kernels.SUPPORTED_BITS} are built in this implementation")
     if kwargs["round_type"] != "real-nearest":
         raise NotImplementedError("only round_type='real-nearest' is built in this implementation")
     if kwargs["scale_type"] not in ("group", "rank1"):
@@ -145,8 +145,8 @@ def vectorwise_quant(x, **kwargs):
     """Quantize ``x`` -> ``(packed int8 codes, generated metadata)`` (reference functional.py:26-59).
 
     The codes use the reference's layout: the normalised tensor regrouped into zero-padded rows of
-    2048, two 4-bit codes per byte, one trailing byte (functional.py:359-369,
-    quantization_kernel.cu:475-477; the trailing byte, uninitialised there, is 0 here)."""
+    2048, two 4-bit codes (or one wider code) per byte, one trailing byte (functional.py:359-369,
+    quantization_kernel.cu:475-477, 552-554; the trailing byte, uninitialised there, is 0 here)."""
     _check_supported(kwargs)
     qmap = _resolve_qmap(kwargs)
     x = x.detach()
@@ -156,12 +156,12 @@ def vectorwise_quant(x, **kwargs):
         gp_sz = kwargs["gp_sz"] if kwargs["scale_type"] == "group" else 128  # rank1 on vectors: 128 (functional.py:193)
         if kwargs["scale_type"] == "rank1":
             md["dim"] = x.dim()
-        codes, max1 = _kernels.quant_group(xc, qmap, gp_sz)
+        codes, max1 = _kernels.quant_group(xc, qmap, gp_sz, kwargs["b"])
         md["max1"] = max1
         md["scaled_shape"] = torch.Size([max1.shape[0], gp_sz])
     else:
         md["dim"] = x.dim()
-        codes, max_dims = _kernels.quant_rank1(xc, qmap)
+        codes, max_dims = _kernels.quant_rank1(xc, qmap, kwargs["b"])
         md["max_dims"] = max_dims
         md["max1"] = None
         md["scaled_shape"] = x.shape
@@ -176,12 +176,12 @@ def vectorwise_dequant(qx, denormalized=True, **kwargs):
     grouped = kwargs["scale_type"] == "group" or kwargs.get("dim") == 1
     if not denormalized:
         n = kwargs["scaled_shape"].numel()
-        return _kernels.dequant_plain(qx, qmap, n).view(kwargs["scaled_shape"])
+        return _kernels.dequant_plain(qx, qmap, n, kwargs["b"]).view(kwargs["scaled_shape"])
     if grouped:
         gp_sz = kwargs["scaled_shape"][1]
-        x = _kernels.dequant_group(qx, qmap, kwargs["max1"], shape.numel(), gp_sz).view(shape)
+        x = _kernels.dequant_group(qx, qmap, kwargs["max1"], shape.numel(), gp_sz, kwargs["b"]).view(shape)
     else:
-        x = _kernels.dequant_rank1(qx, qmap, kwargs["max_dims"], shape)
+        x = _kernels.dequant_rank1(qx, qmap, kwargs["max_dims"], shape, kwargs["b"])
     if x.stride() != stride:
         out = torch.empty_strided(x.shape, stride, dtype=dtype, layout=torch.strided, device=x.device)
         out.copy_(x)

@@ -127,6 +127,11 @@ class AdamW(LowBitOptimizer):
                 raise ValueError("For same tensor, exp_avg and exp_avg_sq should be both quantized or unquantized "
                                  f"simultaneously, but get ({en_m} {en_v})")
             if en_m:
+                if md_m["b"] != 4 or md_v["b"] != 4:
+                    # the reference's fused kernel reads the first 16 entries of a wider map as a 4-bit map
+                    # (fused_adamw_kernel.cu:27-60); that is not reproduced
+                    raise NotImplementedError("the fused step stores 4-bit codes; use fused=False for "
+                                              f"{md_m['b']}/{md_v['b']}-bit states")
                 if not warned and (md_m["scale_type"] != "group" or md_v["scale_type"] != "group"):
                     print("Warning: fused_adamw4bit only support block-wise scaling, but get scale types "
                           f"({md_m['scale_type']}, {md_v['scale_type']}).")

@@ -35,6 +35,8 @@ def lib():
         L.lpmm_oracle_code.argtypes = [vp, i32, f]
         L.lpmm_oracle_pack4.argtypes = [vp, i64, vp, vp]
         L.lpmm_oracle_unpack4.argtypes = [vp, i64, vp, vp]
+        L.lpmm_oracle_pack8.argtypes = [vp, i64, vp, i32, vp]
+        L.lpmm_oracle_unpack8.argtypes = [vp, i64, vp, i32, vp]
         L.lpmm_oracle_bias_corrections.argtypes = [f, f, f, vp]
         L.lpmm_oracle_adamw4bit_c.argtypes = [vp] * 8 + [f] * 7 + [i64, i32]
         L.lpmm_oracle_adamw4bit.argtypes = [vp] * 8 + [f] * 6 + [i64, i32]
@@ -42,7 +44,7 @@ def lib():
         L.lpmm_oracle_adamw_fp32.argtypes = [vp] * 4 + [f] * 6 + [i64, i32]
         L.lpmm_oracle_threads.restype = i32
         L.lpmm_oracle_set_threads.argtypes = [i32]
-        for n in ("lpmm_oracle_pack4", "lpmm_oracle_unpack4", "lpmm_oracle_bias_corrections",
+        for n in ("lpmm_oracle_pack4", "lpmm_oracle_unpack4", "lpmm_oracle_pack8", "lpmm_oracle_unpack8", "lpmm_oracle_bias_corrections",
                   "lpmm_oracle_adamw4bit_c", "lpmm_oracle_adamw4bit", "lpmm_oracle_adamw_fp32_c",
                   "lpmm_oracle_adamw_fp32", "lpmm_oracle_set_threads"):
             getattr(L, n).restype = None
@@ -103,6 +105,27 @@ def unpack4(packed, qmap, num_groups, group_size):
     out = np.empty(n, np.float32)
     qmap = _f32(qmap)
     lib().lpmm_oracle_unpack4(_ptr(packed), n, _ptr(qmap), _ptr(out))
+    return out.reshape(num_groups, group_size)
+
+
+def pack8(data, qmap, bits):
+    """``pack_nonlinear(data[G, S], qmap, bits, False)`` for 5 <= bits <= 8: uint8[G*S + 1], last byte 0."""
+    data = _f32(data)
+    qmap = _f32(qmap)
+    assert 5 <= bits <= 8 and qmap.size == 1 << bits
+    packed = np.zeros(data.size + 1, np.uint8)
+    lib().lpmm_oracle_pack8(_ptr(data), data.size, _ptr(qmap), bits, _ptr(packed))
+    return packed
+
+
+def unpack8(packed, qmap, bits, num_groups, group_size):
+    """``unpack_nonlinear(packed, qmap, bits, num_groups, group_size)`` for 5 <= bits <= 8."""
+    packed = np.ascontiguousarray(packed).view(np.uint8)
+    qmap = _f32(qmap)
+    assert 5 <= bits <= 8 and qmap.size == 1 << bits
+    n = num_groups * group_size
+    out = np.empty(n, np.float32)
+    lib().lpmm_oracle_unpack8(_ptr(packed), n, _ptr(qmap), bits, _ptr(out))
     return out.reshape(num_groups, group_size)
 
 

@@ -68,6 +68,27 @@ void lpmm_oracle_unpack4(const uint8_t* packed, int64_t n, const float* qmap, fl
   }
 }
 
+/* pack_nonlinear_8bit_kernel<float,false> (quantization_kernel.cu:515-537) for bits 5 ... 8: one code
+ * per byte, the search's result cast to uint8_t without a mask, so a NaN (search result -1) is
+ * stored as 255 whatever the width.  n bytes; the caller provides the trailing byte of the
+ * (total_bits + 8) / 8 allocation (quantization_kernel.cu:552-554). */
+void lpmm_oracle_pack8(const float* data, int64_t n, const float* qmap, int bits, uint8_t* packed) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n; ++i) {
+    float x = data[i];
+    packed[i] = (x != x) ? (uint8_t)255 : (uint8_t)lpmm_oracle_code(qmap, bits, x);
+  }
+}
+
+/* unpack_nonlinear_8bit_kernel<float> (quantization_kernel.cu:655-672): out[i] = qmap[byte].  A byte
+ * beyond the map (the 255 of a NaN in a map of fewer than 8 bits), which the reference reads from
+ * whatever follows its map, decodes to NaN here. */
+void lpmm_oracle_unpack8(const uint8_t* packed, int64_t n, const float* qmap, int bits, float* out) {
+  const int entries = 1 << bits;
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n; ++i) out[i] = (packed[i] < entries) ? qmap[packed[i]] : NAN;
+}
+
 /* Bias corrections of the fused kernels (fused_adamw_kernel.cu:103-104, 72-73), with the host's
  * powf.  The device's powf may differ in the last bit, so tests that want bit-equal parameters
  * pass the device's values to the *_c variants below instead. */

@@ -122,7 +122,7 @@ def _install_yacs():
 
 
 def _cpu_quantization_module():
-    """CPU stand-in for lpmm.cpp_extension.quantization (4-bit, round-to-nearest only)."""
+    """CPU stand-in for lpmm.cpp_extension.quantization (4 to 8 bits, round-to-nearest only)."""
     import torch
     from . import cpu
 
@@ -130,16 +130,23 @@ def _cpu_quantization_module():
 
     def pack_nonlinear(data, qmap, bits, stochastic):
         # quantization.cc:54-63: bits <= 8, data 2-D float, qmap 1-D float
-        assert bits == 4 and not stochastic, "the CPU stand-in covers 4-bit round-to-nearest only"
+        assert 4 <= bits <= 8 and not stochastic, "the CPU stand-in covers 4 to 8 bits, round-to-nearest only"
         assert data.dim() == 2 and qmap.dim() == 1
-        assert data.shape[1] % 8 == 0  # quantization_kernel.cu:473
-        packed = cpu.pack4(data.detach().contiguous().numpy(), qmap.numpy())
+        if bits == 4:  # quantization_kernel.cu:596-600
+            assert data.shape[1] % 8 == 0  # quantization_kernel.cu:473
+            packed = cpu.pack4(data.detach().contiguous().numpy(), qmap.numpy())
+        else:
+            assert data.shape[1] % 4 == 0  # quantization_kernel.cu:550
+            packed = cpu.pack8(data.detach().contiguous().numpy(), qmap.numpy(), bits)
         return torch.from_numpy(packed.view(np.int8))
 
     def unpack_nonlinear(data, qmap, bits, num_groups, group_size):
         # quantization.cc:65-76
-        assert bits == 4 and data.dim() == 1 and data.dtype == torch.int8
-        out = cpu.unpack4(data.contiguous().numpy(), qmap.numpy(), int(num_groups), int(group_size))
+        assert 4 <= bits <= 8 and data.dim() == 1 and data.dtype == torch.int8
+        if bits == 4:  # quantization_kernel.cu:700-704
+            out = cpu.unpack4(data.contiguous().numpy(), qmap.numpy(), int(num_groups), int(group_size))
+        else:
+            out = cpu.unpack8(data.contiguous().numpy(), qmap.numpy(), bits, int(num_groups), int(group_size))
         return torch.from_numpy(out)
 
     mod.pack_nonlinear = pack_nonlinear

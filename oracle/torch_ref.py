@@ -26,27 +26,37 @@ def midpoints(qmap):
 
 
 def codes_of(x, qmap):
-    """quantize_bsearch<false> (quantization_kernel.cu:397-427): #midpoints < x, NaN -> 15."""
+    """quantize_bsearch<false> (quantization_kernel.cu:397-427): #midpoints < x.  A NaN makes the
+    search return -1, stored as 15 by the 4-bit kernel (mask, :454) and as 255 by the
+    one-code-per-byte kernel (cast, :533)."""
     c = torch.bucketize(x, midpoints(qmap), right=False)
-    c = torch.where(torch.isnan(x), torch.full_like(c, qmap.numel() - 1), c)
+    nan_code = 15 if qmap.numel() == 16 else 255
+    c = torch.where(torch.isnan(x), torch.full_like(c, nan_code), c)
     return c.to(torch.uint8)
 
 
 def pack_nonlinear(data, qmap):
-    """pack_nonlinear(data[G, S], qmap, 4, False) (quantization_kernel.cu:430-513): int8[G*S/2 + 1];
-    the trailing byte (uninitialised in the reference) is 0 here."""
+    """pack_nonlinear(data[G, S], qmap, bits, False) with bits = log2(len(qmap)): two codes per byte for
+    4 bits (quantization_kernel.cu:430-513), one per byte for 5 ... 8 (:515-591), plus the trailing
+    byte (uninitialised in the reference, 0 here)."""
     c = codes_of(data.reshape(-1), qmap)
-    packed = (c[0::2] | (c[1::2] << 4)).to(torch.uint8)
+    packed = (c[0::2] | (c[1::2] << 4)).to(torch.uint8) if qmap.numel() == 16 else c
     out = torch.zeros(packed.numel() + 1, dtype=torch.uint8, device=data.device)
     out[:-1] = packed
     return out.view(torch.int8)
 
 
 def unpack_nonlinear(packed, qmap, num_groups, group_size):
-    """unpack_nonlinear (quantization_kernel.cu:604-653): float[num_groups, group_size]."""
-    b = packed.view(torch.uint8)[: num_groups * group_size // 2].to(torch.int64)
-    idx = torch.stack([b & 15, b >> 4], dim=1).reshape(-1)
-    return qmap[idx].reshape(num_groups, group_size)
+    """unpack_nonlinear (quantization_kernel.cu:604-653, 655-693): float[num_groups, group_size].  A
+    byte beyond a map of fewer than 8 bits (the 255 of a NaN) decodes to NaN."""
+    n = num_groups * group_size
+    if qmap.numel() == 16:
+        b = packed.view(torch.uint8)[: n // 2].to(torch.int64)
+        idx = torch.stack([b & 15, b >> 4], dim=1).reshape(-1)
+        return qmap[idx].reshape(num_groups, group_size)
+    idx = packed.view(torch.uint8)[:n].to(torch.int64)
+    ext = torch.cat([qmap, torch.full((256 - qmap.numel(),), float("nan"), dtype=qmap.dtype, device=qmap.device)])
+    return ext[idx].reshape(num_groups, group_size)
 
 
 # ---- grouping (functional.py:404-431) -------------------------------------------------------
@@ -122,7 +132,7 @@ def vectorwise_dequant(q, qmap, scale_type, shape, md):
 
 # ---- non-fused AdamW (adamw.py:332-436) -----------------------------------------------------
 def adamw_step(p, g, st, qmap_m, qmap_v, *, m_quant, v_quant, v_scale_type, beta1, beta2, lr, weight_decay, eps,
-               step):
+               step, m_gp_sz=128, v_gp_sz=128):
     """One tensor of _single_tensor_adamw4bit.  ``st`` is a dict: 'm', 'v' hold either None (not yet
     initialised), an fp32 tensor (not quantized) or packed codes with 'm_md' / 'v_md' metadata."""
     p.mul_(1 - lr * weight_decay)                                        # :369
@@ -147,11 +157,11 @@ def adamw_step(p, g, st, qmap_m, qmap_v, *, m_quant, v_quant, v_scale_type, beta
     denom = (v.sqrt() / bc2_sqrt).add_(eps)                              # :421
     p.addcdiv_(m, denom, value=-step_size)                               # :422
     if m_quant:
-        st["m"], st["m_md"] = vectorwise_quant(m, qmap_m, "group")       # :425-428
+        st["m"], st["m_md"] = vectorwise_quant(m, qmap_m, "group", m_gp_sz)   # :425-428
     else:
         st["m"] = m
     if v_quant:
-        st["v"], st["v_md"] = vectorwise_quant(v, qmap_v, v_scale_type)  # :431-434
+        st["v"], st["v_md"] = vectorwise_quant(v, qmap_v, v_scale_type, v_gp_sz)  # :431-434
     else:
         st["v"] = v
 
@@ -162,7 +172,7 @@ def approx_sq_grad(row, col):
     return torch.mul(r, col.unsqueeze(-2))
 
 
-def factored_step(p, g, st, qmap_m, *, m_quant, beta1, beta2, lr, weight_decay, eps, step):
+def factored_step(p, g, st, qmap_m, *, m_quant, beta1, beta2, lr, weight_decay, eps, step, m_gp_sz=128):
     """param decay (adamw.py:369/478) followed by _single_quantized_factored_update (579-627).
     st: 'm' as above, 'row', 'col' fp32 accumulators."""
     p.mul_(1 - lr * weight_decay)
@@ -183,13 +193,13 @@ def factored_step(p, g, st, qmap_m, *, m_quant, beta1, beta2, lr, weight_decay, 
     denom = (v.sqrt() / math.sqrt(bc2)).add_(eps)                        # :618
     p.addcdiv_(m, denom, value=-step_size)                               # :619
     if m_quant:
-        st["m"], st["m_md"] = vectorwise_quant(m, qmap_m, "group")       # :622-625
+        st["m"], st["m_md"] = vectorwise_quant(m, qmap_m, "group", m_gp_sz)   # :622-625
     else:
         st["m"] = m
 
 
 # ---- SGD with momentum (sgd.py:133-187) -----------------------------------------------------
-def sgd_step(p, g, st, qmap, *, quant, weight_decay, momentum, lr, dampening, nesterov, maximize):
+def sgd_step(p, g, st, qmap, *, quant, weight_decay, momentum, lr, dampening, nesterov, maximize, gp_sz=128):
     d_p = g if not maximize else -g
     if weight_decay != 0:
         d_p = d_p.add(p, alpha=weight_decay)                             # :156
@@ -203,6 +213,6 @@ def sgd_step(p, g, st, qmap, *, quant, weight_decay, momentum, lr, dampening, ne
     p.add_(d_p, alpha=-lr)                                               # :182
     if momentum != 0:
         if quant:
-            st["buf"], st["buf_md"] = vectorwise_quant(buf, qmap, "group")   # :185-187
+            st["buf"], st["buf_md"] = vectorwise_quant(buf, qmap, "group", gp_sz)   # :185-187
         else:
             st["buf"] = buf

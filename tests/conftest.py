@@ -24,5 +24,8 @@ def golden_dir():
 @pytest.fixture(scope="session")
 def qmaps():
     import numpy as np
-    z = np.load(os.path.join(GOLDEN, "qmaps.npz"))
-    return {k: z[k] for k in z.files}
+    out = {}
+    for f in ("qmaps.npz", "qmaps_wide.npz"):
+        z = np.load(os.path.join(GOLDEN, f))
+        out.update({k: z[k] for k in z.files})
+    return out

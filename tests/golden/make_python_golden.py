@@ -36,6 +36,15 @@ CASES = {
     "sgd_momentum": ("SGD", dict(lr=1e-2, momentum=0.9, weight_decay=1e-4, qconfig=None), [(72, 64), (4097,), (100,)], 4, 0.0),
     "sgd_nesterov": ("SGD", dict(lr=1e-2, momentum=0.8, dampening=0.0, nesterov=True, weight_decay=0.0, qconfig=None),
                      [(5000,), (6, 700)], 3, 0.0),
+    # wider codes (one per byte) and larger first-moment groups
+    "adamw_8bit": ("AdamW", dict(qconfig="default_8b.yml", **HYPER), [(72, 64), (4097,), (5000, 1)], 4, 0.0),
+    "adamw_5bit": ("AdamW", dict(qconfig="default_5b.yml", **HYPER), [(70, 61), (4100,)], 3, 0.0),
+    "adamw_m_group_512": ("AdamW", dict(qconfig="1st_moment_group_512.yml", **HYPER), [(72, 64), (4097,), (9000,)], 4, 0.0),
+    "adamw_m_group_4096": ("AdamW", dict(qconfig="1st_moment_group_4096.yml", **HYPER),
+                           [(70, 61), (10000,), (5000, 1)], 3, 0.0),
+    "sgd_8bit": ("SGD", dict(lr=1e-2, momentum=0.9, weight_decay=1e-4, qconfig="default_8b.yml"), [(72, 64), (4097,)], 3, 0.0),
+    "sgd_group_1024": ("SGD", dict(lr=1e-2, momentum=0.9, weight_decay=0.0, qconfig="1st_moment_group_1024.yml"),
+                       [(5000,), (6, 700)], 3, 0.0),
 }
 
 
@@ -103,18 +112,28 @@ def run_case(lpmm, name, ref_root):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--only", nargs="*", default=None, help="generate just these cases (and no map files)")
     a = ap.parse_args()
     from oracle.ref_loader import load_reference
     cwd = os.getcwd()
     os.chdir("/tmp")  # the reference writes ./lpmm_config.txt on construction
     lpmm = load_reference(a.reference)
     import contextlib, io
-    for name in CASES:
+    for name in (a.only if a.only else CASES):
         with contextlib.redirect_stdout(io.StringIO()):
             n = run_case(lpmm, name, a.reference)
         print(f"{name}: {n} arrays")
-    # the two quantization maps, as the reference builds them
     import lpmm.functional as F
+    # the maps of the wider configurations: signed 'nonlinear' and unsigned 'power-1' for 5 ... 8 bits
+    wide = {}
+    for b in (5, 6, 7, 8):
+        wide[f"nonlinear_{b}"] = F.create_general_qmap("nonlinear", b, True).numpy()
+        wide[f"power1_{b}"] = F.create_general_qmap("power-1", b, False).numpy()
+    np.savez_compressed(os.path.join(HERE, "qmaps_wide.npz"), **wide)
+    if a.only:
+        os.chdir(cwd)
+        return
+    # the two quantization maps, as the reference builds them
     np.savez(os.path.join(HERE, "qmaps.npz"), m=F.create_general_qmap("nonlinear", 4, True).numpy(),
              v=F.create_general_qmap("power-1", 4, False).numpy(),
              nonlinear_unsigned=F.create_general_qmap("nonlinear", 4, False).numpy(),

@@ -41,6 +41,21 @@ def device_qmaps(qmaps):
     return _qbuf[64:80], _qbuf[128:144], _qbuf[192:208]
 
 
+_wide_bufs = {}
+
+
+def device_map(qmaps, name):
+    """One map of the fixture on the device, carved out of the middle of a larger zero buffer (the
+    reference's kernels may read one entry before a map and, for the byte 255 of a map with fewer
+    than 256 entries, up to 255 entries after its start)."""
+    if name not in _wide_bufs:
+        a = torch.from_numpy(np.ascontiguousarray(qmaps[name]))
+        buf = torch.zeros(64 + 512, dtype=torch.float32, device=device())
+        buf[64:64 + a.numel()] = a
+        _wide_bufs[name] = buf
+    return _wide_bufs[name][64:64 + len(qmaps[name])]
+
+
 def student_t(shape, seed, dev=None, zero_fraction=0.0, scale=1e-3):
     """Seeded Student-t(3) gradients with 1 % of rows (>= 2-D) scaled by 50."""
     dev = dev or device()

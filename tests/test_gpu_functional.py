@@ -5,7 +5,7 @@ import numpy as np
 import pytest
 import torch
 
-from gpu_helpers import bits_equal, device, device_qmaps, load_reference_extension, student_t
+from gpu_helpers import bits_equal, device, device_map, device_qmaps, load_reference_extension, student_t
 
 pytestmark = pytest.mark.gpu
 
@@ -39,6 +39,43 @@ def test_pack_unpack_match_reference_kernels(qmaps, which):
         torch.cuda.synchronize()
         assert torch.equal(packed[:-1], r_packed[:-1]), "codes differ from the reference's kernel"
         assert bits_equal(out, ref.unpack_nonlinear(r_packed, qmap, 4, x.shape[0], 2048))
+
+
+@pytest.mark.parametrize("bits", [5, 6, 7, 8])
+@pytest.mark.parametrize("kind", ["nonlinear", "power1"])
+def test_pack_unpack_one_code_per_byte_match_reference_kernels(qmaps, bits, kind):
+    """Maps of 5 to 8 bits (pack_nonlinear_8bit / unpack_nonlinear_8bit in the reference).  NaN is
+    left out of the comparison with the reference's kernel: it stores 255 there, which its unpack
+    kernel then reads from beyond a map of fewer than 256 entries; the 255 itself is checked
+    against the restated rule."""
+    from lpmm.cpp_extension import quantization as mine
+    from oracle import torch_ref as T
+    ref = load_reference_extension("quantization")
+    qmap = device_map(qmaps, f"{kind}_{bits}")
+    assert qmap.numel() == 1 << bits
+    torch.manual_seed(bits)
+    special = _special_values(qmap)
+    x = torch.cat([special[~torch.isnan(special)], torch.rand(2048 * 5) * 2.2 - 1.1])
+    x = torch.cat([x, torch.zeros((-x.numel()) % 2048)]).to(device()).view(-1, 2048)
+    packed = mine.pack_nonlinear(x, qmap, bits, False)
+    assert packed.dtype == torch.int8 and packed.numel() == x.numel() + 1 and int(packed[-1]) == 0
+    assert torch.equal(packed, T.pack_nonlinear(x, qmap)), "codes differ from the restated rule"
+    out = mine.unpack_nonlinear(packed, qmap, bits, x.shape[0], 2048)
+    assert out.shape == x.shape and bits_equal(out, T.unpack_nonlinear(packed, qmap, x.shape[0], 2048))
+    if ref is not None:
+        r_packed = ref.pack_nonlinear(x, qmap, bits, False)
+        torch.cuda.synchronize()
+        assert torch.equal(packed[:-1], r_packed[:-1]), "codes differ from the reference's kernel"
+        assert bits_equal(out, ref.unpack_nonlinear(r_packed, qmap, bits, x.shape[0], 2048))
+    xn = x.clone()
+    xn[0, :7] = float("nan")
+    pn = mine.pack_nonlinear(xn, qmap, bits, False)
+    assert torch.equal(pn, T.pack_nonlinear(xn, qmap)) and (pn[:7].view(torch.uint8) == 255).all()
+    back = mine.unpack_nonlinear(pn, qmap, bits, x.shape[0], 2048)
+    if bits < 8:
+        assert torch.isnan(back[0, :7]).all()
+    else:
+        assert bits_equal(back[0, :7], qmap[255].expand(7).contiguous())
 
 
 def test_pack_argument_checks(qmaps):
@@ -87,13 +124,49 @@ def test_vectorwise_quant_dequant_match_restated_reference(qmaps, shape, scale_t
     assert back.shape == x.shape and bits_equal(back, o_back)
 
 
+@pytest.mark.parametrize("shape", [(4097,), (127,), (300, 130), (3, 3, 24, 24), (5000, 1), (9000,)])
+@pytest.mark.parametrize("bits,gp_sz,scale_type,kind", [
+    (8, 128, "group", "nonlinear"), (8, 128, "rank1", "power1"), (5, 128, "group", "nonlinear"),
+    (6, 128, "rank1", "power1"), (7, 128, "group", "power1"), (4, 256, "group", "m"), (4, 512, "group", "m"),
+    (4, 1024, "group", "v"), (4, 2048, "group", "m"), (4, 4096, "group", "m"), (8, 4096, "group", "nonlinear"),
+    (5, 512, "group", "nonlinear")])
+def test_vectorwise_quant_dequant_wider_codes_and_larger_groups(qmaps, shape, bits, gp_sz, scale_type, kind):
+    import lpmm.functional as F
+    from oracle import torch_ref as T
+    name = kind if bits == 4 else f"{kind}_{bits}"
+    qmap = device_map(qmaps, name)
+    unsigned = kind in ("v", "power1")
+    x = student_t(shape, 78)  # dense: with one code per byte an all-zero group is NaN in the reference as well
+    if unsigned:
+        x = x * x
+    kw = dict(_META, b=bits, gp_sz=gp_sz, quant_type="power-1" if unsigned else "nonlinear", signed=not unsigned,
+              scale_type=scale_type)
+    codes, md = F.vectorwise_quant(x, qmap=qmap, shape=x.shape, **kw)
+    o_codes, o_md = T.vectorwise_quant(x, qmap, scale_type, gp_sz)
+    assert codes.dtype == torch.int8 and codes.numel() == o_codes.numel()
+    assert torch.equal(codes.view(torch.uint8), o_codes.view(torch.uint8)), "codes differ"
+    assert md["scaled_shape"] == o_md["scaled_shape"]
+    if scale_type == "rank1" and len(shape) > 1:
+        for a, b in zip(md["max_dims"], o_md["max_dims"]):
+            assert a.shape == b.shape and bits_equal(a, b)
+    else:
+        assert bits_equal(md["max1"], o_md["max1"]) and md["max1"].shape == o_md["max1"].shape
+    back = F.vectorwise_dequant(codes, qmap=qmap, shape=x.shape, **{**kw, **md})
+    o_back = T.vectorwise_dequant(o_codes, qmap, scale_type, x.shape, o_md)
+    assert back.shape == x.shape and bits_equal(back, o_back)
+
+
 def test_vectorwise_quant_rejects_what_is_not_built(qmaps):
     import lpmm.functional as F
     qm, _, _ = device_qmaps(qmaps)
     x = torch.randn(4096, device=device())
     base = dict(_META, quant_type="nonlinear", signed=True, scale_type="group", qmap=qm, shape=x.shape)
     with pytest.raises(NotImplementedError):
-        F.vectorwise_quant(x, **{**base, "b": 8})
+        F.vectorwise_quant(x, **{**base, "b": 2})
+    with pytest.raises(NotImplementedError):
+        F.vectorwise_quant(x, **{**base, "gp_sz": 64})
+    with pytest.raises(RuntimeError):
+        F.vectorwise_quant(x, **{**base, "b": 8})  # a 16-entry map is not an 8-bit map
     with pytest.raises(NotImplementedError):
         F.vectorwise_quant(x, **{**base, "round_type": "sr"})
     with pytest.raises(NotImplementedError):

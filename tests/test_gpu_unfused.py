@@ -9,7 +9,7 @@ import numpy as np
 import pytest
 import torch
 
-from golden_cases import CASES, THRESHOLD
+from golden_cases import CASES, THRESHOLD, layout
 from gpu_helpers import bits_equal, device, nibbles, student_t
 
 pytestmark = pytest.mark.gpu
@@ -33,10 +33,10 @@ def _make_opt(kind, params, kw):
     return getattr(lpmm.optim, kind)(params, **kw)
 
 
-def _run_pair_adamw(shapes, p0s, grads_of_step, steps, kw, qmaps, v_scale):
+def _run_pair_adamw(shapes, p0s, grads_of_step, steps, kw, qmaps, v_scale, maps=("m", "v"), m_gp=128):
     """Returns (optimizer, params, oracle states, oracle params)."""
     from oracle import torch_ref as T
-    qm, qv = _dev(qmaps["m"]), _dev(qmaps["v"])
+    qm, qv = _dev(qmaps[maps[0]]), _dev(qmaps[maps[1]])
     params = [torch.nn.Parameter(p.clone()) for p in p0s]
     opt = _make_opt("AdamW", params, kw)
     o_params = [p.clone() for p in p0s]
@@ -55,22 +55,23 @@ def _run_pair_adamw(shapes, p0s, grads_of_step, steps, kw, qmaps, v_scale):
             quant = op.numel() > THRESHOLD
             common = dict(beta1=b1, beta2=b2, lr=kw["lr"], weight_decay=kw["weight_decay"], eps=kw["eps"], step=float(s))
             if factored and op.dim() >= 2:
-                T.factored_step(op, g, o_states[i], qm, m_quant=quant, **common)
+                T.factored_step(op, g, o_states[i], qm, m_quant=quant, m_gp_sz=m_gp, **common)
             else:
-                T.adamw_step(op, g, o_states[i], qm, qv, m_quant=quant, v_quant=quant, v_scale_type=v_scale, **common)
+                T.adamw_step(op, g, o_states[i], qm, qv, m_quant=quant, v_quant=quant, v_scale_type=v_scale,
+                             m_gp_sz=m_gp, **common)
     torch.cuda.synchronize()
     return opt, params, o_states, o_params
 
 
-def _check_group_state(mine_codes, mine_max1, o_codes, o_md, n, what):
-    groups = (n + 127) // 128
+def _check_group_state(mine_codes, mine_max1, o_codes, o_md, n, what, gp=128):
+    groups = (n + gp - 1) // gp
     assert mine_codes.numel() == o_codes.numel(), f"{what}: packed length"
     assert torch.equal(mine_codes.view(torch.uint8), o_codes.view(torch.uint8)), f"{what}: codes (incl. padding) differ"
     assert bits_equal(mine_max1.reshape(-1), o_md["max1"].reshape(-1)), f"{what}: scales differ"
     assert mine_max1.numel() == groups
 
 
-def _check_adamw(opt, params, o_states, o_params, v_scale, factored=False, p_exact=True):
+def _check_adamw(opt, params, o_states, o_params, v_scale, factored=False, p_exact=True, m_gp=128):
     for i, p in enumerate(params):
         st, os_, op = opt.state[p], o_states[i], o_params[i]
         quant = p.numel() > THRESHOLD
@@ -82,7 +83,7 @@ def _check_adamw(opt, params, o_states, o_params, v_scale, factored=False, p_exa
             assert bits_equal(p.detach(), op), f"tensor {i}: params differ"
         if quant:
             _check_group_state(st["exp_avg"], st["exp_avg_qstate"]["overhead"]["max1"], os_["m"], os_["m_md"], p.numel(),
-                               f"tensor {i} exp_avg")
+                               f"tensor {i} exp_avg", m_gp)
         else:
             assert bits_equal(st["exp_avg"], os_["m"]), f"tensor {i}: fp32 exp_avg differs"
         if fac:
@@ -104,24 +105,36 @@ def _check_adamw(opt, params, o_states, o_params, v_scale, factored=False, p_exa
                                p.numel(), f"tensor {i} exp_avg_sq")
 
 
-@pytest.mark.parametrize("name", ["adamw_rank1", "adamw_group", "adamw_rank1_ragged"])
+def _codes(t, n, bits):
+    """The first n codes of a packed tensor as uint8."""
+    return nibbles(t, n) if bits == 4 else t.view(torch.uint8)[:n]
+
+
+@pytest.mark.parametrize("name", ["adamw_rank1", "adamw_group", "adamw_rank1_ragged", "adamw_8bit", "adamw_5bit",
+                                  "adamw_m_group_512", "adamw_m_group_4096"])
 def test_adamw_unfused_on_golden_inputs(golden_dir, qmaps, name):
     G = _golden(golden_dir, name)
     _, kw, shapes = CASES[name]
-    v_scale = "rank1" if kw["qconfig"] == "default.yml" else "group"
+    L = layout(name)
+    v_scale = L["v_scale"]
     steps = int(G["steps"])
     p0s = [_dev(G[f"p0.{i}"]) for i in range(len(shapes))]
     opt, params, o_states, o_params = _run_pair_adamw(
-        shapes, p0s, lambda s: [_dev(G[f"g{s}.{i}"]) for i in range(len(shapes))], steps, kw, qmaps, v_scale)
-    _check_adamw(opt, params, o_states, o_params, v_scale)
+        shapes, p0s, lambda s: [_dev(G[f"g{s}.{i}"]) for i in range(len(shapes))], steps, kw, qmaps, v_scale,
+        maps=L["maps"], m_gp=L["m_gp"])
+    _check_adamw(opt, params, o_states, o_params, v_scale, m_gp=L["m_gp"])
     # and against what the reference's Python produced on CPU: same codes up to fp ties, same params to 1e-6
     for i, p in enumerate(params):
         ref_p = _dev(G[f"p.{i}"])
         assert ((p.detach() - ref_p).norm() / ref_p.norm()).item() <= 1e-6
         if p.numel() > THRESHOLD:
             n = p.numel()
-            mism = (nibbles(opt.state[p]["exp_avg"], n) != nibbles(_dev(G[f"s.{i}.exp_avg"]), n)).float().mean().item()
-            assert mism <= 1e-3, f"tensor {i}: {mism} of first-moment codes differ from the CPU run"
+            assert opt.state[p]["exp_avg"].numel() == G[f"s.{i}.exp_avg"].size, "packed length differs from the CPU run"
+            mism = (_codes(opt.state[p]["exp_avg"], n, L["bits"])
+                    != _codes(_dev(G[f"s.{i}.exp_avg"]), n, L["bits"])).float().mean().item()
+            # wider maps have closer midpoints, so the last-bit differences between CPU and GPU torch ops
+            # flip proportionally more codes
+            assert mism <= (1e-3 if L["bits"] == 4 else 2e-2), f"tensor {i}: {mism} of first-moment codes differ from the CPU run"
 
 
 def test_adamw_unfused_larger_ragged_shapes(qmaps):
@@ -136,6 +149,31 @@ def test_adamw_unfused_larger_ragged_shapes(qmaps):
         shapes, p0s, lambda s: [student_t(sh, s * 100003 + i, zero_fraction=0.2) for i, sh in enumerate(shapes)], 6, kw,
         qmaps, "rank1")
     _check_adamw(opt, params, o_states, o_params, "rank1")
+
+
+@pytest.mark.parametrize("cfg,bits,m_gp", [("default_8b.yml", 8, 128), ("default_6b.yml", 6, 128),
+                                           ("default_7b.yml", 7, 128), ("1st_moment_group_256.yml", 4, 256),
+                                           ("1st_moment_group_1024.yml", 4, 1024),
+                                           ("1st_moment_group_2048.yml", 4, 2048),
+                                           ("1st_moment_group_4096.yml", 4, 4096)])
+def test_adamw_wider_codes_and_larger_groups_ragged_shapes(qmaps, golden_dir, cfg, bits, m_gp):
+    """Every remaining configuration file on ragged shapes (group padding that crosses a 2048-row,
+    tensors shorter than one group, a column vector), 20 % exact zeros where the format allows
+    it: with one code per byte an all-zero group becomes NaN in the reference (its 0/0 is stored
+    as 255, which the unpack kernel reads past the end of a map of fewer than 256 entries), so those
+    cases use dense gradients."""
+    shapes = [(3, 3, 64, 64), (1000, 768), (4097,), (6000,), (4096,), (50000, 1), (777, 13)]
+    kw = dict(qconfig=cfg, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01)
+    maps = ("m", "v") if bits == 4 else (f"nonlinear_{bits}", f"power1_{bits}")
+    if bits not in (4,) and maps[0] not in qmaps:
+        pytest.skip("map fixture missing")
+    torch.manual_seed(5)
+    p0s = [torch.randn(s, device=device()) * 0.02 for s in shapes]
+    zf = 0.2 if bits == 4 else 0.0
+    opt, params, o_states, o_params = _run_pair_adamw(
+        shapes, p0s, lambda s: [student_t(sh, s * 100003 + i, zero_fraction=zf) for i, sh in enumerate(shapes)], 5, kw,
+        qmaps, "rank1", maps=maps, m_gp=m_gp)
+    _check_adamw(opt, params, o_states, o_params, "rank1", m_gp=m_gp)
 
 
 def test_adamw_group_config_matrix(qmaps):
@@ -168,13 +206,14 @@ def test_adamw_factored_gpt2_like_shapes(qmaps):
     _check_adamw(opt, params, o_states, o_params, "group", factored=True)
 
 
-@pytest.mark.parametrize("name", ["sgd_momentum", "sgd_nesterov"])
+@pytest.mark.parametrize("name", ["sgd_momentum", "sgd_nesterov", "sgd_8bit", "sgd_group_1024"])
 def test_sgd_on_golden_inputs(golden_dir, qmaps, name):
     from oracle import torch_ref as T
     G = _golden(golden_dir, name)
     _, kw, shapes = CASES[name]
+    L = layout(name)
     steps = int(G["steps"])
-    qm = _dev(qmaps["m"])
+    qm = _dev(qmaps[L["maps"][0]])
     params = [torch.nn.Parameter(_dev(G[f"p0.{i}"])) for i in range(len(shapes))]
     opt = _make_opt("SGD", params, kw)
     o_params = [_dev(G[f"p0.{i}"]) for i in range(len(shapes))]
@@ -185,7 +224,7 @@ def test_sgd_on_golden_inputs(golden_dir, qmaps, name):
             p.grad = g.clone()
             T.sgd_step(o_params[i], g, o_states[i], qm, quant=p.numel() > THRESHOLD, weight_decay=kw["weight_decay"],
                        momentum=kw["momentum"], lr=kw["lr"], dampening=kw.get("dampening", 0),
-                       nesterov=kw.get("nesterov", False), maximize=False)
+                       nesterov=kw.get("nesterov", False), maximize=False, gp_sz=L["m_gp"])
         opt.step()
     torch.cuda.synchronize()
     for i, p in enumerate(params):
@@ -193,7 +232,7 @@ def test_sgd_on_golden_inputs(golden_dir, qmaps, name):
         st = opt.state[p]
         if p.numel() > THRESHOLD:
             _check_group_state(st["momentum_buffer"], st["momentum_buffer_qstate"]["overhead"]["max1"], o_states[i]["buf"],
-                               o_states[i]["buf_md"], p.numel(), f"tensor {i} buffer")
+                               o_states[i]["buf_md"], p.numel(), f"tensor {i} buffer", L["m_gp"])
         else:
             assert bits_equal(st["momentum_buffer"], o_states[i]["buf"])
         ref_p = _dev(G[f"p.{i}"])

@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 import torch
 
-from golden_cases import CASES, THRESHOLD
+from golden_cases import CASES, THRESHOLD, layout
 from oracle import torch_ref as T
 
 
@@ -25,12 +25,14 @@ def _same_codes(a, b, numel_codes):
     return np.array_equal(a, b)
 
 
-@pytest.mark.parametrize("name", ["adamw_rank1", "adamw_group", "adamw_rank1_ragged"])
+@pytest.mark.parametrize("name", ["adamw_rank1", "adamw_group", "adamw_rank1_ragged", "adamw_8bit", "adamw_5bit",
+                                  "adamw_m_group_512", "adamw_m_group_4096"])
 def test_adamw_unfused_matches_reference_python(golden_dir, qmaps, name):
     G = _load(golden_dir, name)
     _, kw, shapes = CASES[name]
-    v_scale = "rank1" if kw["qconfig"] == "default.yml" else "group"
-    qm, qv = _t(qmaps["m"]), _t(qmaps["v"])
+    L = layout(name)
+    v_scale = L["v_scale"]
+    qm, qv = _t(qmaps[L["maps"][0]]), _t(qmaps[L["maps"][1]])
     steps = int(G["steps"])
     for i, shape in enumerate(shapes):
         p = _t(G[f"p0.{i}"]).clone()
@@ -38,12 +40,14 @@ def test_adamw_unfused_matches_reference_python(golden_dir, qmaps, name):
         st = {}
         for s in range(1, steps + 1):
             T.adamw_step(p, _t(G[f"g{s}.{i}"]), st, qm, qv, m_quant=quant, v_quant=quant, v_scale_type=v_scale,
-                         beta1=0.9, beta2=0.999, lr=1e-3, weight_decay=0.01, eps=1e-8, step=float(s))
+                         beta1=0.9, beta2=0.999, lr=1e-3, weight_decay=0.01, eps=1e-8, step=float(s),
+                         m_gp_sz=L["m_gp"])
         assert np.array_equal(p.numpy(), G[f"p.{i}"]), f"params of tensor {i}"
         if quant:
-            n_codes = G[f"s.{i}.exp_avg"].size - 1  # last byte is not written by the reference
-            assert _same_codes(st["m"].numpy(), G[f"s.{i}.exp_avg"], n_codes)
-            assert _same_codes(st["v"].numpy(), G[f"s.{i}.exp_avg_sq"], n_codes)
+            # last byte is not written by the reference
+            assert st["m"].numel() == G[f"s.{i}.exp_avg"].size and st["v"].numel() == G[f"s.{i}.exp_avg_sq"].size
+            assert _same_codes(st["m"].numpy(), G[f"s.{i}.exp_avg"], G[f"s.{i}.exp_avg"].size - 1)
+            assert _same_codes(st["v"].numpy(), G[f"s.{i}.exp_avg_sq"], G[f"s.{i}.exp_avg_sq"].size - 1)
             assert np.array_equal(st["m_md"]["max1"].numpy(), G[f"s.{i}.exp_avg_qstate.overhead.max1"])
             if v_scale == "rank1" and len(shape) > 1:
                 for d in range(len(shape)):
@@ -83,11 +87,12 @@ def test_adamw_factored_matches_reference_python(golden_dir, qmaps):
             assert np.array_equal(st["m"].numpy(), G[f"s.{i}.exp_avg"])
 
 
-@pytest.mark.parametrize("name", ["sgd_momentum", "sgd_nesterov"])
+@pytest.mark.parametrize("name", ["sgd_momentum", "sgd_nesterov", "sgd_8bit", "sgd_group_1024"])
 def test_sgd_matches_reference_python(golden_dir, qmaps, name):
     G = _load(golden_dir, name)
     _, kw, shapes = CASES[name]
-    qm = _t(qmaps["m"])
+    L = layout(name)
+    qm = _t(qmaps[L["maps"][0]])
     steps = int(G["steps"])
     for i, shape in enumerate(shapes):
         p = _t(G[f"p0.{i}"]).clone()
@@ -96,7 +101,7 @@ def test_sgd_matches_reference_python(golden_dir, qmaps, name):
         for s in range(1, steps + 1):
             T.sgd_step(p, _t(G[f"g{s}.{i}"]), st, qm, quant=quant, weight_decay=kw["weight_decay"],
                        momentum=kw["momentum"], lr=kw["lr"], dampening=kw.get("dampening", 0),
-                       nesterov=kw.get("nesterov", False), maximize=False)
+                       nesterov=kw.get("nesterov", False), maximize=False, gp_sz=L["m_gp"])
         assert np.array_equal(p.numpy(), G[f"p.{i}"])
         if quant:
             assert _same_codes(st["buf"].numpy(), G[f"s.{i}.momentum_buffer"], G[f"s.{i}.momentum_buffer"].size - 1)
