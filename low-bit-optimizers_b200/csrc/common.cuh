@@ -236,6 +236,16 @@ __device__ __forceinline__ f2 f2_fma(f2 a, f2 b, f2 c) {
   asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
   return r;
 }
+// RN(RN(a * b) + c) per half, two roundings.  Done with scalar instructions: a packed mul.rn
+// whose only use is a packed add.rn was observed (random inputs, against the scalar pair) to come
+// out as one fused multiply-add, and so was an fma with a -0.0 addend followed by the add.
+__device__ __forceinline__ f2 f2_mul_then_add(f2 a, f2 b, f2 c) {
+  float a0, a1, b0, b1, c0, c1;
+  f2_unpack(a, a0, a1);
+  f2_unpack(b, b0, b1);
+  f2_unpack(c, c0, c1);
+  return f2_pack(__fadd_rn(__fmul_rn(a0, b0), c0), __fadd_rn(__fmul_rn(a1, b1), c1));
+}
 
 struct f2x4 {
   f2 v[4];

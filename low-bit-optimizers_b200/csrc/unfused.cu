@@ -22,6 +22,8 @@
 // CTA whose maxima are combined through shared memory.
 #include <math.h>
 
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace lpmm_b200 {
@@ -69,6 +71,7 @@ struct Maps {
   float mm[256];  // midpoints of qm, padded with +inf
   float mv[256];
   int zero_m, zero_v;  // code of 0.0f in each map (what padding quantizes to)
+  int linear_v;        // qv[i] == (i + 1) / 2^bits exactly: the closed-form code applies
 };
 
 // Nearest-code rule as a branch-free search over the sorted midpoints: code = #{midpoints < x}.
@@ -135,9 +138,17 @@ __device__ __forceinline__ Codes8<W> codes_by_group_scale(const float* __restric
   Codes8<W> out;
   out.clear();
   if (udiv_ok(d)) {
-    const float r = rcp_nr(d);
+    const f2 r2 = f2_splat(rcp_nr(d)), nd2 = f2_splat(-d);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) out.set(k, code_of<W>(mids, bits, udiv(x[k], d, r)));
+    for (int j = 0; j < 4; ++j) {  // udiv on two elements per instruction
+      const f2 xj = f2_pack(x[2 * j], x[2 * j + 1]);
+      f2 q = f2_mul(xj, r2);
+      q = f2_fma(f2_fma(q, nd2, xj), r2, q);
+      float qa, qb;
+      f2_unpack(q, qa, qb);
+      out.set(2 * j, code_of<W>(mids, bits, qa));
+      out.set(2 * j + 1, code_of<W>(mids, bits, qb));
+    }
   } else {
 #pragma unroll
     for (int k = 0; k < 8; ++k) out.set(k, code_of<W>(mids, bits, __fdiv_rn(x[k], d)));
@@ -167,8 +178,21 @@ __device__ __forceinline__ void load_maps(Maps& M, const float* __restrict__ qm,
   if (threadIdx.x == 0) {
     M.zero_m = code_of<W>(M.mm, bits_m, 0.0f);
     M.zero_v = code_of<W>(M.mv, bits_v, 0.0f);
+    int lin = qv != nullptr;
+    const float step = 1.0f / (float)nv;  // a power of two: (i + 1) * step is exact
+    for (int i = 0; i < nv; ++i) lin &= (M.qv[i] == (float)(i + 1) * step);
+    M.linear_v = lin;
   }
   __syncthreads();
+}
+
+// Closed form of the nearest-code rule for the map q[i] = (i + 1) / N, N = 2^bits (midpoints
+// (2k + 1) / (2N)): code = ceil(N x - 1.5) clamped to [0, N - 1].  N x - 1.5 is exact whenever it is
+// positive (both terms are multiples of ulp(N x) and the difference is smaller than N x), a negative
+// value saturates to 0 in the conversion, so the result equals the search for every x <= 1.
+__device__ __forceinline__ int linear_code(float x, float N, int top) {
+  const int c = (int)__float2uint_ru(__fmaf_rn(x, N, -1.5f));
+  return c < top ? c : top;
 }
 
 __device__ __forceinline__ float hmax16(float x, unsigned mask) {
@@ -225,6 +249,11 @@ __device__ __forceinline__ float axis_min(const float* const* vecs, const int* c
   return st;
 }
 
+// e / d for non-negative operands, in 32 bits when both fit.
+__device__ __forceinline__ long long div_nn(long long e, long long d) {
+  return ((e | d) >> 32) ? e / d : (long long)((unsigned)e / (unsigned)d);
+}
+
 // min_i vecs[i][idx_i] for the 8 consecutive elements starting at flat index e0.  2-D tensors whose
 // lane stays inside one row read the row value once and the 8 column values as two 128-bit loads.
 template <int ND>
@@ -232,7 +261,7 @@ __device__ __forceinline__ void lane_scales(const float* const* vecs, long long 
                                             float* out) {
   if (ND == 2) {
     const long long C = s.dim[1];
-    const long long r = e0 / C;
+    const long long r = div_nn(e0, C);
     const long long col = e0 - r * C;
     if (col + 8 <= C && e0 + 8 <= n && ((reinterpret_cast<uintptr_t>(vecs[1] + col) & 15) == 0)) {
       const float rv = __ldg(vecs[0] + r);
@@ -276,13 +305,63 @@ __device__ __forceinline__ float upd_param(const UConsts& c, float p, float m, f
   return __fmaf_rn(c.alpha, __fdiv_rn(m, d), p1);
 }
 
+// The same update for two elements per instruction (sm_100 packed fp32: each half is the IEEE
+// result of the scalar instruction), for lanes whose 8 elements all exist and hyper-parameters in
+// the domain of the short sqrt / division sequences.
+struct UConsts2 {
+  f2 wd_mul, lerp_a, beta2, omb2, inv_bc2s, eps, alpha, mone, half, one;
+  int lerp_small;
+};
+__device__ __forceinline__ UConsts2 make_consts2(const UConsts& c) {
+  UConsts2 k;
+  k.wd_mul = f2_splat(c.wd_mul);
+  k.lerp_a = f2_splat(c.lerp_small ? c.lerp_w : -c.lerp_omw);  // fma(-d, w', g) == fma(d, -w', g)
+  k.beta2 = f2_splat(c.beta2);
+  k.omb2 = f2_splat(c.omb2);
+  k.inv_bc2s = f2_splat(c.inv_bc2s);
+  k.eps = f2_splat(c.eps);
+  k.alpha = f2_splat(c.alpha);
+  k.mone = f2_splat(-1.0f);
+  k.half = f2_splat(0.5f);
+  k.one = f2_splat(1.0f);
+  k.lerp_small = c.lerp_small;
+  return k;
+}
+// In: g, p, the old moments m0, v0 (pairs).  Out: m, v, p updated; returns nothing, maxima via am / av.
+__device__ __forceinline__ void update_pair(const UConsts2& k, f2 g, f2& p, f2 m0, f2 v0, f2& m, f2& v, float& am,
+                                            float& av) {
+  const f2 diff = f2_fma(m0, k.mone, g);                       // g - m0
+  m = f2_fma(k.lerp_a, diff, k.lerp_small ? m0 : g);           // lerp
+  v = f2_fma(k.omb2, f2_mul(g, g), f2_mul(v0, k.beta2));       // mul_ then addcmul_
+  float ma, mb, va, vb;
+  f2_unpack(m, ma, mb);
+  f2_unpack(v, va, vb);
+  am = fmaxf(am, fmaxf(fabsf(ma), fabsf(mb)));
+  av = fmaxf(av, fmaxf(va, vb));
+  // sqrt(v) as in sqrt_rn_fast
+  const f2 y = f2_pack(mufu_rsq(fmaxf(va, 1.17549435e-38f)), mufu_rsq(fmaxf(vb, 1.17549435e-38f)));
+  f2 sq = f2_mul(v, y);
+  const f2 e = f2_fma(sq, f2_mul(sq, k.mone), v);
+  sq = f2_fma(e, f2_mul(k.half, y), sq);
+  // d = sqrt(v) * (1 / bc2s) + eps; m / d as in div_rn_fast, on the negated denominator
+  const f2 d = f2_mul_then_add(sq, k.inv_bc2s, k.eps);  // two roundings, like the torch ops
+  const f2 nd = f2_mul(d, k.mone);
+  float da, db;
+  f2_unpack(d, da, db);
+  const f2 r0 = f2_pack(mufu_rcp(da), mufu_rcp(db));
+  const f2 r = f2_fma(r0, f2_fma(nd, r0, k.one), r0);
+  const f2 q = f2_mul(m, r);
+  const f2 quo = f2_fma(f2_fma(nd, q, m), r, q);
+  p = f2_fma(k.alpha, quo, f2_mul(p, k.wd_mul));               // addcdiv_ on the decayed parameter
+}
+
 // ---------------------------------------------------------------------------------------------
 // AdamW, non-fused semantics.  MM: first-moment storage, VM: second-moment storage / source.
 // ---------------------------------------------------------------------------------------------
 // Register budget: 64 per thread (4 CTAs of 256 threads per SM) except for the rank-1 variants, whose
 // index arithmetic needs more.
 template <int MM, int VM, int ND, bool W>
-__global__ void __launch_bounds__(UTMAX, (VM == LPMM_B200_STATE_RANK1_4) ? 1 : 2) unfused_adamw_kernel(const StepArgs a, const UConsts c,
+__global__ void __launch_bounds__(UTMAX, (VM == LPMM_B200_STATE_RANK1_4 && ND != 2) ? 1 : 2) unfused_adamw_kernel(const StepArgs a, const UConsts c,
                                                                const float* __restrict__ qmap_m,
                                                                const float* __restrict__ qmap_v) {
   __shared__ Maps M;
@@ -301,6 +380,7 @@ __global__ void __launch_bounds__(UTMAX, (VM == LPMM_B200_STATE_RANK1_4) ? 1 : 2
                                                          : (n + 127) / 128;
   const long long C = (VM == LPMM_B200_STATE_FACTORED) ? a.s.dim[a.s.nd - 1] : 1;
   const long long RC = (VM == LPMM_B200_STATE_FACTORED) ? C * a.s.dim[a.s.nd - 2] : 1;
+  const UConsts2 c2 = make_consts2(c);
   // a.units is a multiple of the half-warps per CTA, so every half-warp of a CTA makes the same
   // number of trips and the group reductions below may synchronise the CTA.  The two states may
   // have different padded lengths (group padding vs none): each is stored up to its own.
@@ -347,40 +427,79 @@ __global__ void __launch_bounds__(UTMAX, (VM == LPMM_B200_STATE_RANK1_4) ? 1 : 2
         px[k] = (e0 + k < n) ? a.p[e0 + k] : 0.0f;
       }
     }
+    // the update of the lane's 8 elements; FULL: all 8 exist, no per-element guards
+    auto update_lane = [&](auto full_tag) {
+      constexpr bool FULL = decltype(full_tag)::value;
+      if (FULL && VM != LPMM_B200_STATE_FACTORED && c.fast) {  // two elements per instruction
+        float* mf = reinterpret_cast<float*>(a.m);
+        float* vf = reinterpret_cast<float*>(a.v);
+        const f2 sm2 = f2_splat(sm), sv2 = f2_splat(sv);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      const long long e = e0 + k;
-      m[k] = 0.0f;
-      v[k] = 0.0f;
-      if (e < n) {
-        const float g = gx[k];
-        float m0 = 0.0f, v0 = 0.0f;
-        if (!a.first) {
-          if (MQ) m0 = __fmul_rn(M.qm[mcodes.get(k)], sm);
-          else m0 = reinterpret_cast<const float*>(a.m)[e];
-          if (VM == LPMM_B200_STATE_GROUP4) v0 = __fmul_rn(M.qv[vcodes.get(k)], sv);
-          else if (VM == LPMM_B200_STATE_RANK1_4) v0 = __fmul_rn(M.qv[vcodes.get(k)], st_old[k]);
-          else if (VM == LPMM_B200_STATE_FP32) v0 = reinterpret_cast<const float*>(a.v)[e];
+        for (int j = 0; j < 4; ++j) {
+          const int k0 = 2 * j, k1 = 2 * j + 1;
+          f2 m0 = f2_splat(0.0f), v0 = f2_splat(0.0f);
+          if (!a.first) {
+            if (MQ) m0 = f2_mul(f2_pack(M.qm[mcodes.get(k0)], M.qm[mcodes.get(k1)]), sm2);
+            else m0 = f2_pack(mf[e0 + k0], mf[e0 + k1]);
+            if (VM == LPMM_B200_STATE_GROUP4)
+              v0 = f2_mul(f2_pack(M.qv[vcodes.get(k0)], M.qv[vcodes.get(k1)]), sv2);
+            else if (VM == LPMM_B200_STATE_RANK1_4)
+              v0 = f2_mul(f2_pack(M.qv[vcodes.get(k0)], M.qv[vcodes.get(k1)]), f2_pack(st_old[k0], st_old[k1]));
+            else v0 = f2_pack(vf[e0 + k0], vf[e0 + k1]);
+          }
+          f2 pj = f2_pack(px[k0], px[k1]), mj, vj;
+          update_pair(c2, f2_pack(gx[k0], gx[k1]), pj, m0, v0, mj, vj, am, av);
+          f2_unpack(pj, px[k0], px[k1]);
+          f2_unpack(mj, m[k0], m[k1]);
+          f2_unpack(vj, v[k0], v[k1]);
+          if (MM == LPMM_B200_STATE_FP32) {
+            mf[e0 + k0] = m[k0];
+            mf[e0 + k1] = m[k1];
+          }
+          if (VM == LPMM_B200_STATE_FP32) {
+            vf[e0 + k0] = v[k0];
+            vf[e0 + k1] = v[k1];
+          }
         }
-        m[k] = lerp_m(c, m0, g);
-        if (VM == LPMM_B200_STATE_FACTORED) {
-          const float rf = __fdiv_rn(a.row[rowi], a.row_mean[bi]);
-          v[k] = __fmul_rn(rf, a.col[bi * C + cc]);
-        } else {
-          v[k] = upd_v2(c, v0, g);
+        return;
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const long long e = e0 + k;
+        m[k] = 0.0f;
+        v[k] = 0.0f;
+        if (FULL || e < n) {
+          const float g = gx[k];
+          float m0 = 0.0f, v0 = 0.0f;
+          if (!a.first) {
+            if (MQ) m0 = __fmul_rn(M.qm[mcodes.get(k)], sm);
+            else m0 = reinterpret_cast<const float*>(a.m)[e];
+            if (VM == LPMM_B200_STATE_GROUP4) v0 = __fmul_rn(M.qv[vcodes.get(k)], sv);
+            else if (VM == LPMM_B200_STATE_RANK1_4) v0 = __fmul_rn(M.qv[vcodes.get(k)], st_old[k]);
+            else if (VM == LPMM_B200_STATE_FP32) v0 = reinterpret_cast<const float*>(a.v)[e];
+          }
+          m[k] = lerp_m(c, m0, g);
+          if (VM == LPMM_B200_STATE_FACTORED) {
+            const float rf = __fdiv_rn(a.row[rowi], a.row_mean[bi]);
+            v[k] = __fmul_rn(rf, a.col[bi * C + cc]);
+          } else {
+            v[k] = upd_v2(c, v0, g);
+          }
+          px[k] = upd_param(c, px[k], m[k], v[k]);
+          am = fmaxf(am, fabsf(m[k]));
+          av = fmaxf(av, v[k]);
+          if (MM == LPMM_B200_STATE_FP32) reinterpret_cast<float*>(a.m)[e] = m[k];
+          if (VM == LPMM_B200_STATE_FP32) reinterpret_cast<float*>(a.v)[e] = v[k];
         }
-        px[k] = upd_param(c, px[k], m[k], v[k]);
-        am = fmaxf(am, fabsf(m[k]));
-        av = fmaxf(av, v[k]);
-        if (MM == LPMM_B200_STATE_FP32) reinterpret_cast<float*>(a.m)[e] = m[k];
-        if (VM == LPMM_B200_STATE_FP32) reinterpret_cast<float*>(a.v)[e] = v[k];
+        if (VM == LPMM_B200_STATE_FACTORED && ++cc == C) {
+          cc = 0;
+          ++rowi;
+          bi = rowi / a.s.dim[a.s.nd - 2];
+        }
       }
-      if (VM == LPMM_B200_STATE_FACTORED && ++cc == C) {
-        cc = 0;
-        ++rowi;
-        bi = rowi / a.s.dim[a.s.nd - 2];
-      }
-    }
+    };
+    if (full) update_lane(std::true_type{});
+    else update_lane(std::false_type{});
     if (full) {
       *reinterpret_cast<float4*>(a.p + e0) = make_float4(px[0], px[1], px[2], px[3]);
       *reinterpret_cast<float4*>(a.p + e0 + 4) = make_float4(px[4], px[5], px[6], px[7]);
@@ -414,9 +533,41 @@ __global__ void __launch_bounds__(UTMAX, (VM == LPMM_B200_STATE_RANK1_4) ? 1 : 2
     if (VM == LPMM_B200_STATE_RANK1_4) {
       Codes8<W> out;
       out.clear();
+      bool quick = full && M.linear_v;  // linear map, 8 elements, every divisor in the exact-division domain
+      if (quick) {
+        float lo = st_new[0], hi = st_new[0];
 #pragma unroll
-      for (int k = 0; k < 8; ++k)
-        out.set(k, (e0 + k < n) ? code_of<W>(M.mv, a.bits_v, __fdiv_rn(v[k], st_new[k])) : M.zero_v);
+        for (int k = 1; k < 8; ++k) {
+          lo = fminf(lo, st_new[k]);
+          hi = fmaxf(hi, st_new[k]);
+        }
+        quick = (lo >= 0x1p-60f) && (hi <= 0x1p60f);
+      }
+      if (quick) {
+        // v / scale by reciprocal + residual correction (equal to IEEE division for quotients of at
+        // least 2^-18; smaller ones are code 0 either way), then the closed-form code
+        const int top = (1 << a.bits_v) - 1;
+        const float N = (float)(top + 1);
+        const f2 N2 = f2_splat(N), k15 = f2_splat(-1.5f), one2 = f2_splat(1.0f), mone2 = f2_splat(-1.0f);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const f2 d = f2_pack(st_new[2 * j], st_new[2 * j + 1]), x = f2_pack(v[2 * j], v[2 * j + 1]);
+          const f2 nd = f2_mul(d, mone2);
+          const f2 r0 = f2_pack(mufu_rcp(st_new[2 * j]), mufu_rcp(st_new[2 * j + 1]));
+          const f2 r = f2_fma(r0, f2_fma(nd, r0, one2), r0);
+          f2 q = f2_mul(x, r);
+          q = f2_fma(f2_fma(q, nd, x), r, q);
+          float ta, tb;
+          f2_unpack(f2_fma(q, N2, k15), ta, tb);
+          const int ca = (int)__float2uint_ru(ta), cb = (int)__float2uint_ru(tb);
+          out.set(2 * j, ca < top ? ca : top);
+          out.set(2 * j + 1, cb < top ? cb : top);
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          out.set(k, (e0 + k < n) ? code_of<W>(M.mv, a.bits_v, __fdiv_rn(v[k], st_new[k])) : M.zero_v);
+      }
       if (u < a.units_v) out.store(vb);
     }
   }
