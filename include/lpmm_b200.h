@@ -251,6 +251,20 @@ int lpmm_b200_sgd_lowbit_step(float* p, const float* g, int64_t numel, void* buf
                               double momentum, double lr, double dampening, int nesterov, int maximize,
                               void* stream);
 
+/* Momentum SGD of a whole parameter list in one launch (the reference has no fused SGD: sgd.py:31-32
+ * raises for fused=True).  Arithmetic and state layout are those of lpmm_b200_sgd4bit_step, i.e. of
+ * _single_tensor_sgd4bit (lpmm/optim/sgd.py:133-187), so a buffer may be stepped by either entry
+ * point.  Per tensor: p, g, m = the momentum buffer (KIND_Q4: packed 4-bit codes in the
+ * vectorwise_quant layout of lpmm_b200_packed_len(ceil(numel/128)*128) bytes, m_scale = float[ceil(
+ * numel/128)]; KIND_FP32: float[numel]); v and v_scale are ignored.  Buffers must already be
+ * initialised (the first step of a tensor, buffer = clone of the decayed gradient, belongs to
+ * lpmm_b200_sgd4bit_step, which also writes the layout's padding).  momentum must be non-zero.
+ * [group_begin, group_end) selects a range of the list's global 128-element group sequence
+ * (group_end < 0: all), as in lpmm_b200_adamw4bit_multi_tensor. */
+int lpmm_b200_sgd4bit_multi_tensor(const lpmm_b200_tensor* tensors, int n_tensors, const float* qmap,
+                                   double weight_decay, double momentum, double lr, double dampening, int nesterov,
+                                   int maximize, int64_t group_begin, int64_t group_end, void* stream);
+
 /* Allocation-free variant of the factored step, for callers that cannot allocate device memory.
  * It has no counterpart in the reference.
  *

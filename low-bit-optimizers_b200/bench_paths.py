@@ -1,0 +1,97 @@
+"""Step times of the secondary paths of the package on a B200: the non-fused AdamW configurations
+(rank-1, group, wider codes, larger groups), the factored second moment, momentum SGD per tensor and
+fused, next to the fused AdamW step on the same shapes.  Seeded synthetic inputs.
+
+    python low-bit-optimizers_b200/bench_paths.py [--iters 10] [--only SUBSTRING]
+
+One line per case: parameters, CUDA-event time per step (after 3 warm-up steps), wall time per step,
+parameters per second.  The headline benchmark of the repository is ``bench.py``; this script is
+where the figures of ``profiles/unfused_rank1_factored_kernels.md`` come from.
+"""
+import argparse
+import os
+import sys
+import time
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+import lpmm  # noqa: E402
+from lpmm.config import CONFIG_DIR  # noqa: E402
+
+
+def gpt2_medium_shapes():
+    shapes = [(50257, 1024), (1024, 1024)]
+    for _ in range(24):
+        shapes += [(1024, 3072), (1024, 1024), (1024, 4096), (4096, 1024)] + [(1024,)] * 4
+    return shapes
+
+
+LINEAR = [(4096, 4096), (4096,)]
+RAGGED = [(3, 3, 64, 64), (1000, 768), (768, 3072), (4097,), (127,), (4096,), (50000, 1)]
+
+
+def cfg(name):
+    return os.path.join(CONFIG_DIR, name)
+
+
+def cases():
+    adamw = dict(lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01)
+    sgd = dict(lr=1e-2, momentum=0.9, weight_decay=1e-4)
+    out = [
+        ("linear4096 adamw rank-1 (default.yml)", "AdamW", LINEAR, dict(adamw, qconfig=cfg("default.yml"))),
+        ("linear4096 adamw group (qconfig=None)", "AdamW", LINEAR, dict(adamw, qconfig=None)),
+        ("linear4096 adamw fused", "AdamW", LINEAR, dict(adamw, fused=True)),
+    ]
+    for c in ("default_8b.yml", "default_5b.yml", "1st_moment_group_512.yml", "1st_moment_group_4096.yml"):
+        out.append((f"linear4096 adamw {c}", "AdamW", LINEAR, dict(adamw, qconfig=cfg(c))))
+    out += [
+        ("linear4096 sgd per tensor", "SGD", LINEAR, dict(sgd)),
+        ("linear4096 sgd fused", "SGD", LINEAR, dict(sgd, fused=True)),
+        ("gpt2-medium adamw factored", "AdamW", gpt2_medium_shapes(), dict(adamw, factor_second_moment=True)),
+        ("gpt2-medium adamw rank-1 (default.yml)", "AdamW", gpt2_medium_shapes(), dict(adamw, qconfig=cfg("default.yml"))),
+        ("gpt2-medium adamw fused", "AdamW", gpt2_medium_shapes(), dict(adamw, fused=True)),
+        ("gpt2-medium sgd per tensor", "SGD", gpt2_medium_shapes(), dict(sgd)),
+        ("gpt2-medium sgd fused", "SGD", gpt2_medium_shapes(), dict(sgd, fused=True)),
+        ("ragged adamw rank-1 (default.yml)", "AdamW", RAGGED, dict(adamw, qconfig=cfg("default.yml"))),
+    ]
+    return out
+
+
+def run(name, kind, shapes, kw, iters):
+    dev = torch.device("cuda:0")
+    torch.manual_seed(0)
+    params = [torch.nn.Parameter(torch.randn(s, device=dev) * 0.02) for s in shapes]
+    for p in params:
+        p.grad = torch.randn_like(p) * 1e-3
+    opt = getattr(lpmm.optim, kind)(params, **kw)
+    for _ in range(3):
+        opt.step()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    a.record()
+    for _ in range(iters):
+        opt.step()
+    b.record()
+    torch.cuda.synchronize()
+    wall = (time.perf_counter() - t0) / iters * 1e3
+    ms = a.elapsed_time(b) / iters
+    n = sum(p.numel() for p in params)
+    print(f"{name}: {n} params, {ms:.3f} ms/step (wall {wall:.3f}), {n / ms / 1e6:.1f} Gparam/s", flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--only", default=None)
+    a = ap.parse_args()
+    if not torch.cuda.is_available():
+        raise SystemExit("needs a CUDA device")
+    for name, kind, shapes, kw in cases():
+        if a.only is None or a.only in name:
+            run(name, kind, shapes, kw, a.iters)
+
+
+if __name__ == "__main__":
+    main()

@@ -22,36 +22,11 @@
 #include <math.h>
 
 #include "common.cuh"
+#include "multi_tensor.cuh"
 
 namespace lpmm_b200 {
 
-constexpr int MAX_TENSORS = 400;  // descriptors per launch (28.9 KB of the 32 KB parameter space)
-// One 1024-thread CTA per SM: measured faster than 2 x 512 or 3 x 256 (6.2 vs 5.9 vs 5.3 TB/s in a burst).
-constexpr unsigned PF_DIST = 1;  // the L2 prefetch runs this many of a half-warp's iterations ahead (2: same, 3: slower)
-constexpr int CTA_THREADS = 1024;
-constexpr int CTAS_PER_SM = 1;
-constexpr int HW_PER_CTA = CTA_THREADS / 16;
 constexpr size_t DYN_SMEM = 2 * LUT_ENTRIES * sizeof(LutEnt);  // one table per moment
-
-struct TDesc {
-  float* p;
-  const float* g;
-  void* m;
-  void* v;
-  float* sm;
-  float* sv;
-  long long numel;
-  long long gstart;  // first global group index of this tensor
-  int kind;          // LPMM_B200_KIND_*
-  int aligned;       // all pointers satisfy the vector-access alignment
-};
-
-struct Table {
-  int n;
-  int pad;
-  long long gtotal;  // groups in this table
-  TDesc t[MAX_TENSORS];
-};
 
 struct Consts {
   float beta1, beta2, omb1, omb2, lr, wd, eps, c1;
@@ -87,16 +62,6 @@ __device__ __forceinline__ float upd_p(const Consts& c, float p, float m, float 
   const float q = FAST ? div_rn_fast(m, d) : __fdiv_rn(m, d);
   const float u = __fmaf_rn(c.wd, p, q);
   return __fmaf_rn(-c.lr, u, p);
-}
-
-__device__ __forceinline__ float hw_max(float x, unsigned mask) {
-#pragma unroll
-  for (int o = 8; o; o >>= 1) x = fmaxf(x, __shfl_xor_sync(mask, x, o, 16));
-  return x;
-}
-
-__device__ __forceinline__ void prefetch_l2(const void* ptr) {
-  asm volatile("prefetch.global.L2 [%0];" ::"l"(ptr));
 }
 
 // Any 4-bit group, any alignment, any map: scalar accesses predicated on numel
@@ -509,8 +474,6 @@ __global__ void bias_corrections_kernel(float beta1, float beta2, float step, fl
   out[0] = __fsub_rn(1.0f, powf(beta1, step));
   out[1] = __fsqrt_rn(__fsub_rn(1.0f, powf(beta2, step)));
 }
-
-static inline int64_t groups_of(int64_t numel) { return (numel + 127) / 128; }
 
 // The short sqrt/division sequences are exact for denominators in [2^-60, 2^60]; the denominator
 // is at least eps * (1 - beta1^step) >= eps * (1 - beta1).

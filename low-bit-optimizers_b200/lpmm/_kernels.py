@@ -105,6 +105,17 @@ def adamw4bit_multi_tensor(tl, qmap_m, qmap_v, beta1, beta2, lr, weight_decay, e
                                                    _stream()))
 
 
+def sgd4bit_multi_tensor(tl, qmap, *, weight_decay, momentum, lr, dampening, nesterov, maximize, group_begin=0,
+                         group_end=-1):
+    """Momentum SGD of a ``TensorList`` (entries ``(p, g, buffer, buffer, max1 or None, None)``) in one
+    launch; buffers must be initialised."""
+    if tl.n == 0:
+        return
+    N.check(N.lib.lpmm_b200_sgd4bit_multi_tensor(tl.array, tl.n, _ptr(qmap), weight_decay, momentum, lr, dampening,
+                                                 int(bool(nesterov)), int(bool(maximize)), group_begin, group_end,
+                                                 _stream()))
+
+
 # ----------------------------------------------------------------------------------------------
 # standalone quantize / dequantize
 # ----------------------------------------------------------------------------------------------

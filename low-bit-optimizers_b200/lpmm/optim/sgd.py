@@ -2,8 +2,13 @@
 
 The momentum buffer of tensors above the threshold is stored as 4-bit codes with the first-moment
 config (``QUANT.M``: signed 'nonlinear' map, group-128 scales) in the layout of
-``vectorwise_quant``; each tensor is updated by one fused launch that reproduces the reference's
-sequence of torch operations (sgd.py:152-187).
+``vectorwise_quant``; each tensor is updated by one launch that reproduces the reference's sequence
+of torch operations (sgd.py:152-187).
+
+``fused=True``, which the reference rejects (sgd.py:31-32), is accepted here: every parameter group
+is then stepped by one multi-tensor launch with the same arithmetic and the same state layout (the
+results and the ``state_dict`` are those of ``fused=False``).  A tensor's first step, which creates
+its buffer, still goes through the per-tensor launch.
 """
 from typing import Optional
 
@@ -24,11 +29,11 @@ class SGD(LowBitOptimizer):
             raise ValueError("Invalid momentum value: {}".format(momentum))
         if weight_decay < 0.0:
             raise ValueError("Invalid weight_decay value: {}".format(weight_decay))
-        if fused is True:
-            raise ValueError("Not support fused SGD currently.")
         defaults = dict(lr=lr, momentum=momentum, weight_decay=weight_decay, dampening=dampening, nesterov=nesterov,
                         maximize=maximize)
         super().__init__(params, defaults, qconfig)
+        self._fused = bool(fused)  # not a param_group entry: the state_dict stays the reference's
+        self._lists = {}  # (group index, device) -> (pointer key, TensorList) of the multi-tensor launch
 
     def get_subqconfig(self, optimizer_state_name):
         if optimizer_state_name == "momentum_buffer":
@@ -42,7 +47,11 @@ class SGD(LowBitOptimizer):
             with torch.enable_grad():
                 loss = closure()
         md = self.get_qmetadata_by_state_name("momentum_buffer")
-        for group in self.param_groups:
+        multi_ok = (md["b"] == 4 and md["gp_sz"] == 128 and md["scale_type"] == "group"
+                    and md["round_type"] == "real-nearest")
+        for gi, group in enumerate(self.param_groups):
+            fused = self._fused and group["momentum"] != 0 and multi_ok
+            batch = {}  # device -> entries of the multi-tensor launch
             for p in group["params"]:
                 if p.grad is None:
                     continue
@@ -52,8 +61,28 @@ class SGD(LowBitOptimizer):
                 if len(state) == 0:
                     state["momentum_buffer"] = torch.zeros((), dtype=torch.float, device=p.device)
                     self.init_qstate(p, "momentum_buffer")
+                buf = state["momentum_buffer"]
+                if fused and buf.numel() > 1 and p.is_cuda and p.dtype == torch.float32 and p.is_contiguous() \
+                        and p.grad.dtype == torch.float32 and p.grad.is_contiguous():
+                    quant = self._q_enabled(p, "momentum_buffer")
+                    max1 = state["momentum_buffer_qstate"]["overhead"].get("max1") if quant else None
+                    if (quant and buf.dtype == torch.int8 and max1 is not None) or (not quant and buf.dtype == torch.float32):
+                        batch.setdefault(p.device, []).append((p, p.grad, buf, buf, max1, None))
+                        continue
                 _kernels.sgd4bit_step(p, p.grad, state, self._q_enabled(p, "momentum_buffer"), md,
                                       weight_decay=group["weight_decay"], momentum=group["momentum"], lr=group["lr"],
                                       dampening=group["dampening"], nesterov=group["nesterov"],
                                       maximize=group["maximize"])
+            for device, entries in batch.items():
+                key = tuple((e[0].data_ptr(), e[1].data_ptr(), e[2].data_ptr()) for e in entries)
+                cached = self._lists.get((gi, device))
+                if cached is None or cached[0] != key:
+                    cached = (key, _kernels.TensorList(entries))
+                    self._lists[(gi, device)] = cached
+                qmap = self.state[entries[0][0]]["momentum_buffer_qstate"]["qmap"]
+                with torch.cuda.device(device):
+                    _kernels.sgd4bit_multi_tensor(cached[1], qmap, weight_decay=group["weight_decay"],
+                                                  momentum=group["momentum"], lr=group["lr"],
+                                                  dampening=group["dampening"], nesterov=group["nesterov"],
+                                                  maximize=group["maximize"])
         return loss

