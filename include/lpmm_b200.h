@@ -239,6 +239,16 @@ int lpmm_b200_adamw4bit_unfused_step(const lpmm_b200_step_tensor* t, const float
                                      double step, void* scratch, int64_t scratch_bytes, void* stream);
 int64_t lpmm_b200_factored_scratch_bytes(const int64_t* shape, int ndim);
 
+/* The same step for n tensors in one call: tensors[i] is stepped with steps[i] (the reference keeps
+ * one step counter per parameter), all with the same maps and hyper-parameters, in order, on
+ * `stream`; `scratch` must serve the largest FACTORED tensor of the list.  It replaces the reference's
+ * per-parameter Python loop (lpmm/optim/adamw.py:332-436); results are those of n single calls. The
+ * first non-zero status ends the call (earlier tensors have been stepped). */
+int lpmm_b200_adamw4bit_unfused_step_many(const lpmm_b200_step_tensor* const* tensors, int n, const float* qmap_m,
+                                          const float* qmap_v, double beta1, double beta2, double lr,
+                                          double weight_decay, double eps, const double* steps, void* scratch,
+                                          int64_t scratch_bytes, void* stream);
+
 /* One momentum-SGD step of one tensor with the arithmetic of _single_tensor_sgd4bit
  * (lpmm/optim/sgd.py:133-187).  buf_mode FP32 or GROUP4; first != 0: the buffer is created from
  * the (decayed) gradient.  momentum == 0 ignores the buffer. */

@@ -1372,6 +1372,21 @@ extern "C" int lpmm_b200_adamw4bit_unfused_step(const lpmm_b200_step_tensor* t, 
   return LPMM_B200_OK;
 }
 
+extern "C" int lpmm_b200_adamw4bit_unfused_step_many(const lpmm_b200_step_tensor* const* tensors, int n,
+                                                     const float* qmap_m, const float* qmap_v, double beta1,
+                                                     double beta2, double lr, double weight_decay, double eps,
+                                                     const double* steps, void* scratch, int64_t scratch_bytes,
+                                                     void* stream) {
+  if (n < 0) return LPMM_B200_ERR_BAD_SIZE;
+  if (n > 0 && (!tensors || !steps)) return LPMM_B200_ERR_NULL_POINTER;
+  for (int i = 0; i < n; ++i) {
+    const int rc = lpmm_b200_adamw4bit_unfused_step(tensors[i], qmap_m, qmap_v, beta1, beta2, lr, weight_decay, eps,
+                                                    steps[i], scratch, scratch_bytes, stream);
+    if (rc != LPMM_B200_OK) return rc;
+  }
+  return LPMM_B200_OK;
+}
+
 extern "C" int lpmm_b200_sgd_lowbit_step(float* p, const float* g, int64_t numel, void* buf, float* buf_max1,
                                          int buf_mode, int bits, int64_t group_size, int first, const float* qmap,
                                          double weight_decay, double momentum, double lr, double dampening,

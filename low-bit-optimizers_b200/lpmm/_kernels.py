@@ -324,10 +324,78 @@ def _ensure_group_state(state, name, p, quantized, bits=4, gp_sz=128):
     return t, None, first
 
 
+class _StepPlan:
+    """The ``lpmm_b200_step_tensor`` of one parameter, kept between steps: as long as the parameter, its
+    state tensors and their storage are the ones the plan was built for, a step only refreshes the
+    gradient pointer and launches.  Rank-1 tensors alternate between two descriptors (the per-axis
+    maxima the codes were written with / the ones being computed swap roles every step)."""
+    __slots__ = ("p_ptr", "m", "v", "m_ptr", "v_ptr", "g_ptr", "numel", "descs", "which", "axis_sets", "oh_v",
+                 "scratch", "extra")
+
+    def matches(self, p, state):
+        m, v = state["exp_avg"], state.get("exp_avg_sq")
+        return (p.data_ptr() == self.p_ptr and m is self.m and v is self.v and m.data_ptr() == self.m_ptr
+                and (v is None or v.data_ptr() == self.v_ptr)
+                and (self.axis_sets is None or self.oh_v.get("max_dims") is self.axis_sets[self.which])
+                and all(state.get(k) is t and t.data_ptr() == ptr for k, t, ptr in self.extra))
+
+    def set_grad(self, g):
+        gp = g.data_ptr()
+        if gp != self.g_ptr:
+            if g.dtype != torch.float32 or not g.is_cuda or not g.is_contiguous() or g.numel() != self.numel:
+                return False
+            for d in self.descs:
+                d.g = gp
+            self.g_ptr = gp
+        return True
+
+
+def _make_plan(t, p, g, state, axis_sets=None, oh_v=None):
+    plan = _StepPlan()
+    plan.p_ptr, plan.g_ptr, plan.numel = p.data_ptr(), g.data_ptr(), p.numel()
+    plan.m, plan.v = state["exp_avg"], state.get("exp_avg_sq")
+    plan.m_ptr = plan.m.data_ptr()
+    plan.v_ptr = plan.v.data_ptr() if plan.v is not None else None
+    plan.axis_sets, plan.oh_v, plan.which, plan.scratch, plan.extra = axis_sets, oh_v, 0, None, ()
+    t.first = 0
+    if axis_sets is None:
+        plan.descs = [t]
+    else:
+        # descriptor k reads the maxima in axis_sets[k] and writes axis_sets[1 - k]
+        t2 = N.StepTensor()
+        ctypes.memmove(ctypes.byref(t2), ctypes.byref(t), ctypes.sizeof(t))
+        for i in range(len(axis_sets[0])):
+            t.v_max_dims_old[i], t.v_max_dims_new[i] = axis_sets[0][i].data_ptr(), axis_sets[1][i].data_ptr()
+            t2.v_max_dims_old[i], t2.v_max_dims_new[i] = axis_sets[1][i].data_ptr(), axis_sets[0][i].data_ptr()
+        plan.descs = [t, t2]
+    return plan
+
+
 def adamw4bit_unfused_step(p, g, state, m_quant, v_quant, md_m, md_v, spare, *, beta1, beta2, lr, weight_decay, eps,
-                           step):
+                           step, stream=None):
     """``spare`` is a dict owned by the optimizer (not part of its state) that keeps the second set
-    of per-axis maxima a rank-1 tensor alternates with."""
+    of per-axis maxima a rank-1 tensor alternates with, and the descriptor cached between steps.
+    ``stream``: raw handle of torch's current stream when the caller has already looked it up and
+    ``p``'s device is the current device (saves both look-ups per tensor)."""
+    plan = spare.get("plan")
+    if plan is not None:
+        if plan.matches(p, state) and plan.set_grad(g):
+            qm = state["exp_avg_qstate"]["qmap"]
+            qv = state["exp_avg_sq_qstate"]["qmap"]
+            if stream is not None:
+                N.check(N.lib.lpmm_b200_adamw4bit_unfused_step(ctypes.byref(plan.descs[plan.which]), _ptr(qm), _ptr(qv),
+                                                               beta1, beta2, lr, weight_decay, eps, step, None, 0,
+                                                               _vp(stream)))
+            else:
+                with torch.cuda.device(p.device):
+                    N.check(N.lib.lpmm_b200_adamw4bit_unfused_step(ctypes.byref(plan.descs[plan.which]), _ptr(qm),
+                                                                   _ptr(qv), beta1, beta2, lr, weight_decay, eps, step,
+                                                                   None, 0, _stream()))
+            if plan.axis_sets is not None:  # the freshly written maxima become the state's, the old set the spare
+                plan.which ^= 1
+                plan.oh_v["max_dims"], spare["max_dims"] = plan.axis_sets[plan.which], plan.axis_sets[plan.which ^ 1]
+            return
+        del spare["plan"]
     _check_param_grad(p, g)
     if m_quant:
         _check_group_md(md_m, "first moment")
@@ -352,6 +420,7 @@ def adamw4bit_unfused_step(p, g, state, m_quant, v_quant, md_m, md_v, spare, *, 
     t.m, t.m_max1 = m.data_ptr(), (m_max1.data_ptr() if m_max1 is not None else None)
     rank1 = v_quant and md_v["scale_type"] == "rank1" and p.dim() >= 2
     oh_v = state["exp_avg_sq_qstate"]["overhead"]
+    axis_sets = None
     if rank1:
         v = state["exp_avg_sq"]
         first_v = v.numel() <= 1
@@ -365,8 +434,10 @@ def adamw4bit_unfused_step(p, g, state, m_quant, v_quant, md_m, md_v, spare, *, 
             t.v_max_dims_old[i] = old[i].data_ptr()
             t.v_max_dims_new[i] = new[i].data_ptr()
         t.v_mode, t.v = N.STATE_RANK1_4, v.data_ptr()
-        oh_v["max_dims"], spare["max_dims"] = new, list(old)
+        new, old = list(new), list(old)
+        oh_v["max_dims"], spare["max_dims"] = new, old
         oh_v.update(dim=p.dim(), max1=None, scaled_shape=p.shape, dtype=p.dtype, stride=p.stride())
+        axis_sets = [new, old]  # after this step the state's maxima are `new`
     else:
         v, v_max1, first_v = _ensure_group_state(state, "exp_avg_sq", p, v_quant, md_v["b"], md_v["gp_sz"])
         if v_quant and md_v["scale_type"] == "rank1":
@@ -381,9 +452,31 @@ def adamw4bit_unfused_step(p, g, state, m_quant, v_quant, md_m, md_v, spare, *, 
     with torch.cuda.device(p.device):
         N.check(N.lib.lpmm_b200_adamw4bit_unfused_step(ctypes.byref(t), _ptr(qm), _ptr(qv), beta1, beta2, lr,
                                                        weight_decay, eps, step, None, 0, _stream()))
+    spare["plan"] = _make_plan(t, p, g, state, axis_sets, oh_v if rank1 else None)
 
 
-def adamw4bit_factored_step(p, g, state, m_quant, md_m, *, beta1, beta2, lr, weight_decay, eps, step):
+def adamw4bit_unfused_step_many(ptrs, n, qm, qv, steps, scratch_need, device, *, beta1, beta2, lr, weight_decay, eps):
+    """``ptrs``: ctypes array of n addresses of ``lpmm_b200_step_tensor`` descriptors (kept alive and up
+    to date by the caller), ``steps``: ctypes array of n doubles.  The caller guarantees that ``device``
+    is the current device."""
+    scratch = _scratch_for(device, scratch_need) if scratch_need else None
+    N.check(N.lib.lpmm_b200_adamw4bit_unfused_step_many(ptrs, n, _ptr(qm), _ptr(qv), beta1, beta2, lr, weight_decay, eps,
+                                                        steps, _ptr(scratch), scratch.numel() if scratch is not None else 0,
+                                                        _stream()))
+
+
+def adamw4bit_factored_step(p, g, state, m_quant, md_m, *, beta1, beta2, lr, weight_decay, eps, step, spare=None):
+    plan = spare.get("plan") if spare is not None else None
+    if plan is not None:
+        if plan.matches(p, state) and plan.set_grad(g):
+            scratch = _scratch_for(p.device, plan.scratch)
+            with torch.cuda.device(p.device):
+                N.check(N.lib.lpmm_b200_adamw4bit_unfused_step(ctypes.byref(plan.descs[0]),
+                                                               _ptr(state["exp_avg_qstate"]["qmap"]), None, beta1, beta2,
+                                                               lr, weight_decay, eps, step, _ptr(scratch),
+                                                               scratch.numel(), _stream()))
+            return
+        del spare["plan"]
     _check_param_grad(p, g)
     if m_quant:
         _check_group_md(md_m, "first moment")
@@ -410,6 +503,12 @@ def adamw4bit_factored_step(p, g, state, m_quant, md_m, *, beta1, beta2, lr, wei
     with torch.cuda.device(p.device):
         N.check(N.lib.lpmm_b200_adamw4bit_unfused_step(ctypes.byref(t), _ptr(qm), None, beta1, beta2, lr, weight_decay,
                                                        eps, step, _ptr(scratch), scratch.numel(), _stream()))
+    if spare is not None:
+        plan = _make_plan(t, p, g, state)
+        plan.scratch = need
+        # the accumulators are part of what the descriptor points at
+        plan.extra = (("exp_avg_sq_row", row, row.data_ptr()), ("exp_avg_sq_col", col, col.data_ptr()))
+        spare["plan"] = plan
 
 
 def sgd4bit_step(p, g, state, quant, md, *, weight_decay, momentum, lr, dampening, nesterov, maximize):

@@ -43,12 +43,14 @@ class AdamW(LowBitOptimizer):
         self._lists = {}  # cached descriptor arrays of the multi-tensor step, per param group
         self._spare = {}  # per-parameter buffers that are not optimizer state (alternate rank-1 maxima)
         self._plans = {}  # fused groups: everything needed to repeat the last launch
+        self._batches = {}  # non-fused groups: the descriptors of all tensors, stepped by one library call
 
     def __setstate__(self, state):
         super().__setstate__(state)
         self._lists = {}
         self._spare = {}
         self._plans = {}
+        self._batches = {}
         for group in self.param_groups:
             group.setdefault("fused", None)
         values = list(self.state.values())
@@ -103,7 +105,7 @@ class AdamW(LowBitOptimizer):
             if group["fused"]:
                 self._step_fused(gi, group, params)
             else:
-                self._step_single(group, params)
+                self._step_single(gi, group, params)
         return loss
 
     # ---- fused=True ---------------------------------------------------------------------------
@@ -225,10 +227,85 @@ class AdamW(LowBitOptimizer):
         return cached[1]
 
     # ---- fused=False --------------------------------------------------------------------------
-    def _step_single(self, group, params):
+    def _step_single(self, gi, group, params):
+        if self._step_single_batched(gi, group, params):
+            return
+        self._step_single_each(group, params)
+        self._prepare_batch(gi, params)
+
+    def _prepare_batch(self, gi, params):
+        """After a per-tensor step: if every tensor now has a cached descriptor, on the current device and
+        with the same two maps, keep them as one array for ``lpmm_b200_adamw4bit_unfused_step_many``."""
+        import ctypes
+        if not torch.cuda.is_available():
+            return
+        cur = torch.cuda.current_device()
+        spares, plans, states, maps = [], [], [], set()
+        for p in params:
+            sp = self._spare.get(id(p))
+            plan = sp.get("plan") if sp else None
+            st = self.state[p]
+            if plan is None or not p.is_cuda or p.device.index != cur or not plan.matches(p, st):
+                return
+            maps.add((st["exp_avg_qstate"]["qmap"].data_ptr(), st["exp_avg_sq_qstate"]["qmap"].data_ptr()))
+            spares.append(sp)
+            plans.append(plan)
+            states.append(st)
+        if len(maps) != 1:
+            return
+        n = len(params)
+        ptrs = (ctypes.c_void_p * n)()
+        addrs = []
+        for i, plan in enumerate(plans):
+            a = tuple(ctypes.addressof(d) for d in plan.descs)
+            addrs.append(a)
+            ptrs[i] = a[plan.which if len(a) > 1 else 0]
+        self._batches[gi] = dict(params=list(params), plans=plans, states=states, spares=spares, ptrs=ptrs, addrs=addrs,
+                                 steps=(ctypes.c_double * n)(), device=cur, qm=states[0]["exp_avg_qstate"]["qmap"],
+                                 qv=states[0]["exp_avg_sq_qstate"]["qmap"],
+                                 scratch=max([pl.scratch or 0 for pl in plans] + [0]))
+
+    def _step_single_batched(self, gi, group, params):
+        """All tensors of a non-fused group through one library call.  Returns False (after dropping the
+        cached batch) whenever a tensor, a state or a storage is not the one the batch was built for."""
+        b = self._batches.get(gi)
+        if b is None:
+            return False
+        plans, states = b["plans"], b["states"]
+        ok = len(params) == len(plans) and torch.cuda.current_device() == b["device"]
+        if ok:
+            bp = b["params"]
+            for i, p in enumerate(params):
+                if p is not bp[i] or not plans[i].matches(p, states[i]) or not plans[i].set_grad(p.grad):
+                    ok = False
+                    break
+        if not ok:
+            del self._batches[gi]
+            return False
+        steps, ptrs, addrs = b["steps"], b["ptrs"], b["addrs"]
+        for i, st in enumerate(states):
+            st["step"] += 1
+            steps[i] = st["step"].item()
+        beta1, beta2 = group["betas"]
+        _kernels.adamw4bit_unfused_step_many(ptrs, len(plans), b["qm"], b["qv"], steps, b["scratch"], params[0].device,
+                                             beta1=beta1, beta2=beta2, lr=group["lr"],
+                                             weight_decay=group["weight_decay"], eps=group["eps"])
+        for i, plan in enumerate(plans):
+            if plan.axis_sets is not None:  # rank-1: the freshly written maxima become the state's
+                plan.which ^= 1
+                plan.oh_v["max_dims"] = plan.axis_sets[plan.which]
+                b["spares"][i]["max_dims"] = plan.axis_sets[plan.which ^ 1]
+                ptrs[i] = addrs[i][plan.which]
+        return True
+
+    def _step_single_each(self, group, params):
         beta1, beta2 = group["betas"]
         md_m = self.get_qmetadata_by_state_name("exp_avg")
         md_v = self.get_qmetadata_by_state_name("exp_avg_sq")
+        # torch's current device and stream, looked up once for all tensors that live on that device
+        cur = torch.cuda.current_device() if torch.cuda.is_available() else -1
+        handle = torch.cuda.current_stream().cuda_stream if cur >= 0 else None
+        lr, wd, eps = group["lr"], group["weight_decay"], group["eps"]
         for p in params:
             state = self.state[p]
             factored, _ = self._get_options(group, p.shape)
@@ -239,12 +316,12 @@ class AdamW(LowBitOptimizer):
             _kernels.adamw4bit_unfused_step(
                 p, p.grad, state, self._q_enabled(p, "exp_avg"), self._q_enabled(p, "exp_avg_sq"), md_m, md_v,
                 self._spare.setdefault(id(p), {}),
-                beta1=beta1, beta2=beta2, lr=group["lr"], weight_decay=group["weight_decay"], eps=group["eps"],
-                step=state["step"].item())
+                beta1=beta1, beta2=beta2, lr=lr, weight_decay=wd, eps=eps, step=state["step"].item(),
+                stream=handle if (p.is_cuda and p.device.index == cur) else None)
 
     def _factored_update(self, group, p, state):
         beta1, beta2 = group["betas"]
         _kernels.adamw4bit_factored_step(
             p, p.grad, state, self._q_enabled(p, "exp_avg"), self.get_qmetadata_by_state_name("exp_avg"),
             beta1=beta1, beta2=beta2, lr=group["lr"], weight_decay=group["weight_decay"], eps=group["eps"],
-            step=state["step"].item())
+            step=state["step"].item(), spare=self._spare.setdefault(id(p), {}))
