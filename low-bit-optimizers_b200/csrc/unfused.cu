@@ -20,11 +20,13 @@
 // 5 to 8 bits store one code per byte ("wide", template parameter W).  A group of 128 elements is
 // one half-warp; larger groups (256 ... 4096, powers of two) are 2 ... 32 adjacent half-warps of one
 // CTA whose maxima are combined through shared memory.
+#include <cooperative_groups.h>
 #include <math.h>
 
 #include <type_traits>
 
 #include "common.cuh"
+#include "multi_tensor.cuh"
 
 namespace lpmm_b200 {
 
@@ -305,6 +307,36 @@ __device__ __forceinline__ float upd_param(const UConsts& c, float p, float m, f
   return __fmaf_rn(c.alpha, __fdiv_rn(m, d), p1);
 }
 
+// All fp32-state tensors of a list (the numel <= threshold fallback: biases, norms) in one launch.
+// Each is a few hundred elements, so one launch per tensor is pure launch latency.  A half-warp
+// takes 128 consecutive elements of the list's global group sequence; arithmetic as above.
+__global__ void __launch_bounds__(UT) unfused_fp32_multi_kernel(const __grid_constant__ Table tab, const UConsts c) {
+  const int l16 = threadIdx.x & 15;
+  long long gi = (long long)blockIdx.x * (UT / 16) + (threadIdx.x >> 4);
+  const long long stride = (long long)gridDim.x * (UT / 16);
+  for (int ti = 0; ti < tab.n; ++ti) {
+    const TDesc& t = tab.t[ti];
+    const long long tend = (ti + 1 < tab.n) ? tab.t[ti + 1].gstart : tab.gtotal;
+    float* mp = reinterpret_cast<float*>(t.m);
+    float* vp = reinterpret_cast<float*>(t.v);
+    for (; gi < tend; gi += stride) {
+      const long long e0 = (gi - t.gstart) * 128 + l16 * 8;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const long long e = e0 + k;
+        if (e < t.numel) {
+          const float g = t.g[e];
+          const float m = lerp_m(c, mp[e], g);
+          const float v = upd_v2(c, vp[e], g);
+          mp[e] = m;
+          vp[e] = v;
+          t.p[e] = upd_param(c, t.p[e], m, v);
+        }
+      }
+    }
+  }
+}
+
 // The same update for two elements per instruction (sm_100 packed fp32: each half is the IEEE
 // result of the scalar instruction), for lanes whose 8 elements all exist and hyper-parameters in
 // the domain of the short sqrt / division sequences.
@@ -366,9 +398,9 @@ __global__ void __launch_bounds__(UTMAX, (VM == LPMM_B200_STATE_RANK1_4 && ND !=
                                                                const float* __restrict__ qmap_v) {
   __shared__ Maps M;
   __shared__ float red[UTMAX / 16];
-  load_maps<W>(M, qmap_m, qmap_v, a.bits_m, a.bits_v);
   constexpr bool MQ = (MM == LPMM_B200_STATE_GROUP4);
   constexpr bool VQ = (VM == LPMM_B200_STATE_GROUP4 || VM == LPMM_B200_STATE_RANK1_4);
+  if (MQ || VQ) load_maps<W>(M, qmap_m, qmap_v, a.bits_m, a.bits_v);
   const int l16 = threadIdx.x & 15;
   const int hw = threadIdx.x >> 4, hw_per_cta = blockDim.x >> 4;
   const unsigned hmask = 0xFFFFu << (threadIdx.x & 16);
@@ -656,12 +688,20 @@ __global__ void __launch_bounds__(UT) rank1_stats_kernel(const StepArgs a, const
 }
 
 // The same statistics pass for a matrix whose row length is a multiple of 8: a thread keeps its 8
-// columns for all the rows of its CTA, so column maxima live in registers and reach global memory
-// once per CTA; a row's maximum is reduced across the warp and costs one atomic per warp and row.
+// columns for all the rows of its CTA, so column maxima live in registers; a row's maximum is reduced
+// across the warp and costs one atomic per warp and row.  Atomics on one 128-byte line serialise (about
+// 2 ns each, measured as ~35 us for a 1024 x 1024 matrix cut into 512 row slices), so the column maxima
+// of the CTAs of a thread-block cluster (stacked along the rows; the cluster size is a launch
+// attribute) are first combined through distributed shared memory and only the cluster's first CTA
+// issues atomics.  The host asks for clusters of STATS_CLUSTER when the row slices are thin (many
+// CTAs per column, little work each) and for none when they are thick.
+constexpr int STATS_CLUSTER = 8;
+constexpr int STATS_CLUSTER_MAX_ROWS = 8;  // rows per CTA up to which clusters pay (4096 x 4096 has 12: measured slower)
 template <bool W>
-__global__ void __launch_bounds__(UT) rank1_stats2d_kernel(const StepArgs a, const UConsts c,
-                                                            const float* __restrict__ qmap_v, int rows_per_cta) {
+__global__ void __launch_bounds__(UT)
+rank1_stats2d_kernel(const StepArgs a, const UConsts c, const float* __restrict__ qmap_v, int rows_per_cta) {
   __shared__ Maps M;
+  __shared__ float colbuf[8 * UT];  // this CTA's column maxima, [k][thread]
   load_maps<W>(M, nullptr, qmap_v, 4, a.bits_v);
   const long long R = a.s.dim[0], C = a.s.dim[1];
   const long long c0 = ((long long)blockIdx.x * UT + threadIdx.x) * 8;
@@ -699,10 +739,22 @@ __global__ void __launch_bounds__(UT) rank1_stats2d_kernel(const StepArgs a, con
     for (int o = 16; o; o >>= 1) row_max = fmaxf(row_max, __shfl_xor_sync(0xffffffffu, row_max, o));
     if ((threadIdx.x & 31) == 0) atomic_max_nonneg(a.v_new[0] + r, row_max);
   }
-  if (active) {
+  // every CTA of the cluster reaches both barriers (CTAs past the last row have an empty row loop)
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
+#pragma unroll
+  for (int k = 0; k < 8; ++k) colbuf[k * UT + threadIdx.x] = col_max[k];
+  cluster.sync();
+  if (cluster.block_rank() == 0 && active) {
+    for (unsigned r = 1; r < cluster.num_blocks(); ++r) {
+      const float* peer = cluster.map_shared_rank(colbuf, r);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) col_max[k] = fmaxf(col_max[k], peer[k * UT + threadIdx.x]);
+    }
 #pragma unroll
     for (int k = 0; k < 8; ++k) atomic_max_nonneg(a.v_new[1] + c0 + k, col_max[k]);
   }
+  cluster.sync();  // peers keep their shared memory until the first CTA has read it
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1331,11 +1383,27 @@ extern "C" int lpmm_b200_adamw4bit_unfused_step(const lpmm_b200_step_tensor* t, 
       const long long col_ctas = (C / 8 + UT - 1) / UT;
       long long row_ctas = ((long long)num_sms() * 6 + col_ctas - 1) / col_ctas;
       if (row_ctas > R) row_ctas = R;
-      if (row_ctas > 65535) row_ctas = 65535;
+      if (row_ctas > 65528) row_ctas = 65528;  // grid.y limit, rounded down to whole clusters
       const int rows_per_cta = (int)((R + row_ctas - 1) / row_ctas);
       row_ctas = (R + rows_per_cta - 1) / rows_per_cta;
-      LPMM_DISPATCH_W(lv.wide, (rank1_stats2d_kernel<W><<<dim3((unsigned)col_ctas, (unsigned)row_ctas), UT, 0, st>>>(
-                                   a, c, qmap_v, rows_per_cta)));
+      if (rows_per_cta <= STATS_CLUSTER_MAX_ROWS) {
+        row_ctas = (row_ctas + STATS_CLUSTER - 1) / STATS_CLUSTER * STATS_CLUSTER;  // whole clusters; extra CTAs have no rows
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)col_ctas, (unsigned)row_ctas);
+        cfg.blockDim = dim3(UT);
+        cfg.stream = st;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 1;
+        attr.val.clusterDim.y = STATS_CLUSTER;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        LPMM_DISPATCH_W(lv.wide, LPMM_CUDA_TRY(cudaLaunchKernelEx(&cfg, rank1_stats2d_kernel<W>, a, c, qmap_v, rows_per_cta)));
+      } else {
+        LPMM_DISPATCH_W(lv.wide, (rank1_stats2d_kernel<W><<<dim3((unsigned)col_ctas, (unsigned)row_ctas), UT, 0, st>>>(
+                                     a, c, qmap_v, rows_per_cta)));
+      }
     } else {
       LPMM_DISPATCH_W(lv.wide, LPMM_DISPATCH_ND(t->ndim, (rank1_stats_kernel<ND, W><<<grid_for((a.n + 7) / 8, UT, 3), UT,
                                                                                     0, st>>>(a, c, qmap_v))));
@@ -1379,12 +1447,54 @@ extern "C" int lpmm_b200_adamw4bit_unfused_step_many(const lpmm_b200_step_tensor
                                                      void* stream) {
   if (n < 0) return LPMM_B200_ERR_BAD_SIZE;
   if (n > 0 && (!tensors || !steps)) return LPMM_B200_ERR_NULL_POINTER;
+  // fp32-state tensors that share a step count go into one launch (per window of MAX_TENSORS); all
+  // others are stepped one by one.  Tensors are independent, so the order of the launches is free.
+  static thread_local Table tab;
+  int cnt = 0;
+  int64_t groups = 0;
+  double batch_step = 0.0;
+  auto flush = [&]() -> int {
+    if (cnt == 0) return LPMM_B200_OK;
+    tab.n = cnt;
+    tab.pad = 0;
+    tab.gtotal = groups;
+    const UConsts c = make_consts(beta1, beta2, lr, weight_decay, eps, batch_step);
+    unfused_fp32_multi_kernel<<<grid_for(groups, UT / 16), UT, 0, (cudaStream_t)stream>>>(tab, c);
+    cnt = 0;
+    groups = 0;
+    LPMM_CUDA_TRY(cudaGetLastError());
+    return LPMM_B200_OK;
+  };
   for (int i = 0; i < n; ++i) {
-    const int rc = lpmm_b200_adamw4bit_unfused_step(tensors[i], qmap_m, qmap_v, beta1, beta2, lr, weight_decay, eps,
-                                                    steps[i], scratch, scratch_bytes, stream);
+    const lpmm_b200_step_tensor* t = tensors[i];
+    if (!t) return LPMM_B200_ERR_NULL_POINTER;
+    const bool plain = t->m_mode == LPMM_B200_STATE_FP32 && t->v_mode == LPMM_B200_STATE_FP32 && !t->first &&
+                       t->numel > 0 && t->p && t->g && t->m && t->v;
+    if (plain && (cnt == 0 || steps[i] == batch_step)) {
+      if (cnt == MAX_TENSORS) {
+        const int rc = flush();
+        if (rc != LPMM_B200_OK) return rc;
+      }
+      batch_step = steps[i];
+      TDesc& d = tab.t[cnt++];
+      d.p = t->p;
+      d.g = t->g;
+      d.m = t->m;
+      d.v = t->v;
+      d.sm = nullptr;
+      d.sv = nullptr;
+      d.numel = t->numel;
+      d.gstart = groups;
+      d.kind = LPMM_B200_KIND_FP32;
+      d.aligned = 0;
+      groups += groups_of(t->numel);
+      continue;
+    }
+    const int rc = lpmm_b200_adamw4bit_unfused_step(t, qmap_m, qmap_v, beta1, beta2, lr, weight_decay, eps, steps[i],
+                                                    scratch, scratch_bytes, stream);
     if (rc != LPMM_B200_OK) return rc;
   }
-  return LPMM_B200_OK;
+  return flush();
 }
 
 extern "C" int lpmm_b200_sgd_lowbit_step(float* p, const float* g, int64_t numel, void* buf, float* buf_max1,
