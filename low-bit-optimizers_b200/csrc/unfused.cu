@@ -23,6 +23,7 @@
 #include <cooperative_groups.h>
 #include <math.h>
 
+#include <mutex>
 #include <type_traits>
 
 #include "common.cuh"
@@ -1440,6 +1441,36 @@ extern "C" int lpmm_b200_adamw4bit_unfused_step(const lpmm_b200_step_tensor* t, 
   return LPMM_B200_OK;
 }
 
+// Side streams of lpmm_b200_adamw4bit_unfused_step_many: the tensors of a list are independent and most
+// of them are small (a few launches of a few microseconds each, one waiting for the other), so their
+// launch chains are spread over SIDE_STREAMS streams that fork from the caller's stream and join it
+// again before the call returns; to the caller everything is ordered on `stream` as before.  One set
+// per device, created on first use and kept for the life of the process; a mutex serialises callers
+// of one device while they enqueue (the events are shared).
+constexpr int SIDE_STREAMS = 4;
+struct SideStreams {
+  cudaStream_t s[SIDE_STREAMS];
+  cudaEvent_t fork, join[SIDE_STREAMS];
+  int state;  // 0: not tried, 1: ready, -1: could not be created (single-stream operation)
+  std::mutex mu;
+};
+static SideStreams* side_streams_of_current_device() {
+  static SideStreams all[64];
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  SideStreams& x = all[dev];
+  std::lock_guard<std::mutex> lock(x.mu);
+  if (x.state == 0) {
+    bool ok = cudaEventCreateWithFlags(&x.fork, cudaEventDisableTiming) == cudaSuccess;
+    for (int k = 0; ok && k < SIDE_STREAMS; ++k)
+      ok = cudaStreamCreateWithFlags(&x.s[k], cudaStreamNonBlocking) == cudaSuccess &&
+           cudaEventCreateWithFlags(&x.join[k], cudaEventDisableTiming) == cudaSuccess;
+    if (!ok) cudaGetLastError();  // leave no sticky "last error" behind
+    x.state = ok ? 1 : -1;
+  }
+  return x.state == 1 ? &x : nullptr;
+}
+
 extern "C" int lpmm_b200_adamw4bit_unfused_step_many(const lpmm_b200_step_tensor* const* tensors, int n,
                                                      const float* qmap_m, const float* qmap_v, double beta1,
                                                      double beta2, double lr, double weight_decay, double eps,
@@ -1447,6 +1478,42 @@ extern "C" int lpmm_b200_adamw4bit_unfused_step_many(const lpmm_b200_step_tensor
                                                      void* stream) {
   if (n < 0) return LPMM_B200_ERR_BAD_SIZE;
   if (n > 0 && (!tensors || !steps)) return LPMM_B200_ERR_NULL_POINTER;
+  cudaStream_t user = (cudaStream_t)stream;
+  // which tensors go into the shared fp32 launch, how many need launches of their own, and the
+  // largest scratch need among the factored ones
+  auto is_plain = [&](const lpmm_b200_step_tensor* t) {
+    return t->m_mode == LPMM_B200_STATE_FP32 && t->v_mode == LPMM_B200_STATE_FP32 && !t->first && t->numel > 0 &&
+           t->p && t->g && t->m && t->v;
+  };
+  int own = 0;
+  int64_t max_need = 0;
+  for (int i = 0; i < n; ++i) {
+    if (!tensors[i]) return LPMM_B200_ERR_NULL_POINTER;
+    if (is_plain(tensors[i])) continue;
+    ++own;
+    if (tensors[i]->v_mode == LPMM_B200_STATE_FACTORED) {
+      const int64_t need = lpmm_b200_factored_scratch_bytes(tensors[i]->shape, tensors[i]->ndim);
+      if (need > max_need) max_need = need;
+    }
+  }
+  SideStreams* side = nullptr;
+  if (own >= 2) {
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(user, &cap) == cudaSuccess && cap == cudaStreamCaptureStatusNone)
+      side = side_streams_of_current_device();
+    else
+      cudaGetLastError();
+  }
+  std::unique_lock<std::mutex> lock;
+  if (side) {
+    lock = std::unique_lock<std::mutex>(side->mu);
+    LPMM_CUDA_TRY(cudaEventRecord(side->fork, user));
+    for (int k = 0; k < SIDE_STREAMS; ++k) LPMM_CUDA_TRY(cudaStreamWaitEvent(side->s[k], side->fork, 0));
+  }
+  // factored tensors share `scratch`: each side stream gets its own slice when the largest need fits
+  // one, otherwise all factored tensors stay on one stream and use all of it
+  const int64_t slice = side ? (scratch_bytes / SIDE_STREAMS) & ~(int64_t)255 : 0;
+  const bool sliced = side && scratch && max_need <= slice;
   // fp32-state tensors that share a step count go into one launch (per window of MAX_TENSORS); all
   // others are stepped one by one.  Tensors are independent, so the order of the launches is free.
   static thread_local Table tab;
@@ -1459,21 +1526,20 @@ extern "C" int lpmm_b200_adamw4bit_unfused_step_many(const lpmm_b200_step_tensor
     tab.pad = 0;
     tab.gtotal = groups;
     const UConsts c = make_consts(beta1, beta2, lr, weight_decay, eps, batch_step);
-    unfused_fp32_multi_kernel<<<grid_for(groups, UT / 16), UT, 0, (cudaStream_t)stream>>>(tab, c);
+    unfused_fp32_multi_kernel<<<grid_for(groups, UT / 16), UT, 0, user>>>(tab, c);
     cnt = 0;
     groups = 0;
     LPMM_CUDA_TRY(cudaGetLastError());
     return LPMM_B200_OK;
   };
-  for (int i = 0; i < n; ++i) {
+  int rr = 0;  // round-robin position
+  int rc = LPMM_B200_OK;
+  for (int i = 0; i < n && rc == LPMM_B200_OK; ++i) {
     const lpmm_b200_step_tensor* t = tensors[i];
-    if (!t) return LPMM_B200_ERR_NULL_POINTER;
-    const bool plain = t->m_mode == LPMM_B200_STATE_FP32 && t->v_mode == LPMM_B200_STATE_FP32 && !t->first &&
-                       t->numel > 0 && t->p && t->g && t->m && t->v;
-    if (plain && (cnt == 0 || steps[i] == batch_step)) {
+    if (is_plain(t) && (cnt == 0 || steps[i] == batch_step)) {
       if (cnt == MAX_TENSORS) {
-        const int rc = flush();
-        if (rc != LPMM_B200_OK) return rc;
+        rc = flush();
+        if (rc != LPMM_B200_OK) break;
       }
       batch_step = steps[i];
       TDesc& d = tab.t[cnt++];
@@ -1490,11 +1556,34 @@ extern "C" int lpmm_b200_adamw4bit_unfused_step_many(const lpmm_b200_step_tensor
       groups += groups_of(t->numel);
       continue;
     }
-    const int rc = lpmm_b200_adamw4bit_unfused_step(t, qmap_m, qmap_v, beta1, beta2, lr, weight_decay, eps, steps[i],
-                                                    scratch, scratch_bytes, stream);
-    if (rc != LPMM_B200_OK) return rc;
+    cudaStream_t st = user;
+    void* sc = scratch;
+    int64_t sc_bytes = scratch_bytes;
+    if (side) {
+      int k = rr++ % SIDE_STREAMS;
+      if (t->v_mode == LPMM_B200_STATE_FACTORED) {
+        if (sliced) {
+          sc = static_cast<char*>(scratch) + (int64_t)k * slice;
+          sc_bytes = slice;
+        } else {
+          k = 0;
+        }
+      }
+      st = side->s[k];
+    }
+    rc = lpmm_b200_adamw4bit_unfused_step(t, qmap_m, qmap_v, beta1, beta2, lr, weight_decay, eps, steps[i], sc, sc_bytes,
+                                          st);
   }
-  return flush();
+  if (rc == LPMM_B200_OK) rc = flush();
+  if (side) {  // join even after an error: the caller's stream must not run ahead of what was enqueued
+    for (int k = 0; k < SIDE_STREAMS; ++k) {
+      if (cudaEventRecord(side->join[k], side->s[k]) != cudaSuccess ||
+          cudaStreamWaitEvent(user, side->join[k], 0) != cudaSuccess) {
+        if (rc == LPMM_B200_OK) rc = set_cuda_error(cudaGetLastError());
+      }
+    }
+  }
+  return rc;
 }
 
 extern "C" int lpmm_b200_sgd_lowbit_step(float* p, const float* g, int64_t numel, void* buf, float* buf_max1,

@@ -46,6 +46,24 @@ def test_argument_validation_without_a_gpu():
     tiles = (100 + 63) // 64
     assert lib.lpmm_b200_factored_scratch_bytes(shape, 3) == 4 * (2 * tiles * 64 + 2)
     assert lib.lpmm_b200_factored_scratch_bytes(shape, 1) == -2
+    # code widths and group sizes
+    assert lib.lpmm_b200_packed_len_bits(2049, 4) == 2049 and lib.lpmm_b200_packed_len_bits(2049, 8) == 4097
+    assert lib.lpmm_b200_packed_len_bits(10, 3) == -5 and lib.lpmm_b200_packed_len_bits(10, 9) == -3
+    assert lib.lpmm_b200_quant_group(None, 10, None, 4, 100, None, None, None) == -5      # not a power of two
+    assert lib.lpmm_b200_quant_group(None, 10, None, 4, 8192, None, None, None) == -5     # larger than 4096
+    assert lib.lpmm_b200_quant_group(None, 10, None, 4, 256, None, None, None) == -1      # null pointers
+    assert lib.lpmm_b200_pack_nonlinear(None, 7, None, 8, None, None) == -1               # odd counts are fine for bytes
+    # list entry points
+    assert lib.lpmm_b200_adamw4bit_unfused_step_many(None, -1, None, None, 0.9, 0.999, 1e-3, 0.0, 1e-8, None, None, 0,
+                                                     None) == -2
+    assert lib.lpmm_b200_adamw4bit_unfused_step_many(None, 2, None, None, 0.9, 0.999, 1e-3, 0.0, 1e-8, None, None, 0,
+                                                     None) == -1
+    assert lib.lpmm_b200_adamw4bit_unfused_step_many(None, 0, None, None, 0.9, 0.999, 1e-3, 0.0, 1e-8, None, None, 0,
+                                                     None) == 0
+    arr[0].kind = N.KIND_Q4
+    assert lib.lpmm_b200_sgd4bit_multi_tensor(arr, 2, None, 0.0, 0.0, 1e-2, 0.0, 0, 0, 0, -1, None) == -3  # momentum 0
+    assert lib.lpmm_b200_sgd4bit_multi_tensor(arr, 2, None, 0.0, 0.9, 1e-2, 0.0, 0, 0, 0, -1, None) == -1  # null data
+    assert lib.lpmm_b200_sgd4bit_multi_tensor(None, -1, None, 0.0, 0.9, 1e-2, 0.0, 0, 0, 0, -1, None) == -2
 
 
 def test_maps_are_the_reference_maps(qmaps):
@@ -58,6 +76,10 @@ def test_maps_are_the_reference_maps(qmaps):
     assert create_general_qmap("linear", 4, True) is None
     with pytest.raises(ValueError):
         create_general_qmap("no-such-map", 4, True)
+    for b in (5, 6, 7, 8):  # the maps of default_{5,6,7,8}b.yml
+        assert np.array_equal(create_general_qmap("nonlinear", b, True).numpy(), qmaps[f"nonlinear_{b}"])
+        assert np.array_equal(create_general_qmap("power-1", b, False).numpy(), qmaps[f"power1_{b}"])
+        assert np.all(np.diff(qmaps[f"nonlinear_{b}"]) > 0) and len(qmaps[f"nonlinear_{b}"]) == 1 << b
 
 
 def test_config_defaults_files_and_pickle(tmp_path):
