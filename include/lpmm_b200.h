@@ -243,7 +243,14 @@ int64_t lpmm_b200_factored_scratch_bytes(const int64_t* shape, int ndim);
  * one step counter per parameter), all with the same maps and hyper-parameters, in order, on
  * `stream`; `scratch` must serve the largest FACTORED tensor of the list.  It replaces the reference's
  * per-parameter Python loop (lpmm/optim/adamw.py:332-436); results are those of n single calls. The
- * first non-zero status ends the call (earlier tensors have been stepped). */
+ * first non-zero status ends the call (earlier tensors have been stepped).
+ * Tensors whose moments are both fp32 and that share a step count are updated by one launch.  The
+ * launch chains of the other tensors are spread over four streams owned by the library (created on
+ * the first such call on a device, never destroyed); they start after everything already enqueued on
+ * `stream`, and `stream` waits for them before the call returns, so the caller's ordering is that of
+ * a call that used `stream` alone.  While `stream` is being captured the library's streams are not used.
+ * FACTORED tensors run concurrently only if `scratch_bytes` / 4 (rounded down to 256) covers the
+ * largest lpmm_b200_factored_scratch_bytes() of the list; otherwise they run one after the other. */
 int lpmm_b200_adamw4bit_unfused_step_many(const lpmm_b200_step_tensor* const* tensors, int n, const float* qmap_m,
                                           const float* qmap_v, double beta1, double beta2, double lr,
                                           double weight_decay, double eps, const double* steps, void* scratch,
