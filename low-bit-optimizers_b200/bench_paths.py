@@ -5,7 +5,8 @@ fused, next to the fused AdamW step on the same shapes.  Seeded synthetic inputs
     python low-bit-optimizers_b200/bench_paths.py [--iters 10] [--only SUBSTRING]
 
 One line per case: parameters, CUDA-event time per step (after 3 warm-up steps), wall time per step,
-parameters per second.  The headline benchmark of the repository is ``bench.py``; this script is
+parameters per second.  ``LPMM_SGD_PER_TENSOR=1`` in the environment times the per-tensor SGD launches
+instead of the multi-tensor one.  The headline benchmark of the repository is ``bench.py``; this script is
 where the figures of ``profiles/unfused_rank1_factored_kernels.md`` come from.
 """
 import argparse
@@ -46,13 +47,11 @@ def cases():
     for c in ("default_8b.yml", "default_5b.yml", "1st_moment_group_512.yml", "1st_moment_group_4096.yml"):
         out.append((f"linear4096 adamw {c}", "AdamW", LINEAR, dict(adamw, qconfig=cfg(c))))
     out += [
-        ("linear4096 sgd per tensor", "SGD", LINEAR, dict(sgd)),
-        ("linear4096 sgd fused", "SGD", LINEAR, dict(sgd, fused=True)),
+        ("linear4096 sgd", "SGD", LINEAR, dict(sgd)),
         ("gpt2-medium adamw factored", "AdamW", gpt2_medium_shapes(), dict(adamw, factor_second_moment=True)),
         ("gpt2-medium adamw rank-1 (default.yml)", "AdamW", gpt2_medium_shapes(), dict(adamw, qconfig=cfg("default.yml"))),
         ("gpt2-medium adamw fused", "AdamW", gpt2_medium_shapes(), dict(adamw, fused=True)),
-        ("gpt2-medium sgd per tensor", "SGD", gpt2_medium_shapes(), dict(sgd)),
-        ("gpt2-medium sgd fused", "SGD", gpt2_medium_shapes(), dict(sgd, fused=True)),
+        ("gpt2-medium sgd", "SGD", gpt2_medium_shapes(), dict(sgd)),
         ("ragged adamw rank-1 (default.yml)", "AdamW", RAGGED, dict(adamw, qconfig=cfg("default.yml"))),
     ]
     return out

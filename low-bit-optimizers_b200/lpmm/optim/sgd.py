@@ -5,11 +5,14 @@ config (``QUANT.M``: signed 'nonlinear' map, group-128 scales) in the layout of
 ``vectorwise_quant``; each tensor is updated by one launch that reproduces the reference's sequence
 of torch operations (sgd.py:152-187).
 
-``fused=True``, which the reference rejects (sgd.py:31-32), is accepted here: every parameter group
-is then stepped by one multi-tensor launch with the same arithmetic and the same state layout (the
-results and the ``state_dict`` are those of ``fused=False``).  A tensor's first step, which creates
-its buffer, still goes through the per-tensor launch.
+Once the buffers exist, every parameter group is stepped by one multi-tensor launch with the same
+arithmetic and the same state layout as the per-tensor launch (results and ``state_dict`` are
+identical bit for bit); a tensor's first step, which creates its buffer, and configurations the
+multi-tensor kernel does not cover (wider codes, larger groups, no momentum) use the per-tensor
+launch.  ``fused=True``, which the reference rejects (sgd.py:31-32), is accepted and means the same;
+``fused=False`` with ``LPMM_SGD_PER_TENSOR=1`` in the environment forces the per-tensor launches.
 """
+import os
 from typing import Optional
 
 import torch
@@ -32,7 +35,8 @@ class SGD(LowBitOptimizer):
         defaults = dict(lr=lr, momentum=momentum, weight_decay=weight_decay, dampening=dampening, nesterov=nesterov,
                         maximize=maximize)
         super().__init__(params, defaults, qconfig)
-        self._fused = bool(fused)  # not a param_group entry: the state_dict stays the reference's
+        # not a param_group entry: the state_dict stays the reference's
+        self._fused = bool(fused) or os.environ.get("LPMM_SGD_PER_TENSOR", "0") != "1"
         self._lists = {}  # (group index, device) -> (pointer key, TensorList) of the multi-tensor launch
 
     def get_subqconfig(self, optimizer_state_name):

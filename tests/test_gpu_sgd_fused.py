@@ -1,4 +1,4 @@
-"""``lpmm.optim.SGD(fused=True)`` -- one multi-tensor launch per parameter group -- on a B200:
+"""``lpmm.optim.SGD`` with one multi-tensor launch per parameter group (its normal mode) on a B200:
 bit-identical parameters, codes and scales to the per-tensor path and to the torch-op restatement of
 the reference's ``_single_tensor_sgd4bit`` (``oracle/torch_ref.py``), for every option combination,
 ragged and unaligned tensors, and group ranges (shards) of the list."""
@@ -24,6 +24,7 @@ def _run(kw, steps, fused, zero_fraction=0.0):
     import lpmm
     params = [torch.nn.Parameter(p.clone()) for p in _params(11)]
     opt = lpmm.optim.SGD(params, fused=fused, **kw)
+    opt._fused = fused  # False: the per-tensor launches (what LPMM_SGD_PER_TENSOR=1 selects)
     for s in range(1, steps + 1):
         for i, p in enumerate(params):
             p.grad = student_t(p.shape, 1000 * s + i, zero_fraction=zero_fraction)
