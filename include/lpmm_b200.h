@@ -239,13 +239,26 @@ int lpmm_b200_adamw4bit_unfused_step(const lpmm_b200_step_tensor* t, const float
                                      double step, void* scratch, int64_t scratch_bytes, void* stream);
 int64_t lpmm_b200_factored_scratch_bytes(const int64_t* shape, int ndim);
 
+/* The non-fused step of a whole list in ONE launch, for tensors whose two moments are both 4-bit with
+ * group-128 scales (the reference's configuration when no qconfig is given; kind LPMM_B200_KIND_Q4: m, v
+ * = packed codes in the vectorwise_quant layout of lpmm_b200_packed_len(ceil(numel/128)*128) bytes,
+ * m_scale, v_scale = float[ceil(numel/128)]) or both fp32 (LPMM_B200_KIND_FP32).  Arithmetic and layout
+ * are those of lpmm_b200_adamw4bit_unfused_step with GROUP4 / GROUP4 or FP32 / FP32 states, so a tensor
+ * may be stepped by either; the states must already be initialised (a tensor's first step belongs to
+ * lpmm_b200_adamw4bit_unfused_step, which also writes the layout's padding).  All tensors share `step`.
+ * [group_begin, group_end) selects a range of the list's 128-element group sequence (group_end < 0: all). */
+int lpmm_b200_adamw4bit_unfused_multi_tensor(const lpmm_b200_tensor* tensors, int n_tensors, const float* qmap_m,
+                                             const float* qmap_v, double beta1, double beta2, double lr,
+                                             double weight_decay, double eps, double step, int64_t group_begin,
+                                             int64_t group_end, void* stream);
+
 /* The same step for n tensors in one call: tensors[i] is stepped with steps[i] (the reference keeps
  * one step counter per parameter), all with the same maps and hyper-parameters, in order, on
  * `stream`; `scratch` must serve the largest FACTORED tensor of the list.  It replaces the reference's
  * per-parameter Python loop (lpmm/optim/adamw.py:332-436); results are those of n single calls. The
  * first non-zero status ends the call (earlier tensors have been stepped).
- * Tensors whose moments are both fp32 and that share a step count are updated by one launch.  The
- * launch chains of the other tensors are spread over four streams owned by the library (created on
+ * Tensors that lpmm_b200_adamw4bit_unfused_multi_tensor covers and that share a step count are updated
+ * by one launch of it.  The launch chains of the other tensors are spread over four streams owned by the library (created on
  * the first such call on a device, never destroyed); they start after everything already enqueued on
  * `stream`, and `stream` waits for them before the call returns, so the caller's ordering is that of
  * a call that used `stream` alone.  While `stream` is being captured the library's streams are not used.

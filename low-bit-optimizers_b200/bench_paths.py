@@ -50,6 +50,7 @@ def cases():
         ("linear4096 sgd", "SGD", LINEAR, dict(sgd)),
         ("gpt2-medium adamw factored", "AdamW", gpt2_medium_shapes(), dict(adamw, factor_second_moment=True)),
         ("gpt2-medium adamw rank-1 (default.yml)", "AdamW", gpt2_medium_shapes(), dict(adamw, qconfig=cfg("default.yml"))),
+        ("gpt2-medium adamw group (qconfig=None)", "AdamW", gpt2_medium_shapes(), dict(adamw, qconfig=None)),
         ("gpt2-medium adamw fused", "AdamW", gpt2_medium_shapes(), dict(adamw, fused=True)),
         ("gpt2-medium sgd", "SGD", gpt2_medium_shapes(), dict(sgd)),
         ("ragged adamw rank-1 (default.yml)", "AdamW", RAGGED, dict(adamw, qconfig=cfg("default.yml"))),

@@ -25,9 +25,11 @@
 
 #include <mutex>
 #include <type_traits>
+#include <vector>
 
 #include "common.cuh"
 #include "multi_tensor.cuh"
+#include "unfused_math.cuh"
 
 namespace lpmm_b200 {
 
@@ -37,12 +39,6 @@ constexpr int UTMAX = 512;  // threads per CTA when a group spans 32 half-warps 
 struct Shape {
   int nd;
   long long dim[8];
-};
-
-struct UConsts {
-  float wd_mul, lerp_w, lerp_omw, beta2, omb2, inv_bc2s, bc2s, eps, alpha;
-  int lerp_small;
-  int fast;  // eps keeps the denominator inside the domain of the short exact sqrt / division sequences
 };
 
 struct StepArgs {
@@ -289,103 +285,6 @@ __device__ __forceinline__ void lane_scales(const float* const* vecs, long long 
 // small, so skipping the atomic when the value is not larger is always safe.
 __device__ __forceinline__ void atomic_max_nonneg(float* addr, float val) {
   if (val > *reinterpret_cast<volatile float*>(addr)) atomicMax(reinterpret_cast<int*>(addr), __float_as_int(val));
-}
-
-__device__ __forceinline__ float lerp_m(const UConsts& c, float m0, float g) {
-  const float diff = __fsub_rn(g, m0);
-  return c.lerp_small ? __fmaf_rn(c.lerp_w, diff, m0) : __fmaf_rn(-diff, c.lerp_omw, g);
-}
-__device__ __forceinline__ float upd_v2(const UConsts& c, float v0, float g) {
-  return __fmaf_rn(c.omb2, __fmul_rn(g, g), __fmul_rn(v0, c.beta2));
-}
-__device__ __forceinline__ float upd_param(const UConsts& c, float p, float m, float v) {
-  const float p1 = __fmul_rn(p, c.wd_mul);
-  if (c.fast) {
-    const float d = __fadd_rn(__fmul_rn(sqrt_rn_fast(v), c.inv_bc2s), c.eps);
-    return __fmaf_rn(c.alpha, div_rn_fast(m, d), p1);
-  }
-  const float d = __fadd_rn(__fmul_rn(__fsqrt_rn(v), c.inv_bc2s), c.eps);
-  return __fmaf_rn(c.alpha, __fdiv_rn(m, d), p1);
-}
-
-// All fp32-state tensors of a list (the numel <= threshold fallback: biases, norms) in one launch.
-// Each is a few hundred elements, so one launch per tensor is pure launch latency.  A half-warp
-// takes 128 consecutive elements of the list's global group sequence; arithmetic as above.
-__global__ void __launch_bounds__(UT) unfused_fp32_multi_kernel(const __grid_constant__ Table tab, const UConsts c) {
-  const int l16 = threadIdx.x & 15;
-  long long gi = (long long)blockIdx.x * (UT / 16) + (threadIdx.x >> 4);
-  const long long stride = (long long)gridDim.x * (UT / 16);
-  for (int ti = 0; ti < tab.n; ++ti) {
-    const TDesc& t = tab.t[ti];
-    const long long tend = (ti + 1 < tab.n) ? tab.t[ti + 1].gstart : tab.gtotal;
-    float* mp = reinterpret_cast<float*>(t.m);
-    float* vp = reinterpret_cast<float*>(t.v);
-    for (; gi < tend; gi += stride) {
-      const long long e0 = (gi - t.gstart) * 128 + l16 * 8;
-#pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        const long long e = e0 + k;
-        if (e < t.numel) {
-          const float g = t.g[e];
-          const float m = lerp_m(c, mp[e], g);
-          const float v = upd_v2(c, vp[e], g);
-          mp[e] = m;
-          vp[e] = v;
-          t.p[e] = upd_param(c, t.p[e], m, v);
-        }
-      }
-    }
-  }
-}
-
-// The same update for two elements per instruction (sm_100 packed fp32: each half is the IEEE
-// result of the scalar instruction), for lanes whose 8 elements all exist and hyper-parameters in
-// the domain of the short sqrt / division sequences.
-struct UConsts2 {
-  f2 wd_mul, lerp_a, beta2, omb2, inv_bc2s, eps, alpha, mone, half, one;
-  int lerp_small;
-};
-__device__ __forceinline__ UConsts2 make_consts2(const UConsts& c) {
-  UConsts2 k;
-  k.wd_mul = f2_splat(c.wd_mul);
-  k.lerp_a = f2_splat(c.lerp_small ? c.lerp_w : -c.lerp_omw);  // fma(-d, w', g) == fma(d, -w', g)
-  k.beta2 = f2_splat(c.beta2);
-  k.omb2 = f2_splat(c.omb2);
-  k.inv_bc2s = f2_splat(c.inv_bc2s);
-  k.eps = f2_splat(c.eps);
-  k.alpha = f2_splat(c.alpha);
-  k.mone = f2_splat(-1.0f);
-  k.half = f2_splat(0.5f);
-  k.one = f2_splat(1.0f);
-  k.lerp_small = c.lerp_small;
-  return k;
-}
-// In: g, p, the old moments m0, v0 (pairs).  Out: m, v, p updated; returns nothing, maxima via am / av.
-__device__ __forceinline__ void update_pair(const UConsts2& k, f2 g, f2& p, f2 m0, f2 v0, f2& m, f2& v, float& am,
-                                            float& av) {
-  const f2 diff = f2_fma(m0, k.mone, g);                       // g - m0
-  m = f2_fma(k.lerp_a, diff, k.lerp_small ? m0 : g);           // lerp
-  v = f2_fma(k.omb2, f2_mul(g, g), f2_mul(v0, k.beta2));       // mul_ then addcmul_
-  float ma, mb, va, vb;
-  f2_unpack(m, ma, mb);
-  f2_unpack(v, va, vb);
-  am = fmaxf(am, fmaxf(fabsf(ma), fabsf(mb)));
-  av = fmaxf(av, fmaxf(va, vb));
-  // sqrt(v) as in sqrt_rn_fast
-  const f2 y = f2_pack(mufu_rsq(fmaxf(va, 1.17549435e-38f)), mufu_rsq(fmaxf(vb, 1.17549435e-38f)));
-  f2 sq = f2_mul(v, y);
-  const f2 e = f2_fma(sq, f2_mul(sq, k.mone), v);
-  sq = f2_fma(e, f2_mul(k.half, y), sq);
-  // d = sqrt(v) * (1 / bc2s) + eps; m / d as in div_rn_fast, on the negated denominator
-  const f2 d = f2_mul_then_add(sq, k.inv_bc2s, k.eps);  // two roundings, like the torch ops
-  const f2 nd = f2_mul(d, k.mone);
-  float da, db;
-  f2_unpack(d, da, db);
-  const f2 r0 = f2_pack(mufu_rcp(da), mufu_rcp(db));
-  const f2 r = f2_fma(r0, f2_fma(nd, r0, k.one), r0);
-  const f2 q = f2_mul(m, r);
-  const f2 quo = f2_fma(f2_fma(nd, q, m), r, q);
-  p = f2_fma(k.alpha, quo, f2_mul(p, k.wd_mul));               // addcdiv_ on the decayed parameter
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1059,24 +958,6 @@ static int fill_shape(Shape& s, const int64_t* shape, int ndim, long long* numel
   *numel_out = n;
   return LPMM_B200_OK;
 }
-static UConsts make_consts(double beta1, double beta2, double lr, double wd, double eps, double step) {
-  UConsts c;
-  const double bc1 = 1.0 - pow(beta1, step);
-  const double bc2 = 1.0 - pow(beta2, step);
-  const double step_size = lr / bc1;
-  c.wd_mul = (float)(1.0 - lr * wd);
-  c.lerp_w = (float)(1.0 - beta1);
-  c.lerp_omw = 1.0f - c.lerp_w;
-  c.lerp_small = fabsf(c.lerp_w) < 0.5f;
-  c.beta2 = (float)beta2;
-  c.omb2 = (float)(1.0 - beta2);
-  c.bc2s = (float)sqrt(bc2);
-  c.inv_bc2s = (float)(1.0 / sqrt(bc2));  // torch divides by a host scalar as x * float(1.0 / s)
-  c.eps = (float)eps;
-  c.alpha = (float)(-step_size);
-  c.fast = (eps >= 0x1p-40 && eps <= 0x1p30 && bc2 >= 0x1p-40);
-  return c;
-}
 
 }  // namespace lpmm_b200
 
@@ -1479,11 +1360,16 @@ extern "C" int lpmm_b200_adamw4bit_unfused_step_many(const lpmm_b200_step_tensor
   if (n < 0) return LPMM_B200_ERR_BAD_SIZE;
   if (n > 0 && (!tensors || !steps)) return LPMM_B200_ERR_NULL_POINTER;
   cudaStream_t user = (cudaStream_t)stream;
-  // which tensors go into the shared fp32 launch, how many need launches of their own, and the
-  // largest scratch need among the factored ones
+  // which tensors go into the shared multi-tensor launch (both moments fp32, or both 4-bit with
+  // groups of 128, already initialised), how many need launches of their own, and the largest
+  // scratch need among the factored ones
   auto is_plain = [&](const lpmm_b200_step_tensor* t) {
-    return t->m_mode == LPMM_B200_STATE_FP32 && t->v_mode == LPMM_B200_STATE_FP32 && !t->first && t->numel > 0 &&
-           t->p && t->g && t->m && t->v;
+    if (t->first || t->numel <= 0 || !t->p || !t->g || !t->m || !t->v) return false;
+    if (t->m_mode == LPMM_B200_STATE_FP32 && t->v_mode == LPMM_B200_STATE_FP32) return true;
+    return t->m_mode == LPMM_B200_STATE_GROUP4 && t->v_mode == LPMM_B200_STATE_GROUP4 &&
+           (t->m_bits == 0 || t->m_bits == 4) && (t->v_bits == 0 || t->v_bits == 4) &&
+           (t->m_group == 0 || t->m_group == 128) && (t->v_group == 0 || t->v_group == 128) && t->m_max1 &&
+           t->v_max1 && qmap_m && qmap_v;
   };
   int own = 0;
   int64_t max_need = 0;
@@ -1514,46 +1400,28 @@ extern "C" int lpmm_b200_adamw4bit_unfused_step_many(const lpmm_b200_step_tensor
   // one, otherwise all factored tensors stay on one stream and use all of it
   const int64_t slice = side ? (scratch_bytes / SIDE_STREAMS) & ~(int64_t)255 : 0;
   const bool sliced = side && scratch && max_need <= slice;
-  // fp32-state tensors that share a step count go into one launch (per window of MAX_TENSORS); all
-  // others are stepped one by one.  Tensors are independent, so the order of the launches is free.
-  static thread_local Table tab;
-  int cnt = 0;
-  int64_t groups = 0;
+  // the tensors of the shared launch must share a step count (it sets the bias corrections); a tensor
+  // with another count is stepped on its own.  Tensors are independent, so the order is free.
+  static thread_local std::vector<lpmm_b200_tensor> batch;
+  batch.clear();
   double batch_step = 0.0;
-  auto flush = [&]() -> int {
-    if (cnt == 0) return LPMM_B200_OK;
-    tab.n = cnt;
-    tab.pad = 0;
-    tab.gtotal = groups;
-    const UConsts c = make_consts(beta1, beta2, lr, weight_decay, eps, batch_step);
-    unfused_fp32_multi_kernel<<<grid_for(groups, UT / 16), UT, 0, user>>>(tab, c);
-    cnt = 0;
-    groups = 0;
-    LPMM_CUDA_TRY(cudaGetLastError());
-    return LPMM_B200_OK;
-  };
   int rr = 0;  // round-robin position
   int rc = LPMM_B200_OK;
   for (int i = 0; i < n && rc == LPMM_B200_OK; ++i) {
     const lpmm_b200_step_tensor* t = tensors[i];
-    if (is_plain(t) && (cnt == 0 || steps[i] == batch_step)) {
-      if (cnt == MAX_TENSORS) {
-        rc = flush();
-        if (rc != LPMM_B200_OK) break;
-      }
+    if (is_plain(t) && (batch.empty() || steps[i] == batch_step)) {
       batch_step = steps[i];
-      TDesc& d = tab.t[cnt++];
+      lpmm_b200_tensor d;
       d.p = t->p;
       d.g = t->g;
       d.m = t->m;
       d.v = t->v;
-      d.sm = nullptr;
-      d.sv = nullptr;
+      d.m_scale = t->m_max1;
+      d.v_scale = t->v_max1;
       d.numel = t->numel;
-      d.gstart = groups;
-      d.kind = LPMM_B200_KIND_FP32;
-      d.aligned = 0;
-      groups += groups_of(t->numel);
+      d.kind = (t->m_mode == LPMM_B200_STATE_FP32) ? LPMM_B200_KIND_FP32 : LPMM_B200_KIND_Q4;
+      d.reserved = 0;
+      batch.push_back(d);
       continue;
     }
     cudaStream_t st = user;
@@ -1574,7 +1442,9 @@ extern "C" int lpmm_b200_adamw4bit_unfused_step_many(const lpmm_b200_step_tensor
     rc = lpmm_b200_adamw4bit_unfused_step(t, qmap_m, qmap_v, beta1, beta2, lr, weight_decay, eps, steps[i], sc, sc_bytes,
                                           st);
   }
-  if (rc == LPMM_B200_OK) rc = flush();
+  if (rc == LPMM_B200_OK && !batch.empty())
+    rc = lpmm_b200_adamw4bit_unfused_multi_tensor(batch.data(), (int)batch.size(), qmap_m, qmap_v, beta1, beta2, lr,
+                                                  weight_decay, eps, batch_step, 0, -1, user);
   if (side) {  // join even after an error: the caller's stream must not run ahead of what was enqueued
     for (int k = 0; k < SIDE_STREAMS; ++k) {
       if (cudaEventRecord(side->join[k], side->s[k]) != cudaSuccess ||

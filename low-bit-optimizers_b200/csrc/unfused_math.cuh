@@ -1,0 +1,110 @@
+// Arithmetic of the reference's non-fused AdamW step (lpmm/optim/adamw.py:369, 412-422), i.e. of the
+// torch CUDA kernels it runs, operation by operation:
+//   p1 = p * float(1 - lr*wd)
+//   m  = fma(w, g - m0, m0),  w = float(1 - beta1)                  torch lerp, weight < 0.5
+//   v  = fma(float(1 - beta2), g*g, v0 * float(beta2))              mul_ then addcmul_
+//   d  = sqrt(v) * float(1.0 / sqrt(1 - beta2^step)) + float(eps)    division by a host scalar
+//   p  = fma(float(-lr / (1 - beta1^step)), m / d, p1)              addcdiv_
+// with the scalar constants computed in double on the host exactly as Python computes them.
+#pragma once
+#include <math.h>
+
+#include "common.cuh"
+
+namespace lpmm_b200 {
+
+struct UConsts {
+  float wd_mul, lerp_w, lerp_omw, beta2, omb2, inv_bc2s, bc2s, eps, alpha;
+  int lerp_small;
+  int fast;  // eps keeps the denominator inside the domain of the short exact sqrt / division sequences
+};
+
+
+__device__ __forceinline__ float lerp_m(const UConsts& c, float m0, float g) {
+  const float diff = __fsub_rn(g, m0);
+  return c.lerp_small ? __fmaf_rn(c.lerp_w, diff, m0) : __fmaf_rn(-diff, c.lerp_omw, g);
+}
+__device__ __forceinline__ float upd_v2(const UConsts& c, float v0, float g) {
+  return __fmaf_rn(c.omb2, __fmul_rn(g, g), __fmul_rn(v0, c.beta2));
+}
+__device__ __forceinline__ float upd_param(const UConsts& c, float p, float m, float v) {
+  const float p1 = __fmul_rn(p, c.wd_mul);
+  if (c.fast) {
+    const float d = __fadd_rn(__fmul_rn(sqrt_rn_fast(v), c.inv_bc2s), c.eps);
+    return __fmaf_rn(c.alpha, div_rn_fast(m, d), p1);
+  }
+  const float d = __fadd_rn(__fmul_rn(__fsqrt_rn(v), c.inv_bc2s), c.eps);
+  return __fmaf_rn(c.alpha, __fdiv_rn(m, d), p1);
+}
+
+// The same update for two elements per instruction (sm_100 packed fp32: each half is the IEEE
+// result of the scalar instruction), for lanes whose 8 elements all exist and hyper-parameters in
+// the domain of the short sqrt / division sequences.
+struct UConsts2 {
+  f2 wd_mul, lerp_a, beta2, omb2, inv_bc2s, eps, alpha, mone, half, one;
+  int lerp_small;
+};
+__device__ __forceinline__ UConsts2 make_consts2(const UConsts& c) {
+  UConsts2 k;
+  k.wd_mul = f2_splat(c.wd_mul);
+  k.lerp_a = f2_splat(c.lerp_small ? c.lerp_w : -c.lerp_omw);  // fma(-d, w', g) == fma(d, -w', g)
+  k.beta2 = f2_splat(c.beta2);
+  k.omb2 = f2_splat(c.omb2);
+  k.inv_bc2s = f2_splat(c.inv_bc2s);
+  k.eps = f2_splat(c.eps);
+  k.alpha = f2_splat(c.alpha);
+  k.mone = f2_splat(-1.0f);
+  k.half = f2_splat(0.5f);
+  k.one = f2_splat(1.0f);
+  k.lerp_small = c.lerp_small;
+  return k;
+}
+// In: g, p, the old moments m0, v0 (pairs).  Out: m, v, p updated; returns nothing, maxima via am / av.
+__device__ __forceinline__ void update_pair(const UConsts2& k, f2 g, f2& p, f2 m0, f2 v0, f2& m, f2& v, float& am,
+                                            float& av) {
+  const f2 diff = f2_fma(m0, k.mone, g);                       // g - m0
+  m = f2_fma(k.lerp_a, diff, k.lerp_small ? m0 : g);           // lerp
+  v = f2_fma(k.omb2, f2_mul(g, g), f2_mul(v0, k.beta2));       // mul_ then addcmul_
+  float ma, mb, va, vb;
+  f2_unpack(m, ma, mb);
+  f2_unpack(v, va, vb);
+  am = fmaxf(am, fmaxf(fabsf(ma), fabsf(mb)));
+  av = fmaxf(av, fmaxf(va, vb));
+  // sqrt(v) as in sqrt_rn_fast
+  const f2 y = f2_pack(mufu_rsq(fmaxf(va, 1.17549435e-38f)), mufu_rsq(fmaxf(vb, 1.17549435e-38f)));
+  f2 sq = f2_mul(v, y);
+  const f2 e = f2_fma(sq, f2_mul(sq, k.mone), v);
+  sq = f2_fma(e, f2_mul(k.half, y), sq);
+  // d = sqrt(v) * (1 / bc2s) + eps; m / d as in div_rn_fast, on the negated denominator
+  const f2 d = f2_mul_then_add(sq, k.inv_bc2s, k.eps);  // two roundings, like the torch ops
+  const f2 nd = f2_mul(d, k.mone);
+  float da, db;
+  f2_unpack(d, da, db);
+  const f2 r0 = f2_pack(mufu_rcp(da), mufu_rcp(db));
+  const f2 r = f2_fma(r0, f2_fma(nd, r0, k.one), r0);
+  const f2 q = f2_mul(m, r);
+  const f2 quo = f2_fma(f2_fma(nd, q, m), r, q);
+  p = f2_fma(k.alpha, quo, f2_mul(p, k.wd_mul));               // addcdiv_ on the decayed parameter
+}
+
+// Host side: the constants of one step.
+static inline UConsts make_consts(double beta1, double beta2, double lr, double wd, double eps, double step) {
+  UConsts c;
+  const double bc1 = 1.0 - pow(beta1, step);
+  const double bc2 = 1.0 - pow(beta2, step);
+  const double step_size = lr / bc1;
+  c.wd_mul = (float)(1.0 - lr * wd);
+  c.lerp_w = (float)(1.0 - beta1);
+  c.lerp_omw = 1.0f - c.lerp_w;
+  c.lerp_small = fabsf(c.lerp_w) < 0.5f;
+  c.beta2 = (float)beta2;
+  c.omb2 = (float)(1.0 - beta2);
+  c.bc2s = (float)sqrt(bc2);
+  c.inv_bc2s = (float)(1.0 / sqrt(bc2));  // torch divides by a host scalar as x * float(1.0 / s)
+  c.eps = (float)eps;
+  c.alpha = (float)(-step_size);
+  c.fast = (eps >= 0x1p-40 && eps <= 0x1p30 && bc2 >= 0x1p-40);
+  return c;
+}
+
+}  // namespace lpmm_b200

@@ -1,0 +1,100 @@
+"""``lpmm_b200_adamw4bit_unfused_multi_tensor`` -- the non-fused step of a whole group/group list in one
+launch -- on a B200: the optimizer (``lpmm.optim.AdamW(qconfig=None)``, which reaches it from a
+tensor's second step on) against the torch-op restatement of the reference, and the entry point itself
+against per-tensor calls of ``lpmm_b200_adamw4bit_unfused_step``, on unaligned views and in group ranges."""
+import ctypes
+
+import pytest
+import torch
+
+from gpu_helpers import bits_equal, device, student_t
+from test_gpu_unfused import _check_adamw, _run_pair_adamw
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("hyper", [dict(lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01),
+                                   dict(lr=3e-4, betas=(0.8, 0.95), eps=1e-6, weight_decay=0.0),
+                                   dict(lr=1e-3, betas=(0.9, 0.999), eps=1e-30, weight_decay=0.1)])
+def test_optimizer_group_config_ragged_list(qmaps, hyper):
+    """Ragged shapes, 20 % exact zeros, 7 steps (6 of them through the multi-tensor launch); eps = 1e-30
+    takes the IEEE sqrt / division instantiation."""
+    shapes = [(300, 130), (4097,), (127,), (64, 128), (5000, 1), (3, 3, 24, 24), (4096,), (9000,), (1000, 768)]
+    kw = dict(qconfig=None, **hyper)
+    torch.manual_seed(21)
+    p0s = [torch.randn(s, device=device()) * 0.02 for s in shapes]
+    opt, params, o_states, o_params = _run_pair_adamw(
+        shapes, p0s, lambda s: [student_t(sh, s * 100003 + i, zero_fraction=0.2) for i, sh in enumerate(shapes)], 7, kw,
+        qmaps, "group")
+    _check_adamw(opt, params, o_states, o_params, "group")
+
+
+def _vp(t):
+    return ctypes.c_void_p(t.data_ptr() if t is not None else None)
+
+
+def test_entry_point_equals_per_tensor_calls_on_unaligned_views_and_ranges(qmaps):
+    from lpmm import _kernels, _native as N
+    qm = torch.from_numpy(qmaps["m"]).to(device())
+    qv = torch.from_numpy(qmaps["v"]).to(device())
+    sizes = [128 * 40 + 5, 4097, 128 * 64, 333, 100]
+    kinds = [N.KIND_Q4, N.KIND_Q4, N.KIND_Q4, N.KIND_Q4, N.KIND_FP32]
+
+    def build(seed):
+        torch.manual_seed(seed)
+        out, keep = [], []
+        for i, n in enumerate(sizes):
+            base = torch.randn(n + 3, device=device()) * 0.02
+            gbase = torch.randn(n + 3, device=device()) * 1e-3
+            off = 1 if i % 2 == 0 else 0  # odd float offset: not 32-byte aligned
+            p, g = base[off:off + n], gbase[off:off + n]
+            groups = (n + 127) // 128
+            if kinds[i] == N.KIND_Q4:
+                m = torch.randint(-128, 128, (_kernels.packed_len(groups * 128),), dtype=torch.int8, device=device())
+                v = torch.randint(-128, 128, (_kernels.packed_len(groups * 128),), dtype=torch.int8, device=device())
+                sm = torch.rand(groups, 1, device=device()) * 1e-3
+                sv = torch.rand(groups, 1, device=device()) * 1e-6
+            else:
+                m, v, sm, sv = torch.randn(n, device=device()) * 1e-3, torch.rand(n, device=device()) * 1e-6, None, None
+            out.append((p, g, m, v, sm, sv))
+            keep += [base, gbase]
+        return out, keep
+
+    hyper = (0.9, 0.999, 1e-3, 0.01, 1e-8, 7.0)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def multi(entries, lo=0, hi=-1):
+        tl = _kernels.TensorList(entries)
+        N.check(N.lib.lpmm_b200_adamw4bit_unfused_multi_tensor(tl.array, tl.n, _vp(qm), _vp(qv), *hyper, lo, hi, stream))
+        return tl
+
+    ea, _ka = build(9)
+    ta = multi(ea)
+    eb, _kb = build(9)
+    total = ta.total_groups
+    cuts = [0, total // 3 + 1, 2 * total // 3, total]
+    for lo, hi in zip(cuts[:-1], cuts[1:]):
+        multi(eb, lo, hi)
+    ec, _kc = build(9)
+    for (p, g, m, v, sm, sv), kind in zip(ec, kinds):
+        t = N.StepTensor()
+        t.p, t.g, t.numel, t.ndim, t.first = p.data_ptr(), g.data_ptr(), p.numel(), 1, 0
+        t.shape[0] = p.numel()
+        mode = N.STATE_GROUP4 if kind == N.KIND_Q4 else N.STATE_FP32
+        t.m_mode = t.v_mode = mode
+        t.m, t.v = m.data_ptr(), v.data_ptr()
+        if sm is not None:
+            t.m_max1, t.v_max1 = sm.data_ptr(), sv.data_ptr()
+        N.check(N.lib.lpmm_b200_adamw4bit_unfused_step(ctypes.byref(t), _vp(qm), _vp(qv), *hyper, None, 0, stream))
+    torch.cuda.synchronize()
+    for i, (a, b, c) in enumerate(zip(ea, eb, ec)):
+        n = a[0].numel()
+        nbytes = (n + 127) // 128 * 64
+        for other, what in ((b, "group ranges"), (c, "per-tensor calls")):
+            assert bits_equal(a[0], other[0]), f"tensor {i}: parameters vs {what}"
+            if kinds[i] == N.KIND_Q4:
+                assert torch.equal(a[2][:nbytes], other[2][:nbytes]), f"tensor {i}: first-moment codes vs {what}"
+                assert torch.equal(a[3][:nbytes], other[3][:nbytes]), f"tensor {i}: second-moment codes vs {what}"
+                assert bits_equal(a[4], other[4]) and bits_equal(a[5], other[5]), f"tensor {i}: scales vs {what}"
+            else:
+                assert bits_equal(a[2], other[2]) and bits_equal(a[3], other[3]), f"tensor {i}: fp32 moments vs {what}"
