@@ -2,7 +2,7 @@
 (rank-1, group, wider codes, larger groups), the factored second moment, momentum SGD per tensor and
 fused, next to the fused AdamW step on the same shapes.  Seeded synthetic inputs.
 
-    python low-bit-optimizers_b200/bench_paths.py [--iters 10] [--only SUBSTRING]
+    python low-bit-optimizers_b200/bench_paths.py [--iters 10] [--only SUBSTRING] [--big]
 
 One line per case: parameters, CUDA-event time per step (after 3 warm-up steps), wall time per step,
 parameters per second.  ``LPMM_SGD_PER_TENSOR=1`` in the environment times the per-tensor SGD launches
@@ -26,6 +26,13 @@ def gpt2_medium_shapes():
     for _ in range(24):
         shapes += [(1024, 3072), (1024, 1024), (1024, 4096), (4096, 1024)] + [(1024,)] * 4
     return shapes
+
+
+def llama7b_shapes(layers=32, hidden=4096, inter=11008, vocab=32000):
+    shapes = [(vocab, hidden)]
+    for _ in range(layers):
+        shapes += [(hidden, hidden)] * 4 + [(inter, hidden), (inter, hidden), (hidden, inter), (hidden,), (hidden,)]
+    return shapes + [(hidden,), (vocab, hidden)]
 
 
 LINEAR = [(4096, 4096), (4096,)]
@@ -58,12 +65,22 @@ def cases():
     return out
 
 
+def big_cases():
+    """The LLaMA-7B-shaped list of ``bench.py`` (61 GB of parameters, gradients and states)."""
+    adamw = dict(lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01)
+    return [
+        ("llama7b adamw group (qconfig=None)", "AdamW", llama7b_shapes(), dict(adamw, qconfig=None)),
+        ("llama7b adamw fused", "AdamW", llama7b_shapes(), dict(adamw, fused=True)),
+        ("llama7b sgd", "SGD", llama7b_shapes(), dict(lr=1e-2, momentum=0.9, weight_decay=1e-4)),
+    ]
+
+
 def run(name, kind, shapes, kw, iters):
     dev = torch.device("cuda:0")
     torch.manual_seed(0)
-    params = [torch.nn.Parameter(torch.randn(s, device=dev) * 0.02) for s in shapes]
+    params = [torch.nn.Parameter(torch.empty(s, device=dev).normal_(0.0, 0.02)) for s in shapes]
     for p in params:
-        p.grad = torch.randn_like(p) * 1e-3
+        p.grad = torch.empty_like(p).normal_(0.0, 1e-3)
     opt = getattr(lpmm.optim, kind)(params, **kw)
     for _ in range(3):
         opt.step()
@@ -85,12 +102,14 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--only", default=None)
+    ap.add_argument("--big", action="store_true", help="the LLaMA-7B-shaped list instead (needs ~70 GB)")
     a = ap.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("needs a CUDA device")
-    for name, kind, shapes, kw in cases():
+    for name, kind, shapes, kw in (big_cases() if a.big else cases()):
         if a.only is None or a.only in name:
             run(name, kind, shapes, kw, a.iters)
+            torch.cuda.empty_cache()
 
 
 if __name__ == "__main__":
