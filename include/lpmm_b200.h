@@ -258,7 +258,10 @@ int lpmm_b200_adamw4bit_unfused_multi_tensor(const lpmm_b200_tensor* tensors, in
  * per-parameter Python loop (lpmm/optim/adamw.py:332-436); results are those of n single calls. The
  * first non-zero status ends the call (earlier tensors have been stepped).
  * Tensors that lpmm_b200_adamw4bit_unfused_multi_tensor covers and that share a step count are updated
- * by one launch of it.  The launch chains of the other tensors are spread over four streams owned by the library (created on
+ * by one launch of it; 2-D RANK1_4 tensors (4-bit codes, group-128 first moment, row length a multiple
+ * of 8, 16-byte aligned) that share a step count are stepped together in three launches, their
+ * descriptor table (under 256 bytes per tensor) taken from the end of `scratch` -- without enough
+ * scratch they are stepped one by one.  The launch chains of the other tensors are spread over four streams owned by the library (created on
  * the first such call on a device, never destroyed); they start after everything already enqueued on
  * `stream`, and `stream` waits for them before the call returns, so the caller's ordering is that of
  * a call that used `stream` alone.  While `stream` is being captured the library's streams are not used.

@@ -1,0 +1,419 @@
+// The non-fused step of the reference's default.yml configuration -- first moment 4-bit with group-128
+// scales, second moment 4-bit with rank-1 (per-row / per-column maxima) scales -- for ALL matrices of a
+// parameter list in three launches: zero the new maxima, a statistics pass that recomputes every second
+// moment and folds it into the new row / column maxima (the first pass of the two-pass grid
+// reduction), and the update pass (dequantise with the old maxima, AdamW, requantise with the new).
+// The reference does this per parameter in Python (lpmm/optim/adamw.py:332-436 with
+// lpmm/functional.py:190-203, 97-106, 512-531); arithmetic and state layout here are those of the
+// per-tensor launches in unfused.cu, bit for bit.
+//
+// The tensors are described by a table in device memory (the launch parameters cannot hold per-tensor
+// shapes and five state pointers for hundreds of tensors).  Work is cut into tiles (statistics) and
+// 128-element units (update) numbered across the whole list, and a fixed grid of persistent CTAs
+// strides over them, so small and large matrices share the machine and nothing waits for a tiny launch.
+#include <math.h>
+
+#include <vector>
+
+#include "common.cuh"
+#include "multi_tensor.cuh"
+#include "unfused_math.cuh"
+
+namespace lpmm_b200 {
+
+constexpr int R1T = 256;                   // threads per CTA
+constexpr size_t R1_DYN_SMEM = LUT_ENTRIES * sizeof(LutEnt);
+
+struct R1Desc {
+  float* p;
+  const float* g;
+  uint8_t* m;
+  float* m_max1;
+  uint8_t* v;
+  const float* old_r;  // maxima the stored codes were normalised with: per row, per column
+  const float* old_c;
+  float* new_r;        // maxima of the updated second moment
+  float* new_c;
+  long long n;
+  long long ustart;    // first global 128-element unit of this tensor
+  long long tstart;    // first global statistics tile of this tensor
+  int R, C;
+  int tiles_x, rows_per_tile;
+  int tx_shift;        // statistics: log2 of the column-threads of a tile (8 columns each)
+  int pad_;
+};
+
+__device__ __forceinline__ void r1_atomic_max(float* addr, float val) {
+  if (val > *reinterpret_cast<volatile float*>(addr)) atomicMax(reinterpret_cast<int*>(addr), __float_as_int(val));
+}
+
+// Index of the last descriptor whose `start` field (ustart / tstart) is <= x.
+template <bool TILES>
+__device__ __forceinline__ int r1_find(const R1Desc* __restrict__ d, int n, long long x) {
+  int lo = 0, hi = n - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if ((TILES ? d[mid].tstart : d[mid].ustart) <= x) lo = mid;
+    else hi = mid - 1;
+  }
+  return lo;
+}
+
+__global__ void __launch_bounds__(R1T) r1_zero_kernel(const R1Desc* __restrict__ d) {
+  const R1Desc& t = d[blockIdx.x];
+  for (int i = threadIdx.x; i < t.R; i += R1T) t.new_r[i] = 0.0f;
+  for (int i = threadIdx.x; i < t.C; i += R1T) t.new_c[i] = 0.0f;
+}
+
+// Statistics: a tile is (8 << tx_shift) columns by rows_per_tile rows of one matrix.  The CTA's 256
+// threads form 2^tx_shift column-threads (8 columns each) by 256 >> tx_shift row-lanes, so a narrow
+// matrix keeps every thread busy; a thread keeps its 8 columns for all its rows of the tile (column
+// maxima in registers, one atomic per thread and column at the end), a row's maximum is reduced across
+// the lanes that share the row (one atomic per warp and row).  Two rows per thread are in flight.
+// Rows are multiples of 8 floats and 16-byte aligned (host-checked).
+__device__ __forceinline__ float r1_row_pass(const R1Desc& t, long long r, long long c0, const float* qv,
+                                             const float* col_old, float* col_max, const UConsts& c,
+                                             const float4& g0, const float4& g1, uint32_t codes, float row_old) {
+  const float gx[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+  float row_max = 0.0f;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const float v0 = __fmul_rn(qv[(codes >> (4 * k)) & 15u], fminf(row_old, col_old[k]));
+    const float v = upd_v2(c, v0, gx[k]);
+    col_max[k] = fmaxf(col_max[k], v);
+    row_max = fmaxf(row_max, v);
+  }
+  return row_max;
+}
+
+__global__ void __launch_bounds__(R1T) r1_stats_kernel(const R1Desc* __restrict__ d, int n, long long total_tiles,
+                                                        const float* __restrict__ qmap_v, const UConsts c) {
+  __shared__ float qv[16];
+  if (threadIdx.x < 16) qv[threadIdx.x] = qmap_v[threadIdx.x];
+  __syncthreads();
+  for (long long tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+    const R1Desc& t = d[r1_find<true>(d, n, tile)];
+    const long long local = tile - t.tstart;
+    const int tx_count = 1 << t.tx_shift, ty_count = R1T >> t.tx_shift;
+    const int tx = threadIdx.x & (tx_count - 1), ty = threadIdx.x >> t.tx_shift;
+    const int tile_x = (int)(local % t.tiles_x);
+    const long long tile_y = local / t.tiles_x;
+    const long long C = t.C;
+    const long long c0 = ((long long)tile_x * tx_count + tx) * 8;
+    const bool active = c0 < C;
+    float col_old[8], col_max[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      col_old[k] = active ? __ldg(t.old_c + c0 + k) : 0.0f;
+      col_max[k] = 0.0f;
+    }
+    const long long r_begin = tile_y * t.rows_per_tile;
+    const long long r_end = (r_begin + t.rows_per_tile < t.R) ? r_begin + t.rows_per_tile : t.R;
+    const int seg = tx_count < 32 ? tx_count : 32;  // lanes that share a row inside a warp
+    // all lanes of a warp make the same number of trips (the shuffles below need the whole warp)
+    for (long long rb = r_begin; rb < r_end; rb += 2 * ty_count) {
+      const long long ra = rb + ty, rc = rb + ty_count + ty;
+      const bool ha = active && ra < r_end, hc = active && rc < r_end;
+      float4 ga0 = make_float4(0.f, 0.f, 0.f, 0.f), ga1 = ga0, gc0 = ga0, gc1 = ga0;
+      uint32_t ca = 0, cc = 0;
+      float oa = 0.0f, oc = 0.0f;
+      if (ha) {
+        const long long e0 = ra * C + c0;
+        ga0 = *reinterpret_cast<const float4*>(t.g + e0);
+        ga1 = *reinterpret_cast<const float4*>(t.g + e0 + 4);
+        ca = *reinterpret_cast<const uint32_t*>(t.v + (e0 >> 1));
+        oa = __ldg(t.old_r + ra);
+      }
+      if (hc) {
+        const long long e0 = rc * C + c0;
+        gc0 = *reinterpret_cast<const float4*>(t.g + e0);
+        gc1 = *reinterpret_cast<const float4*>(t.g + e0 + 4);
+        cc = *reinterpret_cast<const uint32_t*>(t.v + (e0 >> 1));
+        oc = __ldg(t.old_r + rc);
+      }
+      float ma = ha ? r1_row_pass(t, ra, c0, qv, col_old, col_max, c, ga0, ga1, ca, oa) : 0.0f;
+      float mc = hc ? r1_row_pass(t, rc, c0, qv, col_old, col_max, c, gc0, gc1, cc, oc) : 0.0f;
+      for (int o = seg >> 1; o; o >>= 1) {
+        ma = fmaxf(ma, __shfl_xor_sync(0xffffffffu, ma, o));
+        mc = fmaxf(mc, __shfl_xor_sync(0xffffffffu, mc, o));
+      }
+      if ((threadIdx.x & (seg - 1)) == 0) {
+        if (ra < r_end) r1_atomic_max(t.new_r + ra, ma);
+        if (rc < r_end) r1_atomic_max(t.new_r + rc, mc);
+      }
+    }
+    if (active) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) r1_atomic_max(t.new_c + c0 + k, col_max[k]);
+    }
+  }
+}
+
+__device__ __forceinline__ int r1_code16(const float* __restrict__ mids, float x) {
+  int c = (mids[7] < x) ? 8 : 0;
+  c += (mids[c + 3] < x) ? 4 : 0;
+  c += (mids[c + 1] < x) ? 2 : 0;
+  c += (mids[c] < x) ? 1 : 0;
+  return (x != x) ? 15 : c;
+}
+
+// One 128-element unit of one matrix.  FULL lanes (8 elements inside one row, 16-byte aligned, short
+// exact sequences applicable) use packed arithmetic; every other lane takes the scalar IEEE path.
+__device__ __forceinline__ void r1_unit(const R1Desc& t, long long u, int l16, unsigned hmask, const UConsts& c,
+                                        const UConsts2& c2, const QMapSmem& Sm, const QMapSmem& Sv,
+                                        const LutEnt* __restrict__ lut_m, bool lut_ok) {
+  const long long n = t.n, C = t.C;
+  const long long e0 = u * 128 + l16 * 8;
+  uint8_t* mb = t.m + (e0 >> 1);
+  uint8_t* vb = t.v + (e0 >> 1);
+  const bool has_data = e0 < n;
+  uint32_t mcodes = 0, vcodes = 0;
+  float sm = 0.0f;
+  if (has_data) {
+    mcodes = *reinterpret_cast<const uint32_t*>(mb);
+    vcodes = *reinterpret_cast<const uint32_t*>(vb);
+    sm = t.m_max1[u];
+  }
+  long long r = 0, col = 0;
+  if (has_data) {
+    r = ((e0 | C) >> 32) ? e0 / C : (long long)((unsigned)e0 / (unsigned)C);
+    col = e0 - r * C;
+  }
+  const bool full = c.fast && (e0 + 8 <= n) && (col + 8 <= C);  // C % 8 == 0 and aligned bases: host-checked
+  float m[8], v[8], st_new[8];
+  float am = 0.0f;
+  if (full) {
+    const float ro = __ldg(t.old_r + r), rn = t.new_r[r];
+    const float4 o0 = __ldg(reinterpret_cast<const float4*>(t.old_c + col));
+    const float4 o1 = __ldg(reinterpret_cast<const float4*>(t.old_c + col + 4));
+    const float4 n0 = *reinterpret_cast<const float4*>(t.new_c + col);
+    const float4 n1 = *reinterpret_cast<const float4*>(t.new_c + col + 4);
+    const float st_old[8] = {fminf(ro, o0.x), fminf(ro, o0.y), fminf(ro, o0.z), fminf(ro, o0.w),
+                             fminf(ro, o1.x), fminf(ro, o1.y), fminf(ro, o1.z), fminf(ro, o1.w)};
+    st_new[0] = fminf(rn, n0.x); st_new[1] = fminf(rn, n0.y); st_new[2] = fminf(rn, n0.z); st_new[3] = fminf(rn, n0.w);
+    st_new[4] = fminf(rn, n1.x); st_new[5] = fminf(rn, n1.y); st_new[6] = fminf(rn, n1.z); st_new[7] = fminf(rn, n1.w);
+    f2x4 g, p;
+    {
+      const float4 a0 = *reinterpret_cast<const float4*>(t.g + e0), a1 = *reinterpret_cast<const float4*>(t.g + e0 + 4);
+      const float4 b0 = *reinterpret_cast<const float4*>(t.p + e0), b1 = *reinterpret_cast<const float4*>(t.p + e0 + 4);
+      g.v[0] = f2_pack(a0.x, a0.y); g.v[1] = f2_pack(a0.z, a0.w); g.v[2] = f2_pack(a1.x, a1.y); g.v[3] = f2_pack(a1.z, a1.w);
+      p.v[0] = f2_pack(b0.x, b0.y); p.v[1] = f2_pack(b0.z, b0.w); p.v[2] = f2_pack(b1.x, b1.y); p.v[3] = f2_pack(b1.z, b1.w);
+    }
+    const f2 sm2 = f2_splat(sm);
+    float av = 0.0f;
+    float px[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int k0 = 2 * j, k1 = 2 * j + 1;
+      const f2 m0 = f2_mul(f2_pack(Sm.qmap[(mcodes >> (4 * k0)) & 15u], Sm.qmap[(mcodes >> (4 * k1)) & 15u]), sm2);
+      const f2 v0 = f2_mul(f2_pack(Sv.qmap[(vcodes >> (4 * k0)) & 15u], Sv.qmap[(vcodes >> (4 * k1)) & 15u]),
+                           f2_pack(st_old[k0], st_old[k1]));
+      f2 mj, vj;
+      update_pair(c2, g.v[j], p.v[j], m0, v0, mj, vj, am, av);
+      f2_unpack(mj, m[k0], m[k1]);
+      f2_unpack(vj, v[k0], v[k1]);
+      f2_unpack(p.v[j], px[k0], px[k1]);
+    }
+    *reinterpret_cast<float4*>(t.p + e0) = make_float4(px[0], px[1], px[2], px[3]);
+    *reinterpret_cast<float4*>(t.p + e0 + 4) = make_float4(px[4], px[5], px[6], px[7]);
+  } else {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const long long e = e0 + k;
+      m[k] = 0.0f;
+      v[k] = 0.0f;
+      st_new[k] = 1.0f;
+      if (e < n) {
+        const long long rr = e / C, cc = e - rr * C;
+        const float so = fminf(__ldg(t.old_r + rr), __ldg(t.old_c + cc));
+        st_new[k] = fminf(t.new_r[rr], t.new_c[cc]);
+        const float g = t.g[e];
+        const float m0 = __fmul_rn(Sm.qmap[(mcodes >> (4 * k)) & 15u], sm);
+        const float v0 = __fmul_rn(Sv.qmap[(vcodes >> (4 * k)) & 15u], so);
+        m[k] = lerp_m(c, m0, g);
+        v[k] = upd_v2(c, v0, g);
+        t.p[e] = upd_param(c, t.p[e], m[k], v[k]);
+        am = fmaxf(am, fabsf(m[k]));
+      }
+    }
+  }
+  // first moment: group maximum over the half-warp (every lane takes part), codes of this lane
+  am = hw_max(am, hmask);
+  uint32_t mo = 0;
+  if (udiv_ok(am)) {
+    const f2 r2 = f2_splat(rcp_nr(am)), nam2 = f2_splat(-am);
+#pragma unroll
+    for (int j = 3; j >= 0; --j) {
+      const f2 xj = f2_pack(m[2 * j], m[2 * j + 1]);
+      f2 q = f2_mul(xj, r2);
+      q = f2_fma(f2_fma(q, nam2, xj), r2, q);
+      float qa, qb;
+      f2_unpack(q, qa, qb);
+      mo = (mo << 4) + (uint32_t)(lut_ok ? lut_code(lut_m, qb) : r1_code16(Sm.mids, qb));
+      mo = (mo << 4) + (uint32_t)(lut_ok ? lut_code(lut_m, qa) : r1_code16(Sm.mids, qa));
+    }
+    if (am == 0.0f) mo = 0xFFFFFFFFu;  // 0/0 = NaN -> code 15 for the whole group
+  } else {
+#pragma unroll
+    for (int k = 7; k >= 0; --k) mo = (mo << 4) + (uint32_t)r1_code16(Sm.mids, __fdiv_rn(m[k], am));
+  }
+  // second moment: v / min(new row max, new column max) per element
+  uint32_t vo = 0;
+  bool quick = full && Sv.linear16;
+  if (quick) {
+    float lo = st_new[0], hi = st_new[0];
+#pragma unroll
+    for (int k = 1; k < 8; ++k) {
+      lo = fminf(lo, st_new[k]);
+      hi = fmaxf(hi, st_new[k]);
+    }
+    quick = (lo >= 0x1p-60f) && (hi <= 0x1p60f);
+  }
+  if (quick) {
+    const f2 k16 = f2_splat(16.0f), k15 = f2_splat(-1.5f), one2 = f2_splat(1.0f), mone2 = f2_splat(-1.0f);
+#pragma unroll
+    for (int j = 3; j >= 0; --j) {
+      const f2 dd = f2_pack(st_new[2 * j], st_new[2 * j + 1]), x = f2_pack(v[2 * j], v[2 * j + 1]);
+      const f2 nd = f2_mul(dd, mone2);
+      const f2 r0 = f2_pack(mufu_rcp(st_new[2 * j]), mufu_rcp(st_new[2 * j + 1]));
+      const f2 rr = f2_fma(r0, f2_fma(nd, r0, one2), r0);
+      f2 q = f2_mul(x, rr);
+      q = f2_fma(f2_fma(q, nd, x), rr, q);
+      float ta, tb;
+      f2_unpack(f2_fma(q, k16, k15), ta, tb);
+      const uint32_t ca = __float2uint_ru(ta), cb = __float2uint_ru(tb);
+      vo = (vo << 4) + (cb < 15u ? cb : 15u);
+      vo = (vo << 4) + (ca < 15u ? ca : 15u);
+    }
+  } else {
+    const int zero_v = r1_code16(Sv.mids, 0.0f);
+#pragma unroll
+    for (int k = 7; k >= 0; --k)
+      vo = (vo << 4) + (uint32_t)((e0 + k < n) ? r1_code16(Sv.mids, __fdiv_rn(v[k], st_new[k])) : zero_v);
+  }
+  // the unit lies inside the padded layout (rows of 2048 codes), so all 16 lanes may store
+  *reinterpret_cast<uint32_t*>(mb) = mo;
+  *reinterpret_cast<uint32_t*>(vb) = vo;
+  if (l16 == 0) t.m_max1[u] = am;
+}
+
+__global__ void __launch_bounds__(R1T, 4) r1_update_kernel(const R1Desc* __restrict__ d, int n, long long total_units,
+                                                            const float* __restrict__ qmap_m,
+                                                            const float* __restrict__ qmap_v, const UConsts c) {
+  extern __shared__ __align__(16) unsigned char dyn_smem[];
+  __shared__ QMapSmem Sm, Sv;
+  LutEnt* lut_m = reinterpret_cast<LutEnt*>(dyn_smem);
+  lut_build(Sv, nullptr, qmap_v);
+  lut_build(Sm, lut_m, qmap_m);
+  const bool lut_ok = Sm.valid != 0;
+  const UConsts2 c2 = make_consts2(c);
+  const int l16 = threadIdx.x & 15;
+  const unsigned hmask = 0xFFFFu << (threadIdx.x & 16);
+  long long gi = (long long)blockIdx.x * (R1T / 16) + (threadIdx.x >> 4);
+  const long long stride = (long long)gridDim.x * (R1T / 16);
+  // every half-warp walks gi, gi + stride, ... through the tensors in order; the tensor loop is uniform
+  for (int ti = 0; ti < n; ++ti) {
+    const R1Desc& t = d[ti];
+    const long long uend = (ti + 1 < n) ? d[ti + 1].ustart : total_units;
+    for (; gi < uend; gi += stride) r1_unit(t, gi - t.ustart, l16, hmask, c, c2, Sm, Sv, lut_m, lut_ok);
+  }
+}
+
+}  // namespace lpmm_b200
+
+using namespace lpmm_b200;
+
+// Host side.  `ts`: n tensors that all satisfy lpmm_b200_rank1_multi_ok; `table`: device memory for n
+// descriptors (lpmm_b200_rank1_multi_table_bytes(n)).  Not part of the public header: called by
+// lpmm_b200_adamw4bit_unfused_step_many.
+extern "C" int64_t lpmm_b200_rank1_multi_table_bytes(int n) { return (int64_t)sizeof(R1Desc) * (n > 0 ? n : 0); }
+
+extern "C" int lpmm_b200_rank1_multi_ok(const lpmm_b200_step_tensor* t) {
+  if (!t || t->first || t->numel <= 0 || t->ndim != 2) return 0;
+  if (t->m_mode != LPMM_B200_STATE_GROUP4 || t->v_mode != LPMM_B200_STATE_RANK1_4) return 0;
+  if ((t->m_bits != 0 && t->m_bits != 4) || (t->v_bits != 0 && t->v_bits != 4)) return 0;
+  if (t->m_group != 0 && t->m_group != 128) return 0;
+  if (t->shape[1] % 8 != 0 || t->shape[0] <= 0 || t->shape[0] > 0x7fffffffLL || t->shape[1] > 0x7fffffffLL) return 0;
+  if (t->shape[0] * t->shape[1] != t->numel) return 0;
+  if (!t->p || !t->g || !t->m || !t->m_max1 || !t->v) return 0;
+  for (int i = 0; i < 2; ++i)
+    if (!t->v_max_dims_old[i] || !t->v_max_dims_new[i]) return 0;
+  const uintptr_t a16 = (uintptr_t)t->p | (uintptr_t)t->g | (uintptr_t)t->v_max_dims_old[1] | (uintptr_t)t->v_max_dims_new[1];
+  if (a16 & 15) return 0;
+  if (((uintptr_t)t->m | (uintptr_t)t->v) & 3) return 0;
+  return 1;
+}
+
+extern "C" int lpmm_b200_rank1_multi_step(const lpmm_b200_step_tensor* const* ts, int n, const float* qmap_m,
+                                          const float* qmap_v, double beta1, double beta2, double lr,
+                                          double weight_decay, double eps, double step, void* table,
+                                          int64_t table_bytes, void* stream) {
+  if (n <= 0) return LPMM_B200_OK;
+  if (!ts || !qmap_m || !qmap_v || !table) return LPMM_B200_ERR_NULL_POINTER;
+  if (table_bytes < lpmm_b200_rank1_multi_table_bytes(n)) return LPMM_B200_ERR_BAD_SIZE;
+  cudaStream_t st = (cudaStream_t)stream;
+  static thread_local std::vector<R1Desc> host;
+  host.resize(n);
+  long long total_elems = 0;
+  for (int i = 0; i < n; ++i) {
+    if (!lpmm_b200_rank1_multi_ok(ts[i])) return LPMM_B200_ERR_UNSUPPORTED;
+    total_elems += ts[i]->numel;
+  }
+  // statistics tiles: about six per SM over the whole list, at least 4 rows each
+  const long long target_tiles = (long long)num_sms() * 6;
+  long long per_tile = (total_elems + target_tiles - 1) / target_tiles;
+  if (per_tile < 8192) per_tile = 8192;
+  long long units = 0, tiles = 0;
+  for (int i = 0; i < n; ++i) {
+    const lpmm_b200_step_tensor* t = ts[i];
+    R1Desc& d = host[i];
+    d.p = t->p;
+    d.g = t->g;
+    d.m = reinterpret_cast<uint8_t*>(t->m);
+    d.m_max1 = t->m_max1;
+    d.v = reinterpret_cast<uint8_t*>(t->v);
+    d.old_r = t->v_max_dims_old[0];
+    d.old_c = t->v_max_dims_old[1];
+    d.new_r = t->v_max_dims_new[0];
+    d.new_c = t->v_max_dims_new[1];
+    d.n = t->numel;
+    d.R = (int)t->shape[0];
+    d.C = (int)t->shape[1];
+    d.ustart = units;
+    d.tstart = tiles;
+    int shift = 0;
+    while (shift < 8 && (8 << shift) < d.C) ++shift;  // column-threads: the power of two covering C / 8, at most 256
+    d.tx_shift = shift;
+    d.pad_ = 0;
+    const int tile_cols = 8 << shift;
+    d.tiles_x = (d.C + tile_cols - 1) / tile_cols;
+    const long long width = d.C < tile_cols ? d.C : tile_cols;
+    long long rows = (per_tile + width - 1) / width;
+    if (rows < 4) rows = 4;
+    if (rows > d.R) rows = d.R;
+    d.rows_per_tile = (int)rows;
+    units += (t->numel + 127) / 128;
+    tiles += (long long)d.tiles_x * ((d.R + rows - 1) / rows);
+  }
+  LPMM_CUDA_TRY(cudaMemcpyAsync(table, host.data(), sizeof(R1Desc) * (size_t)n, cudaMemcpyHostToDevice, st));
+  const R1Desc* dev = reinterpret_cast<const R1Desc*>(table);
+  const UConsts c = make_consts(beta1, beta2, lr, weight_decay, eps, step);
+  r1_zero_kernel<<<(unsigned)n, R1T, 0, st>>>(dev);
+  LPMM_CUDA_TRY(cudaGetLastError());
+  long long sgrid = tiles < target_tiles ? tiles : target_tiles;
+  r1_stats_kernel<<<(unsigned)sgrid, R1T, 0, st>>>(dev, n, tiles, qmap_v, c);
+  LPMM_CUDA_TRY(cudaGetLastError());
+  static bool attr_set[64] = {};
+  int devi = 0;
+  cudaGetDevice(&devi);
+  if (devi >= 0 && devi < 64 && !attr_set[devi]) {
+    LPMM_CUDA_TRY(cudaFuncSetAttribute(r1_update_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)R1_DYN_SMEM));
+    attr_set[devi] = true;
+  }
+  long long ugrid = (units + R1T / 16 - 1) / (R1T / 16);
+  const long long ucap = (long long)num_sms() * 4;
+  if (ugrid > ucap) ugrid = ucap;
+  r1_update_kernel<<<(unsigned)ugrid, R1T, R1_DYN_SMEM, st>>>(dev, n, units, qmap_m, qmap_v, c);
+  LPMM_CUDA_TRY(cudaGetLastError());
+  return LPMM_B200_OK;
+}

@@ -1322,6 +1322,14 @@ extern "C" int lpmm_b200_adamw4bit_unfused_step(const lpmm_b200_step_tensor* t, 
   return LPMM_B200_OK;
 }
 
+// rank1_multi.cu: all rank-1 matrices of a list in three launches (internal to the library)
+extern "C" int64_t lpmm_b200_rank1_multi_table_bytes(int n);
+extern "C" int lpmm_b200_rank1_multi_ok(const lpmm_b200_step_tensor* t);
+extern "C" int lpmm_b200_rank1_multi_step(const lpmm_b200_step_tensor* const* ts, int n, const float* qmap_m,
+                                          const float* qmap_v, double beta1, double beta2, double lr,
+                                          double weight_decay, double eps, double step, void* table,
+                                          int64_t table_bytes, void* stream);
+
 // Side streams of lpmm_b200_adamw4bit_unfused_step_many: the tensors of a list are independent and most
 // of them are small (a few launches of a few microseconds each, one waiting for the other), so their
 // launch chains are spread over SIDE_STREAMS streams that fork from the caller's stream and join it
@@ -1371,11 +1379,43 @@ extern "C" int lpmm_b200_adamw4bit_unfused_step_many(const lpmm_b200_step_tensor
            (t->m_group == 0 || t->m_group == 128) && (t->v_group == 0 || t->v_group == 128) && t->m_max1 &&
            t->v_max1 && qmap_m && qmap_v;
   };
+  // rank-1 matrices that share a step count are stepped together (rank1_multi.cu) when the caller's
+  // scratch has room for their descriptor table (taken from its end)
+  // (not while `stream` is being captured: the table is uploaded from pageable host memory)
+  bool capturing = true;
+  {
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(user, &cap) == cudaSuccess) capturing = cap != cudaStreamCaptureStatusNone;
+    else cudaGetLastError();
+  }
+  static thread_local std::vector<const lpmm_b200_step_tensor*> r1;
+  r1.clear();
+  double r1_step = 0.0;
+  for (int i = 0; i < n; ++i) {
+    if (!tensors[i]) return LPMM_B200_ERR_NULL_POINTER;
+    if (!capturing && qmap_m && qmap_v && lpmm_b200_rank1_multi_ok(tensors[i]) &&
+        (r1.empty() || steps[i] == r1_step)) {
+      r1_step = steps[i];
+      r1.push_back(tensors[i]);
+    }
+  }
+  void* r1_table = nullptr;
+  int64_t r1_bytes = 0;
+  if (r1.size() >= 2 && scratch) {
+    r1_bytes = (lpmm_b200_rank1_multi_table_bytes((int)r1.size()) + 255) & ~(int64_t)255;
+    if (r1_bytes <= scratch_bytes) {
+      scratch_bytes = (scratch_bytes - r1_bytes) & ~(int64_t)255;
+      r1_table = static_cast<char*>(scratch) + scratch_bytes;
+    }
+  }
+  if (!r1_table) r1.clear();
+  auto in_r1 = [&](const lpmm_b200_step_tensor* t, double s) {
+    return !r1.empty() && s == r1_step && lpmm_b200_rank1_multi_ok(t);
+  };
   int own = 0;
   int64_t max_need = 0;
   for (int i = 0; i < n; ++i) {
-    if (!tensors[i]) return LPMM_B200_ERR_NULL_POINTER;
-    if (is_plain(tensors[i])) continue;
+    if (is_plain(tensors[i]) || in_r1(tensors[i], steps[i])) continue;
     ++own;
     if (tensors[i]->v_mode == LPMM_B200_STATE_FACTORED) {
       const int64_t need = lpmm_b200_factored_scratch_bytes(tensors[i]->shape, tensors[i]->ndim);
@@ -1383,13 +1423,7 @@ extern "C" int lpmm_b200_adamw4bit_unfused_step_many(const lpmm_b200_step_tensor
     }
   }
   SideStreams* side = nullptr;
-  if (own >= 2) {
-    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-    if (cudaStreamIsCapturing(user, &cap) == cudaSuccess && cap == cudaStreamCaptureStatusNone)
-      side = side_streams_of_current_device();
-    else
-      cudaGetLastError();
-  }
+  if (own >= 2 && !capturing) side = side_streams_of_current_device();
   std::unique_lock<std::mutex> lock;
   if (side) {
     lock = std::unique_lock<std::mutex>(side->mu);
@@ -1424,6 +1458,7 @@ extern "C" int lpmm_b200_adamw4bit_unfused_step_many(const lpmm_b200_step_tensor
       batch.push_back(d);
       continue;
     }
+    if (in_r1(t, steps[i])) continue;  // stepped together below
     cudaStream_t st = user;
     void* sc = scratch;
     int64_t sc_bytes = scratch_bytes;
@@ -1442,6 +1477,9 @@ extern "C" int lpmm_b200_adamw4bit_unfused_step_many(const lpmm_b200_step_tensor
     rc = lpmm_b200_adamw4bit_unfused_step(t, qmap_m, qmap_v, beta1, beta2, lr, weight_decay, eps, steps[i], sc, sc_bytes,
                                           st);
   }
+  if (rc == LPMM_B200_OK && !r1.empty())
+    rc = lpmm_b200_rank1_multi_step(r1.data(), (int)r1.size(), qmap_m, qmap_v, beta1, beta2, lr, weight_decay, eps,
+                                    r1_step, r1_table, r1_bytes, user);
   if (rc == LPMM_B200_OK && !batch.empty())
     rc = lpmm_b200_adamw4bit_unfused_multi_tensor(batch.data(), (int)batch.size(), qmap_m, qmap_v, beta1, beta2, lr,
                                                   weight_decay, eps, batch_step, 0, -1, user);

@@ -1,5 +1,6 @@
-"""``lpmm_b200_adamw4bit_unfused_multi_tensor`` -- the non-fused step of a whole group/group list in one
-launch -- on a B200: the optimizer (``lpmm.optim.AdamW(qconfig=None)``, which reaches it from a
+"""The multi-tensor forms of the non-fused step on a B200.  ``lpmm_b200_adamw4bit_unfused_multi_tensor``
+-- a whole group/group list in one launch -- and the rank-1 matrices of a list stepped together
+(``csrc/rank1_multi.cu``, reached through ``lpmm_b200_adamw4bit_unfused_step_many``): the optimizer (``lpmm.optim.AdamW(qconfig=None)``, which reaches it from a
 tensor's second step on) against the torch-op restatement of the reference, and the entry point itself
 against per-tensor calls of ``lpmm_b200_adamw4bit_unfused_step``, on unaligned views and in group ranges."""
 import ctypes
@@ -27,6 +28,24 @@ def test_optimizer_group_config_ragged_list(qmaps, hyper):
         shapes, p0s, lambda s: [student_t(sh, s * 100003 + i, zero_fraction=0.2) for i, sh in enumerate(shapes)], 7, kw,
         qmaps, "group")
     _check_adamw(opt, params, o_states, o_params, "group")
+
+
+@pytest.mark.parametrize("hyper", [dict(lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01),
+                                   dict(lr=1e-3, betas=(0.9, 0.999), eps=1e-30, weight_decay=0.1)])
+def test_optimizer_rank1_config_many_matrices(qmaps, hyper):
+    """default.yml on a list with several matrices whose rows are multiples of 8 (stepped together from
+    the second step on: one table, three launches), next to shapes that stay on per-tensor launches (odd
+    row length, 4-D, vectors): wide rows that span several statistics tiles, very narrow rows, rows that
+    do not fill a 128-element unit, 20 % exact zeros."""
+    shapes = [(1000, 768), (768, 3072), (130, 4104), (4097, 8), (333, 1024), (1024,), (3, 3, 64, 64), (70, 61),
+              (5000, 16), (4100,)]
+    kw = dict(qconfig="default.yml", **hyper)
+    torch.manual_seed(31)
+    p0s = [torch.randn(s, device=device()) * 0.02 for s in shapes]
+    opt, params, o_states, o_params = _run_pair_adamw(
+        shapes, p0s, lambda s: [student_t(sh, s * 100003 + i, zero_fraction=0.2) for i, sh in enumerate(shapes)], 7, kw,
+        qmaps, "rank1")
+    _check_adamw(opt, params, o_states, o_params, "rank1")
 
 
 def _vp(t):
