@@ -261,12 +261,18 @@ int lpmm_b200_adamw4bit_unfused_multi_tensor(const lpmm_b200_tensor* tensors, in
  * by one launch of it; 2-D RANK1_4 tensors (4-bit codes, group-128 first moment, row length a multiple
  * of 8, 16-byte aligned) that share a step count are stepped together in three launches, their
  * descriptor table (under 256 bytes per tensor) taken from the end of `scratch` -- without enough
- * scratch they are stepped one by one.  The launch chains of the other tensors are spread over four streams owned by the library (created on
+ * scratch they are stepped one by one.  2-D FACTORED tensors (fp32 or 4-bit group-128 first moment,
+ * same shape conditions) that share a step count are likewise stepped together in four launches, their
+ * table and partial sums taken from `scratch` (lpmm_b200_unfused_step_many_scratch_bytes gives a size
+ * that serves everything).  `scratch` should be 256-byte aligned.  The launch chains of the other tensors are spread over four streams owned by the library (created on
  * the first such call on a device, never destroyed); they start after everything already enqueued on
  * `stream`, and `stream` waits for them before the call returns, so the caller's ordering is that of
  * a call that used `stream` alone.  While `stream` is being captured the library's streams are not used.
  * FACTORED tensors run concurrently only if `scratch_bytes` / 4 (rounded down to 256) covers the
  * largest lpmm_b200_factored_scratch_bytes() of the list; otherwise they run one after the other. */
+/* Scratch size with which lpmm_b200_adamw4bit_unfused_step_many takes all its list-wide paths for
+ * these tensors (shapes, modes and pointers alignment are read; `first` is ignored). */
+int64_t lpmm_b200_unfused_step_many_scratch_bytes(const lpmm_b200_step_tensor* const* tensors, int n);
 int lpmm_b200_adamw4bit_unfused_step_many(const lpmm_b200_step_tensor* const* tensors, int n, const float* qmap_m,
                                           const float* qmap_v, double beta1, double beta2, double lr,
                                           double weight_decay, double eps, const double* steps, void* scratch,

@@ -1330,6 +1330,13 @@ extern "C" int lpmm_b200_rank1_multi_step(const lpmm_b200_step_tensor* const* ts
                                           double weight_decay, double eps, double step, void* table,
                                           int64_t table_bytes, void* stream);
 
+// factored_multi.cu: all factored matrices of a list in four launches (internal to the library)
+extern "C" int lpmm_b200_factored_multi_ok(const lpmm_b200_step_tensor* t);
+extern "C" int64_t lpmm_b200_factored_multi_scratch_bytes(const lpmm_b200_step_tensor* const* ts, int n);
+extern "C" int lpmm_b200_factored_multi_step(const lpmm_b200_step_tensor* const* ts, int n, const float* qmap_m,
+                                             double beta1, double beta2, double lr, double weight_decay, double eps,
+                                             double step, void* scratch, int64_t scratch_bytes, void* stream);
+
 // Side streams of lpmm_b200_adamw4bit_unfused_step_many: the tensors of a list are independent and most
 // of them are small (a few launches of a few microseconds each, one waiting for the other), so their
 // launch chains are spread over SIDE_STREAMS streams that fork from the caller's stream and join it
@@ -1358,6 +1365,29 @@ static SideStreams* side_streams_of_current_device() {
     x.state = ok ? 1 : -1;
   }
   return x.state == 1 ? &x : nullptr;
+}
+
+extern "C" int64_t lpmm_b200_unfused_step_many_scratch_bytes(const lpmm_b200_step_tensor* const* tensors, int n) {
+  if (n < 0 || (n > 0 && !tensors)) return LPMM_B200_ERR_BAD_SIZE;
+  std::vector<const lpmm_b200_step_tensor*> fmv;
+  int64_t max_need = 0;
+  int r1n = 0;
+  for (int i = 0; i < n; ++i) {
+    const lpmm_b200_step_tensor* t = tensors[i];
+    if (!t) return LPMM_B200_ERR_NULL_POINTER;
+    if (t->v_mode == LPMM_B200_STATE_FACTORED) {
+      const int64_t need = lpmm_b200_factored_scratch_bytes(t->shape, t->ndim);
+      if (need > max_need) max_need = need;
+      lpmm_b200_step_tensor probe = *t;
+      probe.first = 0;  // sized for the steady state
+      if (lpmm_b200_factored_multi_ok(&probe)) fmv.push_back(t);
+    }
+    if (t->v_mode == LPMM_B200_STATE_RANK1_4) ++r1n;
+  }
+  int64_t total = (int64_t)SIDE_STREAMS * ((max_need + 255) & ~(int64_t)255);
+  if (fmv.size() >= 2) total += (lpmm_b200_factored_multi_scratch_bytes(fmv.data(), (int)fmv.size()) + 511) & ~(int64_t)255;
+  total += (lpmm_b200_rank1_multi_table_bytes(r1n) + 511) & ~(int64_t)255;
+  return total + 1024;
 }
 
 extern "C" int lpmm_b200_adamw4bit_unfused_step_many(const lpmm_b200_step_tensor* const* tensors, int n,
@@ -1412,10 +1442,35 @@ extern "C" int lpmm_b200_adamw4bit_unfused_step_many(const lpmm_b200_step_tensor
   auto in_r1 = [&](const lpmm_b200_step_tensor* t, double s) {
     return !r1.empty() && s == r1_step && lpmm_b200_rank1_multi_ok(t);
   };
+  // factored matrices that share a step count, likewise (factored_multi.cu); their table and partial
+  // sums come from the end of what is left of the scratch
+  static thread_local std::vector<const lpmm_b200_step_tensor*> fm;
+  fm.clear();
+  double fm_step = 0.0;
+  for (int i = 0; i < n; ++i) {
+    if (!capturing && lpmm_b200_factored_multi_ok(tensors[i]) && (fm.empty() || steps[i] == fm_step) &&
+        (tensors[i]->m_mode == LPMM_B200_STATE_FP32 || qmap_m)) {
+      fm_step = steps[i];
+      fm.push_back(tensors[i]);
+    }
+  }
+  void* fm_scratch = nullptr;
+  int64_t fm_bytes = 0;
+  if (fm.size() >= 2 && scratch && (((uintptr_t)scratch & 255) == 0)) {
+    fm_bytes = (lpmm_b200_factored_multi_scratch_bytes(fm.data(), (int)fm.size()) + 255) & ~(int64_t)255;
+    if (fm_bytes <= scratch_bytes) {
+      scratch_bytes = (scratch_bytes - fm_bytes) & ~(int64_t)255;
+      fm_scratch = static_cast<char*>(scratch) + scratch_bytes;
+    }
+  }
+  if (!fm_scratch) fm.clear();
+  auto in_fm = [&](const lpmm_b200_step_tensor* t, double s) {
+    return !fm.empty() && s == fm_step && lpmm_b200_factored_multi_ok(t);
+  };
   int own = 0;
   int64_t max_need = 0;
   for (int i = 0; i < n; ++i) {
-    if (is_plain(tensors[i]) || in_r1(tensors[i], steps[i])) continue;
+    if (is_plain(tensors[i]) || in_r1(tensors[i], steps[i]) || in_fm(tensors[i], steps[i])) continue;
     ++own;
     if (tensors[i]->v_mode == LPMM_B200_STATE_FACTORED) {
       const int64_t need = lpmm_b200_factored_scratch_bytes(tensors[i]->shape, tensors[i]->ndim);
@@ -1458,7 +1513,7 @@ extern "C" int lpmm_b200_adamw4bit_unfused_step_many(const lpmm_b200_step_tensor
       batch.push_back(d);
       continue;
     }
-    if (in_r1(t, steps[i])) continue;  // stepped together below
+    if (in_r1(t, steps[i]) || in_fm(t, steps[i])) continue;  // stepped together below
     cudaStream_t st = user;
     void* sc = scratch;
     int64_t sc_bytes = scratch_bytes;
@@ -1480,6 +1535,9 @@ extern "C" int lpmm_b200_adamw4bit_unfused_step_many(const lpmm_b200_step_tensor
   if (rc == LPMM_B200_OK && !r1.empty())
     rc = lpmm_b200_rank1_multi_step(r1.data(), (int)r1.size(), qmap_m, qmap_v, beta1, beta2, lr, weight_decay, eps,
                                     r1_step, r1_table, r1_bytes, user);
+  if (rc == LPMM_B200_OK && !fm.empty())
+    rc = lpmm_b200_factored_multi_step(fm.data(), (int)fm.size(), qmap_m, beta1, beta2, lr, weight_decay, eps, fm_step,
+                                       fm_scratch, fm_bytes, user);
   if (rc == LPMM_B200_OK && !batch.empty())
     rc = lpmm_b200_adamw4bit_unfused_multi_tensor(batch.data(), (int)batch.size(), qmap_m, qmap_v, beta1, beta2, lr,
                                                   weight_decay, eps, batch_step, 0, -1, user);

@@ -59,23 +59,15 @@ __device__ __forceinline__ UConsts2 make_consts2(const UConsts& c) {
   k.lerp_small = c.lerp_small;
   return k;
 }
-// In: g, p, the old moments m0, v0 (pairs).  Out: m, v, p updated; returns nothing, maxima via am / av.
-__device__ __forceinline__ void update_pair(const UConsts2& k, f2 g, f2& p, f2 m0, f2 v0, f2& m, f2& v, float& am,
-                                            float& av) {
-  const f2 diff = f2_fma(m0, k.mone, g);                       // g - m0
-  m = f2_fma(k.lerp_a, diff, k.lerp_small ? m0 : g);           // lerp
-  v = f2_fma(k.omb2, f2_mul(g, g), f2_mul(v0, k.beta2));       // mul_ then addcmul_
-  float ma, mb, va, vb;
-  f2_unpack(m, ma, mb);
+// p updated from the new moments m, v (pairs): sqrt and division as in sqrt_rn_fast / div_rn_fast.
+__device__ __forceinline__ void param_pair(const UConsts2& k, f2& p, f2 m, f2 v) {
+  float va, vb;
   f2_unpack(v, va, vb);
-  am = fmaxf(am, fmaxf(fabsf(ma), fabsf(mb)));
-  av = fmaxf(av, fmaxf(va, vb));
-  // sqrt(v) as in sqrt_rn_fast
   const f2 y = f2_pack(mufu_rsq(fmaxf(va, 1.17549435e-38f)), mufu_rsq(fmaxf(vb, 1.17549435e-38f)));
   f2 sq = f2_mul(v, y);
   const f2 e = f2_fma(sq, f2_mul(sq, k.mone), v);
   sq = f2_fma(e, f2_mul(k.half, y), sq);
-  // d = sqrt(v) * (1 / bc2s) + eps; m / d as in div_rn_fast, on the negated denominator
+  // d = sqrt(v) * (1 / bc2s) + eps; m / d on the negated denominator
   const f2 d = f2_mul_then_add(sq, k.inv_bc2s, k.eps);  // two roundings, like the torch ops
   const f2 nd = f2_mul(d, k.mone);
   float da, db;
@@ -85,6 +77,25 @@ __device__ __forceinline__ void update_pair(const UConsts2& k, f2 g, f2& p, f2 m
   const f2 q = f2_mul(m, r);
   const f2 quo = f2_fma(f2_fma(nd, q, m), r, q);
   p = f2_fma(k.alpha, quo, f2_mul(p, k.wd_mul));               // addcdiv_ on the decayed parameter
+}
+// First moment of a pair: lerp_(g, 1 - beta1); am collects max |m|.
+__device__ __forceinline__ f2 lerp_pair(const UConsts2& k, f2 g, f2 m0, float& am) {
+  const f2 diff = f2_fma(m0, k.mone, g);                       // g - m0
+  const f2 m = f2_fma(k.lerp_a, diff, k.lerp_small ? m0 : g);
+  float ma, mb;
+  f2_unpack(m, ma, mb);
+  am = fmaxf(am, fmaxf(fabsf(ma), fabsf(mb)));
+  return m;
+}
+// In: g, p, the old moments m0, v0 (pairs).  Out: m, v, p updated; maxima via am / av.
+__device__ __forceinline__ void update_pair(const UConsts2& k, f2 g, f2& p, f2 m0, f2 v0, f2& m, f2& v, float& am,
+                                            float& av) {
+  m = lerp_pair(k, g, m0, am);
+  v = f2_fma(k.omb2, f2_mul(g, g), f2_mul(v0, k.beta2));       // mul_ then addcmul_
+  float va, vb;
+  f2_unpack(v, va, vb);
+  av = fmaxf(av, fmaxf(va, vb));
+  param_pair(k, p, m, v);
 }
 
 // Host side: the constants of one step.

@@ -455,13 +455,19 @@ def adamw4bit_unfused_step(p, g, state, m_quant, v_quant, md_m, md_v, spare, *, 
     spare["plan"] = _make_plan(t, p, g, state, axis_sets, oh_v if rank1 else None)
 
 
+def unfused_step_many_scratch_bytes(ptrs, n):
+    need = int(N.lib.lpmm_b200_unfused_step_many_scratch_bytes(ptrs, n))
+    if need < 0:
+        N.check(need)
+    return need
+
+
 def adamw4bit_unfused_step_many(ptrs, n, qm, qv, steps, scratch_need, device, *, beta1, beta2, lr, weight_decay, eps):
     """``ptrs``: ctypes array of n addresses of ``lpmm_b200_step_tensor`` descriptors (kept alive and up
-    to date by the caller), ``steps``: ctypes array of n doubles.  The caller guarantees that ``device``
-    is the current device."""
-    # four slices (the library steps factored tensors on up to four streams at once, each with its own slice) and
-    # room for the descriptor table of the rank-1 matrices it steps together (under 256 bytes each)
-    scratch = _scratch_for(device, 4 * (scratch_need + 256) + 256 * (n + 1))
+    to date by the caller), ``steps``: ctypes array of n doubles, ``scratch_need``: what
+    ``unfused_step_many_scratch_bytes`` returned for them.  The caller guarantees that ``device`` is the
+    current device."""
+    scratch = _scratch_for(device, scratch_need)
     N.check(N.lib.lpmm_b200_adamw4bit_unfused_step_many(ptrs, n, _ptr(qm), _ptr(qv), beta1, beta2, lr, weight_decay, eps,
                                                         steps, _ptr(scratch), scratch.numel() if scratch is not None else 0,
                                                         _stream()))

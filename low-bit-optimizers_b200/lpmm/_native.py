@@ -108,6 +108,7 @@ def _load():
         "lpmm_b200_adamw4bit_unfused_step": (i32, [ctypes.POINTER(StepTensor), vp, vp] + [d] * 6 + [vp, i64, vp]),
         "lpmm_b200_adamw4bit_unfused_multi_tensor": (i32, [ctypes.POINTER(Tensor), i32, vp, vp] + [d] * 6
                                                      + [i64, i64, vp]),
+        "lpmm_b200_unfused_step_many_scratch_bytes": (i64, [ctypes.POINTER(vp), i32]),
         "lpmm_b200_adamw4bit_unfused_step_many": (i32, [ctypes.POINTER(vp), i32, vp, vp] + [d] * 5
                                                   + [ctypes.POINTER(d), vp, i64, vp]),
         "lpmm_b200_factored_scratch_bytes": (i64, [ctypes.POINTER(i64), i32]),

@@ -263,7 +263,7 @@ class AdamW(LowBitOptimizer):
         self._batches[gi] = dict(params=list(params), plans=plans, states=states, spares=spares, ptrs=ptrs, addrs=addrs,
                                  steps=(ctypes.c_double * n)(), device=cur, qm=states[0]["exp_avg_qstate"]["qmap"],
                                  qv=states[0]["exp_avg_sq_qstate"]["qmap"],
-                                 scratch=max([pl.scratch or 0 for pl in plans] + [0]))
+                                 scratch=_kernels.unfused_step_many_scratch_bytes(ptrs, n))
 
     def _step_single_batched(self, gi, group, params):
         """All tensors of a non-fused group through one library call.  Returns False (after dropping the

@@ -48,6 +48,21 @@ def test_optimizer_rank1_config_many_matrices(qmaps, hyper):
     _check_adamw(opt, params, o_states, o_params, "rank1")
 
 
+def test_optimizer_factored_many_matrices(qmaps):
+    """factor_second_moment=True on a list with several matrices (stepped together from the second step
+    on: partial sums, reduction, row means and update in four launches), fp32 and 4-bit first moments,
+    next to shapes that stay on per-tensor launches (odd row length, 4-D) and vectors.  Accumulators and
+    parameters to 1e-6 relative (fixed summation order, not torch's); first-moment codes identical."""
+    shapes = [(1000, 768), (768, 3072), (130, 4104), (40, 8), (333, 1024), (1024,), (2, 3, 32, 32), (70, 61),
+              (5000, 16), (4100,), (64, 64)]
+    kw = dict(qconfig=None, factor_second_moment=True, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01)
+    torch.manual_seed(41)
+    p0s = [torch.randn(s, device=device()) * 0.02 for s in shapes]
+    opt, params, o_states, o_params = _run_pair_adamw(
+        shapes, p0s, lambda s: [student_t(sh, s * 100003 + i) for i, sh in enumerate(shapes)], 7, kw, qmaps, "group")
+    _check_adamw(opt, params, o_states, o_params, "group", factored=True)
+
+
 def _vp(t):
     return ctypes.c_void_p(t.data_ptr() if t is not None else None)
 
