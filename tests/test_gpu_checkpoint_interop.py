@@ -9,7 +9,7 @@ import numpy as np
 import pytest
 import torch
 
-from golden_cases import CASES, THRESHOLD
+from golden_cases import CASES, THRESHOLD, layout
 from gpu_helpers import bits_equal, device, student_t
 
 pytestmark = pytest.mark.gpu
@@ -19,7 +19,8 @@ def _t(a):
     return torch.from_numpy(np.ascontiguousarray(a))
 
 
-@pytest.mark.parametrize("name", ["adamw_rank1", "adamw_group"])
+@pytest.mark.parametrize("name", ["adamw_rank1", "adamw_group", "adamw_8bit", "adamw_5bit", "adamw_m_group_512",
+                                  "adamw_m_group_4096"])
 def test_reference_layout_state_dict_loads_and_continues(golden_dir, qmaps, name):
     import lpmm
     from lpmm.config import CONFIG_DIR, get_config
@@ -27,10 +28,11 @@ def test_reference_layout_state_dict_loads_and_continues(golden_dir, qmaps, name
     z = np.load(os.path.join(golden_dir, f"python_{name}.npz"))
     G = {k: z[k] for k in z.files}
     _, kw, shapes = CASES[name]
-    rank1 = kw["qconfig"] == "default.yml"
-    cfg_path = os.path.join(CONFIG_DIR, "default.yml") if rank1 else None
+    L = layout(name)
+    rank1 = L["v_scale"] == "rank1"
+    cfg_path = os.path.join(CONFIG_DIR, kw["qconfig"]) if kw["qconfig"] else None
     steps = int(G["steps"])
-    qm_cpu, qv_cpu = _t(qmaps["m"]), _t(qmaps["v"])
+    qm_cpu, qv_cpu = _t(qmaps[L["maps"][0]]), _t(qmaps[L["maps"][1]])
 
     # ---- a state_dict as the reference writes it (CPU tensors, as torch.save / torch.load would give)
     state, o_states = {}, []
@@ -80,7 +82,8 @@ def test_reference_layout_state_dict_loads_and_continues(golden_dir, qmaps, name
     for i, (op, g) in enumerate(zip(o_params, grads)):
         quant = op.numel() > THRESHOLD
         T.adamw_step(op, g, o_states[i], qm, qv, m_quant=quant, v_quant=quant, v_scale_type="rank1" if rank1 else "group",
-                     beta1=0.9, beta2=0.999, lr=1e-3, weight_decay=0.01, eps=1e-8, step=float(steps + 1))
+                     beta1=0.9, beta2=0.999, lr=1e-3, weight_decay=0.01, eps=1e-8, step=float(steps + 1),
+                     m_gp_sz=L["m_gp"])
     torch.cuda.synchronize()
     for i, p in enumerate(params):
         assert bits_equal(p.detach(), o_params[i]), f"tensor {i}: params differ after the resumed step"
