@@ -197,6 +197,22 @@ int lpmm_b200_quant_rank1(const float* x, const int64_t* shape, int ndim, const 
 int lpmm_b200_dequant_rank1(const int8_t* codes, const float* qmap, int bits, const float* const* max_dims,
                             const int64_t* shape, int ndim, float* out, void* stream);
 
+/* Stochastic rounding (round_type 'real-sr': pack_nonlinear(..., stochastic=True),
+ * quantization_kernel.cu:397-427, 431-459, 517-537).  Between the two neighbouring map values the
+ * upper one is taken with probability (x - lower) / (upper - lower).  The uniforms are those of the
+ * reference: curand Philox4_32_10, one subsequence per reference thread (8 consecutive elements of the
+ * padded layout for 4-bit codes, 4 for wider ones), started at (seed, offset) -- the pair the reference
+ * takes from torch's default CUDA generator with philox_engine_inputs(16384) (4-bit) or (8192) (wider)
+ * on every pack_nonlinear call, stochastic or not.  The caller reads and advances the generator.  With
+ * the same (seed, offset) the codes equal the reference's bit for bit; a NaN gives the last code (the
+ * reference reads before the start of its map there).  n must be a multiple of 8 in the pack call. */
+int lpmm_b200_pack_nonlinear_sr(const float* data, int64_t n, const float* qmap, int bits, int8_t* packed,
+                                uint64_t seed, uint64_t offset, void* stream);
+int lpmm_b200_quant_group_sr(const float* x, int64_t numel, const float* qmap, int bits, int64_t group_size,
+                             int8_t* codes, float* max1, uint64_t seed, uint64_t offset, void* stream);
+int lpmm_b200_quant_rank1_sr(const float* x, const int64_t* shape, int ndim, const float* qmap, int bits,
+                             float* const* max_dims, int8_t* codes, uint64_t seed, uint64_t offset, void* stream);
+
 /* ------------------------------------------------------------------------------------------- */
 /* One-launch-per-tensor steps with the arithmetic of the reference's non-fused Python path     */
 /* ------------------------------------------------------------------------------------------- */

@@ -21,6 +21,7 @@
 // one half-warp; larger groups (256 ... 4096, powers of two) are 2 ... 32 adjacent half-warps of one
 // CTA whose maxima are combined through shared memory.
 #include <cooperative_groups.h>
+#include <curand_kernel.h>
 #include <math.h>
 
 #include <mutex>
@@ -800,7 +801,68 @@ __global__ void __launch_bounds__(UTMAX, 2) sgd_kernel(float* __restrict__ p, co
 // ---------------------------------------------------------------------------------------------
 // Standalone quantize / dequantize
 // ---------------------------------------------------------------------------------------------
+// Stochastic rounding as in quantize_bsearch<true> (quantization_kernel.cu:397-427): between the two
+// neighbouring map values the upper one is taken with probability (x - lower) / (upper - lower), decided
+// by `noise`, a uniform in (0, 1] from the Philox stream of the reference's thread that handles the
+// element.  A NaN (where the reference reads before the start of its map) gives the last code.
+__device__ __forceinline__ int sr_code(const float* __restrict__ q, int nq, float x, float noise) {
+  if (x <= q[0]) return 0;
+  if (q[nq - 1] <= x) return nq - 1;
+  int lo = 0, hi = nq;
+  while (lo < hi) {
+    const int mi = (lo + hi) >> 1;
+    if (q[mi] <= x) lo = mi + 1;
+    else hi = mi;
+  }
+  if (lo == 0) return nq - 1;
+  const float proba = __fdiv_rn(__fsub_rn(x, q[lo - 1]), __fsub_rn(q[lo], q[lo - 1]));
+  const int flag = __float2int_rn(__fsub_rn(__fadd_rn(proba, noise), 0.5f));
+  return flag ? lo : lo - 1;
+}
+// The uniforms of the 8 elements that start at padded-layout index e0, drawn exactly as the reference's
+// pack kernels draw them: one Philox4_32_10 stream per thread (subsequence = thread index), a thread
+// owning 8 consecutive elements in the two-codes-per-byte kernel (quantization_kernel.cu:431-459) and 4
+// in the one-code-per-byte kernel (:517-537), one curand_uniform per element in element order.
+template <bool W>
+__device__ __forceinline__ void sr_noise8(unsigned long long seed, unsigned long long offset, long long e0,
+                                          float* noise) {
+  curandStatePhilox4_32_10_t st;
+  if (W) {
+    curand_init(seed, (unsigned long long)(e0 >> 2), offset, &st);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) noise[k] = curand_uniform(&st);
+    curand_init(seed, (unsigned long long)(e0 >> 2) + 1, offset, &st);
+#pragma unroll
+    for (int k = 4; k < 8; ++k) noise[k] = curand_uniform(&st);
+  } else {
+    curand_init(seed, (unsigned long long)(e0 >> 3), offset, &st);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) noise[k] = curand_uniform(&st);
+  }
+}
+
 // pack / unpack of already normalised values (quantization_kernel.cu:429-460, 515-537, 603-627, 655-672)
+// Stochastic pack: one thread per 8 elements (n is a multiple of 8 here, as in the reference).
+template <bool W>
+__global__ void __launch_bounds__(UT) pack_sr_kernel(const float* __restrict__ x, long long n,
+                                                      const float* __restrict__ qmap, int bits,
+                                                      uint8_t* __restrict__ out, unsigned long long seed,
+                                                      unsigned long long offset) {
+  __shared__ Maps M;
+  load_maps<W>(M, qmap, nullptr, bits, 4);
+  const int nq = 1 << bits;
+  for (long long ch = (long long)blockIdx.x * UT + threadIdx.x; ch < n / 8; ch += (long long)gridDim.x * UT) {
+    const long long e0 = ch * 8;
+    float noise[8];
+    sr_noise8<W>(seed, offset, e0, noise);
+    Codes8<W> c;
+    c.clear();
+#pragma unroll
+    for (int k = 0; k < 8; ++k) c.set(k, sr_code(M.qm, nq, x[e0 + k], noise[k]));
+    c.store(out + Codes8<W>::byte_off(e0));
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0) out[W ? n : n / 2] = 0;
+}
 template <bool W>
 __global__ void __launch_bounds__(UT) pack_kernel(const float* __restrict__ x, long long n,
                                                    const float* __restrict__ qmap, int bits,
@@ -832,11 +894,13 @@ __global__ void __launch_bounds__(UT) unpack_kernel(const uint8_t* __restrict__ 
   }
 }
 // mode 0: group scales (computes max1); mode 1: rank-1 scales from given per-axis maxima.
-template <int MODE, int ND, bool W>
+// SR: stochastic rounding with the reference's random stream (seed, offset); else round to nearest.
+template <int MODE, int ND, bool W, bool SR = false>
 __global__ void __launch_bounds__(UTMAX, 2) quant_kernel(const float* __restrict__ x, long long n, long long units,
                                                        const float* __restrict__ qmap, int bits, int hpg, int sh,
                                                        uint8_t* __restrict__ codes, float* __restrict__ max1,
-                                                       const StepArgs a) {
+                                                       const StepArgs a, unsigned long long seed = 0,
+                                                       unsigned long long offset = 0) {
   __shared__ Maps M;
   __shared__ float red[UTMAX / 16];
   load_maps<W>(M, qmap, nullptr, bits, 4);
@@ -863,7 +927,22 @@ __global__ void __launch_bounds__(UTMAX, 2) quant_kernel(const float* __restrict
       if (MODE == 1 && e0 < n) advance<ND>(co, a.s);
     }
     Codes8<W> out;
-    if (MODE == 0) {
+    if (SR) {
+      // normalise with IEEE division (torch's div), then the reference's stochastic rule; padding behind
+      // the last group is a zero, which the rule maps to the code of zero whatever the noise
+      if (MODE == 0) ax = group_max(hmax16(ax, hmask), hpg, red);
+      float noise[8];
+      sr_noise8<W>(seed, offset, e0, noise);
+      const int nq = 1 << bits;
+      out.clear();
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const bool inside = (MODE == 0) ? (u < in_units) : (e0 + k < n);
+        const float xn = inside ? __fdiv_rn(xv[k], MODE == 0 ? ax : st[k]) : 0.0f;
+        out.set(k, sr_code(M.qm, nq, xn, noise[k]));
+      }
+      if (MODE == 0 && u < in_units && l16 == 0 && (u & (hpg - 1)) == 0) max1[u >> sh] = ax;
+    } else if (MODE == 0) {
       ax = group_max(hmax16(ax, hmask), hpg, red);
       if (u < in_units) {
         out = codes_by_group_scale<W>(M.mm, bits, xv, ax);
@@ -1017,6 +1096,20 @@ extern "C" int lpmm_b200_pack_nonlinear(const float* data, int64_t n, const floa
   LPMM_CUDA_TRY(cudaGetLastError());
   return LPMM_B200_OK;
 }
+extern "C" int lpmm_b200_pack_nonlinear_sr(const float* data, int64_t n, const float* qmap, int bits, int8_t* packed,
+                                           uint64_t seed, uint64_t offset, void* stream) {
+  Layout l;
+  const int rc = make_layout(bits, 128, &l);
+  if (rc) return rc;
+  if (n < 0 || (n & 7)) return LPMM_B200_ERR_BAD_SIZE;
+  if (!qmap || !packed || (n > 0 && !data)) return LPMM_B200_ERR_NULL_POINTER;
+  if (!aligned_for(packed, l.wide)) return LPMM_B200_ERR_BAD_SIZE;
+  LPMM_DISPATCH_W(l.wide, (pack_sr_kernel<W><<<grid_for(n / 8, UT), UT, 0, (cudaStream_t)stream>>>(
+                              data, n, qmap, l.bits, (uint8_t*)packed, seed, offset)));
+  LPMM_CUDA_TRY(cudaGetLastError());
+  return LPMM_B200_OK;
+}
+
 extern "C" int lpmm_b200_pack_nonlinear4(const float* data, int64_t n, const float* qmap, int8_t* packed,
                                          void* stream) {
   return lpmm_b200_pack_nonlinear(data, n, qmap, 4, packed, stream);
@@ -1056,6 +1149,23 @@ extern "C" int lpmm_b200_quant_group(const float* x, int64_t numel, const float*
   LPMM_CUDA_TRY(cudaGetLastError());
   return LPMM_B200_OK;
 }
+extern "C" int lpmm_b200_quant_group_sr(const float* x, int64_t numel, const float* qmap, int bits, int64_t group_size,
+                                        int8_t* codes, float* max1, uint64_t seed, uint64_t offset, void* stream) {
+  Layout l;
+  const int rc = make_layout(bits, group_size, &l);
+  if (rc) return rc;
+  if (numel < 0) return LPMM_B200_ERR_BAD_SIZE;
+  if (!qmap || !codes || (numel > 0 && (!x || !max1))) return LPMM_B200_ERR_NULL_POINTER;
+  if (!aligned_for(codes, l.wide)) return LPMM_B200_ERR_BAD_SIZE;
+  StepArgs a = {};
+  const long long units = padded_units(numel, 128LL * l.hpg);
+  const int th = threads_for(l.hpg);
+  LPMM_DISPATCH_W(l.wide, (quant_kernel<0, 2, W, true><<<grid_for(units, th / 16), th, 0, (cudaStream_t)stream>>>(
+                              x, numel, units, qmap, l.bits, l.hpg, l.sh, (uint8_t*)codes, max1, a, seed, offset)));
+  LPMM_CUDA_TRY(cudaGetLastError());
+  return LPMM_B200_OK;
+}
+
 extern "C" int lpmm_b200_quant_group4(const float* x, int64_t numel, const float* qmap, int8_t* codes, float* max1,
                                       void* stream) {
   return lpmm_b200_quant_group(x, numel, qmap, 4, 128, codes, max1, stream);
@@ -1124,6 +1234,29 @@ extern "C" int lpmm_b200_quant_rank1(const float* x, const int64_t* shape, int n
   LPMM_CUDA_TRY(cudaGetLastError());
   return LPMM_B200_OK;
 }
+extern "C" int lpmm_b200_quant_rank1_sr(const float* x, const int64_t* shape, int ndim, const float* qmap, int bits,
+                                        float* const* max_dims, int8_t* codes, uint64_t seed, uint64_t offset,
+                                        void* stream) {
+  Layout l;
+  int rc = make_layout(bits, 128, &l);
+  if (rc) return rc;
+  if (ndim < 2) return LPMM_B200_ERR_BAD_SIZE;
+  rc = lpmm_b200_axis_absmax(x, shape, ndim, max_dims, stream);
+  if (rc) return rc;
+  if (!qmap || !codes) return LPMM_B200_ERR_NULL_POINTER;
+  if (!aligned_for(codes, l.wide)) return LPMM_B200_ERR_BAD_SIZE;
+  StepArgs a = {};
+  fill_shape(a.s, shape, ndim, &a.n);
+  for (int i = 0; i < ndim; ++i) a.v_new[i] = max_dims[i];
+  const long long units = pad_to(a.n, 2048) / 128;
+  LPMM_DISPATCH_W(l.wide, LPMM_DISPATCH_ND(ndim, (quant_kernel<1, ND, W, true><<<grid_for(units, UT / 16), UT, 0,
+                                                                                  (cudaStream_t)stream>>>(
+                                                     x, a.n, units, qmap, l.bits, 1, 0, (uint8_t*)codes, nullptr, a, seed,
+                                                     offset))));
+  LPMM_CUDA_TRY(cudaGetLastError());
+  return LPMM_B200_OK;
+}
+
 extern "C" int lpmm_b200_quant_rank1_4(const float* x, const int64_t* shape, int ndim, const float* qmap,
                                        float* const* max_dims, int8_t* codes, void* stream) {
   return lpmm_b200_quant_rank1(x, shape, ndim, qmap, 4, max_dims, codes, stream);

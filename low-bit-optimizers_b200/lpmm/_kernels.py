@@ -150,16 +150,27 @@ def _ptr_array(tensors):
     return (_vp * max(len(tensors), 1))(*[t.data_ptr() for t in tensors])
 
 
+def philox_inputs(device, bits):
+    """What the reference's pack kernels take from torch's default CUDA generator on every call,
+    stochastic or not (``gen->philox_engine_inputs(group_size * work_per_thread)`` with group_size 2048,
+    quantization_kernel.cu:479-487, 556-564): returns ``(seed, offset)`` and advances the generator's
+    offset by 16384 (4-bit codes) or 8192 (wider codes)."""
+    gen = torch.cuda.default_generators[device.index if device.index is not None else torch.cuda.current_device()]
+    offset = gen.get_offset()
+    gen.set_offset(offset + (16384 if bits == 4 else 8192))
+    return gen.initial_seed(), offset
+
+
 def pack_nonlinear(data, qmap, bits, stochastic):
-    """``quantization.pack_nonlinear`` (reference quantization.cc:54-63)."""
+    """``quantization.pack_nonlinear`` (reference quantization.cc:54-63).  ``stochastic=True`` draws from
+    torch's default CUDA generator exactly as the reference does (same codes for the same generator
+    state); ``stochastic=False`` leaves the generator alone (the reference advances it there too)."""
     if bits > 8:
         raise RuntimeError("bits <= 8")
     _check_cuda_float(data, "data")
     _check_cuda_float(qmap, "qmap")
     if data.dim() != 2 or qmap.dim() != 1:
         raise RuntimeError("The dimension of data / qmap is not correct!")
-    if stochastic:
-        raise NotImplementedError("only the round-to-nearest pack is built in this implementation")
     _check_layout(bits)
     _check_qmap(qmap, bits)
     if data.shape[1] % (8 if bits == 4 else 4) != 0:
@@ -167,7 +178,13 @@ def pack_nonlinear(data, qmap, bits, stochastic):
     n = data.numel()
     out = torch.empty((n // 2 if bits == 4 else n) + 1, dtype=torch.int8, device=data.device)
     with torch.cuda.device(data.device):
-        N.check(N.lib.lpmm_b200_pack_nonlinear(_ptr(data), n, _ptr(qmap), bits, _ptr(out), _stream()))
+        if stochastic:
+            if n % 8 != 0:
+                raise NotImplementedError("the stochastic pack needs a multiple of 8 values")
+            seed, offset = philox_inputs(data.device, bits)
+            N.check(N.lib.lpmm_b200_pack_nonlinear_sr(_ptr(data), n, _ptr(qmap), bits, _ptr(out), seed, offset, _stream()))
+        else:
+            N.check(N.lib.lpmm_b200_pack_nonlinear(_ptr(data), n, _ptr(qmap), bits, _ptr(out), _stream()))
     return out
 
 
@@ -198,7 +215,8 @@ def _groups(n, gp_sz):
     return (n + gp_sz - 1) // gp_sz
 
 
-def quant_group(x, qmap, gp_sz, bits=4):
+def quant_group(x, qmap, gp_sz, bits=4, sr=None):
+    """``sr``: ``(seed, offset)`` from ``philox_inputs`` for stochastic rounding, None for nearest."""
     _check_layout(bits, gp_sz)
     _check_qmap(qmap, bits)
     _check_cuda_float(x, "x")
@@ -207,8 +225,12 @@ def quant_group(x, qmap, gp_sz, bits=4):
     codes = torch.empty(packed_len(groups * gp_sz, bits), dtype=torch.int8, device=x.device)
     max1 = torch.empty((groups, 1), dtype=torch.float32, device=x.device)
     with torch.cuda.device(x.device):
-        N.check(N.lib.lpmm_b200_quant_group(_ptr(x), n, _ptr(_qmap_on(qmap, x.device)), bits, gp_sz, _ptr(codes),
-                                            _ptr(max1), _stream()))
+        if sr is not None:
+            N.check(N.lib.lpmm_b200_quant_group_sr(_ptr(x), n, _ptr(_qmap_on(qmap, x.device)), bits, gp_sz, _ptr(codes),
+                                                   _ptr(max1), sr[0], sr[1], _stream()))
+        else:
+            N.check(N.lib.lpmm_b200_quant_group(_ptr(x), n, _ptr(_qmap_on(qmap, x.device)), bits, gp_sz, _ptr(codes),
+                                                _ptr(max1), _stream()))
     return codes, max1
 
 
@@ -251,7 +273,7 @@ def axis_absmax(x):
     return vecs
 
 
-def quant_rank1(x, qmap, bits=4):
+def quant_rank1(x, qmap, bits=4, sr=None):
     _check_layout(bits)
     _check_qmap(qmap, bits)
     _check_cuda_float(x, "x")
@@ -260,8 +282,14 @@ def quant_rank1(x, qmap, bits=4):
     vecs = _axis_vectors(tuple(x.shape), x.device)
     codes = torch.empty(packed_len(x.numel(), bits), dtype=torch.int8, device=x.device)
     with torch.cuda.device(x.device):
-        N.check(N.lib.lpmm_b200_quant_rank1(_ptr(x), _i64_array(list(x.shape)), x.dim(), _ptr(_qmap_on(qmap, x.device)),
-                                            bits, _ptr_array(vecs), _ptr(codes), _stream()))
+        if sr is not None:
+            N.check(N.lib.lpmm_b200_quant_rank1_sr(_ptr(x), _i64_array(list(x.shape)), x.dim(),
+                                                   _ptr(_qmap_on(qmap, x.device)), bits, _ptr_array(vecs), _ptr(codes),
+                                                   sr[0], sr[1], _stream()))
+        else:
+            N.check(N.lib.lpmm_b200_quant_rank1(_ptr(x), _i64_array(list(x.shape)), x.dim(),
+                                                _ptr(_qmap_on(qmap, x.device)), bits, _ptr_array(vecs), _ptr(codes),
+                                                _stream()))
     return codes, vecs
 
 
@@ -471,6 +499,41 @@ def adamw4bit_unfused_step_many(ptrs, n, qm, qv, steps, scratch_need, device, *,
     N.check(N.lib.lpmm_b200_adamw4bit_unfused_step_many(ptrs, n, _ptr(qm), _ptr(qv), beta1, beta2, lr, weight_decay, eps,
                                                         steps, _ptr(scratch), scratch.numel() if scratch is not None else 0,
                                                         _stream()))
+
+
+def adamw_fp32_moments_step(p, g, m, v, row, col, *, beta1, beta2, lr, weight_decay, eps, step):
+    """One non-fused step on fp32 moments given as plain tensors (``v`` None: factored, ``row`` / ``col``
+    are the accumulators).  Used where the moments are quantized outside the step (stochastic rounding)."""
+    _check_param_grad(p, g)
+    _check_cuda_float(m, "exp_avg")
+    t = N.StepTensor()
+    t.p, t.g, t.numel, t.ndim, t.first = p.data_ptr(), g.data_ptr(), p.numel(), max(p.dim(), 1), 0
+    for i, d in enumerate(p.shape):
+        t.shape[i] = d
+    t.m_mode, t.m = N.STATE_FP32, m.data_ptr()
+    scratch = None
+    if v is not None:
+        _check_cuda_float(v, "exp_avg_sq")
+        t.v_mode, t.v = N.STATE_FP32, v.data_ptr()
+    else:
+        _check_cuda_float(row, "exp_avg_sq_row")
+        _check_cuda_float(col, "exp_avg_sq_col")
+        t.v_mode, t.row, t.col = N.STATE_FACTORED, row.data_ptr(), col.data_ptr()
+        need = int(N.lib.lpmm_b200_factored_scratch_bytes(_i64_array(list(p.shape)), p.dim()))
+        scratch = _scratch_for(p.device, need)
+    with torch.cuda.device(p.device):
+        N.check(N.lib.lpmm_b200_adamw4bit_unfused_step(ctypes.byref(t), None, None, beta1, beta2, lr, weight_decay, eps,
+                                                       step, _ptr(scratch), scratch.numel() if scratch is not None else 0,
+                                                       _stream()))
+
+
+def sgd_fp32_buffer_step(p, g, buf, first, *, weight_decay, momentum, lr, dampening, nesterov, maximize):
+    """Momentum SGD on an fp32 buffer given as a plain tensor (``first``: it receives the decayed gradient)."""
+    _check_param_grad(p, g)
+    with torch.cuda.device(p.device):
+        N.check(N.lib.lpmm_b200_sgd_lowbit_step(_ptr(p), _ptr(g), p.numel(), _ptr(buf), None, N.STATE_FP32, 4, 128,
+                                                int(first), None, weight_decay, momentum, lr, dampening,
+                                                int(bool(nesterov)), int(bool(maximize)), _stream()))
 
 
 def adamw4bit_factored_step(p, g, state, m_quant, md_m, *, beta1, beta2, lr, weight_decay, eps, step, spare=None):

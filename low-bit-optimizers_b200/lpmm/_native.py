@@ -103,6 +103,10 @@ def _load():
         "lpmm_b200_dequant_group": (i32, [vp, vp, i32, i64, vp, i64, vp, vp]),
         "lpmm_b200_quant_rank1": (i32, [vp, ctypes.POINTER(i64), i32, vp, i32, ctypes.POINTER(vp), vp, vp]),
         "lpmm_b200_dequant_rank1": (i32, [vp, vp, i32, ctypes.POINTER(vp), ctypes.POINTER(i64), i32, vp, vp]),
+        "lpmm_b200_pack_nonlinear_sr": (i32, [vp, i64, vp, i32, vp, ctypes.c_uint64, ctypes.c_uint64, vp]),
+        "lpmm_b200_quant_group_sr": (i32, [vp, i64, vp, i32, i64, vp, vp, ctypes.c_uint64, ctypes.c_uint64, vp]),
+        "lpmm_b200_quant_rank1_sr": (i32, [vp, ctypes.POINTER(i64), i32, vp, i32, ctypes.POINTER(vp), vp, ctypes.c_uint64,
+                                           ctypes.c_uint64, vp]),
         "lpmm_b200_sgd_lowbit_step": (i32, [vp, vp, i64, vp, vp, i32, i32, i64, i32, vp, d, d, d, d, i32, i32, vp]),
         "lpmm_b200_sgd4bit_multi_tensor": (i32, [ctypes.POINTER(Tensor), i32, vp, d, d, d, d, i32, i32, i64, i64, vp]),
         "lpmm_b200_adamw4bit_unfused_step": (i32, [ctypes.POINTER(StepTensor), vp, vp] + [d] * 6 + [vp, i64, vp]),

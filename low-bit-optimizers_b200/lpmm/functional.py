@@ -4,7 +4,8 @@ The maps are built with the same torch calls as the reference so their fp32 valu
 identical (functional.py:244-315, 644-656).  ``vectorwise_quant`` / ``vectorwise_dequant`` keep the
 reference's signature and metadata dictionaries for the configurations of the low-bit optimizers
 -- ``scale_type`` 'group' (128 ... 4096) or 'rank1', ``quant_type`` 'nonlinear' or 'power-*',
-``round_type`` 'real-nearest', 4 to 8 bits -- and run on the CUDA library; anything else raises.
+``round_type`` 'real-nearest' or 'real-sr', 4 to 8 bits -- and run on the CUDA library; anything else
+raises.
 """
 import torch
 
@@ -135,8 +136,8 @@ def _check_supported(kwargs):
         raise ValueError(f"Not support {kwargs['quant_type']} quant type.")
     if kwargs["b"] not in _kernels.SUPPORTED_BITS:
         raise NotImplementedError(f"code widths {_kernels.SUPPORTED_BITS} are built in this implementation")
-    if kwargs["round_type"] != "real-nearest":
-        raise NotImplementedError("only round_type='real-nearest' is built in this implementation")
+    if kwargs["round_type"] not in ("real-nearest", "real-sr"):
+        raise NotImplementedError("only round_type 'real-nearest' and 'real-sr' are built in this implementation")
     if kwargs["scale_type"] not in ("group", "rank1"):
         raise NotImplementedError("only scale_type 'group' and 'rank1' are built in this implementation")
 
@@ -152,16 +153,24 @@ def vectorwise_quant(x, **kwargs):
     x = x.detach()
     md = {"dtype": x.dtype, "stride": x.stride()}
     xc = x.contiguous()
+    # 'real-sr': the (seed, offset) the reference's pack kernel would take from torch's CUDA generator;
+    # ``mimic_rng`` (set by the optimizers when any state is stochastic) advances the generator for a
+    # nearest-rounded state too, as the reference's pack call does, so that later draws line up
+    sr = None
+    if kwargs["round_type"] == "real-sr":
+        sr = _kernels.philox_inputs(xc.device, kwargs["b"])
+    elif kwargs.get("mimic_rng"):
+        _kernels.philox_inputs(xc.device, kwargs["b"])
     if kwargs["scale_type"] == "group" or x.dim() == 1:
         gp_sz = kwargs["gp_sz"] if kwargs["scale_type"] == "group" else 128  # rank1 on vectors: 128 (functional.py:193)
         if kwargs["scale_type"] == "rank1":
             md["dim"] = x.dim()
-        codes, max1 = _kernels.quant_group(xc, qmap, gp_sz, kwargs["b"])
+        codes, max1 = _kernels.quant_group(xc, qmap, gp_sz, kwargs["b"], sr)
         md["max1"] = max1
         md["scaled_shape"] = torch.Size([max1.shape[0], gp_sz])
     else:
         md["dim"] = x.dim()
-        codes, max_dims = _kernels.quant_rank1(xc, qmap, kwargs["b"])
+        codes, max_dims = _kernels.quant_rank1(xc, qmap, kwargs["b"], sr)
         md["max_dims"] = max_dims
         md["max1"] = None
         md["scaled_shape"] = x.shape

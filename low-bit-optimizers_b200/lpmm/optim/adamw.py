@@ -228,10 +228,54 @@ class AdamW(LowBitOptimizer):
 
     # ---- fused=False --------------------------------------------------------------------------
     def _step_single(self, gi, group, params):
+        md_m = self.get_qmetadata_by_state_name("exp_avg")
+        md_v = self.get_qmetadata_by_state_name("exp_avg_sq")
+        if md_m["round_type"] == "real-sr" or md_v["round_type"] == "real-sr":
+            return self._step_single_stochastic(group, params, md_m, md_v)
         if self._step_single_batched(gi, group, params):
             return
         self._step_single_each(group, params)
         self._prepare_batch(gi, params)
+
+    def _step_single_stochastic(self, group, params, md_m, md_v):
+        """Configurations with stochastic rounding ('real-sr'): the reference's own sequence per parameter
+        (adamw.py:332-436, 579-627) -- dequantise, one fp32 step, quantise -- so that every quantisation
+        call takes its random stream from torch's CUDA generator in the reference's order (first moment,
+        then second moment, parameter by parameter; nearest-rounded states advance the generator too)."""
+        for p in params:
+            state = self.state[p]
+            state["step"] += 1
+            self._stochastic_update(group, p, state, md_m, md_v)
+
+    def _stochastic_update(self, group, p, state, md_m, md_v):
+        from ..functional import vectorwise_dequant, vectorwise_quant
+        beta1, beta2 = group["betas"]
+        factored, _ = self._get_options(group, p.shape)
+        moments = {}
+        for name, md in (("exp_avg", md_m), ("exp_avg_sq", md_v)):
+            if name == "exp_avg_sq" and factored:
+                continue
+            t, qs = state[name], state[f"{name}_qstate"]
+            if t.numel() <= 1:
+                moments[name] = torch.zeros_like(p, memory_format=torch.preserve_format)
+            elif self._q_enabled(p, name):
+                moments[name] = vectorwise_dequant(t, qmap=qs["qmap"], shape=p.shape, **md, **qs["overhead"]).contiguous()
+            else:
+                moments[name] = t
+        _kernels.adamw_fp32_moments_step(
+            p, p.grad, moments["exp_avg"], moments.get("exp_avg_sq"), state.get("exp_avg_sq_row"),
+            state.get("exp_avg_sq_col"), beta1=beta1, beta2=beta2, lr=group["lr"],
+            weight_decay=group["weight_decay"], eps=group["eps"], step=state["step"].item())
+        for name, md in (("exp_avg", md_m), ("exp_avg_sq", md_v)):
+            if name not in moments:
+                continue
+            qs = state[f"{name}_qstate"]
+            if self._q_enabled(p, name):
+                qx, gen = vectorwise_quant(moments[name], qmap=qs["qmap"], shape=p.shape, mimic_rng=True, **md)
+                state[name] = qx
+                qs["overhead"].update(gen)
+            else:
+                state[name] = moments[name]
 
     def _prepare_batch(self, gi, params):
         """After a per-tensor step: if every tensor now has a cached descriptor, on the current device and
@@ -320,6 +364,9 @@ class AdamW(LowBitOptimizer):
                 stream=handle if (p.is_cuda and p.device.index == cur) else None)
 
     def _factored_update(self, group, p, state):
+        md_m = self.get_qmetadata_by_state_name("exp_avg")
+        if md_m["round_type"] == "real-sr":
+            return self._stochastic_update(group, p, state, md_m, self.get_qmetadata_by_state_name("exp_avg_sq"))
         beta1, beta2 = group["betas"]
         _kernels.adamw4bit_factored_step(
             p, p.grad, state, self._q_enabled(p, "exp_avg"), self.get_qmetadata_by_state_name("exp_avg"),

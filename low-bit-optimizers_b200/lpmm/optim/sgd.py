@@ -53,6 +53,8 @@ class SGD(LowBitOptimizer):
         md = self.get_qmetadata_by_state_name("momentum_buffer")
         multi_ok = (md["b"] == 4 and md["gp_sz"] == 128 and md["scale_type"] == "group"
                     and md["round_type"] == "real-nearest")
+        if md["round_type"] == "real-sr":
+            return self._step_stochastic(md, loss)
         for gi, group in enumerate(self.param_groups):
             fused = self._fused and group["momentum"] != 0 and multi_ok
             batch = {}  # device -> entries of the multi-tensor launch
@@ -89,4 +91,42 @@ class SGD(LowBitOptimizer):
                                                   momentum=group["momentum"], lr=group["lr"],
                                                   dampening=group["dampening"], nesterov=group["nesterov"],
                                                   maximize=group["maximize"])
+        return loss
+
+    def _step_stochastic(self, md, loss):
+        """'real-sr' momentum buffers: dequantise, fp32 step, quantise with the reference's random stream
+        (sgd.py:152-187), parameter by parameter."""
+        from ..functional import vectorwise_dequant, vectorwise_quant
+        for group in self.param_groups:
+            for p in group["params"]:
+                if p.grad is None:
+                    continue
+                if p.grad.is_sparse:
+                    raise RuntimeError("SGD does not support sparse gradients")
+                state = self.state[p]
+                if len(state) == 0:
+                    state["momentum_buffer"] = torch.zeros((), dtype=torch.float, device=p.device)
+                    self.init_qstate(p, "momentum_buffer")
+                quant = self._q_enabled(p, "momentum_buffer")
+                buf, first = None, False
+                if group["momentum"] != 0:
+                    t, qs = state["momentum_buffer"], state["momentum_buffer_qstate"]
+                    first = t.numel() <= 1
+                    if first:
+                        buf = torch.empty_like(p, memory_format=torch.preserve_format)
+                    elif quant:
+                        buf = vectorwise_dequant(t, qmap=qs["qmap"], shape=p.shape, **md, **qs["overhead"]).contiguous()
+                    else:
+                        buf = t
+                _kernels.sgd_fp32_buffer_step(p, p.grad, buf, first, weight_decay=group["weight_decay"],
+                                              momentum=group["momentum"], lr=group["lr"], dampening=group["dampening"],
+                                              nesterov=group["nesterov"], maximize=group["maximize"])
+                if group["momentum"] != 0:
+                    qs = state["momentum_buffer_qstate"]
+                    if quant:
+                        qx, gen = vectorwise_quant(buf, qmap=qs["qmap"], shape=p.shape, mimic_rng=True, **md)
+                        state["momentum_buffer"] = qx
+                        qs["overhead"].update(gen)
+                    else:
+                        state["momentum_buffer"] = buf
         return loss

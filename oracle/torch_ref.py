@@ -90,8 +90,12 @@ def scale_tensor(max_dims):
 
 
 # ---- vectorwise_quant / vectorwise_dequant for the optimizer's configurations ---------------
-def vectorwise_quant(x, qmap, scale_type, gp_sz=128):
-    """functional.py:26-59 with quant_scaling (154-241) and nonlinear_quant (359-369)."""
+def vectorwise_quant(x, qmap, scale_type, gp_sz=128, ref_pack=None, stochastic=False):
+    """functional.py:26-59 with quant_scaling (154-241) and nonlinear_quant (359-369).
+
+    ``ref_pack``: the reference's own compiled ``pack_nonlinear`` (CUDA only).  When given it does the
+    packing, with ``stochastic`` as its flag -- it draws from torch's default CUDA generator (and
+    advances it even when not stochastic), which is what 'real-sr' configurations are checked against."""
     md = {"dtype": x.dtype, "stride": x.stride()}
     qx = x.detach()
     if scale_type == "group" or (scale_type == "rank1" and qx.dim() == 1):
@@ -112,7 +116,13 @@ def vectorwise_quant(x, qmap, scale_type, gp_sz=128):
     else:
         raise NotImplementedError(scale_type)
     md["scaled_shape"] = qx.shape
-    return pack_nonlinear(group_tensor(qx, PACK_ROW), qmap), md
+    grouped = group_tensor(qx, PACK_ROW)
+    if ref_pack is not None:
+        bits = int(math.log2(qmap.numel()))
+        packed = ref_pack(grouped.contiguous(), qmap, bits, bool(stochastic))
+        packed[-1] = 0  # the byte the reference leaves unwritten
+        return packed, md
+    return pack_nonlinear(grouped, qmap), md
 
 
 def vectorwise_dequant(q, qmap, scale_type, shape, md):
@@ -132,7 +142,7 @@ def vectorwise_dequant(q, qmap, scale_type, shape, md):
 
 # ---- non-fused AdamW (adamw.py:332-436) -----------------------------------------------------
 def adamw_step(p, g, st, qmap_m, qmap_v, *, m_quant, v_quant, v_scale_type, beta1, beta2, lr, weight_decay, eps,
-               step, m_gp_sz=128, v_gp_sz=128):
+               step, m_gp_sz=128, v_gp_sz=128, ref_pack=None, m_stochastic=False, v_stochastic=False):
     """One tensor of _single_tensor_adamw4bit.  ``st`` is a dict: 'm', 'v' hold either None (not yet
     initialised), an fp32 tensor (not quantized) or packed codes with 'm_md' / 'v_md' metadata."""
     p.mul_(1 - lr * weight_decay)                                        # :369
@@ -157,11 +167,11 @@ def adamw_step(p, g, st, qmap_m, qmap_v, *, m_quant, v_quant, v_scale_type, beta
     denom = (v.sqrt() / bc2_sqrt).add_(eps)                              # :421
     p.addcdiv_(m, denom, value=-step_size)                               # :422
     if m_quant:
-        st["m"], st["m_md"] = vectorwise_quant(m, qmap_m, "group", m_gp_sz)   # :425-428
+        st["m"], st["m_md"] = vectorwise_quant(m, qmap_m, "group", m_gp_sz, ref_pack, m_stochastic)   # :425-428
     else:
         st["m"] = m
     if v_quant:
-        st["v"], st["v_md"] = vectorwise_quant(v, qmap_v, v_scale_type, v_gp_sz)  # :431-434
+        st["v"], st["v_md"] = vectorwise_quant(v, qmap_v, v_scale_type, v_gp_sz, ref_pack, v_stochastic)  # :431-434
     else:
         st["v"] = v
 
@@ -199,7 +209,8 @@ def factored_step(p, g, st, qmap_m, *, m_quant, beta1, beta2, lr, weight_decay, 
 
 
 # ---- SGD with momentum (sgd.py:133-187) -----------------------------------------------------
-def sgd_step(p, g, st, qmap, *, quant, weight_decay, momentum, lr, dampening, nesterov, maximize, gp_sz=128):
+def sgd_step(p, g, st, qmap, *, quant, weight_decay, momentum, lr, dampening, nesterov, maximize, gp_sz=128,
+             ref_pack=None, stochastic=False):
     d_p = g if not maximize else -g
     if weight_decay != 0:
         d_p = d_p.add(p, alpha=weight_decay)                             # :156
@@ -213,6 +224,6 @@ def sgd_step(p, g, st, qmap, *, quant, weight_decay, momentum, lr, dampening, ne
     p.add_(d_p, alpha=-lr)                                               # :182
     if momentum != 0:
         if quant:
-            st["buf"], st["buf_md"] = vectorwise_quant(buf, qmap, "group", gp_sz)   # :185-187
+            st["buf"], st["buf_md"] = vectorwise_quant(buf, qmap, "group", gp_sz, ref_pack, stochastic)   # :185-187
         else:
             st["buf"] = buf
