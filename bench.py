@@ -212,7 +212,12 @@ def run_own(args):
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    shapes = llama7b_shapes(layers=args.layers)
+    n_layers = args.layers
+    if args.model == "13b":  # the ZeRO-1 configuration of the benchmark description: 40 layers, hidden 5120, inter 13824
+        n_layers = 40 if args.layers == 32 else args.layers
+        shapes = llama7b_shapes(layers=n_layers, hidden=5120, inter=13824)
+    else:
+        shapes = llama7b_shapes(layers=args.layers)
     total = sum(numel(s) for s in shapes)
     alg_bytes, nq, nf = algorithmic_bytes(shapes)
     launches = [0]
@@ -385,8 +390,8 @@ def run_own(args):
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic (seeded N(0,0.02) params, Student-t(3)*1e-3 grads with 1% outlier rows; one gradient set reused every step)",
-            "config": {"workload": "llama7b_shaped_fp32_list_fused_4bit_adamw", "params": total, "tensors": len(shapes),
-                       "params_4bit": nq, "params_fp32_state": nf, "layers": args.layers,
+            "config": {"workload": f"llama{args.model}_shaped_fp32_list_fused_4bit_adamw", "params": total, "tensors": len(shapes),
+                       "params_4bit": nq, "params_fp32_state": nf, "layers": n_layers,
                        "parallelism": "single GPU" if world == 1 else (
                            f"ZeRO-1 over {world} GPUs, group-aligned shards, fp32 params reach the peers by "
                            + ("NVLink stores inside the update kernel" if args.gather == "fused" else "an NCCL all-gather after the update")),
@@ -406,6 +411,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
     ap.add_argument("--layers", type=int, default=32, help="transformer layers of the list (32 = the 7B workload)")
+    ap.add_argument("--model", default="7b", choices=["7b", "13b"],
+                    help="7b: the headline list; 13b: the LLaMA-13B-shaped list (52 GB of fp32 parameters per GPU)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
                     help="N > 1: parameters reach the peers by stores inside the update kernel, or by an NCCL all-gather after it")
