@@ -72,7 +72,12 @@ class ClockSampler:
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
-        self.index, self.proc, self.lines = index, None, []
+        self.index, self.proc, self.lines, self.first = index, None, [], 0
+
+    def mark(self):
+        """Samples from here on count (called when the timed region starts; the process was started
+        earlier, because nvidia-smi needs up to a second before its first line)."""
+        self.first = len(self.lines)
 
     def start(self):
         try:
@@ -96,7 +101,7 @@ class ClockSampler:
         except Exception:
             pass
         sm, mx, reasons = [], [], set()
-        for ln in self.lines:
+        for ln in self.lines[self.first:]:
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 7:
                 continue
@@ -258,10 +263,11 @@ def run_own(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    sampler.start()
     for _ in range(args.warmup):
         step()
     barrier()
-    sampler.start()
+    sampler.mark()
     launches[0] = 0
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
