@@ -71,6 +71,8 @@ def big_cases():
     return [
         ("llama7b adamw group (qconfig=None)", "AdamW", llama7b_shapes(), dict(adamw, qconfig=None)),
         ("llama7b adamw fused", "AdamW", llama7b_shapes(), dict(adamw, fused=True)),
+        ("llama7b adamw rank-1 (default.yml)", "AdamW", llama7b_shapes(), dict(adamw, qconfig=cfg("default.yml"))),
+        ("llama7b adamw factored", "AdamW", llama7b_shapes(), dict(adamw, factor_second_moment=True)),
         ("llama7b sgd", "SGD", llama7b_shapes(), dict(lr=1e-2, momentum=0.9, weight_decay=1e-4)),
     ]
 
