@@ -63,6 +63,48 @@ def test_optimizer_factored_many_matrices(qmaps):
     _check_adamw(opt, params, o_states, o_params, "group", factored=True)
 
 
+@pytest.mark.parametrize("cfg,v_scale", [(None, "group"), ("default.yml", "rank1")])
+def test_a_parameter_that_skips_a_step_keeps_its_own_step_count(qmaps, cfg, v_scale):
+    """One parameter has no gradient at the third step: afterwards its step counter (hence its bias
+    corrections) lags behind the others.  The list step must not put it into a launch that assumes a
+    common step count; results equal the restated reference stepping each tensor with its own counter."""
+    import os
+    import lpmm
+    from lpmm.config import CONFIG_DIR
+    from oracle import torch_ref as T
+    from golden_cases import THRESHOLD
+    shapes = [(96, 64), (64, 128), (130, 72), (200,)]
+    hyper = dict(lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01)
+    torch.manual_seed(51)
+    p0s = [torch.randn(s, device=device()) * 0.02 for s in shapes]
+    params = [torch.nn.Parameter(p.clone()) for p in p0s]
+    opt = lpmm.optim.AdamW(params, qconfig=os.path.join(CONFIG_DIR, cfg) if cfg else None, **hyper)
+    qm, qv = torch.from_numpy(qmaps["m"]).to(device()), torch.from_numpy(qmaps["v"]).to(device())
+    o_params = [p.clone() for p in p0s]
+    o_states = [dict() for _ in shapes]
+    counts = [0] * len(shapes)
+    for s in range(1, 7):
+        for i, p in enumerate(params):
+            skip = (s == 3 and i == 1)
+            p.grad = None if skip else student_t(p.shape, 40 * s + i)
+        opt.step()
+        for i, op in enumerate(o_params):
+            if s == 3 and i == 1:
+                continue
+            counts[i] += 1
+            quant = op.numel() > THRESHOLD
+            T.adamw_step(op, student_t(op.shape, 40 * s + i), o_states[i], qm, qv, m_quant=quant, v_quant=quant,
+                         v_scale_type=v_scale, beta1=0.9, beta2=0.999, lr=1e-3, weight_decay=0.01, eps=1e-8,
+                         step=float(counts[i]))
+    torch.cuda.synchronize()
+    for i, p in enumerate(params):
+        assert float(opt.state[p]["step"]) == counts[i]
+        assert bits_equal(p.detach(), o_params[i]), f"tensor {i}: parameters differ"
+        if p.numel() > THRESHOLD:
+            assert torch.equal(opt.state[p]["exp_avg"].view(torch.uint8), o_states[i]["m"].view(torch.uint8))
+            assert torch.equal(opt.state[p]["exp_avg_sq"].view(torch.uint8), o_states[i]["v"].view(torch.uint8))
+
+
 def _vp(t):
     return ctypes.c_void_p(t.data_ptr() if t is not None else None)
 
