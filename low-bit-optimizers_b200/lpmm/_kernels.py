@@ -362,10 +362,16 @@ class _StepPlan:
 
     def matches(self, p, state):
         m, v = state["exp_avg"], state.get("exp_avg_sq")
-        return (p.data_ptr() == self.p_ptr and m is self.m and v is self.v and m.data_ptr() == self.m_ptr
-                and (v is None or v.data_ptr() == self.v_ptr)
-                and (self.axis_sets is None or self.oh_v.get("max_dims") is self.axis_sets[self.which])
-                and all(state.get(k) is t and t.data_ptr() == ptr for k, t, ptr in self.extra))
+        if p.data_ptr() != self.p_ptr or m is not self.m or v is not self.v or m.data_ptr() != self.m_ptr:
+            return False
+        if v is not None and v.data_ptr() != self.v_ptr:
+            return False
+        if self.axis_sets is not None and self.oh_v.get("max_dims") is not self.axis_sets[self.which]:
+            return False
+        for k, t, ptr in self.extra:
+            if state.get(k) is not t or t.data_ptr() != ptr:
+                return False
+        return True
 
     def set_grad(self, g):
         gp = g.data_ptr()

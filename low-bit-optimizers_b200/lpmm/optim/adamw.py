@@ -307,6 +307,7 @@ class AdamW(LowBitOptimizer):
         self._batches[gi] = dict(params=list(params), plans=plans, states=states, spares=spares, ptrs=ptrs, addrs=addrs,
                                  steps=(ctypes.c_double * n)(), device=cur, qm=states[0]["exp_avg_qstate"]["qmap"],
                                  qv=states[0]["exp_avg_sq_qstate"]["qmap"],
+                                 rank1_index=[i for i, pl in enumerate(plans) if pl.axis_sets is not None],
                                  scratch=_kernels.unfused_step_many_scratch_bytes(ptrs, n))
 
     def _step_single_batched(self, gi, group, params):
@@ -327,19 +328,21 @@ class AdamW(LowBitOptimizer):
             del self._batches[gi]
             return False
         steps, ptrs, addrs = b["steps"], b["ptrs"], b["addrs"]
-        for i, st in enumerate(states):
-            st["step"] += 1
-            steps[i] = st["step"].item()
+        step_tensors = b.get("step_tensors")
+        if step_tensors is None or any(st["step"] is not t for st, t in zip(states, step_tensors)):
+            step_tensors = b["step_tensors"] = [st["step"] for st in states]
+        torch._foreach_add_(step_tensors, 1.0)  # one call instead of one CPU tensor op per parameter
+        steps[:] = torch.stack(step_tensors).tolist()
         beta1, beta2 = group["betas"]
         _kernels.adamw4bit_unfused_step_many(ptrs, len(plans), b["qm"], b["qv"], steps, b["scratch"], params[0].device,
                                              beta1=beta1, beta2=beta2, lr=group["lr"],
                                              weight_decay=group["weight_decay"], eps=group["eps"])
-        for i, plan in enumerate(plans):
-            if plan.axis_sets is not None:  # rank-1: the freshly written maxima become the state's
-                plan.which ^= 1
-                plan.oh_v["max_dims"] = plan.axis_sets[plan.which]
-                b["spares"][i]["max_dims"] = plan.axis_sets[plan.which ^ 1]
-                ptrs[i] = addrs[i][plan.which]
+        for i in b["rank1_index"]:  # rank-1: the freshly written maxima become the state's
+            plan = plans[i]
+            plan.which ^= 1
+            plan.oh_v["max_dims"] = plan.axis_sets[plan.which]
+            b["spares"][i]["max_dims"] = plan.axis_sets[plan.which ^ 1]
+            ptrs[i] = addrs[i][plan.which]
         return True
 
     def _step_single_each(self, group, params):
