@@ -517,73 +517,29 @@ static int launch_multi(const lpmm_b200_tensor* ts, int n, const float* qm, cons
   // the part of [gbeg, gend) that falls inside it.
   static thread_local Table tab;  // 28.9 KB; copied into the launch parameters by the runtime
   const bool fast = fast_math_ok(h);
-  int64_t gcursor = 0;            // global group index of the window's first tensor
+  int64_t gcursor = 0;
   int i = 0;
   while (i < n) {
-    int cnt = 0;
-    int64_t g = 0;
-    bool any_q4 = false;
-    for (; i < n && cnt < MAX_TENSORS; ++i) {
-      const lpmm_b200_tensor& s = ts[i];
-      if (s.numel == 0) continue;
-      TDesc& d = tab.t[cnt++];
-      d.p = s.p;
-      d.g = s.g;
-      d.m = s.m;
-      d.v = s.v;
-      d.sm = s.m_scale;
-      d.sv = s.v_scale;
-      d.numel = s.numel;
-      d.gstart = g;
-      d.kind = s.kind;
-      any_q4 = any_q4 || s.kind == LPMM_B200_KIND_Q4;
-      const uintptr_t a = (uintptr_t)s.p | (uintptr_t)s.g;
-      if (s.kind == LPMM_B200_KIND_Q4)
-        d.aligned = ((a & 31) == 0) && ((((uintptr_t)s.m | (uintptr_t)s.v) & 3) == 0);
-      else
-        d.aligned = (((a | (uintptr_t)s.m | (uintptr_t)s.v) & 31) == 0);
-      g += groups_of(s.numel);
-    }
-    tab.n = cnt;
-    tab.pad = 0;
-    tab.gtotal = g;
-    // intersect [gbeg, gend) with this window's [gcursor, gcursor + g)
-    const int64_t lo = (gbeg > gcursor ? gbeg : gcursor) - gcursor;
-    const int64_t hi = (gend < gcursor + g ? gend : gcursor + g) - gcursor;
-    gcursor += g;
-    if (cnt == 0 || hi <= lo) continue;
-    const int64_t work = hi - lo;
-    int64_t grid = (work + HW_PER_CTA - 1) / HW_PER_CTA;
-    const int64_t cap = (int64_t)num_sms() * CTAS_PER_SM;
-    if (grid > cap) grid = cap;
+    const Window w = next_window(ts, n, i, gcursor, gbeg, gend, true, tab);
+    if (!w.work) continue;
+    const unsigned grid = multi_grid(w);
     cudaError_t e;
     if (pi.n > 0)
-      e = any_q4 ? launch_fast_or_exact<true, true>(fast, tab, (unsigned)grid, qm, qv, h, lo, hi, st, pi)
-                 : launch_fast_or_exact<false, true>(fast, tab, (unsigned)grid, qm, qv, h, lo, hi, st, pi);
+      e = w.any_q4 ? launch_fast_or_exact<true, true>(fast, tab, grid, qm, qv, h, w.lo, w.hi, st, pi)
+                   : launch_fast_or_exact<false, true>(fast, tab, grid, qm, qv, h, w.lo, w.hi, st, pi);
     else
-      e = any_q4 ? launch_fast_or_exact<true, false>(fast, tab, (unsigned)grid, qm, qv, h, lo, hi, st, pi)
-                 : launch_fast_or_exact<false, false>(fast, tab, (unsigned)grid, qm, qv, h, lo, hi, st, pi);
+      e = w.any_q4 ? launch_fast_or_exact<true, false>(fast, tab, grid, qm, qv, h, w.lo, w.hi, st, pi)
+                   : launch_fast_or_exact<false, false>(fast, tab, grid, qm, qv, h, w.lo, w.hi, st, pi);
     LPMM_CUDA_TRY(e);
   }
   return LPMM_B200_OK;
 }
 
 static int check_list(const lpmm_b200_tensor* ts, int n, bool need_qmaps, const float* qm, const float* qv) {
-  if (n < 0) return LPMM_B200_ERR_BAD_SIZE;
-  if (n > 0 && !ts) return LPMM_B200_ERR_NULL_POINTER;
   bool any_q4 = false;
-  for (int i = 0; i < n; ++i) {
-    const lpmm_b200_tensor& s = ts[i];
-    if (s.numel < 0) return LPMM_B200_ERR_BAD_SIZE;
-    if (s.numel > (int64_t)1 << 37) return LPMM_B200_ERR_TOO_LARGE;  // 32-bit group index per tensor
-    if (s.kind != LPMM_B200_KIND_Q4 && s.kind != LPMM_B200_KIND_FP32) return LPMM_B200_ERR_BAD_KIND;
-    if (s.numel == 0) continue;
-    if (!s.p || !s.g || !s.m || !s.v) return LPMM_B200_ERR_NULL_POINTER;
-    if (s.kind == LPMM_B200_KIND_Q4) {
-      any_q4 = true;
-      if (!s.m_scale || !s.v_scale) return LPMM_B200_ERR_NULL_POINTER;
-    }
-  }
+  int64_t total = 0;
+  const int rc = check_tensor_list(ts, n, true, &any_q4, &total);
+  if (rc != LPMM_B200_OK) return rc;
   if ((any_q4 || need_qmaps) && (!qm || !qv)) return LPMM_B200_ERR_NULL_POINTER;
   return LPMM_B200_OK;
 }

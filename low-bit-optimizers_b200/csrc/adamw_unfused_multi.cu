@@ -261,66 +261,23 @@ extern "C" int lpmm_b200_adamw4bit_unfused_multi_tensor(const lpmm_b200_tensor* 
                                                         const float* qmap_v, double beta1, double beta2, double lr,
                                                         double weight_decay, double eps, double step,
                                                         int64_t group_begin, int64_t group_end, void* stream) {
-  if (n < 0) return LPMM_B200_ERR_BAD_SIZE;
-  if (n > 0 && !ts) return LPMM_B200_ERR_NULL_POINTER;
   bool any_q4 = false;
   int64_t total = 0;
-  for (int i = 0; i < n; ++i) {
-    const lpmm_b200_tensor& s = ts[i];
-    if (s.numel < 0) return LPMM_B200_ERR_BAD_SIZE;
-    if (s.numel > (int64_t)1 << 37) return LPMM_B200_ERR_TOO_LARGE;  // 32-bit group index per tensor
-    if (s.kind != LPMM_B200_KIND_Q4 && s.kind != LPMM_B200_KIND_FP32) return LPMM_B200_ERR_BAD_KIND;
-    total += groups_of(s.numel);
-    if (s.numel == 0) continue;
-    if (!s.p || !s.g || !s.m || !s.v) return LPMM_B200_ERR_NULL_POINTER;
-    if (s.kind == LPMM_B200_KIND_Q4) {
-      any_q4 = true;
-      if (!s.m_scale || !s.v_scale) return LPMM_B200_ERR_NULL_POINTER;
-    }
-  }
+  const int rc = check_tensor_list(ts, n, true, &any_q4, &total);
+  if (rc != LPMM_B200_OK) return rc;
   if (any_q4 && (!qmap_m || !qmap_v)) return LPMM_B200_ERR_NULL_POINTER;
   if (group_end < 0) group_end = total;
   if (group_begin < 0 || group_begin > group_end || group_end > total) return LPMM_B200_ERR_BAD_SIZE;
   if (group_begin == group_end) return LPMM_B200_OK;
   const UConsts c = make_consts(beta1, beta2, lr, weight_decay, eps, step);
-  // `ts` may hold more than MAX_TENSORS entries: walk it in windows, each window one launch over
-  // the part of [group_begin, group_end) that falls inside it.
   static thread_local Table tab;
   int64_t gcursor = 0;
   int i = 0;
   while (i < n) {
-    int cnt = 0;
-    int64_t g = 0;
-    bool win_q4 = false;
-    for (; i < n && cnt < MAX_TENSORS; ++i) {
-      const lpmm_b200_tensor& s = ts[i];
-      if (s.numel == 0) continue;
-      TDesc& d = tab.t[cnt++];
-      d.p = s.p;
-      d.g = s.g;
-      d.m = s.m;
-      d.v = s.v;
-      d.sm = s.m_scale;
-      d.sv = s.v_scale;
-      d.numel = s.numel;
-      d.gstart = g;
-      d.kind = s.kind;
-      win_q4 = win_q4 || s.kind == LPMM_B200_KIND_Q4;
-      d.aligned = ((((uintptr_t)s.p | (uintptr_t)s.g) & 31) == 0) && ((((uintptr_t)s.m | (uintptr_t)s.v) & 3) == 0);
-      g += groups_of(s.numel);
-    }
-    tab.n = cnt;
-    tab.pad = 0;
-    tab.gtotal = g;
-    const int64_t lo = (group_begin > gcursor ? group_begin : gcursor) - gcursor;
-    const int64_t hi = (group_end < gcursor + g ? group_end : gcursor + g) - gcursor;
-    gcursor += g;
-    if (cnt == 0 || hi <= lo) continue;
-    int64_t grid = (hi - lo + HW_PER_CTA - 1) / HW_PER_CTA;
-    const int64_t cap = (int64_t)num_sms() * CTAS_PER_SM;
-    if (grid > cap) grid = cap;
-    const cudaError_t e = win_q4 ? launch_um<true>(tab, (unsigned)grid, qmap_m, qmap_v, c, lo, hi, (cudaStream_t)stream)
-                                 : launch_um<false>(tab, (unsigned)grid, qmap_m, qmap_v, c, lo, hi, (cudaStream_t)stream);
+    const Window w = next_window(ts, n, i, gcursor, group_begin, group_end, true, tab);
+    if (!w.work) continue;
+    const cudaError_t e = w.any_q4 ? launch_um<true>(tab, multi_grid(w), qmap_m, qmap_v, c, w.lo, w.hi, (cudaStream_t)stream)
+                                   : launch_um<false>(tab, multi_grid(w), qmap_m, qmap_v, c, w.lo, w.hi, (cudaStream_t)stream);
     LPMM_CUDA_TRY(e);
   }
   return LPMM_B200_OK;

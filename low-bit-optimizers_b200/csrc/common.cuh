@@ -134,6 +134,22 @@ __device__ __forceinline__ uint32_t linear16_code(float x) {
   return __float2uint_ru(__fmaf_rn(x, 16.0f, -1.5f));
 }
 
+// Nearest-code rule of a 16-entry map as a branch-free four-step search over its 15 sorted midpoints
+// (padded with +inf): code = #{midpoints < x}; a NaN gives 15 like the reference's search.
+__device__ __forceinline__ int code16(const float* __restrict__ mids, float x) {
+  int c = (mids[7] < x) ? 8 : 0;
+  c += (mids[c + 3] < x) ? 4 : 0;
+  c += (mids[c + 1] < x) ? 2 : 0;
+  c += (mids[c] < x) ? 1 : 0;
+  return (x != x) ? 15 : c;
+}
+
+// Monotone max of a non-negative float through an integer atomic; a stale read can only be too
+// small, so skipping the atomic when the value is not larger is always safe.
+__device__ __forceinline__ void atomic_max_nonneg(float* addr, float val) {
+  if (val > *reinterpret_cast<volatile float*>(addr)) atomicMax(reinterpret_cast<int*>(addr), __float_as_int(val));
+}
+
 // The reference's search, verbatim in behaviour, for maps the table cannot hold.
 __device__ __forceinline__ int bsearch_code(const float* __restrict__ q, float x) {
   if (x <= q[0]) return 0;

@@ -159,13 +159,6 @@ __global__ void __launch_bounds__(FT) f_row_mean_kernel(const FDesc* __restrict_
   if (threadIdx.x == 0) *t.row_mean = __fdiv_rn(red[0], (float)t.R);
 }
 
-__device__ __forceinline__ int f_code16(const float* __restrict__ mids, float x) {
-  int c = (mids[7] < x) ? 8 : 0;
-  c += (mids[c + 3] < x) ? 4 : 0;
-  c += (mids[c + 1] < x) ? 2 : 0;
-  c += (mids[c] < x) ? 1 : 0;
-  return (x != x) ? 15 : c;
-}
 
 // Pass 4: one 128-element unit: v = (row / row_mean) * col, AdamW, first moment requantised.
 __device__ __forceinline__ void f_unit(const FDesc& t, long long u, int l16, unsigned hmask, const UConsts& c,
@@ -246,13 +239,13 @@ __device__ __forceinline__ void f_unit(const FDesc& t, long long u, int l16, uns
       q = f2_fma(f2_fma(q, nam2, xj), r2, q);
       float qa, qb;
       f2_unpack(q, qa, qb);
-      mo = (mo << 4) + (uint32_t)(lut_ok ? lut_code(lut_m, qb) : f_code16(Sm.mids, qb));
-      mo = (mo << 4) + (uint32_t)(lut_ok ? lut_code(lut_m, qa) : f_code16(Sm.mids, qa));
+      mo = (mo << 4) + (uint32_t)(lut_ok ? lut_code(lut_m, qb) : code16(Sm.mids, qb));
+      mo = (mo << 4) + (uint32_t)(lut_ok ? lut_code(lut_m, qa) : code16(Sm.mids, qa));
     }
     if (am == 0.0f) mo = 0xFFFFFFFFu;  // 0/0 = NaN -> code 15 for the whole group
   } else {
 #pragma unroll
-    for (int k = 7; k >= 0; --k) mo = (mo << 4) + (uint32_t)f_code16(Sm.mids, __fdiv_rn(m[k], am));
+    for (int k = 7; k >= 0; --k) mo = (mo << 4) + (uint32_t)code16(Sm.mids, __fdiv_rn(m[k], am));
   }
   *reinterpret_cast<uint32_t*>(mb) = mo;  // inside the padded layout for every lane of the unit
   if (l16 == 0) t.m_max1[u] = am;

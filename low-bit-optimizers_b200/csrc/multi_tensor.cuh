@@ -46,4 +46,77 @@ __device__ __forceinline__ void prefetch_l2(const void* ptr) {
 
 static inline int64_t groups_of(int64_t numel) { return (numel + 127) / 128; }
 
+// Host side of every multi-tensor launch.  A list may hold more tensors than a table: it is walked in
+// windows of at most MAX_TENSORS non-empty tensors, one launch per window over the part of the
+// caller's group range [gbeg, gend) that falls inside it.
+struct Window {
+  int64_t lo, hi;  // the launch's group range, relative to the window
+  bool any_q4;     // the window holds a 4-bit tensor (tables needed)
+  bool work;       // false: nothing of [gbeg, gend) lies in this window
+};
+// Fills `tab` from ts[i...] and advances i and gcursor (global group index of the next window's first
+// tensor).  uses_v: the step has a second state (AdamW); otherwise v / v_scale are ignored (SGD).
+// `aligned` of a 4-bit tensor: p, g 32-byte aligned (256-bit accesses), codes 4-byte aligned; of an
+// fp32-state tensor: everything 32-byte aligned.
+static inline Window next_window(const lpmm_b200_tensor* ts, int n, int& i, int64_t& gcursor, int64_t gbeg, int64_t gend,
+                                 bool uses_v, Table& tab) {
+  int cnt = 0;
+  int64_t g = 0;
+  Window w = {0, 0, false, false};
+  for (; i < n && cnt < MAX_TENSORS; ++i) {
+    const lpmm_b200_tensor& s = ts[i];
+    if (s.numel == 0) continue;
+    TDesc& d = tab.t[cnt++];
+    d.p = s.p;
+    d.g = s.g;
+    d.m = s.m;
+    d.v = uses_v ? s.v : nullptr;
+    d.sm = s.m_scale;
+    d.sv = uses_v ? s.v_scale : nullptr;
+    d.numel = s.numel;
+    d.gstart = g;
+    d.kind = s.kind;
+    w.any_q4 = w.any_q4 || s.kind == LPMM_B200_KIND_Q4;
+    const uintptr_t pg = (uintptr_t)s.p | (uintptr_t)s.g;
+    const uintptr_t states = (uintptr_t)s.m | (uses_v ? (uintptr_t)s.v : 0);
+    d.aligned = (s.kind == LPMM_B200_KIND_Q4) ? (((pg & 31) == 0) && ((states & 3) == 0)) : (((pg | states) & 31) == 0);
+    g += groups_of(s.numel);
+  }
+  tab.n = cnt;
+  tab.pad = 0;
+  tab.gtotal = g;
+  w.lo = (gbeg > gcursor ? gbeg : gcursor) - gcursor;
+  w.hi = (gend < gcursor + g ? gend : gcursor + g) - gcursor;
+  gcursor += g;
+  w.work = cnt > 0 && w.hi > w.lo;
+  return w;
+}
+// One CTA per SM at most (persistent CTAs stride over the groups).
+static inline unsigned multi_grid(const Window& w) {
+  int64_t grid = (w.hi - w.lo + HW_PER_CTA - 1) / HW_PER_CTA;
+  const int64_t cap = (int64_t)num_sms() * CTAS_PER_SM;
+  return (unsigned)(grid > cap ? cap : grid);
+}
+// Argument checks shared by the list entry points; total receives the list's group count.
+static inline int check_tensor_list(const lpmm_b200_tensor* ts, int n, bool uses_v, bool* any_q4, int64_t* total) {
+  if (n < 0) return LPMM_B200_ERR_BAD_SIZE;
+  if (n > 0 && !ts) return LPMM_B200_ERR_NULL_POINTER;
+  *any_q4 = false;
+  *total = 0;
+  for (int i = 0; i < n; ++i) {
+    const lpmm_b200_tensor& s = ts[i];
+    if (s.numel < 0) return LPMM_B200_ERR_BAD_SIZE;
+    if (s.numel > (int64_t)1 << 37) return LPMM_B200_ERR_TOO_LARGE;  // 32-bit group index per tensor
+    if (s.kind != LPMM_B200_KIND_Q4 && s.kind != LPMM_B200_KIND_FP32) return LPMM_B200_ERR_BAD_KIND;
+    *total += groups_of(s.numel);
+    if (s.numel == 0) continue;
+    if (!s.p || !s.g || !s.m || (uses_v && !s.v)) return LPMM_B200_ERR_NULL_POINTER;
+    if (s.kind == LPMM_B200_KIND_Q4) {
+      *any_q4 = true;
+      if (!s.m_scale || (uses_v && !s.v_scale)) return LPMM_B200_ERR_NULL_POINTER;
+    }
+  }
+  return LPMM_B200_OK;
+}
+
 }  // namespace lpmm_b200

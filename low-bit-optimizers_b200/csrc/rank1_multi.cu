@@ -43,9 +43,6 @@ struct R1Desc {
   int pad_;
 };
 
-__device__ __forceinline__ void r1_atomic_max(float* addr, float val) {
-  if (val > *reinterpret_cast<volatile float*>(addr)) atomicMax(reinterpret_cast<int*>(addr), __float_as_int(val));
-}
 
 // Index of the last descriptor whose `start` field (ustart / tstart) is <= x.
 template <bool TILES>
@@ -138,24 +135,17 @@ __global__ void __launch_bounds__(R1T) r1_stats_kernel(const R1Desc* __restrict_
         mc = fmaxf(mc, __shfl_xor_sync(0xffffffffu, mc, o));
       }
       if ((threadIdx.x & (seg - 1)) == 0) {
-        if (ra < r_end) r1_atomic_max(t.new_r + ra, ma);
-        if (rc < r_end) r1_atomic_max(t.new_r + rc, mc);
+        if (ra < r_end) atomic_max_nonneg(t.new_r + ra, ma);
+        if (rc < r_end) atomic_max_nonneg(t.new_r + rc, mc);
       }
     }
     if (active) {
 #pragma unroll
-      for (int k = 0; k < 8; ++k) r1_atomic_max(t.new_c + c0 + k, col_max[k]);
+      for (int k = 0; k < 8; ++k) atomic_max_nonneg(t.new_c + c0 + k, col_max[k]);
     }
   }
 }
 
-__device__ __forceinline__ int r1_code16(const float* __restrict__ mids, float x) {
-  int c = (mids[7] < x) ? 8 : 0;
-  c += (mids[c + 3] < x) ? 4 : 0;
-  c += (mids[c + 1] < x) ? 2 : 0;
-  c += (mids[c] < x) ? 1 : 0;
-  return (x != x) ? 15 : c;
-}
 
 // One 128-element unit of one matrix.  FULL lanes (8 elements inside one row, 16-byte aligned, short
 // exact sequences applicable) use packed arithmetic; every other lane takes the scalar IEEE path.
@@ -249,13 +239,13 @@ __device__ __forceinline__ void r1_unit(const R1Desc& t, long long u, int l16, u
       q = f2_fma(f2_fma(q, nam2, xj), r2, q);
       float qa, qb;
       f2_unpack(q, qa, qb);
-      mo = (mo << 4) + (uint32_t)(lut_ok ? lut_code(lut_m, qb) : r1_code16(Sm.mids, qb));
-      mo = (mo << 4) + (uint32_t)(lut_ok ? lut_code(lut_m, qa) : r1_code16(Sm.mids, qa));
+      mo = (mo << 4) + (uint32_t)(lut_ok ? lut_code(lut_m, qb) : code16(Sm.mids, qb));
+      mo = (mo << 4) + (uint32_t)(lut_ok ? lut_code(lut_m, qa) : code16(Sm.mids, qa));
     }
     if (am == 0.0f) mo = 0xFFFFFFFFu;  // 0/0 = NaN -> code 15 for the whole group
   } else {
 #pragma unroll
-    for (int k = 7; k >= 0; --k) mo = (mo << 4) + (uint32_t)r1_code16(Sm.mids, __fdiv_rn(m[k], am));
+    for (int k = 7; k >= 0; --k) mo = (mo << 4) + (uint32_t)code16(Sm.mids, __fdiv_rn(m[k], am));
   }
   // second moment: v / min(new row max, new column max) per element
   uint32_t vo = 0;
@@ -286,10 +276,10 @@ __device__ __forceinline__ void r1_unit(const R1Desc& t, long long u, int l16, u
       vo = (vo << 4) + (ca < 15u ? ca : 15u);
     }
   } else {
-    const int zero_v = r1_code16(Sv.mids, 0.0f);
+    const int zero_v = code16(Sv.mids, 0.0f);
 #pragma unroll
     for (int k = 7; k >= 0; --k)
-      vo = (vo << 4) + (uint32_t)((e0 + k < n) ? r1_code16(Sv.mids, __fdiv_rn(v[k], st_new[k])) : zero_v);
+      vo = (vo << 4) + (uint32_t)((e0 + k < n) ? code16(Sv.mids, __fdiv_rn(v[k], st_new[k])) : zero_v);
   }
   // the unit lies inside the padded layout (rows of 2048 codes), so all 16 lanes may store
   *reinterpret_cast<uint32_t*>(mb) = mo;

@@ -231,24 +231,11 @@ extern "C" int lpmm_b200_sgd4bit_multi_tensor(const lpmm_b200_tensor* ts, int n,
                                               double weight_decay, double momentum, double lr, double dampening,
                                               int nesterov, int maximize, int64_t group_begin, int64_t group_end,
                                               void* stream) {
-  if (n < 0) return LPMM_B200_ERR_BAD_SIZE;
-  if (n > 0 && !ts) return LPMM_B200_ERR_NULL_POINTER;
-  if (momentum == 0.0) return LPMM_B200_ERR_BAD_KIND;  // no buffer to step: use the per-tensor entry point
+  if (momentum == 0.0 && n >= 0) return LPMM_B200_ERR_BAD_KIND;  // no buffer to step: use the per-tensor entry point
   bool any_q4 = false;
   int64_t total = 0;
-  for (int i = 0; i < n; ++i) {
-    const lpmm_b200_tensor& s = ts[i];
-    if (s.numel < 0) return LPMM_B200_ERR_BAD_SIZE;
-    if (s.numel > (int64_t)1 << 37) return LPMM_B200_ERR_TOO_LARGE;  // 32-bit group index per tensor
-    if (s.kind != LPMM_B200_KIND_Q4 && s.kind != LPMM_B200_KIND_FP32) return LPMM_B200_ERR_BAD_KIND;
-    total += groups_of(s.numel);
-    if (s.numel == 0) continue;
-    if (!s.p || !s.g || !s.m) return LPMM_B200_ERR_NULL_POINTER;
-    if (s.kind == LPMM_B200_KIND_Q4) {
-      any_q4 = true;
-      if (!s.m_scale) return LPMM_B200_ERR_NULL_POINTER;
-    }
-  }
+  const int rc = check_tensor_list(ts, n, false, &any_q4, &total);
+  if (rc != LPMM_B200_OK) return rc;
   if (any_q4 && !qmap) return LPMM_B200_ERR_NULL_POINTER;
   if (group_end < 0) group_end = total;
   if (group_begin < 0 || group_begin > group_end || group_end > total) return LPMM_B200_ERR_BAD_SIZE;
@@ -261,44 +248,14 @@ extern "C" int lpmm_b200_sgd4bit_multi_tensor(const lpmm_b200_tensor* ts, int n,
   c.has_wd = weight_decay != 0.0;
   c.nesterov = nesterov != 0;
   c.maximize = maximize != 0;
-  // `ts` may hold more than MAX_TENSORS entries: walk it in windows, each window one launch over
-  // the part of [group_begin, group_end) that falls inside it.
   static thread_local Table tab;
   int64_t gcursor = 0;
   int i = 0;
   while (i < n) {
-    int cnt = 0;
-    int64_t g = 0;
-    bool win_q4 = false;
-    for (; i < n && cnt < MAX_TENSORS; ++i) {
-      const lpmm_b200_tensor& s = ts[i];
-      if (s.numel == 0) continue;
-      TDesc& d = tab.t[cnt++];
-      d.p = s.p;
-      d.g = s.g;
-      d.m = s.m;
-      d.v = nullptr;
-      d.sm = s.m_scale;
-      d.sv = nullptr;
-      d.numel = s.numel;
-      d.gstart = g;
-      d.kind = s.kind;
-      win_q4 = win_q4 || s.kind == LPMM_B200_KIND_Q4;
-      d.aligned = ((((uintptr_t)s.p | (uintptr_t)s.g) & 31) == 0) && (((uintptr_t)s.m & 3) == 0);
-      g += groups_of(s.numel);
-    }
-    tab.n = cnt;
-    tab.pad = 0;
-    tab.gtotal = g;
-    const int64_t lo = (group_begin > gcursor ? group_begin : gcursor) - gcursor;
-    const int64_t hi = (group_end < gcursor + g ? group_end : gcursor + g) - gcursor;
-    gcursor += g;
-    if (cnt == 0 || hi <= lo) continue;
-    int64_t grid = (hi - lo + HW_PER_CTA - 1) / HW_PER_CTA;
-    const int64_t cap = (int64_t)num_sms() * CTAS_PER_SM;
-    if (grid > cap) grid = cap;
-    const cudaError_t e = win_q4 ? launch_sgd<true>(tab, (unsigned)grid, qmap, c, lo, hi, (cudaStream_t)stream)
-                                 : launch_sgd<false>(tab, (unsigned)grid, qmap, c, lo, hi, (cudaStream_t)stream);
+    const Window w = next_window(ts, n, i, gcursor, group_begin, group_end, false, tab);
+    if (!w.work) continue;
+    const cudaError_t e = w.any_q4 ? launch_sgd<true>(tab, multi_grid(w), qmap, c, w.lo, w.hi, (cudaStream_t)stream)
+                                   : launch_sgd<false>(tab, multi_grid(w), qmap, c, w.lo, w.hi, (cudaStream_t)stream);
     LPMM_CUDA_TRY(e);
   }
   return LPMM_B200_OK;

@@ -77,13 +77,6 @@ struct Maps {
 // Nearest-code rule as a branch-free search over the sorted midpoints: code = #{midpoints < x}.
 // A NaN gives what the reference's search gives: 15 in the packed 4-bit kernel, (uint8_t)-1 in the
 // one-code-per-byte kernel (quantization_kernel.cu:398-427, :533).
-__device__ __forceinline__ int code16(const float* __restrict__ mids, float x) {
-  int c = (mids[7] < x) ? 8 : 0;
-  c += (mids[c + 3] < x) ? 4 : 0;
-  c += (mids[c + 1] < x) ? 2 : 0;
-  c += (mids[c] < x) ? 1 : 0;
-  return (x != x) ? 15 : c;
-}
 template <bool W>
 __device__ __forceinline__ int code_of(const float* __restrict__ mids, int bits, float x) {
   if (!W) return code16(mids, x);
@@ -282,11 +275,6 @@ __device__ __forceinline__ void lane_scales(const float* const* vecs, long long 
   }
 }
 
-// Monotone max of a non-negative float through an integer atomic; a stale read can only be too
-// small, so skipping the atomic when the value is not larger is always safe.
-__device__ __forceinline__ void atomic_max_nonneg(float* addr, float val) {
-  if (val > *reinterpret_cast<volatile float*>(addr)) atomicMax(reinterpret_cast<int*>(addr), __float_as_int(val));
-}
 
 // ---------------------------------------------------------------------------------------------
 // AdamW, non-fused semantics.  MM: first-moment storage, VM: second-moment storage / source.
