@@ -250,9 +250,14 @@ def run_own(args):
     else:
         from lpmm.zero import Zero1FusedAdamW
         torch.manual_seed(0)
-        opt = Zero1FusedAdamW(shapes, dev, gather=args.gather, **HYPER)
+        opt = Zero1FusedAdamW(shapes, dev, gather=args.gather, reduce_grads=args.reduce_grads, **HYPER)
         opt.init_params_normal_(0.02, seed=0)
-        student_t_(opt.grad_shard.view(-1), 100003 + rank, rows_outliers=False)
+        if args.reduce_grads:  # every rank's own full gradients; the step sums them over the ranks
+            chunk = 1 << 26
+            for lo_ in range(0, opt.grad_flat.numel(), chunk):
+                student_t_(opt.grad_flat[lo_: lo_ + chunk], 100003 + 977 * rank + lo_ // chunk, rows_outliers=False)
+        else:
+            student_t_(opt.grad_shard.view(-1), 100003 + rank, rows_outliers=False)
 
         def step():
             opt.step()
@@ -356,6 +361,8 @@ def run_own(args):
         e_ms = a.elapsed_time(b) / n_e2e
         e2e = {"value": total / (e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": 4 * total, "d2h_bytes_per_step": 4096,
                "ms_per_step": e_ms, "steps": n_e2e}
+    elif args.reduce_grads:
+        e2e = None  # the gradients are produced on each GPU (data-parallel backward); no host copy belongs to this mode
     else:
         # each rank's gradient shard arrives from pinned host memory every step
         n_sh = opt.grad_shard.numel()
@@ -400,7 +407,8 @@ def run_own(args):
                        "params_4bit": nq, "params_fp32_state": nf, "layers": n_layers,
                        "parallelism": "single GPU" if world == 1 else (
                            f"ZeRO-1 over {world} GPUs, group-aligned shards, fp32 params reach the peers by "
-                           + ("NVLink stores inside the update kernel" if args.gather == "fused" else "an NCCL all-gather after the update")),
+                           + ("NVLink stores inside the update kernel" if args.gather == "fused" else "an NCCL all-gather after the update")
+                           + ("; gradients of all ranks summed by NVLink loads inside the same kernel" if args.reduce_grads else "")),
                        "l2": "inputs (>= 90 GB touched per step) exceed the 126 MB L2; no explicit flush"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": n_launch, "roofline": roofline, "cpu_baseline": cpu,
         }
@@ -420,6 +428,9 @@ def main():
     ap.add_argument("--model", default="7b", choices=["7b", "13b"],
                     help="7b: the headline list; 13b: the LLaMA-13B-shaped list (52 GB of fp32 parameters per GPU)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--reduce-grads", action="store_true",
+                    help="N > 1, --gather fused: every rank holds full local gradients and the update kernel also sums "
+                         "them over the ranks (reduce-scatter inside the step); no e2e figure in this mode")
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
                     help="N > 1: parameters reach the peers by stores inside the update kernel, or by an NCCL all-gather after it")
     args = ap.parse_args()

@@ -116,6 +116,22 @@ int lpmm_b200_adamw4bit_multi_tensor_peers(const lpmm_b200_tensor* tensors, int 
                                            int64_t group_end, const int64_t* peer_byte_offsets, int n_peers,
                                            void* stream);
 
+/* The whole ZeRO-1 step in one kernel: additionally to the above, the gradient of every element of
+ * this rank's range is the sum, in the order given, of the values found at the n_grads (<= 8) byte
+ * offsets from its address in this GPU's gradient buffer (tensors[i].g; offset 0 is this GPU's own
+ * copy, the others lead to the same element of the peers' gradient buffers in peer-mapped memory),
+ * multiplied by grad_scale (1/world for a mean).  Each rank thus reads only the gradients of its own
+ * groups from every peer over NVLink (the reduce-scatter) while it stores its updated parameters into
+ * the peers' parameter buffers (the all-gather), both inside the update kernel.  All ranks must have
+ * finished writing their gradients before any rank's call starts reading them, and must not overwrite
+ * them before every call has finished (order with a barrier on the stream).  Offsets must be multiples
+ * of 32.  n_grads == 0: gradients are read from tensors[i].g alone, as in the entry point above. */
+int lpmm_b200_adamw4bit_multi_tensor_zero1(const lpmm_b200_tensor* tensors, int n_tensors, const float* exp_avg_qmap,
+                                           const float* exp_avg_sq_qmap, lpmm_b200_hyper hyper, int64_t group_begin,
+                                           int64_t group_end, const int64_t* peer_byte_offsets, int n_peers,
+                                           const int64_t* grad_byte_offsets, int n_grads, float grad_scale,
+                                           void* stream);
+
 /* Number of 128-element groups of a tensor list (the size of the index space above), or a
  * negative status.  Host-only arithmetic. */
 int64_t lpmm_b200_count_groups(const lpmm_b200_tensor* tensors, int n_tensors);

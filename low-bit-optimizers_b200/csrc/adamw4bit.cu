@@ -40,7 +40,48 @@ struct Consts {
 struct PeerInfo {
   int n;
   long long off[7];
+  // Gradient reduction inside the same kernel: when gn > 0 the gradient of an element is the sum, in
+  // rank order, of the values at the gn byte offsets goff[] from its address in this GPU's gradient
+  // buffer (offset 0 = this GPU's own copy), times gscale.  Each rank reads the gradients of its own
+  // group range from every peer over NVLink: the reduce-scatter of ZeRO-1 happens in the update kernel.
+  int gn;
+  float gscale;
+  long long goff[8];
 };
+// PEERS false (single-GPU instantiations): plain loads, no trace of the above in the code.
+template <bool PEERS>
+__device__ __forceinline__ float load_g1(const float* a, const PeerInfo& pi) {
+  if (!PEERS || pi.gn == 0) return *a;
+  float s = *reinterpret_cast<const float*>(reinterpret_cast<const char*>(a) + pi.goff[0]);
+  for (int i = 1; i < pi.gn; ++i)
+    s = __fadd_rn(s, *reinterpret_cast<const float*>(reinterpret_cast<const char*>(a) + pi.goff[i]));
+  return __fmul_rn(s, pi.gscale);
+}
+template <bool PEERS>
+__device__ __forceinline__ f8 load_g8(const float* a, const PeerInfo& pi) {
+  if (!PEERS || pi.gn == 0) return ldg_f8(a);
+  f8 s = ldg_f8(reinterpret_cast<const float*>(reinterpret_cast<const char*>(a) + pi.goff[0]));
+  for (int i = 1; i < pi.gn; ++i) {
+    const f8 x = ldg_f8(reinterpret_cast<const float*>(reinterpret_cast<const char*>(a) + pi.goff[i]));
+#pragma unroll
+    for (int k = 0; k < 8; ++k) s.x[k] = __fadd_rn(s.x[k], x.x[k]);
+  }
+#pragma unroll
+  for (int k = 0; k < 8; ++k) s.x[k] = __fmul_rn(s.x[k], pi.gscale);
+  return s;
+}
+__device__ __forceinline__ f2x4 load_g2x4(const float* a, const PeerInfo& pi) {
+  f2x4 s = ldg_f2x4(reinterpret_cast<const float*>(reinterpret_cast<const char*>(a) + pi.goff[0]));
+  for (int i = 1; i < pi.gn; ++i) {
+    const f2x4 x = ldg_f2x4(reinterpret_cast<const float*>(reinterpret_cast<const char*>(a) + pi.goff[i]));
+#pragma unroll
+    for (int j = 0; j < 4; ++j) s.v[j] = f2_add(s.v[j], x.v[j]);
+  }
+  const f2 sc = f2_splat(pi.gscale);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) s.v[j] = f2_mul(s.v[j], sc);
+  return s;
+}
 __device__ __forceinline__ void peer_store1(float* addr, float val, const PeerInfo& pi) {
   for (int i = 0; i < pi.n; ++i) *reinterpret_cast<float*>(reinterpret_cast<char*>(addr) + pi.off[i]) = val;
 }
@@ -67,6 +108,7 @@ __device__ __forceinline__ float upd_p(const Consts& c, float p, float m, float 
 // Any 4-bit group, any alignment, any map: scalar accesses predicated on numel
 // (fused_adamw_kernel.cu:114,130-143,160-165), IEEE sqrt and division, the reference's search.
 // The fast path falls back to this before it has stored anything.
+template <bool PEERS>
 __device__ __noinline__ void group_q4_generic(const TDesc& t, long long gl, int l16, unsigned hmask,
                                               const Consts& c, const QMapSmem& Sm, const QMapSmem& Sv,
                                               const PeerInfo& pi) {
@@ -84,7 +126,7 @@ __device__ __noinline__ void group_q4_generic(const TDesc& t, long long gl, int 
     v[k] = 0.0f;
     if (e0 + k < n) {
       const uint8_t mbyte = mb[k >> 1], vbyte = vb[k >> 1];
-      const float g = t.g[e0 + k];
+      const float g = load_g1<PEERS>(t.g + e0 + k, pi);
       const float m0 = __fmul_rn(Sm.qmap[(mbyte >> (4 * (k & 1))) & 15u], sm);
       const float v0 = __fmul_rn(Sv.qmap[(vbyte >> (4 * (k & 1))) & 15u], sv);
       m[k] = upd_m(c, m0, g);
@@ -147,7 +189,7 @@ struct LanePtrs {
 // One full, aligned 4-bit group: lane owns elements [8*l16, 8*l16+8) of group gl.
 // qm_l / qv_l: this lane's entry of the two maps (qmap[l16]).  pf: how many groups ahead this
 // half-warp's next group lies (0 = none); its lines are requested into L2 now.
-template <bool FAST, bool VLIN>
+template <bool FAST, bool VLIN, bool PEERS>
 __device__ __forceinline__ void group_q4_fast(const LanePtrs& t, unsigned gl, int l16, unsigned hmask,
                                               const Consts& c, const QMapSmem& Sm, const QMapSmem& Sv,
                                               const LutEnt* __restrict__ lut_m, const LutEnt* __restrict__ lut_v,
@@ -157,7 +199,7 @@ __device__ __forceinline__ void group_q4_fast(const LanePtrs& t, unsigned gl, in
   uint32_t* mcp = t.mc + (size_t)gl * 16;
   uint32_t* vcp = t.vc + (size_t)gl * 16;
   f8 p = ldg_f8(pp);
-  const f8 g = ldg_f8(gp);
+  const f8 g = load_g8<PEERS>(gp, pi);
   const uint32_t mc = *mcp;
   const uint32_t vc = *vcp;
   const float pm = __fmul_rn(qm_l, t.sm[gl]);  // lane i: qmap_m[i] * scale
@@ -231,7 +273,7 @@ __device__ __forceinline__ void group_q4_x2(const LanePtrs& t, unsigned gl, int 
   uint32_t* mcp = t.mc + (size_t)gl * 16;
   uint32_t* vcp = t.vc + (size_t)gl * 16;
   f2x4 p = ldg_f2x4(pp);
-  const f2x4 g = ldg_f2x4(gp);
+  const f2x4 g = (PEERS && pi.gn > 0) ? load_g2x4(gp, pi) : ldg_f2x4(gp);
   const uint32_t mc = *mcp;
   const uint32_t vc = *vcp;
   const float pm = __fmul_rn(qm_l, t.sm[gl]);  // lane i: qmap_m[i] * scale
@@ -331,14 +373,14 @@ __device__ __forceinline__ void group_q4_x2(const LanePtrs& t, unsigned gl, int 
 }
 
 // fp32-state tensors (the numel <= threshold fallback), 128 elements per half-warp step.
-template <bool FAST>
+template <bool FAST, bool PEERS>
 __device__ __forceinline__ void group_fp32(const TDesc& t, long long gl, int l16, const Consts& c, const PeerInfo& pi) {
   const long long e0 = gl * 128 + l16 * 8;
   float* mp = reinterpret_cast<float*>(t.m);
   float* vp = reinterpret_cast<float*>(t.v);
   if (t.aligned && (gl + 1) * 128 <= t.numel) {
     f8 p = ldg_f8(t.p + e0);
-    const f8 g = ldg_f8(t.g + e0);
+    const f8 g = load_g8<PEERS>(t.g + e0, pi);
     f8 m = ldg_f8(mp + e0);
     f8 v = ldg_f8(vp + e0);
 #pragma unroll
@@ -355,7 +397,7 @@ __device__ __forceinline__ void group_fp32(const TDesc& t, long long gl, int l16
     for (int k = 0; k < 8; ++k) {
       const long long e = e0 + k;
       if (e < t.numel) {
-        const float g = t.g[e];
+        const float g = load_g1<PEERS>(t.g + e, pi);
         const float m = upd_m(c, mp[e], g);
         const float v = upd_v(c, vp[e], g);
         mp[e] = m;
@@ -425,15 +467,15 @@ __device__ __forceinline__ void run_groups(const Table& tab, const Consts& c, co
                                        (gl + PF_DIST * st < lim) ? PF_DIST * st : 0u, pi);
           } else {
             for (; gl < lim; gl += st)
-              group_q4_fast<FAST, VLIN>(lp, gl, l16, hmask, c, Sm, Sv, lut_m, lut_v, qm_l, qv_l,
+              group_q4_fast<FAST, VLIN, PEERS>(lp, gl, l16, hmask, c, Sm, Sv, lut_m, lut_v, qm_l, qv_l,
                                         (gl + st < lim) ? st : 0u, pi);
           }
           gi = tstart + gl;
         }
       }
-      for (; gi < tend; gi += stride) group_q4_generic(t, gi - tstart, l16, hmask, c, Sm, Sv, pi);
+      for (; gi < tend; gi += stride) group_q4_generic<PEERS>(t, gi - tstart, l16, hmask, c, Sm, Sv, pi);
     } else {
-      for (; gi < tend; gi += stride) group_fp32<FAST>(t, gi - tstart, l16, c, pi);
+      for (; gi < tend; gi += stride) group_fp32<FAST, PEERS>(t, gi - tstart, l16, c, pi);
     }
   }
 }
@@ -524,7 +566,7 @@ static int launch_multi(const lpmm_b200_tensor* ts, int n, const float* qm, cons
     if (!w.work) continue;
     const unsigned grid = multi_grid(w);
     cudaError_t e;
-    if (pi.n > 0)
+    if (pi.n > 0 || pi.gn > 0)
       e = w.any_q4 ? launch_fast_or_exact<true, true>(fast, tab, grid, qm, qv, h, w.lo, w.hi, st, pi)
                    : launch_fast_or_exact<false, true>(fast, tab, grid, qm, qv, h, w.lo, w.hi, st, pi);
     else
@@ -639,6 +681,36 @@ extern "C" int lpmm_b200_adamw4bit_multi_tensor_peers(const lpmm_b200_tensor* te
   for (int i = 0; i < n_peers; ++i) {
     if (peer_byte_offsets[i] % 32 != 0) return LPMM_B200_ERR_BAD_SIZE;  // keeps the 256-bit stores aligned
     pi.off[i] = peer_byte_offsets[i];
+  }
+  return launch_multi(tensors, n_tensors, exp_avg_qmap, exp_avg_sq_qmap, hyper, group_begin, group_end,
+                      (cudaStream_t)stream, pi);
+}
+
+extern "C" int lpmm_b200_adamw4bit_multi_tensor_zero1(const lpmm_b200_tensor* tensors, int n_tensors,
+                                                      const float* exp_avg_qmap, const float* exp_avg_sq_qmap,
+                                                      lpmm_b200_hyper hyper, int64_t group_begin, int64_t group_end,
+                                                      const int64_t* peer_byte_offsets, int n_peers,
+                                                      const int64_t* grad_byte_offsets, int n_grads, float grad_scale,
+                                                      void* stream) {
+  if (n_peers < 0 || n_peers > 7 || n_grads < 0 || n_grads > 8) return LPMM_B200_ERR_BAD_SIZE;
+  if ((n_peers > 0 && !peer_byte_offsets) || (n_grads > 0 && !grad_byte_offsets)) return LPMM_B200_ERR_NULL_POINTER;
+  int rc = check_list(tensors, n_tensors, false, exp_avg_qmap, exp_avg_sq_qmap);
+  if (rc != LPMM_B200_OK) return rc;
+  const int64_t total = lpmm_b200_count_groups(tensors, n_tensors);
+  if (group_end < 0) group_end = total;
+  if (group_begin < 0 || group_begin > group_end || group_end > total) return LPMM_B200_ERR_BAD_SIZE;
+  if (group_begin == group_end) return LPMM_B200_OK;
+  PeerInfo pi = {};
+  pi.n = n_peers;
+  for (int i = 0; i < n_peers; ++i) {
+    if (peer_byte_offsets[i] % 32 != 0) return LPMM_B200_ERR_BAD_SIZE;  // keeps the 256-bit stores aligned
+    pi.off[i] = peer_byte_offsets[i];
+  }
+  pi.gn = n_grads;
+  pi.gscale = grad_scale;
+  for (int i = 0; i < n_grads; ++i) {
+    if (grad_byte_offsets[i] % 32 != 0) return LPMM_B200_ERR_BAD_SIZE;  // keeps the 256-bit loads aligned
+    pi.goff[i] = grad_byte_offsets[i];
   }
   return launch_multi(tensors, n_tensors, exp_avg_qmap, exp_avg_sq_qmap, hyper, group_begin, group_end,
                       (cudaStream_t)stream, pi);

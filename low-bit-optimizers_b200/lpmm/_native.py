@@ -86,6 +86,8 @@ def _load():
         "lpmm_b200_adamw4bit_multi_tensor": (i32, [ctypes.POINTER(Tensor), i32, vp, vp, Hyper, i64, i64, vp]),
         "lpmm_b200_adamw4bit_multi_tensor_peers": (i32, [ctypes.POINTER(Tensor), i32, vp, vp, Hyper, i64, i64,
                                                          ctypes.POINTER(i64), i32, vp]),
+        "lpmm_b200_adamw4bit_multi_tensor_zero1": (i32, [ctypes.POINTER(Tensor), i32, vp, vp, Hyper, i64, i64,
+                                                         ctypes.POINTER(i64), i32, ctypes.POINTER(i64), i32, f, vp]),
         "lpmm_b200_count_groups": (i64, [ctypes.POINTER(Tensor), i32]),
         "lpmm_b200_bias_corrections": (i32, [f, f, f, vp, vp]),
         "lpmm_b200_packed_len": (i64, [i64]),

@@ -15,6 +15,12 @@ ranges of equal length S = ceil(G / world) and rank r
   memory (plain vectorised stores over NVLink, no multicast), so transfer and update overlap group
   by group and only a barrier follows.
 
+With ``reduce_grads=True`` the gradient reduce-scatter moves into the launch as well: every rank keeps
+its full local gradients in a peer-mapped buffer and the update kernel sums, for each element of the
+rank's own range, the values of all ranks (fixed rank order) before the update -- reads of the peers'
+gradients and stores into the peers' parameters travel over NVLink in opposite directions while the
+kernel computes.  The whole ZeRO-1 step (reduce-scatter, update, all-gather) is then one kernel.
+
 The result is bit-identical to the unsharded step.  A shard may cut a tensor but never a group.
 """
 import ctypes
@@ -68,7 +74,7 @@ class Zero1FusedAdamW:
     """
 
     def __init__(self, shapes, device, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=1e-2, process_group=None,
-                 rank=None, world=None, gather="nccl"):
+                 rank=None, world=None, gather="nccl", reduce_grads=False, grad_scale=None):
         from .functional import create_general_qmap
         self.shapes = [tuple(s) for s in shapes]
         self.numels = [int(torch.Size(s).numel()) for s in self.shapes]
@@ -100,6 +106,25 @@ class Zero1FusedAdamW:
         self.params = [self.flat[gs * GROUP: gs * GROUP + n].view(s)
                        for s, n, gs in zip(self.shapes, self.numels, self.gstart)]
         self.grad_shard = torch.zeros(S * GROUP, dtype=torch.float32, device=self.device)
+        # reduce_grads: every rank holds a FULL flat gradient buffer (its local gradients, as data-parallel
+        # backward leaves them) in symmetric memory, ``self.grads[i]`` its views; the update kernel of a rank
+        # sums the gradients of its own group range over all ranks (rank order 0 .. world-1) and multiplies
+        # by ``grad_scale`` (default 1/world): the reduce-scatter happens inside the step.
+        self.reduce_grads = bool(reduce_grads) and self.world > 1
+        self.grad_offsets = None
+        if self.reduce_grads:
+            if self.gather != "fused":
+                raise ValueError("reduce_grads needs gather='fused' (peer-mapped buffers)")
+            import torch.distributed._symmetric_memory as symm_mem
+            self.grad_flat = symm_mem.empty(self.world * S * GROUP, dtype=torch.float32, device=self.device)
+            self.grad_flat.zero_()
+            self._gsymm = symm_mem.rendezvous(self.grad_flat, process_group if process_group is not None else dist.group.WORLD)
+            gptrs = list(self._gsymm.buffer_ptrs)
+            gmine = self.grad_flat.data_ptr()
+            self.grad_offsets = [int(gptrs[r]) - gmine for r in range(self.world)]
+            self.grad_scale = float(grad_scale) if grad_scale is not None else 1.0 / self.world
+            self.grads = [self.grad_flat[gs * GROUP: gs * GROUP + n].view(s)
+                          for s, n, gs in zip(self.shapes, self.numels, self.gstart)]
         # states of the owned range only
         self.m_codes = torch.zeros(S * (GROUP // 2), dtype=torch.int8, device=self.device)
         self.v_codes = torch.zeros(S * (GROUP // 2), dtype=torch.int8, device=self.device)
@@ -168,7 +193,10 @@ class Zero1FusedAdamW:
         for n, gs, fs in zip(self.numels, self.gstart, self.fstart):
             d = gs - self.lo  # may be negative
             p = self.flat.data_ptr() + gs * GROUP * 4
-            g = self.grad_shard.data_ptr() + d * GROUP * 4
+            if self.reduce_grads:
+                g = self.grad_flat.data_ptr() + gs * GROUP * 4
+            else:
+                g = self.grad_shard.data_ptr() + d * GROUP * 4
             if n > THRESHOLD:
                 out.append((p, g, self.m_codes.data_ptr() + d * (GROUP // 2), self.v_codes.data_ptr() + d * (GROUP // 2),
                             self.m_scale.data_ptr() + d * 4, self.v_scale.data_ptr() + d * 4, n, 0))
@@ -191,7 +219,13 @@ class Zero1FusedAdamW:
         with torch.cuda.device(self.device):
             qm, qv = ctypes.c_void_p(self.qmap_m.data_ptr()), ctypes.c_void_p(self.qmap_v.data_ptr())
             st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
-            if self.peer_offsets:
+            if self.reduce_grads:
+                offs = (ctypes.c_int64 * len(self.peer_offsets))(*self.peer_offsets)
+                goffs = (ctypes.c_int64 * len(self.grad_offsets))(*self.grad_offsets)
+                N.check(N.lib.lpmm_b200_adamw4bit_multi_tensor_zero1(self._tl, len(self.numels), qm, qv, h, lo, hi, offs,
+                                                                     len(self.peer_offsets), goffs, len(self.grad_offsets),
+                                                                     self.grad_scale, st))
+            elif self.peer_offsets:
                 offs = (ctypes.c_int64 * len(self.peer_offsets))(*self.peer_offsets)
                 N.check(N.lib.lpmm_b200_adamw4bit_multi_tensor_peers(self._tl, len(self.numels), qm, qv, h, lo, hi, offs,
                                                                      len(self.peer_offsets), st))
@@ -210,6 +244,10 @@ class Zero1FusedAdamW:
 
     def step(self):
         self.step_count += 1
+        if self.reduce_grads:
+            # every rank's gradients must be complete before any rank reads them; the barrier after the
+            # update (in _gather) keeps them from being overwritten while a peer still reads
+            dist.all_reduce(self._flag, group=self.pg)
         if self.hi > self.lo:
             self._update(self.lo, self.hi)
         self._gather()

@@ -1,6 +1,8 @@
 """Run under torch.distributed.run on 2 or more GPUs (tests/test_gpu_zero_multi.py does): the ZeRO-1 step
 with parameters pushed to the peers by stores inside the update kernel equals the ZeRO-1 step followed by an
-NCCL all-gather, bit for bit, and every rank ends with the same parameter buffer.  Prints one OK line per rank."""
+NCCL all-gather, bit for bit, and every rank ends with the same parameter buffer; and the step that also
+reduces the gradients of all ranks inside the update kernel equals the step on gradients summed beforehand.
+Prints one OK line per rank."""
 import os, sys, torch, torch.distributed as dist
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, os.path.join(ROOT, "low-bit-optimizers_b200"))
@@ -25,5 +27,31 @@ same = bool(torch.equal(a.view(torch.int32), b.view(torch.int32)))
 chk = torch.tensor([float(b.double().sum())], device=dev, dtype=torch.float64); lst = [torch.zeros_like(chk) for _ in range(world)]
 dist.all_gather(lst, chk)
 ok = same and all(float(x) == float(lst[0]) for x in lst)
-print(f"rank {rank}: {'OK' if ok else 'MISMATCH'} (fused == nccl: {same})", flush=True)
+# ---- gradient reduce-scatter inside the update kernel: every rank contributes its own gradients; the result
+# must equal the step on gradients summed in rank order and scaled by 1/world with torch ops
+red = Zero1FusedAdamW(shapes, dev, gather="fused", reduce_grads=True, **H)
+ref = Zero1FusedAdamW(shapes, dev, gather="nccl", **H)
+red.init_params_normal_(0.02, seed=0); ref.init_params_normal_(0.02, seed=0)
+for step in range(1, 4):
+    per_rank = []
+    for r in range(world):
+        gs = []
+        for i, s in enumerate(shapes):
+            g = torch.Generator(device=dev); g.manual_seed(step * 100003 + 1000 * r + i)
+            gs.append(torch.randn(s, generator=g, device=dev) * 1e-3)
+        per_rank.append(gs)
+    for i in range(len(shapes)):
+        red.grads[i].copy_(per_rank[rank][i])
+    summed = []
+    for i in range(len(shapes)):
+        acc = per_rank[0][i].clone()
+        for r in range(1, world):
+            acc = acc + per_rank[r][i]
+        summed.append(acc * (1.0 / world))
+    ref.set_grad_shard_from_full(summed)
+    red.step(); ref.step()
+torch.cuda.synchronize(); dist.barrier()
+same2 = bool(torch.equal(red.flat.view(torch.int32), ref.flat.view(torch.int32)))
+ok = ok and same2
+print(f"rank {rank}: {'OK' if ok else 'MISMATCH'} (fused == nccl: {same}, in-kernel gradient reduction == summed gradients: {same2})", flush=True)
 dist.destroy_process_group()
