@@ -61,6 +61,10 @@ def test_argument_validation_without_a_gpu():
     assert lib.lpmm_b200_adamw4bit_unfused_step_many(None, 0, None, None, 0.9, 0.999, 1e-3, 0.0, 1e-8, None, None, 0,
                                                      None) == 0
     arr[0].kind = N.KIND_Q4
+    offs = (ctypes.c_int64 * 9)(*([32] * 9))
+    assert lib.lpmm_b200_adamw4bit_multi_tensor_zero1(arr, 2, None, None, N.Hyper(), 0, -1, offs, 8, offs, 2, 0.5, None) == -2
+    assert lib.lpmm_b200_adamw4bit_multi_tensor_zero1(arr, 2, None, None, N.Hyper(), 0, -1, offs, 1, offs, 9, 0.5, None) == -2
+    assert lib.lpmm_b200_adamw4bit_multi_tensor_zero1(arr, 2, None, None, N.Hyper(), 0, -1, offs, 1, None, 2, 0.5, None) == -1
     assert lib.lpmm_b200_sgd4bit_multi_tensor(arr, 2, None, 0.0, 0.0, 1e-2, 0.0, 0, 0, 0, -1, None) == -3  # momentum 0
     assert lib.lpmm_b200_sgd4bit_multi_tensor(arr, 2, None, 0.0, 0.9, 1e-2, 0.0, 0, 0, 0, -1, None) == -1  # null data
     assert lib.lpmm_b200_sgd4bit_multi_tensor(None, -1, None, 0.0, 0.9, 1e-2, 0.0, 0, 0, 0, -1, None) == -2
