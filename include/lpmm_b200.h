@@ -310,6 +310,25 @@ int lpmm_b200_adamw4bit_unfused_step_many(const lpmm_b200_step_tensor* const* te
                                           double weight_decay, double eps, const double* steps, void* scratch,
                                           int64_t scratch_bytes, void* stream);
 
+/* The fused step on the non-fused state layout: the arithmetic of the reference's fused kernel
+ * (lpmm/cpp_extension/fused_adamw_kernel.cu:103-128: float hyper-parameters, bias corrections by the
+ * device's powf, m = fma(b1, m0, (1-b1)g), v = fma(b2, v0, ((1-b2)g)g), d = (sqrt(v)/c2s + eps)c1,
+ * p = fma(-lr, fma(wd, p, m/d), p)) on the states of lpmm_b200_adamw4bit_unfused_step, which the
+ * fused kernel itself cannot hold: above all a RANK1_4 second moment (per-axis maxima by the two-pass
+ * grid reduction).  The reference has no such step: with a rank-1 configuration its fused=True warns
+ * and uses group scales (lpmm/optim/adamw.py:503-506).  4-bit codes only; the moments are both FP32,
+ * both GROUP4, or GROUP4 + RANK1_4; FACTORED is not covered (LPMM_B200_ERR_UNSUPPORTED).  States that
+ * are all zero (zero maxima) step like first != 0.  The _many form follows
+ * lpmm_b200_adamw4bit_unfused_step_many: eligible 2-D RANK1_4 tensors that share a step count take
+ * three launches together, the others a launch chain each on the library's streams. */
+int lpmm_b200_adamw4bit_fused_arith_step(const lpmm_b200_step_tensor* t, const float* qmap_m, const float* qmap_v,
+                                         double beta1, double beta2, double lr, double weight_decay, double eps,
+                                         double step, void* stream);
+int lpmm_b200_adamw4bit_fused_arith_step_many(const lpmm_b200_step_tensor* const* tensors, int n, const float* qmap_m,
+                                              const float* qmap_v, double beta1, double beta2, double lr,
+                                              double weight_decay, double eps, const double* steps, void* scratch,
+                                              int64_t scratch_bytes, void* stream);
+
 /* One momentum-SGD step of one tensor with the arithmetic of _single_tensor_sgd4bit
  * (lpmm/optim/sgd.py:133-187).  buf_mode FP32 or GROUP4; first != 0: the buffer is created from
  * the (decayed) gradient.  momentum == 0 ignores the buffer. */

@@ -50,6 +50,8 @@ def cases():
         ("linear4096 adamw rank-1 (default.yml)", "AdamW", LINEAR, dict(adamw, qconfig=cfg("default.yml"))),
         ("linear4096 adamw group (qconfig=None)", "AdamW", LINEAR, dict(adamw, qconfig=None)),
         ("linear4096 adamw fused", "AdamW", LINEAR, dict(adamw, fused=True)),
+        ("linear4096 adamw fused rank-1 (default.yml, fused_rank1)", "AdamW", LINEAR,
+         dict(adamw, qconfig=cfg("default.yml"), fused=True, fused_rank1=True)),
     ]
     for c in ("default_8b.yml", "default_5b.yml", "1st_moment_group_512.yml", "1st_moment_group_4096.yml"):
         out.append((f"linear4096 adamw {c}", "AdamW", LINEAR, dict(adamw, qconfig=cfg(c))))
@@ -59,6 +61,8 @@ def cases():
         ("gpt2-medium adamw rank-1 (default.yml)", "AdamW", gpt2_medium_shapes(), dict(adamw, qconfig=cfg("default.yml"))),
         ("gpt2-medium adamw group (qconfig=None)", "AdamW", gpt2_medium_shapes(), dict(adamw, qconfig=None)),
         ("gpt2-medium adamw fused", "AdamW", gpt2_medium_shapes(), dict(adamw, fused=True)),
+        ("gpt2-medium adamw fused rank-1 (default.yml, fused_rank1)", "AdamW", gpt2_medium_shapes(),
+         dict(adamw, qconfig=cfg("default.yml"), fused=True, fused_rank1=True)),
         ("gpt2-medium sgd", "SGD", gpt2_medium_shapes(), dict(sgd)),
         ("ragged adamw rank-1 (default.yml)", "AdamW", RAGGED, dict(adamw, qconfig=cfg("default.yml"))),
     ]
@@ -72,6 +76,8 @@ def big_cases():
         ("llama7b adamw group (qconfig=None)", "AdamW", llama7b_shapes(), dict(adamw, qconfig=None)),
         ("llama7b adamw fused", "AdamW", llama7b_shapes(), dict(adamw, fused=True)),
         ("llama7b adamw rank-1 (default.yml)", "AdamW", llama7b_shapes(), dict(adamw, qconfig=cfg("default.yml"))),
+        ("llama7b adamw fused rank-1 (default.yml, fused_rank1)", "AdamW", llama7b_shapes(),
+         dict(adamw, qconfig=cfg("default.yml"), fused=True, fused_rank1=True)),
         ("llama7b adamw factored", "AdamW", llama7b_shapes(), dict(adamw, factor_second_moment=True)),
         ("llama7b sgd", "SGD", llama7b_shapes(), dict(lr=1e-2, momentum=0.9, weight_decay=1e-4)),
     ]

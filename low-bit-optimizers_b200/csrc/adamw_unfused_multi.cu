@@ -24,6 +24,7 @@ constexpr size_t UM_DYN_SMEM = 2 * LUT_ENTRIES * sizeof(LutEnt);  // one table p
 
 // Any 4-bit group, any alignment, any map: scalar accesses predicated on numel, IEEE division, the
 // reference's search.  The whole group is requantised (its padding is 0 / max).
+template <bool A>
 __device__ __noinline__ void um_group_generic(const TDesc& t, long long gl, int l16, unsigned hmask, const UConsts& c,
                                               const QMapSmem& Sm, const QMapSmem& Sv) {
   const long long e0 = gl * 128 + l16 * 8;
@@ -43,9 +44,9 @@ __device__ __noinline__ void um_group_generic(const TDesc& t, long long gl, int 
       const float g = t.g[e0 + k];
       const float m0 = __fmul_rn(Sm.qmap[(mbyte >> (4 * (k & 1))) & 15u], sm);
       const float v0 = __fmul_rn(Sv.qmap[(vbyte >> (4 * (k & 1))) & 15u], sv);
-      m[k] = lerp_m(c, m0, g);
-      v[k] = upd_v2(c, v0, g);
-      t.p[e0 + k] = upd_param(c, t.p[e0 + k], m[k], v[k]);
+      m[k] = lerp_m<A>(c, m0, g);
+      v[k] = upd_v2<A>(c, v0, g);
+      t.p[e0 + k] = upd_param<A>(c, t.p[e0 + k], m[k], v[k]);
       am = fmaxf(am, fabsf(m[k]));
       av = fmaxf(av, v[k]);
     }
@@ -159,6 +160,7 @@ __device__ __forceinline__ void um_group_x2(const UmLane& t, unsigned gl, int l1
 }
 
 // fp32 moments (the numel <= threshold fallback), 128 elements per half-warp step.
+template <bool A>
 __device__ __forceinline__ void um_group_fp32(const TDesc& t, long long gl, int l16, const UConsts& c) {
   const long long e0 = gl * 128 + l16 * 8;
   float* mp = reinterpret_cast<float*>(t.m);
@@ -168,19 +170,23 @@ __device__ __forceinline__ void um_group_fp32(const TDesc& t, long long gl, int 
     const long long e = e0 + k;
     if (e < t.numel) {
       const float g = t.g[e];
-      const float m = lerp_m(c, mp[e], g);
-      const float v = upd_v2(c, vp[e], g);
+      const float m = lerp_m<A>(c, mp[e], g);
+      const float v = upd_v2<A>(c, vp[e], g);
       mp[e] = m;
       vp[e] = v;
-      t.p[e] = upd_param(c, t.p[e], m, v);
+      t.p[e] = upd_param<A>(c, t.p[e], m, v);
     }
   }
 }
 
-template <bool HAS_Q4>
+// A: the arithmetic of the reference's fused kernel (scalar paths only) instead of its torch operations.
+template <bool HAS_Q4, bool A>
 __global__ void __launch_bounds__(CTA_THREADS, CTAS_PER_SM)
 adamw_unfused_multi_kernel(const __grid_constant__ Table tab, const float* __restrict__ qmap_m,
-                           const float* __restrict__ qmap_v, const UConsts c, long long gbeg, long long gend) {
+                           const float* __restrict__ qmap_v, const UConsts cin, long long gbeg, long long gend) {
+  UConsts cf;
+  if (A) cf = fused_consts(cin);
+  const UConsts& c = A ? cf : cin;
   extern __shared__ __align__(16) unsigned char dyn_smem[];
   __shared__ QMapSmem Sm, Sv;
   LutEnt* lut_m = reinterpret_cast<LutEnt*>(dyn_smem);
@@ -209,7 +215,7 @@ adamw_unfused_multi_kernel(const __grid_constant__ Table tab, const float* __res
     long long tend = (ti + 1 < tab.n) ? tab.t[ti + 1].gstart : tab.gtotal;
     if (tend > gend) tend = gend;
     if (t.kind == LPMM_B200_KIND_Q4) {
-      if (tables_ok && t.aligned && c.fast) {
+      if (!A && tables_ok && t.aligned && c.fast) {
         long long fend = tstart + t.numel / 128;  // end of the full groups
         if (fend > tend) fend = tend;
         if (gi < fend) {
@@ -229,14 +235,14 @@ adamw_unfused_multi_kernel(const __grid_constant__ Table tab, const float* __res
           gi = tstart + gl;
         }
       }
-      for (; gi < tend; gi += stride) um_group_generic(t, gi - tstart, l16, hmask, c, Sm, Sv);
+      for (; gi < tend; gi += stride) um_group_generic<A>(t, gi - tstart, l16, hmask, c, Sm, Sv);
     } else {
-      for (; gi < tend; gi += stride) um_group_fp32(t, gi - tstart, l16, c);
+      for (; gi < tend; gi += stride) um_group_fp32<A>(t, gi - tstart, l16, c);
     }
   }
 }
 
-template <bool HAS_Q4>
+template <bool HAS_Q4, bool A>
 static cudaError_t launch_um(const Table& tab, unsigned grid, const float* qm, const float* qv, const UConsts& c,
                              long long lo, long long hi, cudaStream_t st) {
   static bool attr_set[64] = {};
@@ -244,12 +250,12 @@ static cudaError_t launch_um(const Table& tab, unsigned grid, const float* qm, c
   cudaGetDevice(&dev);
   const size_t smem = HAS_Q4 ? UM_DYN_SMEM : 0;
   if (HAS_Q4 && dev >= 0 && dev < 64 && !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(adamw_unfused_multi_kernel<HAS_Q4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(adamw_unfused_multi_kernel<HAS_Q4, A>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)UM_DYN_SMEM);
     if (e != cudaSuccess) return e;
     attr_set[dev] = true;
   }
-  adamw_unfused_multi_kernel<HAS_Q4><<<grid, CTA_THREADS, smem, st>>>(tab, qm, qv, c, lo, hi);
+  adamw_unfused_multi_kernel<HAS_Q4, A><<<grid, CTA_THREADS, smem, st>>>(tab, qm, qv, c, lo, hi);
   return cudaGetLastError();
 }
 
@@ -257,10 +263,9 @@ static cudaError_t launch_um(const Table& tab, unsigned grid, const float* qm, c
 
 using namespace lpmm_b200;
 
-extern "C" int lpmm_b200_adamw4bit_unfused_multi_tensor(const lpmm_b200_tensor* ts, int n, const float* qmap_m,
-                                                        const float* qmap_v, double beta1, double beta2, double lr,
-                                                        double weight_decay, double eps, double step,
-                                                        int64_t group_begin, int64_t group_end, void* stream) {
+static int um_step(const lpmm_b200_tensor* ts, int n, const float* qmap_m, const float* qmap_v, double beta1, double beta2,
+                   double lr, double weight_decay, double eps, double step, int64_t group_begin, int64_t group_end,
+                   void* stream, int arith) {
   bool any_q4 = false;
   int64_t total = 0;
   const int rc = check_tensor_list(ts, n, true, &any_q4, &total);
@@ -276,9 +281,29 @@ extern "C" int lpmm_b200_adamw4bit_unfused_multi_tensor(const lpmm_b200_tensor* 
   while (i < n) {
     const Window w = next_window(ts, n, i, gcursor, group_begin, group_end, true, tab);
     if (!w.work) continue;
-    const cudaError_t e = w.any_q4 ? launch_um<true>(tab, multi_grid(w), qmap_m, qmap_v, c, w.lo, w.hi, (cudaStream_t)stream)
-                                   : launch_um<false>(tab, multi_grid(w), qmap_m, qmap_v, c, w.lo, w.hi, (cudaStream_t)stream);
+    const unsigned grid = multi_grid(w);
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e;
+    if (arith) e = w.any_q4 ? launch_um<true, true>(tab, grid, qmap_m, qmap_v, c, w.lo, w.hi, st)
+                            : launch_um<false, true>(tab, grid, qmap_m, qmap_v, c, w.lo, w.hi, st);
+    else e = w.any_q4 ? launch_um<true, false>(tab, grid, qmap_m, qmap_v, c, w.lo, w.hi, st)
+                      : launch_um<false, false>(tab, grid, qmap_m, qmap_v, c, w.lo, w.hi, st);
     LPMM_CUDA_TRY(e);
   }
   return LPMM_B200_OK;
+}
+
+extern "C" int lpmm_b200_adamw4bit_unfused_multi_tensor(const lpmm_b200_tensor* ts, int n, const float* qmap_m,
+                                                        const float* qmap_v, double beta1, double beta2, double lr,
+                                                        double weight_decay, double eps, double step,
+                                                        int64_t group_begin, int64_t group_end, void* stream) {
+  return um_step(ts, n, qmap_m, qmap_v, beta1, beta2, lr, weight_decay, eps, step, group_begin, group_end, stream, 0);
+}
+
+// The same launch with the fused kernel's arithmetic on these (padded) states; internal to the library,
+// reached through lpmm_b200_adamw4bit_fused_arith_step_many.
+extern "C" int lpmm_b200_fused_arith_multi_tensor(const lpmm_b200_tensor* ts, int n, const float* qmap_m,
+                                                  const float* qmap_v, double beta1, double beta2, double lr,
+                                                  double weight_decay, double eps, double step, void* stream) {
+  return um_step(ts, n, qmap_m, qmap_v, beta1, beta2, lr, weight_decay, eps, step, 0, -1, stream, 1);
 }

@@ -68,6 +68,7 @@ __global__ void __launch_bounds__(R1T) r1_zero_kernel(const R1Desc* __restrict__
 // maxima in registers, one atomic per thread and column at the end), a row's maximum is reduced across
 // the lanes that share the row (one atomic per warp and row).  Two rows per thread are in flight.
 // Rows are multiples of 8 floats and 16-byte aligned (host-checked).
+template <bool A>
 __device__ __forceinline__ float r1_row_pass(const R1Desc& t, long long r, long long c0, const float* qv,
                                              const float* col_old, float* col_max, const UConsts& c,
                                              const float4& g0, const float4& g1, uint32_t codes, float row_old) {
@@ -76,15 +77,19 @@ __device__ __forceinline__ float r1_row_pass(const R1Desc& t, long long r, long 
 #pragma unroll
   for (int k = 0; k < 8; ++k) {
     const float v0 = __fmul_rn(qv[(codes >> (4 * k)) & 15u], fminf(row_old, col_old[k]));
-    const float v = upd_v2(c, v0, gx[k]);
+    const float v = upd_v2<A>(c, v0, gx[k]);
     col_max[k] = fmaxf(col_max[k], v);
     row_max = fmaxf(row_max, v);
   }
   return row_max;
 }
 
+template <bool A>
 __global__ void __launch_bounds__(R1T) r1_stats_kernel(const R1Desc* __restrict__ d, int n, long long total_tiles,
-                                                        const float* __restrict__ qmap_v, const UConsts c) {
+                                                        const float* __restrict__ qmap_v, const UConsts cin) {
+  UConsts cf;
+  if (A) cf = fused_consts(cin);
+  const UConsts& c = A ? cf : cin;
   __shared__ float qv[16];
   if (threadIdx.x < 16) qv[threadIdx.x] = qmap_v[threadIdx.x];
   __syncthreads();
@@ -128,8 +133,8 @@ __global__ void __launch_bounds__(R1T) r1_stats_kernel(const R1Desc* __restrict_
         cc = *reinterpret_cast<const uint32_t*>(t.v + (e0 >> 1));
         oc = __ldg(t.old_r + rc);
       }
-      float ma = ha ? r1_row_pass(t, ra, c0, qv, col_old, col_max, c, ga0, ga1, ca, oa) : 0.0f;
-      float mc = hc ? r1_row_pass(t, rc, c0, qv, col_old, col_max, c, gc0, gc1, cc, oc) : 0.0f;
+      float ma = ha ? r1_row_pass<A>(t, ra, c0, qv, col_old, col_max, c, ga0, ga1, ca, oa) : 0.0f;
+      float mc = hc ? r1_row_pass<A>(t, rc, c0, qv, col_old, col_max, c, gc0, gc1, cc, oc) : 0.0f;
       for (int o = seg >> 1; o; o >>= 1) {
         ma = fmaxf(ma, __shfl_xor_sync(0xffffffffu, ma, o));
         mc = fmaxf(mc, __shfl_xor_sync(0xffffffffu, mc, o));
@@ -149,6 +154,9 @@ __global__ void __launch_bounds__(R1T) r1_stats_kernel(const R1Desc* __restrict_
 
 // One 128-element unit of one matrix.  FULL lanes (8 elements inside one row, 16-byte aligned, short
 // exact sequences applicable) use packed arithmetic; every other lane takes the scalar IEEE path.
+// A (the fused kernel's arithmetic): FULL lanes keep the vector accesses and the quick requantisation
+// but update element by element.
+template <bool A>
 __device__ __forceinline__ void r1_unit(const R1Desc& t, long long u, int l16, unsigned hmask, const UConsts& c,
                                         const UConsts2& c2, const QMapSmem& Sm, const QMapSmem& Sv,
                                         const LutEnt* __restrict__ lut_m, bool lut_ok) {
@@ -169,7 +177,7 @@ __device__ __forceinline__ void r1_unit(const R1Desc& t, long long u, int l16, u
     r = ((e0 | C) >> 32) ? e0 / C : (long long)((unsigned)e0 / (unsigned)C);
     col = e0 - r * C;
   }
-  const bool full = c.fast && (e0 + 8 <= n) && (col + 8 <= C);  // C % 8 == 0 and aligned bases: host-checked
+  const bool full = (A ? c.f_fast : c.fast) && (e0 + 8 <= n) && (col + 8 <= C);  // C % 8 == 0 and aligned bases: host-checked
   float m[8], v[8], st_new[8];
   float am = 0.0f;
   if (full) {
@@ -192,6 +200,25 @@ __device__ __forceinline__ void r1_unit(const R1Desc& t, long long u, int l16, u
     const f2 sm2 = f2_splat(sm);
     float av = 0.0f;
     float px[8];
+    if (A) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float ga, gb, pa, pb;
+        f2_unpack(g.v[j], ga, gb);
+        f2_unpack(p.v[j], pa, pb);
+        const float gg[2] = {ga, gb}, pp[2] = {pa, pb};
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int k = 2 * j + h;
+          const float m0 = __fmul_rn(Sm.qmap[(mcodes >> (4 * k)) & 15u], sm);
+          const float v0 = __fmul_rn(Sv.qmap[(vcodes >> (4 * k)) & 15u], st_old[k]);
+          m[k] = lerp_m<true>(c, m0, gg[h]);
+          v[k] = upd_v2<true>(c, v0, gg[h]);
+          px[k] = upd_param<true>(c, pp[h], m[k], v[k]);
+          am = fmaxf(am, fabsf(m[k]));
+        }
+      }
+    } else {
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int k0 = 2 * j, k1 = 2 * j + 1;
@@ -203,6 +230,7 @@ __device__ __forceinline__ void r1_unit(const R1Desc& t, long long u, int l16, u
       f2_unpack(mj, m[k0], m[k1]);
       f2_unpack(vj, v[k0], v[k1]);
       f2_unpack(p.v[j], px[k0], px[k1]);
+    }
     }
     *reinterpret_cast<float4*>(t.p + e0) = make_float4(px[0], px[1], px[2], px[3]);
     *reinterpret_cast<float4*>(t.p + e0 + 4) = make_float4(px[4], px[5], px[6], px[7]);
@@ -220,9 +248,9 @@ __device__ __forceinline__ void r1_unit(const R1Desc& t, long long u, int l16, u
         const float g = t.g[e];
         const float m0 = __fmul_rn(Sm.qmap[(mcodes >> (4 * k)) & 15u], sm);
         const float v0 = __fmul_rn(Sv.qmap[(vcodes >> (4 * k)) & 15u], so);
-        m[k] = lerp_m(c, m0, g);
-        v[k] = upd_v2(c, v0, g);
-        t.p[e] = upd_param(c, t.p[e], m[k], v[k]);
+        m[k] = lerp_m<A>(c, m0, g);
+        v[k] = upd_v2<A>(c, v0, g);
+        t.p[e] = upd_param<A>(c, t.p[e], m[k], v[k]);
         am = fmaxf(am, fabsf(m[k]));
       }
     }
@@ -287,9 +315,13 @@ __device__ __forceinline__ void r1_unit(const R1Desc& t, long long u, int l16, u
   if (l16 == 0) t.m_max1[u] = am;
 }
 
+template <bool A>
 __global__ void __launch_bounds__(R1T, 4) r1_update_kernel(const R1Desc* __restrict__ d, int n, long long total_units,
                                                             const float* __restrict__ qmap_m,
-                                                            const float* __restrict__ qmap_v, const UConsts c) {
+                                                            const float* __restrict__ qmap_v, const UConsts cin) {
+  UConsts cf;
+  if (A) cf = fused_consts(cin);
+  const UConsts& c = A ? cf : cin;
   extern __shared__ __align__(16) unsigned char dyn_smem[];
   __shared__ QMapSmem Sm, Sv;
   LutEnt* lut_m = reinterpret_cast<LutEnt*>(dyn_smem);
@@ -305,7 +337,7 @@ __global__ void __launch_bounds__(R1T, 4) r1_update_kernel(const R1Desc* __restr
   for (int ti = 0; ti < n; ++ti) {
     const R1Desc& t = d[ti];
     const long long uend = (ti + 1 < n) ? d[ti + 1].ustart : total_units;
-    for (; gi < uend; gi += stride) r1_unit(t, gi - t.ustart, l16, hmask, c, c2, Sm, Sv, lut_m, lut_ok);
+    for (; gi < uend; gi += stride) r1_unit<A>(t, gi - t.ustart, l16, hmask, c, c2, Sm, Sv, lut_m, lut_ok);
   }
 }
 
@@ -337,7 +369,7 @@ extern "C" int lpmm_b200_rank1_multi_ok(const lpmm_b200_step_tensor* t) {
 extern "C" int lpmm_b200_rank1_multi_step(const lpmm_b200_step_tensor* const* ts, int n, const float* qmap_m,
                                           const float* qmap_v, double beta1, double beta2, double lr,
                                           double weight_decay, double eps, double step, void* table,
-                                          int64_t table_bytes, void* stream) {
+                                          int64_t table_bytes, void* stream, int arith) {
   if (n <= 0) return LPMM_B200_OK;
   if (!ts || !qmap_m || !qmap_v || !table) return LPMM_B200_ERR_NULL_POINTER;
   if (table_bytes < lpmm_b200_rank1_multi_table_bytes(n)) return LPMM_B200_ERR_BAD_SIZE;
@@ -391,19 +423,22 @@ extern "C" int lpmm_b200_rank1_multi_step(const lpmm_b200_step_tensor* const* ts
   r1_zero_kernel<<<(unsigned)n, R1T, 0, st>>>(dev);
   LPMM_CUDA_TRY(cudaGetLastError());
   long long sgrid = tiles < target_tiles ? tiles : target_tiles;
-  r1_stats_kernel<<<(unsigned)sgrid, R1T, 0, st>>>(dev, n, tiles, qmap_v, c);
+  if (arith) r1_stats_kernel<true><<<(unsigned)sgrid, R1T, 0, st>>>(dev, n, tiles, qmap_v, c);
+  else r1_stats_kernel<false><<<(unsigned)sgrid, R1T, 0, st>>>(dev, n, tiles, qmap_v, c);
   LPMM_CUDA_TRY(cudaGetLastError());
   static bool attr_set[64] = {};
   int devi = 0;
   cudaGetDevice(&devi);
   if (devi >= 0 && devi < 64 && !attr_set[devi]) {
-    LPMM_CUDA_TRY(cudaFuncSetAttribute(r1_update_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)R1_DYN_SMEM));
+    LPMM_CUDA_TRY(cudaFuncSetAttribute(r1_update_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)R1_DYN_SMEM));
+    LPMM_CUDA_TRY(cudaFuncSetAttribute(r1_update_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)R1_DYN_SMEM));
     attr_set[devi] = true;
   }
   long long ugrid = (units + R1T / 16 - 1) / (R1T / 16);
   const long long ucap = (long long)num_sms() * 4;
   if (ugrid > ucap) ugrid = ucap;
-  r1_update_kernel<<<(unsigned)ugrid, R1T, R1_DYN_SMEM, st>>>(dev, n, units, qmap_m, qmap_v, c);
+  if (arith) r1_update_kernel<true><<<(unsigned)ugrid, R1T, R1_DYN_SMEM, st>>>(dev, n, units, qmap_m, qmap_v, c);
+  else r1_update_kernel<false><<<(unsigned)ugrid, R1T, R1_DYN_SMEM, st>>>(dev, n, units, qmap_m, qmap_v, c);
   LPMM_CUDA_TRY(cudaGetLastError());
   return LPMM_B200_OK;
 }

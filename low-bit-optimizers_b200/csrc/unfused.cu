@@ -281,10 +281,14 @@ __device__ __forceinline__ void lane_scales(const float* const* vecs, long long 
 // ---------------------------------------------------------------------------------------------
 // Register budget: 64 per thread (4 CTAs of 256 threads per SM) except for the rank-1 variants, whose
 // index arithmetic needs more.
-template <int MM, int VM, int ND, bool W>
-__global__ void __launch_bounds__(UTMAX, (VM == LPMM_B200_STATE_RANK1_4 && ND != 2) ? 1 : 2) unfused_adamw_kernel(const StepArgs a, const UConsts c,
+// A: the arithmetic of the reference's fused kernel instead of that of its torch operations (scalar path only).
+template <int MM, int VM, int ND, bool W, bool A = false>
+__global__ void __launch_bounds__(UTMAX, (VM == LPMM_B200_STATE_RANK1_4 && ND != 2) ? 1 : 2) unfused_adamw_kernel(const StepArgs a, const UConsts cin,
                                                                const float* __restrict__ qmap_m,
                                                                const float* __restrict__ qmap_v) {
+  UConsts cf;
+  if (A) cf = fused_consts(cin);
+  const UConsts& c = A ? cf : cin;
   __shared__ Maps M;
   __shared__ float red[UTMAX / 16];
   constexpr bool MQ = (MM == LPMM_B200_STATE_GROUP4);
@@ -351,7 +355,7 @@ __global__ void __launch_bounds__(UTMAX, (VM == LPMM_B200_STATE_RANK1_4 && ND !=
     // the update of the lane's 8 elements; FULL: all 8 exist, no per-element guards
     auto update_lane = [&](auto full_tag) {
       constexpr bool FULL = decltype(full_tag)::value;
-      if (FULL && VM != LPMM_B200_STATE_FACTORED && c.fast) {  // two elements per instruction
+      if (!A && FULL && VM != LPMM_B200_STATE_FACTORED && c.fast) {  // two elements per instruction
         float* mf = reinterpret_cast<float*>(a.m);
         float* vf = reinterpret_cast<float*>(a.v);
         const f2 sm2 = f2_splat(sm), sv2 = f2_splat(sv);
@@ -399,14 +403,14 @@ __global__ void __launch_bounds__(UTMAX, (VM == LPMM_B200_STATE_RANK1_4 && ND !=
             else if (VM == LPMM_B200_STATE_RANK1_4) v0 = __fmul_rn(M.qv[vcodes.get(k)], st_old[k]);
             else if (VM == LPMM_B200_STATE_FP32) v0 = reinterpret_cast<const float*>(a.v)[e];
           }
-          m[k] = lerp_m(c, m0, g);
+          m[k] = lerp_m<A>(c, m0, g);
           if (VM == LPMM_B200_STATE_FACTORED) {
             const float rf = __fdiv_rn(a.row[rowi], a.row_mean[bi]);
             v[k] = __fmul_rn(rf, a.col[bi * C + cc]);
           } else {
-            v[k] = upd_v2(c, v0, g);
+            v[k] = upd_v2<A>(c, v0, g);
           }
-          px[k] = upd_param(c, px[k], m[k], v[k]);
+          px[k] = upd_param<A>(c, px[k], m[k], v[k]);
           am = fmaxf(am, fabsf(m[k]));
           av = fmaxf(av, v[k]);
           if (MM == LPMM_B200_STATE_FP32) reinterpret_cast<float*>(a.m)[e] = m[k];
@@ -504,9 +508,12 @@ __global__ void __launch_bounds__(UTMAX, (VM == LPMM_B200_STATE_RANK1_4 && ND !=
 // flushed once per CTA; the outer axes change rarely along a lane's 8 consecutive elements, so a
 // lane combines runs of equal coordinates in registers before touching global memory.
 constexpr int STAT_LAST = 8192;
-template <int ND, bool W>
-__global__ void __launch_bounds__(UT) rank1_stats_kernel(const StepArgs a, const UConsts c,
+template <int ND, bool W, bool A = false>
+__global__ void __launch_bounds__(UT) rank1_stats_kernel(const StepArgs a, const UConsts cin,
                                                           const float* __restrict__ qmap_v) {
+  UConsts cf;
+  if (A) cf = fused_consts(cin);
+  const UConsts& c = A ? cf : cin;
   __shared__ Maps M;
   __shared__ int lastmax[STAT_LAST];
   load_maps<W>(M, nullptr, qmap_v, 4, a.bits_v);
@@ -546,7 +553,7 @@ __global__ void __launch_bounds__(UT) rank1_stats_kernel(const StepArgs a, const
       if (e0 + k < n) {
         float v0 = 0.0f;
         if (!a.first) v0 = __fmul_rn(M.qv[vcodes.get(k)], st_old[k]);
-        const float v = upd_v2(c, v0, gx[k]);
+        const float v = upd_v2<A>(c, v0, gx[k]);
 #pragma unroll
         for (int i = 0; i < ND; ++i) {
           if (ND < 8 || i < nd) {
@@ -586,9 +593,12 @@ __global__ void __launch_bounds__(UT) rank1_stats_kernel(const StepArgs a, const
 // CTAs per column, little work each) and for none when they are thick.
 constexpr int STATS_CLUSTER = 8;
 constexpr int STATS_CLUSTER_MAX_ROWS = 8;  // rows per CTA up to which clusters pay (4096 x 4096 has 12: measured slower)
-template <bool W>
+template <bool W, bool A = false>
 __global__ void __launch_bounds__(UT)
-rank1_stats2d_kernel(const StepArgs a, const UConsts c, const float* __restrict__ qmap_v, int rows_per_cta) {
+rank1_stats2d_kernel(const StepArgs a, const UConsts cin, const float* __restrict__ qmap_v, int rows_per_cta) {
+  UConsts cf;
+  if (A) cf = fused_consts(cin);
+  const UConsts& c = A ? cf : cin;
   __shared__ Maps M;
   __shared__ float colbuf[8 * UT];  // this CTA's column maxima, [k][thread]
   load_maps<W>(M, nullptr, qmap_v, 4, a.bits_v);
@@ -619,7 +629,7 @@ rank1_stats2d_kernel(const StepArgs a, const UConsts c, const float* __restrict_
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
         const float v0 = a.first ? 0.0f : __fmul_rn(M.qv[vcodes.get(k)], fminf(row_old, col_old[k]));
-        const float v = upd_v2(c, v0, gx[k]);
+        const float v = upd_v2<A>(c, v0, gx[k]);
         col_max[k] = fmaxf(col_max[k], v);
         row_max = fmaxf(row_max, v);
       }
@@ -1307,10 +1317,23 @@ static cudaError_t launch_unfused(int vm, unsigned grid, int threads, cudaStream
   return cudaGetLastError();
 }
 
-extern "C" int lpmm_b200_adamw4bit_unfused_step(const lpmm_b200_step_tensor* t, const float* qmap_m,
-                                                const float* qmap_v, double beta1, double beta2, double lr,
-                                                double weight_decay, double eps, double step, void* scratch,
-                                                int64_t scratch_bytes, void* stream) {
+// The same kernels with the fused kernel's arithmetic: 4-bit codes only; both moments fp32, both in
+// groups, or a grouped first moment with a rank-1 second moment.
+static cudaError_t launch_fused_arith(bool mq, int vm, unsigned grid, int threads, cudaStream_t st, const StepArgs& a,
+                                      const UConsts& c, const float* qm, const float* qv) {
+  constexpr int F = LPMM_B200_STATE_FP32, G = LPMM_B200_STATE_GROUP4, R = LPMM_B200_STATE_RANK1_4;
+  if (!mq && vm == F) unfused_adamw_kernel<F, F, 2, false, true><<<grid, threads, 0, st>>>(a, c, qm, qv);
+  else if (mq && vm == G) unfused_adamw_kernel<G, G, 2, false, true><<<grid, threads, 0, st>>>(a, c, qm, qv);
+  else if (mq && vm == R)
+    LPMM_DISPATCH_ND(a.s.nd, (unfused_adamw_kernel<G, R, ND, false, true><<<grid, threads, 0, st>>>(a, c, qm, qv)));
+  else return cudaErrorInvalidValue;
+  return cudaGetLastError();
+}
+
+// arith 0: the arithmetic of the reference's torch operations; 1: that of its fused kernel.
+static int step_one_tensor(const lpmm_b200_step_tensor* t, const float* qmap_m, const float* qmap_v, double beta1,
+                           double beta2, double lr, double weight_decay, double eps, double step, void* scratch,
+                           int64_t scratch_bytes, void* stream, int arith) {
   if (!t) return LPMM_B200_ERR_NULL_POINTER;
   if (t->numel < 0) return LPMM_B200_ERR_BAD_SIZE;
   if (t->m_mode != LPMM_B200_STATE_FP32 && t->m_mode != LPMM_B200_STATE_GROUP4) return LPMM_B200_ERR_BAD_KIND;
@@ -1328,6 +1351,10 @@ extern "C" int lpmm_b200_adamw4bit_unfused_step(const lpmm_b200_step_tensor* t, 
   }
   if (mq && vq && lm.wide != lv.wide) return LPMM_B200_ERR_UNSUPPORTED;  // one storage format per launch
   const bool wide = mq ? lm.wide : (vq && lv.wide);
+  if (arith) {
+    const bool pair_ok = (!mq && t->v_mode == LPMM_B200_STATE_FP32) || (mq && vq);
+    if (wide || !pair_ok) return LPMM_B200_ERR_UNSUPPORTED;
+  }
   if (t->numel == 0) return LPMM_B200_OK;
   if (!t->p || !t->g) return LPMM_B200_ERR_NULL_POINTER;
   if (!t->m) return LPMM_B200_ERR_NULL_POINTER;
@@ -1402,11 +1429,16 @@ extern "C" int lpmm_b200_adamw4bit_unfused_step(const lpmm_b200_step_tensor* t, 
         attr.val.clusterDim.z = 1;
         cfg.attrs = &attr;
         cfg.numAttrs = 1;
-        LPMM_DISPATCH_W(lv.wide, LPMM_CUDA_TRY(cudaLaunchKernelEx(&cfg, rank1_stats2d_kernel<W>, a, c, qmap_v, rows_per_cta)));
+        if (arith) LPMM_CUDA_TRY(cudaLaunchKernelEx(&cfg, rank1_stats2d_kernel<false, true>, a, c, qmap_v, rows_per_cta));
+        else LPMM_DISPATCH_W(lv.wide, LPMM_CUDA_TRY(cudaLaunchKernelEx(&cfg, rank1_stats2d_kernel<W>, a, c, qmap_v, rows_per_cta)));
+      } else if (arith) {
+        rank1_stats2d_kernel<false, true><<<dim3((unsigned)col_ctas, (unsigned)row_ctas), UT, 0, st>>>(a, c, qmap_v, rows_per_cta);
       } else {
         LPMM_DISPATCH_W(lv.wide, (rank1_stats2d_kernel<W><<<dim3((unsigned)col_ctas, (unsigned)row_ctas), UT, 0, st>>>(
                                      a, c, qmap_v, rows_per_cta)));
       }
+    } else if (arith) {
+      LPMM_DISPATCH_ND(t->ndim, (rank1_stats_kernel<ND, false, true><<<grid_for((a.n + 7) / 8, UT, 3), UT, 0, st>>>(a, c, qmap_v)));
     } else {
       LPMM_DISPATCH_W(lv.wide, LPMM_DISPATCH_ND(t->ndim, (rank1_stats_kernel<ND, W><<<grid_for((a.n + 7) / 8, UT, 3), UT,
                                                                                     0, st>>>(a, c, qmap_v))));
@@ -1437,11 +1469,33 @@ extern "C" int lpmm_b200_adamw4bit_unfused_step(const lpmm_b200_step_tensor* t, 
   const int threads = threads_for(hpg_max);
   const unsigned grid = grid_for(a.units, threads / 16, threads == UT ? 8 : 4);
   cudaError_t e = cudaSuccess;
-  LPMM_DISPATCH_W(wide, (e = mq ? launch_unfused<LPMM_B200_STATE_GROUP4, W>(t->v_mode, grid, threads, st, a, c, qmap_m, qmap_v)
-                                : launch_unfused<LPMM_B200_STATE_FP32, W>(t->v_mode, grid, threads, st, a, c, qmap_m, qmap_v)));
+  if (arith) {
+    e = launch_fused_arith(mq, t->v_mode, grid, threads, st, a, c, qmap_m, qmap_v);
+  } else {
+    LPMM_DISPATCH_W(wide, (e = mq ? launch_unfused<LPMM_B200_STATE_GROUP4, W>(t->v_mode, grid, threads, st, a, c, qmap_m, qmap_v)
+                                  : launch_unfused<LPMM_B200_STATE_FP32, W>(t->v_mode, grid, threads, st, a, c, qmap_m, qmap_v)));
+  }
   LPMM_CUDA_TRY(e);
   return LPMM_B200_OK;
 }
+
+extern "C" int lpmm_b200_adamw4bit_unfused_step(const lpmm_b200_step_tensor* t, const float* qmap_m,
+                                                const float* qmap_v, double beta1, double beta2, double lr,
+                                                double weight_decay, double eps, double step, void* scratch,
+                                                int64_t scratch_bytes, void* stream) {
+  return step_one_tensor(t, qmap_m, qmap_v, beta1, beta2, lr, weight_decay, eps, step, scratch, scratch_bytes, stream, 0);
+}
+
+extern "C" int lpmm_b200_adamw4bit_fused_arith_step(const lpmm_b200_step_tensor* t, const float* qmap_m,
+                                                    const float* qmap_v, double beta1, double beta2, double lr,
+                                                    double weight_decay, double eps, double step, void* stream) {
+  return step_one_tensor(t, qmap_m, qmap_v, beta1, beta2, lr, weight_decay, eps, step, nullptr, 0, stream, 1);
+}
+
+// adamw_unfused_multi.cu: the shared launch with the fused kernel's arithmetic (internal to the library)
+extern "C" int lpmm_b200_fused_arith_multi_tensor(const lpmm_b200_tensor* ts, int n, const float* qmap_m,
+                                                  const float* qmap_v, double beta1, double beta2, double lr,
+                                                  double weight_decay, double eps, double step, void* stream);
 
 // rank1_multi.cu: all rank-1 matrices of a list in three launches (internal to the library)
 extern "C" int64_t lpmm_b200_rank1_multi_table_bytes(int n);
@@ -1449,7 +1503,7 @@ extern "C" int lpmm_b200_rank1_multi_ok(const lpmm_b200_step_tensor* t);
 extern "C" int lpmm_b200_rank1_multi_step(const lpmm_b200_step_tensor* const* ts, int n, const float* qmap_m,
                                           const float* qmap_v, double beta1, double beta2, double lr,
                                           double weight_decay, double eps, double step, void* table,
-                                          int64_t table_bytes, void* stream);
+                                          int64_t table_bytes, void* stream, int arith);
 
 // factored_multi.cu: all factored matrices of a list in four launches (internal to the library)
 extern "C" int lpmm_b200_factored_multi_ok(const lpmm_b200_step_tensor* t);
@@ -1511,11 +1565,9 @@ extern "C" int64_t lpmm_b200_unfused_step_many_scratch_bytes(const lpmm_b200_ste
   return total + 1024;
 }
 
-extern "C" int lpmm_b200_adamw4bit_unfused_step_many(const lpmm_b200_step_tensor* const* tensors, int n,
-                                                     const float* qmap_m, const float* qmap_v, double beta1,
-                                                     double beta2, double lr, double weight_decay, double eps,
-                                                     const double* steps, void* scratch, int64_t scratch_bytes,
-                                                     void* stream) {
+static int step_many(const lpmm_b200_step_tensor* const* tensors, int n, const float* qmap_m, const float* qmap_v,
+                     double beta1, double beta2, double lr, double weight_decay, double eps, const double* steps,
+                     void* scratch, int64_t scratch_bytes, void* stream, int arith) {
   if (n < 0) return LPMM_B200_ERR_BAD_SIZE;
   if (n > 0 && (!tensors || !steps)) return LPMM_B200_ERR_NULL_POINTER;
   cudaStream_t user = (cudaStream_t)stream;
@@ -1569,7 +1621,7 @@ extern "C" int lpmm_b200_adamw4bit_unfused_step_many(const lpmm_b200_step_tensor
   fm.clear();
   double fm_step = 0.0;
   for (int i = 0; i < n; ++i) {
-    if (!capturing && lpmm_b200_factored_multi_ok(tensors[i]) && (fm.empty() || steps[i] == fm_step) &&
+    if (!arith && !capturing && lpmm_b200_factored_multi_ok(tensors[i]) && (fm.empty() || steps[i] == fm_step) &&
         (tensors[i]->m_mode == LPMM_B200_STATE_FP32 || qmap_m)) {
       fm_step = steps[i];
       fm.push_back(tensors[i]);
@@ -1650,18 +1702,19 @@ extern "C" int lpmm_b200_adamw4bit_unfused_step_many(const lpmm_b200_step_tensor
       }
       st = side->s[k];
     }
-    rc = lpmm_b200_adamw4bit_unfused_step(t, qmap_m, qmap_v, beta1, beta2, lr, weight_decay, eps, steps[i], sc, sc_bytes,
-                                          st);
+    rc = step_one_tensor(t, qmap_m, qmap_v, beta1, beta2, lr, weight_decay, eps, steps[i], sc, sc_bytes, st, arith);
   }
   if (rc == LPMM_B200_OK && !r1.empty())
     rc = lpmm_b200_rank1_multi_step(r1.data(), (int)r1.size(), qmap_m, qmap_v, beta1, beta2, lr, weight_decay, eps,
-                                    r1_step, r1_table, r1_bytes, user);
+                                    r1_step, r1_table, r1_bytes, user, arith);
   if (rc == LPMM_B200_OK && !fm.empty())
     rc = lpmm_b200_factored_multi_step(fm.data(), (int)fm.size(), qmap_m, beta1, beta2, lr, weight_decay, eps, fm_step,
                                        fm_scratch, fm_bytes, user);
   if (rc == LPMM_B200_OK && !batch.empty())
-    rc = lpmm_b200_adamw4bit_unfused_multi_tensor(batch.data(), (int)batch.size(), qmap_m, qmap_v, beta1, beta2, lr,
-                                                  weight_decay, eps, batch_step, 0, -1, user);
+    rc = arith ? lpmm_b200_fused_arith_multi_tensor(batch.data(), (int)batch.size(), qmap_m, qmap_v, beta1, beta2, lr,
+                                                    weight_decay, eps, batch_step, user)
+               : lpmm_b200_adamw4bit_unfused_multi_tensor(batch.data(), (int)batch.size(), qmap_m, qmap_v, beta1, beta2,
+                                                          lr, weight_decay, eps, batch_step, 0, -1, user);
   if (side) {  // join even after an error: the caller's stream must not run ahead of what was enqueued
     for (int k = 0; k < SIDE_STREAMS; ++k) {
       if (cudaEventRecord(side->join[k], side->s[k]) != cudaSuccess ||
@@ -1671,6 +1724,24 @@ extern "C" int lpmm_b200_adamw4bit_unfused_step_many(const lpmm_b200_step_tensor
     }
   }
   return rc;
+}
+
+extern "C" int lpmm_b200_adamw4bit_unfused_step_many(const lpmm_b200_step_tensor* const* tensors, int n,
+                                                     const float* qmap_m, const float* qmap_v, double beta1,
+                                                     double beta2, double lr, double weight_decay, double eps,
+                                                     const double* steps, void* scratch, int64_t scratch_bytes,
+                                                     void* stream) {
+  return step_many(tensors, n, qmap_m, qmap_v, beta1, beta2, lr, weight_decay, eps, steps, scratch, scratch_bytes,
+                   stream, 0);
+}
+
+extern "C" int lpmm_b200_adamw4bit_fused_arith_step_many(const lpmm_b200_step_tensor* const* tensors, int n,
+                                                         const float* qmap_m, const float* qmap_v, double beta1,
+                                                         double beta2, double lr, double weight_decay, double eps,
+                                                         const double* steps, void* scratch, int64_t scratch_bytes,
+                                                         void* stream) {
+  return step_many(tensors, n, qmap_m, qmap_v, beta1, beta2, lr, weight_decay, eps, steps, scratch, scratch_bytes,
+                   stream, 1);
 }
 
 extern "C" int lpmm_b200_sgd_lowbit_step(float* p, const float* g, int64_t numel, void* buf, float* buf_max1,

@@ -6,6 +6,13 @@
 //   d  = sqrt(v) * float(1.0 / sqrt(1 - beta2^step)) + float(eps)    division by a host scalar
 //   p  = fma(float(-lr / (1 - beta1^step)), m / d, p1)              addcdiv_
 // with the scalar constants computed in double on the host exactly as Python computes them.
+//
+// The scalar functions also come in a second flavour (template argument A = true): the arithmetic of
+// the reference's fused kernel (lpmm/cpp_extension/fused_adamw_kernel.cu:103-128), all in float,
+//   m = fma(b1, m0, (1-b1)*g) ; v = fma(b2, v0, ((1-b2)*g)*g)
+//   d = (sqrt(v)/sqrt(1-b2^t) + eps) * (1-b1^t) ; p = fma(-lr, fma(wd, p, m/d), p)
+// with the bias corrections from the device's powf.  It lets the kernels built on this header run the
+// fused step on the states the fused kernel cannot hold (rank-1 second-moment scales).
 #pragma once
 #include <math.h>
 
@@ -17,17 +24,40 @@ struct UConsts {
   float wd_mul, lerp_w, lerp_omw, beta2, omb2, inv_bc2s, bc2s, eps, alpha;
   int lerp_small;
   int fast;  // eps keeps the denominator inside the domain of the short exact sqrt / division sequences
+  // fused-kernel arithmetic (A = true): the hyper-parameters as floats; c1, c2s, rc2s are filled in on
+  // the device by fused_consts()
+  float f_beta1, f_omb1, f_beta2, f_omb2, f_lr, f_wd, f_eps, f_step, c1, c2s, rc2s;
+  int f_fast;
 };
 
+// 1 - beta1^t, sqrt(1 - beta2^t) and the latter's reciprocal, as the fused kernel computes them.
+__device__ __forceinline__ UConsts fused_consts(UConsts c) {
+  c.c1 = __fsub_rn(1.0f, powf(c.f_beta1, c.f_step));
+  c.c2s = __fsqrt_rn(__fsub_rn(1.0f, powf(c.f_beta2, c.f_step)));
+  c.rc2s = __frcp_rn(c.c2s);
+  return c;
+}
 
+
+template <bool A = false>
 __device__ __forceinline__ float lerp_m(const UConsts& c, float m0, float g) {
+  if (A) return __fmaf_rn(c.f_beta1, m0, __fmul_rn(c.f_omb1, g));
   const float diff = __fsub_rn(g, m0);
   return c.lerp_small ? __fmaf_rn(c.lerp_w, diff, m0) : __fmaf_rn(-diff, c.lerp_omw, g);
 }
+template <bool A = false>
 __device__ __forceinline__ float upd_v2(const UConsts& c, float v0, float g) {
+  if (A) return __fmaf_rn(c.f_beta2, v0, __fmul_rn(__fmul_rn(c.f_omb2, g), g));
   return __fmaf_rn(c.omb2, __fmul_rn(g, g), __fmul_rn(v0, c.beta2));
 }
+template <bool A = false>
 __device__ __forceinline__ float upd_param(const UConsts& c, float p, float m, float v) {
+  if (A) {
+    float d = c.f_fast ? udiv(sqrt_rn_fast(v), c.c2s, c.rc2s) : __fdiv_rn(__fsqrt_rn(v), c.c2s);
+    d = __fmul_rn(__fadd_rn(d, c.f_eps), c.c1);
+    const float q = c.f_fast ? div_rn_fast(m, d) : __fdiv_rn(m, d);
+    return __fmaf_rn(-c.f_lr, __fmaf_rn(c.f_wd, p, q), p);
+  }
   const float p1 = __fmul_rn(p, c.wd_mul);
   if (c.fast) {
     const float d = __fadd_rn(__fmul_rn(sqrt_rn_fast(v), c.inv_bc2s), c.eps);
@@ -115,6 +145,20 @@ static inline UConsts make_consts(double beta1, double beta2, double lr, double 
   c.eps = (float)eps;
   c.alpha = (float)(-step_size);
   c.fast = (eps >= 0x1p-40 && eps <= 0x1p30 && bc2 >= 0x1p-40);
+  // fused-kernel flavour: everything a float, as the reference's binding passes it
+  c.f_beta1 = (float)beta1;
+  c.f_beta2 = (float)beta2;
+  c.f_omb1 = 1.0f - c.f_beta1;
+  c.f_omb2 = 1.0f - c.f_beta2;
+  c.f_lr = (float)lr;
+  c.f_wd = (float)wd;
+  c.f_eps = (float)eps;
+  c.f_step = (float)step;
+  c.c1 = c.c2s = c.rc2s = 0.0f;
+  // the short sequences need the denominator, at least eps * (1 - beta1), inside [2^-60, 2^60]
+  c.f_fast = (c.f_beta1 >= 0.0f && c.f_beta1 < 1.0f && c.f_beta2 >= 0.0f && c.f_beta2 < 1.0f && c.f_step >= 1.0f &&
+              (double)c.f_eps * (1.0 - (double)c.f_beta1) >= 0x1p-50 && c.f_eps <= 0x1p30f &&
+              sqrt(1.0 - (double)c.f_beta2) >= 0x1p-20);
   return c;
 }
 

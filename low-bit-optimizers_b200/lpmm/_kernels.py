@@ -405,26 +405,34 @@ def _make_plan(t, p, g, state, axis_sets=None, oh_v=None):
     return plan
 
 
+def _step_one(desc, qm, qv, beta1, beta2, lr, weight_decay, eps, step, stream, fused_arith):
+    if fused_arith:
+        N.check(N.lib.lpmm_b200_adamw4bit_fused_arith_step(ctypes.byref(desc), _ptr(qm), _ptr(qv), beta1, beta2, lr,
+                                                           weight_decay, eps, step, stream))
+    else:
+        N.check(N.lib.lpmm_b200_adamw4bit_unfused_step(ctypes.byref(desc), _ptr(qm), _ptr(qv), beta1, beta2, lr,
+                                                       weight_decay, eps, step, None, 0, stream))
+
+
 def adamw4bit_unfused_step(p, g, state, m_quant, v_quant, md_m, md_v, spare, *, beta1, beta2, lr, weight_decay, eps,
-                           step, stream=None):
+                           step, stream=None, fused_arith=False):
     """``spare`` is a dict owned by the optimizer (not part of its state) that keeps the second set
     of per-axis maxima a rank-1 tensor alternates with, and the descriptor cached between steps.
     ``stream``: raw handle of torch's current stream when the caller has already looked it up and
-    ``p``'s device is the current device (saves both look-ups per tensor)."""
+    ``p``'s device is the current device (saves both look-ups per tensor).
+    ``fused_arith``: the arithmetic of the reference's fused kernel on these states
+    (``lpmm_b200_adamw4bit_fused_arith_step``) instead of that of its torch operations."""
     plan = spare.get("plan")
     if plan is not None:
         if plan.matches(p, state) and plan.set_grad(g):
             qm = state["exp_avg_qstate"]["qmap"]
             qv = state["exp_avg_sq_qstate"]["qmap"]
             if stream is not None:
-                N.check(N.lib.lpmm_b200_adamw4bit_unfused_step(ctypes.byref(plan.descs[plan.which]), _ptr(qm), _ptr(qv),
-                                                               beta1, beta2, lr, weight_decay, eps, step, None, 0,
-                                                               _vp(stream)))
+                _step_one(plan.descs[plan.which], qm, qv, beta1, beta2, lr, weight_decay, eps, step, _vp(stream), fused_arith)
             else:
                 with torch.cuda.device(p.device):
-                    N.check(N.lib.lpmm_b200_adamw4bit_unfused_step(ctypes.byref(plan.descs[plan.which]), _ptr(qm),
-                                                                   _ptr(qv), beta1, beta2, lr, weight_decay, eps, step,
-                                                                   None, 0, _stream()))
+                    _step_one(plan.descs[plan.which], qm, qv, beta1, beta2, lr, weight_decay, eps, step, _stream(),
+                              fused_arith)
             if plan.axis_sets is not None:  # the freshly written maxima become the state's, the old set the spare
                 plan.which ^= 1
                 plan.oh_v["max_dims"], spare["max_dims"] = plan.axis_sets[plan.which], plan.axis_sets[plan.which ^ 1]
@@ -484,8 +492,7 @@ def adamw4bit_unfused_step(p, g, state, m_quant, v_quant, md_m, md_v, spare, *, 
     qm = state["exp_avg_qstate"]["qmap"]
     qv = state["exp_avg_sq_qstate"]["qmap"]
     with torch.cuda.device(p.device):
-        N.check(N.lib.lpmm_b200_adamw4bit_unfused_step(ctypes.byref(t), _ptr(qm), _ptr(qv), beta1, beta2, lr,
-                                                       weight_decay, eps, step, None, 0, _stream()))
+        _step_one(t, qm, qv, beta1, beta2, lr, weight_decay, eps, step, _stream(), fused_arith)
     spare["plan"] = _make_plan(t, p, g, state, axis_sets, oh_v if rank1 else None)
 
 
@@ -496,15 +503,16 @@ def unfused_step_many_scratch_bytes(ptrs, n):
     return need
 
 
-def adamw4bit_unfused_step_many(ptrs, n, qm, qv, steps, scratch_need, device, *, beta1, beta2, lr, weight_decay, eps):
+def adamw4bit_unfused_step_many(ptrs, n, qm, qv, steps, scratch_need, device, *, beta1, beta2, lr, weight_decay, eps,
+                                fused_arith=False):
     """``ptrs``: ctypes array of n addresses of ``lpmm_b200_step_tensor`` descriptors (kept alive and up
     to date by the caller), ``steps``: ctypes array of n doubles, ``scratch_need``: what
     ``unfused_step_many_scratch_bytes`` returned for them.  The caller guarantees that ``device`` is the
     current device."""
     scratch = _scratch_for(device, scratch_need)
-    N.check(N.lib.lpmm_b200_adamw4bit_unfused_step_many(ptrs, n, _ptr(qm), _ptr(qv), beta1, beta2, lr, weight_decay, eps,
-                                                        steps, _ptr(scratch), scratch.numel() if scratch is not None else 0,
-                                                        _stream()))
+    fn = N.lib.lpmm_b200_adamw4bit_fused_arith_step_many if fused_arith else N.lib.lpmm_b200_adamw4bit_unfused_step_many
+    N.check(fn(ptrs, n, _ptr(qm), _ptr(qv), beta1, beta2, lr, weight_decay, eps, steps, _ptr(scratch),
+               scratch.numel() if scratch is not None else 0, _stream()))
 
 
 def adamw_fp32_moments_step(p, g, m, v, row, col, *, beta1, beta2, lr, weight_decay, eps, step):

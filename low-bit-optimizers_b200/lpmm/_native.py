@@ -117,6 +117,9 @@ def _load():
         "lpmm_b200_unfused_step_many_scratch_bytes": (i64, [ctypes.POINTER(vp), i32]),
         "lpmm_b200_adamw4bit_unfused_step_many": (i32, [ctypes.POINTER(vp), i32, vp, vp] + [d] * 5
                                                   + [ctypes.POINTER(d), vp, i64, vp]),
+        "lpmm_b200_adamw4bit_fused_arith_step": (i32, [ctypes.POINTER(StepTensor), vp, vp] + [d] * 6 + [vp]),
+        "lpmm_b200_adamw4bit_fused_arith_step_many": (i32, [ctypes.POINTER(vp), i32, vp, vp] + [d] * 5
+                                                      + [ctypes.POINTER(d), vp, i64, vp]),
         "lpmm_b200_factored_scratch_bytes": (i64, [ctypes.POINTER(i64), i32]),
         "lpmm_b200_adamw4bit_factored_step_noalloc": (i32, [ctypes.POINTER(StepTensor), vp] + [d] * 6 + [vp]),
         "lpmm_b200_sgd4bit_step": (i32, [vp, vp, i64, vp, vp, i32, i32, vp, d, d, d, d, i32, i32, vp]),

@@ -10,6 +10,10 @@ Constructor, lazily created state, state names and layouts are those of the refe
   generated metadata (``max1`` or ``max_dims``, ``dim``, ``scaled_shape``, ``dtype``, ``stride``)
   in ``overhead`` (adamw.py:425-434); each tensor is updated by one fused launch that reproduces
   the reference's sequence of torch operations (adamw.py:369-422).
+* ``fused=True, fused_rank1=True`` (an extension; the reference's fused step cannot hold rank-1 scales and
+  falls back to group scales with a warning, adamw.py:503-506) -- with a rank-1 second-moment
+  configuration the states have the ``fused=False`` layout (per-axis maxima in ``max_dims``) and are
+  stepped with the fused kernel's arithmetic (``lpmm_b200_adamw4bit_fused_arith_step_many``).
 * tensors with at most ``THRESHOLD`` (4096) elements, or overridden, keep fp32 moments.
 * ``factor_second_moment=True`` keeps fp32 row/column accumulators for every >=2-D tensor
   (adamw.py:124-126, 579-627).
@@ -26,7 +30,7 @@ __all__ = ["AdamW"]
 
 class AdamW(LowBitOptimizer):
     def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=1e-2, use_first_moment=True,
-                 factor_second_moment=False, qconfig=None, *, fused: Optional[bool] = False):
+                 factor_second_moment=False, qconfig=None, *, fused: Optional[bool] = False, fused_rank1: bool = False):
         if not 0.0 <= lr:
             raise ValueError("Invalid learning rate: {}".format(lr))
         if not 0.0 <= eps:
@@ -40,6 +44,7 @@ class AdamW(LowBitOptimizer):
         defaults = dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, fused=fused,
                         use_first_moment=use_first_moment, factor_second_moment=factor_second_moment)
         super().__init__(params, defaults, qconfig)
+        self._fused_rank1 = bool(fused_rank1)
         self._lists = {}  # cached descriptor arrays of the multi-tensor step, per param group
         self._spare = {}  # per-parameter buffers that are not optimizer state (alternate rank-1 maxima)
         self._plans = {}  # fused groups: everything needed to repeat the last launch
@@ -47,6 +52,7 @@ class AdamW(LowBitOptimizer):
 
     def __setstate__(self, state):
         super().__setstate__(state)
+        self.__dict__.setdefault("_fused_rank1", False)
         self._lists = {}
         self._spare = {}
         self._plans = {}
@@ -102,11 +108,29 @@ class AdamW(LowBitOptimizer):
                 params.append(p)
             if not params:
                 continue
-            if group["fused"]:
+            if group["fused"] and self._fused_rank1_applies(group):
+                self._step_single(gi, group, params, fused_arith=True)
+            elif group["fused"]:
                 self._step_fused(gi, group, params)
             else:
                 self._step_single(gi, group, params)
         return loss
+
+    def _fused_rank1_applies(self, group):
+        """fused_rank1=True and a configuration the fused kernel cannot hold as such: a rank-1 second moment
+        (4-bit codes, nearest rounding, no factored second moment)."""
+        if not self._fused_rank1 or group["factor_second_moment"]:
+            return False
+        md_m = self.get_qmetadata_by_state_name("exp_avg")
+        md_v = self.get_qmetadata_by_state_name("exp_avg_sq")
+        if md_v["scale_type"] != "rank1" or md_m["scale_type"] != "group":
+            return False
+        if md_m["b"] != 4 or md_v["b"] != 4:
+            raise NotImplementedError("the fused step stores 4-bit codes; use fused=False for "
+                                      f"{md_m['b']}/{md_v['b']}-bit states")
+        if md_m["round_type"] == "real-sr" or md_v["round_type"] == "real-sr":
+            raise NotImplementedError("the fused step rounds to nearest; use fused=False for stochastic rounding")
+        return True
 
     # ---- fused=True ---------------------------------------------------------------------------
     def _step_fused(self, gi, group, params):
@@ -227,14 +251,14 @@ class AdamW(LowBitOptimizer):
         return cached[1]
 
     # ---- fused=False --------------------------------------------------------------------------
-    def _step_single(self, gi, group, params):
+    def _step_single(self, gi, group, params, fused_arith=False):
         md_m = self.get_qmetadata_by_state_name("exp_avg")
         md_v = self.get_qmetadata_by_state_name("exp_avg_sq")
         if md_m["round_type"] == "real-sr" or md_v["round_type"] == "real-sr":
             return self._step_single_stochastic(group, params, md_m, md_v)
-        if self._step_single_batched(gi, group, params):
+        if self._step_single_batched(gi, group, params, fused_arith):
             return
-        self._step_single_each(group, params)
+        self._step_single_each(group, params, fused_arith)
         self._prepare_batch(gi, params)
 
     def _step_single_stochastic(self, group, params, md_m, md_v):
@@ -310,7 +334,7 @@ class AdamW(LowBitOptimizer):
                                  rank1_index=[i for i, pl in enumerate(plans) if pl.axis_sets is not None],
                                  scratch=_kernels.unfused_step_many_scratch_bytes(ptrs, n))
 
-    def _step_single_batched(self, gi, group, params):
+    def _step_single_batched(self, gi, group, params, fused_arith=False):
         """All tensors of a non-fused group through one library call.  Returns False (after dropping the
         cached batch) whenever a tensor, a state or a storage is not the one the batch was built for."""
         b = self._batches.get(gi)
@@ -336,7 +360,7 @@ class AdamW(LowBitOptimizer):
         beta1, beta2 = group["betas"]
         _kernels.adamw4bit_unfused_step_many(ptrs, len(plans), b["qm"], b["qv"], steps, b["scratch"], params[0].device,
                                              beta1=beta1, beta2=beta2, lr=group["lr"],
-                                             weight_decay=group["weight_decay"], eps=group["eps"])
+                                             weight_decay=group["weight_decay"], eps=group["eps"], fused_arith=fused_arith)
         for i in b["rank1_index"]:  # rank-1: the freshly written maxima become the state's
             plan = plans[i]
             plan.which ^= 1
@@ -345,7 +369,7 @@ class AdamW(LowBitOptimizer):
             ptrs[i] = addrs[i][plan.which]
         return True
 
-    def _step_single_each(self, group, params):
+    def _step_single_each(self, group, params, fused_arith=False):
         beta1, beta2 = group["betas"]
         md_m = self.get_qmetadata_by_state_name("exp_avg")
         md_v = self.get_qmetadata_by_state_name("exp_avg_sq")
@@ -364,7 +388,7 @@ class AdamW(LowBitOptimizer):
                 p, p.grad, state, self._q_enabled(p, "exp_avg"), self._q_enabled(p, "exp_avg_sq"), md_m, md_v,
                 self._spare.setdefault(id(p), {}),
                 beta1=beta1, beta2=beta2, lr=lr, weight_decay=wd, eps=eps, step=state["step"].item(),
-                stream=handle if (p.is_cuda and p.device.index == cur) else None)
+                stream=handle if (p.is_cuda and p.device.index == cur) else None, fused_arith=fused_arith)
 
     def _factored_update(self, group, p, state):
         md_m = self.get_qmetadata_by_state_name("exp_avg")

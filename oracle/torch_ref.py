@@ -142,10 +142,18 @@ def vectorwise_dequant(q, qmap, scale_type, shape, md):
 
 # ---- non-fused AdamW (adamw.py:332-436) -----------------------------------------------------
 def adamw_step(p, g, st, qmap_m, qmap_v, *, m_quant, v_quant, v_scale_type, beta1, beta2, lr, weight_decay, eps,
-               step, m_gp_sz=128, v_gp_sz=128, ref_pack=None, m_stochastic=False, v_stochastic=False):
+               step, m_gp_sz=128, v_gp_sz=128, ref_pack=None, m_stochastic=False, v_stochastic=False,
+               arithmetic="torch", c=None):
     """One tensor of _single_tensor_adamw4bit.  ``st`` is a dict: 'm', 'v' hold either None (not yet
-    initialised), an fp32 tensor (not quantized) or packed codes with 'm_md' / 'v_md' metadata."""
-    p.mul_(1 - lr * weight_decay)                                        # :369
+    initialised), an fp32 tensor (not quantized) or packed codes with 'm_md' / 'v_md' metadata.
+
+    ``arithmetic="fused"``: between the reference's dequantisation and quantisation, the element-wise
+    update of its fused kernels (fused_adamw_kernel.cu:69-77 = 121-128) through the C restatement
+    (``cpu.adamw_fp32``), ``c`` = the device's (1 - beta1^t, sqrt(1 - beta2^t)).  The reference has no step
+    that combines the two; this composition of its parts is what the library's fused step on rank-1 states is
+    checked against."""
+    if arithmetic == "torch":
+        p.mul_(1 - lr * weight_decay)                                    # :369
     if st.get("m") is None:
         m = torch.zeros_like(p)                                          # :394-395
     elif m_quant:
@@ -158,14 +166,22 @@ def adamw_step(p, g, st, qmap_m, qmap_v, *, m_quant, v_quant, v_scale_type, beta
         v = vectorwise_dequant(st["v"], qmap_v, v_scale_type, p.shape, st["v_md"])
     else:
         v = st["v"]
-    m.lerp_(g, 1 - beta1)                                                # :412
-    v.mul_(beta2).addcmul_(g, g, value=1 - beta2)                        # :413
-    bc1 = 1 - beta1 ** step                                              # :416-419
-    bc2 = 1 - beta2 ** step
-    step_size = lr / bc1
-    bc2_sqrt = math.sqrt(bc2)
-    denom = (v.sqrt() / bc2_sqrt).add_(eps)                              # :421
-    p.addcdiv_(m, denom, value=-step_size)                               # :422
+    if arithmetic == "fused":
+        from . import cpu
+        host = [t.detach().cpu().contiguous().numpy().reshape(-1).copy() for t in (p, g, m, v)]
+        cpu.adamw_fp32(*host, beta1, beta2, lr, weight_decay, eps, step, c=c)
+        p.copy_(torch.from_numpy(host[0]).view(p.shape))
+        m = torch.from_numpy(host[2]).view(p.shape).to(p.device)
+        v = torch.from_numpy(host[3]).view(p.shape).to(p.device)
+    else:
+        m.lerp_(g, 1 - beta1)                                            # :412
+        v.mul_(beta2).addcmul_(g, g, value=1 - beta2)                    # :413
+        bc1 = 1 - beta1 ** step                                          # :416-419
+        bc2 = 1 - beta2 ** step
+        step_size = lr / bc1
+        bc2_sqrt = math.sqrt(bc2)
+        denom = (v.sqrt() / bc2_sqrt).add_(eps)                          # :421
+        p.addcdiv_(m, denom, value=-step_size)                           # :422
     if m_quant:
         st["m"], st["m_md"] = vectorwise_quant(m, qmap_m, "group", m_gp_sz, ref_pack, m_stochastic)   # :425-428
     else:

@@ -125,6 +125,29 @@ def test_optimizer_constructors_validate_like_the_reference():
     assert set(opt.state_dict()) >= {"state", "param_groups", "qconfig"}
 
 
+def test_fused_rank1_option_applies_only_to_rank1_configurations():
+    """fused_rank1 is an extension that is off by default; it takes effect only for a 4-bit rank-1 second
+    moment without factorisation, and says so for wider codes instead of silently changing the layout."""
+    import os
+    import lpmm
+    from lpmm.config import CONFIG_DIR
+    w = torch.nn.Parameter(torch.zeros(8, 8))
+    cfg = lambda n: os.path.join(CONFIG_DIR, n)
+    opt = lpmm.optim.AdamW([w], fused=True)
+    assert opt._fused_rank1 is False and not opt._fused_rank1_applies(opt.param_groups[0])
+    opt = lpmm.optim.AdamW([w], fused=True, fused_rank1=True, qconfig=cfg("default.yml"))
+    assert opt._fused_rank1_applies(opt.param_groups[0])
+    assert "fused_rank1" not in opt.state_dict()["param_groups"][0]  # param_group keys stay the reference's
+    opt = lpmm.optim.AdamW([w], fused=True, fused_rank1=True, qconfig=cfg("default.yml"), factor_second_moment=True)
+    assert not opt._fused_rank1_applies(opt.param_groups[0])
+    opt = lpmm.optim.AdamW([w], fused=True, fused_rank1=True)  # group scales: the fused kernel holds them itself
+    assert not opt._fused_rank1_applies(opt.param_groups[0])
+    opt = lpmm.optim.AdamW([w], fused=True, fused_rank1=True, qconfig=cfg("default_8b.yml"))
+    if opt.get_qmetadata_by_state_name("exp_avg_sq")["scale_type"] == "rank1":
+        with pytest.raises(NotImplementedError):
+            opt._fused_rank1_applies(opt.param_groups[0])
+
+
 def test_enable_rule_and_override():
     import lpmm
     from lpmm.optim.optimizer import quantize_enabled
