@@ -43,6 +43,10 @@ extern "C" {
 #define LPMM_B200_KIND_Q4 0               /* 4-bit m and v, group-128 absmax scales            */
 #define LPMM_B200_KIND_FP32 1             /* fp32 m and v (the numel <= threshold fallback)    */
 
+/* element type of p and g in lpmm_b200_adamw4bit_multi_tensor_16bit */
+#define LPMM_B200_DTYPE_BF16 1
+#define LPMM_B200_DTYPE_FP16 2
+
 /* One parameter tensor of a multi-tensor step.  All pointers are device pointers into
  * contiguous arrays.  kind Q4: m, v are int8[(numel+1)/2] packed codes, m_scale, v_scale are
  * float[(numel+127)/128].  kind FP32: m, v are float[numel], the scale pointers are ignored. */
@@ -103,6 +107,17 @@ int lpmm_b200_adamw_single_tensor(float* p, const float* g, float* exp_avg, floa
 int lpmm_b200_adamw4bit_multi_tensor(const lpmm_b200_tensor* tensors, int n_tensors, const float* exp_avg_qmap,
                                      const float* exp_avg_sq_qmap, lpmm_b200_hyper hyper, int64_t group_begin,
                                      int64_t group_end, void* stream);
+
+/* The fused step for 16-bit parameters and gradients: `p` and `g` of every tensor point to bf16 or fp16
+ * arrays (dtype = LPMM_B200_DTYPE_*; the struct's float* is reinterpreted), everything else is as in
+ * lpmm_b200_adamw4bit_multi_tensor: 4-bit codes, fp32 scales, fp32 moments for kind FP32.
+ * Parameters and gradients are widened to fp32 on load, the step is the fp32 step to the bit, the new
+ * parameter is rounded to nearest-even on store.  The reference instantiates its kernel for half
+ * (fused_adamw_kernel.cu:188,222) but cannot reach it: the launcher wants half scale tensors where
+ * lpmm/optim/adamw.py:515-521 allocates fp32 ones, and bf16 is not dispatched. */
+int lpmm_b200_adamw4bit_multi_tensor_16bit(const lpmm_b200_tensor* tensors, int n_tensors, int dtype,
+                                           const float* exp_avg_qmap, const float* exp_avg_sq_qmap,
+                                           lpmm_b200_hyper hyper, int64_t group_begin, int64_t group_end, void* stream);
 
 /* The same step for a ZeRO-1 rank, with the all-gather of the updated parameters folded into the
  * kernel.  It has no counterpart in the reference (which has no distributed step).

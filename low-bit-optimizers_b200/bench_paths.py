@@ -63,6 +63,8 @@ def cases():
         ("gpt2-medium adamw fused", "AdamW", gpt2_medium_shapes(), dict(adamw, fused=True)),
         ("gpt2-medium adamw fused rank-1 (default.yml, fused_rank1)", "AdamW", gpt2_medium_shapes(),
          dict(adamw, qconfig=cfg("default.yml"), fused=True, fused_rank1=True)),
+        ("gpt2-medium adamw fused bf16 parameters", "AdamW", gpt2_medium_shapes(),
+         dict(adamw, fused=True, param_dtype=torch.bfloat16)),
         ("gpt2-medium sgd", "SGD", gpt2_medium_shapes(), dict(sgd)),
         ("ragged adamw rank-1 (default.yml)", "AdamW", RAGGED, dict(adamw, qconfig=cfg("default.yml"))),
     ]
@@ -75,6 +77,7 @@ def big_cases():
     return [
         ("llama7b adamw group (qconfig=None)", "AdamW", llama7b_shapes(), dict(adamw, qconfig=None)),
         ("llama7b adamw fused", "AdamW", llama7b_shapes(), dict(adamw, fused=True)),
+        ("llama7b adamw fused bf16 parameters", "AdamW", llama7b_shapes(), dict(adamw, fused=True, param_dtype=torch.bfloat16)),
         ("llama7b adamw rank-1 (default.yml)", "AdamW", llama7b_shapes(), dict(adamw, qconfig=cfg("default.yml"))),
         ("llama7b adamw fused rank-1 (default.yml, fused_rank1)", "AdamW", llama7b_shapes(),
          dict(adamw, qconfig=cfg("default.yml"), fused=True, fused_rank1=True)),
@@ -86,9 +89,11 @@ def big_cases():
 def run(name, kind, shapes, kw, iters):
     dev = torch.device("cuda:0")
     torch.manual_seed(0)
-    params = [torch.nn.Parameter(torch.empty(s, device=dev).normal_(0.0, 0.02)) for s in shapes]
+    kw = dict(kw)
+    dtype = kw.pop("param_dtype", torch.float32)  # not an optimizer argument: element type of parameters and gradients
+    params = [torch.nn.Parameter(torch.empty(s, device=dev).normal_(0.0, 0.02).to(dtype)) for s in shapes]
     for p in params:
-        p.grad = torch.empty_like(p).normal_(0.0, 1e-3)
+        p.grad = torch.empty(p.shape, device=dev).normal_(0.0, 1e-3).to(dtype)
     opt = getattr(lpmm.optim, kind)(params, **kw)
     for _ in range(3):
         opt.step()

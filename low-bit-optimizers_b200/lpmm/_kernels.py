@@ -97,10 +97,20 @@ class TensorList:
             self.array[i].g = g.data_ptr()
 
 
-def adamw4bit_multi_tensor(tl, qmap_m, qmap_v, beta1, beta2, lr, weight_decay, eps, step, group_begin=0, group_end=-1):
+_DTYPE16 = {torch.bfloat16: N.DTYPE_BF16, torch.float16: N.DTYPE_FP16}
+
+
+def adamw4bit_multi_tensor(tl, qmap_m, qmap_v, beta1, beta2, lr, weight_decay, eps, step, group_begin=0, group_end=-1,
+                           dtype=torch.float32):
+    """``dtype``: element type of every parameter and gradient of the list (fp32, or bf16 / fp16 for
+    ``lpmm_b200_adamw4bit_multi_tensor_16bit``)."""
     if tl.n == 0:
         return
     h = N.Hyper(beta1, beta2, lr, weight_decay, eps, step)
+    if dtype != torch.float32:
+        N.check(N.lib.lpmm_b200_adamw4bit_multi_tensor_16bit(tl.array, tl.n, _DTYPE16[dtype], _ptr(qmap_m), _ptr(qmap_v), h,
+                                                             group_begin, group_end, _stream()))
+        return
     N.check(N.lib.lpmm_b200_adamw4bit_multi_tensor(tl.array, tl.n, _ptr(qmap_m), _ptr(qmap_v), h, group_begin, group_end,
                                                    _stream()))
 

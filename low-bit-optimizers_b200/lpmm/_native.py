@@ -61,6 +61,8 @@ class StepTensor(ctypes.Structure):
 STATE_FP32, STATE_GROUP4, STATE_RANK1_4, STATE_FACTORED = 0, 1, 2, 3
 KIND_Q4 = 0
 KIND_FP32 = 1
+DTYPE_BF16 = 1
+DTYPE_FP16 = 2
 GROUP = 128
 PACK_GROUP = 2048
 STATIC_SCRATCH_BYTES = 8 * 1024 * 1024
@@ -84,6 +86,7 @@ def _load():
         "lpmm_b200_adamw4bit_single_tensor": (i32, [vp] * 8 + [f] * 6 + [i64, vp]),
         "lpmm_b200_adamw_single_tensor": (i32, [vp] * 4 + [f] * 6 + [i64, vp]),
         "lpmm_b200_adamw4bit_multi_tensor": (i32, [ctypes.POINTER(Tensor), i32, vp, vp, Hyper, i64, i64, vp]),
+        "lpmm_b200_adamw4bit_multi_tensor_16bit": (i32, [ctypes.POINTER(Tensor), i32, i32, vp, vp, Hyper, i64, i64, vp]),
         "lpmm_b200_adamw4bit_multi_tensor_peers": (i32, [ctypes.POINTER(Tensor), i32, vp, vp, Hyper, i64, i64,
                                                          ctypes.POINTER(i64), i32, vp]),
         "lpmm_b200_adamw4bit_multi_tensor_zero1": (i32, [ctypes.POINTER(Tensor), i32, vp, vp, Hyper, i64, i64,

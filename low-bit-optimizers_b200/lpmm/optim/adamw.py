@@ -174,33 +174,35 @@ class AdamW(LowBitOptimizer):
                     oh_v["max1"] = torch.zeros(((n + 127) // 128,), dtype=torch.float32, device=p.device)
                 entry = (p, p.grad, state["exp_avg"], state["exp_avg_sq"], oh_m["max1"], oh_v["max1"])
             else:
-                if state["exp_avg"].numel() <= 1:
-                    state["exp_avg"].data = torch.zeros_like(p, memory_format=torch.preserve_format)
+                if state["exp_avg"].numel() <= 1:  # fp32 moments also next to 16-bit parameters
+                    state["exp_avg"].data = torch.zeros_like(p, dtype=torch.float32, memory_format=torch.preserve_format)
                 if state["exp_avg_sq"].numel() <= 1:
-                    state["exp_avg_sq"].data = torch.zeros_like(p, memory_format=torch.preserve_format)
+                    state["exp_avg_sq"].data = torch.zeros_like(p, dtype=torch.float32, memory_format=torch.preserve_format)
                 entry = (p, p.grad, state["exp_avg"], state["exp_avg_sq"], None, None)
             for t, nm in zip(entry[:4], ("p", "g", "exp_avg", "exp_avg_sq")):
                 if not t.is_contiguous():
                     raise RuntimeError(f"{nm} must be contiguous!")
                 if not t.is_cuda:
                     raise RuntimeError(f"{nm} must be a CUDA tensor!")
-            if p.dtype != torch.float32 or p.grad.dtype != torch.float32:
-                raise RuntimeError("The type of p / g is not kFloat32!")
-            key = (float(state["step"].item()), p.device)
+            if p.dtype not in (torch.float32, torch.bfloat16, torch.float16) or p.grad.dtype != p.dtype:
+                raise RuntimeError("The type of p / g is not kFloat32 (or both kBFloat16 / kHalf)!")
+            if entry[2].dtype not in (torch.int8, torch.float32) or entry[3].dtype != entry[2].dtype:
+                raise RuntimeError("exp_avg / exp_avg_sq must be packed int8 codes or float32!")
+            key = (float(state["step"].item()), p.device, p.dtype)
             by_step.setdefault(key, []).append((entry, state))
-        for (step, device), items in by_step.items():
+        for (step, device, dtype), items in by_step.items():
             entries = [e for e, _ in items]
             qm = items[0][1]["exp_avg_qstate"]["qmap"]
             qv = items[0][1]["exp_avg_sq_qstate"]["qmap"]
-            tl = self._tensor_list((gi, step if len(by_step) > 1 else None, device), entries)
+            tl = self._tensor_list((gi, (step, dtype) if len(by_step) > 1 else None, device), entries)
             with torch.cuda.device(device):
                 _kernels.adamw4bit_multi_tensor(tl, qm, qv, beta1, beta2, group["lr"], group["weight_decay"],
-                                                group["eps"], step)
+                                                group["eps"], step, dtype=dtype)
             if len(by_step) == 1 and len(items) == len(params):
                 # every tensor of the group took this one launch: remember it, so that the following steps
                 # only bump the counters, refresh changed gradient pointers and launch
                 self._plans[gi] = dict(
-                    params=list(params), tl=tl, step=step, device=device, qm=qm, qv=qv,
+                    params=list(params), tl=tl, step=step, device=device, qm=qm, qv=qv, dtype=dtype,
                     states=[st for _, st in items], steps=[st["step"] for _, st in items],
                     m=[e[2] for e in entries], v=[e[3] for e in entries],
                     ptrs=[(e[0].data_ptr(), e[2].data_ptr(), e[3].data_ptr()) for e in entries],
@@ -228,7 +230,7 @@ class AdamW(LowBitOptimizer):
             g = p.grad
             gp = g.data_ptr()
             if gp != gptrs[i]:
-                if g.dtype != torch.float32 or not g.is_cuda or not g.is_contiguous() or g.numel() != p.numel():
+                if g.dtype != plan["dtype"] or not g.is_cuda or not g.is_contiguous() or g.numel() != p.numel():
                     del self._plans[gi]
                     return False
                 tl.array[i].g = gp
@@ -238,7 +240,7 @@ class AdamW(LowBitOptimizer):
         beta1, beta2 = group["betas"]
         with torch.cuda.device(plan["device"]):
             _kernels.adamw4bit_multi_tensor(tl, plan["qm"], plan["qv"], beta1, beta2, group["lr"], group["weight_decay"],
-                                            group["eps"], plan["step"])
+                                            group["eps"], plan["step"], dtype=plan["dtype"])
         return True
 
     def _tensor_list(self, key, entries):

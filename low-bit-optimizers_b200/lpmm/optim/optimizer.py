@@ -99,7 +99,9 @@ class LowBitOptimizer(torch.optim.Optimizer):
             if isinstance(value, torch.Tensor):
                 if key == "step":
                     return value
-                if param.is_floating_point() and value.dtype != torch.int8 and value.is_floating_point():
+                # scales and moments next to 16-bit parameters (fused step for bf16 / fp16) stay fp32
+                if (param.is_floating_point() and value.dtype != torch.int8 and value.is_floating_point()
+                        and param.dtype not in (torch.bfloat16, torch.float16)):
                     value = value.to(param.dtype)
                 return value.to(param.device)
             if isinstance(value, dict):

@@ -148,6 +148,18 @@ def test_fused_rank1_option_applies_only_to_rank1_configurations():
             opt._fused_rank1_applies(opt.param_groups[0])
 
 
+def test_fused_16bit_entry_point_argument_checks():
+    """Argument errors of the bf16 / fp16 step are found before any CUDA call."""
+    from lpmm import _native as N
+    h = N.Hyper(0.9, 0.999, 1e-3, 0.01, 1e-8, 1.0)
+    arr = (N.Tensor * 1)()
+    fn = N.lib.lpmm_b200_adamw4bit_multi_tensor_16bit
+    assert fn(arr, 0, 7, None, None, h, 0, -1, None) == -3           # unknown element type
+    assert fn(arr, 0, N.DTYPE_BF16, None, None, h, 0, -1, None) == 0  # an empty list is a no-op
+    assert fn(None, 1, N.DTYPE_FP16, None, None, h, 0, -1, None) == -1
+    assert fn(arr, 0, N.DTYPE_FP16, None, None, h, 0, 5, None) == -2  # range beyond the list
+
+
 def test_enable_rule_and_override():
     import lpmm
     from lpmm.optim.optimizer import quantize_enabled
