@@ -56,6 +56,170 @@ __device__ __forceinline__ uint4 narrow8(const float* x) {
   return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
+// Pairs: one 32-bit word holds elements (2j, 2j+1); each half widens exactly and narrows to nearest-even.
+template <typename T>
+__device__ __forceinline__ f2 widen2(unsigned w);
+template <>
+__device__ __forceinline__ f2 widen2<__nv_bfloat16>(unsigned w) {
+  return f2_pack(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u));
+}
+template <>
+__device__ __forceinline__ f2 widen2<__half>(unsigned w) {
+  const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+  return f2_pack(f.x, f.y);
+}
+template <typename T>
+__device__ __forceinline__ unsigned narrow2(f2 x);
+template <>
+__device__ __forceinline__ unsigned narrow2<__nv_bfloat16>(f2 x) {
+  float lo, hi;
+  f2_unpack(x, lo, hi);
+  const __nv_bfloat162 r = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const unsigned*>(&r);
+}
+template <>
+__device__ __forceinline__ unsigned narrow2<__half>(f2 x) {
+  float lo, hi;
+  f2_unpack(x, lo, hi);
+  const __half2 r = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const unsigned*>(&r);
+}
+
+// Packed constants of the fp32x2 path (the fused arithmetic; see adamw4bit.cu).
+struct HConsts2 {
+  f2 beta1, beta2, omb1, omb2, wd, nlr, eps, nc1, nc2s, rc2s, half, mone, one, k16, km15;
+};
+__device__ __forceinline__ HConsts2 make_hconsts2(const UConsts& c) {
+  HConsts2 k;
+  k.beta1 = f2_splat(c.f_beta1);
+  k.beta2 = f2_splat(c.f_beta2);
+  k.omb1 = f2_splat(c.f_omb1);
+  k.omb2 = f2_splat(c.f_omb2);
+  k.wd = f2_splat(c.f_wd);
+  k.nlr = f2_splat(-c.f_lr);
+  k.eps = f2_splat(c.f_eps);
+  k.nc1 = f2_splat(-c.c1);
+  k.nc2s = f2_splat(-c.c2s);
+  k.rc2s = f2_splat(c.rc2s);
+  k.half = f2_splat(0.5f);
+  k.mone = f2_splat(-1.0f);
+  k.one = f2_splat(1.0f);
+  k.k16 = f2_splat(16.0f);
+  k.km15 = f2_splat(-1.5f);
+  return k;
+}
+
+// One full, aligned 4-bit group with packed fp32x2 instructions: elements (2j, 2j+1) share every
+// multiply / add / fma, each half rounding like the scalar instruction, so the results are those of
+// h_group_fast with the short sqrt / division sequences (selected only where those apply).
+template <typename T, bool VLIN>
+__device__ __forceinline__ void h_group_x2(const TDesc& t, unsigned gl, int l16, unsigned hmask, const HConsts2& c,
+                                           const QMapSmem& Sm, const QMapSmem& Sv, const LutEnt* __restrict__ lut_m,
+                                           const LutEnt* __restrict__ lut_v, float qm_l, float qv_l, unsigned pf) {
+  const size_t e0 = (size_t)gl * 128 + (size_t)l16 * 8;
+  uint4* pp = reinterpret_cast<uint4*>(reinterpret_cast<unsigned short*>(t.p) + e0);
+  const uint4* gp = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(t.g) + e0);
+  uint32_t* mcp = reinterpret_cast<uint32_t*>(t.m) + (size_t)gl * 16 + l16;
+  uint32_t* vcp = reinterpret_cast<uint32_t*>(t.v) + (size_t)gl * 16 + l16;
+  const uint4 praw = *pp;
+  const uint4 graw = __ldg(gp);
+  const uint32_t mc = *mcp;
+  const uint32_t vc = *vcp;
+  const float pm = __fmul_rn(qm_l, t.sm[gl]);
+  const float pv = __fmul_rn(qv_l, t.sv[gl]);
+  if (pf) {
+    prefetch_l2(pp + (size_t)pf * 16);
+    prefetch_l2(gp + (size_t)pf * 16);
+    prefetch_l2(mcp + (size_t)pf * 16);
+    prefetch_l2(vcp + (size_t)pf * 16);
+  }
+  const unsigned pw[4] = {praw.x, praw.y, praw.z, praw.w}, gw[4] = {graw.x, graw.y, graw.z, graw.w};
+  unsigned po[4];
+  f2 m[4], v[4];
+  float am = 0.0f, av = 0.0f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float m0a = __shfl_sync(hmask, pm, (int)(mc >> (8 * j)), 16);  // source lane = code (mod 16)
+    const float m0b = __shfl_sync(hmask, pm, (int)(mc >> (8 * j + 4)), 16);
+    const float v0a = __shfl_sync(hmask, pv, (int)(vc >> (8 * j)), 16);
+    const float v0b = __shfl_sync(hmask, pv, (int)(vc >> (8 * j + 4)), 16);
+    const f2 gj = widen2<T>(gw[j]);
+    const f2 pj = widen2<T>(pw[j]);
+    m[j] = f2_fma(c.beta1, f2_pack(m0a, m0b), f2_mul(c.omb1, gj));
+    v[j] = f2_fma(c.beta2, f2_pack(v0a, v0b), f2_mul(f2_mul(c.omb2, gj), gj));
+    float ma, mb, va, vb;
+    f2_unpack(m[j], ma, mb);
+    f2_unpack(v[j], va, vb);
+    am = fmaxf(am, fmaxf(fabsf(ma), fabsf(mb)));
+    av = fmaxf(av, fmaxf(va, vb));
+    // sqrt(v): y = rsqrt(max(v, FLT_MIN)); s = v*y; s += (v - s*s) * (y/2)
+    const f2 y = f2_pack(mufu_rsq(fmaxf(va, 1.17549435e-38f)), mufu_rsq(fmaxf(vb, 1.17549435e-38f)));
+    f2 s = f2_mul(v[j], y);
+    const f2 e = f2_fma(s, f2_mul(s, c.mone), v[j]);
+    s = f2_fma(e, f2_mul(c.half, y), s);
+    // nd = -(s / c2s + eps) * c1
+    f2 q = f2_mul(s, c.rc2s);
+    q = f2_fma(f2_fma(q, c.nc2s, s), c.rc2s, q);
+    const f2 nd = f2_mul(f2_add(q, c.eps), c.nc1);
+    // m / d: r = rcp(d) refined once, quotient corrected by its exact residual
+    float nda, ndb;
+    f2_unpack(nd, nda, ndb);
+    const f2 r0 = f2_pack(mufu_rcp(fabsf(nda)), mufu_rcp(fabsf(ndb)));
+    const f2 r = f2_fma(r0, f2_fma(nd, r0, c.one), r0);
+    const f2 qq = f2_mul(m[j], r);
+    const f2 quo = f2_fma(f2_fma(nd, qq, m[j]), r, qq);
+    po[j] = narrow2<T>(f2_fma(c.nlr, f2_fma(c.wd, pj, quo), pj));
+  }
+  *pp = make_uint4(po[0], po[1], po[2], po[3]);
+  am = hw_max(am, hmask);
+  av = hw_max(av, hmask);
+  uint32_t mo = 0, vo = 0;
+  if (udiv_ok(am) && udiv_ok(av)) {
+    const float rm = rcp_nr(am), rv = rcp_nr(av);
+    const f2 rm2 = f2_splat(rm), rv2 = f2_splat(rv), nam2 = f2_splat(-am), nav2 = f2_splat(-av);
+#pragma unroll
+    for (int j = 3; j >= 0; --j) {
+      f2 xm = f2_mul(m[j], rm2);
+      xm = f2_fma(f2_fma(xm, nam2, m[j]), rm2, xm);
+      f2 xv = f2_mul(v[j], rv2);
+      xv = f2_fma(f2_fma(xv, nav2, v[j]), rv2, xv);
+      float xa, xb;
+      f2_unpack(xm, xa, xb);
+      mo = (mo << 4) + (uint32_t)lut_code(lut_m, xb);
+      mo = (mo << 4) + (uint32_t)lut_code(lut_m, xa);
+      if (VLIN) {
+        float ta, tb;
+        f2_unpack(f2_fma(xv, c.k16, c.km15), ta, tb);
+        vo = vo * 16u + __float2uint_ru(tb);
+        vo = vo * 16u + __float2uint_ru(ta);
+      } else {
+        f2_unpack(xv, xa, xb);
+        vo = (vo << 4) + (uint32_t)lut_code(lut_v, xb);
+        vo = (vo << 4) + (uint32_t)lut_code(lut_v, xa);
+      }
+    }
+    if (am == 0.0f) mo = 0xFFFFFFFFu;  // 0/0 = NaN -> code 15 for the whole group
+    if (av == 0.0f) vo = 0xFFFFFFFFu;
+  } else {  // scales outside the shared-reciprocal domain
+#pragma unroll
+    for (int j = 3; j >= 0; --j) {
+      float ma, mb, va, vb;
+      f2_unpack(m[j], ma, mb);
+      f2_unpack(v[j], va, vb);
+      mo = (mo << 4) + (uint32_t)(bsearch_code(Sm.qmap, __fdiv_rn(mb, am)) & 15);
+      mo = (mo << 4) + (uint32_t)(bsearch_code(Sm.qmap, __fdiv_rn(ma, am)) & 15);
+      vo = (vo << 4) + (uint32_t)(bsearch_code(Sv.qmap, __fdiv_rn(vb, av)) & 15);
+      vo = (vo << 4) + (uint32_t)(bsearch_code(Sv.qmap, __fdiv_rn(va, av)) & 15);
+    }
+  }
+  *mcp = mo;
+  *vcp = vo;
+  if (l16 == 0) {
+    t.sm[gl] = am;
+    t.sv[gl] = av;
+  }
+}
+
 // Any 4-bit group, any alignment, any map: scalar accesses predicated on numel, IEEE sqrt and
 // division, the reference's search (fused_adamw_kernel.cu:114,130-143,160-165).
 template <typename T>
@@ -110,8 +274,9 @@ __device__ __noinline__ void h_group_generic(const TDesc& t, long long gl, int l
   }
 }
 
-// One full, aligned 4-bit group with the short exact sqrt / division sequences.  qm_l / qv_l: this
-// lane's entry of the two maps; the dequantised values come from a shuffle whose source lane is the code.
+// One full, aligned 4-bit group, element by element (IEEE sqrt / division when the hyper-parameters lie
+// outside the short sequences' domain).  qm_l / qv_l: this lane's entry of the two maps; the
+// dequantised values come from a shuffle whose source lane is the code.
 template <typename T, bool VLIN>
 __device__ __forceinline__ void h_group_fast(const TDesc& t, unsigned gl, int l16, unsigned hmask, const UConsts& c,
                                              const QMapSmem& Sm, const QMapSmem& Sv, const LutEnt* __restrict__ lut_m,
@@ -217,6 +382,7 @@ adamw4bit_half_kernel(const __grid_constant__ Table tab, const float* __restrict
     lut_build(Sm, lut_m, qmap_m);
     tables_ok = Sm.valid && Sv.valid;
   }
+  const HConsts2 k2 = make_hconsts2(c);
   const int l16 = threadIdx.x & 15;
   const unsigned hmask = 0xFFFFu << (threadIdx.x & 16);
   long long gi = gbeg + (long long)blockIdx.x * HW_PER_CTA + (threadIdx.x >> 4);
@@ -231,14 +397,22 @@ adamw4bit_half_kernel(const __grid_constant__ Table tab, const float* __restrict
     long long tend = (ti + 1 < tab.n) ? tab.t[ti + 1].gstart : tab.gtotal;
     if (tend > gend) tend = gend;
     if (t.kind == LPMM_B200_KIND_Q4) {
-      if (tables_ok && t.aligned && c.f_fast) {
+      if (tables_ok && t.aligned) {
         long long fend = tstart + t.numel / 128;  // end of the full groups
         if (fend > tend) fend = tend;
         if (gi < fend) {
           unsigned gl = (unsigned)(gi - tstart);
           const unsigned lim = (unsigned)(fend - tstart);
           const unsigned st = (unsigned)stride;
-          if (vlin) {
+          if (c.f_fast && vlin) {
+            for (; gl < lim; gl += st)
+              h_group_x2<T, true>(t, gl, l16, hmask, k2, Sm, Sv, lut_m, lut_v, qm_l, qv_l,
+                                  (gl + PF_DIST * st < lim) ? PF_DIST * st : 0u);
+          } else if (c.f_fast) {
+            for (; gl < lim; gl += st)
+              h_group_x2<T, false>(t, gl, l16, hmask, k2, Sm, Sv, lut_m, lut_v, qm_l, qv_l,
+                                   (gl + PF_DIST * st < lim) ? PF_DIST * st : 0u);
+          } else if (vlin) {  // hyper-parameters outside the short sequences' domain: IEEE sqrt and division
             for (; gl < lim; gl += st)
               h_group_fast<T, true>(t, gl, l16, hmask, c, Sm, Sv, lut_m, lut_v, qm_l, qv_l,
                                     (gl + PF_DIST * st < lim) ? PF_DIST * st : 0u);
