@@ -148,6 +148,31 @@ def test_fused_rank1_option_applies_only_to_rank1_configurations():
             opt._fused_rank1_applies(opt.param_groups[0])
 
 
+def test_fused_arith_entry_points_refuse_what_they_do_not_cover():
+    """The fused arithmetic on non-fused states: 4-bit codes only, no factored second moment, moments both fp32
+    or both quantized -- refused before any CUDA call."""
+    from lpmm import _native as N
+    one = N.lib.lpmm_b200_adamw4bit_fused_arith_step
+    many = N.lib.lpmm_b200_adamw4bit_fused_arith_step_many
+    hp = (0.9, 0.999, 1e-3, 0.01, 1e-8)
+    t = N.StepTensor()
+    t.numel, t.ndim = 0, 2
+    t.shape[0], t.shape[1] = 0, 8
+    t.m_mode, t.v_mode = N.STATE_GROUP4, N.STATE_RANK1_4
+    assert one(ctypes.byref(t), None, None, *hp, 1.0, None) == 0          # empty tensor: nothing to do
+    t.m_bits = t.v_bits = 8
+    assert one(ctypes.byref(t), None, None, *hp, 1.0, None) == -5         # wider codes
+    t.m_bits = t.v_bits = 4
+    t.v_mode = N.STATE_FACTORED
+    assert one(ctypes.byref(t), None, None, *hp, 1.0, None) == -5         # factored second moment
+    t.m_mode, t.v_mode = N.STATE_FP32, N.STATE_GROUP4
+    assert one(ctypes.byref(t), None, None, *hp, 1.0, None) == -5         # mixed fp32 / quantized moments
+    assert one(None, None, None, *hp, 1.0, None) == -1
+    assert many(None, -1, None, None, *hp, None, None, 0, None) == -2
+    assert many(None, 2, None, None, *hp, None, None, 0, None) == -1
+    assert many(None, 0, None, None, *hp, None, None, 0, None) == 0
+
+
 def test_fused_16bit_entry_point_argument_checks():
     """Argument errors of the bf16 / fp16 step are found before any CUDA call."""
     from lpmm import _native as N
