@@ -314,13 +314,16 @@ def run_own(args):
         # fused update + peer stores: the target time is the slower of HBM and NVLink; this kernel is NVLink-bound
         link_bytes = 4.0 * opt.shard_groups * 128 * (world - 1)      # sent (and received) per rank per launch
         link_peak = 770.0                                            # GB/s per direction, measured peer copy on this pool
-        t_hbm, t_link = k_bytes / (peak * 1e9), link_bytes / (link_peak * 1e9)
-        roofline = {"bound": "nvlink" if t_link >= t_hbm else "hbm", "achieved": link_bytes / (k_ms * 1e-3) / 1e9,
+        # with the gradient reduction in the kernel a rank also RECEIVES its shard's gradients from every peer, on
+        # the same direction of its links as the peers' parameter stores: that direction carries twice the bytes
+        link_busiest = link_bytes * (2.0 if args.reduce_grads else 1.0)
+        t_hbm, t_link = k_bytes / (peak * 1e9), link_busiest / (link_peak * 1e9)
+        roofline = {"bound": "nvlink" if t_link >= t_hbm else "hbm", "achieved": link_busiest / (k_ms * 1e-3) / 1e9,
                     "peak": link_peak, "unit": "GB/s", "frac": max(t_hbm, t_link) / (k_ms * 1e-3), "traffic": None,
                     "peak_kind": "measured peer-copy rate of this pool (770 GB/s per direction); HBM side of measured",
                     "kernel": "adamw4bit_multi_kernel (update + stores to all peers)", "launch_ms": k_ms,
                     "algorithmic_bytes_per_launch": k_bytes, "nvlink_bytes_sent_per_rank_per_launch": link_bytes,
-                    "target_ms": max(t_hbm, t_link) * 1e3}
+                    "nvlink_bytes_received_per_rank_per_launch": link_busiest, "target_ms": max(t_hbm, t_link) * 1e3}
 
     # end to end through the public API with the gradients coming from pinned host memory
     e2e = None
