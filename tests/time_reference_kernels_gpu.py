@@ -1,9 +1,13 @@
 """Like-for-like step time on one B200: the reference's own fused kernels (``oracle/_ref/fused_adamw``,
 its sources compiled unmodified for sm_100a) driven as ``_fused_adamw4bit`` drives them -- one launch per
 tensor (lpmm/optim/adamw.py:463-561) -- against this library's one-launch step, on the same
-LLaMA-7B-shaped fp32 list and the same buffers.  Not a test (pytest does not collect it); run it as
+LLaMA-7B-shaped fp32 list and the same buffers.  With ``--nonfused`` instead: the reference's non-fused step (``_single_tensor_adamw4bit``,
+lpmm/optim/adamw.py:332-436) as its sequence of torch CUDA operations per parameter (``oracle/torch_ref.py``)
+with the reference's compiled ``pack_nonlinear``, against ``lpmm.optim.AdamW`` of this package, on the
+GPT-2-medium-shaped list, for the group and the rank-1 second-moment configuration.
+Not a test (pytest does not collect it); run it as
 
-    python tests/time_reference_kernels_gpu.py [--layers 32] [--iters 10]
+    python tests/time_reference_kernels_gpu.py [--layers 32] [--iters 10] [--nonfused]
 
 The figures in ``profiles/reference_kernels_vs_one_launch_step_7b_list.md`` come from it."""
 import argparse
@@ -20,11 +24,70 @@ from gpu_helpers import HYPER, llama7b_shapes, load_reference_extension  # noqa:
 THRESHOLD = 4096
 
 
+def gpt2_medium_shapes():
+    shapes = [(50257, 1024), (1024, 1024)]
+    for _ in range(24):
+        shapes += [(1024, 3072), (1024, 1024), (1024, 4096), (4096, 1024)] + [(1024,)] * 4
+    return shapes
+
+
+def nonfused(iters):
+    import lpmm
+    from lpmm.config import CONFIG_DIR
+    from oracle import torch_ref as T
+    quant = load_reference_extension("quantization")
+    if quant is None:
+        raise SystemExit("oracle/_ref/quantization is not built")
+    dev = torch.device("cuda:0")
+    shapes = gpt2_medium_shapes()
+    buf = torch.zeros(256, device=dev)
+    buf[64:80] = lpmm.functional.create_general_qmap("nonlinear", 4, True).to(dev)
+    buf[128:144] = lpmm.functional.create_general_qmap("power-1", 4, False).to(dev)
+    qm, qv = buf[64:80], buf[128:144]
+    kw = dict(lr=HYPER["lr"], betas=(HYPER["beta1"], HYPER["beta2"]), eps=HYPER["eps"], weight_decay=HYPER["weight_decay"])
+    for v_scale, cfg in (("group", None), ("rank1", os.path.join(CONFIG_DIR, "default.yml"))):
+        torch.manual_seed(0)
+        ps = [torch.empty(s, device=dev).normal_(0.0, 0.02) for s in shapes]
+        gs = [torch.empty(s, device=dev).normal_(0.0, 1e-3) for s in shapes]
+        total = sum(p.numel() for p in ps)
+        states = [dict() for _ in ps]
+
+        def step_reference(step):
+            for p, g, st in zip(ps, gs, states):
+                q = p.numel() > THRESHOLD
+                T.adamw_step(p, g, st, qm, qv, m_quant=q, v_quant=q, v_scale_type=v_scale, beta1=HYPER["beta1"],
+                             beta2=HYPER["beta2"], lr=HYPER["lr"], weight_decay=HYPER["weight_decay"], eps=HYPER["eps"],
+                             step=float(step), ref_pack=quant.pack_nonlinear)
+
+        params = [torch.nn.Parameter(p.clone()) for p in ps]
+        for p, g in zip(params, gs):
+            p.grad = g
+        opt = lpmm.optim.AdamW(params, qconfig=cfg, **kw)
+        for name, fn in ((f"torch-op sequence of the reference + its pack kernel, v {v_scale}", step_reference),
+                         (f"lpmm.optim.AdamW of this package, v {v_scale}", lambda s: opt.step())):
+            for s in range(1, 4):
+                fn(s)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for s in range(4, 4 + iters):
+                fn(s)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / iters
+            print(f"{name}: {len(ps)} tensors, {total} params, {ms:.3f} ms/step, {total / ms / 1e6:.1f} Gparam/s", flush=True)
+        del opt, params, states, ps, gs
+        torch.cuda.empty_cache()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--nonfused", action="store_true")
     a = ap.parse_args()
+    if a.nonfused:
+        return nonfused(a.iters)
     import lpmm
     from lpmm import _kernels
     ref = load_reference_extension("fused_adamw")
