@@ -275,9 +275,13 @@ def run_own(args):
     sampler.mark()
     launches[0] = 0
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    marks = []  # one event after every step: a step is one launch of the multi-tensor kernel (N = 1)
     e0.record()
     for _ in range(args.steps):
         step()
+        if world == 1:
+            marks.append(torch.cuda.Event(enable_timing=True))
+            marks[-1].record()
     e1.record()
     barrier()
     clocks = sampler.stop()
@@ -290,16 +294,10 @@ def run_own(args):
     ms_per_step = ms / args.steps
     value = total / (ms_per_step * 1e-3)
 
-    # dominant kernel alone: events around each launch of the multi-tensor step
+    # dominant kernel: the launches of the timed region itself, each measured from the end of the launch before it
+    # to its own end (the queue never runs dry, so that is the launch's duration)
     if world == 1:
-        ks = []
-        for _ in range(max(3, min(args.steps, 10))):
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
-            step()
-            b.record()
-            torch.cuda.synchronize()
-            ks.append(a.elapsed_time(b))
+        ks = [a.elapsed_time(b) for a, b in zip([e0] + marks[:-1], marks)]
         k_ms = sum(ks) / len(ks)
         k_bytes = alg_bytes
     else:
@@ -310,6 +308,8 @@ def run_own(args):
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "traffic": NCU_TRAFFIC_PER_PARAM * (k_bytes / BYTES_Q4), "peak_kind": f"of {peak_kind}",
                 "kernel": "adamw4bit_multi_kernel", "algorithmic_bytes_per_launch": k_bytes, "launch_ms": k_ms}
+    if world == 1:
+        roofline["launch_ms_min_max"] = [min(ks), max(ks)]
     if world > 1 and args.gather == "fused":
         # fused update + peer stores: the target time is the slower of HBM and NVLink; this kernel is NVLink-bound
         link_bytes = 4.0 * opt.shard_groups * 128 * (world - 1)      # sent (and received) per rank per launch
