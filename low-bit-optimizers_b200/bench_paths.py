@@ -111,14 +111,41 @@ def run(name, kind, shapes, kw, iters):
     print(f"{name}: {n} params, {ms:.3f} ms/step (wall {wall:.3f}), {n / ms / 1e6:.1f} Gparam/s", flush=True)
 
 
+def copy_rate(seconds=3.0):
+    """Context for the roofline fractions: torch's device-to-device copy (the kind of kernel the measured
+    peak comes from) as a burst of 10 and sustained for a few seconds under the power cap."""
+    dev = torch.device("cuda:0")
+    n = 1 << 30
+    src = torch.empty(n, dtype=torch.bfloat16, device=dev).normal_()
+    dst = torch.empty_like(src)
+    nbytes = 2.0 * n * 2
+    for label, iters in (("burst of 10", 10), (f"sustained, ~{seconds:.0f} s", int(seconds / (nbytes / 6.0e12)))):
+        for _ in range(3):
+            dst.copy_(src)
+        torch.cuda.synchronize()
+        if label.startswith("burst"):
+            time.sleep(1.0)  # let the clocks recover
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            dst.copy_(src)
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / iters
+        print(f"copy_ of {n} bf16 elements ({label}, {iters} copies): {ms:.3f} ms, {nbytes / ms / 1e6:.0f} GB/s", flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--only", default=None)
     ap.add_argument("--big", action="store_true", help="the LLaMA-7B-shaped list instead (needs ~70 GB)")
+    ap.add_argument("--copy", action="store_true", help="time torch's device copy instead (burst and sustained)")
     a = ap.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("needs a CUDA device")
+    if a.copy:
+        return copy_rate()
     for name, kind, shapes, kw in (big_cases() if a.big else cases()):
         if a.only is None or a.only in name:
             run(name, kind, shapes, kw, a.iters)
