@@ -150,8 +150,9 @@ def time_cpu_oracle(steps, warmup, sample_shapes, threads=None):
     from oracle import cpu as O
     z = np.load(os.path.join(ROOT, "tests", "golden", "qmaps.npz"))
     qm, qv = z["m"], z["v"]
-    if threads:
-        O.set_threads(threads)
+    if not threads:  # every host thread this process may run on (torchrun exports OMP_NUM_THREADS=1: not that)
+        threads = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    O.set_threads(threads)
     rng = np.random.default_rng(0)
     tensors = []
     for s in sample_shapes:
