@@ -22,6 +22,7 @@
 #include <math.h>
 
 #include "common.cuh"
+#include "fused_x2.cuh"
 #include "multi_tensor.cuh"
 
 namespace lpmm_b200 {
@@ -254,11 +255,6 @@ __device__ __forceinline__ void group_q4_fast(const LanePtrs& t, unsigned gl, in
   }
 }
 
-// Packed constants of the fp32x2 path.
-struct Consts2 {
-  f2 beta1, beta2, omb1, omb2, wd, nlr, eps, nc1, nc2s, rc2s, half, mone, one, k16, km15;
-};
-
 // The same group update written with packed fp32x2 instructions: elements (2j, 2j+1) of a lane share
 // every multiply / add / fma, each half rounding exactly like the scalar instruction, so results
 // are bit-identical to group_q4_fast<true, VLIN>.  Uses the short sqrt/division sequences, so it is
@@ -292,32 +288,7 @@ __device__ __forceinline__ void group_q4_x2(const LanePtrs& t, unsigned gl, int 
     const float m0b = __shfl_sync(hmask, pm, (int)(mc >> (8 * j + 4)), 16);
     const float v0a = __shfl_sync(hmask, pv, (int)(vc >> (8 * j)), 16);
     const float v0b = __shfl_sync(hmask, pv, (int)(vc >> (8 * j + 4)), 16);
-    const f2 gj = g.v[j];
-    m[j] = f2_fma(c.beta1, f2_pack(m0a, m0b), f2_mul(c.omb1, gj));
-    v[j] = f2_fma(c.beta2, f2_pack(v0a, v0b), f2_mul(f2_mul(c.omb2, gj), gj));
-    float ma, mb, va, vb;
-    f2_unpack(m[j], ma, mb);
-    f2_unpack(v[j], va, vb);
-    am = fmaxf(am, fmaxf(fabsf(ma), fabsf(mb)));
-    av = fmaxf(av, fmaxf(va, vb));
-    // sqrt(v): y = rsqrt(max(v, FLT_MIN)); s = v*y; s += (v - s*s) * (y/2)
-    const f2 y = f2_pack(mufu_rsq(fmaxf(va, 1.17549435e-38f)), mufu_rsq(fmaxf(vb, 1.17549435e-38f)));
-    f2 s = f2_mul(v[j], y);
-    const f2 e = f2_fma(s, f2_mul(s, c.mone), v[j]);
-    s = f2_fma(e, f2_mul(c.half, y), s);
-    // nd = -(s / c2s + eps) * c1  (the negated denominator: what the division's residuals need)
-    f2 q = f2_mul(s, c.rc2s);
-    q = f2_fma(f2_fma(q, c.nc2s, s), c.rc2s, q);
-    const f2 nd = f2_mul(f2_add(q, c.eps), c.nc1);
-    // m / d: r = rcp(d) refined once, quotient corrected by its exact residual
-    float nda, ndb;
-    f2_unpack(nd, nda, ndb);
-    const f2 r0 = f2_pack(mufu_rcp(fabsf(nda)), mufu_rcp(fabsf(ndb)));
-    const f2 r = f2_fma(r0, f2_fma(nd, r0, c.one), r0);
-    const f2 qq = f2_mul(m[j], r);
-    const f2 quo = f2_fma(f2_fma(nd, qq, m[j]), r, qq);
-    // p -= lr * (quo + wd * p)
-    p.v[j] = f2_fma(c.nlr, f2_fma(c.wd, p.v[j], quo), p.v[j]);
+    p.v[j] = fused_pair_x2(c, g.v[j], p.v[j], f2_pack(m0a, m0b), f2_pack(v0a, v0b), m[j], v[j], am, av);
   }
   stg_f2x4(pp, p);
   if (PEERS) {
@@ -327,31 +298,7 @@ __device__ __forceinline__ void group_q4_x2(const LanePtrs& t, unsigned gl, int 
   av = hw_max(av, hmask);
   uint32_t mo = 0, vo = 0;
   if (udiv_ok(am) && udiv_ok(av)) {
-    const float rm = rcp_nr(am), rv = rcp_nr(av);
-    const f2 rm2 = f2_splat(rm), rv2 = f2_splat(rv), nam2 = f2_splat(-am), nav2 = f2_splat(-av);
-#pragma unroll
-    for (int j = 3; j >= 0; --j) {
-      f2 xm = f2_mul(m[j], rm2);
-      xm = f2_fma(f2_fma(xm, nam2, m[j]), rm2, xm);
-      f2 xv = f2_mul(v[j], rv2);
-      xv = f2_fma(f2_fma(xv, nav2, v[j]), rv2, xv);
-      float xa, xb;
-      f2_unpack(xm, xa, xb);
-      mo = (mo << 4) + (uint32_t)lut_code(lut_m, xb);
-      mo = (mo << 4) + (uint32_t)lut_code(lut_m, xa);
-      if (VLIN) {
-        float ta, tb;
-        f2_unpack(f2_fma(xv, c.k16, c.km15), ta, tb);
-        vo = vo * 16u + __float2uint_ru(tb);
-        vo = vo * 16u + __float2uint_ru(ta);
-      } else {
-        f2_unpack(xv, xa, xb);
-        vo = (vo << 4) + (uint32_t)lut_code(lut_v, xb);
-        vo = (vo << 4) + (uint32_t)lut_code(lut_v, xa);
-      }
-    }
-    if (am == 0.0f) mo = 0xFFFFFFFFu;  // 0/0 = NaN -> code 15 for the whole group
-    if (av == 0.0f) vo = 0xFFFFFFFFu;
+    requant_x2<VLIN>(c, m, v, am, av, lut_m, lut_v, mo, vo);
   } else {  // scales outside the shared-reciprocal domain
     float mm[8], vv[8];
 #pragma unroll
@@ -446,22 +393,7 @@ __device__ __forceinline__ void run_groups(const Table& tab, const Consts& c, co
           const unsigned lim = (unsigned)(fend - tstart);
           const unsigned st = (unsigned)stride;
           if (FAST) {
-            Consts2 c2;
-            c2.beta1 = f2_splat(c.beta1);
-            c2.beta2 = f2_splat(c.beta2);
-            c2.omb1 = f2_splat(c.omb1);
-            c2.omb2 = f2_splat(c.omb2);
-            c2.wd = f2_splat(c.wd);
-            c2.nlr = f2_splat(-c.lr);
-            c2.eps = f2_splat(c.eps);
-            c2.nc1 = f2_splat(-c.c1);
-            c2.nc2s = f2_splat(-c.c2s);
-            c2.rc2s = f2_splat(c.rc2s);
-            c2.half = f2_splat(0.5f);
-            c2.mone = f2_splat(-1.0f);
-            c2.one = f2_splat(1.0f);
-            c2.k16 = f2_splat(16.0f);
-            c2.km15 = f2_splat(-1.5f);
+            const Consts2 c2 = make_consts_x2(c.beta1, c.beta2, c.omb1, c.omb2, c.lr, c.wd, c.eps, c.c1, c.c2s, c.rc2s);
             for (; gl < lim; gl += st)
               group_q4_x2<VLIN, PEERS>(lp, gl, l16, hmask, c2, Sm, Sv, lut_m, lut_v, qm_l, qv_l,
                                        (gl + PF_DIST * st < lim) ? PF_DIST * st : 0u, pi);

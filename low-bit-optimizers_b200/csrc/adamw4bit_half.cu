@@ -18,6 +18,7 @@
 #include <math.h>
 
 #include "common.cuh"
+#include "fused_x2.cuh"
 #include "multi_tensor.cuh"
 #include "unfused_math.cuh"
 
@@ -85,35 +86,11 @@ __device__ __forceinline__ unsigned narrow2<__half>(f2 x) {
   return *reinterpret_cast<const unsigned*>(&r);
 }
 
-// Packed constants of the fp32x2 path (the fused arithmetic; see adamw4bit.cu).
-struct HConsts2 {
-  f2 beta1, beta2, omb1, omb2, wd, nlr, eps, nc1, nc2s, rc2s, half, mone, one, k16, km15;
-};
-__device__ __forceinline__ HConsts2 make_hconsts2(const UConsts& c) {
-  HConsts2 k;
-  k.beta1 = f2_splat(c.f_beta1);
-  k.beta2 = f2_splat(c.f_beta2);
-  k.omb1 = f2_splat(c.f_omb1);
-  k.omb2 = f2_splat(c.f_omb2);
-  k.wd = f2_splat(c.f_wd);
-  k.nlr = f2_splat(-c.f_lr);
-  k.eps = f2_splat(c.f_eps);
-  k.nc1 = f2_splat(-c.c1);
-  k.nc2s = f2_splat(-c.c2s);
-  k.rc2s = f2_splat(c.rc2s);
-  k.half = f2_splat(0.5f);
-  k.mone = f2_splat(-1.0f);
-  k.one = f2_splat(1.0f);
-  k.k16 = f2_splat(16.0f);
-  k.km15 = f2_splat(-1.5f);
-  return k;
-}
-
 // One full, aligned 4-bit group with packed fp32x2 instructions: elements (2j, 2j+1) share every
 // multiply / add / fma, each half rounding like the scalar instruction, so the results are those of
 // h_group_fast with the short sqrt / division sequences (selected only where those apply).
 template <typename T, bool VLIN>
-__device__ __forceinline__ void h_group_x2(const TDesc& t, unsigned gl, int l16, unsigned hmask, const HConsts2& c,
+__device__ __forceinline__ void h_group_x2(const TDesc& t, unsigned gl, int l16, unsigned hmask, const Consts2& c,
                                            const QMapSmem& Sm, const QMapSmem& Sv, const LutEnt* __restrict__ lut_m,
                                            const LutEnt* __restrict__ lut_v, float qm_l, float qv_l, unsigned pf) {
   const size_t e0 = (size_t)gl * 128 + (size_t)l16 * 8;
@@ -145,61 +122,14 @@ __device__ __forceinline__ void h_group_x2(const TDesc& t, unsigned gl, int l16,
     const float v0b = __shfl_sync(hmask, pv, (int)(vc >> (8 * j + 4)), 16);
     const f2 gj = widen2<T>(gw[j]);
     const f2 pj = widen2<T>(pw[j]);
-    m[j] = f2_fma(c.beta1, f2_pack(m0a, m0b), f2_mul(c.omb1, gj));
-    v[j] = f2_fma(c.beta2, f2_pack(v0a, v0b), f2_mul(f2_mul(c.omb2, gj), gj));
-    float ma, mb, va, vb;
-    f2_unpack(m[j], ma, mb);
-    f2_unpack(v[j], va, vb);
-    am = fmaxf(am, fmaxf(fabsf(ma), fabsf(mb)));
-    av = fmaxf(av, fmaxf(va, vb));
-    // sqrt(v): y = rsqrt(max(v, FLT_MIN)); s = v*y; s += (v - s*s) * (y/2)
-    const f2 y = f2_pack(mufu_rsq(fmaxf(va, 1.17549435e-38f)), mufu_rsq(fmaxf(vb, 1.17549435e-38f)));
-    f2 s = f2_mul(v[j], y);
-    const f2 e = f2_fma(s, f2_mul(s, c.mone), v[j]);
-    s = f2_fma(e, f2_mul(c.half, y), s);
-    // nd = -(s / c2s + eps) * c1
-    f2 q = f2_mul(s, c.rc2s);
-    q = f2_fma(f2_fma(q, c.nc2s, s), c.rc2s, q);
-    const f2 nd = f2_mul(f2_add(q, c.eps), c.nc1);
-    // m / d: r = rcp(d) refined once, quotient corrected by its exact residual
-    float nda, ndb;
-    f2_unpack(nd, nda, ndb);
-    const f2 r0 = f2_pack(mufu_rcp(fabsf(nda)), mufu_rcp(fabsf(ndb)));
-    const f2 r = f2_fma(r0, f2_fma(nd, r0, c.one), r0);
-    const f2 qq = f2_mul(m[j], r);
-    const f2 quo = f2_fma(f2_fma(nd, qq, m[j]), r, qq);
-    po[j] = narrow2<T>(f2_fma(c.nlr, f2_fma(c.wd, pj, quo), pj));
+    po[j] = narrow2<T>(fused_pair_x2(c, gj, pj, f2_pack(m0a, m0b), f2_pack(v0a, v0b), m[j], v[j], am, av));
   }
   *pp = make_uint4(po[0], po[1], po[2], po[3]);
   am = hw_max(am, hmask);
   av = hw_max(av, hmask);
   uint32_t mo = 0, vo = 0;
   if (udiv_ok(am) && udiv_ok(av)) {
-    const float rm = rcp_nr(am), rv = rcp_nr(av);
-    const f2 rm2 = f2_splat(rm), rv2 = f2_splat(rv), nam2 = f2_splat(-am), nav2 = f2_splat(-av);
-#pragma unroll
-    for (int j = 3; j >= 0; --j) {
-      f2 xm = f2_mul(m[j], rm2);
-      xm = f2_fma(f2_fma(xm, nam2, m[j]), rm2, xm);
-      f2 xv = f2_mul(v[j], rv2);
-      xv = f2_fma(f2_fma(xv, nav2, v[j]), rv2, xv);
-      float xa, xb;
-      f2_unpack(xm, xa, xb);
-      mo = (mo << 4) + (uint32_t)lut_code(lut_m, xb);
-      mo = (mo << 4) + (uint32_t)lut_code(lut_m, xa);
-      if (VLIN) {
-        float ta, tb;
-        f2_unpack(f2_fma(xv, c.k16, c.km15), ta, tb);
-        vo = vo * 16u + __float2uint_ru(tb);
-        vo = vo * 16u + __float2uint_ru(ta);
-      } else {
-        f2_unpack(xv, xa, xb);
-        vo = (vo << 4) + (uint32_t)lut_code(lut_v, xb);
-        vo = (vo << 4) + (uint32_t)lut_code(lut_v, xa);
-      }
-    }
-    if (am == 0.0f) mo = 0xFFFFFFFFu;  // 0/0 = NaN -> code 15 for the whole group
-    if (av == 0.0f) vo = 0xFFFFFFFFu;
+    requant_x2<VLIN>(c, m, v, am, av, lut_m, lut_v, mo, vo);
   } else {  // scales outside the shared-reciprocal domain
 #pragma unroll
     for (int j = 3; j >= 0; --j) {
@@ -382,7 +312,7 @@ adamw4bit_half_kernel(const __grid_constant__ Table tab, const float* __restrict
     lut_build(Sm, lut_m, qmap_m);
     tables_ok = Sm.valid && Sv.valid;
   }
-  const HConsts2 k2 = make_hconsts2(c);
+  const Consts2 k2 = make_consts_x2(c.f_beta1, c.f_beta2, c.f_omb1, c.f_omb2, c.f_lr, c.f_wd, c.f_eps, c.c1, c.c2s, c.rc2s);
   const int l16 = threadIdx.x & 15;
   const unsigned hmask = 0xFFFFu << (threadIdx.x & 16);
   long long gi = gbeg + (long long)blockIdx.x * HW_PER_CTA + (threadIdx.x >> 4);
