@@ -16,6 +16,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "fused_x2.cuh"
 #include "multi_tensor.cuh"
 #include "unfused_math.cuh"
 
@@ -154,11 +155,10 @@ __global__ void __launch_bounds__(R1T) r1_stats_kernel(const R1Desc* __restrict_
 
 // One 128-element unit of one matrix.  FULL lanes (8 elements inside one row, 16-byte aligned, short
 // exact sequences applicable) use packed arithmetic; every other lane takes the scalar IEEE path.
-// A (the fused kernel's arithmetic): FULL lanes keep the vector accesses and the quick requantisation
-// but update element by element.
+// A: the fused kernel's arithmetic (packed for FULL lanes as well, fused_x2.cuh).
 template <bool A>
 __device__ __forceinline__ void r1_unit(const R1Desc& t, long long u, int l16, unsigned hmask, const UConsts& c,
-                                        const UConsts2& c2, const QMapSmem& Sm, const QMapSmem& Sv,
+                                        const UConsts2& c2, const Consts2& kf, const QMapSmem& Sm, const QMapSmem& Sv,
                                         const LutEnt* __restrict__ lut_m, bool lut_ok) {
   const long long n = t.n, C = t.C;
   const long long e0 = u * 128 + l16 * 8;
@@ -203,20 +203,15 @@ __device__ __forceinline__ void r1_unit(const R1Desc& t, long long u, int l16, u
     if (A) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        float ga, gb, pa, pb;
-        f2_unpack(g.v[j], ga, gb);
-        f2_unpack(p.v[j], pa, pb);
-        const float gg[2] = {ga, gb}, pp[2] = {pa, pb};
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const int k = 2 * j + h;
-          const float m0 = __fmul_rn(Sm.qmap[(mcodes >> (4 * k)) & 15u], sm);
-          const float v0 = __fmul_rn(Sv.qmap[(vcodes >> (4 * k)) & 15u], st_old[k]);
-          m[k] = lerp_m<true>(c, m0, gg[h]);
-          v[k] = upd_v2<true>(c, v0, gg[h]);
-          px[k] = upd_param<true>(c, pp[h], m[k], v[k]);
-          am = fmaxf(am, fabsf(m[k]));
-        }
+        const int k0 = 2 * j, k1 = 2 * j + 1;
+        const f2 m0 = f2_mul(f2_pack(Sm.qmap[(mcodes >> (4 * k0)) & 15u], Sm.qmap[(mcodes >> (4 * k1)) & 15u]), sm2);
+        const f2 v0 = f2_mul(f2_pack(Sv.qmap[(vcodes >> (4 * k0)) & 15u], Sv.qmap[(vcodes >> (4 * k1)) & 15u]),
+                             f2_pack(st_old[k0], st_old[k1]));
+        f2 mj, vj;
+        const f2 pj = fused_pair_x2(kf, g.v[j], p.v[j], m0, v0, mj, vj, am, av);
+        f2_unpack(mj, m[k0], m[k1]);
+        f2_unpack(vj, v[k0], v[k1]);
+        f2_unpack(pj, px[k0], px[k1]);
       }
     } else {
 #pragma unroll
@@ -329,6 +324,7 @@ __global__ void __launch_bounds__(R1T, 4) r1_update_kernel(const R1Desc* __restr
   lut_build(Sm, lut_m, qmap_m);
   const bool lut_ok = Sm.valid != 0;
   const UConsts2 c2 = make_consts2(c);
+  const Consts2 kf = make_consts_x2(c.f_beta1, c.f_beta2, c.f_omb1, c.f_omb2, c.f_lr, c.f_wd, c.f_eps, c.c1, c.c2s, c.rc2s);
   const int l16 = threadIdx.x & 15;
   const unsigned hmask = 0xFFFFu << (threadIdx.x & 16);
   long long gi = (long long)blockIdx.x * (R1T / 16) + (threadIdx.x >> 4);
@@ -337,7 +333,7 @@ __global__ void __launch_bounds__(R1T, 4) r1_update_kernel(const R1Desc* __restr
   for (int ti = 0; ti < n; ++ti) {
     const R1Desc& t = d[ti];
     const long long uend = (ti + 1 < n) ? d[ti + 1].ustart : total_units;
-    for (; gi < uend; gi += stride) r1_unit<A>(t, gi - t.ustart, l16, hmask, c, c2, Sm, Sv, lut_m, lut_ok);
+    for (; gi < uend; gi += stride) r1_unit<A>(t, gi - t.ustart, l16, hmask, c, c2, kf, Sm, Sv, lut_m, lut_ok);
   }
 }
 
