@@ -14,8 +14,9 @@ own arm      one step = ``lpmm.optim.AdamW(fused=True).step()`` over the whole l
              and a device->host read of a result inside the timed region.  With N > 1 the list is
              ZeRO-1 sharded by whole 128-element groups and the timed step ends with the NCCL
              all-gather of the updated parameters.
-reference    the CPU restatement of the reference's kernel (the C oracle, all host threads) on a
-arm          bounded sample of the same list, rank 0 only.
+reference    the reference's own Python CPU path (``lpmm.optim.AdamW`` unchanged, group-128 4-bit states, its
+arm          CUDA pack/unpack extension replaced by a C restatement) with all host threads on a bounded
+             sample of the same list, rank 0 only; the C port of the fused kernel when that Python is absent.
 """
 import argparse
 import json
@@ -138,11 +139,23 @@ def student_t_(out, seed, rows_outliers=True):
 
 
 # --------------------------------------------------------------------------------------------------
-# reference arm / CPU baseline: the C oracle on a bounded sample of the list
+# reference arm / CPU baseline: the reference's own Python CPU path (or, without it, the C port) on a
+# bounded sample of the list
 # --------------------------------------------------------------------------------------------------
 def cpu_sample_shapes():
-    """One transformer layer of the list: 202 383 360 parameters."""
+    """One transformer layer of the list: 202 383 360 parameters (the sample of the C port)."""
     return llama7b_shapes()[1:10]
+
+
+def python_sample_shapes():
+    """The sample of the reference's Python path, which is an order of magnitude slower than the C port: one
+    attention projection, one MLP projection and one norm vector of a layer, 61 870 080 parameters."""
+    return [(4096, 4096), (11008, 4096), (4096,)]
+
+
+def host_threads():
+    """Every host thread this process may run on (torchrun exports OMP_NUM_THREADS=1: not that)."""
+    return len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
 
 
 def time_cpu_oracle(steps, warmup, sample_shapes, threads=None):
@@ -150,9 +163,7 @@ def time_cpu_oracle(steps, warmup, sample_shapes, threads=None):
     from oracle import cpu as O
     z = np.load(os.path.join(ROOT, "tests", "golden", "qmaps.npz"))
     qm, qv = z["m"], z["v"]
-    if not threads:  # every host thread this process may run on (torchrun exports OMP_NUM_THREADS=1: not that)
-        threads = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
-    O.set_threads(threads)
+    O.set_threads(threads or host_threads())
     rng = np.random.default_rng(0)
     tensors = []
     for s in sample_shapes:
@@ -183,21 +194,108 @@ def time_cpu_oracle(steps, warmup, sample_shapes, threads=None):
     return total / sec, sec, O.threads(), total
 
 
+def reference_python_root():
+    """Where the reference's own Python layer can be imported from on this machine: the copy that
+    ``oracle/build_ref.py`` leaves under the git-ignored ``oracle/_ref/lpmm_py`` (it travels with the tree), else
+    a reference checkout.  None: not available."""
+    from oracle import build_ref
+    if build_ref.have_python():
+        return build_ref.PY_OUT
+    return build_ref.reference_root()
+
+
+def time_reference_python(steps, warmup, sample_shapes, ref_root, threads=None):
+    """The reference's own ``lpmm.optim.AdamW`` (its Python, unchanged) on CPU tensors: ``qconfig=None``, i.e. both
+    moments 4-bit with group-128 scales like the fused step, non-fused arithmetic (the reference has no CPU form
+    of its fused kernel).  Its CUDA pack / unpack extension is replaced by the C oracle's CPU restatement of those
+    two functions (``oracle/ref_loader.py``); everything else is the reference's torch code on the host cores.
+    Must run in a process that has not imported this repository's package of the same name."""
+    import contextlib
+    import io
+    import tempfile
+    import torch
+    from oracle import cpu as O
+    from oracle.ref_loader import load_reference
+    threads = threads or host_threads()
+    torch.set_num_threads(threads)
+    O.set_threads(threads)
+    cwd = os.getcwd()
+    os.chdir(tempfile.mkdtemp())  # the reference writes ./lpmm_config.txt on construction
+    try:
+        ref = load_reference(ref_root)
+        torch.manual_seed(0)
+        params = [torch.nn.Parameter(torch.empty(s).normal_(0, 0.02)) for s in sample_shapes]
+        gen = torch.Generator().manual_seed(1)
+        for p in params:
+            z = torch.randn((4,) + tuple(p.shape), generator=gen)
+            p.grad = z[0] / torch.sqrt((z[1] ** 2 + z[2] ** 2 + z[3] ** 2) / 3.0) * 1e-3
+            del z
+        with contextlib.redirect_stdout(io.StringIO()):
+            opt = ref.optim.AdamW(params, qconfig=None, fused=False, **HYPER)
+        times = []
+        for it in range(warmup + steps):
+            t0 = time.perf_counter()
+            opt.step()
+            dt = time.perf_counter() - t0
+            if it >= warmup:
+                times.append(dt)
+    finally:
+        os.chdir(cwd)
+    total = sum(numel(s) for s in sample_shapes)
+    sec = sum(times) / len(times)
+    return total / sec, sec, threads, total
+
+
+def reference_measurement(steps, warmup):
+    """(value, seconds per step, cpu_baseline dict): the reference's Python when it is importable here, else the
+    C port."""
+    root = reference_python_root()
+    if root is not None:
+        value, sec, threads, total = time_reference_python(steps, warmup, python_sample_shapes(), root)
+        desc = (f"a 4096x4096 and an 11008x4096 projection and a 4096 norm vector of the list ({total} params) per step; the "
+                f"reference's own Python (lpmm.optim.AdamW, qconfig=None, fused=False) on CPU tensors, torch with {threads} "
+                f"threads, its CUDA pack/unpack extension replaced by a C restatement of those two functions")
+        kind = "reference-python"
+    else:
+        value, sec, threads, total = time_cpu_oracle(steps, warmup, cpu_sample_shapes())
+        desc = f"one transformer layer of the list ({total} params) per step, C restatement of the reference kernel, OpenMP"
+        kind = "port"
+    return value, sec, {"value": value, "unit": UNIT, "cores": threads, "kind": kind, "sample": desc}
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    sample = cpu_sample_shapes()
-    value, sec, threads, total = time_cpu_oracle(args.steps, args.warmup, sample)
-    desc = f"one transformer layer of the list ({total} params) per step, C restatement of the reference kernel, OpenMP"
+    value, sec, cpu = reference_measurement(args.steps, args.warmup)
+    if cpu["kind"] == "reference-python" and not args.no_port:
+        # the faster C port of the fused kernel beside it, for scale
+        v2, _, th2, tot2 = time_cpu_oracle(2, 1, cpu_sample_shapes())
+        cpu["c_port_of_the_fused_kernel"] = {"value": v2, "unit": UNIT, "cores": th2, "kind": "port",
+                                             "sample": f"one transformer layer ({tot2} params), OpenMP"}
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong" if args.gpus > 1 else "weak",
+        "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "llama7b_shaped_fp32_list_fused_4bit_adamw", "sample": desc},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc},
+        "config": {"workload": "llama7b_shaped_fp32_list_fused_4bit_adamw", "sample": cpu["sample"]},
+        "cpu_baseline": cpu,
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }), flush=True)
+
+
+def cpu_baseline_in_subprocess(steps=2, warmup=1):
+    """The ``cpu_baseline`` leg of the own arm: the reference's package has the same name as this repository's, so
+    it is timed in a child process (``bench.py --impl reference``) and its JSON line is read back."""
+    env = dict(os.environ)
+    for k in ("RANK", "LOCAL_RANK", "WORLD_SIZE"):
+        env.pop(k, None)
+    env.pop("OMP_NUM_THREADS", None)
+    res = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "reference", "--steps", str(steps), "--warmup",
+                          str(warmup)], capture_output=True, text=True, env=env, timeout=900)
+    for line in reversed(res.stdout.strip().splitlines()):
+        if line.startswith("{"):
+            return json.loads(line)["cpu_baseline"]
+    raise RuntimeError("the reference arm printed no JSON line: " + res.stderr[-500:])
 
 
 # --------------------------------------------------------------------------------------------------
@@ -311,6 +409,29 @@ def run_own(args):
                 "kernel": "adamw4bit_multi_kernel", "algorithmic_bytes_per_launch": k_bytes, "launch_ms": k_ms}
     if world == 1:
         roofline["launch_ms_min_max"] = [min(ks), max(ks)]
+        # the tolerance mode of the same step (moments, scales and codes bit-identical; parameters within 1e-6
+        # relative): same list, same states continued, timed the same way
+        opt._exact_params = False
+        for _ in range(max(3, args.warmup)):
+            step()
+        torch.cuda.synchronize()
+        tm = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+        tm[0].record()
+        for i in range(args.steps):
+            step()
+            tm[i + 1].record()
+        torch.cuda.synchronize()
+        opt._exact_params = True
+        tks = [a.elapsed_time(b) for a, b in zip(tm[:-1], tm[1:])]
+        t_ms = sum(tks) / len(tks)
+        t_ach = alg_bytes / (t_ms * 1e-3) / 1e9
+        extra["tolerance_mode"] = {
+            "what": "AdamW(fused=True, exact_params=False): codes and scales bit-identical, parameters within 1e-6 relative",
+            "ms_per_step": t_ms, "value": total / (t_ms * 1e-3), "unit": UNIT,
+            "roofline": {"bound": "hbm", "achieved": t_ach, "peak": peak, "unit": "GB/s", "frac": t_ach / peak,
+                         "peak_kind": f"of {peak_kind}", "launch_ms": t_ms, "launch_ms_min_max": [min(tks), max(tks)],
+                         "frac_of_nominal_8000": t_ach / 8000.0}}
+        roofline["frac_of_nominal_8000"] = achieved / 8000.0
     if world > 1 and args.gather == "fused":
         # fused update + peer stores: the target time is the slower of HBM and NVLink; this kernel is NVLink-bound
         link_bytes = 4.0 * opt.shard_groups * 128 * (world - 1)      # sent (and received) per rank per launch
@@ -397,11 +518,8 @@ def run_own(args):
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        sample = cpu_sample_shapes()
-        v, sec, threads, tot = time_cpu_oracle(2, 1, sample)
-        cpu = {"value": v, "unit": UNIT, "cores": threads, "kind": "port",
-               "sample": f"one transformer layer of the list ({tot} params), 2 timed steps after 1 warm-up, C restatement "
-                         f"of the reference kernel with OpenMP"}
+        cpu = cpu_baseline_in_subprocess(2, 1)
+        cpu["sample"] += "; 2 timed steps after 1 warm-up"
     if rank == 0:
         out = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -432,6 +550,7 @@ def main():
     ap.add_argument("--model", default="7b", choices=["7b", "13b"],
                     help="7b: the headline list; 13b: the LLaMA-13B-shaped list (52 GB of fp32 parameters per GPU)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-port", action="store_true", help="reference arm: skip the extra timing of the C port")
     ap.add_argument("--reduce-grads", action="store_true",
                     help="N > 1, --gather fused: every rank holds full local gradients and the update kernel also sums "
                          "them over the ranks (reduce-scatter inside the step); no e2e figure in this mode")

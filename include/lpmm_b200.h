@@ -108,6 +108,20 @@ int lpmm_b200_adamw4bit_multi_tensor(const lpmm_b200_tensor* tensors, int n_tens
                                      const float* exp_avg_sq_qmap, lpmm_b200_hyper hyper, int64_t group_begin,
                                      int64_t group_end, void* stream);
 
+/* Options of the fused step (the ..._flags entry points; 0 = the behaviour of the plain ones).
+ *
+ * LPMM_B200_FLAG_PARAMS_WITHIN_TOLERANCE: moments, group maxima and packed codes are computed exactly as without
+ * the flag (they never depend on the parameter: fused_adamw_kernel.cu:120-124,146-162), but the parameter
+ * update p -= lr * (m / ((sqrt(v)/c2s + eps) * c1) + wd * p) (fused_adamw_kernel.cu:126-128) uses the GPU's
+ * approximate square root and reciprocal (2^-23 relative each) with lr, c1 and c2s folded into constants,
+ * instead of correctly rounded operations.  A step lr*m/d then differs from the reference's by less than 1e-6
+ * of its own size, a parameter by a few 1e-10 per step at lr = 1e-3.  Full, aligned 4-bit groups take it;
+ * ragged groups, fp32-state tensors and hyper-parameters outside lr in [2^-60, 2^30] keep the exact update. */
+#define LPMM_B200_FLAG_PARAMS_WITHIN_TOLERANCE 1u
+int lpmm_b200_adamw4bit_multi_tensor_flags(const lpmm_b200_tensor* tensors, int n_tensors, const float* exp_avg_qmap,
+                                           const float* exp_avg_sq_qmap, lpmm_b200_hyper hyper, int64_t group_begin,
+                                           int64_t group_end, uint32_t flags, void* stream);
+
 /* The fused step for 16-bit parameters and gradients: `p` and `g` of every tensor point to bf16 or fp16
  * arrays (dtype = LPMM_B200_DTYPE_*; the struct's float* is reinterpreted), everything else is as in
  * lpmm_b200_adamw4bit_multi_tensor: 4-bit codes, fp32 scales, fp32 moments for kind FP32.
@@ -118,6 +132,11 @@ int lpmm_b200_adamw4bit_multi_tensor(const lpmm_b200_tensor* tensors, int n_tens
 int lpmm_b200_adamw4bit_multi_tensor_16bit(const lpmm_b200_tensor* tensors, int n_tensors, int dtype,
                                            const float* exp_avg_qmap, const float* exp_avg_sq_qmap,
                                            lpmm_b200_hyper hyper, int64_t group_begin, int64_t group_end, void* stream);
+
+int lpmm_b200_adamw4bit_multi_tensor_16bit_flags(const lpmm_b200_tensor* tensors, int n_tensors, int dtype,
+                                                 const float* exp_avg_qmap, const float* exp_avg_sq_qmap,
+                                                 lpmm_b200_hyper hyper, int64_t group_begin, int64_t group_end,
+                                                 uint32_t flags, void* stream);
 
 /* The same step for a ZeRO-1 rank, with the all-gather of the updated parameters folded into the
  * kernel.  It has no counterpart in the reference (which has no distributed step).
@@ -130,6 +149,12 @@ int lpmm_b200_adamw4bit_multi_tensor_peers(const lpmm_b200_tensor* tensors, int 
                                            const float* exp_avg_sq_qmap, lpmm_b200_hyper hyper, int64_t group_begin,
                                            int64_t group_end, const int64_t* peer_byte_offsets, int n_peers,
                                            void* stream);
+
+int lpmm_b200_adamw4bit_multi_tensor_peers_flags(const lpmm_b200_tensor* tensors, int n_tensors,
+                                                 const float* exp_avg_qmap, const float* exp_avg_sq_qmap,
+                                                 lpmm_b200_hyper hyper, int64_t group_begin, int64_t group_end,
+                                                 const int64_t* peer_byte_offsets, int n_peers, uint32_t flags,
+                                                 void* stream);
 
 /* The whole ZeRO-1 step in one kernel: additionally to the above, the gradient of every element of
  * this rank's range is the sum, in the order given, of the values found at the n_grads (<= 8) byte
@@ -399,6 +424,20 @@ int lpmm_b200_sgd4bit_multi_tensor(const lpmm_b200_tensor* tensors, int n_tensor
 int lpmm_b200_adamw4bit_factored_step_noalloc(const lpmm_b200_step_tensor* t, const float* qmap_m, double beta1,
                                               double beta2, double lr, double weight_decay, double eps, double step,
                                               void* stream);
+
+/* Self-test hook (no counterpart in the reference; not part of any step).  The step kernels replace IEEE
+ * division and square root and the reference's nearest-code search (fused_adamw_kernel.cu:27-49) by shorter
+ * sequences that give the same result on a stated domain.  This runs one of those comparisons on the GPU over
+ * n_samples pseudo-random and adversarial operands (seeded) and writes to out[0] the number of mismatches and to
+ * out[1] the number of operands inside the domain (out: device pointer to two 64-bit counters, zeroed here).
+ *   check 0  x / d by the shared reciprocal with residual correction  vs  div.rn   (2^-60 <= d <= 2^60, |x| <= d)
+ *   check 1  the code of x / d (table, or closed form for the map k/16) vs the search on div.rn's quotient
+ *   check 2  the short square root  vs  sqrt.rn    (v >= 2^-102 or v == 0)
+ *   check 3  the short division     vs  div.rn     (2^-60 <= d <= 2^60, 2^-60 <= |m| <= 2^30 or m == 0)
+ *   check 4  the code of an arbitrary float (table / closed form)  vs  the search
+ * qmap (16 floats, device) selects the map of checks 1 and 4. */
+int lpmm_b200_test_exactness(int check, const float* qmap, uint64_t seed, int64_t n_samples, unsigned long long* out,
+                             void* stream);
 
 #ifdef __cplusplus
 }

@@ -259,7 +259,8 @@ __device__ __forceinline__ void group_q4_fast(const LanePtrs& t, unsigned gl, in
 // every multiply / add / fma, each half rounding exactly like the scalar instruction, so results
 // are bit-identical to group_q4_fast<true, VLIN>.  Uses the short sqrt/division sequences, so it is
 // selected only where those are (FAST).
-template <bool VLIN, bool PEERS>
+// APX: the tolerance mode of the parameter update (fused_x2.cuh); moments, maxima and codes unchanged.
+template <bool VLIN, bool PEERS, bool APX>
 __device__ __forceinline__ void group_q4_x2(const LanePtrs& t, unsigned gl, int l16, unsigned hmask,
                                             const Consts2& c, const QMapSmem& Sm, const QMapSmem& Sv,
                                             const LutEnt* __restrict__ lut_m, const LutEnt* __restrict__ lut_v,
@@ -288,7 +289,7 @@ __device__ __forceinline__ void group_q4_x2(const LanePtrs& t, unsigned gl, int 
     const float m0b = __shfl_sync(hmask, pm, (int)(mc >> (8 * j + 4)), 16);
     const float v0a = __shfl_sync(hmask, pv, (int)(vc >> (8 * j)), 16);
     const float v0b = __shfl_sync(hmask, pv, (int)(vc >> (8 * j + 4)), 16);
-    p.v[j] = fused_pair_x2(c, g.v[j], p.v[j], f2_pack(m0a, m0b), f2_pack(v0a, v0b), m[j], v[j], am, av);
+    p.v[j] = fused_pair_x2<APX>(c, g.v[j], p.v[j], f2_pack(m0a, m0b), f2_pack(v0a, v0b), m[j], v[j], am, av);
   }
   stg_f2x4(pp, p);
   if (PEERS) {
@@ -360,10 +361,13 @@ __device__ __forceinline__ void group_fp32(const TDesc& t, long long gl, int l16
 // The tensor loop is uniform across the CTA (descriptor fields come from the launch parameters
 // through uniform loads); each half-warp walks its own arithmetic progression of global group
 // indices gi = gbeg + id, gbeg + id + stride, ... through the tensors in order.
-template <bool FAST, bool VLIN, bool PEERS>
+// MATH: 0 = IEEE sqrt / division, 1 = the short exact sequences (same results), 2 = as 1 with the tolerance-mode
+// parameter update on full aligned 4-bit groups.
+template <int MATH, bool VLIN, bool PEERS>
 __device__ __forceinline__ void run_groups(const Table& tab, const Consts& c, const QMapSmem& Sm,
                                            const QMapSmem& Sv, const LutEnt* lut_m, const LutEnt* lut_v,
                                            bool tables_ok, long long gbeg, long long gend, const PeerInfo& pi) {
+  constexpr bool FAST = MATH >= 1;
   const int l16 = threadIdx.x & 15;
   const unsigned hmask = 0xFFFFu << (threadIdx.x & 16);
   long long gi = gbeg + (long long)blockIdx.x * HW_PER_CTA + (threadIdx.x >> 4);
@@ -395,7 +399,7 @@ __device__ __forceinline__ void run_groups(const Table& tab, const Consts& c, co
           if (FAST) {
             const Consts2 c2 = make_consts_x2(c.beta1, c.beta2, c.omb1, c.omb2, c.lr, c.wd, c.eps, c.c1, c.c2s, c.rc2s);
             for (; gl < lim; gl += st)
-              group_q4_x2<VLIN, PEERS>(lp, gl, l16, hmask, c2, Sm, Sv, lut_m, lut_v, qm_l, qv_l,
+              group_q4_x2<VLIN, PEERS, MATH == 2>(lp, gl, l16, hmask, c2, Sm, Sv, lut_m, lut_v, qm_l, qv_l,
                                        (gl + PF_DIST * st < lim) ? PF_DIST * st : 0u, pi);
           } else {
             for (; gl < lim; gl += st)
@@ -412,7 +416,7 @@ __device__ __forceinline__ void run_groups(const Table& tab, const Consts& c, co
   }
 }
 
-template <bool HAS_Q4, bool FAST, bool PEERS>
+template <bool HAS_Q4, int MATH, bool PEERS>
 __global__ void __launch_bounds__(CTA_THREADS, CTAS_PER_SM)
 adamw4bit_multi_kernel(const __grid_constant__ Table tab, const float* __restrict__ qmap_m,
                        const float* __restrict__ qmap_v, const lpmm_b200_hyper h, long long gbeg, long long gend,
@@ -440,8 +444,8 @@ adamw4bit_multi_kernel(const __grid_constant__ Table tab, const float* __restric
   c.c1 = __fsub_rn(1.0f, powf(h.beta1, h.step));
   c.c2s = __fsqrt_rn(__fsub_rn(1.0f, powf(h.beta2, h.step)));
   c.rc2s = __frcp_rn(c.c2s);
-  if (vlin) run_groups<FAST, true, PEERS>(tab, c, Sm, Sv, lut_m, lut_v, tables_ok, gbeg, gend, pi);
-  else run_groups<FAST, false, PEERS>(tab, c, Sm, Sv, lut_m, lut_v, tables_ok, gbeg, gend, pi);
+  if (vlin) run_groups<MATH, true, PEERS>(tab, c, Sm, Sv, lut_m, lut_v, tables_ok, gbeg, gend, pi);
+  else run_groups<MATH, false, PEERS>(tab, c, Sm, Sv, lut_m, lut_v, tables_ok, gbeg, gend, pi);
 }
 
 __global__ void bias_corrections_kernel(float beta1, float beta2, float step, float* out) {
@@ -457,8 +461,12 @@ static bool fast_math_ok(const lpmm_b200_hyper& h) {
   const double c2s_min = sqrt(1.0 - (double)h.beta2);
   return dmin >= 0x1p-50 && h.eps <= 0x1p30f && c2s_min >= 0x1p-20;
 }
+// The tolerance-mode parameter update folds 1 / -lr into its constants.
+static bool approx_math_ok(const lpmm_b200_hyper& h) {
+  return fast_math_ok(h) && h.lr >= 0x1p-60f && h.lr <= 0x1p30f && h.weight_decay <= 0x1p30f;
+}
 
-template <bool HAS_Q4, bool FAST, bool PEERS>
+template <bool HAS_Q4, int MATH, bool PEERS>
 static cudaError_t launch_one(const Table& tab, unsigned grid, const float* qm, const float* qv,
                               const lpmm_b200_hyper& h, long long lo, long long hi, cudaStream_t st,
                               const PeerInfo& pi) {
@@ -467,30 +475,31 @@ static cudaError_t launch_one(const Table& tab, unsigned grid, const float* qm, 
   cudaGetDevice(&dev);
   const size_t smem = HAS_Q4 ? DYN_SMEM : 0;
   if (HAS_Q4 && dev >= 0 && dev < 64 && !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(adamw4bit_multi_kernel<HAS_Q4, FAST, PEERS>,
+    cudaError_t e = cudaFuncSetAttribute(adamw4bit_multi_kernel<HAS_Q4, MATH, PEERS>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DYN_SMEM);
     if (e != cudaSuccess) return e;
     attr_set[dev] = true;
   }
-  adamw4bit_multi_kernel<HAS_Q4, FAST, PEERS><<<grid, CTA_THREADS, smem, st>>>(tab, qm, qv, h, lo, hi, pi);
+  adamw4bit_multi_kernel<HAS_Q4, MATH, PEERS><<<grid, CTA_THREADS, smem, st>>>(tab, qm, qv, h, lo, hi, pi);
   return cudaGetLastError();
 }
 
 template <bool HAS_Q4, bool PEERS>
-static cudaError_t launch_fast_or_exact(bool fast, const Table& tab, unsigned grid, const float* qm, const float* qv,
+static cudaError_t launch_fast_or_exact(int math, const Table& tab, unsigned grid, const float* qm, const float* qv,
                                         const lpmm_b200_hyper& h, long long lo, long long hi, cudaStream_t st,
                                         const PeerInfo& pi) {
-  return fast ? launch_one<HAS_Q4, true, PEERS>(tab, grid, qm, qv, h, lo, hi, st, pi)
-              : launch_one<HAS_Q4, false, PEERS>(tab, grid, qm, qv, h, lo, hi, st, pi);
+  if (math == 2 && HAS_Q4) return launch_one<HAS_Q4, HAS_Q4 ? 2 : 1, PEERS>(tab, grid, qm, qv, h, lo, hi, st, pi);
+  return math ? launch_one<HAS_Q4, 1, PEERS>(tab, grid, qm, qv, h, lo, hi, st, pi)
+              : launch_one<HAS_Q4, 0, PEERS>(tab, grid, qm, qv, h, lo, hi, st, pi);
 }
 
 static int launch_multi(const lpmm_b200_tensor* ts, int n, const float* qm, const float* qv,
                         const lpmm_b200_hyper& h, int64_t gbeg, int64_t gend, cudaStream_t st,
-                        const PeerInfo& pi = PeerInfo{}) {
+                        const PeerInfo& pi = PeerInfo{}, uint32_t flags = 0) {
   // `ts` may hold more than MAX_TENSORS entries: walk it in windows, each window one launch over
   // the part of [gbeg, gend) that falls inside it.
   static thread_local Table tab;  // 28.9 KB; copied into the launch parameters by the runtime
-  const bool fast = fast_math_ok(h);
+  const int fast = ((flags & LPMM_B200_FLAG_PARAMS_WITHIN_TOLERANCE) && approx_math_ok(h)) ? 2 : (fast_math_ok(h) ? 1 : 0);
   int64_t gcursor = 0;
   int i = 0;
   while (i < n) {
@@ -533,18 +542,37 @@ extern "C" int64_t lpmm_b200_count_groups(const lpmm_b200_tensor* tensors, int n
   return g;
 }
 
+// Range checks shared by the list entry points; on success *run tells whether anything is to be launched.
+static int check_range(const lpmm_b200_tensor* tensors, int n_tensors, const float* qm, const float* qv,
+                       int64_t group_begin, int64_t* group_end, uint32_t flags, bool* run) {
+  *run = false;
+  if (flags & ~(uint32_t)LPMM_B200_FLAG_PARAMS_WITHIN_TOLERANCE) return LPMM_B200_ERR_BAD_KIND;
+  int rc = check_list(tensors, n_tensors, false, qm, qv);
+  if (rc != LPMM_B200_OK) return rc;
+  const int64_t total = lpmm_b200_count_groups(tensors, n_tensors);
+  if (*group_end < 0) *group_end = total;
+  if (group_begin < 0 || group_begin > *group_end || *group_end > total) return LPMM_B200_ERR_BAD_SIZE;
+  *run = group_begin != *group_end;
+  return LPMM_B200_OK;
+}
+
+extern "C" int lpmm_b200_adamw4bit_multi_tensor_flags(const lpmm_b200_tensor* tensors, int n_tensors,
+                                                      const float* exp_avg_qmap, const float* exp_avg_sq_qmap,
+                                                      lpmm_b200_hyper hyper, int64_t group_begin, int64_t group_end,
+                                                      uint32_t flags, void* stream) {
+  bool run;
+  const int rc = check_range(tensors, n_tensors, exp_avg_qmap, exp_avg_sq_qmap, group_begin, &group_end, flags, &run);
+  if (rc != LPMM_B200_OK || !run) return rc;
+  return launch_multi(tensors, n_tensors, exp_avg_qmap, exp_avg_sq_qmap, hyper, group_begin, group_end,
+                      (cudaStream_t)stream, PeerInfo{}, flags);
+}
+
 extern "C" int lpmm_b200_adamw4bit_multi_tensor(const lpmm_b200_tensor* tensors, int n_tensors,
                                                 const float* exp_avg_qmap, const float* exp_avg_sq_qmap,
                                                 lpmm_b200_hyper hyper, int64_t group_begin, int64_t group_end,
                                                 void* stream) {
-  int rc = check_list(tensors, n_tensors, false, exp_avg_qmap, exp_avg_sq_qmap);
-  if (rc != LPMM_B200_OK) return rc;
-  const int64_t total = lpmm_b200_count_groups(tensors, n_tensors);
-  if (group_end < 0) group_end = total;
-  if (group_begin < 0 || group_begin > group_end || group_end > total) return LPMM_B200_ERR_BAD_SIZE;
-  if (group_begin == group_end) return LPMM_B200_OK;
-  return launch_multi(tensors, n_tensors, exp_avg_qmap, exp_avg_sq_qmap, hyper, group_begin, group_end,
-                      (cudaStream_t)stream);
+  return lpmm_b200_adamw4bit_multi_tensor_flags(tensors, n_tensors, exp_avg_qmap, exp_avg_sq_qmap, hyper, group_begin,
+                                                group_end, 0u, stream);
 }
 
 extern "C" int lpmm_b200_adamw4bit_single_tensor(float* p, const float* g, int8_t* exp_avg, int8_t* exp_avg_sq,
@@ -596,18 +624,16 @@ extern "C" int lpmm_b200_bias_corrections(float beta1, float beta2, float step, 
   return LPMM_B200_OK;
 }
 
-extern "C" int lpmm_b200_adamw4bit_multi_tensor_peers(const lpmm_b200_tensor* tensors, int n_tensors,
-                                                      const float* exp_avg_qmap, const float* exp_avg_sq_qmap,
-                                                      lpmm_b200_hyper hyper, int64_t group_begin, int64_t group_end,
-                                                      const int64_t* peer_byte_offsets, int n_peers, void* stream) {
+extern "C" int lpmm_b200_adamw4bit_multi_tensor_peers_flags(const lpmm_b200_tensor* tensors, int n_tensors,
+                                                            const float* exp_avg_qmap, const float* exp_avg_sq_qmap,
+                                                            lpmm_b200_hyper hyper, int64_t group_begin,
+                                                            int64_t group_end, const int64_t* peer_byte_offsets,
+                                                            int n_peers, uint32_t flags, void* stream) {
   if (n_peers < 0 || n_peers > 7) return LPMM_B200_ERR_BAD_SIZE;
   if (n_peers > 0 && !peer_byte_offsets) return LPMM_B200_ERR_NULL_POINTER;
-  int rc = check_list(tensors, n_tensors, false, exp_avg_qmap, exp_avg_sq_qmap);
-  if (rc != LPMM_B200_OK) return rc;
-  const int64_t total = lpmm_b200_count_groups(tensors, n_tensors);
-  if (group_end < 0) group_end = total;
-  if (group_begin < 0 || group_begin > group_end || group_end > total) return LPMM_B200_ERR_BAD_SIZE;
-  if (group_begin == group_end) return LPMM_B200_OK;
+  bool run;
+  const int rc = check_range(tensors, n_tensors, exp_avg_qmap, exp_avg_sq_qmap, group_begin, &group_end, flags, &run);
+  if (rc != LPMM_B200_OK || !run) return rc;
   PeerInfo pi = {};
   pi.n = n_peers;
   for (int i = 0; i < n_peers; ++i) {
@@ -615,7 +641,15 @@ extern "C" int lpmm_b200_adamw4bit_multi_tensor_peers(const lpmm_b200_tensor* te
     pi.off[i] = peer_byte_offsets[i];
   }
   return launch_multi(tensors, n_tensors, exp_avg_qmap, exp_avg_sq_qmap, hyper, group_begin, group_end,
-                      (cudaStream_t)stream, pi);
+                      (cudaStream_t)stream, pi, flags);
+}
+
+extern "C" int lpmm_b200_adamw4bit_multi_tensor_peers(const lpmm_b200_tensor* tensors, int n_tensors,
+                                                      const float* exp_avg_qmap, const float* exp_avg_sq_qmap,
+                                                      lpmm_b200_hyper hyper, int64_t group_begin, int64_t group_end,
+                                                      const int64_t* peer_byte_offsets, int n_peers, void* stream) {
+  return lpmm_b200_adamw4bit_multi_tensor_peers_flags(tensors, n_tensors, exp_avg_qmap, exp_avg_sq_qmap, hyper,
+                                                      group_begin, group_end, peer_byte_offsets, n_peers, 0u, stream);
 }
 
 extern "C" int lpmm_b200_adamw4bit_multi_tensor_zero1(const lpmm_b200_tensor* tensors, int n_tensors,

@@ -89,7 +89,8 @@ __device__ __forceinline__ unsigned narrow2<__half>(f2 x) {
 // One full, aligned 4-bit group with packed fp32x2 instructions: elements (2j, 2j+1) share every
 // multiply / add / fma, each half rounding like the scalar instruction, so the results are those of
 // h_group_fast with the short sqrt / division sequences (selected only where those apply).
-template <typename T, bool VLIN>
+// APX: the tolerance mode of the parameter update (fused_x2.cuh); moments, maxima and codes unchanged.
+template <typename T, bool VLIN, bool APX>
 __device__ __forceinline__ void h_group_x2(const TDesc& t, unsigned gl, int l16, unsigned hmask, const Consts2& c,
                                            const QMapSmem& Sm, const QMapSmem& Sv, const LutEnt* __restrict__ lut_m,
                                            const LutEnt* __restrict__ lut_v, float qm_l, float qv_l, unsigned pf) {
@@ -122,7 +123,7 @@ __device__ __forceinline__ void h_group_x2(const TDesc& t, unsigned gl, int l16,
     const float v0b = __shfl_sync(hmask, pv, (int)(vc >> (8 * j + 4)), 16);
     const f2 gj = widen2<T>(gw[j]);
     const f2 pj = widen2<T>(pw[j]);
-    po[j] = narrow2<T>(fused_pair_x2(c, gj, pj, f2_pack(m0a, m0b), f2_pack(v0a, v0b), m[j], v[j], am, av));
+    po[j] = narrow2<T>(fused_pair_x2<APX>(c, gj, pj, f2_pack(m0a, m0b), f2_pack(v0a, v0b), m[j], v[j], am, av));
   }
   *pp = make_uint4(po[0], po[1], po[2], po[3]);
   am = hw_max(am, hmask);
@@ -295,7 +296,7 @@ __device__ __forceinline__ void h_group_fp32(const TDesc& t, long long gl, int l
   }
 }
 
-template <typename T, bool HAS_Q4>
+template <typename T, bool HAS_Q4, bool APX>
 __global__ void __launch_bounds__(CTA_THREADS, CTAS_PER_SM)
 adamw4bit_half_kernel(const __grid_constant__ Table tab, const float* __restrict__ qmap_m,
                       const float* __restrict__ qmap_v, const UConsts cin, long long gbeg, long long gend) {
@@ -336,11 +337,11 @@ adamw4bit_half_kernel(const __grid_constant__ Table tab, const float* __restrict
           const unsigned st = (unsigned)stride;
           if (c.f_fast && vlin) {
             for (; gl < lim; gl += st)
-              h_group_x2<T, true>(t, gl, l16, hmask, k2, Sm, Sv, lut_m, lut_v, qm_l, qv_l,
+              h_group_x2<T, true, APX>(t, gl, l16, hmask, k2, Sm, Sv, lut_m, lut_v, qm_l, qv_l,
                                   (gl + PF_DIST * st < lim) ? PF_DIST * st : 0u);
           } else if (c.f_fast) {
             for (; gl < lim; gl += st)
-              h_group_x2<T, false>(t, gl, l16, hmask, k2, Sm, Sv, lut_m, lut_v, qm_l, qv_l,
+              h_group_x2<T, false, APX>(t, gl, l16, hmask, k2, Sm, Sv, lut_m, lut_v, qm_l, qv_l,
                                    (gl + PF_DIST * st < lim) ? PF_DIST * st : 0u);
           } else if (vlin) {  // hyper-parameters outside the short sequences' domain: IEEE sqrt and division
             for (; gl < lim; gl += st)
@@ -361,7 +362,7 @@ adamw4bit_half_kernel(const __grid_constant__ Table tab, const float* __restrict
   }
 }
 
-template <typename T, bool HAS_Q4>
+template <typename T, bool HAS_Q4, bool APX>
 static cudaError_t launch_half(const Table& tab, unsigned grid, const float* qm, const float* qv, const UConsts& c,
                                long long lo, long long hi, cudaStream_t st) {
   static bool attr_set[64] = {};
@@ -369,12 +370,12 @@ static cudaError_t launch_half(const Table& tab, unsigned grid, const float* qm,
   cudaGetDevice(&dev);
   const size_t smem = HAS_Q4 ? H_DYN_SMEM : 0;
   if (HAS_Q4 && dev >= 0 && dev < 64 && !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(adamw4bit_half_kernel<T, HAS_Q4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(adamw4bit_half_kernel<T, HAS_Q4, APX>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)H_DYN_SMEM);
     if (e != cudaSuccess) return e;
     attr_set[dev] = true;
   }
-  adamw4bit_half_kernel<T, HAS_Q4><<<grid, CTA_THREADS, smem, st>>>(tab, qm, qv, c, lo, hi);
+  adamw4bit_half_kernel<T, HAS_Q4, APX><<<grid, CTA_THREADS, smem, st>>>(tab, qm, qv, c, lo, hi);
   return cudaGetLastError();
 }
 
@@ -382,10 +383,20 @@ static cudaError_t launch_half(const Table& tab, unsigned grid, const float* qm,
 
 using namespace lpmm_b200;
 
-extern "C" int lpmm_b200_adamw4bit_multi_tensor_16bit(const lpmm_b200_tensor* ts, int n, int dtype, const float* qmap_m,
-                                                      const float* qmap_v, lpmm_b200_hyper h, int64_t group_begin,
-                                                      int64_t group_end, void* stream) {
+template <typename T>
+static cudaError_t launch_half_any(bool any_q4, bool apx, const Table& tab, unsigned grid, const float* qm, const float* qv,
+                                   const UConsts& c, long long lo, long long hi, cudaStream_t st) {
+  if (!any_q4) return launch_half<T, false, false>(tab, grid, qm, qv, c, lo, hi, st);
+  return apx ? launch_half<T, true, true>(tab, grid, qm, qv, c, lo, hi, st)
+             : launch_half<T, true, false>(tab, grid, qm, qv, c, lo, hi, st);
+}
+
+extern "C" int lpmm_b200_adamw4bit_multi_tensor_16bit_flags(const lpmm_b200_tensor* ts, int n, int dtype,
+                                                            const float* qmap_m, const float* qmap_v, lpmm_b200_hyper h,
+                                                            int64_t group_begin, int64_t group_end, uint32_t flags,
+                                                            void* stream) {
   if (dtype != LPMM_B200_DTYPE_BF16 && dtype != LPMM_B200_DTYPE_FP16) return LPMM_B200_ERR_BAD_KIND;
+  if (flags & ~(uint32_t)LPMM_B200_FLAG_PARAMS_WITHIN_TOLERANCE) return LPMM_B200_ERR_BAD_KIND;
   bool any_q4 = false;
   int64_t total = 0;
   const int rc = check_tensor_list(ts, n, true, &any_q4, &total);
@@ -395,6 +406,9 @@ extern "C" int lpmm_b200_adamw4bit_multi_tensor_16bit(const lpmm_b200_tensor* ts
   if (group_begin < 0 || group_begin > group_end || group_end > total) return LPMM_B200_ERR_BAD_SIZE;
   if (group_begin == group_end) return LPMM_B200_OK;
   const UConsts c = make_consts(h.beta1, h.beta2, h.lr, h.weight_decay, h.eps, h.step);
+  // the folded constants of the tolerance mode need a finite 1 / lr
+  const bool apx = (flags & LPMM_B200_FLAG_PARAMS_WITHIN_TOLERANCE) && c.f_fast && h.lr >= 0x1p-60f && h.lr <= 0x1p30f &&
+                   h.weight_decay <= 0x1p30f;
   static thread_local Table tab;
   int64_t gcursor = 0;
   int i = 0;
@@ -403,14 +417,16 @@ extern "C" int lpmm_b200_adamw4bit_multi_tensor_16bit(const lpmm_b200_tensor* ts
     const Window w = next_window(ts, n, i, gcursor, group_begin, group_end, true, tab);
     if (!w.work) continue;
     const unsigned grid = multi_grid(w);
-    cudaError_t e;
-    if (dtype == LPMM_B200_DTYPE_BF16)
-      e = w.any_q4 ? launch_half<__nv_bfloat16, true>(tab, grid, qmap_m, qmap_v, c, w.lo, w.hi, st)
-                   : launch_half<__nv_bfloat16, false>(tab, grid, qmap_m, qmap_v, c, w.lo, w.hi, st);
-    else
-      e = w.any_q4 ? launch_half<__half, true>(tab, grid, qmap_m, qmap_v, c, w.lo, w.hi, st)
-                   : launch_half<__half, false>(tab, grid, qmap_m, qmap_v, c, w.lo, w.hi, st);
+    const cudaError_t e = dtype == LPMM_B200_DTYPE_BF16
+                              ? launch_half_any<__nv_bfloat16>(w.any_q4, apx, tab, grid, qmap_m, qmap_v, c, w.lo, w.hi, st)
+                              : launch_half_any<__half>(w.any_q4, apx, tab, grid, qmap_m, qmap_v, c, w.lo, w.hi, st);
     LPMM_CUDA_TRY(e);
   }
   return LPMM_B200_OK;
+}
+
+extern "C" int lpmm_b200_adamw4bit_multi_tensor_16bit(const lpmm_b200_tensor* ts, int n, int dtype, const float* qmap_m,
+                                                      const float* qmap_v, lpmm_b200_hyper h, int64_t group_begin,
+                                                      int64_t group_end, void* stream) {
+  return lpmm_b200_adamw4bit_multi_tensor_16bit_flags(ts, n, dtype, qmap_m, qmap_v, h, group_begin, group_end, 0u, stream);
 }

@@ -41,4 +41,4 @@ extern "C" const char* lpmm_b200_strerror(int status) {
 
 extern "C" const char* lpmm_b200_last_cuda_error(void) { return lpmm_b200::g_last_cuda_error.c_str(); }
 
-extern "C" int lpmm_b200_abi_version(void) { return 2; }
+extern "C" int lpmm_b200_abi_version(void) { return 3; }

@@ -199,6 +199,13 @@ __device__ __forceinline__ float mufu_rcp(float x) {
   return y;
 }
 
+// Approximate square root (within 2^-23 relative; 0 and denormals give 0): tolerance-mode parameter update only.
+__device__ __forceinline__ float sqrt_approx(float x) {
+  float y;
+  asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // MUFU reciprocal refined once; the reciprocal both fma-corrected divisions below are built on.
 __device__ __forceinline__ float rcp_nr(float d) {
   const float r = mufu_rcp(d);

@@ -9,6 +9,9 @@ namespace lpmm_b200 {
 
 struct Consts2 {
   f2 beta1, beta2, omb1, omb2, wd, nlr, eps, nc1, nc2s, rc2s, half, mone, one, k16, km15;
+  // tolerance-mode parameter update (fused_pair_x2<true>): -lr / d = 1 / (sqrt(v) * apx_a + apx_b),
+  // apx_a = c1 / (c2s * -lr), apx_b = eps * c1 / -lr;  p' = p + fma(apx_w, p, m * (-lr / d)), apx_w = -lr * wd
+  f2 apx_a, apx_b, apx_w;
 };
 
 // beta1, beta2, omb1 = 1 - beta1, omb2 = 1 - beta2 (float subtraction), lr, wd, eps, c1 = 1 - beta1^t,
@@ -31,12 +34,23 @@ __device__ __forceinline__ Consts2 make_consts_x2(float beta1, float beta2, floa
   k.one = f2_splat(1.0f);
   k.k16 = f2_splat(16.0f);
   k.km15 = f2_splat(-1.5f);
+  k.apx_a = f2_splat(__fdiv_rn(c1, __fmul_rn(c2s, -lr)));
+  k.apx_b = f2_splat(__fdiv_rn(__fmul_rn(eps, c1), -lr));
+  k.apx_w = f2_splat(__fmul_rn(-lr, wd));
   return k;
 }
 
 // One pair: new moments from the old ones and the gradient (their maxima folded into am / av), new parameter
 // returned.  m = fma(b1, m0, (1-b1) g); v = fma(b2, v0, ((1-b2) g) g); d = (sqrt(v)/c2s + eps) c1;
 // p' = fma(-lr, fma(wd, p, m/d), p).
+// APX (the tolerance mode of the parameter update): the moments -- and with them every code and scale --
+// are computed exactly as above, but the new parameter comes from the hardware's approximate square root
+// and reciprocal (each within 2^-23 relative) with the constant factors folded on the host side of the
+// loop: p' = p + ((-lr*wd) p + m / ((sqrt(v)/c2s + eps) c1 / -lr)), the parameter itself rounded once as in
+// the exact update.  The step lr*(m/d) is then within ~4e-7 of its own size of the exact one, i.e. off by at
+// most a few 1e-10 for a step of size 1e-3: the new parameter equals the exact one or its fp32 neighbour.
+// Needs lr >= 2^-60 (the folded constants stay finite); callers check.
+template <bool APX = false>
 __device__ __forceinline__ f2 fused_pair_x2(const Consts2& c, f2 gj, f2 pj, f2 m0, f2 v0, f2& m, f2& v, float& am,
                                             float& av) {
   m = f2_fma(c.beta1, m0, f2_mul(c.omb1, gj));
@@ -46,6 +60,14 @@ __device__ __forceinline__ f2 fused_pair_x2(const Consts2& c, f2 gj, f2 pj, f2 m
   f2_unpack(v, va, vb);
   am = fmaxf(am, fmaxf(fabsf(ma), fabsf(mb)));
   av = fmaxf(av, fmaxf(va, vb));
+  if (APX) {
+    const f2 s = f2_pack(sqrt_approx(va), sqrt_approx(vb));
+    float da, db;
+    f2_unpack(f2_fma(s, c.apx_a, c.apx_b), da, db);
+    const f2 r = f2_pack(mufu_rcp(da), mufu_rcp(db));
+    // one rounding of the parameter itself, like the exact update: p + (-lr*wd*p - lr*m/d)
+    return f2_add(pj, f2_fma(c.apx_w, pj, f2_mul(m, r)));
+  }
   // sqrt(v): y = rsqrt(max(v, FLT_MIN)); s = v*y; s += (v - s*s) * (y/2)
   const f2 y = f2_pack(mufu_rsq(fmaxf(va, 1.17549435e-38f)), mufu_rsq(fmaxf(vb, 1.17549435e-38f)));
   f2 s = f2_mul(v, y);

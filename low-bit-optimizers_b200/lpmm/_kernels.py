@@ -101,18 +101,22 @@ _DTYPE16 = {torch.bfloat16: N.DTYPE_BF16, torch.float16: N.DTYPE_FP16}
 
 
 def adamw4bit_multi_tensor(tl, qmap_m, qmap_v, beta1, beta2, lr, weight_decay, eps, step, group_begin=0, group_end=-1,
-                           dtype=torch.float32):
+                           dtype=torch.float32, exact_params=True):
     """``dtype``: element type of every parameter and gradient of the list (fp32, or bf16 / fp16 for
-    ``lpmm_b200_adamw4bit_multi_tensor_16bit``)."""
+    ``lpmm_b200_adamw4bit_multi_tensor_16bit``).  ``exact_params=False``: the parameter update may differ from
+    the reference's in the last bits (``LPMM_B200_FLAG_PARAMS_WITHIN_TOLERANCE``); moments, scales and codes
+    are the same either way."""
     if tl.n == 0:
         return
     h = N.Hyper(beta1, beta2, lr, weight_decay, eps, step)
+    flags = 0 if exact_params else N.FLAG_PARAMS_WITHIN_TOLERANCE
     if dtype != torch.float32:
-        N.check(N.lib.lpmm_b200_adamw4bit_multi_tensor_16bit(tl.array, tl.n, _DTYPE16[dtype], _ptr(qmap_m), _ptr(qmap_v), h,
-                                                             group_begin, group_end, _stream()))
+        N.check(N.lib.lpmm_b200_adamw4bit_multi_tensor_16bit_flags(tl.array, tl.n, _DTYPE16[dtype], _ptr(qmap_m),
+                                                                   _ptr(qmap_v), h, group_begin, group_end, flags,
+                                                                   _stream()))
         return
-    N.check(N.lib.lpmm_b200_adamw4bit_multi_tensor(tl.array, tl.n, _ptr(qmap_m), _ptr(qmap_v), h, group_begin, group_end,
-                                                   _stream()))
+    N.check(N.lib.lpmm_b200_adamw4bit_multi_tensor_flags(tl.array, tl.n, _ptr(qmap_m), _ptr(qmap_v), h, group_begin,
+                                                         group_end, flags, _stream()))
 
 
 def sgd4bit_multi_tensor(tl, qmap, *, weight_decay, momentum, lr, dampening, nesterov, maximize, group_begin=0,
@@ -350,9 +354,22 @@ def _ensure_group_state(state, name, p, quantized, bits=4, gp_sz=128):
     if quantized:
         n = p.numel()
         groups = _groups(n, gp_sz)
-        if first or t.dtype != torch.int8:
+        if not first and t.dtype != torch.int8:
+            # an initialised moment that is not packed although quantization is now enabled (a checkpoint saved
+            # with this state in fp32, a changed threshold): quantise what is there, never pair fresh storage
+            # with first = False
+            if t.numel() != n or not t.is_floating_point():
+                raise RuntimeError(f"{name}: an initialised state of {t.numel()} {t.dtype} elements cannot become the "
+                                   f"quantized state of a parameter of {n} elements")
+            codes, max1 = quant_group(t.detach().to(torch.float32).contiguous().view(-1),
+                                      state[f"{name}_qstate"]["qmap"], gp_sz, bits)
+            t.data = codes
+            oh["max1"] = max1
+        elif first:
             t.data = torch.empty(packed_len(groups * gp_sz, bits), dtype=torch.int8, device=p.device)
         if not isinstance(oh.get("max1"), torch.Tensor) or oh["max1"].numel() != groups:
+            if not first:
+                raise RuntimeError(f"{name}: packed codes without their {groups} group scales (overhead['max1'])")
             oh["max1"] = torch.empty((groups, 1), dtype=torch.float32, device=p.device)
         oh["dtype"], oh["stride"] = p.dtype, p.stride()
         oh["scaled_shape"] = torch.Size([groups, gp_sz])

@@ -63,6 +63,7 @@ KIND_Q4 = 0
 KIND_FP32 = 1
 DTYPE_BF16 = 1
 DTYPE_FP16 = 2
+FLAG_PARAMS_WITHIN_TOLERANCE = 1
 GROUP = 128
 PACK_GROUP = 2048
 STATIC_SCRATCH_BYTES = 8 * 1024 * 1024
@@ -86,7 +87,13 @@ def _load():
         "lpmm_b200_adamw4bit_single_tensor": (i32, [vp] * 8 + [f] * 6 + [i64, vp]),
         "lpmm_b200_adamw_single_tensor": (i32, [vp] * 4 + [f] * 6 + [i64, vp]),
         "lpmm_b200_adamw4bit_multi_tensor": (i32, [ctypes.POINTER(Tensor), i32, vp, vp, Hyper, i64, i64, vp]),
+        "lpmm_b200_adamw4bit_multi_tensor_flags": (i32, [ctypes.POINTER(Tensor), i32, vp, vp, Hyper, i64, i64,
+                                                         ctypes.c_uint32, vp]),
         "lpmm_b200_adamw4bit_multi_tensor_16bit": (i32, [ctypes.POINTER(Tensor), i32, i32, vp, vp, Hyper, i64, i64, vp]),
+        "lpmm_b200_adamw4bit_multi_tensor_16bit_flags": (i32, [ctypes.POINTER(Tensor), i32, i32, vp, vp, Hyper, i64, i64,
+                                                               ctypes.c_uint32, vp]),
+        "lpmm_b200_adamw4bit_multi_tensor_peers_flags": (i32, [ctypes.POINTER(Tensor), i32, vp, vp, Hyper, i64, i64,
+                                                               ctypes.POINTER(i64), i32, ctypes.c_uint32, vp]),
         "lpmm_b200_adamw4bit_multi_tensor_peers": (i32, [ctypes.POINTER(Tensor), i32, vp, vp, Hyper, i64, i64,
                                                          ctypes.POINTER(i64), i32, vp]),
         "lpmm_b200_adamw4bit_multi_tensor_zero1": (i32, [ctypes.POINTER(Tensor), i32, vp, vp, Hyper, i64, i64,
@@ -125,6 +132,7 @@ def _load():
                                                       + [ctypes.POINTER(d), vp, i64, vp]),
         "lpmm_b200_factored_scratch_bytes": (i64, [ctypes.POINTER(i64), i32]),
         "lpmm_b200_adamw4bit_factored_step_noalloc": (i32, [ctypes.POINTER(StepTensor), vp] + [d] * 6 + [vp]),
+        "lpmm_b200_test_exactness": (i32, [i32, vp, ctypes.c_uint64, i64, vp, vp]),
         "lpmm_b200_sgd4bit_step": (i32, [vp, vp, i64, vp, vp, i32, i32, vp, d, d, d, d, i32, i32, vp]),
     }
     for name, (res, args) in sigs.items():

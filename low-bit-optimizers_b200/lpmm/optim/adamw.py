@@ -14,6 +14,9 @@ Constructor, lazily created state, state names and layouts are those of the refe
   falls back to group scales with a warning, adamw.py:503-506) -- with a rank-1 second-moment
   configuration the states have the ``fused=False`` layout (per-axis maxima in ``max_dims``) and are
   stepped with the fused kernel's arithmetic (``lpmm_b200_adamw4bit_fused_arith_step_many``).
+* ``fused=True, exact_params=False`` (an extension) -- the tolerance mode of the fused step: moments, scales
+  and packed codes stay bit-identical to the reference's kernel, the parameters follow it to within 1e-6
+  relative (approximate square root and reciprocal in the parameter update only), for fewer instructions.
 * tensors with at most ``THRESHOLD`` (4096) elements, or overridden, keep fp32 moments.
 * ``factor_second_moment=True`` keeps fp32 row/column accumulators for every >=2-D tensor
   (adamw.py:124-126, 579-627).
@@ -30,7 +33,8 @@ __all__ = ["AdamW"]
 
 class AdamW(LowBitOptimizer):
     def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=1e-2, use_first_moment=True,
-                 factor_second_moment=False, qconfig=None, *, fused: Optional[bool] = False, fused_rank1: bool = False):
+                 factor_second_moment=False, qconfig=None, *, fused: Optional[bool] = False, fused_rank1: bool = False,
+                 exact_params: bool = True):
         if not 0.0 <= lr:
             raise ValueError("Invalid learning rate: {}".format(lr))
         if not 0.0 <= eps:
@@ -45,6 +49,7 @@ class AdamW(LowBitOptimizer):
                         use_first_moment=use_first_moment, factor_second_moment=factor_second_moment)
         super().__init__(params, defaults, qconfig)
         self._fused_rank1 = bool(fused_rank1)
+        self._exact_params = bool(exact_params)
         self._lists = {}  # cached descriptor arrays of the multi-tensor step, per param group
         self._spare = {}  # per-parameter buffers that are not optimizer state (alternate rank-1 maxima)
         self._plans = {}  # fused groups: everything needed to repeat the last launch
@@ -53,6 +58,7 @@ class AdamW(LowBitOptimizer):
     def __setstate__(self, state):
         super().__setstate__(state)
         self.__dict__.setdefault("_fused_rank1", False)
+        self.__dict__.setdefault("_exact_params", True)
         self._lists = {}
         self._spare = {}
         self._plans = {}
@@ -197,7 +203,7 @@ class AdamW(LowBitOptimizer):
             tl = self._tensor_list((gi, (step, dtype) if len(by_step) > 1 else None, device), entries)
             with torch.cuda.device(device):
                 _kernels.adamw4bit_multi_tensor(tl, qm, qv, beta1, beta2, group["lr"], group["weight_decay"],
-                                                group["eps"], step, dtype=dtype)
+                                                group["eps"], step, dtype=dtype, exact_params=self._exact_params)
             if len(by_step) == 1 and len(items) == len(params):
                 # every tensor of the group took this one launch: remember it, so that the following steps
                 # only bump the counters, refresh changed gradient pointers and launch
@@ -240,7 +246,8 @@ class AdamW(LowBitOptimizer):
         beta1, beta2 = group["betas"]
         with torch.cuda.device(plan["device"]):
             _kernels.adamw4bit_multi_tensor(tl, plan["qm"], plan["qv"], beta1, beta2, group["lr"], group["weight_decay"],
-                                            group["eps"], plan["step"], dtype=plan["dtype"])
+                                            group["eps"], plan["step"], dtype=plan["dtype"],
+                                            exact_params=self._exact_params)
         return True
 
     def _tensor_list(self, key, entries):

@@ -244,9 +244,12 @@ class Zero1FusedAdamW:
 
     def step(self):
         self.step_count += 1
-        if self.reduce_grads:
-            # every rank's gradients must be complete before any rank reads them; the barrier after the
-            # update (in _gather) keeps them from being overwritten while a peer still reads
+        if self.gather == "fused":
+            # The launch stores into every peer's parameter buffer: no rank may start it while another still reads
+            # its parameters (forward / backward of a slower rank), and with reduce_grads every rank's gradients must
+            # be complete before any rank reads them.  One tiny all-reduce on the stream orders the ranks; the one
+            # after the update (in _gather) keeps parameters and gradients from being touched while a peer still
+            # writes or reads them.
             dist.all_reduce(self._flag, group=self.pg)
         if self.hi > self.lo:
             self._update(self.lo, self.hi)

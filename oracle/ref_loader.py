@@ -154,10 +154,16 @@ def _cpu_quantization_module():
     return mod
 
 
-def load_reference(reference_root="/root/reference"):
-    """Import and return the reference's ``lpmm`` package (CPU only)."""
-    if not os.path.isdir(os.path.join(reference_root, "lpmm")):
-        raise FileNotFoundError(f"no reference checkout at {reference_root}")
+def load_reference(reference_root=None):
+    """Import and return the reference's ``lpmm`` package (CPU only).  ``reference_root``: a directory that
+    holds the reference's ``lpmm`` package -- a checkout, or the Python layer that ``oracle/build_ref.py``
+    placed under ``oracle/_ref/lpmm_py``; default: the checkout ``build_ref.reference_root()`` finds, else
+    that copy."""
+    if reference_root is None:
+        from . import build_ref
+        reference_root = build_ref.reference_root() or (build_ref.PY_OUT if build_ref.have_python() else None)
+    if reference_root is None or not os.path.isdir(os.path.join(reference_root, "lpmm")):
+        raise FileNotFoundError(f"no reference package at {reference_root}")
     if "lpmm" in sys.modules and not getattr(sys.modules["lpmm"], "__file__", "").startswith(reference_root):
         raise RuntimeError("another package named lpmm is already imported in this process")
     _install_yacs()

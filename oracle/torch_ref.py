@@ -5,7 +5,7 @@ calls (pack/unpack).  This module restates those sequences op for op, so that ru
 device reproduces what the reference computes on that device:
 
 * on CPU, in a container that holds the reference checkout, it is compared bit for bit with the
-  reference's own Python (tests/test_oracle_cpu.py, fixtures under tests/golden/ made by
+  reference's own Python (tests/test_oracle_python_path.py, fixtures under tests/golden/ made by
   tests/golden/make_python_golden.py) -- that pins it;
 * on a GPU it is the parity target of the CUDA kernels (same torch CUDA kernels the reference
   would run), with the pack/unpack pair replaced by the bucketize form below, itself checked

@@ -45,6 +45,14 @@ CASES = {
     "sgd_8bit": ("SGD", dict(lr=1e-2, momentum=0.9, weight_decay=1e-4, qconfig="default_8b.yml"), [(72, 64), (4097,)], 3, 0.0),
     "sgd_group_1024": ("SGD", dict(lr=1e-2, momentum=0.9, weight_decay=0.0, qconfig="1st_moment_group_1024.yml"),
                        [(5000,), (6, 700)], 3, 0.0),
+    # first moment kept in fp32, second moment 4-bit (rank-1 / group scales)
+    "adamw_2nd_only_rank1": ("AdamW", dict(qconfig="2nd_moment_only_default.yml", **HYPER),
+                             [(72, 64), (4097,), (100,), (2, 3, 32, 32)], 4, 0.0),
+    "adamw_2nd_only_group": ("AdamW", dict(qconfig="2nd_moment_only_group_128.yml", **HYPER), [(70, 61), (5000,)], 3, 0.0),
+    # override_quantize_enable before the first step: tensor 0 (4608 elements) forced to fp32 states, tensor 1
+    # (3000 elements, below the threshold) forced to quantized states
+    "adamw_override": ("AdamW", dict(qconfig="default.yml", **HYPER), [(72, 64), (3000,), (5000,), (50, 40)], 4, 0.0,
+                       [(0, False), (1, True), (3, True)]),
 }
 
 
@@ -83,13 +91,18 @@ def flatten_state(prefix, value, out):
 
 
 def run_case(lpmm, name, ref_root):
-    opt_name, kwargs, shapes, steps, zf = CASES[name]
+    opt_name, kwargs, shapes, steps, zf = CASES[name][:5]
+    overrides = CASES[name][5] if len(CASES[name]) > 5 else []
     kwargs = dict(kwargs)
     if isinstance(kwargs.get("qconfig"), str):
         kwargs["qconfig"] = os.path.join(ref_root, "lpmm", "configs", kwargs["qconfig"])
     params = make_params(shapes)
     out = {f"p0.{i}": p.detach().numpy().copy() for i, p in enumerate(params)}
     opt = getattr(lpmm.optim, opt_name)(params, **kwargs)
+    holder = torch.nn.Module()
+    for i, enable in overrides:  # the reference's API takes (module, attribute name, enable)
+        holder.register_parameter(f"p{i}", params[i])
+        opt.override_quantize_enable(holder, f"p{i}", enable)
     for step in range(1, steps + 1):
         for i, p in enumerate(params):
             p.grad = make_grad(p.shape, step, i, zf)
@@ -111,10 +124,15 @@ def run_case(lpmm, name, ref_root):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=None,
+                    help="the reference checkout (default: $LPMM_REFERENCE_ROOT, else ../reference beside this repository)")
     ap.add_argument("--only", nargs="*", default=None, help="generate just these cases (and no map files)")
     a = ap.parse_args()
+    from oracle.build_ref import reference_root
     from oracle.ref_loader import load_reference
+    a.reference = reference_root(a.reference)
+    if a.reference is None:
+        raise SystemExit("no reference checkout found (give --reference or set LPMM_REFERENCE_ROOT)")
     cwd = os.getcwd()
     os.chdir("/tmp")  # the reference writes ./lpmm_config.txt on construction
     lpmm = load_reference(a.reference)

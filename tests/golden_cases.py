@@ -18,7 +18,13 @@ CASES = {
     "sgd_8bit": ("SGD", dict(lr=1e-2, momentum=0.9, weight_decay=1e-4, qconfig="default_8b.yml"), [(72, 64), (4097,)]),
     "sgd_group_1024": ("SGD", dict(lr=1e-2, momentum=0.9, weight_decay=0.0, qconfig="1st_moment_group_1024.yml"),
                        [(5000,), (6, 700)]),
+    "adamw_2nd_only_rank1": ("AdamW", dict(qconfig="2nd_moment_only_default.yml", **HYPER),
+                             [(72, 64), (4097,), (100,), (2, 3, 32, 32)]),
+    "adamw_2nd_only_group": ("AdamW", dict(qconfig="2nd_moment_only_group_128.yml", **HYPER), [(70, 61), (5000,)]),
+    "adamw_override": ("AdamW", dict(qconfig="default.yml", **HYPER), [(72, 64), (3000,), (5000,), (50, 40)]),
 }
+# override_quantize_enable calls made before the first step: case -> [(parameter index, enable)]
+OVERRIDES = {"adamw_override": [(0, False), (1, True), (3, True)]}
 THRESHOLD = 4096
 
 # Code width and first-moment group size of each case's configuration; names of its two maps in the
@@ -31,6 +37,6 @@ def layout(name):
             bits = int(cfg[len("default_"):-len("b.yml")])
         if cfg.startswith("1st_moment_group_"):
             m_gp = int(cfg[len("1st_moment_group_"):-len(".yml")])
-    v_scale = "group" if cfg is None else "rank1"
+    v_scale = "group" if cfg is None or cfg == "2nd_moment_only_group_128.yml" else "rank1"
     maps = ("m", "v") if bits == 4 else (f"nonlinear_{bits}", f"power1_{bits}")
     return dict(bits=bits, m_gp=m_gp, v_scale=v_scale, maps=maps)

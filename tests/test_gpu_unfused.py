@@ -33,12 +33,24 @@ def _make_opt(kind, params, kw):
     return getattr(lpmm.optim, kind)(params, **kw)
 
 
-def _run_pair_adamw(shapes, p0s, grads_of_step, steps, kw, qmaps, v_scale, maps=("m", "v"), m_gp=128):
-    """Returns (optimizer, params, oracle states, oracle params)."""
+def _default_quant(i, numel):
+    return numel > THRESHOLD, numel > THRESHOLD
+
+
+def _run_pair_adamw(shapes, p0s, grads_of_step, steps, kw, qmaps, v_scale, maps=("m", "v"), m_gp=128, quant_of=None,
+                    overrides=()):
+    """Returns (optimizer, params, oracle states, oracle params).  ``quant_of(i, numel)`` -> (first moment
+    quantized, second moment quantized) of tensor i (default: both iff numel > 4096); ``overrides``:
+    (tensor index, enable) pairs passed to ``override_quantize_enable`` before the first step."""
     from oracle import torch_ref as T
+    quant_of = quant_of or _default_quant
     qm, qv = _dev(qmaps[maps[0]]), _dev(qmaps[maps[1]])
     params = [torch.nn.Parameter(p.clone()) for p in p0s]
     opt = _make_opt("AdamW", params, kw)
+    holder = torch.nn.Module()
+    for i, enable in overrides:
+        holder.register_parameter(f"p{i}", params[i])
+        opt.override_quantize_enable(holder, f"p{i}", enable)
     o_params = [p.clone() for p in p0s]
     o_states = [dict() for _ in p0s]
     factored = kw.get("factor_second_moment", False)
@@ -52,12 +64,12 @@ def _run_pair_adamw(shapes, p0s, grads_of_step, steps, kw, qmaps, v_scale, maps=
             p.grad = g.clone()
         opt.step()
         for i, (op, g) in enumerate(zip(o_params, grads)):
-            quant = op.numel() > THRESHOLD
+            mq, vq = quant_of(i, op.numel())
             common = dict(beta1=b1, beta2=b2, lr=kw["lr"], weight_decay=kw["weight_decay"], eps=kw["eps"], step=float(s))
             if factored and op.dim() >= 2:
-                T.factored_step(op, g, o_states[i], qm, m_quant=quant, m_gp_sz=m_gp, **common)
+                T.factored_step(op, g, o_states[i], qm, m_quant=mq, m_gp_sz=m_gp, **common)
             else:
-                T.adamw_step(op, g, o_states[i], qm, qv, m_quant=quant, v_quant=quant, v_scale_type=v_scale,
+                T.adamw_step(op, g, o_states[i], qm, qv, m_quant=mq, v_quant=vq, v_scale_type=v_scale,
                              m_gp_sz=m_gp, **common)
     torch.cuda.synchronize()
     return opt, params, o_states, o_params
@@ -71,10 +83,14 @@ def _check_group_state(mine_codes, mine_max1, o_codes, o_md, n, what, gp=128):
     assert mine_max1.numel() == groups
 
 
-def _check_adamw(opt, params, o_states, o_params, v_scale, factored=False, p_exact=True, m_gp=128):
+def _check_adamw(opt, params, o_states, o_params, v_scale, factored=False, p_exact=True, m_gp=128, quant_of=None,
+                 acc_tol=1e-6):
+    """``acc_tol``: relative tolerance (of the largest entry) on the factored row / column accumulators, whose sums
+    are taken in another order than torch's."""
+    quant_of = quant_of or _default_quant
     for i, p in enumerate(params):
         st, os_, op = opt.state[p], o_states[i], o_params[i]
-        quant = p.numel() > THRESHOLD
+        quant, v_quant = quant_of(i, p.numel())
         fac = factored and p.dim() >= 2
         if fac or not p_exact:
             rel = ((p.detach() - op).norm() / op.norm()).item()
@@ -89,9 +105,9 @@ def _check_adamw(opt, params, o_states, o_params, v_scale, factored=False, p_exa
         if fac:
             for mine, orc in ((st["exp_avg_sq_row"], os_["row"]), (st["exp_avg_sq_col"], os_["col"])):
                 rel = ((mine - orc).abs().max() / orc.abs().max()).item()
-                assert rel <= 1e-6, f"tensor {i}: accumulator rel err {rel}"
+                assert rel <= acc_tol, f"tensor {i}: accumulator rel err {rel}"
             continue
-        if not quant:
+        if not v_quant:
             assert bits_equal(st["exp_avg_sq"], os_["v"]), f"tensor {i}: fp32 exp_avg_sq differs"
         elif v_scale == "rank1" and p.dim() >= 2:
             oh = st["exp_avg_sq_qstate"]["overhead"]

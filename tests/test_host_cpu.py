@@ -22,7 +22,7 @@ def test_library_exports_every_declared_symbol():
     for name in sorted(declared):
         assert hasattr(lib, name), f"{name} is declared in include/lpmm_b200.h but not exported"
     assert declared == set(N.SIGNATURES), "the ctypes table and the header disagree"
-    assert N.lib.lpmm_b200_abi_version() == 2
+    assert N.lib.lpmm_b200_abi_version() == 3
 
 
 def test_argument_validation_without_a_gpu():

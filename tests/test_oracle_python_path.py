@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 import torch
 
-from golden_cases import CASES, THRESHOLD, layout
+from golden_cases import CASES, OVERRIDES, THRESHOLD, layout
 from oracle import torch_ref as T
 
 
@@ -25,8 +25,22 @@ def _same_codes(a, b, numel_codes):
     return np.array_equal(a, b)
 
 
+def quant_flags(name, i, numel):
+    """(first moment quantized, second moment quantized) of tensor i of a golden case: the threshold rule
+    (reference optimizer.py:156-163), M.ENABLE False in the 2nd_moment_only configurations, and the case's
+    override_quantize_enable calls (reference adamw.py:143-144)."""
+    over = dict(OVERRIDES.get(name, []))
+    if i in over:
+        return over[i], over[i]
+    big = numel > THRESHOLD
+    cfg = CASES[name][1].get("qconfig")
+    m_enabled = not (isinstance(cfg, str) and cfg.startswith("2nd_moment_only"))
+    return big and m_enabled, big
+
+
 @pytest.mark.parametrize("name", ["adamw_rank1", "adamw_group", "adamw_rank1_ragged", "adamw_8bit", "adamw_5bit",
-                                  "adamw_m_group_512", "adamw_m_group_4096"])
+                                  "adamw_m_group_512", "adamw_m_group_4096", "adamw_2nd_only_rank1",
+                                  "adamw_2nd_only_group", "adamw_override"])
 def test_adamw_unfused_matches_reference_python(golden_dir, qmaps, name):
     G = _load(golden_dir, name)
     _, kw, shapes = CASES[name]
@@ -36,19 +50,23 @@ def test_adamw_unfused_matches_reference_python(golden_dir, qmaps, name):
     steps = int(G["steps"])
     for i, shape in enumerate(shapes):
         p = _t(G[f"p0.{i}"]).clone()
-        quant = p.numel() > THRESHOLD
+        quant, v_quant = quant_flags(name, i, p.numel())
         st = {}
         for s in range(1, steps + 1):
-            T.adamw_step(p, _t(G[f"g{s}.{i}"]), st, qm, qv, m_quant=quant, v_quant=quant, v_scale_type=v_scale,
+            T.adamw_step(p, _t(G[f"g{s}.{i}"]), st, qm, qv, m_quant=quant, v_quant=v_quant, v_scale_type=v_scale,
                          beta1=0.9, beta2=0.999, lr=1e-3, weight_decay=0.01, eps=1e-8, step=float(s),
                          m_gp_sz=L["m_gp"])
         assert np.array_equal(p.numpy(), G[f"p.{i}"]), f"params of tensor {i}"
         if quant:
             # last byte is not written by the reference
-            assert st["m"].numel() == G[f"s.{i}.exp_avg"].size and st["v"].numel() == G[f"s.{i}.exp_avg_sq"].size
+            assert st["m"].numel() == G[f"s.{i}.exp_avg"].size
             assert _same_codes(st["m"].numpy(), G[f"s.{i}.exp_avg"], G[f"s.{i}.exp_avg"].size - 1)
-            assert _same_codes(st["v"].numpy(), G[f"s.{i}.exp_avg_sq"], G[f"s.{i}.exp_avg_sq"].size - 1)
             assert np.array_equal(st["m_md"]["max1"].numpy(), G[f"s.{i}.exp_avg_qstate.overhead.max1"])
+        else:
+            assert np.array_equal(st["m"].numpy(), G[f"s.{i}.exp_avg"])
+        if v_quant:
+            assert st["v"].numel() == G[f"s.{i}.exp_avg_sq"].size
+            assert _same_codes(st["v"].numpy(), G[f"s.{i}.exp_avg_sq"], G[f"s.{i}.exp_avg_sq"].size - 1)
             if v_scale == "rank1" and len(shape) > 1:
                 for d in range(len(shape)):
                     assert np.array_equal(st["v_md"]["max_dims"][d].numpy(),
@@ -56,7 +74,6 @@ def test_adamw_unfused_matches_reference_python(golden_dir, qmaps, name):
             else:
                 assert np.array_equal(st["v_md"]["max1"].numpy(), G[f"s.{i}.exp_avg_sq_qstate.overhead.max1"])
         else:
-            assert np.array_equal(st["m"].numpy(), G[f"s.{i}.exp_avg"])
             assert np.array_equal(st["v"].numpy(), G[f"s.{i}.exp_avg_sq"])
 
 
