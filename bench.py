@@ -11,9 +11,15 @@ which the 64 norm vectors (exactly 4096 elements) keep fp32 moments.  Data are s
 own arm      one step = ``lpmm.optim.AdamW(fused=True).step()`` over the whole list (one multi-tensor
              launch).  ``value`` is timed with parameters, gradients and states resident in HBM;
              ``e2e`` is the same call with the step's gradients arriving from pinned host memory
-             and a device->host read of a result inside the timed region.  With N > 1 the list is
-             ZeRO-1 sharded by whole 128-element groups and the timed step ends with the NCCL
-             all-gather of the updated parameters.
+             and a device->host read of a result inside the timed region.  ``tolerance_mode``: the same
+             step with ``exact_params=False`` (codes and scales bit-identical, parameters within 1e-6).
+             With N > 1 the list is ZeRO-1 sharded by whole 128-element groups (``lpmm.zero``); the updated
+             parameters reach the other ranks by NVLink stores inside the update kernel (``--gather fused``,
+             the default) or by an NCCL all-gather after it (``--gather nccl``).  The whole step is timed
+             (``"scaling": "strong"``: the list is fixed, the ranks share it); extra keys give the check that
+             the sharded step equals the unsharded one (``zero1_check``), the update alone per GPU
+             (``local_update``), the same list with bf16 parameters (``params_bf16``) and the
+             LLaMA-13B-shaped list (``llama13b``).
 reference    the reference's own Python CPU path (``lpmm.optim.AdamW`` unchanged, group-128 4-bit states, its
 arm          CUDA pack/unpack extension replaced by a C restatement) with all host threads on a bounded
              sample of the same list, rank 0 only; the C port of the fused kernel when that Python is absent.
@@ -301,6 +307,99 @@ def cpu_baseline_in_subprocess(steps=2, warmup=1):
 # --------------------------------------------------------------------------------------------------
 # own arm
 # --------------------------------------------------------------------------------------------------
+CHECK_SHAPES = [(300, 128), (4096,), (5000,), (77, 129), (128,), (64, 64, 3), (2048, 1024)]
+
+
+def zero1_check(opt, world, rank, dev, gather):
+    """Is the sharded step right?  (1) After the timed steps every rank's copy of the whole parameter buffer has the
+    same 64-bit checksum.  (2) A small list (4-bit tensors, fp32-state tensors, ragged sizes) is stepped three times
+    both ZeRO-1 sharded over all ranks (same gather mode) and unsharded by ``lpmm.optim.AdamW(fused=True)`` on every
+    rank, on the same seeded gradients: the parameters must be equal bit for bit on every rank."""
+    import torch
+    import torch.distributed as dist
+    import lpmm
+    from lpmm.zero import Zero1FusedAdamW
+    c = opt.flat_checksum().reshape(1)
+    lo, hi = c.clone(), c.clone()
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+    dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    same_sum = bool((lo == hi).item())
+    z = Zero1FusedAdamW(CHECK_SHAPES, dev, gather=gather, **HYPER)
+    z.init_params_normal_(0.02, seed=0)
+    plain = [torch.nn.Parameter(v.detach().clone()) for v in z.params]
+    po = lpmm.optim.AdamW(plain, fused=True, **HYPER)
+    for step in range(1, 4):
+        grads = []
+        for i, sh in enumerate(CHECK_SHAPES):
+            g = torch.empty(sh, device=dev)
+            student_t_(g, step * 100003 + i)
+            grads.append(g)
+        z.set_grad_shard_from_full(grads)
+        z.step()
+        for p, g in zip(plain, grads):
+            p.grad = g
+        po.step()
+    torch.cuda.synchronize()
+    equal = all(bool(torch.equal(v.view(torch.int32), p.detach().view(torch.int32))) for v, p in zip(z.params, plain))
+    flag = torch.tensor([1 if equal else 0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if same_sum and int(flag.item()) == 1:
+        return "ok"
+    return ("MISMATCH:" + ("" if same_sum else " the ranks' parameter buffers differ after the timed steps;")
+            + ("" if int(flag.item()) == 1 else " sharded != unsharded on the small list"))
+
+
+def local_update_rate(opt, iters, peak, world):
+    """The update alone on each GPU's own shard, without the stores into the peers (what scales with the number of
+    GPUs; it leaves the replicas inconsistent, so it runs after the check).  Max over ranks."""
+    import torch
+    import torch.distributed as dist
+    ms, nbytes = opt.time_update_only(iters, peers=False)
+    t = torch.tensor([ms], device=opt.device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    n_own = (opt.hi - opt.lo) * 128
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    return {"ms": ms, "params_per_s_per_gpu": n_own / (ms * 1e-3), "aggregate_params_per_s": n_own * world / (ms * 1e-3),
+            "hbm_gb_per_s_per_gpu": gbs, "frac_of_measured_hbm_peak": gbs / peak}
+
+
+def sharded_step_line(shapes, dev, gather, dtype, iters, world):
+    """Whole sharded step (update + exchange) of another list / element type, timed like the headline: max over ranks."""
+    import torch
+    import torch.distributed as dist
+    from lpmm.zero import Zero1FusedAdamW
+    z = Zero1FusedAdamW(shapes, dev, gather=gather, dtype=dtype, **HYPER)
+    z.init_params_normal_(0.02, seed=0)
+    tmp = torch.empty(min(z.grad_shard.numel(), 1 << 26), device=dev)
+    student_t_(tmp, 100003 + dist.get_rank(), rows_outliers=False)
+    for lo in range(0, z.grad_shard.numel(), tmp.numel()):
+        hi = min(lo + tmp.numel(), z.grad_shard.numel())
+        z.grad_shard[lo:hi].copy_(tmp[: hi - lo])
+    del tmp
+    for _ in range(3):
+        z.step()
+    dist.barrier()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        z.step()
+    b.record()
+    dist.barrier()
+    torch.cuda.synchronize()
+    t = torch.tensor([a.elapsed_time(b) / iters], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    total = sum(numel(s) for s in shapes)
+    sent = float(z.esize) * z.shard_groups * 128 * (world - 1)
+    out = {"params": total, "dtype": str(dtype).replace("torch.", ""), "ms_per_step": ms, "value": total / (ms * 1e-3), "unit": UNIT,
+           "steps": iters, "nvlink_bytes_sent_per_rank_per_step": sent, "nvlink_gb_per_s_per_rank": sent / (ms * 1e-3) / 1e9}
+    del z
+    torch.cuda.empty_cache()
+    return out
+
+
 def run_own(args):
     import torch
     import torch.distributed as dist
@@ -403,6 +502,9 @@ def run_own(args):
         k_ms, k_bytes = opt.time_update_only(max(3, min(args.steps, 10)))
         extra.update(opt.breakdown(max(3, min(args.steps, 10))))
     peak, peak_kind = measured_peak()
+    if world > 1:
+        extra["zero1_check"] = zero1_check(opt, world, rank, dev, args.gather)
+        extra["local_update"] = local_update_rate(opt, max(3, min(args.steps, 10)), peak, world)
     achieved = k_bytes / (k_ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "traffic": NCU_TRAFFIC_PER_PARAM * (k_bytes / BYTES_Q4), "peak_kind": f"of {peak_kind}",
@@ -516,6 +618,20 @@ def run_own(args):
         e2e = {"value": total / (e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": 4 * n_sh * world,
                "d2h_bytes_per_step": 4096 * world, "ms_per_step": e_ms, "steps": n_e2e}
 
+    if world > 1 and not args.no_extras and not args.reduce_grads:
+        del opt
+        torch.cuda.empty_cache()
+        n_x = max(3, min(args.steps, 10))
+        try:
+            extra["params_bf16"] = sharded_step_line(shapes, dev, args.gather, torch.bfloat16, n_x, world)
+        except Exception as e:  # an extra must not cost the headline line
+            extra["params_bf16"] = {"error": repr(e)[:200]}
+        if args.model == "7b":
+            try:
+                s13 = llama7b_shapes(layers=40, hidden=5120, inter=13824)
+                extra["llama13b"] = sharded_step_line(s13, dev, args.gather, torch.float32, n_x, world)
+            except Exception as e:
+                extra["llama13b"] = {"error": repr(e)[:200]}
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cpu = cpu_baseline_in_subprocess(2, 1)
@@ -523,7 +639,7 @@ def run_own(args):
     if rank == 0:
         out = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic (seeded N(0,0.02) params, Student-t(3)*1e-3 grads with 1% outlier rows; one gradient set reused every step)",
             "config": {"workload": f"llama{args.model}_shaped_fp32_list_fused_4bit_adamw", "params": total, "tensors": len(shapes),
                        "params_4bit": nq, "params_fp32_state": nf, "layers": n_layers,
@@ -550,6 +666,7 @@ def main():
     ap.add_argument("--model", default="7b", choices=["7b", "13b"],
                     help="7b: the headline list; 13b: the LLaMA-13B-shaped list (52 GB of fp32 parameters per GPU)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="N > 1: skip the bf16 and 13B-shaped extra measurements")
     ap.add_argument("--no-port", action="store_true", help="reference arm: skip the extra timing of the C port")
     ap.add_argument("--reduce-grads", action="store_true",
                     help="N > 1, --gather fused: every rank holds full local gradients and the update kernel also sums "

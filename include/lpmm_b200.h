@@ -156,6 +156,16 @@ int lpmm_b200_adamw4bit_multi_tensor_peers_flags(const lpmm_b200_tensor* tensors
                                                  const int64_t* peer_byte_offsets, int n_peers, uint32_t flags,
                                                  void* stream);
 
+/* The ZeRO-1 step with the all-gather folded in, for 16-bit parameters and gradients (dtype = LPMM_B200_DTYPE_*):
+ * lpmm_b200_adamw4bit_multi_tensor_16bit_flags whose every updated parameter is also stored at its address plus each
+ * of the n_peers (<= 7) byte offsets (multiples of 16) -- half the NVLink bytes of the fp32 form.  No counterpart in
+ * the reference.  Both quantization maps are required whenever n_peers > 0. */
+int lpmm_b200_adamw4bit_multi_tensor_16bit_peers(const lpmm_b200_tensor* tensors, int n_tensors, int dtype,
+                                                 const float* exp_avg_qmap, const float* exp_avg_sq_qmap,
+                                                 lpmm_b200_hyper hyper, int64_t group_begin, int64_t group_end,
+                                                 const int64_t* peer_byte_offsets, int n_peers, uint32_t flags,
+                                                 void* stream);
+
 /* The whole ZeRO-1 step in one kernel: additionally to the above, the gradient of every element of
  * this rank's range is the sum, in the order given, of the values found at the n_grads (<= 8) byte
  * offsets from its address in this GPU's gradient buffer (tensors[i].g; offset 0 is this GPU's own

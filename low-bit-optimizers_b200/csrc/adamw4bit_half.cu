@@ -90,10 +90,11 @@ __device__ __forceinline__ unsigned narrow2<__half>(f2 x) {
 // multiply / add / fma, each half rounding like the scalar instruction, so the results are those of
 // h_group_fast with the short sqrt / division sequences (selected only where those apply).
 // APX: the tolerance mode of the parameter update (fused_x2.cuh); moments, maxima and codes unchanged.
-template <typename T, bool VLIN, bool APX>
+template <typename T, bool VLIN, bool APX, bool PEERS>
 __device__ __forceinline__ void h_group_x2(const TDesc& t, unsigned gl, int l16, unsigned hmask, const Consts2& c,
                                            const QMapSmem& Sm, const QMapSmem& Sv, const LutEnt* __restrict__ lut_m,
-                                           const LutEnt* __restrict__ lut_v, float qm_l, float qv_l, unsigned pf) {
+                                           const LutEnt* __restrict__ lut_v, float qm_l, float qv_l, unsigned pf,
+                                           const PeerStores& ps) {
   const size_t e0 = (size_t)gl * 128 + (size_t)l16 * 8;
   uint4* pp = reinterpret_cast<uint4*>(reinterpret_cast<unsigned short*>(t.p) + e0);
   const uint4* gp = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(t.g) + e0);
@@ -125,7 +126,11 @@ __device__ __forceinline__ void h_group_x2(const TDesc& t, unsigned gl, int l16,
     const f2 pj = widen2<T>(pw[j]);
     po[j] = narrow2<T>(fused_pair_x2<APX>(c, gj, pj, f2_pack(m0a, m0b), f2_pack(v0a, v0b), m[j], v[j], am, av));
   }
-  *pp = make_uint4(po[0], po[1], po[2], po[3]);
+  const uint4 pnew = make_uint4(po[0], po[1], po[2], po[3]);
+  *pp = pnew;
+  if (PEERS) {
+    for (int i = 0; i < ps.n; ++i) *reinterpret_cast<uint4*>(reinterpret_cast<char*>(pp) + ps.off[i]) = pnew;
+  }
   am = hw_max(am, hmask);
   av = hw_max(av, hmask);
   uint32_t mo = 0, vo = 0;
@@ -155,7 +160,7 @@ __device__ __forceinline__ void h_group_x2(const TDesc& t, unsigned gl, int l16,
 // division, the reference's search (fused_adamw_kernel.cu:114,130-143,160-165).
 template <typename T>
 __device__ __noinline__ void h_group_generic(const TDesc& t, long long gl, int l16, unsigned hmask, const UConsts& c,
-                                             const QMapSmem& Sm, const QMapSmem& Sv) {
+                                             const QMapSmem& Sm, const QMapSmem& Sv, const PeerStores& ps) {
   const long long e0 = gl * 128 + l16 * 8;
   const long long n = t.numel;
   unsigned short* p16 = reinterpret_cast<unsigned short*>(t.p);
@@ -179,7 +184,9 @@ __device__ __noinline__ void h_group_generic(const TDesc& t, long long gl, int l
       const float v0 = __fmul_rn(Sv.qmap[(vbyte >> (4 * (k & 1))) & 15u], sv);
       m[k] = lerp_m<true>(ce, m0, g);
       v[k] = upd_v2<true>(ce, v0, g);
-      p16[e0 + k] = Half16<T>::narrow(upd_param<true>(ce, Half16<T>::widen(p16[e0 + k]), m[k], v[k]));
+      const unsigned short pn = Half16<T>::narrow(upd_param<true>(ce, Half16<T>::widen(p16[e0 + k]), m[k], v[k]));
+      p16[e0 + k] = pn;
+      for (int i = 0; i < ps.n; ++i) *reinterpret_cast<unsigned short*>(reinterpret_cast<char*>(p16 + e0 + k) + ps.off[i]) = pn;
       am = fmaxf(am, fabsf(m[k]));
       av = fmaxf(av, v[k]);
     }
@@ -211,7 +218,8 @@ __device__ __noinline__ void h_group_generic(const TDesc& t, long long gl, int l
 template <typename T, bool VLIN>
 __device__ __forceinline__ void h_group_fast(const TDesc& t, unsigned gl, int l16, unsigned hmask, const UConsts& c,
                                              const QMapSmem& Sm, const QMapSmem& Sv, const LutEnt* __restrict__ lut_m,
-                                             const LutEnt* __restrict__ lut_v, float qm_l, float qv_l, unsigned pf) {
+                                             const LutEnt* __restrict__ lut_v, float qm_l, float qv_l, unsigned pf,
+                                             const PeerStores& ps) {
   const size_t e0 = (size_t)gl * 128 + (size_t)l16 * 8;
   uint4* pp = reinterpret_cast<uint4*>(reinterpret_cast<unsigned short*>(t.p) + e0);
   const uint4* gp = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(t.g) + e0);
@@ -243,7 +251,9 @@ __device__ __forceinline__ void h_group_fast(const TDesc& t, unsigned gl, int l1
     am = fmaxf(am, fabsf(m[k]));
     av = fmaxf(av, v[k]);
   }
-  *pp = narrow8<T>(p);
+  const uint4 pnew = narrow8<T>(p);
+  *pp = pnew;
+  for (int i = 0; i < ps.n; ++i) *reinterpret_cast<uint4*>(reinterpret_cast<char*>(pp) + ps.off[i]) = pnew;
   am = hw_max(am, hmask);
   av = hw_max(av, hmask);
   uint32_t mo = 0, vo = 0;
@@ -276,7 +286,7 @@ __device__ __forceinline__ void h_group_fast(const TDesc& t, unsigned gl, int l1
 
 // fp32 moments (the numel <= threshold fallback) next to 16-bit parameters.
 template <typename T>
-__device__ __forceinline__ void h_group_fp32(const TDesc& t, long long gl, int l16, const UConsts& c) {
+__device__ __forceinline__ void h_group_fp32(const TDesc& t, long long gl, int l16, const UConsts& c, const PeerStores& ps) {
   const long long e0 = gl * 128 + l16 * 8;
   unsigned short* p16 = reinterpret_cast<unsigned short*>(t.p);
   const unsigned short* g16 = reinterpret_cast<const unsigned short*>(t.g);
@@ -291,15 +301,20 @@ __device__ __forceinline__ void h_group_fp32(const TDesc& t, long long gl, int l
       const float v = upd_v2<true>(c, vp[e], g);
       mp[e] = m;
       vp[e] = v;
-      p16[e] = Half16<T>::narrow(upd_param<true>(c, Half16<T>::widen(p16[e]), m, v));
+      const unsigned short pn = Half16<T>::narrow(upd_param<true>(c, Half16<T>::widen(p16[e]), m, v));
+      p16[e] = pn;
+      for (int i = 0; i < ps.n; ++i) *reinterpret_cast<unsigned short*>(reinterpret_cast<char*>(p16 + e) + ps.off[i]) = pn;
     }
   }
 }
 
-template <typename T, bool HAS_Q4, bool APX>
+// PEERS: every updated parameter also goes to the ZeRO-1 peers (ps); without it ps.n is 0 and the stores vanish
+// from the packed path.
+template <typename T, bool HAS_Q4, bool APX, bool PEERS>
 __global__ void __launch_bounds__(CTA_THREADS, CTAS_PER_SM)
 adamw4bit_half_kernel(const __grid_constant__ Table tab, const float* __restrict__ qmap_m,
-                      const float* __restrict__ qmap_v, const UConsts cin, long long gbeg, long long gend) {
+                      const float* __restrict__ qmap_v, const UConsts cin, long long gbeg, long long gend,
+                      const PeerStores ps) {
   const UConsts c = fused_consts(cin);
   extern __shared__ __align__(16) unsigned char dyn_smem[];
   __shared__ QMapSmem Sm, Sv;
@@ -337,45 +352,45 @@ adamw4bit_half_kernel(const __grid_constant__ Table tab, const float* __restrict
           const unsigned st = (unsigned)stride;
           if (c.f_fast && vlin) {
             for (; gl < lim; gl += st)
-              h_group_x2<T, true, APX>(t, gl, l16, hmask, k2, Sm, Sv, lut_m, lut_v, qm_l, qv_l,
-                                  (gl + PF_DIST * st < lim) ? PF_DIST * st : 0u);
+              h_group_x2<T, true, APX, PEERS>(t, gl, l16, hmask, k2, Sm, Sv, lut_m, lut_v, qm_l, qv_l,
+                                              (gl + PF_DIST * st < lim) ? PF_DIST * st : 0u, ps);
           } else if (c.f_fast) {
             for (; gl < lim; gl += st)
-              h_group_x2<T, false, APX>(t, gl, l16, hmask, k2, Sm, Sv, lut_m, lut_v, qm_l, qv_l,
-                                   (gl + PF_DIST * st < lim) ? PF_DIST * st : 0u);
+              h_group_x2<T, false, APX, PEERS>(t, gl, l16, hmask, k2, Sm, Sv, lut_m, lut_v, qm_l, qv_l,
+                                               (gl + PF_DIST * st < lim) ? PF_DIST * st : 0u, ps);
           } else if (vlin) {  // hyper-parameters outside the short sequences' domain: IEEE sqrt and division
             for (; gl < lim; gl += st)
               h_group_fast<T, true>(t, gl, l16, hmask, c, Sm, Sv, lut_m, lut_v, qm_l, qv_l,
-                                    (gl + PF_DIST * st < lim) ? PF_DIST * st : 0u);
+                                    (gl + PF_DIST * st < lim) ? PF_DIST * st : 0u, ps);
           } else {
             for (; gl < lim; gl += st)
               h_group_fast<T, false>(t, gl, l16, hmask, c, Sm, Sv, lut_m, lut_v, qm_l, qv_l,
-                                     (gl + PF_DIST * st < lim) ? PF_DIST * st : 0u);
+                                     (gl + PF_DIST * st < lim) ? PF_DIST * st : 0u, ps);
           }
           gi = tstart + gl;
         }
       }
-      for (; gi < tend; gi += stride) h_group_generic<T>(t, gi - tstart, l16, hmask, c, Sm, Sv);
+      for (; gi < tend; gi += stride) h_group_generic<T>(t, gi - tstart, l16, hmask, c, Sm, Sv, ps);
     } else {
-      for (; gi < tend; gi += stride) h_group_fp32<T>(t, gi - tstart, l16, c);
+      for (; gi < tend; gi += stride) h_group_fp32<T>(t, gi - tstart, l16, c, ps);
     }
   }
 }
 
-template <typename T, bool HAS_Q4, bool APX>
+template <typename T, bool HAS_Q4, bool APX, bool PEERS>
 static cudaError_t launch_half(const Table& tab, unsigned grid, const float* qm, const float* qv, const UConsts& c,
-                               long long lo, long long hi, cudaStream_t st) {
+                               long long lo, long long hi, cudaStream_t st, const PeerStores& ps) {
   static bool attr_set[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   const size_t smem = HAS_Q4 ? H_DYN_SMEM : 0;
   if (HAS_Q4 && dev >= 0 && dev < 64 && !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(adamw4bit_half_kernel<T, HAS_Q4, APX>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(adamw4bit_half_kernel<T, HAS_Q4, APX, PEERS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)H_DYN_SMEM);
     if (e != cudaSuccess) return e;
     attr_set[dev] = true;
   }
-  adamw4bit_half_kernel<T, HAS_Q4, APX><<<grid, CTA_THREADS, smem, st>>>(tab, qm, qv, c, lo, hi);
+  adamw4bit_half_kernel<T, HAS_Q4, APX, PEERS><<<grid, CTA_THREADS, smem, st>>>(tab, qm, qv, c, lo, hi, ps);
   return cudaGetLastError();
 }
 
@@ -385,23 +400,25 @@ using namespace lpmm_b200;
 
 template <typename T>
 static cudaError_t launch_half_any(bool any_q4, bool apx, const Table& tab, unsigned grid, const float* qm, const float* qv,
-                                   const UConsts& c, long long lo, long long hi, cudaStream_t st) {
-  if (!any_q4) return launch_half<T, false, false>(tab, grid, qm, qv, c, lo, hi, st);
-  return apx ? launch_half<T, true, true>(tab, grid, qm, qv, c, lo, hi, st)
-             : launch_half<T, true, false>(tab, grid, qm, qv, c, lo, hi, st);
+                                   const UConsts& c, long long lo, long long hi, cudaStream_t st, const PeerStores& ps) {
+  if (ps.n > 0)  // with peers always the 4-bit instantiation (it also steps fp32-state tensors); the maps are required
+    return apx ? launch_half<T, true, true, true>(tab, grid, qm, qv, c, lo, hi, st, ps)
+               : launch_half<T, true, false, true>(tab, grid, qm, qv, c, lo, hi, st, ps);
+  if (!any_q4) return launch_half<T, false, false, false>(tab, grid, qm, qv, c, lo, hi, st, ps);
+  return apx ? launch_half<T, true, true, false>(tab, grid, qm, qv, c, lo, hi, st, ps)
+             : launch_half<T, true, false, false>(tab, grid, qm, qv, c, lo, hi, st, ps);
 }
 
-extern "C" int lpmm_b200_adamw4bit_multi_tensor_16bit_flags(const lpmm_b200_tensor* ts, int n, int dtype,
-                                                            const float* qmap_m, const float* qmap_v, lpmm_b200_hyper h,
-                                                            int64_t group_begin, int64_t group_end, uint32_t flags,
-                                                            void* stream) {
+static int half_entry(const lpmm_b200_tensor* ts, int n, int dtype, const float* qmap_m, const float* qmap_v,
+                      lpmm_b200_hyper h, int64_t group_begin, int64_t group_end, uint32_t flags, void* stream,
+                      const PeerStores& ps) {
   if (dtype != LPMM_B200_DTYPE_BF16 && dtype != LPMM_B200_DTYPE_FP16) return LPMM_B200_ERR_BAD_KIND;
   if (flags & ~(uint32_t)LPMM_B200_FLAG_PARAMS_WITHIN_TOLERANCE) return LPMM_B200_ERR_BAD_KIND;
   bool any_q4 = false;
   int64_t total = 0;
   const int rc = check_tensor_list(ts, n, true, &any_q4, &total);
   if (rc != LPMM_B200_OK) return rc;
-  if (any_q4 && (!qmap_m || !qmap_v)) return LPMM_B200_ERR_NULL_POINTER;
+  if ((any_q4 || ps.n > 0) && (!qmap_m || !qmap_v)) return LPMM_B200_ERR_NULL_POINTER;
   if (group_end < 0) group_end = total;
   if (group_begin < 0 || group_begin > group_end || group_end > total) return LPMM_B200_ERR_BAD_SIZE;
   if (group_begin == group_end) return LPMM_B200_OK;
@@ -418,11 +435,34 @@ extern "C" int lpmm_b200_adamw4bit_multi_tensor_16bit_flags(const lpmm_b200_tens
     if (!w.work) continue;
     const unsigned grid = multi_grid(w);
     const cudaError_t e = dtype == LPMM_B200_DTYPE_BF16
-                              ? launch_half_any<__nv_bfloat16>(w.any_q4, apx, tab, grid, qmap_m, qmap_v, c, w.lo, w.hi, st)
-                              : launch_half_any<__half>(w.any_q4, apx, tab, grid, qmap_m, qmap_v, c, w.lo, w.hi, st);
+                              ? launch_half_any<__nv_bfloat16>(w.any_q4, apx, tab, grid, qmap_m, qmap_v, c, w.lo, w.hi, st, ps)
+                              : launch_half_any<__half>(w.any_q4, apx, tab, grid, qmap_m, qmap_v, c, w.lo, w.hi, st, ps);
     LPMM_CUDA_TRY(e);
   }
   return LPMM_B200_OK;
+}
+
+extern "C" int lpmm_b200_adamw4bit_multi_tensor_16bit_flags(const lpmm_b200_tensor* ts, int n, int dtype,
+                                                            const float* qmap_m, const float* qmap_v, lpmm_b200_hyper h,
+                                                            int64_t group_begin, int64_t group_end, uint32_t flags,
+                                                            void* stream) {
+  return half_entry(ts, n, dtype, qmap_m, qmap_v, h, group_begin, group_end, flags, stream, PeerStores{});
+}
+
+extern "C" int lpmm_b200_adamw4bit_multi_tensor_16bit_peers(const lpmm_b200_tensor* ts, int n, int dtype,
+                                                            const float* qmap_m, const float* qmap_v, lpmm_b200_hyper h,
+                                                            int64_t group_begin, int64_t group_end,
+                                                            const int64_t* peer_byte_offsets, int n_peers, uint32_t flags,
+                                                            void* stream) {
+  if (n_peers < 0 || n_peers > 7) return LPMM_B200_ERR_BAD_SIZE;
+  if (n_peers > 0 && !peer_byte_offsets) return LPMM_B200_ERR_NULL_POINTER;
+  PeerStores ps = {};
+  ps.n = n_peers;
+  for (int i = 0; i < n_peers; ++i) {
+    if (peer_byte_offsets[i] % 16 != 0) return LPMM_B200_ERR_BAD_SIZE;  // keeps the 128-bit stores aligned
+    ps.off[i] = peer_byte_offsets[i];
+  }
+  return half_entry(ts, n, dtype, qmap_m, qmap_v, h, group_begin, group_end, flags, stream, ps);
 }
 
 extern "C" int lpmm_b200_adamw4bit_multi_tensor_16bit(const lpmm_b200_tensor* ts, int n, int dtype, const float* qmap_m,

@@ -77,17 +77,35 @@ __global__ void __launch_bounds__(FT) f_sums_kernel(const FDesc* __restrict__ d,
     float acc[8];
 #pragma unroll
     for (int k = 0; k < 8; ++k) acc[k] = 0.0f;
+    // the loads of the next pair of rows are issued before the sums of the current pair (two pairs in flight)
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 na0 = zero4, na1 = zero4, nb0 = zero4, nb1 = zero4;
+    {
+      const long long ra = r_begin + ty, rc = r_begin + ty_count + ty;
+      if (active && ra < r_end) {
+        na0 = *reinterpret_cast<const float4*>(t.g + ra * C + c0);
+        na1 = *reinterpret_cast<const float4*>(t.g + ra * C + c0 + 4);
+      }
+      if (active && rc < r_end) {
+        nb0 = *reinterpret_cast<const float4*>(t.g + rc * C + c0);
+        nb1 = *reinterpret_cast<const float4*>(t.g + rc * C + c0 + 4);
+      }
+    }
     for (long long rb = r_begin; rb < r_end; rb += 2 * ty_count) {
       const long long ra = rb + ty, rc = rb + ty_count + ty;
-      const bool ha = active && ra < r_end, hc = active && rc < r_end;
-      float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0, b0 = a0, b1 = a0;
-      if (ha) {
-        a0 = *reinterpret_cast<const float4*>(t.g + ra * C + c0);
-        a1 = *reinterpret_cast<const float4*>(t.g + ra * C + c0 + 4);
-      }
-      if (hc) {
-        b0 = *reinterpret_cast<const float4*>(t.g + rc * C + c0);
-        b1 = *reinterpret_cast<const float4*>(t.g + rc * C + c0 + 4);
+      const float4 a0 = na0, a1 = na1, b0 = nb0, b1 = nb1;
+      {
+        const long long rn = rb + 2 * ty_count;
+        const long long ra2 = rn + ty, rc2 = rn + ty_count + ty;
+        na0 = na1 = nb0 = nb1 = zero4;
+        if (active && ra2 < r_end) {
+          na0 = *reinterpret_cast<const float4*>(t.g + ra2 * C + c0);
+          na1 = *reinterpret_cast<const float4*>(t.g + ra2 * C + c0 + 4);
+        }
+        if (active && rc2 < r_end) {
+          nb0 = *reinterpret_cast<const float4*>(t.g + rc2 * C + c0);
+          nb1 = *reinterpret_cast<const float4*>(t.g + rc2 * C + c0 + 4);
+        }
       }
       const float ga[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
       const float gb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
@@ -156,7 +174,15 @@ __global__ void __launch_bounds__(FT) f_row_mean_kernel(const FDesc* __restrict_
     if ((int)threadIdx.x < o) red[threadIdx.x] = __fadd_rn(red[threadIdx.x], red[threadIdx.x + o]);
     __syncthreads();
   }
-  if (threadIdx.x == 0) *t.row_mean = __fdiv_rn(red[0], (float)t.R);
+  if (threadIdx.x == 0) {
+    red[0] = __fdiv_rn(red[0], (float)t.R);
+    *t.row_mean = red[0];
+  }
+  __syncthreads();
+  // row[r] / mean(row) for every row, for the update pass of wide matrices (f_update2_kernel); the first slot of
+  // the row partials is free again after pass 2
+  const float mean = red[0];
+  for (long long j = threadIdx.x; j < t.R; j += FT) t.row_part[j] = __fdiv_rn(t.row[j], mean);
 }
 
 
@@ -273,6 +299,125 @@ __global__ void __launch_bounds__(FT, 4) f_update_kernel(const FDesc* __restrict
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Pass 4 for matrices whose row length is a multiple of 128 with a 4-bit first moment: a 128-element group lies
+// inside one row, so the half-warp shares row[r] / mean(row) (read from the vector pass 3 left in row_part) and a
+// lane's 8 elements are 8 consecutive columns.  Shape of the fused multi-tensor step (adamw4bit.cu): descriptors in
+// the launch parameters, persistent 1024-thread CTAs, 256-bit accesses, dequantisation by shuffle, packed fp32x2
+// arithmetic, table look-up for the codes.  Arithmetic is that of f_unit's FULL lanes, bit for bit.
+// ---------------------------------------------------------------------------------------------------------
+constexpr int F2_MAX = 400;
+constexpr int F2T = 1024;
+constexpr int F2_HW = F2T / 16;
+
+struct F2Desc {
+  float* p;
+  const float* g;
+  uint32_t* m;
+  float* msc;
+  const float* rowf;   // row[r] / mean(row)
+  const float* col;
+  long long ustart;
+  int gpr;             // groups per row: C / 128
+  int pad_;
+};
+struct F2Table {
+  int n;
+  int pad_;
+  long long total;
+  F2Desc t[F2_MAX];
+};
+
+__device__ __forceinline__ void f2_group(const F2Desc& t, unsigned u, unsigned r, unsigned cb, int l16, unsigned hmask,
+                                         const UConsts2& c2, const QMapSmem& Sm, const LutEnt* __restrict__ lut_m,
+                                         bool lut_ok, float qm_l, unsigned pf) {
+  const size_t e0 = (size_t)u * 128 + (size_t)l16 * 8;
+  float* pp = t.p + e0;
+  const float* gp = t.g + e0;
+  uint32_t* mcp = t.m + (size_t)u * 16 + l16;
+  f2x4 p = ldg_f2x4(pp);
+  const f2x4 g = ldg_f2x4(gp);
+  const uint32_t mc = *mcp;
+  const float pm = __fmul_rn(qm_l, t.msc[u]);
+  const f2 rf2 = f2_splat(__ldg(t.rowf + r));
+  const f2x4 cv = ldg_f2x4(t.col + (size_t)cb * 128 + (size_t)l16 * 8);
+  if (pf) {
+    prefetch_l2(pp + (size_t)pf * 128);
+    prefetch_l2(gp + (size_t)pf * 128);
+    prefetch_l2(mcp + (size_t)pf * 16);
+  }
+  f2 m[4];
+  float am = 0.0f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float m0a = __shfl_sync(hmask, pm, (int)(mc >> (8 * j)), 16);
+    const float m0b = __shfl_sync(hmask, pm, (int)(mc >> (8 * j + 4)), 16);
+    m[j] = lerp_pair(c2, g.v[j], f2_pack(m0a, m0b), am);
+    param_pair(c2, p.v[j], m[j], f2_mul(rf2, cv.v[j]));
+  }
+  stg_f2x4(pp, p);
+  am = hw_max(am, hmask);
+  uint32_t mo = 0;
+  if (udiv_ok(am)) {
+    const f2 r2 = f2_splat(rcp_nr(am)), nam2 = f2_splat(-am);
+#pragma unroll
+    for (int j = 3; j >= 0; --j) {
+      f2 q = f2_mul(m[j], r2);
+      q = f2_fma(f2_fma(q, nam2, m[j]), r2, q);
+      float qa, qb;
+      f2_unpack(q, qa, qb);
+      mo = (mo << 4) + (uint32_t)(lut_ok ? lut_code(lut_m, qb) : code16(Sm.mids, qb));
+      mo = (mo << 4) + (uint32_t)(lut_ok ? lut_code(lut_m, qa) : code16(Sm.mids, qa));
+    }
+    if (am == 0.0f) mo = 0xFFFFFFFFu;  // 0/0 = NaN -> code 15 for the whole group
+  } else {
+#pragma unroll
+    for (int j = 3; j >= 0; --j) {
+      float ma, mb;
+      f2_unpack(m[j], ma, mb);
+      mo = (mo << 4) + (uint32_t)code16(Sm.mids, __fdiv_rn(mb, am));
+      mo = (mo << 4) + (uint32_t)code16(Sm.mids, __fdiv_rn(ma, am));
+    }
+  }
+  *mcp = mo;
+  if (l16 == 0) t.msc[u] = am;
+}
+
+__global__ void __launch_bounds__(F2T, 1) f_update2_kernel(const __grid_constant__ F2Table tab,
+                                                           const float* __restrict__ qmap_m, const UConsts c) {
+  extern __shared__ __align__(16) unsigned char dyn_smem[];
+  __shared__ QMapSmem Sm;
+  LutEnt* lut_m = reinterpret_cast<LutEnt*>(dyn_smem);
+  lut_build(Sm, lut_m, qmap_m);
+  const bool lut_ok = Sm.valid != 0;
+  const UConsts2 c2 = make_consts2(c);
+  const int l16 = threadIdx.x & 15;
+  const unsigned hmask = 0xFFFFu << (threadIdx.x & 16);
+  const float qm_l = Sm.qmap[l16];
+  long long gi = (long long)blockIdx.x * F2_HW + (threadIdx.x >> 4);
+  const unsigned stride = gridDim.x * F2_HW;
+  for (int ti = 0; ti < tab.n; ++ti) {
+    const F2Desc& t = tab.t[ti];
+    const long long uend = (ti + 1 < tab.n) ? tab.t[ti + 1].ustart : tab.total;
+    if (gi >= uend) continue;
+    unsigned u = (unsigned)(gi - t.ustart);
+    const unsigned lim = (unsigned)(uend - t.ustart);
+    const unsigned gpr = (unsigned)t.gpr;
+    unsigned r = u / gpr, cb = u - r * gpr;
+    const unsigned sr = stride / gpr, sc = stride - sr * gpr;
+    for (; u < lim; u += stride) {
+      f2_group(t, u, r, cb, l16, hmask, c2, Sm, lut_m, lut_ok, qm_l, (u + stride < lim) ? stride : 0u);
+      cb += sc;
+      r += sr;
+      if (cb >= gpr) {
+        cb -= gpr;
+        ++r;
+      }
+    }
+    gi = t.ustart + u;
+  }
+}
+
 static inline int64_t f_align(int64_t x) { return (x + 63) & ~(int64_t)63; }  // floats: 256-byte granules
 
 }  // namespace lpmm_b200
@@ -322,17 +467,32 @@ extern "C" int lpmm_b200_factored_multi_step(const lpmm_b200_step_tensor* const*
   if ((uintptr_t)scratch & 255) return LPMM_B200_ERR_BAD_SIZE;
   cudaStream_t st = (cudaStream_t)stream;
   static thread_local std::vector<FDesc> host;
+  static thread_local std::vector<int> order;
   host.resize(n);
+  order.clear();
+  const UConsts c = make_consts(beta1, beta2, lr, weight_decay, eps, step);
+  // Matrices whose rows are whole 128-element groups, with a 4-bit first moment, take f_update2_kernel; they come
+  // first in the table.  That kernel has no scalar path: it needs the short exact sequences and 32-byte alignment.
+  auto wide = [&](const lpmm_b200_step_tensor* t) {
+    return c.fast != 0 && t->m_mode == LPMM_B200_STATE_GROUP4 && t->shape[1] % 128 == 0 && t->numel < ((long long)1 << 37) &&
+           ((((uintptr_t)t->p | (uintptr_t)t->g | (uintptr_t)t->col) & 31) == 0);
+  };
+  for (int i = 0; i < n; ++i)
+    if (wide(ts[i])) order.push_back(i);
+  const int n_wide = (int)order.size();
+  for (int i = 0; i < n; ++i)
+    if (!wide(ts[i])) order.push_back(i);
   const int64_t table_bytes = (int64_t)(((sizeof(FDesc) * (size_t)n) + 255) & ~(size_t)255);
   float* fbase = reinterpret_cast<float*>(static_cast<char*>(scratch) + table_bytes);
-  const long long target_tiles = (long long)num_sms() * 6;
+  // about twenty tiles per SM; a grid of resident CTAs (as many as the SMs hold) strides over them
+  const long long target_tiles = (long long)num_sms() * 20;
   long long per_tile = (total_elems + target_tiles - 1) / target_tiles;
   if (per_tile < 8192) per_tile = 8192;
-  long long units = 0, tiles = 0, rc_total = 0;
+  long long units = 0, tiles = 0, rc_total = 0;  // units: of the matrices that are NOT wide, numbered from 0
   int64_t foff = 0;
-  for (int i = 0; i < n; ++i) {
-    const lpmm_b200_step_tensor* t = ts[i];
-    FDesc& d = host[i];
+  for (int k = 0; k < n; ++k) {
+    const lpmm_b200_step_tensor* t = ts[order[k]];
+    FDesc& d = host[k];
     d.p = t->p;
     d.g = t->g;
     d.m = reinterpret_cast<uint8_t*>(t->m);
@@ -364,14 +524,23 @@ extern "C" int lpmm_b200_factored_multi_step(const lpmm_b200_step_tensor* const*
     d.ustart = units;
     d.tstart = tiles;
     d.rstart = rc_total;
-    units += (t->numel + 127) / 128;
+    if (k >= n_wide) units += (t->numel + 127) / 128;
     tiles += (long long)d.tiles_x * d.tiles_y;
     rc_total += (long long)d.R + d.C;
   }
   LPMM_CUDA_TRY(cudaMemcpyAsync(scratch, host.data(), sizeof(FDesc) * (size_t)n, cudaMemcpyHostToDevice, st));
   const FDesc* dev = reinterpret_cast<const FDesc*>(scratch);
-  const UConsts c = make_consts(beta1, beta2, lr, weight_decay, eps, step);
-  const long long sgrid = tiles < target_tiles ? tiles : target_tiles;
+  static int sums_ctas[64] = {};  // CTAs of the sums kernel one SM holds, per device
+  int cur = 0;
+  cudaGetDevice(&cur);
+  int per_sm = (cur >= 0 && cur < 64) ? sums_ctas[cur] : 0;
+  if (per_sm == 0) {
+    LPMM_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, f_sums_kernel, FT, 0));
+    if (per_sm < 1) per_sm = 1;
+    if (cur >= 0 && cur < 64) sums_ctas[cur] = per_sm;
+  }
+  const long long resident = (long long)num_sms() * per_sm;
+  const long long sgrid = tiles < resident ? tiles : resident;
   f_sums_kernel<<<(unsigned)sgrid, FT, 0, st>>>(dev, n, tiles);
   LPMM_CUDA_TRY(cudaGetLastError());
   long long fgrid = (rc_total + FT - 1) / FT;
@@ -385,12 +554,41 @@ extern "C" int lpmm_b200_factored_multi_step(const lpmm_b200_step_tensor* const*
   cudaGetDevice(&devi);
   if (devi >= 0 && devi < 64 && !attr_set[devi]) {
     LPMM_CUDA_TRY(cudaFuncSetAttribute(f_update_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)F_DYN_SMEM));
+    LPMM_CUDA_TRY(cudaFuncSetAttribute(f_update2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)F_DYN_SMEM));
     attr_set[devi] = true;
   }
-  long long ugrid = (units + FT / 16 - 1) / (FT / 16);
-  const long long ucap = (long long)num_sms() * 4;
-  if (ugrid > ucap) ugrid = ucap;
-  f_update_kernel<<<(unsigned)ugrid, FT, F_DYN_SMEM, st>>>(dev, n, units, any_q ? qmap_m : nullptr, c);
-  LPMM_CUDA_TRY(cudaGetLastError());
+  static thread_local F2Table tab;
+  for (int k0 = 0; k0 < n_wide; k0 += F2_MAX) {
+    const int cnt = (n_wide - k0 < F2_MAX) ? n_wide - k0 : F2_MAX;
+    long long g2 = 0;
+    for (int k = 0; k < cnt; ++k) {
+      const FDesc& d = host[k0 + k];
+      F2Desc& w = tab.t[k];
+      w.p = d.p;
+      w.g = d.g;
+      w.m = reinterpret_cast<uint32_t*>(d.m);
+      w.msc = d.m_max1;
+      w.rowf = d.row_part;
+      w.col = d.col;
+      w.ustart = g2;
+      w.gpr = d.C / 128;
+      w.pad_ = 0;
+      g2 += d.n / 128;
+    }
+    tab.n = cnt;
+    tab.pad_ = 0;
+    tab.total = g2;
+    long long grid2 = (g2 + F2_HW - 1) / F2_HW;
+    if (grid2 > num_sms()) grid2 = num_sms();
+    f_update2_kernel<<<(unsigned)grid2, F2T, F_DYN_SMEM, st>>>(tab, qmap_m, c);
+    LPMM_CUDA_TRY(cudaGetLastError());
+  }
+  if (n > n_wide) {
+    long long ugrid = (units + FT / 16 - 1) / (FT / 16);
+    const long long ucap = (long long)num_sms() * 4;
+    if (ugrid > ucap) ugrid = ucap;
+    f_update_kernel<<<(unsigned)ugrid, FT, F_DYN_SMEM, st>>>(dev + n_wide, n - n_wide, units, any_q ? qmap_m : nullptr, c);
+    LPMM_CUDA_TRY(cudaGetLastError());
+  }
   return LPMM_B200_OK;
 }

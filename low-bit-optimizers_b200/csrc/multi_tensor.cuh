@@ -34,6 +34,15 @@ struct Table {
 };
 
 
+// Peers of a ZeRO-1 step for 16-bit parameters: byte offsets from an address in this GPU's flat parameter buffer to
+// the same element in each peer's buffer (peer-mapped memory).  Every updated parameter is stored locally and at
+// each of these offsets.
+struct PeerStores {
+  int n;
+  int pad_;
+  long long off[7];
+};
+
 __device__ __forceinline__ float hw_max(float x, unsigned mask) {
 #pragma unroll
   for (int o = 8; o; o >>= 1) x = fmaxf(x, __shfl_xor_sync(mask, x, o, 16));

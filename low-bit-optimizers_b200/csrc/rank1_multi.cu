@@ -113,26 +113,51 @@ __global__ void __launch_bounds__(R1T) r1_stats_kernel(const R1Desc* __restrict_
     const long long r_begin = tile_y * t.rows_per_tile;
     const long long r_end = (r_begin + t.rows_per_tile < t.R) ? r_begin + t.rows_per_tile : t.R;
     const int seg = tx_count < 32 ? tx_count : 32;  // lanes that share a row inside a warp
-    // all lanes of a warp make the same number of trips (the shuffles below need the whole warp)
+    // all lanes of a warp make the same number of trips (the shuffles below need the whole warp); the loads of the
+    // next pair of rows are issued before the arithmetic of the current pair
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 nga0 = zero4, nga1 = zero4, ngc0 = zero4, ngc1 = zero4;
+    uint32_t nca = 0, ncc = 0;
+    float noa = 0.0f, noc = 0.0f;
+    {
+      const long long ra = r_begin + ty, rc = r_begin + ty_count + ty;
+      if (active && ra < r_end) {
+        const long long e0 = ra * C + c0;
+        nga0 = *reinterpret_cast<const float4*>(t.g + e0);
+        nga1 = *reinterpret_cast<const float4*>(t.g + e0 + 4);
+        nca = *reinterpret_cast<const uint32_t*>(t.v + (e0 >> 1));
+        noa = __ldg(t.old_r + ra);
+      }
+      if (active && rc < r_end) {
+        const long long e0 = rc * C + c0;
+        ngc0 = *reinterpret_cast<const float4*>(t.g + e0);
+        ngc1 = *reinterpret_cast<const float4*>(t.g + e0 + 4);
+        ncc = *reinterpret_cast<const uint32_t*>(t.v + (e0 >> 1));
+        noc = __ldg(t.old_r + rc);
+      }
+    }
     for (long long rb = r_begin; rb < r_end; rb += 2 * ty_count) {
       const long long ra = rb + ty, rc = rb + ty_count + ty;
       const bool ha = active && ra < r_end, hc = active && rc < r_end;
-      float4 ga0 = make_float4(0.f, 0.f, 0.f, 0.f), ga1 = ga0, gc0 = ga0, gc1 = ga0;
-      uint32_t ca = 0, cc = 0;
-      float oa = 0.0f, oc = 0.0f;
-      if (ha) {
-        const long long e0 = ra * C + c0;
-        ga0 = *reinterpret_cast<const float4*>(t.g + e0);
-        ga1 = *reinterpret_cast<const float4*>(t.g + e0 + 4);
-        ca = *reinterpret_cast<const uint32_t*>(t.v + (e0 >> 1));
-        oa = __ldg(t.old_r + ra);
-      }
-      if (hc) {
-        const long long e0 = rc * C + c0;
-        gc0 = *reinterpret_cast<const float4*>(t.g + e0);
-        gc1 = *reinterpret_cast<const float4*>(t.g + e0 + 4);
-        cc = *reinterpret_cast<const uint32_t*>(t.v + (e0 >> 1));
-        oc = __ldg(t.old_r + rc);
+      const float4 ga0 = nga0, ga1 = nga1, gc0 = ngc0, gc1 = ngc1;
+      const uint32_t ca = nca, cc = ncc;
+      const float oa = noa, oc = noc;
+      {
+        const long long ra2 = ra + 2 * ty_count, rc2 = rc + 2 * ty_count;
+        if (active && ra2 < r_end) {
+          const long long e0 = ra2 * C + c0;
+          nga0 = *reinterpret_cast<const float4*>(t.g + e0);
+          nga1 = *reinterpret_cast<const float4*>(t.g + e0 + 4);
+          nca = *reinterpret_cast<const uint32_t*>(t.v + (e0 >> 1));
+          noa = __ldg(t.old_r + ra2);
+        }
+        if (active && rc2 < r_end) {
+          const long long e0 = rc2 * C + c0;
+          ngc0 = *reinterpret_cast<const float4*>(t.g + e0);
+          ngc1 = *reinterpret_cast<const float4*>(t.g + e0 + 4);
+          ncc = *reinterpret_cast<const uint32_t*>(t.v + (e0 >> 1));
+          noc = __ldg(t.old_r + rc2);
+        }
       }
       float ma = ha ? r1_row_pass<A>(t, ra, c0, qv, col_old, col_max, c, ga0, ga1, ca, oa) : 0.0f;
       float mc = hc ? r1_row_pass<A>(t, rc, c0, qv, col_old, col_max, c, gc0, gc1, cc, oc) : 0.0f;
@@ -337,6 +362,186 @@ __global__ void __launch_bounds__(R1T, 4) r1_update_kernel(const R1Desc* __restr
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------------------
+// Update pass for matrices whose row length is a multiple of 128 (every projection of a transformer): a
+// 128-element group then lies inside one row, so the whole half-warp shares the row maxima and a lane's 8
+// elements are 8 consecutive columns.  The kernel has the shape of the fused multi-tensor step
+// (adamw4bit.cu): descriptors in the launch parameters, persistent 1024-thread CTAs, a half-warp per
+// group, 256-bit accesses of parameters and gradients, dequantisation by shuffle (lane i holds map entry i),
+// packed fp32x2 arithmetic, table look-up for the first-moment codes.  What differs is the second moment:
+// its scale is min(row maximum, column maximum) per element, old ones for dequantisation and the new ones
+// from the statistics pass for requantisation.  Arithmetic is that of r1_unit's FULL lanes, bit for bit.
+// ---------------------------------------------------------------------------------------------------------
+constexpr int R2_MAX = 300;      // descriptors per launch (26.4 KB of the 32 KB parameter space)
+constexpr int R2T = 1024;
+constexpr int R2_HW = R2T / 16;
+
+struct R2Desc {
+  float* p;
+  const float* g;
+  uint32_t* m;          // first-moment codes, one word per lane and group
+  uint32_t* v;
+  float* msc;           // first-moment group maxima
+  const float* old_r;
+  const float* old_c;
+  const float* new_r;
+  const float* new_c;
+  long long ustart;     // first global group of this tensor
+  int gpr;              // groups per row: C / 128
+  int pad_;
+};
+struct R2Table {
+  int n;
+  int pad_;
+  long long total;      // groups in this table
+  R2Desc t[R2_MAX];
+};
+
+template <bool A>
+__device__ __forceinline__ void r2_group(const R2Desc& t, unsigned u, unsigned r, unsigned cb, int l16, unsigned hmask,
+                                         const UConsts2& c2, const Consts2& kf, const QMapSmem& Sm, const QMapSmem& Sv,
+                                         const LutEnt* __restrict__ lut_m, bool lut_ok, bool vlin, float qm_l, float qv_l,
+                                         unsigned pf) {
+  const size_t e0 = (size_t)u * 128 + (size_t)l16 * 8;
+  float* pp = t.p + e0;
+  const float* gp = t.g + e0;
+  uint32_t* mcp = t.m + (size_t)u * 16 + l16;
+  uint32_t* vcp = t.v + (size_t)u * 16 + l16;
+  f2x4 p = ldg_f2x4(pp);
+  const f2x4 g = ldg_f2x4(gp);
+  const uint32_t mc = *mcp;
+  const uint32_t vc = *vcp;
+  const float pm = __fmul_rn(qm_l, t.msc[u]);  // lane i: qmap_m[i] * group maximum
+  const float ro = __ldg(t.old_r + r);
+  const size_t c0 = (size_t)cb * 128 + (size_t)l16 * 8;
+  const float4 o0 = __ldg(reinterpret_cast<const float4*>(t.old_c + c0));
+  const float4 o1 = __ldg(reinterpret_cast<const float4*>(t.old_c + c0 + 4));
+  if (pf) {
+    prefetch_l2(pp + (size_t)pf * 128);
+    prefetch_l2(gp + (size_t)pf * 128);
+    prefetch_l2(mcp + (size_t)pf * 16);
+    prefetch_l2(vcp + (size_t)pf * 16);
+  }
+  const float oc[8] = {o0.x, o0.y, o0.z, o0.w, o1.x, o1.y, o1.z, o1.w};
+  f2 m[4], v[4];
+  float am = 0.0f, av = 0.0f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float m0a = __shfl_sync(hmask, pm, (int)(mc >> (8 * j)), 16);  // source lane = code (mod 16)
+    const float m0b = __shfl_sync(hmask, pm, (int)(mc >> (8 * j + 4)), 16);
+    const float qa = __shfl_sync(hmask, qv_l, (int)(vc >> (8 * j)), 16);
+    const float qb = __shfl_sync(hmask, qv_l, (int)(vc >> (8 * j + 4)), 16);
+    const f2 v0 = f2_mul(f2_pack(qa, qb), f2_pack(fminf(ro, oc[2 * j]), fminf(ro, oc[2 * j + 1])));
+    if (A) p.v[j] = fused_pair_x2(kf, g.v[j], p.v[j], f2_pack(m0a, m0b), v0, m[j], v[j], am, av);
+    else update_pair(c2, g.v[j], p.v[j], f2_pack(m0a, m0b), v0, m[j], v[j], am, av);
+  }
+  stg_f2x4(pp, p);
+  // first moment: group maximum over the half-warp, codes of this lane
+  am = hw_max(am, hmask);
+  uint32_t mo = 0;
+  if (udiv_ok(am)) {
+    const f2 r2 = f2_splat(rcp_nr(am)), nam2 = f2_splat(-am);
+#pragma unroll
+    for (int j = 3; j >= 0; --j) {
+      f2 q = f2_mul(m[j], r2);
+      q = f2_fma(f2_fma(q, nam2, m[j]), r2, q);
+      float qa, qb;
+      f2_unpack(q, qa, qb);
+      mo = (mo << 4) + (uint32_t)(lut_ok ? lut_code(lut_m, qb) : code16(Sm.mids, qb));
+      mo = (mo << 4) + (uint32_t)(lut_ok ? lut_code(lut_m, qa) : code16(Sm.mids, qa));
+    }
+    if (am == 0.0f) mo = 0xFFFFFFFFu;  // 0/0 = NaN -> code 15 for the whole group
+  } else {
+#pragma unroll
+    for (int j = 3; j >= 0; --j) {
+      float ma, mb;
+      f2_unpack(m[j], ma, mb);
+      mo = (mo << 4) + (uint32_t)code16(Sm.mids, __fdiv_rn(mb, am));
+      mo = (mo << 4) + (uint32_t)code16(Sm.mids, __fdiv_rn(ma, am));
+    }
+  }
+  // second moment: v / min(new row maximum, new column maximum) per element
+  const float rn = __ldg(t.new_r + r);
+  const float4 n0 = __ldg(reinterpret_cast<const float4*>(t.new_c + c0));
+  const float4 n1 = __ldg(reinterpret_cast<const float4*>(t.new_c + c0 + 4));
+  const float nc[8] = {n0.x, n0.y, n0.z, n0.w, n1.x, n1.y, n1.z, n1.w};
+  const float cmin = fminf(fminf(fminf(nc[0], nc[1]), fminf(nc[2], nc[3])), fminf(fminf(nc[4], nc[5]), fminf(nc[6], nc[7])));
+  uint32_t vo = 0;
+  if (vlin && rn <= 0x1p60f && fminf(rn, cmin) >= 0x1p-60f) {  // every divisor inside the short division's domain
+    const f2 k16 = f2_splat(16.0f), k15 = f2_splat(-1.5f), one2 = f2_splat(1.0f), mone2 = f2_splat(-1.0f);
+#pragma unroll
+    for (int j = 3; j >= 0; --j) {
+      const float da = fminf(rn, nc[2 * j]), db = fminf(rn, nc[2 * j + 1]);
+      const f2 nd = f2_mul(f2_pack(da, db), mone2);
+      const f2 r0 = f2_pack(mufu_rcp(da), mufu_rcp(db));
+      const f2 rr = f2_fma(r0, f2_fma(nd, r0, one2), r0);
+      f2 q = f2_mul(v[j], rr);
+      q = f2_fma(f2_fma(q, nd, v[j]), rr, q);
+      float ta, tb;
+      f2_unpack(f2_fma(q, k16, k15), ta, tb);
+      // no clamp: every v is at most its row and its column maximum (the statistics pass computed them from the
+      // same values with the same roundings), so the quotient is at most 1 and the code at most 15
+      vo = vo * 16u + __float2uint_ru(tb);
+      vo = vo * 16u + __float2uint_ru(ta);
+    }
+  } else {
+#pragma unroll
+    for (int j = 3; j >= 0; --j) {
+      float va, vb;
+      f2_unpack(v[j], va, vb);
+      vo = (vo << 4) + (uint32_t)code16(Sv.mids, __fdiv_rn(vb, fminf(rn, nc[2 * j + 1])));
+      vo = (vo << 4) + (uint32_t)code16(Sv.mids, __fdiv_rn(va, fminf(rn, nc[2 * j])));
+    }
+  }
+  *mcp = mo;
+  *vcp = vo;
+  if (l16 == 0) t.msc[u] = am;
+}
+
+template <bool A>
+__global__ void __launch_bounds__(R2T, 1) r1_update2_kernel(const __grid_constant__ R2Table tab,
+                                                            const float* __restrict__ qmap_m,
+                                                            const float* __restrict__ qmap_v, const UConsts cin) {
+  UConsts cf;
+  if (A) cf = fused_consts(cin);
+  const UConsts& c = A ? cf : cin;
+  extern __shared__ __align__(16) unsigned char dyn_smem[];
+  __shared__ QMapSmem Sm, Sv;
+  LutEnt* lut_m = reinterpret_cast<LutEnt*>(dyn_smem);
+  lut_build(Sv, nullptr, qmap_v);
+  lut_build(Sm, lut_m, qmap_m);
+  const bool lut_ok = Sm.valid != 0, vlin = Sv.linear16 != 0;
+  const UConsts2 c2 = make_consts2(c);
+  const Consts2 kf = make_consts_x2(c.f_beta1, c.f_beta2, c.f_omb1, c.f_omb2, c.f_lr, c.f_wd, c.f_eps, c.c1, c.c2s, c.rc2s);
+  const int l16 = threadIdx.x & 15;
+  const unsigned hmask = 0xFFFFu << (threadIdx.x & 16);
+  const float qm_l = Sm.qmap[l16], qv_l = Sv.qmap[l16];
+  long long gi = (long long)blockIdx.x * R2_HW + (threadIdx.x >> 4);
+  const unsigned stride = gridDim.x * R2_HW;
+  // every half-warp walks gi, gi + stride, ... through the tensors in order; the tensor loop is uniform
+  for (int ti = 0; ti < tab.n; ++ti) {
+    const R2Desc& t = tab.t[ti];
+    const long long uend = (ti + 1 < tab.n) ? tab.t[ti + 1].ustart : tab.total;
+    if (gi >= uend) continue;
+    unsigned u = (unsigned)(gi - t.ustart);
+    const unsigned lim = (unsigned)(uend - t.ustart);
+    const unsigned gpr = (unsigned)t.gpr;
+    unsigned r = u / gpr, cb = u - r * gpr;          // row and column block of the group; advanced incrementally
+    const unsigned sr = stride / gpr, sc = stride - sr * gpr;
+    for (; u < lim; u += stride) {
+      r2_group<A>(t, u, r, cb, l16, hmask, c2, kf, Sm, Sv, lut_m, lut_ok, vlin, qm_l, qv_l, (u + stride < lim) ? stride : 0u);
+      cb += sc;
+      r += sr;
+      if (cb >= gpr) {
+        cb -= gpr;
+        ++r;
+      }
+    }
+    gi = t.ustart + u;
+  }
+}
+
 }  // namespace lpmm_b200
 
 using namespace lpmm_b200;
@@ -371,20 +576,37 @@ extern "C" int lpmm_b200_rank1_multi_step(const lpmm_b200_step_tensor* const* ts
   if (table_bytes < lpmm_b200_rank1_multi_table_bytes(n)) return LPMM_B200_ERR_BAD_SIZE;
   cudaStream_t st = (cudaStream_t)stream;
   static thread_local std::vector<R1Desc> host;
+  static thread_local std::vector<int> order;
   host.resize(n);
+  order.clear();
+  const UConsts c = make_consts(beta1, beta2, lr, weight_decay, eps, step);
   long long total_elems = 0;
   for (int i = 0; i < n; ++i) {
     if (!lpmm_b200_rank1_multi_ok(ts[i])) return LPMM_B200_ERR_UNSUPPORTED;
     total_elems += ts[i]->numel;
   }
-  // statistics tiles: about six per SM over the whole list, at least 4 rows each
-  const long long target_tiles = (long long)num_sms() * 6;
+  // Matrices whose rows are whole 128-element groups take the update kernel shaped like the fused step
+  // (r1_update2_kernel); they come first in the table.  It has no scalar path, so it needs the short exact
+  // sequences (hyper-parameters inside their domain) and 32-byte aligned parameters and gradients.
+  const bool fast = arith ? c.f_fast != 0 : c.fast != 0;
+  auto wide = [&](const lpmm_b200_step_tensor* t) {
+    return fast && t->shape[1] % 128 == 0 && t->numel < ((long long)1 << 37) &&
+           ((((uintptr_t)t->p | (uintptr_t)t->g | (uintptr_t)t->v_max_dims_old[1] | (uintptr_t)t->v_max_dims_new[1]) & 31) == 0);
+  };
+  for (int i = 0; i < n; ++i)
+    if (wide(ts[i])) order.push_back(i);
+  const int n_wide = (int)order.size();
+  for (int i = 0; i < n; ++i)
+    if (!wide(ts[i])) order.push_back(i);
+  // statistics tiles: about sixteen per SM over the whole list, at least 4 rows each; a grid of resident CTAs
+  // (as many of 256 threads as an SM holds) strides over them, so the last tiles level the load
+  const long long target_tiles = (long long)num_sms() * 16;
   long long per_tile = (total_elems + target_tiles - 1) / target_tiles;
   if (per_tile < 8192) per_tile = 8192;
-  long long units = 0, tiles = 0;
-  for (int i = 0; i < n; ++i) {
-    const lpmm_b200_step_tensor* t = ts[i];
-    R1Desc& d = host[i];
+  long long units = 0, tiles = 0;  // units: 128-element units of the matrices that are NOT wide (numbered from 0)
+  for (int k = 0; k < n; ++k) {
+    const lpmm_b200_step_tensor* t = ts[order[k]];
+    R1Desc& d = host[k];
     d.p = t->p;
     d.g = t->g;
     d.m = reinterpret_cast<uint8_t*>(t->m);
@@ -410,15 +632,24 @@ extern "C" int lpmm_b200_rank1_multi_step(const lpmm_b200_step_tensor* const* ts
     if (rows < 4) rows = 4;
     if (rows > d.R) rows = d.R;
     d.rows_per_tile = (int)rows;
-    units += (t->numel + 127) / 128;
+    if (k >= n_wide) units += (t->numel + 127) / 128;
     tiles += (long long)d.tiles_x * ((d.R + rows - 1) / rows);
   }
   LPMM_CUDA_TRY(cudaMemcpyAsync(table, host.data(), sizeof(R1Desc) * (size_t)n, cudaMemcpyHostToDevice, st));
   const R1Desc* dev = reinterpret_cast<const R1Desc*>(table);
-  const UConsts c = make_consts(beta1, beta2, lr, weight_decay, eps, step);
   r1_zero_kernel<<<(unsigned)n, R1T, 0, st>>>(dev);
   LPMM_CUDA_TRY(cudaGetLastError());
-  long long sgrid = tiles < target_tiles ? tiles : target_tiles;
+  static int stats_ctas[64] = {};  // CTAs of the statistics kernel one SM holds, per device
+  int cur = 0;
+  cudaGetDevice(&cur);
+  int per_sm = (cur >= 0 && cur < 64) ? stats_ctas[cur] : 0;
+  if (per_sm == 0) {
+    LPMM_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, r1_stats_kernel<false>, R1T, 0));
+    if (per_sm < 1) per_sm = 1;
+    if (cur >= 0 && cur < 64) stats_ctas[cur] = per_sm;
+  }
+  const long long resident = (long long)num_sms() * per_sm;
+  long long sgrid = tiles < resident ? tiles : resident;
   if (arith) r1_stats_kernel<true><<<(unsigned)sgrid, R1T, 0, st>>>(dev, n, tiles, qmap_v, c);
   else r1_stats_kernel<false><<<(unsigned)sgrid, R1T, 0, st>>>(dev, n, tiles, qmap_v, c);
   LPMM_CUDA_TRY(cudaGetLastError());
@@ -428,13 +659,48 @@ extern "C" int lpmm_b200_rank1_multi_step(const lpmm_b200_step_tensor* const* ts
   if (devi >= 0 && devi < 64 && !attr_set[devi]) {
     LPMM_CUDA_TRY(cudaFuncSetAttribute(r1_update_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)R1_DYN_SMEM));
     LPMM_CUDA_TRY(cudaFuncSetAttribute(r1_update_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)R1_DYN_SMEM));
+    LPMM_CUDA_TRY(cudaFuncSetAttribute(r1_update2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)R1_DYN_SMEM));
+    LPMM_CUDA_TRY(cudaFuncSetAttribute(r1_update2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)R1_DYN_SMEM));
     attr_set[devi] = true;
   }
-  long long ugrid = (units + R1T / 16 - 1) / (R1T / 16);
-  const long long ucap = (long long)num_sms() * 4;
-  if (ugrid > ucap) ugrid = ucap;
-  if (arith) r1_update_kernel<true><<<(unsigned)ugrid, R1T, R1_DYN_SMEM, st>>>(dev, n, units, qmap_m, qmap_v, c);
-  else r1_update_kernel<false><<<(unsigned)ugrid, R1T, R1_DYN_SMEM, st>>>(dev, n, units, qmap_m, qmap_v, c);
-  LPMM_CUDA_TRY(cudaGetLastError());
+  // wide matrices: windows of at most R2_MAX descriptors in the launch parameters
+  static thread_local R2Table tab;
+  for (int k0 = 0; k0 < n_wide; k0 += R2_MAX) {
+    const int cnt = (n_wide - k0 < R2_MAX) ? n_wide - k0 : R2_MAX;
+    long long g2 = 0;
+    for (int k = 0; k < cnt; ++k) {
+      const R1Desc& d = host[k0 + k];
+      R2Desc& w = tab.t[k];
+      w.p = d.p;
+      w.g = d.g;
+      w.m = reinterpret_cast<uint32_t*>(d.m);
+      w.v = reinterpret_cast<uint32_t*>(d.v);
+      w.msc = d.m_max1;
+      w.old_r = d.old_r;
+      w.old_c = d.old_c;
+      w.new_r = d.new_r;
+      w.new_c = d.new_c;
+      w.ustart = g2;
+      w.gpr = d.C / 128;
+      w.pad_ = 0;
+      g2 += d.n / 128;
+    }
+    tab.n = cnt;
+    tab.pad_ = 0;
+    tab.total = g2;
+    long long grid2 = (g2 + R2_HW - 1) / R2_HW;
+    if (grid2 > num_sms()) grid2 = num_sms();
+    if (arith) r1_update2_kernel<true><<<(unsigned)grid2, R2T, R1_DYN_SMEM, st>>>(tab, qmap_m, qmap_v, c);
+    else r1_update2_kernel<false><<<(unsigned)grid2, R2T, R1_DYN_SMEM, st>>>(tab, qmap_m, qmap_v, c);
+    LPMM_CUDA_TRY(cudaGetLastError());
+  }
+  if (n > n_wide) {
+    long long ugrid = (units + R1T / 16 - 1) / (R1T / 16);
+    const long long ucap = (long long)num_sms() * 4;
+    if (ugrid > ucap) ugrid = ucap;
+    if (arith) r1_update_kernel<true><<<(unsigned)ugrid, R1T, R1_DYN_SMEM, st>>>(dev + n_wide, n - n_wide, units, qmap_m, qmap_v, c);
+    else r1_update_kernel<false><<<(unsigned)ugrid, R1T, R1_DYN_SMEM, st>>>(dev + n_wide, n - n_wide, units, qmap_m, qmap_v, c);
+    LPMM_CUDA_TRY(cudaGetLastError());
+  }
   return LPMM_B200_OK;
 }

@@ -92,6 +92,8 @@ def _load():
         "lpmm_b200_adamw4bit_multi_tensor_16bit": (i32, [ctypes.POINTER(Tensor), i32, i32, vp, vp, Hyper, i64, i64, vp]),
         "lpmm_b200_adamw4bit_multi_tensor_16bit_flags": (i32, [ctypes.POINTER(Tensor), i32, i32, vp, vp, Hyper, i64, i64,
                                                                ctypes.c_uint32, vp]),
+        "lpmm_b200_adamw4bit_multi_tensor_16bit_peers": (i32, [ctypes.POINTER(Tensor), i32, i32, vp, vp, Hyper, i64, i64,
+                                                               ctypes.POINTER(i64), i32, ctypes.c_uint32, vp]),
         "lpmm_b200_adamw4bit_multi_tensor_peers_flags": (i32, [ctypes.POINTER(Tensor), i32, vp, vp, Hyper, i64, i64,
                                                                ctypes.POINTER(i64), i32, ctypes.c_uint32, vp]),
         "lpmm_b200_adamw4bit_multi_tensor_peers": (i32, [ctypes.POINTER(Tensor), i32, vp, vp, Hyper, i64, i64,

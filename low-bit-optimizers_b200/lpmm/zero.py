@@ -74,8 +74,18 @@ class Zero1FusedAdamW:
     """
 
     def __init__(self, shapes, device, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=1e-2, process_group=None,
-                 rank=None, world=None, gather="nccl", reduce_grads=False, grad_scale=None):
+                 rank=None, world=None, gather="nccl", reduce_grads=False, grad_scale=None, dtype=torch.float32,
+                 exact_params=True):
+        """``dtype``: element type of parameters and gradients, fp32 or bf16 / fp16 (the 16-bit fused step; half the
+        bytes over NVLink).  ``exact_params=False``: the tolerance mode of the fused step (codes and scales as
+        always, parameters within 1e-6 relative)."""
         from .functional import create_general_qmap
+        if dtype not in (torch.float32, torch.bfloat16, torch.float16):
+            raise ValueError("dtype must be float32, bfloat16 or float16")
+        self.dtype = dtype
+        self.esize = 4 if dtype == torch.float32 else 2
+        self.exact_params = bool(exact_params)
+        self._full_grads = None  # data pointers of whole gradient tensors (use_full_grads) instead of grad_shard
         self.shapes = [tuple(s) for s in shapes]
         self.numels = [int(torch.Size(s).numel()) for s in self.shapes]
         self.device = torch.device(device)
@@ -94,7 +104,7 @@ class Zero1FusedAdamW:
         self.peer_offsets = None
         if self.gather == "fused":
             import torch.distributed._symmetric_memory as symm_mem
-            self.flat = symm_mem.empty(self.world * S * GROUP, dtype=torch.float32, device=self.device)
+            self.flat = symm_mem.empty(self.world * S * GROUP, dtype=self.dtype, device=self.device)
             self.flat.zero_()
             self._symm = symm_mem.rendezvous(self.flat, process_group if process_group is not None else dist.group.WORLD)
             ptrs = list(self._symm.buffer_ptrs)
@@ -102,10 +112,10 @@ class Zero1FusedAdamW:
             self.peer_offsets = [int(ptrs[r]) - mine for r in range(self.world) if r != self.rank]
             self._flag = torch.zeros(1, dtype=torch.float32, device=self.device)
         else:
-            self.flat = torch.zeros(self.world * S * GROUP, dtype=torch.float32, device=self.device)
+            self.flat = torch.zeros(self.world * S * GROUP, dtype=self.dtype, device=self.device)
         self.params = [self.flat[gs * GROUP: gs * GROUP + n].view(s)
                        for s, n, gs in zip(self.shapes, self.numels, self.gstart)]
-        self.grad_shard = torch.zeros(S * GROUP, dtype=torch.float32, device=self.device)
+        self.grad_shard = torch.zeros(S * GROUP, dtype=self.dtype, device=self.device)
         # reduce_grads: every rank holds a FULL flat gradient buffer (its local gradients, as data-parallel
         # backward leaves them) in symmetric memory, ``self.grads[i]`` its views; the update kernel of a rank
         # sums the gradients of its own group range over all ranks (rank order 0 .. world-1) and multiplies
@@ -115,6 +125,8 @@ class Zero1FusedAdamW:
         if self.reduce_grads:
             if self.gather != "fused":
                 raise ValueError("reduce_grads needs gather='fused' (peer-mapped buffers)")
+            if self.dtype != torch.float32:
+                raise NotImplementedError("reduce_grads is built for fp32 parameters and gradients")
             import torch.distributed._symmetric_memory as symm_mem
             self.grad_flat = symm_mem.empty(self.world * S * GROUP, dtype=torch.float32, device=self.device)
             self.grad_flat.zero_()
@@ -190,13 +202,16 @@ class Zero1FusedAdamW:
         indexing by a tensor-local group lands inside the shard buffers for owned groups.  Groups
         outside ``[lo, hi)`` are never touched by the launch."""
         out = []
-        for n, gs, fs in zip(self.numels, self.gstart, self.fstart):
+        es = self.esize
+        for i, (n, gs, fs) in enumerate(zip(self.numels, self.gstart, self.fstart)):
             d = gs - self.lo  # may be negative
-            p = self.flat.data_ptr() + gs * GROUP * 4
-            if self.reduce_grads:
-                g = self.grad_flat.data_ptr() + gs * GROUP * 4
+            p = self.flat.data_ptr() + gs * GROUP * es
+            if self._full_grads is not None:
+                g = self._full_grads[i]  # a whole gradient tensor: indexed by the tensor's own groups
+            elif self.reduce_grads:
+                g = self.grad_flat.data_ptr() + gs * GROUP * es
             else:
-                g = self.grad_shard.data_ptr() + d * GROUP * 4
+                g = self.grad_shard.data_ptr() + d * GROUP * es
             if n > THRESHOLD:
                 out.append((p, g, self.m_codes.data_ptr() + d * (GROUP // 2), self.v_codes.data_ptr() + d * (GROUP // 2),
                             self.m_scale.data_ptr() + d * 4, self.v_scale.data_ptr() + d * 4, n, 0))
@@ -205,8 +220,28 @@ class Zero1FusedAdamW:
                 out.append((p, g, self.m32.data_ptr() + df * GROUP * 4, self.v32.data_ptr() + df * GROUP * 4, 0, 0, n, 1))
         return out
 
-    def _update(self, lo, hi):
-        """Update global groups ``[lo, hi)`` (a sub-range of the owned range) on the current stream."""
+    def use_full_grads(self, grads):
+        """Take the gradients from whole per-tensor gradient tensors (already reduced over the ranks, as data-parallel
+        backward with an all-reduce leaves them) instead of ``grad_shard``: nothing is copied, the launch reads this
+        rank's groups out of them.  Call before every step; descriptors are patched only when a pointer changed."""
+        ptrs = []
+        for g, n in zip(grads, self.numels):
+            if g.dtype != self.dtype or not g.is_contiguous() or g.numel() != n or g.device != self.device:
+                raise RuntimeError("gradients must be contiguous tensors of the parameters' dtype, size and device")
+            ptrs.append(g.data_ptr())
+        if self._tl is not None and self._full_grads is not None:
+            for i, (a, b) in enumerate(zip(ptrs, self._full_grads)):
+                if a != b:
+                    self._tl[i].g = a
+        else:
+            self._tl = None
+        self._full_grads = ptrs
+        self._full_grad_tensors = list(grads)  # kept alive until the next step replaces them
+
+    def _update(self, lo, hi, hyper=None, peers=True):
+        """Update global groups ``[lo, hi)`` (a sub-range of the owned range) on the current stream.  ``hyper``:
+        a dict with lr / betas / eps / weight_decay for this launch (a parameter group's), default the
+        constructor's.  ``peers=False``: no stores into the peers' buffers (measurement of the local update)."""
         from . import _native as N
         if self._tl is None:
             desc = self.descriptors()
@@ -214,23 +249,43 @@ class Zero1FusedAdamW:
             for i, (p, g, m, v, sm, sv, n, kind) in enumerate(desc):
                 arr[i] = N.Tensor(p, g, m, v, sm or None, sv or None, n, kind, 0)
             self._tl = arr
-        b1, b2 = self.hyper["betas"]
-        h = N.Hyper(b1, b2, self.hyper["lr"], self.hyper["weight_decay"], self.hyper["eps"], float(self.step_count))
+        hp = hyper if hyper is not None else self.hyper
+        b1, b2 = hp["betas"]
+        h = N.Hyper(b1, b2, hp["lr"], hp["weight_decay"], hp["eps"], float(self.step_count))
+        flags = 0 if self.exact_params else N.FLAG_PARAMS_WITHIN_TOLERANCE
+        nt = len(self.numels)
         with torch.cuda.device(self.device):
             qm, qv = ctypes.c_void_p(self.qmap_m.data_ptr()), ctypes.c_void_p(self.qmap_v.data_ptr())
             st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
-            if self.reduce_grads:
+            offs = n_offs = None
+            if peers and self.peer_offsets:
                 offs = (ctypes.c_int64 * len(self.peer_offsets))(*self.peer_offsets)
+                n_offs = len(self.peer_offsets)
+            if self.dtype != torch.float32:
+                dt = N.DTYPE_BF16 if self.dtype == torch.bfloat16 else N.DTYPE_FP16
+                if offs is not None:
+                    N.check(N.lib.lpmm_b200_adamw4bit_multi_tensor_16bit_peers(self._tl, nt, dt, qm, qv, h, lo, hi, offs,
+                                                                               n_offs, flags, st))
+                else:
+                    N.check(N.lib.lpmm_b200_adamw4bit_multi_tensor_16bit_flags(self._tl, nt, dt, qm, qv, h, lo, hi, flags, st))
+            elif self.reduce_grads and peers:
                 goffs = (ctypes.c_int64 * len(self.grad_offsets))(*self.grad_offsets)
-                N.check(N.lib.lpmm_b200_adamw4bit_multi_tensor_zero1(self._tl, len(self.numels), qm, qv, h, lo, hi, offs,
-                                                                     len(self.peer_offsets), goffs, len(self.grad_offsets),
-                                                                     self.grad_scale, st))
-            elif self.peer_offsets:
-                offs = (ctypes.c_int64 * len(self.peer_offsets))(*self.peer_offsets)
-                N.check(N.lib.lpmm_b200_adamw4bit_multi_tensor_peers(self._tl, len(self.numels), qm, qv, h, lo, hi, offs,
-                                                                     len(self.peer_offsets), st))
+                N.check(N.lib.lpmm_b200_adamw4bit_multi_tensor_zero1(self._tl, nt, qm, qv, h, lo, hi, offs, n_offs, goffs,
+                                                                     len(self.grad_offsets), self.grad_scale, st))
+            elif offs is not None:
+                N.check(N.lib.lpmm_b200_adamw4bit_multi_tensor_peers_flags(self._tl, nt, qm, qv, h, lo, hi, offs, n_offs,
+                                                                           flags, st))
             else:
-                N.check(N.lib.lpmm_b200_adamw4bit_multi_tensor(self._tl, len(self.numels), qm, qv, h, lo, hi, st))
+                N.check(N.lib.lpmm_b200_adamw4bit_multi_tensor_flags(self._tl, nt, qm, qv, h, lo, hi, flags, st))
+
+    def _pre_step_barrier(self):
+        """gather="fused": the launch stores into every peer's parameter buffer, so no rank may start it while another
+        still reads its parameters (forward / backward of a slower rank), and with reduce_grads every rank's gradients
+        must be complete before any rank reads them.  One tiny all-reduce on the stream orders the ranks; the one
+        after the update (in _gather) keeps parameters and gradients from being touched while a peer still writes or
+        reads them."""
+        if self.gather == "fused":
+            dist.all_reduce(self._flag, group=self.pg)
 
     def _gather(self):
         if self.world == 1:
@@ -244,13 +299,7 @@ class Zero1FusedAdamW:
 
     def step(self):
         self.step_count += 1
-        if self.gather == "fused":
-            # The launch stores into every peer's parameter buffer: no rank may start it while another still reads
-            # its parameters (forward / backward of a slower rank), and with reduce_grads every rank's gradients must
-            # be complete before any rank reads them.  One tiny all-reduce on the stream orders the ranks; the one
-            # after the update (in _gather) keeps parameters and gradients from being touched while a peer still
-            # writes or reads them.
-            dist.all_reduce(self._flag, group=self.pg)
+        self._pre_step_barrier()
         if self.hi > self.lo:
             self._update(self.lo, self.hi)
         self._gather()
@@ -321,21 +370,27 @@ class Zero1FusedAdamW:
                 self.v32[df * GROUP: df * GROUP + (e1 - e0)].copy_(st["exp_avg_sq"].reshape(-1)[e0:e1])
 
     # ---- measurement helpers (bench) -------------------------------------------------------------
-    def time_update_only(self, iters):
-        """Mean duration (ms) of the sharded update launch alone and its algorithmic bytes."""
+    def bytes_per_param(self, small=False):
+        """Algorithmic bytes per parameter of the update: p read + write, g read, for 4-bit tensors two codes read +
+        write and two fp32 scales per 128 elements, for small tensors two fp32 moments read + write."""
+        return (2 * self.esize + self.esize + 16.0) if small else (3 * self.esize + 2.0 + 0.125)
+
+    def time_update_only(self, iters, peers=True):
+        """Mean duration (ms) of the sharded update launch alone and its algorithmic bytes.  ``peers=False``: without
+        the stores into the peers' buffers (the local update: leaves the replicas inconsistent; measurement only)."""
         ms = []
         for _ in range(iters):
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             self.step_count += 1
             a.record()
-            self._update(self.lo, self.hi)
+            self._update(self.lo, self.hi, peers=peers)
             b.record()
             torch.cuda.synchronize()
             ms.append(a.elapsed_time(b))
         nbytes = 0.0
         for i, a_, b_ in owned_pieces(self.numels, self.gstart, self.lo, self.hi):
             cnt = min(b_ * GROUP, self.numels[i]) - a_ * GROUP
-            nbytes += cnt * (14.125 if self.numels[i] > THRESHOLD else 28.0)
+            nbytes += cnt * self.bytes_per_param(self.numels[i] <= THRESHOLD)
         return sum(ms) / len(ms), nbytes
 
     def breakdown(self, iters):
@@ -354,7 +409,7 @@ class Zero1FusedAdamW:
         dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.pg)
         upd_ms, ag_ms = float(t[0]), float(t[1])
         total = sum(self.numels)
-        recv = 4.0 * self.shard_groups * GROUP * (self.world - 1)
+        recv = float(self.esize) * self.shard_groups * GROUP * (self.world - 1)
         if self.gather == "fused":
             return {"update_with_peer_stores": {"ms": upd_ms, "aggregate_params_per_s": total / (upd_ms * 1e-3),
                                                 "nvlink_bytes_sent_per_rank": recv,
@@ -362,3 +417,133 @@ class Zero1FusedAdamW:
                     "rank_barrier": {"ms": ag_ms}}
         return {"update_only": {"ms": upd_ms, "aggregate_params_per_s": total / (upd_ms * 1e-3)},
                 "all_gather": {"ms": ag_ms, "bytes_received_per_rank": recv, "gb_per_s_per_rank": recv / (ag_ms * 1e-3) / 1e9}}
+
+    def flat_checksum(self):
+        """A 64-bit checksum of the whole parameter buffer (sum of its 32-bit words as integers, in chunks)."""
+        words = self.flat.view(torch.int32)
+        total = torch.zeros((), dtype=torch.int64, device=self.device)
+        chunk = 1 << 27
+        for lo in range(0, words.numel(), chunk):
+            total += words[lo:lo + chunk].sum(dtype=torch.int64)
+        return total
+
+
+class ZeroAdamW(torch.optim.Optimizer):
+    """``lpmm.optim.AdamW(params, fused=True)`` with its states ZeRO-1 sharded over the ranks of a process group.
+
+    The model's parameters are adopted into one flat buffer (``p.data`` becomes a view that starts on a
+    128-element group boundary; with ``gather="fused"`` the buffer lives in symmetric memory and the update kernel
+    writes every rank's copy).  Every rank must construct it from identical parameters (a replicated model) and must
+    call ``step()`` with identical, already reduced gradients in ``p.grad`` (what data-parallel backward with an
+    all-reduce leaves): each rank reads only its own groups out of them, nothing is copied.  Parameter groups keep
+    their own ``lr`` / ``betas`` / ``eps`` / ``weight_decay``, read at every step (schedulers work), one launch per
+    group.  ``state_dict()`` gathers the shards into exactly what the unsharded optimizer's ``state_dict()`` holds
+    (the reference's fused layout, lpmm/optim/adamw.py:508-523: ``int8[(numel + 1) // 2]`` codes, fp32 group
+    maxima in ``overhead['max1']``, fp32 moments for tensors of at most 4096 elements) and ``load_state_dict`` takes
+    such a dict, so checkpoints move freely between the two.  Both are collective calls.
+    Not covered: sparse or missing gradients (every parameter needs one), parameter groups added later,
+    configurations other than the fused step's (4-bit group-128 states)."""
+
+    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=1e-2, *, process_group=None,
+                 gather="nccl", exact_params=True, engine_cls=None):
+        from .config import get_config
+        hyper = dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay)
+        # the same group keys as lpmm.optim.AdamW(fused=True), so that state dicts are interchangeable
+        defaults = dict(hyper, fused=True, use_first_moment=True, factor_second_moment=False)
+        super().__init__(params, defaults)
+        plist = [p for g in self.param_groups for p in g["params"]]
+        if not plist:
+            raise ValueError("ZeroAdamW got an empty parameter list")
+        dev, dt = plist[0].device, plist[0].dtype
+        if any(p.device != dev or p.dtype != dt for p in plist):
+            raise ValueError("all parameters must share one device and one dtype")
+        self._plist = plist
+        self.qconfig = get_config(None)
+        self.engine = (engine_cls or Zero1FusedAdamW)([tuple(p.shape) for p in plist], dev, process_group=process_group,
+                                                      gather=gather, dtype=dt, exact_params=exact_params, **hyper)
+        with torch.no_grad():
+            for p, view in zip(plist, self.engine.params):
+                view.copy_(p.detach())
+                p.data = view
+        # global group range of every parameter group (its tensors are consecutive in the flat buffer)
+        self._ranges, i = [], 0
+        eng = self.engine
+        for g in self.param_groups:
+            k = len(g["params"])
+            beg = eng.gstart[i] if k else 0
+            end = (eng.gstart[i + k] if i + k < len(plist) else eng.total_groups) if k else 0
+            self._ranges.append((beg, end))
+            i += k
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        eng = self.engine
+        grads = []
+        for p in self._plist:
+            if p.grad is None:
+                raise RuntimeError("ZeroAdamW needs a gradient for every parameter")
+            if p.grad.is_sparse:
+                raise RuntimeError("AdamW does not support sparse gradients")
+            grads.append(p.grad)
+        eng.use_full_grads(grads)
+        eng.step_count += 1
+        eng._pre_step_barrier()
+        for (beg, end), group in zip(self._ranges, self.param_groups):
+            lo, hi = max(eng.lo, beg), min(eng.hi, end)
+            if lo < hi:
+                eng._update(lo, hi, hyper=group)
+        eng._gather()
+        return loss
+
+    def state_dict(self):
+        """Collective.  The unsharded optimizer's ``state_dict()``: every rank returns the full state."""
+        eng = self.engine
+        full = eng.gather_state()
+        self.state.clear()
+        for p, st in zip(self._plist, full):
+            quant = p.numel() > THRESHOLD
+            oh_m, oh_v = {}, {}
+            m, v = st["exp_avg"], st["exp_avg_sq"]
+            if quant:
+                oh_m["max1"], oh_v["max1"] = st["exp_avg_scale"], st["exp_avg_sq_scale"]
+            else:
+                m, v = m.view(p.shape), v.view(p.shape)
+            self.state[p] = {
+                "step": torch.tensor(float(st["step"])),
+                "exp_avg": m,
+                "exp_avg_qstate": {"enable": quant, "overhead": oh_m, "qmap": eng.qmap_m},
+                "exp_avg_sq": v,
+                "exp_avg_sq_qstate": {"enable": quant, "overhead": oh_v, "qmap": eng.qmap_v},
+            }
+        sd = super().state_dict()
+        self.state.clear()  # the live state is the engine's shards
+        sd["qconfig"] = self.qconfig
+        return sd
+
+    def load_state_dict(self, state_dict):
+        """Collective in the sense that every rank must load the same dict; each keeps its own range."""
+        groups, saved = self.param_groups, state_dict["param_groups"]
+        if len(groups) != len(saved) or any(len(g["params"]) != len(s["params"]) for g, s in zip(groups, saved)):
+            raise ValueError("loaded state dict does not match the optimizer's parameter groups")
+        for g, s in zip(groups, saved):
+            for k, val in s.items():
+                if k != "params":
+                    g[k] = val
+        ids = [i for s in saved for i in s["params"]]
+        states = []
+        for idx, p in zip(ids, self._plist):
+            st = state_dict["state"].get(idx)
+            if st is None:
+                raise ValueError("ZeroAdamW needs the state of every parameter")
+            entry = {"step": float(st["step"]), "exp_avg": st["exp_avg"], "exp_avg_sq": st["exp_avg_sq"]}
+            if p.numel() > THRESHOLD:
+                entry["exp_avg_scale"] = st["exp_avg_qstate"]["overhead"]["max1"]
+                entry["exp_avg_sq_scale"] = st["exp_avg_sq_qstate"]["overhead"]["max1"]
+            states.append(entry)
+        self.engine.load_full_state(states)
+        if "qconfig" in state_dict:
+            self.qconfig = state_dict["qconfig"]

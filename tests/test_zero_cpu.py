@@ -39,36 +39,46 @@ def _grads(step):
     return out
 
 
-def _oracle_update(opt, lo, hi, qm, qv):
+def _oracle_update(opt, lo, hi, qm, qv, hyper=None):
     """What the CUDA launch does for global groups [lo, hi), done by the C oracle on numpy views."""
     from oracle import cpu as O
     from lpmm.zero import GROUP, THRESHOLD, owned_pieces
-    b1, b2 = opt.hyper["betas"]
+    hp = hyper if hyper is not None else opt.hyper
+    b1, b2 = hp["betas"]
     for i, a, b in owned_pieces(opt.numels, opt.gstart, lo, hi):
         n = opt.numels[i]
         e0, e1 = a * GROUP, min(b * GROUP, n)
         cnt = e1 - e0
         d = opt.gstart[i] + a - opt.lo
         p = opt.params[i].reshape(-1)[e0:e1].numpy()
-        g = opt.grad_shard[d * GROUP: d * GROUP + cnt].numpy()
+        if opt._full_grads is not None:  # whole gradient tensors (the optimizer wrapper)
+            g = opt._full_grad_tensors[i].reshape(-1)[e0:e1].numpy()
+        else:
+            g = opt.grad_shard[d * GROUP: d * GROUP + cnt].numpy()
         if n > THRESHOLD:
             nb, ng = (cnt + 1) // 2, b - a
             O.adamw4bit(p, g, opt.m_codes[d * 64: d * 64 + nb].numpy().view(np.uint8),
                         opt.v_codes[d * 64: d * 64 + nb].numpy().view(np.uint8), opt.m_scale[d: d + ng].numpy(),
-                        opt.v_scale[d: d + ng].numpy(), qm, qv, b1, b2, opt.hyper["lr"], opt.hyper["weight_decay"],
-                        opt.hyper["eps"], float(opt.step_count))
+                        opt.v_scale[d: d + ng].numpy(), qm, qv, b1, b2, hp["lr"], hp["weight_decay"],
+                        hp["eps"], float(opt.step_count))
         else:
             df = opt.fstart[i] + a - opt.f_lo
             O.adamw_fp32(p, g, opt.m32[df * GROUP: df * GROUP + cnt].numpy(), opt.v32[df * GROUP: df * GROUP + cnt].numpy(),
-                         b1, b2, opt.hyper["lr"], opt.hyper["weight_decay"], opt.hyper["eps"], float(opt.step_count))
+                         b1, b2, hp["lr"], hp["weight_decay"], hp["eps"], float(opt.step_count))
 
 
-def _make(world, rank, qm, qv):
+def _oracle_engine(qm, qv):
     from lpmm.zero import Zero1FusedAdamW
 
     class OracleZero(Zero1FusedAdamW):
-        def _update(self, lo, hi):
-            _oracle_update(self, lo, hi, qm, qv)
+        def _update(self, lo, hi, hyper=None, peers=True):
+            _oracle_update(self, lo, hi, qm, qv, hyper)
+
+    return OracleZero
+
+
+def _make(world, rank, qm, qv):
+    OracleZero = _oracle_engine(qm, qv)
 
     opt = OracleZero(SHAPES, "cpu", rank=rank, world=world, **HYPER)
     opt.init_params_normal_(0.02, seed=0)
@@ -202,3 +212,94 @@ def test_sharded_state_gathers_to_the_unsharded_layout_and_reloads(golden_dir, t
             if k != "step":
                 assert a[k].dtype == b[k].dtype and a[k].shape == b[k].shape, (i, k)
                 assert torch.equal(a[k].view(torch.uint8), b[k].view(torch.uint8)), f"tensor {i} {k}"
+
+
+# ---- the optimizer wrapper: parameters adopted into the flat buffer, parameter groups, state_dict ------------------
+def _wrapper_run(qm, qv, steps=3, resume_from=None):
+    """A small model stepped by ``lpmm.optim.ZeroAdamW`` (engine = the C oracle): two parameter groups with different
+    weight decay, the learning rate of the second halved at step 2.  Returns (optimizer, parameters)."""
+    import lpmm
+    torch.manual_seed(0)
+    params = [torch.nn.Parameter(torch.randn(s) * 0.02) for s in SHAPES]
+    groups = [dict(params=params[:3], weight_decay=0.01), dict(params=params[3:], weight_decay=0.1, lr=2e-3)]
+    opt = lpmm.optim.ZeroAdamW(groups, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, engine_cls=_oracle_engine(qm, qv))
+    first = 1
+    if resume_from is not None:
+        sd, pvals, first = resume_from
+        opt.load_state_dict(sd)
+        for p, v in zip(params, pvals):
+            p.data.copy_(v)
+    for step in range(first, steps + 1):
+        if step == 2:
+            opt.param_groups[1]["lr"] = 1e-3
+        for p, g in zip(params, _grads(step)):
+            p.grad = g
+        opt.step()
+    return opt, params
+
+
+def _wrapper_worker(rank, world, port, golden_dir, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    z = np.load(os.path.join(golden_dir, "qmaps.npz"))
+    opt, params = _wrapper_run(z["m"], z["v"], steps=2)
+    sd = opt.state_dict()                                   # collective
+    pvals = [p.detach().clone() for p in params]
+    # resume in a fresh wrapper from the gathered dict and take step 3; and take step 3 directly
+    opt2, params2 = _wrapper_run(z["m"], z["v"], steps=3, resume_from=(sd, pvals, 3))
+    for p, g in zip(params, _grads(3)):
+        p.grad = g
+    opt.step()
+    same = all(torch.equal(a.detach().view(torch.int32), b.detach().view(torch.int32)) for a, b in zip(params, params2))
+    final = opt.state_dict()
+    if rank == 0:
+        torch.save({"sd": final, "params": [p.detach().clone() for p in params], "resumed_same": same},
+                   os.path.join(out_dir, "wrapper.pt"))
+    dist.destroy_process_group()
+
+
+def _assert_same_tree(a, b, path="sd"):
+    assert type(a) is type(b) or (isinstance(a, (int, float)) and isinstance(b, (int, float))), (path, type(a), type(b))
+    if isinstance(a, torch.Tensor):
+        assert a.dtype == b.dtype and a.shape == b.shape, (path, a.dtype, b.dtype, a.shape, b.shape)
+        assert torch.equal(a.contiguous().reshape(-1).view(torch.uint8), b.contiguous().reshape(-1).view(torch.uint8)), path
+    elif isinstance(a, dict):
+        assert list(a.keys()) == list(b.keys()), (path, list(a.keys()), list(b.keys()))
+        for k in a:
+            _assert_same_tree(a[k], b[k], f"{path}[{k!r}]")
+    elif isinstance(a, (list, tuple)):
+        assert len(a) == len(b), path
+        for i, (x, y) in enumerate(zip(a, b)):
+            _assert_same_tree(x, y, f"{path}[{i}]")
+    elif path.endswith("['qconfig']"):
+        assert str(a) == str(b), path
+    else:
+        assert a == b, (path, a, b)
+
+
+def test_zero_optimizer_wrapper_two_ranks_equal_one_rank(golden_dir, tmp_path):
+    """Two gloo ranks of ``lpmm.optim.ZeroAdamW`` against the same wrapper on one rank: equal parameters and equal
+    ``state_dict()`` (the unsharded fused layout) after 3 steps with two parameter groups and a changed learning
+    rate; a wrapper resumed from the gathered dict continues identically."""
+    z = np.load(os.path.join(golden_dir, "qmaps.npz"))
+    single, sparams = _wrapper_run(z["m"], z["v"], steps=3)
+    ref = single.state_dict()
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_wrapper_worker, args=(2, port, golden_dir, str(tmp_path)), nprocs=2, join=True)
+    got = torch.load(tmp_path / "wrapper.pt", weights_only=False)
+    assert got["resumed_same"], "a wrapper resumed from the gathered state_dict diverged"
+    for i, (a, b) in enumerate(zip(got["params"], sparams)):
+        assert torch.equal(a.view(torch.int32), b.detach().view(torch.int32)), f"tensor {i}"
+    _assert_same_tree(got["sd"], ref)
+    # the layout of the reference's fused state (lpmm/optim/adamw.py:508-523)
+    st = ref["state"][0]
+    n = int(np.prod(SHAPES[0]))
+    assert list(st.keys()) == ["step", "exp_avg", "exp_avg_qstate", "exp_avg_sq", "exp_avg_sq_qstate"]
+    assert st["exp_avg"].dtype == torch.int8 and st["exp_avg"].numel() == (n + 1) // 2
+    assert st["exp_avg_qstate"]["overhead"]["max1"].numel() == (n + 127) // 128 and st["exp_avg_qstate"]["enable"]
+    small = ref["state"][1]  # 4096 elements: fp32 moments shaped like the parameter
+    assert small["exp_avg"].dtype == torch.float32 and tuple(small["exp_avg"].shape) == SHAPES[1]
+    assert ref["param_groups"][1]["weight_decay"] == 0.1 and ref["param_groups"][1]["lr"] == 1e-3
+    assert "qconfig" in ref

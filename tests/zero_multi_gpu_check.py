@@ -53,5 +53,53 @@ for step in range(1, 4):
 torch.cuda.synchronize(); dist.barrier()
 same2 = bool(torch.equal(red.flat.view(torch.int32), ref.flat.view(torch.int32)))
 ok = ok and same2
-print(f"rank {rank}: {'OK' if ok else 'MISMATCH'} (fused == nccl: {same}, in-kernel gradient reduction == summed gradients: {same2})", flush=True)
+# ---- 16-bit parameters: the sharded step with peer stores == the sharded step with an NCCL all-gather == the
+# unsharded 16-bit fused step on one GPU (same list, same gradients)
+import lpmm
+from lpmm import _kernels as K
+same3 = True
+for dt in (torch.bfloat16, torch.float16):
+    zs = {g: Zero1FusedAdamW(shapes, dev, gather=g, dtype=dt, **H) for g in ("nccl", "fused")}
+    for o in zs.values(): o.init_params_normal_(0.02, seed=0)
+    torch.manual_seed(0)
+    plain = [torch.nn.Parameter(v.detach().clone()) for v in zs["nccl"].params]
+    po = lpmm.optim.AdamW(plain, fused=True, **H)
+    for step in range(1, 4):
+        grads = []
+        for i, s in enumerate(shapes):
+            g = torch.Generator(device=dev); g.manual_seed(step * 100003 + i)
+            grads.append((torch.randn(s, generator=g, device=dev) * 1e-3).to(dt))
+        for o in zs.values():
+            o.set_grad_shard_from_full(grads); o.step()
+        for p, g in zip(plain, grads): p.grad = g
+        po.step()
+    torch.cuda.synchronize(); dist.barrier()
+    a, b = zs["nccl"].flat.view(torch.int16), zs["fused"].flat.view(torch.int16)
+    same3 = same3 and bool(torch.equal(a, b))
+    for v, p in zip(zs["fused"].params, plain):
+        same3 = same3 and bool(torch.equal(v.view(-1).view(torch.int16), p.detach().view(-1).view(torch.int16)))
+    del zs
+# ---- the optimizer wrapper over real parameters: ZeroAdamW (peer stores) == AdamW(fused=True) unsharded
+torch.manual_seed(1)
+wa = [torch.nn.Parameter(torch.randn(s, device=dev) * 0.02) for s in shapes]
+wb = [torch.nn.Parameter(p.detach().clone()) for p in wa]
+grp = lambda ps: [dict(params=ps[:3], weight_decay=0.01), dict(params=ps[3:], weight_decay=0.1, lr=2e-3)]
+za = lpmm.optim.ZeroAdamW(grp(wa), lr=1e-3, gather="fused")
+ob = lpmm.optim.AdamW(grp(wb), lr=1e-3, fused=True)
+for step in range(1, 5):
+    for i, (x, y) in enumerate(zip(wa, wb)):
+        g = torch.Generator(device=dev); g.manual_seed(step * 100003 + 7 * i)
+        x.grad = torch.randn(x.shape, generator=g, device=dev) * 1e-3
+        y.grad = x.grad.clone()
+    if step == 3: za.param_groups[1]["lr"] = ob.param_groups[1]["lr"] = 1e-3
+    za.step(); ob.step()
+torch.cuda.synchronize(); dist.barrier()
+same4 = all(bool(torch.equal(x.detach().view(torch.int32), y.detach().view(torch.int32))) for x, y in zip(wa, wb))
+sd_a, sd_b = za.state_dict(), ob.state_dict()
+for k in sd_b["state"]:
+    for name in ("exp_avg", "exp_avg_sq"):
+        same4 = same4 and bool(torch.equal(sd_a["state"][k][name].view(-1).view(torch.uint8), sd_b["state"][k][name].view(-1).view(torch.uint8)))
+ok = ok and same3 and same4
+print(f"rank {rank}: {'OK' if ok else 'MISMATCH'} (fused == nccl: {same}, in-kernel gradient reduction == summed gradients: {same2}, "
+      f"16-bit sharded == unsharded: {same3}, optimizer wrapper == unsharded optimizer: {same4})", flush=True)
 dist.destroy_process_group()
