@@ -135,17 +135,44 @@ def copy_rate(seconds=3.0):
         print(f"copy_ of {n} bf16 elements ({label}, {iters} copies): {ms:.3f} ms, {nbytes / ms / 1e6:.0f} GB/s", flush=True)
 
 
+def pack_rate(n=1 << 28, iters=10):
+    """The standalone 4-bit pack / unpack of ``lpmm.cpp_extension.quantization`` on n normalised values (4.5 bytes
+    moved per value: 4 read + 0.5 written, or the reverse), next to the copy rate above."""
+    from lpmm.cpp_extension import quantization as Q
+    from lpmm.functional import create_general_qmap
+    dev = torch.device("cuda:0")
+    qmap = create_general_qmap("nonlinear", 4, True).to(dev)
+    x = (torch.rand(n // 2048, 2048, device=dev) * 2 - 1).contiguous()
+    packed = Q.pack_nonlinear(x, qmap, 4, False)
+    for label, fn in (("pack_nonlinear", lambda: Q.pack_nonlinear(x, qmap, 4, False)),
+                      ("unpack_nonlinear", lambda: Q.unpack_nonlinear(packed, qmap, 4, n // 2048, 2048))):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / iters
+        print(f"{label} of {n} values (incl. the output allocation): {ms:.3f} ms, {4.5 * n / ms / 1e6:.0f} GB/s", flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--only", default=None)
     ap.add_argument("--big", action="store_true", help="the LLaMA-7B-shaped list instead (needs ~70 GB)")
     ap.add_argument("--copy", action="store_true", help="time torch's device copy instead (burst and sustained)")
+    ap.add_argument("--pack", action="store_true", help="time the standalone 4-bit pack / unpack of 2^28 values instead")
     a = ap.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("needs a CUDA device")
     if a.copy:
         return copy_rate()
+    if a.pack:
+        return pack_rate()
     for name, kind, shapes, kw in (big_cases() if a.big else cases()):
         if a.only is None or a.only in name:
             run(name, kind, shapes, kw, a.iters)

@@ -37,17 +37,18 @@ struct FDesc {
   long long n;
   long long ustart;  // first global 128-element unit
   long long tstart;  // first global tile
-  long long rstart;  // first global index among rows-then-columns of all tensors (finalize pass)
+  long long rstart;  // first global row index among the rows of all tensors (finalize pass)
+  long long cstart;  // first global 32-column block among the column blocks of all tensors (finalize pass)
   int R, C;
   int tiles_x, tiles_y, rows_per_tile, tx_shift, slots, m_quant;
 };
 
-template <int WHICH>  // 0: ustart, 1: tstart, 2: rstart
+template <int WHICH>  // 0: ustart, 1: tstart, 2: rstart, 3: cstart
 __device__ __forceinline__ int f_find(const FDesc* __restrict__ d, int n, long long x) {
   int lo = 0, hi = n - 1;
   while (lo < hi) {
     const int mid = (lo + hi + 1) >> 1;
-    const long long s = WHICH == 0 ? d[mid].ustart : (WHICH == 1 ? d[mid].tstart : d[mid].rstart);
+    const long long s = WHICH == 0 ? d[mid].ustart : (WHICH == 1 ? d[mid].tstart : (WHICH == 2 ? d[mid].rstart : d[mid].cstart));
     if (s <= x) lo = mid;
     else hi = mid - 1;
   }
@@ -142,35 +143,53 @@ __global__ void __launch_bounds__(FT) f_sums_kernel(const FDesc* __restrict__ d,
   }
 }
 
-// Pass 2: one thread per row or column of any matrix: partials in slot / tile order, then the accumulator
-// update  acc = fma(1 - beta2, mean, acc * beta2)  (adamw.py:609-610: mul_(beta2).add_(mean, alpha=1-beta2)).
-__global__ void __launch_bounds__(FT) f_finalize_kernel(const FDesc* __restrict__ d, int n, long long total,
-                                                         const UConsts c) {
-  for (long long i = (long long)blockIdx.x * FT + threadIdx.x; i < total; i += (long long)gridDim.x * FT) {
+// Pass 2: partials into the accumulators,  acc = fma(1 - beta2, mean, acc * beta2)  (adamw.py:609-610:
+// mul_(beta2).add_(mean, alpha=1-beta2)).  The first row_blocks CTAs take 256 rows each (any matrix): a row's
+// few segment partials in slot order.  The other CTAs take 32 columns of one matrix each: a tall matrix has
+// hundreds of tile partials per column, so the CTA's 8 warps share them (warp w sums tiles w, w + 8, ... in
+// order) and the 8 sums are added in warp order.  Fixed order throughout: results are reproducible.
+__global__ void __launch_bounds__(FT) f_finalize_kernel(const FDesc* __restrict__ d, int n, long long total_rows,
+                                                         long long row_blocks, const UConsts c) {
+  __shared__ float part[8][32];
+  if ((long long)blockIdx.x < row_blocks) {
+    const long long i = (long long)blockIdx.x * FT + threadIdx.x;
+    if (i >= total_rows) return;
     const FDesc& t = d[f_find<2>(d, n, i)];
     const long long j = i - t.rstart;
-    if (j < t.R) {
-      float s = 0.0f;
-      for (int k = 0; k < t.slots; ++k) s = __fadd_rn(s, t.row_part[(long long)k * t.R + j]);
-      t.row[j] = __fmaf_rn(c.omb2, __fdiv_rn(s, (float)t.C), __fmul_rn(t.row[j], c.beta2));
-    } else {
-      const long long cc = j - t.R;
-      float s = 0.0f;
-      for (int k = 0; k < t.tiles_y; ++k) s = __fadd_rn(s, t.col_part[(long long)k * t.C + cc]);
-      t.col[cc] = __fmaf_rn(c.omb2, __fdiv_rn(s, (float)t.R), __fmul_rn(t.col[cc], c.beta2));
-    }
+    float s = 0.0f;
+    for (int k = 0; k < t.slots; ++k) s = __fadd_rn(s, t.row_part[(long long)k * t.R + j]);
+    t.row[j] = __fmaf_rn(c.omb2, __fdiv_rn(s, (float)t.C), __fmul_rn(t.row[j], c.beta2));
+    return;
+  }
+  const long long cblock = (long long)blockIdx.x - row_blocks;
+  const FDesc& t = d[f_find<3>(d, n, cblock)];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const long long cc = (cblock - t.cstart) * 32 + lane;
+  float s = 0.0f;
+  if (cc < t.C)
+    for (int k = w; k < t.tiles_y; k += 8) s = __fadd_rn(s, t.col_part[(long long)k * t.C + cc]);
+  part[w][lane] = s;
+  __syncthreads();
+  if (w == 0 && cc < t.C) {
+    float sum = part[0][lane];
+#pragma unroll
+    for (int k = 1; k < 8; ++k) sum = __fadd_rn(sum, part[k][lane]);
+    t.col[cc] = __fmaf_rn(c.omb2, __fdiv_rn(sum, (float)t.R), __fmul_rn(t.col[cc], c.beta2));
   }
 }
 
-// Pass 3: mean of each matrix's updated row accumulator, one CTA per matrix, fixed order.
-__global__ void __launch_bounds__(FT) f_row_mean_kernel(const FDesc* __restrict__ d) {
-  __shared__ float red[FT];
+// Pass 3: mean of each matrix's updated row accumulator, one CTA of 1024 threads per matrix, fixed order; then
+// row[r] / mean for every row, for the update pass of wide matrices (f_update2_kernel): the first slot of the row
+// partials is free again after pass 2.
+constexpr int FMT = 1024;
+__global__ void __launch_bounds__(FMT) f_row_mean_kernel(const FDesc* __restrict__ d) {
+  __shared__ float red[FMT];
   const FDesc& t = d[blockIdx.x];
   float acc = 0.0f;
-  for (long long j = threadIdx.x; j < t.R; j += FT) acc = __fadd_rn(acc, t.row[j]);
+  for (long long j = threadIdx.x; j < t.R; j += FMT) acc = __fadd_rn(acc, t.row[j]);
   red[threadIdx.x] = acc;
   __syncthreads();
-  for (int o = FT / 2; o; o >>= 1) {
+  for (int o = FMT / 2; o; o >>= 1) {
     if ((int)threadIdx.x < o) red[threadIdx.x] = __fadd_rn(red[threadIdx.x], red[threadIdx.x + o]);
     __syncthreads();
   }
@@ -179,10 +198,8 @@ __global__ void __launch_bounds__(FT) f_row_mean_kernel(const FDesc* __restrict_
     *t.row_mean = red[0];
   }
   __syncthreads();
-  // row[r] / mean(row) for every row, for the update pass of wide matrices (f_update2_kernel); the first slot of
-  // the row partials is free again after pass 2
   const float mean = red[0];
-  for (long long j = threadIdx.x; j < t.R; j += FT) t.row_part[j] = __fdiv_rn(t.row[j], mean);
+  for (long long j = threadIdx.x; j < t.R; j += FMT) t.row_part[j] = __fdiv_rn(t.row[j], mean);
 }
 
 
@@ -488,7 +505,7 @@ extern "C" int lpmm_b200_factored_multi_step(const lpmm_b200_step_tensor* const*
   const long long target_tiles = (long long)num_sms() * 20;
   long long per_tile = (total_elems + target_tiles - 1) / target_tiles;
   if (per_tile < 8192) per_tile = 8192;
-  long long units = 0, tiles = 0, rc_total = 0;  // units: of the matrices that are NOT wide, numbered from 0
+  long long units = 0, tiles = 0, rows_total = 0, cblocks = 0;  // units: of the matrices that are NOT wide, from 0
   int64_t foff = 0;
   for (int k = 0; k < n; ++k) {
     const lpmm_b200_step_tensor* t = ts[order[k]];
@@ -523,10 +540,12 @@ extern "C" int lpmm_b200_factored_multi_step(const lpmm_b200_step_tensor* const*
     foff += 64;
     d.ustart = units;
     d.tstart = tiles;
-    d.rstart = rc_total;
+    d.rstart = rows_total;
+    d.cstart = cblocks;
     if (k >= n_wide) units += (t->numel + 127) / 128;
     tiles += (long long)d.tiles_x * d.tiles_y;
-    rc_total += (long long)d.R + d.C;
+    rows_total += d.R;
+    cblocks += (d.C + 31) / 32;
   }
   LPMM_CUDA_TRY(cudaMemcpyAsync(scratch, host.data(), sizeof(FDesc) * (size_t)n, cudaMemcpyHostToDevice, st));
   const FDesc* dev = reinterpret_cast<const FDesc*>(scratch);
@@ -543,11 +562,10 @@ extern "C" int lpmm_b200_factored_multi_step(const lpmm_b200_step_tensor* const*
   const long long sgrid = tiles < resident ? tiles : resident;
   f_sums_kernel<<<(unsigned)sgrid, FT, 0, st>>>(dev, n, tiles);
   LPMM_CUDA_TRY(cudaGetLastError());
-  long long fgrid = (rc_total + FT - 1) / FT;
-  if (fgrid > (long long)num_sms() * 8) fgrid = (long long)num_sms() * 8;
-  f_finalize_kernel<<<(unsigned)fgrid, FT, 0, st>>>(dev, n, rc_total, c);
+  const long long row_blocks = (rows_total + FT - 1) / FT;
+  f_finalize_kernel<<<(unsigned)(row_blocks + cblocks), FT, 0, st>>>(dev, n, rows_total, row_blocks, c);
   LPMM_CUDA_TRY(cudaGetLastError());
-  f_row_mean_kernel<<<(unsigned)n, FT, 0, st>>>(dev);
+  f_row_mean_kernel<<<(unsigned)n, FMT, 0, st>>>(dev);
   LPMM_CUDA_TRY(cudaGetLastError());
   static bool attr_set[64] = {};
   int devi = 0;

@@ -69,18 +69,28 @@ __global__ void __launch_bounds__(R1T) r1_zero_kernel(const R1Desc* __restrict__
 // maxima in registers, one atomic per thread and column at the end), a row's maximum is reduced across
 // the lanes that share the row (one atomic per warp and row).  Two rows per thread are in flight.
 // Rows are multiples of 8 floats and 16-byte aligned (host-checked).
+// One row's 8 elements of a thread: second moments recomputed from codes, old maxima and gradients, folded into
+// the thread's column maxima; returns their maximum.  qv_l: this lane's entry of the map (lane & 15), read by
+// shuffle with the code as source lane -- every lane of the warp must call this (idle lanes pass zeros, which leave
+// every maximum alone).  Pairs of elements share the packed fp32x2 multiply / fma, each half rounding like the
+// scalar upd_v2.
 template <bool A>
-__device__ __forceinline__ float r1_row_pass(const R1Desc& t, long long r, long long c0, const float* qv,
-                                             const float* col_old, float* col_max, const UConsts& c,
+__device__ __forceinline__ float r1_row_pass(float qv_l, const float* col_old, float* col_max, f2 kb2, f2 komb2,
                                              const float4& g0, const float4& g1, uint32_t codes, float row_old) {
-  const float gx[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+  const f2 gx[4] = {f2_pack(g0.x, g0.y), f2_pack(g0.z, g0.w), f2_pack(g1.x, g1.y), f2_pack(g1.z, g1.w)};
   float row_max = 0.0f;
 #pragma unroll
-  for (int k = 0; k < 8; ++k) {
-    const float v0 = __fmul_rn(qv[(codes >> (4 * k)) & 15u], fminf(row_old, col_old[k]));
-    const float v = upd_v2<A>(c, v0, gx[k]);
-    col_max[k] = fmaxf(col_max[k], v);
-    row_max = fmaxf(row_max, v);
+  for (int j = 0; j < 4; ++j) {
+    const float qa = __shfl_sync(0xffffffffu, qv_l, (int)(codes >> (8 * j)), 16);  // source lane = code (mod 16)
+    const float qb = __shfl_sync(0xffffffffu, qv_l, (int)(codes >> (8 * j + 4)), 16);
+    const f2 v0 = f2_mul(f2_pack(qa, qb), f2_pack(fminf(row_old, col_old[2 * j]), fminf(row_old, col_old[2 * j + 1])));
+    const f2 v = A ? f2_fma(kb2, v0, f2_mul(f2_mul(komb2, gx[j]), gx[j]))       // fma(b2, v0, ((1-b2) g) g)
+                   : f2_fma(komb2, f2_mul(gx[j], gx[j]), f2_mul(v0, kb2));     // fma(1-b2, g g, v0 b2)
+    float va, vb;
+    f2_unpack(v, va, vb);
+    col_max[2 * j] = fmaxf(col_max[2 * j], va);
+    col_max[2 * j + 1] = fmaxf(col_max[2 * j + 1], vb);
+    row_max = fmaxf(row_max, fmaxf(va, vb));
   }
   return row_max;
 }
@@ -91,9 +101,8 @@ __global__ void __launch_bounds__(R1T) r1_stats_kernel(const R1Desc* __restrict_
   UConsts cf;
   if (A) cf = fused_consts(cin);
   const UConsts& c = A ? cf : cin;
-  __shared__ float qv[16];
-  if (threadIdx.x < 16) qv[threadIdx.x] = qmap_v[threadIdx.x];
-  __syncthreads();
+  const float qv_l = __ldg(qmap_v + (threadIdx.x & 15));
+  const f2 kb2 = f2_splat(A ? c.f_beta2 : c.beta2), komb2 = f2_splat(A ? c.f_omb2 : c.omb2);
   for (long long tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
     const R1Desc& t = d[r1_find<true>(d, n, tile)];
     const long long local = tile - t.tstart;
@@ -138,7 +147,6 @@ __global__ void __launch_bounds__(R1T) r1_stats_kernel(const R1Desc* __restrict_
     }
     for (long long rb = r_begin; rb < r_end; rb += 2 * ty_count) {
       const long long ra = rb + ty, rc = rb + ty_count + ty;
-      const bool ha = active && ra < r_end, hc = active && rc < r_end;
       const float4 ga0 = nga0, ga1 = nga1, gc0 = ngc0, gc1 = ngc1;
       const uint32_t ca = nca, cc = ncc;
       const float oa = noa, oc = noc;
@@ -159,8 +167,9 @@ __global__ void __launch_bounds__(R1T) r1_stats_kernel(const R1Desc* __restrict_
           noc = __ldg(t.old_r + rc2);
         }
       }
-      float ma = ha ? r1_row_pass<A>(t, ra, c0, qv, col_old, col_max, c, ga0, ga1, ca, oa) : 0.0f;
-      float mc = hc ? r1_row_pass<A>(t, rc, c0, qv, col_old, col_max, c, gc0, gc1, cc, oc) : 0.0f;
+      // rows that do not exist were loaded as zeros: their second moments are zero and change no maximum
+      float ma = r1_row_pass<A>(qv_l, col_old, col_max, kb2, komb2, ga0, ga1, ca, oa);
+      float mc = r1_row_pass<A>(qv_l, col_old, col_max, kb2, komb2, gc0, gc1, cc, oc);
       for (int o = seg >> 1; o; o >>= 1) {
         ma = fmaxf(ma, __shfl_xor_sync(0xffffffffu, ma, o));
         mc = fmaxf(mc, __shfl_xor_sync(0xffffffffu, mc, o));

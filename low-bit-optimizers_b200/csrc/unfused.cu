@@ -891,6 +891,67 @@ __global__ void __launch_bounds__(UT) unpack_kernel(const uint8_t* __restrict__ 
     else *reinterpret_cast<float2*>(out + 2 * b) = make_float2(M.qm[c & 15], M.qm[c >> 4]);
   }
 }
+// 4-bit pack / unpack with wide accesses: a lane takes 8 consecutive values with one 256-bit access and their 8
+// codes with one 32-bit access (a warp instruction moves 1 KB of values and 128 bytes of codes, both contiguous),
+// four such units in flight per thread.  Codes come from the shared-memory table of common.cuh (one read and one
+// compare per value) when the map fits it, else from the midpoint search; -inf, which the table files under the
+// NaNs, is code 0 as in the reference's search.  The values behind the last whole unit of 8 (n is even) and the
+// trailing byte belong to the caller's byte-wise launch.
+constexpr int PVT = 256;
+__device__ __forceinline__ uint32_t pack8(const f8& v, const LutEnt* __restrict__ lut, const float* __restrict__ mids,
+                                          bool lut_ok) {
+  const float ninf = __int_as_float(0xff800000);
+  uint32_t word = 0;
+#pragma unroll
+  for (int k = 7; k >= 0; --k) {
+    int c = lut_ok ? lut_code(lut, v.x[k]) : code16(mids, v.x[k]);
+    if (v.x[k] == ninf) c = 0;
+    word = (word << 4) + (uint32_t)c;
+  }
+  return word;
+}
+__global__ void __launch_bounds__(PVT) pack4_vec_kernel(const float* __restrict__ x, long long units,
+                                                        const float* __restrict__ qmap, uint32_t* __restrict__ out) {
+  extern __shared__ __align__(16) unsigned char dyn_smem[];
+  __shared__ QMapSmem S;
+  LutEnt* lut = reinterpret_cast<LutEnt*>(dyn_smem);
+  lut_build(S, lut, qmap);
+  const bool lut_ok = S.valid != 0;
+  const long long stride = (long long)gridDim.x * PVT;
+  long long u = (long long)blockIdx.x * PVT + threadIdx.x;
+  for (; u + 3 * stride < units; u += 4 * stride) {
+    const f8 a = ldg_f8(x + u * 8), b = ldg_f8(x + (u + stride) * 8), c = ldg_f8(x + (u + 2 * stride) * 8),
+             d = ldg_f8(x + (u + 3 * stride) * 8);
+    out[u] = pack8(a, lut, S.mids, lut_ok);
+    out[u + stride] = pack8(b, lut, S.mids, lut_ok);
+    out[u + 2 * stride] = pack8(c, lut, S.mids, lut_ok);
+    out[u + 3 * stride] = pack8(d, lut, S.mids, lut_ok);
+  }
+  for (; u < units; u += stride) out[u] = pack8(ldg_f8(x + u * 8), lut, S.mids, lut_ok);
+}
+__device__ __forceinline__ void unpack8(uint32_t w, const float* __restrict__ qm, float* dst) {
+  f8 r;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) r.x[k] = qm[(w >> (4 * k)) & 15u];
+  stg_f8(dst, r);
+}
+__global__ void __launch_bounds__(PVT) unpack4_vec_kernel(const uint32_t* __restrict__ in, long long units,
+                                                          const float* __restrict__ qmap, float* __restrict__ out) {
+  __shared__ float qm[16];
+  if (threadIdx.x < 16) qm[threadIdx.x] = qmap[threadIdx.x];
+  __syncthreads();
+  const long long stride = (long long)gridDim.x * PVT;
+  long long u = (long long)blockIdx.x * PVT + threadIdx.x;
+  for (; u + 3 * stride < units; u += 4 * stride) {
+    const uint32_t a = __ldcs(in + u), b = __ldcs(in + u + stride), c = __ldcs(in + u + 2 * stride),
+                   d = __ldcs(in + u + 3 * stride);
+    unpack8(a, qm, out + u * 8);
+    unpack8(b, qm, out + (u + stride) * 8);
+    unpack8(c, qm, out + (u + 2 * stride) * 8);
+    unpack8(d, qm, out + (u + 3 * stride) * 8);
+  }
+  for (; u < units; u += stride) unpack8(__ldcs(in + u), qm, out + u * 8);
+}
 // mode 0: group scales (computes max1); mode 1: rank-1 scales from given per-axis maxima.
 // SR: stochastic rounding with the reference's random stream (seed, offset); else round to nearest.
 template <int MODE, int ND, bool W, bool SR = false>
@@ -1089,6 +1150,26 @@ extern "C" int lpmm_b200_pack_nonlinear(const float* data, int64_t n, const floa
   if (rc) return rc;
   if (n < 0 || (!l.wide && (n & 1))) return LPMM_B200_ERR_BAD_SIZE;
   if (!qmap || !packed || (n > 0 && !data)) return LPMM_B200_ERR_NULL_POINTER;
+  // two codes per byte, values 32-byte and codes 4-byte aligned: wide accesses for the whole units of 8 values, the
+  // byte-wise kernel for what is left (and the trailing byte)
+  if (!l.wide && n >= 8 && (((uintptr_t)data & 31) == 0) && (((uintptr_t)packed & 3) == 0)) {
+    const long long chunks = n / 8;
+    const size_t smem = LUT_ENTRIES * sizeof(LutEnt);
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+      LPMM_CUDA_TRY(cudaFuncSetAttribute(pack4_vec_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      attr_set[dev] = true;
+    }
+    pack4_vec_kernel<<<grid_for(chunks, PVT, 4), PVT, smem, (cudaStream_t)stream>>>(data, chunks, qmap, (uint32_t*)packed);
+    LPMM_CUDA_TRY(cudaGetLastError());
+    const long long rest = n - chunks * 8;  // even; rest == 0 still writes the trailing byte
+    pack_kernel<false><<<grid_for(rest / 2, UT), UT, 0, (cudaStream_t)stream>>>(data + chunks * 8, rest, qmap, l.bits,
+                                                                               (uint8_t*)packed + chunks * 4);
+    LPMM_CUDA_TRY(cudaGetLastError());
+    return LPMM_B200_OK;
+  }
   LPMM_DISPATCH_W(l.wide, (pack_kernel<W><<<grid_for(l.wide ? n : n / 2, UT), UT, 0, (cudaStream_t)stream>>>(
                               data, n, qmap, l.bits, (uint8_t*)packed)));
   LPMM_CUDA_TRY(cudaGetLastError());
@@ -1121,6 +1202,17 @@ extern "C" int lpmm_b200_unpack_nonlinear(const int8_t* packed, const float* qma
   if (n < 0 || (!l.wide && (n & 1))) return LPMM_B200_ERR_BAD_SIZE;
   if (n == 0) return LPMM_B200_OK;
   if (!qmap || !packed || !out) return LPMM_B200_ERR_NULL_POINTER;
+  if (!l.wide && n >= 8 && (((uintptr_t)out & 31) == 0) && (((uintptr_t)packed & 3) == 0)) {
+    const long long chunks = n / 8, rest = n - chunks * 8;
+    unpack4_vec_kernel<<<grid_for(chunks, PVT, 4), PVT, 0, (cudaStream_t)stream>>>((const uint32_t*)packed, chunks, qmap, out);
+    LPMM_CUDA_TRY(cudaGetLastError());
+    if (rest > 0) {
+      unpack_kernel<false><<<grid_for(rest / 2, UT), UT, 0, (cudaStream_t)stream>>>((const uint8_t*)packed + chunks * 4, rest,
+                                                                                   qmap, l.bits, out + chunks * 8);
+      LPMM_CUDA_TRY(cudaGetLastError());
+    }
+    return LPMM_B200_OK;
+  }
   LPMM_DISPATCH_W(l.wide, (unpack_kernel<W><<<grid_for(l.wide ? n : n / 2, UT), UT, 0, (cudaStream_t)stream>>>(
                               (const uint8_t*)packed, n, qmap, l.bits, out)));
   LPMM_CUDA_TRY(cudaGetLastError());

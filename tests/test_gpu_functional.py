@@ -15,7 +15,8 @@ def _special_values(qmap):
     mids = (q[:-1] + q[1:]) * 0.5
     up = torch.nextafter(mids, torch.full_like(mids, 2.0))
     dn = torch.nextafter(mids, torch.full_like(mids, -2.0))
-    extra = torch.tensor([0.0, -0.0, 1.0, -1.0, 2.0, -2.0, 1e-30, -1e-30, float("inf"), float("nan"), 1.1249, 0.5, 1e-8])
+    extra = torch.tensor([0.0, -0.0, 1.0, -1.0, 2.0, -2.0, 1e-30, -1e-30, float("inf"), float("-inf"), float("nan"), 1.1249,
+                          0.5, 1e-8])
     return torch.cat([q, mids, up, dn, extra])
 
 
@@ -39,6 +40,39 @@ def test_pack_unpack_match_reference_kernels(qmaps, which):
         torch.cuda.synchronize()
         assert torch.equal(packed[:-1], r_packed[:-1]), "codes differ from the reference's kernel"
         assert bits_equal(out, ref.unpack_nonlinear(r_packed, qmap, 4, x.shape[0], 2048))
+
+
+@pytest.mark.parametrize("which", ["m", "v", "power2"])
+@pytest.mark.parametrize("n,offset", [(2048 * 3 + 46, 0), (6, 0), (2048 + 32, 4), (32, 0), (2048 * 2, 8), (2048 * 40 + 8, 0)])
+def test_pack_unpack_sizes_and_alignments_through_the_c_abi(qmaps, which, n, offset):
+    """The 4-bit pack / unpack take wide accesses (8 values per lane) for whole units of 8 values in 32-byte aligned
+    buffers and a byte-wise path for the rest, for shorter inputs and for other alignments: every combination
+    against the restated rule, special values included."""
+    import ctypes
+    from lpmm import _native as N
+    from oracle import torch_ref as T
+    qm, qv, q2 = device_qmaps(qmaps)
+    qmap = {"m": qm, "v": qv, "power2": q2}[which]
+    torch.manual_seed(n + offset)
+    vals = torch.cat([_special_values(qmap), torch.rand(max(n, 64)) * 2.2 - 1.1])
+    vals = vals[torch.randperm(vals.numel())][:n].contiguous()
+    buf = torch.zeros(n + 16, device=device())
+    x = buf[offset: offset + n]
+    x.copy_(vals.to(device()))
+    obuf = torch.full((n // 2 + 1 + 64,), 77, dtype=torch.int8, device=device())
+    out = obuf[4 * offset: 4 * offset + n // 2 + 1]
+    vp = lambda t: ctypes.c_void_p(t.data_ptr())
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    N.check(N.lib.lpmm_b200_pack_nonlinear(vp(x), n, vp(qmap), 4, vp(out), st))
+    torch.cuda.synchronize()
+    assert torch.equal(out, T.pack_nonlinear(x.contiguous().view(1, -1), qmap)), "codes"
+    assert int(obuf[4 * offset + n // 2 + 1]) == 77, "wrote past the trailing byte"
+    back = torch.full((n + 16,), -5.0, device=device())
+    dst = back[offset: offset + n]
+    N.check(N.lib.lpmm_b200_unpack_nonlinear(vp(out), vp(qmap), 4, n, vp(dst), st))
+    torch.cuda.synchronize()
+    assert bits_equal(dst, T.unpack_nonlinear(out, qmap, 1, n).view(-1))
+    assert float(back[offset + n]) == -5.0 and (offset == 0 or float(back[offset - 1]) == -5.0)
 
 
 @pytest.mark.parametrize("bits", [5, 6, 7, 8])
