@@ -41,7 +41,10 @@ METRIC = "optimizer_params_updated_per_second"
 UNIT = "params/s"
 BYTES_Q4 = 14.125   # p 4r+4w, g 4r, m codes .5r+.5w, v codes .5r+.5w, two fp32 scales per 128 elements r+w
 BYTES_FP32 = 28.0   # p, m, v read+write, g read
-NCU_TRAFFIC_PER_PARAM = 14.07  # dram read+write bytes per 4-bit parameter, from profiles/ (ncu, 268M-element case)
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of adamw4bit_multi_kernel<1,1,0> over a 667 M-parameter
+# list (ncu, one launch captured), divided by its 4-bit parameters: every byte moves once, so a launch over a longer
+# list moves proportionally more
+NCU_TRAFFIC_PER_PARAM = 14.23
 
 
 def llama7b_shapes(layers=32, hidden=4096, inter=11008, vocab=32000):
@@ -507,7 +510,10 @@ def run_own(args):
         extra["local_update"] = local_update_rate(opt, max(3, min(args.steps, 10)), peak, world)
     achieved = k_bytes / (k_ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": NCU_TRAFFIC_PER_PARAM * (k_bytes / BYTES_Q4), "peak_kind": f"of {peak_kind}",
+                "traffic": NCU_TRAFFIC_PER_PARAM * (k_bytes / BYTES_Q4),
+                "traffic_source": "ncu capture of this kernel on a 667 M-parameter list (14.23 B per 4-bit parameter), "
+                                  "scaled by the parameters of this launch",
+                "peak_kind": f"of {peak_kind}",
                 "kernel": "adamw4bit_multi_kernel", "algorithmic_bytes_per_launch": k_bytes, "launch_ms": k_ms}
     if world == 1:
         roofline["launch_ms_min_max"] = [min(ks), max(ks)]

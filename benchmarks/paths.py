@@ -2,7 +2,7 @@
 (rank-1, group, wider codes, larger groups), the factored second moment, momentum SGD per tensor and
 fused, next to the fused AdamW step on the same shapes.  Seeded synthetic inputs.
 
-    python low-bit-optimizers_b200/bench_paths.py [--iters 10] [--only SUBSTRING] [--big]
+    python benchmarks/paths.py [--iters 10] [--only SUBSTRING] [--big]
 
 One line per case: parameters, CUDA-event time per step (after 3 warm-up steps), wall time per step,
 parameters per second.  ``LPMM_SGD_PER_TENSOR=1`` in the environment times the per-tensor SGD launches
@@ -16,7 +16,7 @@ import time
 
 import torch
 
-sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "low-bit-optimizers_b200"))
 import lpmm  # noqa: E402
 from lpmm.config import CONFIG_DIR  # noqa: E402
 
@@ -63,8 +63,10 @@ def cases():
         ("gpt2-medium adamw fused", "AdamW", gpt2_medium_shapes(), dict(adamw, fused=True)),
         ("gpt2-medium adamw fused rank-1 (default.yml, fused_rank1)", "AdamW", gpt2_medium_shapes(),
          dict(adamw, qconfig=cfg("default.yml"), fused=True, fused_rank1=True)),
-        ("gpt2-medium adamw fused bf16 parameters", "AdamW", gpt2_medium_shapes(),
+        ("gpt2-medium adamw fused bf16 parameters:", "AdamW", gpt2_medium_shapes(),
          dict(adamw, fused=True, param_dtype=torch.bfloat16)),
+        ("gpt2-medium adamw fused bf16 parameters, tolerance mode", "AdamW", gpt2_medium_shapes(),
+         dict(adamw, fused=True, exact_params=False, param_dtype=torch.bfloat16)),
         ("gpt2-medium sgd", "SGD", gpt2_medium_shapes(), dict(sgd)),
         ("ragged adamw rank-1 (default.yml)", "AdamW", RAGGED, dict(adamw, qconfig=cfg("default.yml"))),
     ]
@@ -77,7 +79,11 @@ def big_cases():
     return [
         ("llama7b adamw group (qconfig=None)", "AdamW", llama7b_shapes(), dict(adamw, qconfig=None)),
         ("llama7b adamw fused", "AdamW", llama7b_shapes(), dict(adamw, fused=True)),
+        ("llama7b adamw fused, tolerance mode (exact_params=False)", "AdamW", llama7b_shapes(),
+         dict(adamw, fused=True, exact_params=False)),
         ("llama7b adamw fused bf16 parameters", "AdamW", llama7b_shapes(), dict(adamw, fused=True, param_dtype=torch.bfloat16)),
+        ("llama7b adamw fused bf16 parameters, tolerance mode", "AdamW", llama7b_shapes(),
+         dict(adamw, fused=True, exact_params=False, param_dtype=torch.bfloat16)),
         ("llama7b adamw rank-1 (default.yml)", "AdamW", llama7b_shapes(), dict(adamw, qconfig=cfg("default.yml"))),
         ("llama7b adamw fused rank-1 (default.yml, fused_rank1)", "AdamW", llama7b_shapes(),
          dict(adamw, qconfig=cfg("default.yml"), fused=True, fused_rank1=True)),

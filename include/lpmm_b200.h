@@ -204,7 +204,8 @@ int64_t lpmm_b200_packed_len(int64_t n_scaled);
 /* Replaces quantization.pack_nonlinear(data[G, S], qmap, 4, False)
  * (lpmm/cpp_extension/quantization.cc:54-63 -> quantization_kernel.cu:430-513).  n = G*S values,
  * n even; packed holds n/2 + 1 bytes, the last one (never written by the reference) is set to 0.
- * Only the 4-bit round-to-nearest form is built. */
+ * This is the 4-bit round-to-nearest form; lpmm_b200_pack_nonlinear takes 4 to 8 bits and
+ * lpmm_b200_pack_nonlinear_sr rounds stochastically. */
 int lpmm_b200_pack_nonlinear4(const float* data, int64_t n, const float* qmap, int8_t* packed, void* stream);
 
 /* Replaces quantization.unpack_nonlinear(packed, qmap, 4, G, S)
@@ -341,12 +342,14 @@ int lpmm_b200_adamw4bit_unfused_multi_tensor(const lpmm_b200_tensor* tensors, in
  * first non-zero status ends the call (earlier tensors have been stepped).
  * Tensors that lpmm_b200_adamw4bit_unfused_multi_tensor covers and that share a step count are updated
  * by one launch of it; 2-D RANK1_4 tensors (4-bit codes, group-128 first moment, row length a multiple
- * of 8, 16-byte aligned) that share a step count are stepped together in three launches, their
- * descriptor table (under 256 bytes per tensor) taken from the end of `scratch` -- without enough
- * scratch they are stepped one by one.  2-D FACTORED tensors (fp32 or 4-bit group-128 first moment,
- * same shape conditions) that share a step count are likewise stepped together in four launches, their
- * table and partial sums taken from `scratch` (lpmm_b200_unfused_step_many_scratch_bytes gives a size
- * that serves everything).  `scratch` should be 256-byte aligned.  The launch chains of the other tensors are spread over four streams owned by the library (created on
+ * of 8, 16-byte aligned) that share a step count are stepped together in three or four launches (zero,
+ * statistics, update; matrices whose rows are multiples of 128 elements take an update kernel of their own),
+ * their descriptors carried in the launch parameters.  2-D FACTORED tensors (fp32 or 4-bit group-128 first
+ * moment, same shape conditions) that share a step count are likewise stepped together in four or five
+ * launches, their partial sums taken from `scratch` (lpmm_b200_unfused_step_many_scratch_bytes gives a size
+ * that serves everything; without enough scratch they are stepped one by one).  Nothing is uploaded, so both
+ * list-wide paths also run while `stream` is being captured.  `scratch` should be 256-byte aligned.  The launch
+ * chains of the other tensors are spread over four streams owned by the library (created on
  * the first such call on a device, never destroyed); they start after everything already enqueued on
  * `stream`, and `stream` waits for them before the call returns, so the caller's ordering is that of
  * a call that used `stream` alone.  While `stream` is being captured the library's streams are not used.

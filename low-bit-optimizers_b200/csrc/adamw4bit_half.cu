@@ -308,9 +308,10 @@ __device__ __forceinline__ void h_group_fp32(const TDesc& t, long long gl, int l
   }
 }
 
-// PEERS: every updated parameter also goes to the ZeRO-1 peers (ps); without it ps.n is 0 and the stores vanish
-// from the packed path.
-template <typename T, bool HAS_Q4, bool APX, bool PEERS>
+// MATH: 0 = IEEE sqrt / division (hyper-parameters outside the short sequences' domain), 1 = the short exact
+// sequences with packed arithmetic, 2 = as 1 with the tolerance-mode parameter update.  PEERS: every updated
+// parameter also goes to the ZeRO-1 peers (ps); without it ps.n is 0 and the stores vanish from the packed path.
+template <typename T, bool HAS_Q4, int MATH, bool PEERS>
 __global__ void __launch_bounds__(CTA_THREADS, CTAS_PER_SM)
 adamw4bit_half_kernel(const __grid_constant__ Table tab, const float* __restrict__ qmap_m,
                       const float* __restrict__ qmap_v, const UConsts cin, long long gbeg, long long gend,
@@ -350,14 +351,14 @@ adamw4bit_half_kernel(const __grid_constant__ Table tab, const float* __restrict
           unsigned gl = (unsigned)(gi - tstart);
           const unsigned lim = (unsigned)(fend - tstart);
           const unsigned st = (unsigned)stride;
-          if (c.f_fast && vlin) {
+          if (MATH >= 1 && vlin) {
             for (; gl < lim; gl += st)
-              h_group_x2<T, true, APX, PEERS>(t, gl, l16, hmask, k2, Sm, Sv, lut_m, lut_v, qm_l, qv_l,
-                                              (gl + PF_DIST * st < lim) ? PF_DIST * st : 0u, ps);
-          } else if (c.f_fast) {
+              h_group_x2<T, true, MATH == 2, PEERS>(t, gl, l16, hmask, k2, Sm, Sv, lut_m, lut_v, qm_l, qv_l,
+                                                    (gl + PF_DIST * st < lim) ? PF_DIST * st : 0u, ps);
+          } else if (MATH >= 1) {
             for (; gl < lim; gl += st)
-              h_group_x2<T, false, APX, PEERS>(t, gl, l16, hmask, k2, Sm, Sv, lut_m, lut_v, qm_l, qv_l,
-                                               (gl + PF_DIST * st < lim) ? PF_DIST * st : 0u, ps);
+              h_group_x2<T, false, MATH == 2, PEERS>(t, gl, l16, hmask, k2, Sm, Sv, lut_m, lut_v, qm_l, qv_l,
+                                                     (gl + PF_DIST * st < lim) ? PF_DIST * st : 0u, ps);
           } else if (vlin) {  // hyper-parameters outside the short sequences' domain: IEEE sqrt and division
             for (; gl < lim; gl += st)
               h_group_fast<T, true>(t, gl, l16, hmask, c, Sm, Sv, lut_m, lut_v, qm_l, qv_l,
@@ -377,7 +378,7 @@ adamw4bit_half_kernel(const __grid_constant__ Table tab, const float* __restrict
   }
 }
 
-template <typename T, bool HAS_Q4, bool APX, bool PEERS>
+template <typename T, bool HAS_Q4, int MATH, bool PEERS>
 static cudaError_t launch_half(const Table& tab, unsigned grid, const float* qm, const float* qv, const UConsts& c,
                                long long lo, long long hi, cudaStream_t st, const PeerStores& ps) {
   static bool attr_set[64] = {};
@@ -385,12 +386,12 @@ static cudaError_t launch_half(const Table& tab, unsigned grid, const float* qm,
   cudaGetDevice(&dev);
   const size_t smem = HAS_Q4 ? H_DYN_SMEM : 0;
   if (HAS_Q4 && dev >= 0 && dev < 64 && !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(adamw4bit_half_kernel<T, HAS_Q4, APX, PEERS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(adamw4bit_half_kernel<T, HAS_Q4, MATH, PEERS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)H_DYN_SMEM);
     if (e != cudaSuccess) return e;
     attr_set[dev] = true;
   }
-  adamw4bit_half_kernel<T, HAS_Q4, APX, PEERS><<<grid, CTA_THREADS, smem, st>>>(tab, qm, qv, c, lo, hi, ps);
+  adamw4bit_half_kernel<T, HAS_Q4, MATH, PEERS><<<grid, CTA_THREADS, smem, st>>>(tab, qm, qv, c, lo, hi, ps);
   return cudaGetLastError();
 }
 
@@ -398,15 +399,22 @@ static cudaError_t launch_half(const Table& tab, unsigned grid, const float* qm,
 
 using namespace lpmm_b200;
 
+template <typename T, bool HAS_Q4, bool PEERS>
+static cudaError_t launch_half_math(int math, const Table& tab, unsigned grid, const float* qm, const float* qv,
+                                    const UConsts& c, long long lo, long long hi, cudaStream_t st, const PeerStores& ps) {
+  if (math == 2 && HAS_Q4) return launch_half<T, HAS_Q4, HAS_Q4 ? 2 : 1, PEERS>(tab, grid, qm, qv, c, lo, hi, st, ps);
+  return math ? launch_half<T, HAS_Q4, 1, PEERS>(tab, grid, qm, qv, c, lo, hi, st, ps)
+              : launch_half<T, HAS_Q4, 0, PEERS>(tab, grid, qm, qv, c, lo, hi, st, ps);
+}
+
+// math: 0 IEEE, 1 short exact sequences, 2 tolerance-mode parameter update
 template <typename T>
-static cudaError_t launch_half_any(bool any_q4, bool apx, const Table& tab, unsigned grid, const float* qm, const float* qv,
+static cudaError_t launch_half_any(bool any_q4, int math, const Table& tab, unsigned grid, const float* qm, const float* qv,
                                    const UConsts& c, long long lo, long long hi, cudaStream_t st, const PeerStores& ps) {
   if (ps.n > 0)  // with peers always the 4-bit instantiation (it also steps fp32-state tensors); the maps are required
-    return apx ? launch_half<T, true, true, true>(tab, grid, qm, qv, c, lo, hi, st, ps)
-               : launch_half<T, true, false, true>(tab, grid, qm, qv, c, lo, hi, st, ps);
-  if (!any_q4) return launch_half<T, false, false, false>(tab, grid, qm, qv, c, lo, hi, st, ps);
-  return apx ? launch_half<T, true, true, false>(tab, grid, qm, qv, c, lo, hi, st, ps)
-             : launch_half<T, true, false, false>(tab, grid, qm, qv, c, lo, hi, st, ps);
+    return launch_half_math<T, true, true>(math, tab, grid, qm, qv, c, lo, hi, st, ps);
+  if (!any_q4) return launch_half_math<T, false, false>(math, tab, grid, qm, qv, c, lo, hi, st, ps);
+  return launch_half_math<T, true, false>(math, tab, grid, qm, qv, c, lo, hi, st, ps);
 }
 
 static int half_entry(const lpmm_b200_tensor* ts, int n, int dtype, const float* qmap_m, const float* qmap_v,
@@ -426,6 +434,7 @@ static int half_entry(const lpmm_b200_tensor* ts, int n, int dtype, const float*
   // the folded constants of the tolerance mode need a finite 1 / lr
   const bool apx = (flags & LPMM_B200_FLAG_PARAMS_WITHIN_TOLERANCE) && c.f_fast && h.lr >= 0x1p-60f && h.lr <= 0x1p30f &&
                    h.weight_decay <= 0x1p30f;
+  const int math = apx ? 2 : (c.f_fast ? 1 : 0);
   static thread_local Table tab;
   int64_t gcursor = 0;
   int i = 0;
@@ -435,8 +444,8 @@ static int half_entry(const lpmm_b200_tensor* ts, int n, int dtype, const float*
     if (!w.work) continue;
     const unsigned grid = multi_grid(w);
     const cudaError_t e = dtype == LPMM_B200_DTYPE_BF16
-                              ? launch_half_any<__nv_bfloat16>(w.any_q4, apx, tab, grid, qmap_m, qmap_v, c, w.lo, w.hi, st, ps)
-                              : launch_half_any<__half>(w.any_q4, apx, tab, grid, qmap_m, qmap_v, c, w.lo, w.hi, st, ps);
+                              ? launch_half_any<__nv_bfloat16>(w.any_q4, math, tab, grid, qmap_m, qmap_v, c, w.lo, w.hi, st, ps)
+                              : launch_half_any<__half>(w.any_q4, math, tab, grid, qmap_m, qmap_v, c, w.lo, w.hi, st, ps);
     LPMM_CUDA_TRY(e);
   }
   return LPMM_B200_OK;

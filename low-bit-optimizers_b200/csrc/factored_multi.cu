@@ -8,8 +8,9 @@
 // from torch's reductions, which is why the accumulators and parameters agree with the reference to
 // 1e-6 relative rather than bit for bit (first-moment codes are still identical in the tests).
 //
-// The tensors are described by a table in device memory; tiles, rows, columns and 128-element units are
-// numbered across the whole list and fixed grids stride over them.
+// The tensors are described by a table carried in the launch parameters (up to F_MAX per launch; a longer list is
+// stepped in windows), so nothing is uploaded and the launches can be captured into a CUDA graph; tiles, rows,
+// column blocks and 128-element units are numbered across the whole window and fixed grids stride over them.
 #include <math.h>
 
 #include <vector>
@@ -43,8 +44,19 @@ struct FDesc {
   int tiles_x, tiles_y, rows_per_tile, tx_shift, slots, m_quant;
 };
 
+constexpr int F_MAX = 224;  // descriptors per launch: 144 bytes each, 32 KB of launch parameters in all
+struct FTable {
+  int n;
+  int first;            // index of the first descriptor the scalar update kernel steps (the wide ones come before)
+  long long tiles;      // tiles of the sums pass
+  long long units;      // 128-element units of the descriptors from `first` on
+  long long rows;       // rows of all matrices of the window
+  long long row_blocks; // CTAs of the finalize pass that take rows (the others take 32-column blocks)
+  FDesc t[F_MAX];
+};
+
 template <int WHICH>  // 0: ustart, 1: tstart, 2: rstart, 3: cstart
-__device__ __forceinline__ int f_find(const FDesc* __restrict__ d, int n, long long x) {
+__device__ __forceinline__ int f_find(const FDesc* d, int n, long long x) {
   int lo = 0, hi = n - 1;
   while (lo < hi) {
     const int mid = (lo + hi + 1) >> 1;
@@ -59,7 +71,10 @@ __device__ __forceinline__ int f_find(const FDesc* __restrict__ d, int n, long l
 // each) by 256 >> tx_shift row-lanes.  Column sums: per thread over its rows (in row order), then over the
 // row-lanes in lane order through shared memory.  Row sums: the thread's 8 squares in column order, then a
 // butterfly over the lanes that share the row inside a warp; one partial per 256-column segment.
-__global__ void __launch_bounds__(FT) f_sums_kernel(const FDesc* __restrict__ d, int n, long long total_tiles) {
+__global__ void __launch_bounds__(FT) f_sums_kernel(const __grid_constant__ FTable tab) {
+  const FDesc* d = tab.t;
+  const int n = tab.n;
+  const long long total_tiles = tab.tiles;
   __shared__ float colbuf[8 * FT];
   for (long long tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
     const FDesc& t = d[f_find<1>(d, n, tile)];
@@ -148,8 +163,10 @@ __global__ void __launch_bounds__(FT) f_sums_kernel(const FDesc* __restrict__ d,
 // few segment partials in slot order.  The other CTAs take 32 columns of one matrix each: a tall matrix has
 // hundreds of tile partials per column, so the CTA's 8 warps share them (warp w sums tiles w, w + 8, ... in
 // order) and the 8 sums are added in warp order.  Fixed order throughout: results are reproducible.
-__global__ void __launch_bounds__(FT) f_finalize_kernel(const FDesc* __restrict__ d, int n, long long total_rows,
-                                                         long long row_blocks, const UConsts c) {
+__global__ void __launch_bounds__(FT) f_finalize_kernel(const __grid_constant__ FTable tab, const UConsts c) {
+  const FDesc* d = tab.t;
+  const int n = tab.n;
+  const long long total_rows = tab.rows, row_blocks = tab.row_blocks;
   __shared__ float part[8][32];
   if ((long long)blockIdx.x < row_blocks) {
     const long long i = (long long)blockIdx.x * FT + threadIdx.x;
@@ -182,9 +199,9 @@ __global__ void __launch_bounds__(FT) f_finalize_kernel(const FDesc* __restrict_
 // row[r] / mean for every row, for the update pass of wide matrices (f_update2_kernel): the first slot of the row
 // partials is free again after pass 2.
 constexpr int FMT = 1024;
-__global__ void __launch_bounds__(FMT) f_row_mean_kernel(const FDesc* __restrict__ d) {
+__global__ void __launch_bounds__(FMT) f_row_mean_kernel(const __grid_constant__ FTable tab) {
   __shared__ float red[FMT];
-  const FDesc& t = d[blockIdx.x];
+  const FDesc& t = tab.t[blockIdx.x];
   float acc = 0.0f;
   for (long long j = threadIdx.x; j < t.R; j += FMT) acc = __fadd_rn(acc, t.row[j]);
   red[threadIdx.x] = acc;
@@ -294,8 +311,11 @@ __device__ __forceinline__ void f_unit(const FDesc& t, long long u, int l16, uns
   if (l16 == 0) t.m_max1[u] = am;
 }
 
-__global__ void __launch_bounds__(FT, 4) f_update_kernel(const FDesc* __restrict__ d, int n, long long total_units,
+__global__ void __launch_bounds__(FT, 4) f_update_kernel(const __grid_constant__ FTable tab,
                                                           const float* __restrict__ qmap_m, const UConsts c) {
+  const FDesc* d = tab.t + tab.first;
+  const int n = tab.n - tab.first;
+  const long long total_units = tab.units;
   extern __shared__ __align__(16) unsigned char dyn_smem[];
   __shared__ QMapSmem Sm;
   LutEnt* lut_m = reinterpret_cast<LutEnt*>(dyn_smem);
@@ -456,38 +476,42 @@ extern "C" int lpmm_b200_factored_multi_ok(const lpmm_b200_step_tensor* t) {
   return 1;
 }
 
-// Bytes of device scratch the list needs: the table, one row-mean slot per tensor and the partial sums
-// (column partials for tiles of at least F_MIN_ROWS rows, row partials per 256-column segment).
+// Bytes of device scratch the list needs: one row-mean slot per tensor and the partial sums (column partials for
+// tiles of at least F_MIN_ROWS rows, row partials per 256-column segment).
 extern "C" int64_t lpmm_b200_factored_multi_scratch_bytes(const lpmm_b200_step_tensor* const* ts, int n) {
   int64_t floats = 0;
   for (int i = 0; i < n; ++i) {
     const int64_t R = ts[i]->shape[0], C = ts[i]->shape[1];
     floats += f_align(((R + F_MIN_ROWS - 1) / F_MIN_ROWS) * C) + f_align(((C + 255) / 256) * R) + 64;
   }
-  return 4 * floats + (int64_t)(((sizeof(FDesc) * (size_t)(n > 0 ? n : 0)) + 255) & ~(size_t)255);
+  return 4 * floats;
 }
 
-extern "C" int lpmm_b200_factored_multi_step(const lpmm_b200_step_tensor* const* ts, int n, const float* qmap_m,
-                                             double beta1, double beta2, double lr, double weight_decay, double eps,
-                                             double step, void* scratch, int64_t scratch_bytes, void* stream) {
-  if (n <= 0) return LPMM_B200_OK;
-  if (!ts || !scratch) return LPMM_B200_ERR_NULL_POINTER;
-  bool any_q = false;
-  long long total_elems = 0;
-  for (int i = 0; i < n; ++i) {
-    if (!lpmm_b200_factored_multi_ok(ts[i])) return LPMM_B200_ERR_UNSUPPORTED;
-    any_q = any_q || ts[i]->m_mode == LPMM_B200_STATE_GROUP4;
-    total_elems += ts[i]->numel;
+static int f_occupancy(int* out) {
+  static int sums_ctas[64] = {};  // CTAs of the sums kernel one SM holds, per device
+  int cur = 0;
+  cudaGetDevice(&cur);
+  int per_sm = (cur >= 0 && cur < 64) ? sums_ctas[cur] : 0;
+  if (per_sm == 0) {
+    LPMM_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, f_sums_kernel, FT, 0));
+    if (per_sm < 1) per_sm = 1;
+    if (cur >= 0 && cur < 64) sums_ctas[cur] = per_sm;
+    LPMM_CUDA_TRY(cudaFuncSetAttribute(f_update_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)F_DYN_SMEM));
+    LPMM_CUDA_TRY(cudaFuncSetAttribute(f_update2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)F_DYN_SMEM));
   }
-  if (any_q && !qmap_m) return LPMM_B200_ERR_NULL_POINTER;
-  if (scratch_bytes < lpmm_b200_factored_multi_scratch_bytes(ts, n)) return LPMM_B200_ERR_BAD_SIZE;
-  if ((uintptr_t)scratch & 255) return LPMM_B200_ERR_BAD_SIZE;
-  cudaStream_t st = (cudaStream_t)stream;
-  static thread_local std::vector<FDesc> host;
+  *out = per_sm;
+  return LPMM_B200_OK;
+}
+
+// One window of at most F_MAX tensors; fbase: this window's slice of the partial-sum scratch.
+static int f_window(const lpmm_b200_step_tensor* const* ts, int n, const float* qmap_m, bool any_q, const UConsts& c,
+                    float* fbase, cudaStream_t st) {
+  static thread_local FTable tab;  // 32 KB; copied into the launch parameters by the runtime
+  static thread_local F2Table tab2;
   static thread_local std::vector<int> order;
-  host.resize(n);
   order.clear();
-  const UConsts c = make_consts(beta1, beta2, lr, weight_decay, eps, step);
+  long long total_elems = 0;
+  for (int i = 0; i < n; ++i) total_elems += ts[i]->numel;
   // Matrices whose rows are whole 128-element groups, with a 4-bit first moment, take f_update2_kernel; they come
   // first in the table.  That kernel has no scalar path: it needs the short exact sequences and 32-byte alignment.
   auto wide = [&](const lpmm_b200_step_tensor* t) {
@@ -499,8 +523,6 @@ extern "C" int lpmm_b200_factored_multi_step(const lpmm_b200_step_tensor* const*
   const int n_wide = (int)order.size();
   for (int i = 0; i < n; ++i)
     if (!wide(ts[i])) order.push_back(i);
-  const int64_t table_bytes = (int64_t)(((sizeof(FDesc) * (size_t)n) + 255) & ~(size_t)255);
-  float* fbase = reinterpret_cast<float*>(static_cast<char*>(scratch) + table_bytes);
   // about twenty tiles per SM; a grid of resident CTAs (as many as the SMs hold) strides over them
   const long long target_tiles = (long long)num_sms() * 20;
   long long per_tile = (total_elems + target_tiles - 1) / target_tiles;
@@ -509,7 +531,7 @@ extern "C" int lpmm_b200_factored_multi_step(const lpmm_b200_step_tensor* const*
   int64_t foff = 0;
   for (int k = 0; k < n; ++k) {
     const lpmm_b200_step_tensor* t = ts[order[k]];
-    FDesc& d = host[k];
+    FDesc& d = tab.t[k];
     d.p = t->p;
     d.g = t->g;
     d.m = reinterpret_cast<uint8_t*>(t->m);
@@ -547,41 +569,28 @@ extern "C" int lpmm_b200_factored_multi_step(const lpmm_b200_step_tensor* const*
     rows_total += d.R;
     cblocks += (d.C + 31) / 32;
   }
-  LPMM_CUDA_TRY(cudaMemcpyAsync(scratch, host.data(), sizeof(FDesc) * (size_t)n, cudaMemcpyHostToDevice, st));
-  const FDesc* dev = reinterpret_cast<const FDesc*>(scratch);
-  static int sums_ctas[64] = {};  // CTAs of the sums kernel one SM holds, per device
-  int cur = 0;
-  cudaGetDevice(&cur);
-  int per_sm = (cur >= 0 && cur < 64) ? sums_ctas[cur] : 0;
-  if (per_sm == 0) {
-    LPMM_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, f_sums_kernel, FT, 0));
-    if (per_sm < 1) per_sm = 1;
-    if (cur >= 0 && cur < 64) sums_ctas[cur] = per_sm;
-  }
+  tab.n = n;
+  tab.first = n_wide;
+  tab.tiles = tiles;
+  tab.units = units;
+  tab.rows = rows_total;
+  tab.row_blocks = (rows_total + FT - 1) / FT;
+  int per_sm = 1;
+  const int rc = f_occupancy(&per_sm);
+  if (rc != LPMM_B200_OK) return rc;
   const long long resident = (long long)num_sms() * per_sm;
   const long long sgrid = tiles < resident ? tiles : resident;
-  f_sums_kernel<<<(unsigned)sgrid, FT, 0, st>>>(dev, n, tiles);
+  f_sums_kernel<<<(unsigned)sgrid, FT, 0, st>>>(tab);
   LPMM_CUDA_TRY(cudaGetLastError());
-  const long long row_blocks = (rows_total + FT - 1) / FT;
-  f_finalize_kernel<<<(unsigned)(row_blocks + cblocks), FT, 0, st>>>(dev, n, rows_total, row_blocks, c);
+  f_finalize_kernel<<<(unsigned)(tab.row_blocks + cblocks), FT, 0, st>>>(tab, c);
   LPMM_CUDA_TRY(cudaGetLastError());
-  f_row_mean_kernel<<<(unsigned)n, FMT, 0, st>>>(dev);
+  f_row_mean_kernel<<<(unsigned)n, FMT, 0, st>>>(tab);
   LPMM_CUDA_TRY(cudaGetLastError());
-  static bool attr_set[64] = {};
-  int devi = 0;
-  cudaGetDevice(&devi);
-  if (devi >= 0 && devi < 64 && !attr_set[devi]) {
-    LPMM_CUDA_TRY(cudaFuncSetAttribute(f_update_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)F_DYN_SMEM));
-    LPMM_CUDA_TRY(cudaFuncSetAttribute(f_update2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)F_DYN_SMEM));
-    attr_set[devi] = true;
-  }
-  static thread_local F2Table tab;
-  for (int k0 = 0; k0 < n_wide; k0 += F2_MAX) {
-    const int cnt = (n_wide - k0 < F2_MAX) ? n_wide - k0 : F2_MAX;
+  if (n_wide > 0) {
     long long g2 = 0;
-    for (int k = 0; k < cnt; ++k) {
-      const FDesc& d = host[k0 + k];
-      F2Desc& w = tab.t[k];
+    for (int k = 0; k < n_wide; ++k) {
+      const FDesc& d = tab.t[k];
+      F2Desc& w = tab2.t[k];
       w.p = d.p;
       w.g = d.g;
       w.m = reinterpret_cast<uint32_t*>(d.m);
@@ -593,20 +602,45 @@ extern "C" int lpmm_b200_factored_multi_step(const lpmm_b200_step_tensor* const*
       w.pad_ = 0;
       g2 += d.n / 128;
     }
-    tab.n = cnt;
-    tab.pad_ = 0;
-    tab.total = g2;
+    tab2.n = n_wide;
+    tab2.pad_ = 0;
+    tab2.total = g2;
     long long grid2 = (g2 + F2_HW - 1) / F2_HW;
     if (grid2 > num_sms()) grid2 = num_sms();
-    f_update2_kernel<<<(unsigned)grid2, F2T, F_DYN_SMEM, st>>>(tab, qmap_m, c);
+    f_update2_kernel<<<(unsigned)grid2, F2T, F_DYN_SMEM, st>>>(tab2, qmap_m, c);
     LPMM_CUDA_TRY(cudaGetLastError());
   }
   if (n > n_wide) {
     long long ugrid = (units + FT / 16 - 1) / (FT / 16);
     const long long ucap = (long long)num_sms() * 4;
     if (ugrid > ucap) ugrid = ucap;
-    f_update_kernel<<<(unsigned)ugrid, FT, F_DYN_SMEM, st>>>(dev + n_wide, n - n_wide, units, any_q ? qmap_m : nullptr, c);
+    f_update_kernel<<<(unsigned)ugrid, FT, F_DYN_SMEM, st>>>(tab, any_q ? qmap_m : nullptr, c);
     LPMM_CUDA_TRY(cudaGetLastError());
+  }
+  return LPMM_B200_OK;
+}
+
+extern "C" int lpmm_b200_factored_multi_step(const lpmm_b200_step_tensor* const* ts, int n, const float* qmap_m,
+                                             double beta1, double beta2, double lr, double weight_decay, double eps,
+                                             double step, void* scratch, int64_t scratch_bytes, void* stream) {
+  if (n <= 0) return LPMM_B200_OK;
+  if (!ts || !scratch) return LPMM_B200_ERR_NULL_POINTER;
+  bool any_q = false;
+  for (int i = 0; i < n; ++i) {
+    if (!lpmm_b200_factored_multi_ok(ts[i])) return LPMM_B200_ERR_UNSUPPORTED;
+    any_q = any_q || ts[i]->m_mode == LPMM_B200_STATE_GROUP4;
+  }
+  if (any_q && !qmap_m) return LPMM_B200_ERR_NULL_POINTER;
+  if (scratch_bytes < lpmm_b200_factored_multi_scratch_bytes(ts, n)) return LPMM_B200_ERR_BAD_SIZE;
+  if ((uintptr_t)scratch & 255) return LPMM_B200_ERR_BAD_SIZE;
+  const UConsts c = make_consts(beta1, beta2, lr, weight_decay, eps, step);
+  static_assert(F_MAX <= F2_MAX, "a window of wide matrices must fit the second table");
+  char* base = static_cast<char*>(scratch);
+  for (int i = 0; i < n; i += F_MAX) {
+    const int cnt = (n - i < F_MAX) ? n - i : F_MAX;
+    const int rc = f_window(ts + i, cnt, qmap_m, any_q, c, reinterpret_cast<float*>(base), (cudaStream_t)stream);
+    if (rc != LPMM_B200_OK) return rc;
+    base += lpmm_b200_factored_multi_scratch_bytes(ts + i, cnt);  // multiples of 256 bytes
   }
   return LPMM_B200_OK;
 }

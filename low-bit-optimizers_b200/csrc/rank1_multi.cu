@@ -7,10 +7,11 @@
 // lpmm/functional.py:190-203, 97-106, 512-531); arithmetic and state layout here are those of the
 // per-tensor launches in unfused.cu, bit for bit.
 //
-// The tensors are described by a table in device memory (the launch parameters cannot hold per-tensor
-// shapes and five state pointers for hundreds of tensors).  Work is cut into tiles (statistics) and
-// 128-element units (update) numbered across the whole list, and a fixed grid of persistent CTAs
-// strides over them, so small and large matrices share the machine and nothing waits for a tiny launch.
+// The tensors are described by a table carried in the launch parameters (up to R1_MAX per launch; a longer list
+// is stepped in windows), so nothing is uploaded and the launches can be captured into a CUDA graph.  Work is
+// cut into tiles (statistics) and 128-element units (update) numbered across the whole window, and a fixed
+// grid of persistent CTAs strides over them, so small and large matrices share the machine and nothing waits
+// for a tiny launch.
 #include <math.h>
 
 #include <vector>
@@ -45,9 +46,18 @@ struct R1Desc {
 };
 
 
+constexpr int R1_MAX = 268;  // descriptors per launch: 120 bytes each, 32 KB of launch parameters in all
+struct R1Table {
+  int n;
+  int first;            // index of the first descriptor the scalar update kernel steps (the wide ones come before)
+  long long tiles;      // statistics tiles of the window
+  long long units;      // 128-element units of the descriptors from `first` on
+  R1Desc t[R1_MAX];
+};
+
 // Index of the last descriptor whose `start` field (ustart / tstart) is <= x.
 template <bool TILES>
-__device__ __forceinline__ int r1_find(const R1Desc* __restrict__ d, int n, long long x) {
+__device__ __forceinline__ int r1_find(const R1Desc* d, int n, long long x) {
   int lo = 0, hi = n - 1;
   while (lo < hi) {
     const int mid = (lo + hi + 1) >> 1;
@@ -57,8 +67,8 @@ __device__ __forceinline__ int r1_find(const R1Desc* __restrict__ d, int n, long
   return lo;
 }
 
-__global__ void __launch_bounds__(R1T) r1_zero_kernel(const R1Desc* __restrict__ d) {
-  const R1Desc& t = d[blockIdx.x];
+__global__ void __launch_bounds__(R1T) r1_zero_kernel(const __grid_constant__ R1Table tab) {
+  const R1Desc& t = tab.t[blockIdx.x];
   for (int i = threadIdx.x; i < t.R; i += R1T) t.new_r[i] = 0.0f;
   for (int i = threadIdx.x; i < t.C; i += R1T) t.new_c[i] = 0.0f;
 }
@@ -96,8 +106,11 @@ __device__ __forceinline__ float r1_row_pass(float qv_l, const float* col_old, f
 }
 
 template <bool A>
-__global__ void __launch_bounds__(R1T) r1_stats_kernel(const R1Desc* __restrict__ d, int n, long long total_tiles,
+__global__ void __launch_bounds__(R1T) r1_stats_kernel(const __grid_constant__ R1Table tab,
                                                         const float* __restrict__ qmap_v, const UConsts cin) {
+  const R1Desc* d = tab.t;
+  const int n = tab.n;
+  const long long total_tiles = tab.tiles;
   UConsts cf;
   if (A) cf = fused_consts(cin);
   const UConsts& c = A ? cf : cin;
@@ -345,9 +358,12 @@ __device__ __forceinline__ void r1_unit(const R1Desc& t, long long u, int l16, u
 }
 
 template <bool A>
-__global__ void __launch_bounds__(R1T, 4) r1_update_kernel(const R1Desc* __restrict__ d, int n, long long total_units,
+__global__ void __launch_bounds__(R1T, 4) r1_update_kernel(const __grid_constant__ R1Table tab,
                                                             const float* __restrict__ qmap_m,
                                                             const float* __restrict__ qmap_v, const UConsts cin) {
+  const R1Desc* d = tab.t + tab.first;
+  const int n = tab.n - tab.first;
+  const long long total_units = tab.units;
   UConsts cf;
   if (A) cf = fused_consts(cin);
   const UConsts& c = A ? cf : cin;
@@ -555,10 +571,13 @@ __global__ void __launch_bounds__(R2T, 1) r1_update2_kernel(const __grid_constan
 
 using namespace lpmm_b200;
 
-// Host side.  `ts`: n tensors that all satisfy lpmm_b200_rank1_multi_ok; `table`: device memory for n
-// descriptors (lpmm_b200_rank1_multi_table_bytes(n)).  Not part of the public header: called by
-// lpmm_b200_adamw4bit_unfused_step_many.
-extern "C" int64_t lpmm_b200_rank1_multi_table_bytes(int n) { return (int64_t)sizeof(R1Desc) * (n > 0 ? n : 0); }
+// Host side.  `ts`: n tensors that all satisfy lpmm_b200_rank1_multi_ok.  Not part of the public header: called
+// by lpmm_b200_adamw4bit_unfused_step_many.  The descriptors travel in the launch parameters: `table` is unused
+// (kept for the callers' signature) and lpmm_b200_rank1_multi_table_bytes is 0.
+extern "C" int64_t lpmm_b200_rank1_multi_table_bytes(int n) {
+  (void)n;
+  return 0;
+}
 
 extern "C" int lpmm_b200_rank1_multi_ok(const lpmm_b200_step_tensor* t) {
   if (!t || t->first || t->numel <= 0 || t->ndim != 2) return 0;
@@ -576,24 +595,33 @@ extern "C" int lpmm_b200_rank1_multi_ok(const lpmm_b200_step_tensor* t) {
   return 1;
 }
 
-extern "C" int lpmm_b200_rank1_multi_step(const lpmm_b200_step_tensor* const* ts, int n, const float* qmap_m,
-                                          const float* qmap_v, double beta1, double beta2, double lr,
-                                          double weight_decay, double eps, double step, void* table,
-                                          int64_t table_bytes, void* stream, int arith) {
-  if (n <= 0) return LPMM_B200_OK;
-  if (!ts || !qmap_m || !qmap_v || !table) return LPMM_B200_ERR_NULL_POINTER;
-  if (table_bytes < lpmm_b200_rank1_multi_table_bytes(n)) return LPMM_B200_ERR_BAD_SIZE;
-  cudaStream_t st = (cudaStream_t)stream;
-  static thread_local std::vector<R1Desc> host;
-  static thread_local std::vector<int> order;
-  host.resize(n);
-  order.clear();
-  const UConsts c = make_consts(beta1, beta2, lr, weight_decay, eps, step);
-  long long total_elems = 0;
-  for (int i = 0; i < n; ++i) {
-    if (!lpmm_b200_rank1_multi_ok(ts[i])) return LPMM_B200_ERR_UNSUPPORTED;
-    total_elems += ts[i]->numel;
+static int r1_occupancy(int* out) {
+  static int stats_ctas[64] = {};  // CTAs of the statistics kernel one SM holds, per device
+  int cur = 0;
+  cudaGetDevice(&cur);
+  int per_sm = (cur >= 0 && cur < 64) ? stats_ctas[cur] : 0;
+  if (per_sm == 0) {
+    LPMM_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, r1_stats_kernel<false>, R1T, 0));
+    if (per_sm < 1) per_sm = 1;
+    if (cur >= 0 && cur < 64) stats_ctas[cur] = per_sm;
+    LPMM_CUDA_TRY(cudaFuncSetAttribute(r1_update_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)R1_DYN_SMEM));
+    LPMM_CUDA_TRY(cudaFuncSetAttribute(r1_update_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)R1_DYN_SMEM));
+    LPMM_CUDA_TRY(cudaFuncSetAttribute(r1_update2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)R1_DYN_SMEM));
+    LPMM_CUDA_TRY(cudaFuncSetAttribute(r1_update2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)R1_DYN_SMEM));
   }
+  *out = per_sm;
+  return LPMM_B200_OK;
+}
+
+// One window of at most R1_MAX tensors: zero, statistics, update.
+static int r1_window(const lpmm_b200_step_tensor* const* ts, int n, const float* qmap_m, const float* qmap_v,
+                     const UConsts& c, cudaStream_t st, int arith) {
+  static thread_local R1Table tab;   // 32 KB; copied into the launch parameters by the runtime
+  static thread_local R2Table tab2;
+  static thread_local std::vector<int> order;
+  order.clear();
+  long long total_elems = 0;
+  for (int i = 0; i < n; ++i) total_elems += ts[i]->numel;
   // Matrices whose rows are whole 128-element groups take the update kernel shaped like the fused step
   // (r1_update2_kernel); they come first in the table.  It has no scalar path, so it needs the short exact
   // sequences (hyper-parameters inside their domain) and 32-byte aligned parameters and gradients.
@@ -607,7 +635,7 @@ extern "C" int lpmm_b200_rank1_multi_step(const lpmm_b200_step_tensor* const* ts
   const int n_wide = (int)order.size();
   for (int i = 0; i < n; ++i)
     if (!wide(ts[i])) order.push_back(i);
-  // statistics tiles: about sixteen per SM over the whole list, at least 4 rows each; a grid of resident CTAs
+  // statistics tiles: about sixteen per SM over the whole window, at least 4 rows each; a grid of resident CTAs
   // (as many of 256 threads as an SM holds) strides over them, so the last tiles level the load
   const long long target_tiles = (long long)num_sms() * 16;
   long long per_tile = (total_elems + target_tiles - 1) / target_tiles;
@@ -615,7 +643,7 @@ extern "C" int lpmm_b200_rank1_multi_step(const lpmm_b200_step_tensor* const* ts
   long long units = 0, tiles = 0;  // units: 128-element units of the matrices that are NOT wide (numbered from 0)
   for (int k = 0; k < n; ++k) {
     const lpmm_b200_step_tensor* t = ts[order[k]];
-    R1Desc& d = host[k];
+    R1Desc& d = tab.t[k];
     d.p = t->p;
     d.g = t->g;
     d.m = reinterpret_cast<uint8_t*>(t->m);
@@ -644,42 +672,25 @@ extern "C" int lpmm_b200_rank1_multi_step(const lpmm_b200_step_tensor* const* ts
     if (k >= n_wide) units += (t->numel + 127) / 128;
     tiles += (long long)d.tiles_x * ((d.R + rows - 1) / rows);
   }
-  LPMM_CUDA_TRY(cudaMemcpyAsync(table, host.data(), sizeof(R1Desc) * (size_t)n, cudaMemcpyHostToDevice, st));
-  const R1Desc* dev = reinterpret_cast<const R1Desc*>(table);
-  r1_zero_kernel<<<(unsigned)n, R1T, 0, st>>>(dev);
+  tab.n = n;
+  tab.first = n_wide;
+  tab.tiles = tiles;
+  tab.units = units;
+  int per_sm = 1;
+  const int rc = r1_occupancy(&per_sm);
+  if (rc != LPMM_B200_OK) return rc;
+  r1_zero_kernel<<<(unsigned)n, R1T, 0, st>>>(tab);
   LPMM_CUDA_TRY(cudaGetLastError());
-  static int stats_ctas[64] = {};  // CTAs of the statistics kernel one SM holds, per device
-  int cur = 0;
-  cudaGetDevice(&cur);
-  int per_sm = (cur >= 0 && cur < 64) ? stats_ctas[cur] : 0;
-  if (per_sm == 0) {
-    LPMM_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, r1_stats_kernel<false>, R1T, 0));
-    if (per_sm < 1) per_sm = 1;
-    if (cur >= 0 && cur < 64) stats_ctas[cur] = per_sm;
-  }
   const long long resident = (long long)num_sms() * per_sm;
-  long long sgrid = tiles < resident ? tiles : resident;
-  if (arith) r1_stats_kernel<true><<<(unsigned)sgrid, R1T, 0, st>>>(dev, n, tiles, qmap_v, c);
-  else r1_stats_kernel<false><<<(unsigned)sgrid, R1T, 0, st>>>(dev, n, tiles, qmap_v, c);
+  const long long sgrid = tiles < resident ? tiles : resident;
+  if (arith) r1_stats_kernel<true><<<(unsigned)sgrid, R1T, 0, st>>>(tab, qmap_v, c);
+  else r1_stats_kernel<false><<<(unsigned)sgrid, R1T, 0, st>>>(tab, qmap_v, c);
   LPMM_CUDA_TRY(cudaGetLastError());
-  static bool attr_set[64] = {};
-  int devi = 0;
-  cudaGetDevice(&devi);
-  if (devi >= 0 && devi < 64 && !attr_set[devi]) {
-    LPMM_CUDA_TRY(cudaFuncSetAttribute(r1_update_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)R1_DYN_SMEM));
-    LPMM_CUDA_TRY(cudaFuncSetAttribute(r1_update_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)R1_DYN_SMEM));
-    LPMM_CUDA_TRY(cudaFuncSetAttribute(r1_update2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)R1_DYN_SMEM));
-    LPMM_CUDA_TRY(cudaFuncSetAttribute(r1_update2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)R1_DYN_SMEM));
-    attr_set[devi] = true;
-  }
-  // wide matrices: windows of at most R2_MAX descriptors in the launch parameters
-  static thread_local R2Table tab;
-  for (int k0 = 0; k0 < n_wide; k0 += R2_MAX) {
-    const int cnt = (n_wide - k0 < R2_MAX) ? n_wide - k0 : R2_MAX;
+  if (n_wide > 0) {
     long long g2 = 0;
-    for (int k = 0; k < cnt; ++k) {
-      const R1Desc& d = host[k0 + k];
-      R2Desc& w = tab.t[k];
+    for (int k = 0; k < n_wide; ++k) {
+      const R1Desc& d = tab.t[k];
+      R2Desc& w = tab2.t[k];
       w.p = d.p;
       w.g = d.g;
       w.m = reinterpret_cast<uint32_t*>(d.m);
@@ -694,22 +705,42 @@ extern "C" int lpmm_b200_rank1_multi_step(const lpmm_b200_step_tensor* const* ts
       w.pad_ = 0;
       g2 += d.n / 128;
     }
-    tab.n = cnt;
-    tab.pad_ = 0;
-    tab.total = g2;
+    tab2.n = n_wide;
+    tab2.pad_ = 0;
+    tab2.total = g2;
     long long grid2 = (g2 + R2_HW - 1) / R2_HW;
     if (grid2 > num_sms()) grid2 = num_sms();
-    if (arith) r1_update2_kernel<true><<<(unsigned)grid2, R2T, R1_DYN_SMEM, st>>>(tab, qmap_m, qmap_v, c);
-    else r1_update2_kernel<false><<<(unsigned)grid2, R2T, R1_DYN_SMEM, st>>>(tab, qmap_m, qmap_v, c);
+    if (arith) r1_update2_kernel<true><<<(unsigned)grid2, R2T, R1_DYN_SMEM, st>>>(tab2, qmap_m, qmap_v, c);
+    else r1_update2_kernel<false><<<(unsigned)grid2, R2T, R1_DYN_SMEM, st>>>(tab2, qmap_m, qmap_v, c);
     LPMM_CUDA_TRY(cudaGetLastError());
   }
   if (n > n_wide) {
     long long ugrid = (units + R1T / 16 - 1) / (R1T / 16);
     const long long ucap = (long long)num_sms() * 4;
     if (ugrid > ucap) ugrid = ucap;
-    if (arith) r1_update_kernel<true><<<(unsigned)ugrid, R1T, R1_DYN_SMEM, st>>>(dev + n_wide, n - n_wide, units, qmap_m, qmap_v, c);
-    else r1_update_kernel<false><<<(unsigned)ugrid, R1T, R1_DYN_SMEM, st>>>(dev + n_wide, n - n_wide, units, qmap_m, qmap_v, c);
+    if (arith) r1_update_kernel<true><<<(unsigned)ugrid, R1T, R1_DYN_SMEM, st>>>(tab, qmap_m, qmap_v, c);
+    else r1_update_kernel<false><<<(unsigned)ugrid, R1T, R1_DYN_SMEM, st>>>(tab, qmap_m, qmap_v, c);
     LPMM_CUDA_TRY(cudaGetLastError());
+  }
+  return LPMM_B200_OK;
+}
+
+extern "C" int lpmm_b200_rank1_multi_step(const lpmm_b200_step_tensor* const* ts, int n, const float* qmap_m,
+                                          const float* qmap_v, double beta1, double beta2, double lr,
+                                          double weight_decay, double eps, double step, void* table,
+                                          int64_t table_bytes, void* stream, int arith) {
+  (void)table;
+  (void)table_bytes;
+  if (n <= 0) return LPMM_B200_OK;
+  if (!ts || !qmap_m || !qmap_v) return LPMM_B200_ERR_NULL_POINTER;
+  for (int i = 0; i < n; ++i)
+    if (!lpmm_b200_rank1_multi_ok(ts[i])) return LPMM_B200_ERR_UNSUPPORTED;
+  const UConsts c = make_consts(beta1, beta2, lr, weight_decay, eps, step);
+  static_assert(R1_MAX <= R2_MAX, "a window of wide matrices must fit the second table");
+  for (int i = 0; i < n; i += R1_MAX) {
+    const int cnt = (n - i < R1_MAX) ? n - i : R1_MAX;
+    const int rc = r1_window(ts + i, cnt, qmap_m, qmap_v, c, (cudaStream_t)stream, arith);
+    if (rc != LPMM_B200_OK) return rc;
   }
   return LPMM_B200_OK;
 }

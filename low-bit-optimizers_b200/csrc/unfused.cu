@@ -1674,9 +1674,8 @@ static int step_many(const lpmm_b200_step_tensor* const* tensors, int n, const f
            (t->m_group == 0 || t->m_group == 128) && (t->v_group == 0 || t->v_group == 128) && t->m_max1 &&
            t->v_max1 && qmap_m && qmap_v;
   };
-  // rank-1 matrices that share a step count are stepped together (rank1_multi.cu) when the caller's
-  // scratch has room for their descriptor table (taken from its end)
-  // (not while `stream` is being captured: the table is uploaded from pageable host memory)
+  // rank-1 matrices that share a step count are stepped together (rank1_multi.cu; their descriptors travel in
+  // the launch parameters, so this also holds while `stream` is being captured)
   bool capturing = true;
   {
     cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
@@ -1688,22 +1687,14 @@ static int step_many(const lpmm_b200_step_tensor* const* tensors, int n, const f
   double r1_step = 0.0;
   for (int i = 0; i < n; ++i) {
     if (!tensors[i]) return LPMM_B200_ERR_NULL_POINTER;
-    if (!capturing && qmap_m && qmap_v && lpmm_b200_rank1_multi_ok(tensors[i]) &&
-        (r1.empty() || steps[i] == r1_step)) {
+    if (qmap_m && qmap_v && lpmm_b200_rank1_multi_ok(tensors[i]) && (r1.empty() || steps[i] == r1_step)) {
       r1_step = steps[i];
       r1.push_back(tensors[i]);
     }
   }
   void* r1_table = nullptr;
-  int64_t r1_bytes = 0;
-  if (r1.size() >= 2 && scratch) {
-    r1_bytes = (lpmm_b200_rank1_multi_table_bytes((int)r1.size()) + 255) & ~(int64_t)255;
-    if (r1_bytes <= scratch_bytes) {
-      scratch_bytes = (scratch_bytes - r1_bytes) & ~(int64_t)255;
-      r1_table = static_cast<char*>(scratch) + scratch_bytes;
-    }
-  }
-  if (!r1_table) r1.clear();
+  const int64_t r1_bytes = 0;
+  if (r1.size() < 2) r1.clear();
   auto in_r1 = [&](const lpmm_b200_step_tensor* t, double s) {
     return !r1.empty() && s == r1_step && lpmm_b200_rank1_multi_ok(t);
   };
@@ -1713,7 +1704,7 @@ static int step_many(const lpmm_b200_step_tensor* const* tensors, int n, const f
   fm.clear();
   double fm_step = 0.0;
   for (int i = 0; i < n; ++i) {
-    if (!arith && !capturing && lpmm_b200_factored_multi_ok(tensors[i]) && (fm.empty() || steps[i] == fm_step) &&
+    if (!arith && lpmm_b200_factored_multi_ok(tensors[i]) && (fm.empty() || steps[i] == fm_step) &&
         (tensors[i]->m_mode == LPMM_B200_STATE_FP32 || qmap_m)) {
       fm_step = steps[i];
       fm.push_back(tensors[i]);

@@ -5,16 +5,20 @@ LLaMA-7B-shaped fp32 list and the same buffers.  With ``--nonfused`` instead: th
 lpmm/optim/adamw.py:332-436) as its sequence of torch CUDA operations per parameter (``oracle/torch_ref.py``)
 with the reference's compiled ``pack_nonlinear``, against ``lpmm.optim.AdamW`` of this package, on the
 GPT-2-medium-shaped list, for the group and the rank-1 second-moment configuration.
-Not a test (pytest does not collect it); run it as
+As a test (``pytest -m gpu``) it runs both comparisons on reduced lists and requires this library's step to be the
+faster one; run as a script it times the full lists:
 
-    python tests/time_reference_kernels_gpu.py [--layers 32] [--iters 10] [--nonfused]
+    python tests/test_gpu_reference_kernels_timing.py [--layers 32] [--iters 10] [--nonfused]
 
 The figures in ``profiles/reference_kernels_vs_one_launch_step_7b_list.md`` come from it."""
 import argparse
 import os
 import sys
 
+import pytest
 import torch
+
+pytestmark = pytest.mark.gpu
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path[:0] = [ROOT, os.path.join(ROOT, "low-bit-optimizers_b200"), os.path.join(ROOT, "tests")]
@@ -31,7 +35,8 @@ def gpt2_medium_shapes():
     return shapes
 
 
-def nonfused(iters):
+def nonfused(iters, shapes=None):
+    """Returns {v scale: (ms of the reference's operation sequence, ms of this package)}."""
     import lpmm
     from lpmm.config import CONFIG_DIR
     from oracle import torch_ref as T
@@ -39,7 +44,8 @@ def nonfused(iters):
     if quant is None:
         raise SystemExit("oracle/_ref/quantization is not built")
     dev = torch.device("cuda:0")
-    shapes = gpt2_medium_shapes()
+    shapes = shapes or gpt2_medium_shapes()
+    out = {}
     buf = torch.zeros(256, device=dev)
     buf[64:80] = lpmm.functional.create_general_qmap("nonlinear", 4, True).to(dev)
     buf[128:144] = lpmm.functional.create_general_qmap("power-1", 4, False).to(dev)
@@ -76,26 +82,20 @@ def nonfused(iters):
             torch.cuda.synchronize()
             ms = e0.elapsed_time(e1) / iters
             print(f"{name}: {len(ps)} tensors, {total} params, {ms:.3f} ms/step, {total / ms / 1e6:.1f} Gparam/s", flush=True)
+            out.setdefault(v_scale, []).append(ms)
         del opt, params, states, ps, gs
         torch.cuda.empty_cache()
+    return out
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--layers", type=int, default=32)
-    ap.add_argument("--iters", type=int, default=10)
-    ap.add_argument("--nonfused", action="store_true")
-    a = ap.parse_args()
-    if a.nonfused:
-        return nonfused(a.iters)
+def fused(layers, iters):
+    """Returns (ms of the reference's kernels launched per tensor, ms of this library's one launch)."""
     import lpmm
     from lpmm import _kernels
     ref = load_reference_extension("fused_adamw")
-    if ref is None:
-        raise SystemExit("oracle/_ref/fused_adamw is not built (python -c 'import __graft_entry__ as g; g.build()')")
     dev = torch.device("cuda:0")
     torch.manual_seed(0)
-    shapes = llama7b_shapes(layers=a.layers)
+    shapes = llama7b_shapes(layers=layers)
     qm = lpmm.functional.create_general_qmap("nonlinear", 4, True).to(dev)
     qv = lpmm.functional.create_general_qmap("power-1", 4, False).to(dev)
     # the maps sit in the middle of a buffer: the reference's search may read one entry before a map
@@ -131,19 +131,53 @@ def main():
         _kernels.adamw4bit_multi_tensor(tl, qm, qv, h["beta1"], h["beta2"], h["lr"], h["weight_decay"], h["eps"],
                                         float(step))
 
+    res = []
     for name, fn in (("reference kernels, one launch per tensor", step_reference), ("this library, one launch", step_own)):
         for s in range(1, 4):
             fn(s)
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for s in range(4, 4 + a.iters):
+        for s in range(4, 4 + iters):
             fn(s)
         e1.record()
         torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1) / a.iters
+        ms = e0.elapsed_time(e1) / iters
+        res.append(ms)
         print(f"{name}: {len(entries)} tensors, {total} params, {ms:.3f} ms/step, {total / ms / 1e6:.1f} Gparam/s, "
               f"{total * 14.125 / ms / 1e6:.0f} GB/s of 14.125 B/param", flush=True)
+    return tuple(res)
+
+
+def test_one_launch_step_is_faster_than_the_reference_kernels_per_tensor():
+    """Two transformer layers plus embedding and head (667 M parameters), 3 timed steps each."""
+    if load_reference_extension("fused_adamw") is None:
+        pytest.skip("oracle/_ref was not built")
+    ms_ref, ms_own = fused(2, 3)
+    assert ms_own < ms_ref
+
+
+def test_nonfused_step_is_faster_than_the_reference_operation_sequence():
+    """Six matrices and vectors of the GPT-2-medium-shaped list, group and rank-1 second moments."""
+    if load_reference_extension("quantization") is None:
+        pytest.skip("oracle/_ref was not built")
+    shapes = [(1024, 3072), (1024, 1024), (1024, 4096), (4096, 1024), (1024,), (1024,)]
+    for v_scale, (ms_ref, ms_own) in nonfused(3, shapes).items():
+        assert ms_own < ms_ref, v_scale
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--layers", type=int, default=32)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--nonfused", action="store_true")
+    a = ap.parse_args()
+    if a.nonfused:
+        return nonfused(a.iters)
+    ref = load_reference_extension("fused_adamw")
+    if ref is None:
+        raise SystemExit("oracle/_ref/fused_adamw is not built (python -c 'import __graft_entry__ as g; g.build()')")
+    fused(a.layers, a.iters)
 
 
 if __name__ == "__main__":

@@ -174,3 +174,51 @@ def test_entry_point_equals_per_tensor_calls_on_unaligned_views_and_ranges(qmaps
                 assert bits_equal(a[4], other[4]) and bits_equal(a[5], other[5]), f"tensor {i}: scales vs {what}"
             else:
                 assert bits_equal(a[2], other[2]) and bits_equal(a[3], other[3]), f"tensor {i}: fp32 moments vs {what}"
+
+
+@pytest.mark.parametrize("kw", [dict(qconfig="default.yml"), dict(qconfig=None, factor_second_moment=True)],
+                         ids=["rank1", "factored"])
+def test_list_wide_steps_can_be_captured_into_a_cuda_graph(kw):
+    """The list-wide rank-1 and factored steps upload nothing (their descriptors travel in the launch parameters), so
+    a step captured into a CUDA graph and replayed once equals the same step launched directly, bit for bit, and
+    the captured step took the list-wide kernels (a handful of graph nodes, not a chain per tensor)."""
+    import os
+    import lpmm
+    from lpmm.config import CONFIG_DIR
+    shapes = [(1024, 768), (768, 3072), (130, 4104), (333, 1024), (1024,), (5000, 16), (512, 512), (256, 1280)]
+    kw = dict(kw, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01)
+    if isinstance(kw.get("qconfig"), str):
+        kw["qconfig"] = os.path.join(CONFIG_DIR, kw["qconfig"])
+    torch.manual_seed(51)
+    init = [torch.randn(s, device=device()) * 0.02 for s in shapes]
+    pa = [torch.nn.Parameter(x.clone()) for x in init]
+    pb = [torch.nn.Parameter(x.clone()) for x in init]
+    oa, ob = lpmm.optim.AdamW(pa, **kw), lpmm.optim.AdamW(pb, **kw)
+    for p in pa + pb:
+        p.grad = torch.zeros_like(p)
+    for s in range(1, 4):  # eager steps: states initialised, descriptors cached, scratch allocated
+        for i, (a, b) in enumerate(zip(pa, pb)):
+            g = student_t(shapes[i], 100003 * s + i)
+            a.grad.copy_(g)
+            b.grad.copy_(g)
+        oa.step()
+        ob.step()
+    for i, (a, b) in enumerate(zip(pa, pb)):
+        g = student_t(shapes[i], 100003 * 4 + i)
+        a.grad.copy_(g)
+        b.grad.copy_(g)
+    torch.cuda.synchronize()
+    oa.step()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        ob.step()
+    graph.replay()
+    torch.cuda.synchronize()
+    for i, (a, b) in enumerate(zip(pa, pb)):
+        assert bits_equal(a.detach(), b.detach()), f"tensor {i}: parameters"
+        sa, sb = oa.state[a], ob.state[b]
+        assert torch.equal(sa["exp_avg"].view(torch.uint8).view(-1), sb["exp_avg"].view(torch.uint8).view(-1)), f"tensor {i}"
+        if "exp_avg_sq" in sa:
+            assert torch.equal(sa["exp_avg_sq"].view(torch.uint8).view(-1), sb["exp_avg_sq"].view(torch.uint8).view(-1))
+        else:
+            assert bits_equal(sa["exp_avg_sq_row"], sb["exp_avg_sq_row"]) and bits_equal(sa["exp_avg_sq_col"], sb["exp_avg_sq_col"])
