@@ -441,8 +441,11 @@ def run_own(args):
     if world == 1:
         torch.manual_seed(0)
         params = [torch.nn.Parameter(torch.empty(s, device=dev).normal_(0, 0.02)) for s in shapes]
+        gflat = torch.empty(total, device=dev)  # the gradients are views of one buffer (the e2e copies are few and large)
+        off = 0
         for i, p in enumerate(params):
-            p.grad = torch.empty_like(p)
+            p.grad = gflat[off:off + p.numel()].view(p.shape)
+            off += p.numel()
             student_t_(p.grad, 100003 + i)
         opt = lpmm.optim.AdamW(params, fused=True, **HYPER)
 
@@ -566,18 +569,14 @@ def run_own(args):
             hi = min(lo + tmp.numel(), pool_n)
             pool[lo:hi].copy_(tmp[: hi - lo])
         del tmp
-        offs, cur = [], 0
-        for s in shapes:
-            n = numel(s)
-            if cur + n > pool_n:
-                cur = 0
-            offs.append(cur)
-            cur += n // 2
         result = torch.empty(1024, dtype=torch.float32, pin_memory=True)
 
         def e2e_step():
-            for p, off in zip(params, offs):
-                p.grad.copy_(pool[off:off + p.numel()].view(p.shape), non_blocking=True)
+            # the step's gradients arrive from pinned host memory: 4 * total bytes in copies of up to 2 GB (the pinned
+            # pool is reused as the source of every chunk)
+            for lo in range(0, total, pool_n):
+                hi = min(lo + pool_n, total)
+                gflat[lo:hi].copy_(pool[: hi - lo], non_blocking=True)
             opt.step()
             result.copy_(params[-1].detach().view(-1)[:1024], non_blocking=True)
 

@@ -106,7 +106,7 @@ __device__ __forceinline__ float r1_row_pass(float qv_l, const float* col_old, f
 }
 
 template <bool A>
-__global__ void __launch_bounds__(R1T) r1_stats_kernel(const __grid_constant__ R1Table tab,
+__global__ void __launch_bounds__(R1T, 3) r1_stats_kernel(const __grid_constant__ R1Table tab,
                                                         const float* __restrict__ qmap_v, const UConsts cin) {
   const R1Desc* d = tab.t;
   const int n = tab.n;
@@ -135,6 +135,7 @@ __global__ void __launch_bounds__(R1T) r1_stats_kernel(const __grid_constant__ R
     const long long r_begin = tile_y * t.rows_per_tile;
     const long long r_end = (r_begin + t.rows_per_tile < t.R) ? r_begin + t.rows_per_tile : t.R;
     const int seg = tx_count < 32 ? tx_count : 32;  // lanes that share a row inside a warp
+    const unsigned segmask = (seg == 32 ? 0xffffffffu : ((1u << seg) - 1u)) << (threadIdx.x & 31 & ~(seg - 1));
     // all lanes of a warp make the same number of trips (the shuffles below need the whole warp); the loads of the
     // next pair of rows are issued before the arithmetic of the current pair
     const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -183,10 +184,10 @@ __global__ void __launch_bounds__(R1T) r1_stats_kernel(const __grid_constant__ R
       // rows that do not exist were loaded as zeros: their second moments are zero and change no maximum
       float ma = r1_row_pass<A>(qv_l, col_old, col_max, kb2, komb2, ga0, ga1, ca, oa);
       float mc = r1_row_pass<A>(qv_l, col_old, col_max, kb2, komb2, gc0, gc1, cc, oc);
-      for (int o = seg >> 1; o; o >>= 1) {
-        ma = fmaxf(ma, __shfl_xor_sync(0xffffffffu, ma, o));
-        mc = fmaxf(mc, __shfl_xor_sync(0xffffffffu, mc, o));
-      }
+      // maximum over the lanes that share the row: the values are non-negative floats, whose order is that of their
+      // bit patterns, so one integer warp reduction per row replaces a shuffle tree
+      ma = __uint_as_float(__reduce_max_sync(segmask, __float_as_uint(ma)));
+      mc = __uint_as_float(__reduce_max_sync(segmask, __float_as_uint(mc)));
       if ((threadIdx.x & (seg - 1)) == 0) {
         if (ra < r_end) atomic_max_nonneg(t.new_r + ra, ma);
         if (rc < r_end) atomic_max_nonneg(t.new_r + rc, mc);
