@@ -496,6 +496,14 @@ def adamw4bit_unfused_step(p, g, state, m_quant, v_quant, md_m, md_v, spare, *, 
         if first_v:
             v.data = torch.empty(packed_len(p.numel(), md_v["b"]), dtype=torch.int8, device=p.device)
             oh_v["max_dims"] = _axis_vectors(tuple(p.shape), p.device)
+        elif v.dtype != torch.int8:
+            # an initialised fp32 second moment met by a step that wants it packed (see _ensure_group_state)
+            if v.numel() != p.numel() or not v.is_floating_point():
+                raise RuntimeError("exp_avg_sq: an initialised state of another size cannot become the quantized state")
+            codes, vecs = quant_rank1(v.detach().to(torch.float32).contiguous().view(p.shape),
+                                      state["exp_avg_sq_qstate"]["qmap"], md_v["b"])
+            v.data = codes
+            oh_v["max_dims"] = vecs
         if "max_dims" not in spare or spare["max_dims"][0].device != p.device:
             spare["max_dims"] = _axis_vectors(tuple(p.shape), p.device)
         old, new = oh_v["max_dims"], spare["max_dims"]

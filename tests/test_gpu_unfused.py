@@ -284,3 +284,53 @@ def test_state_dict_round_trip_keeps_codes_and_continues(qmaps):
     for a, b in zip(pa, pb):
         assert bits_equal(a.detach(), b.detach())
         assert torch.equal(oa.state[a]["exp_avg"], ob.state[b]["exp_avg"])
+
+
+@pytest.mark.parametrize("cfg,v_scale", [(None, "group"), ("default.yml", "rank1")])
+def test_fp32_moment_met_by_a_quantizing_step_is_quantised_in_place(qmaps, cfg, v_scale):
+    """A checkpoint saved with a tensor's moments in fp32 (its quantization was overridden off) and loaded into an
+    optimizer that quantizes that tensor: the initialised fp32 states are quantised as they are on the first step --
+    never replaced by fresh storage that would then be read as the previous moment.  Oracle: the fp32 moments
+    quantised with the restated reference quantizer, then one more restated step."""
+    import lpmm
+    from oracle import torch_ref as T
+    shape = (96, 64)  # 6144 elements
+    kw = dict(lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01)
+    qm, qv = _dev(qmaps["m"]), _dev(qmaps["v"])
+    torch.manual_seed(12)
+    p0 = torch.randn(shape, device=device()) * 0.02
+    p = torch.nn.Parameter(p0.clone())
+    opt = _make_opt("AdamW", [p], dict(kw, qconfig=cfg))
+    holder = torch.nn.Module()
+    holder.register_parameter("w", p)
+    opt.override_quantize_enable(holder, "w", False)
+    op, st = p0.clone(), {}
+    common = dict(beta1=0.9, beta2=0.999, lr=1e-3, weight_decay=0.01, eps=1e-8)
+    for s in (1, 2):
+        g = student_t(shape, 700 + s)
+        p.grad = g.clone()
+        opt.step()
+        T.adamw_step(op, g, st, qm, qv, m_quant=False, v_quant=False, v_scale_type=v_scale, step=float(s), **common)
+    assert opt.state[p]["exp_avg"].dtype == torch.float32 and bits_equal(opt.state[p]["exp_avg"], st["m"])
+    p2 = torch.nn.Parameter(p.detach().clone())
+    opt2 = _make_opt("AdamW", [p2], dict(kw, qconfig=cfg))   # no override: both moments are to be 4-bit
+    opt2.load_state_dict(opt.state_dict())
+    assert opt2.state[p2]["exp_avg"].dtype == torch.float32
+    st["m"], st["m_md"] = T.vectorwise_quant(st["m"], qm, "group")
+    st["v"], st["v_md"] = T.vectorwise_quant(st["v"], qv, v_scale)
+    g = student_t(shape, 703)
+    p2.grad = g.clone()
+    opt2.step()
+    T.adamw_step(op, g, st, qm, qv, m_quant=True, v_quant=True, v_scale_type=v_scale, step=3.0, **common)
+    torch.cuda.synchronize()
+    s2 = opt2.state[p2]
+    assert s2["exp_avg"].dtype == torch.int8 and s2["exp_avg_sq"].dtype == torch.int8
+    assert bits_equal(p2.detach(), op)
+    _check_group_state(s2["exp_avg"], s2["exp_avg_qstate"]["overhead"]["max1"], st["m"], st["m_md"], p2.numel(), "exp_avg")
+    if v_scale == "group":
+        _check_group_state(s2["exp_avg_sq"], s2["exp_avg_sq_qstate"]["overhead"]["max1"], st["v"], st["v_md"], p2.numel(),
+                           "exp_avg_sq")
+    else:
+        assert torch.equal(s2["exp_avg_sq"].view(torch.uint8), st["v"].view(torch.uint8))
+        for d in range(2):
+            assert bits_equal(s2["exp_avg_sq_qstate"]["overhead"]["max_dims"][d], st["v_md"]["max_dims"][d])

@@ -94,6 +94,19 @@ def _worker(rank, world, port, golden_dir, out_dir):
         opt.set_grad_shard_from_full(_grads(step))
         opt.step()
     np.save(os.path.join(out_dir, f"flat_{rank}.npy"), opt.flat.numpy())
+    # ordering of the peer-store mode: the ranks meet before the launch (nobody overwrites parameters a slower rank
+    # still reads) and after it (nobody reads parameters a peer still writes).  The mode itself needs peer-mapped GPU
+    # memory; its host logic runs here with the oracle as the launch.
+    calls = []
+    real_update, real_all_reduce = opt._update, dist.all_reduce
+    opt._update = lambda lo, hi, **kw: (calls.append("update"), real_update(lo, hi, **kw))[1]
+    dist.all_reduce = lambda t, *a, **k: (calls.append("all_reduce"), real_all_reduce(t, *a, **k))[1]
+    opt.gather, opt._flag = "fused", torch.zeros(1)
+    opt.set_grad_shard_from_full(_grads(4))
+    opt.step()
+    dist.all_reduce = real_all_reduce
+    with open(os.path.join(out_dir, f"order_{rank}.txt"), "w") as fh:
+        fh.write(",".join(calls))
     dist.destroy_process_group()
 
 
@@ -108,6 +121,8 @@ def test_two_gloo_ranks_equal_the_unsharded_step(golden_dir, tmp_path):
         port = s.getsockname()[1]
     mp.spawn(_worker, args=(2, port, golden_dir, str(tmp_path)), nprocs=2, join=True)
     flats = [np.load(tmp_path / f"flat_{r}.npy") for r in range(2)]
+    for r in range(2):
+        assert (tmp_path / f"order_{r}.txt").read_text() == "all_reduce,update,all_reduce", "barrier / launch / barrier"
     assert np.array_equal(flats[0].view(np.int32), flats[1].view(np.int32)), "ranks disagree after the all-gather"
     for i, p in enumerate(single.params):
         lo = single.gstart[i] * 128
