@@ -281,7 +281,11 @@ __device__ __forceinline__ f2x4 ldg_f2x4(const float* ptr) {
   return r;
 }
 __device__ __forceinline__ void stg_f2x4(float* ptr, const f2x4& r) {
+#ifdef LPMM_ST_CS  // streaming (evict-first) store hint (experiment)
+    asm volatile("st.global.cs.v4.b64 [%4], {%0,%1,%2,%3};" ::"l"(r.v[0]), "l"(r.v[1]), "l"(r.v[2]), "l"(r.v[3]), "l"(ptr));
+#else
     asm volatile("st.global.v4.b64 [%4], {%0,%1,%2,%3};" ::"l"(r.v[0]), "l"(r.v[1]), "l"(r.v[2]), "l"(r.v[3]), "l"(ptr));
+#endif
 }
 
 }  // namespace lpmm_b200

@@ -8,9 +8,19 @@ namespace lpmm_b200 {
 
 constexpr int MAX_TENSORS = 400;  // descriptors per launch (28.9 KB of the 32 KB parameter space)
 // One 1024-thread CTA per SM: measured faster than 2 x 512 or 3 x 256 (6.2 vs 5.9 vs 5.3 TB/s in a burst).
-constexpr unsigned PF_DIST = 1;  // the L2 prefetch runs this many of a half-warp's iterations ahead (2: same, 3: slower)
-constexpr int CTA_THREADS = 1024;
-constexpr int CTAS_PER_SM = 1;
+// Tuning knobs, overridable at compile time for experiments; the defaults are the measured best.
+#ifndef LPMM_PF_DIST
+#define LPMM_PF_DIST 1
+#endif
+#ifndef LPMM_CTA_THREADS
+#define LPMM_CTA_THREADS 1024
+#endif
+#ifndef LPMM_CTAS_PER_SM
+#define LPMM_CTAS_PER_SM 1
+#endif
+constexpr unsigned PF_DIST = LPMM_PF_DIST;  // the L2 prefetch runs this many of a half-warp's iterations ahead (0: none; 2: same, 3: slower)
+constexpr int CTA_THREADS = LPMM_CTA_THREADS;
+constexpr int CTAS_PER_SM = LPMM_CTAS_PER_SM;
 constexpr int HW_PER_CTA = CTA_THREADS / 16;
 
 struct TDesc {
@@ -43,10 +53,15 @@ struct PeerStores {
   long long off[7];
 };
 
+// Maximum of a non-negative value over the half-warp.
 __device__ __forceinline__ float hw_max(float x, unsigned mask) {
+#ifdef LPMM_HWMAX_REDUX  // one integer warp reduction on the bit patterns (experiment; measured no faster)
+  return __uint_as_float(__reduce_max_sync(mask, __float_as_uint(x)));
+#else
 #pragma unroll
   for (int o = 8; o; o >>= 1) x = fmaxf(x, __shfl_xor_sync(mask, x, o, 16));
   return x;
+#endif
 }
 
 __device__ __forceinline__ void prefetch_l2(const void* ptr) {
