@@ -639,7 +639,13 @@ def run_own(args):
                 extra["llama13b"] = {"error": repr(e)[:200]}
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        cpu = cpu_baseline_in_subprocess(2, 1)
+        try:
+            cpu = cpu_baseline_in_subprocess(2, 1)
+        except Exception as e:  # the child could not run the reference's Python: the C port, in this process
+            v, sec, threads, tot = time_cpu_oracle(2, 1, cpu_sample_shapes())
+            cpu = {"value": v, "unit": UNIT, "cores": threads, "kind": "port",
+                   "sample": f"one transformer layer of the list ({tot} params), C restatement of the reference kernel, OpenMP "
+                             f"(the reference's Python could not be timed: {repr(e)[:120]})"}
         cpu["sample"] += "; 2 timed steps after 1 warm-up"
     if rank == 0:
         out = {

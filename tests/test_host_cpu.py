@@ -212,3 +212,43 @@ def test_cpu_tensors_are_rejected_not_silently_computed():
     opt = lpmm.optim.SGD([w], lr=0.1, momentum=0.9)
     with pytest.raises(RuntimeError):
         opt.step()
+
+
+def test_flags_entry_points_validate_without_a_gpu():
+    """The ..._flags / ..._16bit_peers entry points refuse unknown flags, bad peer counts and unaligned offsets before
+    anything is launched."""
+    import ctypes
+    from lpmm import _native as N
+    t = (N.Tensor * 1)(N.Tensor(0x1000, 0x2000, 0x3000, 0x4000, 0x5000, 0x6000, 256, N.KIND_Q4, 0))
+    h = N.Hyper(0.9, 0.999, 1e-3, 0.01, 1e-8, 1.0)
+    qm = ctypes.c_void_p(0x7000)
+    assert N.lib.lpmm_b200_adamw4bit_multi_tensor_flags(t, 1, qm, qm, h, 0, -1, 4, None) == -3
+    assert N.lib.lpmm_b200_adamw4bit_multi_tensor_flags(t, 1, None, None, h, 0, -1, 1, None) == -1
+    assert N.lib.lpmm_b200_adamw4bit_multi_tensor_flags(t, 1, qm, qm, h, 0, 0, 1, None) == 0  # empty range: nothing to do
+    assert N.lib.lpmm_b200_adamw4bit_multi_tensor_flags(t, 1, qm, qm, h, 1, 5, 1, None) == -2
+    offs = (ctypes.c_int64 * 2)(64, 8)
+    assert N.lib.lpmm_b200_adamw4bit_multi_tensor_16bit_peers(t, 1, N.DTYPE_BF16, qm, qm, h, 0, -1, offs, 9, 0, None) == -2
+    assert N.lib.lpmm_b200_adamw4bit_multi_tensor_16bit_peers(t, 1, N.DTYPE_BF16, qm, qm, h, 0, -1, offs, 2, 0, None) == -2
+    assert N.lib.lpmm_b200_adamw4bit_multi_tensor_16bit_peers(t, 1, N.DTYPE_BF16, qm, qm, h, 0, -1, None, 2, 0, None) == -1
+    assert N.lib.lpmm_b200_adamw4bit_multi_tensor_16bit_peers(t, 1, 7, qm, qm, h, 0, -1, offs, 1, 0, None) == -3
+    assert N.lib.lpmm_b200_adamw4bit_multi_tensor_peers_flags(t, 1, qm, qm, h, 0, -1, offs, 2, 0, None) == -2  # 8 % 32 != 0
+
+
+def test_reference_arm_of_the_bench_prints_its_line(tmp_path):
+    """``bench.py --impl reference`` on the host cores: one JSON line with the keys of the contract; the reference's own
+    Python when ``oracle/_ref/lpmm_py`` (or a checkout) is there, else the C port."""
+    import json
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    res = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "0",
+                          "--no-port"], capture_output=True, text=True, timeout=600, cwd=str(tmp_path))
+    assert res.returncode == 0, res.stderr[-1000:]
+    line = [ln for ln in res.stdout.splitlines() if ln.startswith("{")][-1]
+    d = json.loads(line)
+    assert d["impl"] == "reference" and d["metric"] == "optimizer_params_updated_per_second" and d["unit"] == "params/s"
+    assert d["cpu_baseline"]["kind"] in ("reference-python", "port") and d["cpu_baseline"]["cores"] >= 1
+    assert d["value"] > 0 and d["e2e"]["value"] == d["value"] and d["e2e"]["h2d_bytes_per_step"] == 0
+    from oracle import build_ref
+    if build_ref.have_python() or build_ref.reference_root() is not None:
+        assert d["cpu_baseline"]["kind"] == "reference-python"
