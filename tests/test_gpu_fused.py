@@ -348,3 +348,51 @@ def test_full_7b_list_one_launch_equals_per_tensor_launches(qmaps):
         for j in (0, 2, 3, 4, 5):
             if ea[j] is not None:
                 assert checksum(ea[j]) == checksum(eb[j]), f"tensor {i}, field {j}"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_list_longer_than_one_descriptor_window_equals_per_tensor_steps(qmaps, dtype):
+    """450 tensors (4-bit, fp32-state, ragged) in one call: more than one launch's descriptor table holds (400), so the
+    list is walked in two windows; a group range that crosses the window boundary; both element types.  Against the
+    same tensors stepped one call each."""
+    from lpmm import _kernels as K
+    N = _lib()
+    qm, qv, _ = device_qmaps(qmaps)
+    shapes = [((41, 128) if i % 4 == 0 else (5000,) if i % 4 == 1 else (3000,) if i % 4 == 2 else (128 * 33 + 5,)) for i in range(450)]
+
+    def build():
+        torch.manual_seed(17)
+        out = []
+        for s in shapes:
+            n = int(np.prod(s))
+            p = (torch.randn(s, device=device()) * 0.02).to(dtype)
+            if n > 4096:
+                st = fused_state(n)
+                out.append([p, None, st[0], st[1], st[2], st[3]])
+            else:
+                out.append([p, None, torch.zeros(s, device=device()), torch.zeros(s, device=device()), None, None])
+        return out
+
+    a, b, c = build(), build(), build()
+    for s in range(1, 4):
+        grads = [student_t(sh, 700 + 13 * s + i).to(dtype) for i, sh in enumerate(shapes)]
+        for lst in (a, b, c):
+            for e, g in zip(lst, grads):
+                e[1] = g
+        K.adamw4bit_multi_tensor(K.TensorList([tuple(e) for e in a]), qm, qv, HYPER["beta1"], HYPER["beta2"], HYPER["lr"],
+                                 HYPER["weight_decay"], HYPER["eps"], float(s), dtype=dtype)
+        for e in b:  # one call per tensor
+            K.adamw4bit_multi_tensor(K.TensorList([tuple(e)]), qm, qv, HYPER["beta1"], HYPER["beta2"], HYPER["lr"],
+                                     HYPER["weight_decay"], HYPER["eps"], float(s), dtype=dtype)
+        tl = K.TensorList([tuple(e) for e in c])
+        cut = tl.total_groups * 7 // 8 + 3  # inside the second window
+        for lo, hi in ((0, cut), (cut, tl.total_groups)):
+            K.adamw4bit_multi_tensor(tl, qm, qv, HYPER["beta1"], HYPER["beta2"], HYPER["lr"], HYPER["weight_decay"],
+                                     HYPER["eps"], float(s), lo, hi, dtype=dtype)
+    torch.cuda.synchronize()
+    for i, (ea, eb, ec) in enumerate(zip(a, b, c)):
+        for j in (0, 2, 3, 4, 5):
+            if ea[j] is None:
+                continue
+            x, y, z = (t[j].contiguous().view(-1).view(torch.uint8) for t in (ea, eb, ec))
+            assert torch.equal(x, y) and torch.equal(x, z), f"tensor {i}, field {j}"

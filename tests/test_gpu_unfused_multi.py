@@ -222,3 +222,19 @@ def test_list_wide_steps_can_be_captured_into_a_cuda_graph(kw):
             assert torch.equal(sa["exp_avg_sq"].view(torch.uint8).view(-1), sb["exp_avg_sq"].view(torch.uint8).view(-1))
         else:
             assert bits_equal(sa["exp_avg_sq_row"], sb["exp_avg_sq_row"]) and bits_equal(sa["exp_avg_sq_col"], sb["exp_avg_sq_col"])
+
+
+@pytest.mark.parametrize("kw,v_scale,factored", [(dict(qconfig="default.yml"), "rank1", False),
+                                                 (dict(qconfig=None, factor_second_moment=True), "group", True)],
+                         ids=["rank1", "factored"])
+def test_lists_longer_than_one_descriptor_window(qmaps, kw, v_scale, factored):
+    """300 matrices in one parameter group: more than the launch parameters hold descriptors for (268 rank-1 / 224
+    factored), so the list is stepped in two windows; wide rows (multiples of 128) and narrow ones mixed, so that
+    both update kernels run in both windows."""
+    shapes = [((40, 128) if i % 3 else (136, 40)) for i in range(300)]
+    kw = dict(kw, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01)
+    torch.manual_seed(61)
+    p0s = [torch.randn(s, device=device()) * 0.02 for s in shapes]
+    opt, params, o_states, o_params = _run_pair_adamw(
+        shapes, p0s, lambda s: [student_t(sh, s * 100003 + i) for i, sh in enumerate(shapes)], 4, kw, qmaps, v_scale)
+    _check_adamw(opt, params, o_states, o_params, v_scale, factored=factored)
