@@ -542,8 +542,7 @@ static int f_window(const lpmm_b200_step_tensor* const* ts, int n, const float* 
     d.R = (int)t->shape[0];
     d.C = (int)t->shape[1];
     d.m_quant = t->m_mode == LPMM_B200_STATE_GROUP4;
-    int shift = 0;
-    while (shift < 8 && (8 << shift) < d.C) ++shift;
+    const int shift = tile_shift(d.C);
     d.tx_shift = shift;
     const int tile_cols = 8 << shift;
     d.tiles_x = (d.C + tile_cols - 1) / tile_cols;

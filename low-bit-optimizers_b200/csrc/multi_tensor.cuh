@@ -70,6 +70,27 @@ __device__ __forceinline__ void prefetch_l2(const void* ptr) {
 
 static inline int64_t groups_of(int64_t numel) { return (numel + 127) / 128; }
 
+// Column-threads of a statistics / sums tile of the list-wide rank-1 and factored passes: a tile is 8 << shift
+// columns wide (each of 2^shift column-threads owns 8 columns).  A row shorter than 2048 columns takes the power
+// of two that covers it; a longer one the width among 2048, 1024, 512, 256 that leaves the fewest idle columns in
+// its last tile (3072 -> 1024, 11008 -> 256), the wider one on a tie.
+static inline int tile_shift(long long C) {
+  int shift = 0;
+  while (shift < 8 && (8LL << shift) < C) ++shift;
+  if ((8LL << shift) >= C) return shift;
+  int best = 8;
+  long long best_waste = -1;
+  for (int sh = 8; sh >= 5; --sh) {
+    const long long w = 8LL << sh;
+    const long long waste = (C + w - 1) / w * w - C;
+    if (best_waste < 0 || waste < best_waste) {
+      best = sh;
+      best_waste = waste;
+    }
+  }
+  return best;
+}
+
 // Host side of every multi-tensor launch.  A list may hold more tensors than a table: it is walked in
 // windows of at most MAX_TENSORS non-empty tensors, one launch per window over the part of the
 // caller's group range [gbeg, gend) that falls inside it.

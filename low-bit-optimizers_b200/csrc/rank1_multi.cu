@@ -659,8 +659,7 @@ static int r1_window(const lpmm_b200_step_tensor* const* ts, int n, const float*
     d.C = (int)t->shape[1];
     d.ustart = units;
     d.tstart = tiles;
-    int shift = 0;
-    while (shift < 8 && (8 << shift) < d.C) ++shift;  // column-threads: the power of two covering C / 8, at most 256
+    const int shift = tile_shift(d.C);
     d.tx_shift = shift;
     d.pad_ = 0;
     const int tile_cols = 8 << shift;
