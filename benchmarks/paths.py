@@ -67,6 +67,12 @@ def cases():
          dict(adamw, fused=True, param_dtype=torch.bfloat16)),
         ("gpt2-medium adamw fused bf16 parameters, tolerance mode", "AdamW", gpt2_medium_shapes(),
          dict(adamw, fused=True, exact_params=False, param_dtype=torch.bfloat16)),
+        ("gpt2-medium adamw factored, tolerance mode", "AdamW", gpt2_medium_shapes(),
+         dict(adamw, factor_second_moment=True, exact_params=False)),
+        ("gpt2-medium adamw rank-1 (default.yml), tolerance mode", "AdamW", gpt2_medium_shapes(),
+         dict(adamw, qconfig=cfg("default.yml"), exact_params=False)),
+        ("gpt2-medium adamw group (qconfig=None), tolerance mode", "AdamW", gpt2_medium_shapes(),
+         dict(adamw, qconfig=None, exact_params=False)),
         ("gpt2-medium sgd", "SGD", gpt2_medium_shapes(), dict(sgd)),
         ("ragged adamw rank-1 (default.yml)", "AdamW", RAGGED, dict(adamw, qconfig=cfg("default.yml"))),
     ]
@@ -88,6 +94,14 @@ def big_cases():
         ("llama7b adamw fused rank-1 (default.yml, fused_rank1)", "AdamW", llama7b_shapes(),
          dict(adamw, qconfig=cfg("default.yml"), fused=True, fused_rank1=True)),
         ("llama7b adamw factored", "AdamW", llama7b_shapes(), dict(adamw, factor_second_moment=True)),
+        ("llama7b adamw group (qconfig=None), tolerance mode", "AdamW", llama7b_shapes(),
+         dict(adamw, qconfig=None, exact_params=False)),
+        ("llama7b adamw rank-1 (default.yml), tolerance mode", "AdamW", llama7b_shapes(),
+         dict(adamw, qconfig=cfg("default.yml"), exact_params=False)),
+        ("llama7b adamw fused rank-1 (default.yml, fused_rank1), tolerance mode", "AdamW", llama7b_shapes(),
+         dict(adamw, qconfig=cfg("default.yml"), fused=True, fused_rank1=True, exact_params=False)),
+        ("llama7b adamw factored, tolerance mode", "AdamW", llama7b_shapes(),
+         dict(adamw, factor_second_moment=True, exact_params=False)),
         ("llama7b sgd", "SGD", llama7b_shapes(), dict(lr=1e-2, momentum=0.9, weight_decay=1e-4)),
     ]
 

@@ -362,6 +362,15 @@ int lpmm_b200_adamw4bit_unfused_step_many(const lpmm_b200_step_tensor* const* te
                                           const float* qmap_v, double beta1, double beta2, double lr,
                                           double weight_decay, double eps, const double* steps, void* scratch,
                                           int64_t scratch_bytes, void* stream);
+/* The same with `flags` (0, or LPMM_B200_FLAG_PARAMS_WITHIN_TOLERANCE).  With the flag, the list-wide kernels (the
+ * shared launch of the plain tensors, and the update kernels of the rank-1 and factored matrices whose rows are
+ * multiples of 128 elements) compute the new parameter with the GPU's approximate square root and reciprocal;
+ * moments, maxima, row / column statistics and codes are unchanged, tensors stepped on their own stay exact.  Any
+ * other bit: LPMM_B200_ERR_BAD_KIND.  No counterpart in the reference. */
+int lpmm_b200_adamw4bit_unfused_step_many_flags(const lpmm_b200_step_tensor* const* tensors, int n,
+                                                const float* qmap_m, const float* qmap_v, double beta1, double beta2,
+                                                double lr, double weight_decay, double eps, const double* steps,
+                                                void* scratch, int64_t scratch_bytes, void* stream, uint32_t flags);
 
 /* The fused step on the non-fused state layout: the arithmetic of the reference's fused kernel
  * (lpmm/cpp_extension/fused_adamw_kernel.cu:103-128: float hyper-parameters, bias corrections by the
@@ -381,6 +390,14 @@ int lpmm_b200_adamw4bit_fused_arith_step_many(const lpmm_b200_step_tensor* const
                                               const float* qmap_v, double beta1, double beta2, double lr,
                                               double weight_decay, double eps, const double* steps, void* scratch,
                                               int64_t scratch_bytes, void* stream);
+/* The same with `flags`, as lpmm_b200_adamw4bit_unfused_step_many_flags (the rank-1 update kernel of matrices whose
+ * rows are multiples of 128 elements takes the tolerance mode; learning rate in [2^-60, 2^30] as for the fused step,
+ * otherwise the flag is ignored). */
+int lpmm_b200_adamw4bit_fused_arith_step_many_flags(const lpmm_b200_step_tensor* const* tensors, int n,
+                                                    const float* qmap_m, const float* qmap_v, double beta1,
+                                                    double beta2, double lr, double weight_decay, double eps,
+                                                    const double* steps, void* scratch, int64_t scratch_bytes,
+                                                    void* stream, uint32_t flags);
 
 /* One momentum-SGD step of one tensor with the arithmetic of _single_tensor_sgd4bit
  * (lpmm/optim/sgd.py:133-187).  buf_mode FP32 or GROUP4; first != 0: the buffer is created from

@@ -79,6 +79,8 @@ struct UmLane {
 
 // One full, aligned group with packed arithmetic (update_pair) and the short exact division for the
 // normalisation; selected only when the hyper-parameters are in the domain of the short sequences.
+// APX: the tolerance mode of the parameter update (unfused_math.cuh); moments, maxima and codes unchanged.
+template <bool APX>
 __device__ __forceinline__ void um_group_x2(const UmLane& t, unsigned gl, int l16, unsigned hmask, const UConsts2& k,
                                             const QMapSmem& Sm, const QMapSmem& Sv, const LutEnt* __restrict__ lut_m,
                                             const LutEnt* __restrict__ lut_v, bool vlin, float qm_l, float qv_l,
@@ -107,7 +109,7 @@ __device__ __forceinline__ void um_group_x2(const UmLane& t, unsigned gl, int l1
     const float m0b = __shfl_sync(hmask, pm, (int)(mc >> (8 * j + 4)), 16);
     const float v0a = __shfl_sync(hmask, pv, (int)(vc >> (8 * j)), 16);
     const float v0b = __shfl_sync(hmask, pv, (int)(vc >> (8 * j + 4)), 16);
-    update_pair(k, g.v[j], p.v[j], f2_pack(m0a, m0b), f2_pack(v0a, v0b), m[j], v[j], am, av);
+    update_pair<APX>(k, g.v[j], p.v[j], f2_pack(m0a, m0b), f2_pack(v0a, v0b), m[j], v[j], am, av);
   }
   stg_f2x4(pp, p);
   am = hw_max(am, hmask);
@@ -180,7 +182,8 @@ __device__ __forceinline__ void um_group_fp32(const TDesc& t, long long gl, int 
 }
 
 // A: the arithmetic of the reference's fused kernel (scalar paths only) instead of its torch operations.
-template <bool HAS_Q4, bool A>
+// APX (with A false): the tolerance-mode parameter update on full aligned 4-bit groups.
+template <bool HAS_Q4, bool A, bool APX>
 __global__ void __launch_bounds__(CTA_THREADS, CTAS_PER_SM)
 adamw_unfused_multi_kernel(const __grid_constant__ Table tab, const float* __restrict__ qmap_m,
                            const float* __restrict__ qmap_v, const UConsts cin, long long gbeg, long long gend) {
@@ -230,7 +233,7 @@ adamw_unfused_multi_kernel(const __grid_constant__ Table tab, const float* __res
           const unsigned lim = (unsigned)(fend - tstart);
           const unsigned st = (unsigned)stride;
           for (; gl < lim; gl += st)
-            um_group_x2(lp, gl, l16, hmask, k2, Sm, Sv, lut_m, lut_v, vlin, qm_l, qv_l,
+            um_group_x2<APX>(lp, gl, l16, hmask, k2, Sm, Sv, lut_m, lut_v, vlin, qm_l, qv_l,
                         (gl + PF_DIST * st < lim) ? PF_DIST * st : 0u);
           gi = tstart + gl;
         }
@@ -242,7 +245,7 @@ adamw_unfused_multi_kernel(const __grid_constant__ Table tab, const float* __res
   }
 }
 
-template <bool HAS_Q4, bool A>
+template <bool HAS_Q4, bool A, bool APX>
 static cudaError_t launch_um(const Table& tab, unsigned grid, const float* qm, const float* qv, const UConsts& c,
                              long long lo, long long hi, cudaStream_t st) {
   static bool attr_set[64] = {};
@@ -250,12 +253,12 @@ static cudaError_t launch_um(const Table& tab, unsigned grid, const float* qm, c
   cudaGetDevice(&dev);
   const size_t smem = HAS_Q4 ? UM_DYN_SMEM : 0;
   if (HAS_Q4 && dev >= 0 && dev < 64 && !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(adamw_unfused_multi_kernel<HAS_Q4, A>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(adamw_unfused_multi_kernel<HAS_Q4, A, APX>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)UM_DYN_SMEM);
     if (e != cudaSuccess) return e;
     attr_set[dev] = true;
   }
-  adamw_unfused_multi_kernel<HAS_Q4, A><<<grid, CTA_THREADS, smem, st>>>(tab, qm, qv, c, lo, hi);
+  adamw_unfused_multi_kernel<HAS_Q4, A, APX><<<grid, CTA_THREADS, smem, st>>>(tab, qm, qv, c, lo, hi);
   return cudaGetLastError();
 }
 
@@ -265,7 +268,7 @@ using namespace lpmm_b200;
 
 static int um_step(const lpmm_b200_tensor* ts, int n, const float* qmap_m, const float* qmap_v, double beta1, double beta2,
                    double lr, double weight_decay, double eps, double step, int64_t group_begin, int64_t group_end,
-                   void* stream, int arith) {
+                   void* stream, int arith, int apx) {
   bool any_q4 = false;
   int64_t total = 0;
   const int rc = check_tensor_list(ts, n, true, &any_q4, &total);
@@ -284,10 +287,11 @@ static int um_step(const lpmm_b200_tensor* ts, int n, const float* qmap_m, const
     const unsigned grid = multi_grid(w);
     cudaStream_t st = (cudaStream_t)stream;
     cudaError_t e;
-    if (arith) e = w.any_q4 ? launch_um<true, true>(tab, grid, qmap_m, qmap_v, c, w.lo, w.hi, st)
-                            : launch_um<false, true>(tab, grid, qmap_m, qmap_v, c, w.lo, w.hi, st);
-    else e = w.any_q4 ? launch_um<true, false>(tab, grid, qmap_m, qmap_v, c, w.lo, w.hi, st)
-                      : launch_um<false, false>(tab, grid, qmap_m, qmap_v, c, w.lo, w.hi, st);
+    if (arith) e = w.any_q4 ? launch_um<true, true, false>(tab, grid, qmap_m, qmap_v, c, w.lo, w.hi, st)
+                            : launch_um<false, true, false>(tab, grid, qmap_m, qmap_v, c, w.lo, w.hi, st);
+    else if (apx && w.any_q4) e = launch_um<true, false, true>(tab, grid, qmap_m, qmap_v, c, w.lo, w.hi, st);
+    else e = w.any_q4 ? launch_um<true, false, false>(tab, grid, qmap_m, qmap_v, c, w.lo, w.hi, st)
+                      : launch_um<false, false, false>(tab, grid, qmap_m, qmap_v, c, w.lo, w.hi, st);
     LPMM_CUDA_TRY(e);
   }
   return LPMM_B200_OK;
@@ -297,7 +301,15 @@ extern "C" int lpmm_b200_adamw4bit_unfused_multi_tensor(const lpmm_b200_tensor* 
                                                         const float* qmap_v, double beta1, double beta2, double lr,
                                                         double weight_decay, double eps, double step,
                                                         int64_t group_begin, int64_t group_end, void* stream) {
-  return um_step(ts, n, qmap_m, qmap_v, beta1, beta2, lr, weight_decay, eps, step, group_begin, group_end, stream, 0);
+  return um_step(ts, n, qmap_m, qmap_v, beta1, beta2, lr, weight_decay, eps, step, group_begin, group_end, stream, 0, 0);
+}
+
+// The same launch with the tolerance-mode parameter update (flags & LPMM_B200_FLAG_PARAMS_WITHIN_TOLERANCE); internal
+// to the library, reached through lpmm_b200_adamw4bit_unfused_step_many_flags.
+extern "C" int lpmm_b200_unfused_multi_tensor_apx(const lpmm_b200_tensor* ts, int n, const float* qmap_m,
+                                                  const float* qmap_v, double beta1, double beta2, double lr,
+                                                  double weight_decay, double eps, double step, void* stream) {
+  return um_step(ts, n, qmap_m, qmap_v, beta1, beta2, lr, weight_decay, eps, step, 0, -1, stream, 0, 1);
 }
 
 // The same launch with the fused kernel's arithmetic on these (padded) states; internal to the library,
@@ -305,5 +317,5 @@ extern "C" int lpmm_b200_adamw4bit_unfused_multi_tensor(const lpmm_b200_tensor* 
 extern "C" int lpmm_b200_fused_arith_multi_tensor(const lpmm_b200_tensor* ts, int n, const float* qmap_m,
                                                   const float* qmap_v, double beta1, double beta2, double lr,
                                                   double weight_decay, double eps, double step, void* stream) {
-  return um_step(ts, n, qmap_m, qmap_v, beta1, beta2, lr, weight_decay, eps, step, 0, -1, stream, 1);
+  return um_step(ts, n, qmap_m, qmap_v, beta1, beta2, lr, weight_decay, eps, step, 0, -1, stream, 1, 0);
 }

@@ -365,6 +365,7 @@ struct F2Table {
   F2Desc t[F2_MAX];
 };
 
+template <bool APX>  // APX: the tolerance mode of the parameter update (unfused_math.cuh)
 __device__ __forceinline__ void f2_group(const F2Desc& t, unsigned u, unsigned r, unsigned cb, int l16, unsigned hmask,
                                          const UConsts2& c2, const QMapSmem& Sm, const LutEnt* __restrict__ lut_m,
                                          bool lut_ok, float qm_l, unsigned pf) {
@@ -390,7 +391,8 @@ __device__ __forceinline__ void f2_group(const F2Desc& t, unsigned u, unsigned r
     const float m0a = __shfl_sync(hmask, pm, (int)(mc >> (8 * j)), 16);
     const float m0b = __shfl_sync(hmask, pm, (int)(mc >> (8 * j + 4)), 16);
     m[j] = lerp_pair(c2, g.v[j], f2_pack(m0a, m0b), am);
-    param_pair(c2, p.v[j], m[j], f2_mul(rf2, cv.v[j]));
+    if (APX) param_pair_apx(c2, p.v[j], m[j], f2_mul(rf2, cv.v[j]));
+    else param_pair(c2, p.v[j], m[j], f2_mul(rf2, cv.v[j]));
   }
   stg_f2x4(pp, p);
   am = hw_max(am, hmask);
@@ -420,6 +422,7 @@ __device__ __forceinline__ void f2_group(const F2Desc& t, unsigned u, unsigned r
   if (l16 == 0) t.msc[u] = am;
 }
 
+template <bool APX>
 __global__ void __launch_bounds__(F2T, 1) f_update2_kernel(const __grid_constant__ F2Table tab,
                                                            const float* __restrict__ qmap_m, const UConsts c) {
   extern __shared__ __align__(16) unsigned char dyn_smem[];
@@ -443,7 +446,7 @@ __global__ void __launch_bounds__(F2T, 1) f_update2_kernel(const __grid_constant
     unsigned r = u / gpr, cb = u - r * gpr;
     const unsigned sr = stride / gpr, sc = stride - sr * gpr;
     for (; u < lim; u += stride) {
-      f2_group(t, u, r, cb, l16, hmask, c2, Sm, lut_m, lut_ok, qm_l, (u + stride < lim) ? stride : 0u);
+      f2_group<APX>(t, u, r, cb, l16, hmask, c2, Sm, lut_m, lut_ok, qm_l, (u + stride < lim) ? stride : 0u);
       cb += sc;
       r += sr;
       if (cb >= gpr) {
@@ -497,7 +500,8 @@ static int f_occupancy(int* out) {
     if (per_sm < 1) per_sm = 1;
     if (cur >= 0 && cur < 64) sums_ctas[cur] = per_sm;
     LPMM_CUDA_TRY(cudaFuncSetAttribute(f_update_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)F_DYN_SMEM));
-    LPMM_CUDA_TRY(cudaFuncSetAttribute(f_update2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)F_DYN_SMEM));
+    LPMM_CUDA_TRY(cudaFuncSetAttribute(f_update2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)F_DYN_SMEM));
+    LPMM_CUDA_TRY(cudaFuncSetAttribute(f_update2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)F_DYN_SMEM));
   }
   *out = per_sm;
   return LPMM_B200_OK;
@@ -505,7 +509,7 @@ static int f_occupancy(int* out) {
 
 // One window of at most F_MAX tensors; fbase: this window's slice of the partial-sum scratch.
 static int f_window(const lpmm_b200_step_tensor* const* ts, int n, const float* qmap_m, bool any_q, const UConsts& c,
-                    float* fbase, cudaStream_t st) {
+                    float* fbase, cudaStream_t st, int apx) {
   static thread_local FTable tab;  // 32 KB; copied into the launch parameters by the runtime
   static thread_local F2Table tab2;
   static thread_local std::vector<int> order;
@@ -606,7 +610,8 @@ static int f_window(const lpmm_b200_step_tensor* const* ts, int n, const float* 
     tab2.total = g2;
     long long grid2 = (g2 + F2_HW - 1) / F2_HW;
     if (grid2 > num_sms()) grid2 = num_sms();
-    f_update2_kernel<<<(unsigned)grid2, F2T, F_DYN_SMEM, st>>>(tab2, qmap_m, c);
+    if (apx) f_update2_kernel<true><<<(unsigned)grid2, F2T, F_DYN_SMEM, st>>>(tab2, qmap_m, c);
+    else f_update2_kernel<false><<<(unsigned)grid2, F2T, F_DYN_SMEM, st>>>(tab2, qmap_m, c);
     LPMM_CUDA_TRY(cudaGetLastError());
   }
   if (n > n_wide) {
@@ -621,7 +626,7 @@ static int f_window(const lpmm_b200_step_tensor* const* ts, int n, const float* 
 
 extern "C" int lpmm_b200_factored_multi_step(const lpmm_b200_step_tensor* const* ts, int n, const float* qmap_m,
                                              double beta1, double beta2, double lr, double weight_decay, double eps,
-                                             double step, void* scratch, int64_t scratch_bytes, void* stream) {
+                                             double step, void* scratch, int64_t scratch_bytes, void* stream, int apx) {
   if (n <= 0) return LPMM_B200_OK;
   if (!ts || !scratch) return LPMM_B200_ERR_NULL_POINTER;
   bool any_q = false;
@@ -637,7 +642,7 @@ extern "C" int lpmm_b200_factored_multi_step(const lpmm_b200_step_tensor* const*
   char* base = static_cast<char*>(scratch);
   for (int i = 0; i < n; i += F_MAX) {
     const int cnt = (n - i < F_MAX) ? n - i : F_MAX;
-    const int rc = f_window(ts + i, cnt, qmap_m, any_q, c, reinterpret_cast<float*>(base), (cudaStream_t)stream);
+    const int rc = f_window(ts + i, cnt, qmap_m, any_q, c, reinterpret_cast<float*>(base), (cudaStream_t)stream, apx);
     if (rc != LPMM_B200_OK) return rc;
     base += lpmm_b200_factored_multi_scratch_bytes(ts + i, cnt);  // multiples of 256 bytes
   }

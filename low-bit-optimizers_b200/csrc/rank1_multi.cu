@@ -424,7 +424,8 @@ struct R2Table {
   R2Desc t[R2_MAX];
 };
 
-template <bool A>
+// APX: the tolerance mode of the parameter update (fused_x2.cuh / unfused_math.cuh).
+template <bool A, bool APX>
 __device__ __forceinline__ void r2_group(const R2Desc& t, unsigned u, unsigned r, unsigned cb, int l16, unsigned hmask,
                                          const UConsts2& c2, const Consts2& kf, const QMapSmem& Sm, const QMapSmem& Sv,
                                          const LutEnt* __restrict__ lut_m, bool lut_ok, bool vlin, float qm_l, float qv_l,
@@ -459,8 +460,8 @@ __device__ __forceinline__ void r2_group(const R2Desc& t, unsigned u, unsigned r
     const float qa = __shfl_sync(hmask, qv_l, (int)(vc >> (8 * j)), 16);
     const float qb = __shfl_sync(hmask, qv_l, (int)(vc >> (8 * j + 4)), 16);
     const f2 v0 = f2_mul(f2_pack(qa, qb), f2_pack(fminf(ro, oc[2 * j]), fminf(ro, oc[2 * j + 1])));
-    if (A) p.v[j] = fused_pair_x2(kf, g.v[j], p.v[j], f2_pack(m0a, m0b), v0, m[j], v[j], am, av);
-    else update_pair(c2, g.v[j], p.v[j], f2_pack(m0a, m0b), v0, m[j], v[j], am, av);
+    if (A) p.v[j] = fused_pair_x2<APX>(kf, g.v[j], p.v[j], f2_pack(m0a, m0b), v0, m[j], v[j], am, av);
+    else update_pair<APX>(c2, g.v[j], p.v[j], f2_pack(m0a, m0b), v0, m[j], v[j], am, av);
   }
   stg_f2x4(pp, p);
   // first moment: group maximum over the half-warp, codes of this lane
@@ -525,7 +526,7 @@ __device__ __forceinline__ void r2_group(const R2Desc& t, unsigned u, unsigned r
   if (l16 == 0) t.msc[u] = am;
 }
 
-template <bool A>
+template <bool A, bool APX>
 __global__ void __launch_bounds__(R2T, 1) r1_update2_kernel(const __grid_constant__ R2Table tab,
                                                             const float* __restrict__ qmap_m,
                                                             const float* __restrict__ qmap_v, const UConsts cin) {
@@ -556,7 +557,7 @@ __global__ void __launch_bounds__(R2T, 1) r1_update2_kernel(const __grid_constan
     unsigned r = u / gpr, cb = u - r * gpr;          // row and column block of the group; advanced incrementally
     const unsigned sr = stride / gpr, sc = stride - sr * gpr;
     for (; u < lim; u += stride) {
-      r2_group<A>(t, u, r, cb, l16, hmask, c2, kf, Sm, Sv, lut_m, lut_ok, vlin, qm_l, qv_l, (u + stride < lim) ? stride : 0u);
+      r2_group<A, APX>(t, u, r, cb, l16, hmask, c2, kf, Sm, Sv, lut_m, lut_ok, vlin, qm_l, qv_l, (u + stride < lim) ? stride : 0u);
       cb += sc;
       r += sr;
       if (cb >= gpr) {
@@ -607,8 +608,10 @@ static int r1_occupancy(int* out) {
     if (cur >= 0 && cur < 64) stats_ctas[cur] = per_sm;
     LPMM_CUDA_TRY(cudaFuncSetAttribute(r1_update_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)R1_DYN_SMEM));
     LPMM_CUDA_TRY(cudaFuncSetAttribute(r1_update_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)R1_DYN_SMEM));
-    LPMM_CUDA_TRY(cudaFuncSetAttribute(r1_update2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)R1_DYN_SMEM));
-    LPMM_CUDA_TRY(cudaFuncSetAttribute(r1_update2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)R1_DYN_SMEM));
+    LPMM_CUDA_TRY(cudaFuncSetAttribute(r1_update2_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)R1_DYN_SMEM));
+    LPMM_CUDA_TRY(cudaFuncSetAttribute(r1_update2_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)R1_DYN_SMEM));
+    LPMM_CUDA_TRY(cudaFuncSetAttribute(r1_update2_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)R1_DYN_SMEM));
+    LPMM_CUDA_TRY(cudaFuncSetAttribute(r1_update2_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)R1_DYN_SMEM));
   }
   *out = per_sm;
   return LPMM_B200_OK;
@@ -616,7 +619,7 @@ static int r1_occupancy(int* out) {
 
 // One window of at most R1_MAX tensors: zero, statistics, update.
 static int r1_window(const lpmm_b200_step_tensor* const* ts, int n, const float* qmap_m, const float* qmap_v,
-                     const UConsts& c, cudaStream_t st, int arith) {
+                     const UConsts& c, cudaStream_t st, int arith, int apx) {
   static thread_local R1Table tab;   // 32 KB; copied into the launch parameters by the runtime
   static thread_local R2Table tab2;
   static thread_local std::vector<int> order;
@@ -710,8 +713,12 @@ static int r1_window(const lpmm_b200_step_tensor* const* ts, int n, const float*
     tab2.total = g2;
     long long grid2 = (g2 + R2_HW - 1) / R2_HW;
     if (grid2 > num_sms()) grid2 = num_sms();
-    if (arith) r1_update2_kernel<true><<<(unsigned)grid2, R2T, R1_DYN_SMEM, st>>>(tab2, qmap_m, qmap_v, c);
-    else r1_update2_kernel<false><<<(unsigned)grid2, R2T, R1_DYN_SMEM, st>>>(tab2, qmap_m, qmap_v, c);
+    // the folded constants of the fused arithmetic's tolerance mode need a finite 1 / lr
+    const bool apx_ok = apx && (!arith || (c.f_lr >= 0x1p-60f && c.f_lr <= 0x1p30f && c.f_wd <= 0x1p30f));
+    if (arith && apx_ok) r1_update2_kernel<true, true><<<(unsigned)grid2, R2T, R1_DYN_SMEM, st>>>(tab2, qmap_m, qmap_v, c);
+    else if (arith) r1_update2_kernel<true, false><<<(unsigned)grid2, R2T, R1_DYN_SMEM, st>>>(tab2, qmap_m, qmap_v, c);
+    else if (apx_ok) r1_update2_kernel<false, true><<<(unsigned)grid2, R2T, R1_DYN_SMEM, st>>>(tab2, qmap_m, qmap_v, c);
+    else r1_update2_kernel<false, false><<<(unsigned)grid2, R2T, R1_DYN_SMEM, st>>>(tab2, qmap_m, qmap_v, c);
     LPMM_CUDA_TRY(cudaGetLastError());
   }
   if (n > n_wide) {
@@ -728,7 +735,7 @@ static int r1_window(const lpmm_b200_step_tensor* const* ts, int n, const float*
 extern "C" int lpmm_b200_rank1_multi_step(const lpmm_b200_step_tensor* const* ts, int n, const float* qmap_m,
                                           const float* qmap_v, double beta1, double beta2, double lr,
                                           double weight_decay, double eps, double step, void* table,
-                                          int64_t table_bytes, void* stream, int arith) {
+                                          int64_t table_bytes, void* stream, int arith, int apx) {
   (void)table;
   (void)table_bytes;
   if (n <= 0) return LPMM_B200_OK;
@@ -739,7 +746,7 @@ extern "C" int lpmm_b200_rank1_multi_step(const lpmm_b200_step_tensor* const* ts
   static_assert(R1_MAX <= R2_MAX, "a window of wide matrices must fit the second table");
   for (int i = 0; i < n; i += R1_MAX) {
     const int cnt = (n - i < R1_MAX) ? n - i : R1_MAX;
-    const int rc = r1_window(ts + i, cnt, qmap_m, qmap_v, c, (cudaStream_t)stream, arith);
+    const int rc = r1_window(ts + i, cnt, qmap_m, qmap_v, c, (cudaStream_t)stream, arith, apx);
     if (rc != LPMM_B200_OK) return rc;
   }
   return LPMM_B200_OK;

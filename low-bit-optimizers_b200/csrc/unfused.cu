@@ -1588,6 +1588,10 @@ extern "C" int lpmm_b200_adamw4bit_fused_arith_step(const lpmm_b200_step_tensor*
 extern "C" int lpmm_b200_fused_arith_multi_tensor(const lpmm_b200_tensor* ts, int n, const float* qmap_m,
                                                   const float* qmap_v, double beta1, double beta2, double lr,
                                                   double weight_decay, double eps, double step, void* stream);
+// the shared launch of the torch-operation arithmetic with the tolerance-mode parameter update
+extern "C" int lpmm_b200_unfused_multi_tensor_apx(const lpmm_b200_tensor* ts, int n, const float* qmap_m,
+                                                  const float* qmap_v, double beta1, double beta2, double lr,
+                                                  double weight_decay, double eps, double step, void* stream);
 
 // rank1_multi.cu: all rank-1 matrices of a list in three launches (internal to the library)
 extern "C" int64_t lpmm_b200_rank1_multi_table_bytes(int n);
@@ -1595,14 +1599,15 @@ extern "C" int lpmm_b200_rank1_multi_ok(const lpmm_b200_step_tensor* t);
 extern "C" int lpmm_b200_rank1_multi_step(const lpmm_b200_step_tensor* const* ts, int n, const float* qmap_m,
                                           const float* qmap_v, double beta1, double beta2, double lr,
                                           double weight_decay, double eps, double step, void* table,
-                                          int64_t table_bytes, void* stream, int arith);
+                                          int64_t table_bytes, void* stream, int arith, int apx);
 
 // factored_multi.cu: all factored matrices of a list in four launches (internal to the library)
 extern "C" int lpmm_b200_factored_multi_ok(const lpmm_b200_step_tensor* t);
 extern "C" int64_t lpmm_b200_factored_multi_scratch_bytes(const lpmm_b200_step_tensor* const* ts, int n);
 extern "C" int lpmm_b200_factored_multi_step(const lpmm_b200_step_tensor* const* ts, int n, const float* qmap_m,
                                              double beta1, double beta2, double lr, double weight_decay, double eps,
-                                             double step, void* scratch, int64_t scratch_bytes, void* stream);
+                                             double step, void* scratch, int64_t scratch_bytes, void* stream,
+                                             int apx);
 
 // Side streams of lpmm_b200_adamw4bit_unfused_step_many: the tensors of a list are independent and most
 // of them are small (a few launches of a few microseconds each, one waiting for the other), so their
@@ -1659,9 +1664,12 @@ extern "C" int64_t lpmm_b200_unfused_step_many_scratch_bytes(const lpmm_b200_ste
 
 static int step_many(const lpmm_b200_step_tensor* const* tensors, int n, const float* qmap_m, const float* qmap_v,
                      double beta1, double beta2, double lr, double weight_decay, double eps, const double* steps,
-                     void* scratch, int64_t scratch_bytes, void* stream, int arith) {
+                     void* scratch, int64_t scratch_bytes, void* stream, int arith, uint32_t flags) {
   if (n < 0) return LPMM_B200_ERR_BAD_SIZE;
   if (n > 0 && (!tensors || !steps)) return LPMM_B200_ERR_NULL_POINTER;
+  if (flags & ~(uint32_t)LPMM_B200_FLAG_PARAMS_WITHIN_TOLERANCE) return LPMM_B200_ERR_BAD_KIND;
+  // the tolerance mode applies to the list-wide kernels (full aligned groups); tensors stepped on their own stay exact
+  const int apx = (flags & LPMM_B200_FLAG_PARAMS_WITHIN_TOLERANCE) ? 1 : 0;
   cudaStream_t user = (cudaStream_t)stream;
   // which tensors go into the shared multi-tensor launch (both moments fp32, or both 4-bit with
   // groups of 128, already initialised), how many need launches of their own, and the largest
@@ -1789,12 +1797,14 @@ static int step_many(const lpmm_b200_step_tensor* const* tensors, int n, const f
   }
   if (rc == LPMM_B200_OK && !r1.empty())
     rc = lpmm_b200_rank1_multi_step(r1.data(), (int)r1.size(), qmap_m, qmap_v, beta1, beta2, lr, weight_decay, eps,
-                                    r1_step, r1_table, r1_bytes, user, arith);
+                                    r1_step, r1_table, r1_bytes, user, arith, apx);
   if (rc == LPMM_B200_OK && !fm.empty())
     rc = lpmm_b200_factored_multi_step(fm.data(), (int)fm.size(), qmap_m, beta1, beta2, lr, weight_decay, eps, fm_step,
-                                       fm_scratch, fm_bytes, user);
+                                       fm_scratch, fm_bytes, user, apx);
   if (rc == LPMM_B200_OK && !batch.empty())
     rc = arith ? lpmm_b200_fused_arith_multi_tensor(batch.data(), (int)batch.size(), qmap_m, qmap_v, beta1, beta2, lr,
+                                                    weight_decay, eps, batch_step, user)
+         : apx ? lpmm_b200_unfused_multi_tensor_apx(batch.data(), (int)batch.size(), qmap_m, qmap_v, beta1, beta2, lr,
                                                     weight_decay, eps, batch_step, user)
                : lpmm_b200_adamw4bit_unfused_multi_tensor(batch.data(), (int)batch.size(), qmap_m, qmap_v, beta1, beta2,
                                                           lr, weight_decay, eps, batch_step, 0, -1, user);
@@ -1815,7 +1825,16 @@ extern "C" int lpmm_b200_adamw4bit_unfused_step_many(const lpmm_b200_step_tensor
                                                      const double* steps, void* scratch, int64_t scratch_bytes,
                                                      void* stream) {
   return step_many(tensors, n, qmap_m, qmap_v, beta1, beta2, lr, weight_decay, eps, steps, scratch, scratch_bytes,
-                   stream, 0);
+                   stream, 0, 0);
+}
+
+extern "C" int lpmm_b200_adamw4bit_unfused_step_many_flags(const lpmm_b200_step_tensor* const* tensors, int n,
+                                                           const float* qmap_m, const float* qmap_v, double beta1,
+                                                           double beta2, double lr, double weight_decay, double eps,
+                                                           const double* steps, void* scratch, int64_t scratch_bytes,
+                                                           void* stream, uint32_t flags) {
+  return step_many(tensors, n, qmap_m, qmap_v, beta1, beta2, lr, weight_decay, eps, steps, scratch, scratch_bytes,
+                   stream, 0, flags);
 }
 
 extern "C" int lpmm_b200_adamw4bit_fused_arith_step_many(const lpmm_b200_step_tensor* const* tensors, int n,
@@ -1824,7 +1843,16 @@ extern "C" int lpmm_b200_adamw4bit_fused_arith_step_many(const lpmm_b200_step_te
                                                          const double* steps, void* scratch, int64_t scratch_bytes,
                                                          void* stream) {
   return step_many(tensors, n, qmap_m, qmap_v, beta1, beta2, lr, weight_decay, eps, steps, scratch, scratch_bytes,
-                   stream, 1);
+                   stream, 1, 0);
+}
+
+extern "C" int lpmm_b200_adamw4bit_fused_arith_step_many_flags(const lpmm_b200_step_tensor* const* tensors, int n,
+                                                               const float* qmap_m, const float* qmap_v, double beta1,
+                                                               double beta2, double lr, double weight_decay,
+                                                               double eps, const double* steps, void* scratch,
+                                                               int64_t scratch_bytes, void* stream, uint32_t flags) {
+  return step_many(tensors, n, qmap_m, qmap_v, beta1, beta2, lr, weight_decay, eps, steps, scratch, scratch_bytes,
+                   stream, 1, flags);
 }
 
 extern "C" int lpmm_b200_sgd_lowbit_step(float* p, const float* g, int64_t numel, void* buf, float* buf_max1,

@@ -108,6 +108,18 @@ __device__ __forceinline__ void param_pair(const UConsts2& k, f2& p, f2 m, f2 v)
   const f2 quo = f2_fma(f2_fma(nd, q, m), r, q);
   p = f2_fma(k.alpha, quo, f2_mul(p, k.wd_mul));               // addcdiv_ on the decayed parameter
 }
+// Tolerance mode of the same update (the parameter may differ from the exact path's in its last bits; the moments,
+// and with them every code and scale, do not depend on it): approximate square root and reciprocal (2^-23 relative
+// each), d = fma(sqrt(v), 1/bc2s, eps), p = fma(alpha * m, 1/d, p * wd_mul).  Needs d > 0, i.e. the eps of `fast`.
+__device__ __forceinline__ void param_pair_apx(const UConsts2& k, f2& p, f2 m, f2 v) {
+  float va, vb;
+  f2_unpack(v, va, vb);
+  const f2 sq = f2_pack(sqrt_approx(va), sqrt_approx(vb));
+  float da, db;
+  f2_unpack(f2_fma(sq, k.inv_bc2s, k.eps), da, db);
+  const f2 r = f2_pack(mufu_rcp(da), mufu_rcp(db));
+  p = f2_fma(f2_mul(k.alpha, m), r, f2_mul(p, k.wd_mul));
+}
 // First moment of a pair: lerp_(g, 1 - beta1); am collects max |m|.
 __device__ __forceinline__ f2 lerp_pair(const UConsts2& k, f2 g, f2 m0, float& am) {
   const f2 diff = f2_fma(m0, k.mone, g);                       // g - m0
@@ -117,7 +129,9 @@ __device__ __forceinline__ f2 lerp_pair(const UConsts2& k, f2 g, f2 m0, float& a
   am = fmaxf(am, fmaxf(fabsf(ma), fabsf(mb)));
   return m;
 }
-// In: g, p, the old moments m0, v0 (pairs).  Out: m, v, p updated; maxima via am / av.
+// In: g, p, the old moments m0, v0 (pairs).  Out: m, v, p updated; maxima via am / av.  APX: the tolerance mode
+// of the parameter update.
+template <bool APX = false>
 __device__ __forceinline__ void update_pair(const UConsts2& k, f2 g, f2& p, f2 m0, f2 v0, f2& m, f2& v, float& am,
                                             float& av) {
   m = lerp_pair(k, g, m0, am);
@@ -125,7 +139,8 @@ __device__ __forceinline__ void update_pair(const UConsts2& k, f2 g, f2& p, f2 m
   float va, vb;
   f2_unpack(v, va, vb);
   av = fmaxf(av, fmaxf(va, vb));
-  param_pair(k, p, m, v);
+  if (APX) param_pair_apx(k, p, m, v);
+  else param_pair(k, p, m, v);
 }
 
 // Host side: the constants of one step.

@@ -539,15 +539,18 @@ def unfused_step_many_scratch_bytes(ptrs, n):
 
 
 def adamw4bit_unfused_step_many(ptrs, n, qm, qv, steps, scratch_need, device, *, beta1, beta2, lr, weight_decay, eps,
-                                fused_arith=False):
+                                fused_arith=False, exact_params=True):
     """``ptrs``: ctypes array of n addresses of ``lpmm_b200_step_tensor`` descriptors (kept alive and up
     to date by the caller), ``steps``: ctypes array of n doubles, ``scratch_need``: what
     ``unfused_step_many_scratch_bytes`` returned for them.  The caller guarantees that ``device`` is the
-    current device."""
+    current device.  ``exact_params=False``: the tolerance mode of the list-wide kernels (states unchanged,
+    parameters within 1e-6 relative)."""
     scratch = _scratch_for(device, scratch_need)
-    fn = N.lib.lpmm_b200_adamw4bit_fused_arith_step_many if fused_arith else N.lib.lpmm_b200_adamw4bit_unfused_step_many
+    fn = (N.lib.lpmm_b200_adamw4bit_fused_arith_step_many_flags if fused_arith
+          else N.lib.lpmm_b200_adamw4bit_unfused_step_many_flags)
     N.check(fn(ptrs, n, _ptr(qm), _ptr(qv), beta1, beta2, lr, weight_decay, eps, steps, _ptr(scratch),
-               scratch.numel() if scratch is not None else 0, _stream()))
+               scratch.numel() if scratch is not None else 0, _stream(),
+               0 if exact_params else N.FLAG_PARAMS_WITHIN_TOLERANCE))
 
 
 def adamw_fp32_moments_step(p, g, m, v, row, col, *, beta1, beta2, lr, weight_decay, eps, step):

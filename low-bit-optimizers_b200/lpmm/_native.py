@@ -129,6 +129,10 @@ def _load():
         "lpmm_b200_unfused_step_many_scratch_bytes": (i64, [ctypes.POINTER(vp), i32]),
         "lpmm_b200_adamw4bit_unfused_step_many": (i32, [ctypes.POINTER(vp), i32, vp, vp] + [d] * 5
                                                   + [ctypes.POINTER(d), vp, i64, vp]),
+        "lpmm_b200_adamw4bit_unfused_step_many_flags": (i32, [ctypes.POINTER(vp), i32, vp, vp] + [d] * 5
+                                                        + [ctypes.POINTER(d), vp, i64, vp, ctypes.c_uint32]),
+        "lpmm_b200_adamw4bit_fused_arith_step_many_flags": (i32, [ctypes.POINTER(vp), i32, vp, vp] + [d] * 5
+                                                            + [ctypes.POINTER(d), vp, i64, vp, ctypes.c_uint32]),
         "lpmm_b200_adamw4bit_fused_arith_step": (i32, [ctypes.POINTER(StepTensor), vp, vp] + [d] * 6 + [vp]),
         "lpmm_b200_adamw4bit_fused_arith_step_many": (i32, [ctypes.POINTER(vp), i32, vp, vp] + [d] * 5
                                                       + [ctypes.POINTER(d), vp, i64, vp]),

@@ -14,9 +14,10 @@ Constructor, lazily created state, state names and layouts are those of the refe
   falls back to group scales with a warning, adamw.py:503-506) -- with a rank-1 second-moment
   configuration the states have the ``fused=False`` layout (per-axis maxima in ``max_dims``) and are
   stepped with the fused kernel's arithmetic (``lpmm_b200_adamw4bit_fused_arith_step_many``).
-* ``fused=True, exact_params=False`` (an extension) -- the tolerance mode of the fused step: moments, scales
-  and packed codes stay bit-identical to the reference's kernel, the parameters follow it to within 1e-6
-  relative (approximate square root and reciprocal in the parameter update only), for fewer instructions.
+* ``exact_params=False`` (an extension) -- the tolerance mode: moments, scales and packed codes stay
+  bit-identical to the reference's, the parameters follow it to within 1e-6 relative (approximate square root
+  and reciprocal in the parameter update only), for fewer instructions.  It applies to the fused step and to the
+  list-wide kernels of the non-fused step (plain, rank-1 and factored tensors stepped together).
 * tensors with at most ``THRESHOLD`` (4096) elements, or overridden, keep fp32 moments.
 * ``factor_second_moment=True`` keeps fp32 row/column accumulators for every >=2-D tensor
   (adamw.py:124-126, 579-627).
@@ -369,7 +370,8 @@ class AdamW(LowBitOptimizer):
         beta1, beta2 = group["betas"]
         _kernels.adamw4bit_unfused_step_many(ptrs, len(plans), b["qm"], b["qv"], steps, b["scratch"], params[0].device,
                                              beta1=beta1, beta2=beta2, lr=group["lr"],
-                                             weight_decay=group["weight_decay"], eps=group["eps"], fused_arith=fused_arith)
+                                             weight_decay=group["weight_decay"], eps=group["eps"], fused_arith=fused_arith,
+                                             exact_params=self._exact_params)
         for i in b["rank1_index"]:  # rank-1: the freshly written maxima become the state's
             plan = plans[i]
             plan.which ^= 1

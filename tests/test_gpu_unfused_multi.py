@@ -238,3 +238,74 @@ def test_lists_longer_than_one_descriptor_window(qmaps, kw, v_scale, factored):
     opt, params, o_states, o_params = _run_pair_adamw(
         shapes, p0s, lambda s: [student_t(sh, s * 100003 + i) for i, sh in enumerate(shapes)], 4, kw, qmaps, v_scale)
     _check_adamw(opt, params, o_states, o_params, v_scale, factored=factored)
+
+
+WIDE_SHAPES = [(1000, 768), (768, 3072), (130, 4096), (4097, 8), (333, 1024), (1024,), (3, 3, 64, 64), (70, 61),
+               (5000, 16), (4100,), (64, 128)]
+
+
+@pytest.mark.parametrize("kw,v_scale,factored", [(dict(qconfig=None), "group", False),
+                                                 (dict(qconfig="default.yml"), "rank1", False),
+                                                 (dict(qconfig=None, factor_second_moment=True), "group", True)],
+                         ids=["group", "rank1", "factored"])
+def test_tolerance_mode_of_the_list_wide_kernels_against_the_oracle(qmaps, kw, v_scale, factored):
+    """``exact_params=False`` on the non-fused step: the list-wide kernels take the approximate square root and
+    reciprocal in the parameter update.  Moments do not depend on the parameters, so after 7 steps every code, scale,
+    per-axis maximum and accumulator still equals the restated reference's exactly (the accumulators to their usual
+    summation-order tolerance); the parameters stay within 1e-6 relative.  Matrices with rows that are multiples of
+    128 (the wide update kernels) next to narrow and odd shapes (exact kernels)."""
+    kw = dict(kw, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01, exact_params=False)
+    torch.manual_seed(71)
+    p0s = [torch.randn(s, device=device()) * 0.02 for s in WIDE_SHAPES]
+    opt, params, o_states, o_params = _run_pair_adamw(
+        WIDE_SHAPES, p0s, lambda s: [student_t(sh, s * 100003 + i, zero_fraction=0.2) for i, sh in enumerate(WIDE_SHAPES)],
+        7, kw, qmaps, v_scale)
+    _check_adamw(opt, params, o_states, o_params, v_scale, factored=factored, p_exact=False)
+    for p, op in zip(params, o_params):  # element-wise too: a few ulps of the parameter or of the step taken
+        err = (p.detach() - op).abs()
+        assert bool((err <= 2e-6 * op.abs() + 5e-8).all())
+
+
+@pytest.mark.parametrize("kw", [dict(qconfig=None), dict(qconfig="default.yml"),
+                                dict(qconfig=None, factor_second_moment=True),
+                                dict(qconfig="default.yml", fused=True, fused_rank1=True)],
+                         ids=["group", "rank1", "factored", "fused_rank1"])
+def test_tolerance_mode_of_the_list_wide_kernels_against_the_exact_mode(kw):
+    """The same list stepped by two optimizers, one exact and one in tolerance mode: all state tensors bit-identical
+    after 6 steps, parameters within 1e-6 relative, and not all parameters bit-identical (the flag reached the
+    kernels)."""
+    import os
+    import lpmm
+    from lpmm.config import CONFIG_DIR
+    kw = dict(kw, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01)
+    if isinstance(kw.get("qconfig"), str):
+        kw["qconfig"] = os.path.join(CONFIG_DIR, kw["qconfig"])
+    torch.manual_seed(81)
+    init = [torch.randn(s, device=device()) * 0.02 for s in WIDE_SHAPES]
+    pa = [torch.nn.Parameter(x.clone()) for x in init]
+    pb = [torch.nn.Parameter(x.clone()) for x in init]
+    oa, ob = lpmm.optim.AdamW(pa, **kw), lpmm.optim.AdamW(pb, exact_params=False, **kw)
+    for s in range(1, 7):
+        for i, (a, b) in enumerate(zip(pa, pb)):
+            g = student_t(WIDE_SHAPES[i], 100003 * s + i)
+            a.grad, b.grad = g, g.clone()
+        oa.step()
+        ob.step()
+    torch.cuda.synchronize()
+    differing = 0
+    for i, (a, b) in enumerate(zip(pa, pb)):
+        rel = ((a.detach() - b.detach()).norm() / a.detach().norm()).item()
+        assert rel <= 1e-6, f"tensor {i}: {rel}"
+        differing += int(not bits_equal(a.detach(), b.detach()))
+        sa, sb = oa.state[a], ob.state[b]
+        for key in ("exp_avg", "exp_avg_sq", "exp_avg_sq_row", "exp_avg_sq_col"):
+            if key in sa and torch.is_tensor(sa[key]) and sa[key].numel():
+                assert torch.equal(sa[key].reshape(-1).view(torch.uint8), sb[key].reshape(-1).view(torch.uint8)), f"tensor {i}: {key}"
+        for q in ("exp_avg_qstate", "exp_avg_sq_qstate"):
+            oh_a, oh_b = sa.get(q, {}).get("overhead", {}), sb.get(q, {}).get("overhead", {})
+            if oh_a.get("max1") is not None:
+                assert bits_equal(oh_a["max1"], oh_b["max1"]), f"tensor {i}: {q} scales"
+            if oh_a.get("max_dims") is not None:
+                for x, y in zip(oh_a["max_dims"], oh_b["max_dims"]):
+                    assert bits_equal(x, y), f"tensor {i}: {q} per-axis maxima"
+    assert differing > 0

@@ -232,6 +232,11 @@ def test_flags_entry_points_validate_without_a_gpu():
     assert N.lib.lpmm_b200_adamw4bit_multi_tensor_16bit_peers(t, 1, N.DTYPE_BF16, qm, qm, h, 0, -1, None, 2, 0, None) == -1
     assert N.lib.lpmm_b200_adamw4bit_multi_tensor_16bit_peers(t, 1, 7, qm, qm, h, 0, -1, offs, 1, 0, None) == -3
     assert N.lib.lpmm_b200_adamw4bit_multi_tensor_peers_flags(t, 1, qm, qm, h, 0, -1, offs, 2, 0, None) == -2  # 8 % 32 != 0
+    # the list forms of the non-fused step: unknown flag bits refused, an empty list is a no-op with either flag value
+    for fn in (N.lib.lpmm_b200_adamw4bit_unfused_step_many_flags, N.lib.lpmm_b200_adamw4bit_fused_arith_step_many_flags):
+        assert fn(None, 0, qm, qm, 0.9, 0.999, 1e-3, 0.01, 1e-8, None, None, 0, None, 2) == -3
+        assert fn(None, 0, qm, qm, 0.9, 0.999, 1e-3, 0.01, 1e-8, None, None, 0, None, 1) == 0
+        assert fn(None, 0, qm, qm, 0.9, 0.999, 1e-3, 0.01, 1e-8, None, None, 0, None, 0) == 0
 
 
 def test_reference_arm_of_the_bench_prints_its_line(tmp_path):
