@@ -10,8 +10,9 @@ which the 64 norm vectors (exactly 4096 elements) keep fp32 moments.  Data are s
 
 own arm      one step = ``lpmm.optim.AdamW(fused=True).step()`` over the whole list (one multi-tensor
              launch).  ``value`` is timed with parameters, gradients and states resident in HBM;
-             ``e2e`` is the same call with the step's gradients arriving from pinned host memory
-             and a device->host read of a result inside the timed region.  ``tolerance_mode``: the same
+             ``e2e`` is the step with its gradients arriving from pinned host memory (``step_from_host``:
+             copies on a copy stream, every chunk updated as it lands) and a device->host read of a result
+             inside the timed region; ``copy_then_step_ms`` is the plain sequence timed beside it.  ``tolerance_mode``: the same
              step with ``exact_params=False`` (codes and scales bit-identical, parameters within 1e-6).
              With N > 1 the list is ZeRO-1 sharded by whole 128-element groups (``lpmm.zero``); the updated
              parameters reach the other ranks by NVLink stores inside the update kernel (``--gather fused``,
@@ -571,28 +572,40 @@ def run_own(args):
         del tmp
         result = torch.empty(1024, dtype=torch.float32, pin_memory=True)
 
+        # the step's gradients arrive from pinned host memory, 4 * total bytes per step (the pinned pool is the source
+        # of every tensor's copy).  ``AdamW.step_from_host`` copies them on a copy stream and updates every 256 MB that
+        # has landed while the rest is still on its way; the plain way (copy everything, then step) is timed beside it.
+        host_grads = [pool[: numel(s)] for s in shapes]
+
         def e2e_step():
-            # the step's gradients arrive from pinned host memory: 4 * total bytes in copies of up to 2 GB (the pinned
-            # pool is reused as the source of every chunk)
+            opt.step_from_host(host_grads)
+            result.copy_(params[-1].detach().view(-1)[:1024], non_blocking=True)
+
+        def e2e_plain_step():
             for lo in range(0, total, pool_n):
                 hi = min(lo + pool_n, total)
                 gflat[lo:hi].copy_(pool[: hi - lo], non_blocking=True)
             opt.step()
             result.copy_(params[-1].detach().view(-1)[:1024], non_blocking=True)
 
-        for _ in range(2):
-            e2e_step()
-        torch.cuda.synchronize()
+        def time_e2e(fn, n):
+            for _ in range(2):
+                fn()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(n):
+                fn()
+            b.record()
+            torch.cuda.synchronize()
+            return a.elapsed_time(b) / n
+
         n_e2e = max(2, min(args.steps, 5))
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(n_e2e):
-            e2e_step()
-        b.record()
-        torch.cuda.synchronize()
-        e_ms = a.elapsed_time(b) / n_e2e
+        plain_ms = time_e2e(e2e_plain_step, 2)
+        e_ms = time_e2e(e2e_step, n_e2e)
         e2e = {"value": total / (e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": 4 * total, "d2h_bytes_per_step": 4096,
-               "ms_per_step": e_ms, "steps": n_e2e}
+               "ms_per_step": e_ms, "steps": n_e2e, "call": "AdamW.step_from_host (copies and update overlapped)",
+               "copy_then_step_ms": plain_ms}
     elif args.reduce_grads:
         e2e = None  # the gradients are produced on each GPU (data-parallel backward); no host copy belongs to this mode
     else:
@@ -603,25 +616,36 @@ def run_own(args):
         result = torch.empty(1024, dtype=torch.float32, pin_memory=True)
 
         def e2e_step():
+            opt.step_from_host(pool)
+            result.copy_(opt.flat[:1024], non_blocking=True)
+
+        def e2e_plain_step():
             opt.grad_shard.copy_(pool, non_blocking=True)
             opt.step()
             result.copy_(opt.flat[:1024], non_blocking=True)
 
-        for _ in range(2):
-            e2e_step()
-        barrier()
+        def time_e2e(fn, n):
+            for _ in range(2):
+                fn()
+            barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(n):
+                fn()
+            b.record()
+            barrier()
+            t = torch.tensor([a.elapsed_time(b) / n], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+
         n_e2e = max(2, min(args.steps, 5))
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(n_e2e):
-            e2e_step()
-        b.record()
-        barrier()
-        t = torch.tensor([a.elapsed_time(b) / n_e2e], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e_ms = float(t.item())
-        e2e = {"value": total / (e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": 4 * n_sh * world,
-               "d2h_bytes_per_step": 4096 * world, "ms_per_step": e_ms, "steps": n_e2e}
+        plain_ms = time_e2e(e2e_plain_step, 2)
+        e_ms = time_e2e(e2e_step, n_e2e)
+        owned = torch.tensor([(opt.hi - opt.lo) * 128 * 4], device=dev, dtype=torch.float64)
+        dist.all_reduce(owned)
+        e2e = {"value": total / (e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": int(owned.item()),
+               "d2h_bytes_per_step": 4096 * world, "ms_per_step": e_ms, "steps": n_e2e,
+               "call": "Zero1FusedAdamW.step_from_host (copies and update overlapped)", "copy_then_step_ms": plain_ms}
 
     if world > 1 and not args.no_extras and not args.reduce_grads:
         del opt

@@ -104,24 +104,105 @@ class AdamW(LowBitOptimizer):
             with torch.enable_grad():
                 loss = closure()
         for gi, group in enumerate(self.param_groups):
-            params = []
-            for p in group["params"]:
-                if p.grad is None:
-                    continue
-                if p.grad.is_sparse:
-                    raise RuntimeError("AdamW does not support sparse gradients")
-                if len(self.state[p]) == 0:
-                    self._init_state(group, p)
-                params.append(p)
-            if not params:
-                continue
-            if group["fused"] and self._fused_rank1_applies(group):
-                self._step_single(gi, group, params, fused_arith=True)
-            elif group["fused"]:
-                self._step_fused(gi, group, params)
-            else:
-                self._step_single(gi, group, params)
+            self._step_group(gi, group)
         return loss
+
+    def _params_to_step(self, group):
+        params = []
+        for p in group["params"]:
+            if p.grad is None:
+                continue
+            if p.grad.is_sparse:
+                raise RuntimeError("AdamW does not support sparse gradients")
+            if len(self.state[p]) == 0:
+                self._init_state(group, p)
+            params.append(p)
+        return params
+
+    def _step_group(self, gi, group):
+        params = self._params_to_step(group)
+        if not params:
+            return
+        if group["fused"] and self._fused_rank1_applies(group):
+            self._step_single(gi, group, params, fused_arith=True)
+        elif group["fused"]:
+            self._step_fused(gi, group, params)
+        else:
+            self._step_single(gi, group, params)
+
+    @torch.no_grad()
+    def step_from_host(self, host_grads, chunk_bytes=256 << 20):
+        """One step whose gradients arrive from host memory (an extension; the reference has no such call).
+
+        ``host_grads``: one CPU tensor (pinned, for the copies to be asynchronous) per parameter of the optimizer, in
+        the order of ``param_groups``; ``None`` leaves that parameter out of the step.  Each is copied into the
+        parameter's ``.grad`` (allocated here if missing) on a copy stream.  A ``fused=True`` group that has been stepped
+        before is updated while the copies are still running: every ``chunk_bytes`` of gradients that have landed are
+        followed by a launch over just those tensors' groups (``group_begin`` / ``group_end`` of the list step), so the
+        step ends one chunk's update after the last byte arrives instead of a whole list's.  Other groups wait for
+        their copies and take the ordinary step.  Results are those of copying everything and calling ``step()``."""
+        all_params = [p for group in self.param_groups for p in group["params"]]
+        host = list(host_grads)
+        if len(host) != len(all_params):
+            raise ValueError(f"expected {len(all_params)} host gradients (None for a parameter to skip), got {len(host)}")
+        k = 0
+        for gi, group in enumerate(self.param_groups):
+            pairs = []
+            for p in group["params"]:
+                h = host[k]
+                k += 1
+                if h is None:
+                    p.grad = None
+                    continue
+                if h.numel() != p.numel() or h.dtype != p.dtype:
+                    raise RuntimeError("a host gradient must have its parameter's size and dtype")
+                if p.grad is None:
+                    p.grad = torch.empty_like(p, memory_format=torch.contiguous_format)
+                pairs.append((p, h))
+            if not pairs:
+                continue
+            if not pairs[0][0].is_cuda:  # nothing to overlap
+                for p, h in pairs:
+                    p.grad.copy_(h.view_as(p.grad))
+                self._step_group(gi, group)
+                continue
+            device = pairs[0][0].device
+            main = torch.cuda.current_stream(device)
+            copies = self.__dict__.setdefault("_copy_streams", {})
+            cs = copies.get(device)
+            if cs is None:
+                cs = copies[device] = torch.cuda.Stream(device=device)
+            cs.wait_stream(main)  # work already enqueued may still read the gradient buffers
+            params = self._params_to_step(group)
+            plan = None
+            if group["fused"] and not self._fused_rank1_applies(group):
+                plan = self._plan_ready(gi, params)
+            if plan is None:
+                with torch.cuda.stream(cs):
+                    for p, h in pairs:
+                        p.grad.copy_(h.view_as(p.grad), non_blocking=True)
+                main.wait_stream(cs)
+                self._step_group(gi, group)
+                continue
+            if "gstart" not in plan:  # first group of every tensor in the list-wide group numbering
+                gs, acc = [], 0
+                for p in plan["params"]:
+                    gs.append(acc)
+                    acc += (p.numel() + 127) // 128
+                plan["gstart"] = gs + [acc]
+            torch._foreach_add_(plan["steps"], 1.0)
+            plan["step"] += 1.0
+            gstart, done, pending = plan["gstart"], 0, 0
+            for i, (p, h) in enumerate(pairs):  # pairs and plan["params"] are the same parameters in the same order
+                with torch.cuda.stream(cs):
+                    p.grad.copy_(h.view_as(p.grad), non_blocking=True)
+                pending += p.numel() * p.element_size()
+                if pending >= chunk_bytes or i + 1 == len(pairs):
+                    ev = torch.cuda.Event()
+                    ev.record(cs)
+                    main.wait_event(ev)
+                    self._plan_launch(group, plan, gstart[done], gstart[i + 1])
+                    done, pending = i + 1, 0
 
     def _fused_rank1_applies(self, group):
         """fused_rank1=True and a configuration the fused kernel cannot hold as such: a rank-1 second moment
@@ -218,13 +299,24 @@ class AdamW(LowBitOptimizer):
     def _step_fused_planned(self, gi, group, params):
         """Fast path of a fused group whose tensors, states and step counters are unchanged since the
         last step.  Returns False (after dropping the plan) whenever anything differs."""
-        plan = self._plans.get(gi)
+        plan = self._plan_ready(gi, params)
         if plan is None:
             return False
+        torch._foreach_add_(plan["steps"], 1.0)
+        plan["step"] += 1.0
+        self._plan_launch(group, plan)
+        return True
+
+    def _plan_ready(self, gi, params):
+        """The plan of group ``gi`` if it still describes ``params`` (gradient pointers refreshed), else None (the
+        plan is dropped)."""
+        plan = self._plans.get(gi)
+        if plan is None:
+            return None
         pp = plan["params"]
         if len(pp) != len(params):
             del self._plans[gi]
-            return False
+            return None
         tl, gptrs = plan["tl"], plan["gptrs"]
         for i, p in enumerate(params):
             st = plan["states"][i]
@@ -233,23 +325,23 @@ class AdamW(LowBitOptimizer):
                     or st.get("step") is not plan["steps"][i]
                     or (p.data_ptr(), m.data_ptr(), v.data_ptr()) != plan["ptrs"][i]):
                 del self._plans[gi]
-                return False
+                return None
             g = p.grad
             gp = g.data_ptr()
             if gp != gptrs[i]:
                 if g.dtype != plan["dtype"] or not g.is_cuda or not g.is_contiguous() or g.numel() != p.numel():
                     del self._plans[gi]
-                    return False
+                    return None
                 tl.array[i].g = gp
                 gptrs[i] = gp
-        torch._foreach_add_(plan["steps"], 1.0)
-        plan["step"] += 1.0
+        return plan
+
+    def _plan_launch(self, group, plan, group_begin=0, group_end=-1):
         beta1, beta2 = group["betas"]
         with torch.cuda.device(plan["device"]):
-            _kernels.adamw4bit_multi_tensor(tl, plan["qm"], plan["qv"], beta1, beta2, group["lr"], group["weight_decay"],
-                                            group["eps"], plan["step"], dtype=plan["dtype"],
-                                            exact_params=self._exact_params)
-        return True
+            _kernels.adamw4bit_multi_tensor(plan["tl"], plan["qm"], plan["qv"], beta1, beta2, group["lr"],
+                                            group["weight_decay"], group["eps"], plan["step"], group_begin, group_end,
+                                            dtype=plan["dtype"], exact_params=self._exact_params)
 
     def _tensor_list(self, key, entries):
         """Descriptor array of a parameter list, rebuilt only when a pointer changed."""

@@ -304,6 +304,39 @@ class Zero1FusedAdamW:
             self._update(self.lo, self.hi)
         self._gather()
 
+    def step_from_host(self, host_shard, chunk_bytes=256 << 20):
+        """One step whose gradient shard arrives from (pinned) host memory: ``host_shard`` holds what ``grad_shard``
+        would, ``shard_groups * 128`` elements.  It is copied chunk by chunk on a copy stream, and every chunk that has
+        landed is followed by a launch over just its groups, so the update and its stores to the peers overlap the
+        remaining copies; the step ends one chunk's update after the last byte arrives.  Results are those of
+        ``grad_shard.copy_(host_shard); step()``."""
+        if self._full_grads is not None or self.reduce_grads:
+            raise RuntimeError("step_from_host feeds grad_shard; it does not combine with use_full_grads / reduce_grads")
+        if host_shard.numel() != self.grad_shard.numel() or host_shard.dtype != self.dtype:
+            raise RuntimeError("host_shard must have the size and dtype of grad_shard")
+        if self.device.type != "cuda":  # nothing to overlap
+            self.grad_shard.copy_(host_shard.view(-1))
+            return self.step()
+        self.step_count += 1
+        self._pre_step_barrier()
+        main = torch.cuda.current_stream(self.device)
+        if getattr(self, "_copy_stream", None) is None:
+            self._copy_stream = torch.cuda.Stream(device=self.device)
+        cs = self._copy_stream
+        cs.wait_stream(main)  # launches already enqueued may still read grad_shard
+        per = max(1, int(chunk_bytes) // (GROUP * self.esize))  # groups per chunk
+        src = host_shard.view(-1)
+        for a in range(self.lo, self.hi, per):
+            b = min(a + per, self.hi)
+            e0, e1 = (a - self.lo) * GROUP, (b - self.lo) * GROUP
+            with torch.cuda.stream(cs):
+                self.grad_shard[e0:e1].copy_(src[e0:e1], non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(cs)
+            main.wait_event(ev)
+            self._update(a, b)
+        self._gather()
+
     # ---- checkpoints --------------------------------------------------------------------------
     def gather_state(self):
         """Reassemble, on every rank, the optimizer state of the whole list in the layout of the

@@ -1,0 +1,92 @@
+"""``step_from_host`` (gradients arriving from pinned host memory, updated chunk by chunk while the copies run) gives the
+results of copying everything and calling ``step()``, bit for bit: ``lpmm.optim.AdamW`` with fused, non-fused and
+mixed parameter groups, skipped parameters and chunk sizes that cut the list into many launches; and the ZeRO-1 engine
+on a world of one rank."""
+import pytest
+import torch
+
+from gpu_helpers import device, student_t
+from test_zero_cpu import _assert_same_tree
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [(300, 128), (4096,), (5000,), (77, 129), (128,), (64, 64, 3), (512, 1024), (1000, 768), (4097,)]
+
+
+def _model(dtype=torch.float32):
+    torch.manual_seed(0)
+    return [torch.nn.Parameter((torch.randn(s, device=device()) * 0.02).to(dtype)) for s in SHAPES]
+
+
+def _host_grads(step, dtype=torch.float32, skip=()):
+    return [None if i in skip else student_t(s, 100003 * step + i).to(dtype).cpu().pin_memory()
+            for i, s in enumerate(SHAPES)]
+
+
+def _same(pa, pb, oa, ob):
+    torch.cuda.synchronize()
+    for i, (a, b) in enumerate(zip(pa, pb)):
+        assert torch.equal(a.detach().view(-1).view(torch.uint8), b.detach().view(-1).view(torch.uint8)), f"tensor {i}"
+    _assert_same_tree(oa.state_dict(), ob.state_dict())
+
+
+@pytest.mark.parametrize("chunk", [1 << 12, 1 << 20, 256 << 20])
+@pytest.mark.parametrize("groups", ["fused", "fused_bf16", "mixed", "nonfused"])
+def test_adamw_step_from_host_equals_copy_then_step(chunk, groups):
+    import lpmm
+    dtype = torch.bfloat16 if groups == "fused_bf16" else torch.float32
+    kw = dict(lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01)
+
+    def make(params):
+        if groups in ("fused", "fused_bf16"):
+            return lpmm.optim.AdamW([dict(params=params[:4]), dict(params=params[4:], lr=2e-3)], fused=True, **kw)
+        if groups == "mixed":
+            return lpmm.optim.AdamW([dict(params=params[:4], fused=True), dict(params=params[4:], fused=False)], **kw)
+        return lpmm.optim.AdamW(params, **kw)
+
+    pa, pb = _model(dtype), _model(dtype)
+    oa, ob = make(pa), make(pb)
+    for s in range(1, 7):
+        skip = (2,) if s == 4 else ()  # a parameter of the first group sits out one step: that group's plan is dropped
+        hg = _host_grads(s, dtype, skip)
+        oa.step_from_host(hg, chunk_bytes=chunk)
+        for p, h in zip(pb, hg):
+            p.grad = None if h is None else h.to(device())
+        ob.step()
+    _same(pa, pb, oa, ob)
+    if groups.startswith("fused"):
+        assert 1 in oa._plans, "the second group did not keep its plan: the streamed path was not taken"
+
+
+def test_adamw_step_from_host_validates_its_arguments():
+    import lpmm
+    pa = _model()
+    oa = lpmm.optim.AdamW(pa, fused=True)
+    with pytest.raises(ValueError):
+        oa.step_from_host([None])
+    hg = _host_grads(1)
+    hg[0] = hg[0][:-1]
+    with pytest.raises(RuntimeError):
+        oa.step_from_host(hg)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("chunk", [1 << 12, 1 << 20])
+def test_zero1_engine_step_from_host_equals_copy_then_step(dtype, chunk):
+    from lpmm.zero import Zero1FusedAdamW
+    kw = dict(lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01, rank=0, world=1, dtype=dtype)
+    za, zb = Zero1FusedAdamW(SHAPES, device(), **kw), Zero1FusedAdamW(SHAPES, device(), **kw)
+    za.init_params_normal_(0.02, seed=0)
+    zb.init_params_normal_(0.02, seed=0)
+    for s in range(1, 5):
+        grads = [student_t(sh, 100003 * s + i).to(dtype) for i, sh in enumerate(SHAPES)]
+        zb.set_grad_shard_from_full(grads)
+        host = zb.grad_shard.cpu().pin_memory()
+        zb.step()
+        za.step_from_host(host, chunk_bytes=chunk)
+    torch.cuda.synchronize()
+    assert torch.equal(za.flat.view(torch.uint8), zb.flat.view(torch.uint8))
+    for name in ("m_codes", "v_codes", "m_scale", "v_scale", "m32", "v32"):
+        assert torch.equal(getattr(za, name).view(torch.uint8), getattr(zb, name).view(torch.uint8)), name
+    with pytest.raises(RuntimeError):
+        za.step_from_host(host[:-1])

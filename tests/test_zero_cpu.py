@@ -318,3 +318,19 @@ def test_zero_optimizer_wrapper_two_ranks_equal_one_rank(golden_dir, tmp_path):
     assert small["exp_avg"].dtype == torch.float32 and tuple(small["exp_avg"].shape) == SHAPES[1]
     assert ref["param_groups"][1]["weight_decay"] == 0.1 and ref["param_groups"][1]["lr"] == 1e-3
     assert "qconfig" in ref
+
+
+def test_step_from_host_without_a_gpu_is_copy_then_step(golden_dir):
+    """On a CPU engine (the oracle as the launch) ``step_from_host`` has nothing to overlap: it must equal
+    ``grad_shard.copy_(host); step()`` and refuse a shard of the wrong size."""
+    z = np.load(os.path.join(golden_dir, "qmaps.npz"))
+    a, b = _make(1, 0, z["m"], z["v"]), _make(1, 0, z["m"], z["v"])
+    for step in range(1, 3):
+        b.set_grad_shard_from_full(_grads(step))
+        host = b.grad_shard.clone()
+        b.step()
+        a.step_from_host(host)
+    assert a.step_count == b.step_count == 2
+    assert np.array_equal(a.flat.numpy().view(np.int32), b.flat.numpy().view(np.int32))
+    with pytest.raises(RuntimeError):
+        a.step_from_host(host[:-1])

@@ -1,7 +1,8 @@
 """Run under torch.distributed.run on 2 or more GPUs (tests/test_gpu_zero_multi.py does): the ZeRO-1 step
 with parameters pushed to the peers by stores inside the update kernel equals the ZeRO-1 step followed by an
 NCCL all-gather, bit for bit, and every rank ends with the same parameter buffer; and the step that also
-reduces the gradients of all ranks inside the update kernel equals the step on gradients summed beforehand.
+reduces the gradients of all ranks inside the update kernel equals the step on gradients summed beforehand;
+16-bit parameters, the optimizer wrapper and the step fed from pinned host memory likewise.
 Prints one OK line per rank."""
 import os, sys, torch, torch.distributed as dist
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -99,7 +100,24 @@ sd_a, sd_b = za.state_dict(), ob.state_dict()
 for k in sd_b["state"]:
     for name in ("exp_avg", "exp_avg_sq"):
         same4 = same4 and bool(torch.equal(sd_a["state"][k][name].view(-1).view(torch.uint8), sd_b["state"][k][name].view(-1).view(torch.uint8)))
-ok = ok and same3 and same4
+# ---- gradient shards arriving from pinned host memory, updated chunk by chunk while the copies run (peer stores
+# from several launches per step) == the step on a shard copied beforehand
+sa = Zero1FusedAdamW(shapes, dev, gather="fused", **H)
+sb = Zero1FusedAdamW(shapes, dev, gather="nccl", **H)
+sa.init_params_normal_(0.02, seed=0); sb.init_params_normal_(0.02, seed=0)
+for step in range(1, 4):
+    grads = []
+    for i, s in enumerate(shapes):
+        g = torch.Generator(device=dev); g.manual_seed(step * 100003 + 13 * i)
+        grads.append(torch.randn(s, generator=g, device=dev) * 1e-3)
+    sb.set_grad_shard_from_full(grads)
+    host = sb.grad_shard.cpu().pin_memory()
+    sb.step()
+    sa.step_from_host(host, chunk_bytes=1 << 16)
+torch.cuda.synchronize(); dist.barrier()
+same5 = bool(torch.equal(sa.flat.view(torch.int32), sb.flat.view(torch.int32)))
+ok = ok and same3 and same4 and same5
 print(f"rank {rank}: {'OK' if ok else 'MISMATCH'} (fused == nccl: {same}, in-kernel gradient reduction == summed gradients: {same2}, "
-      f"16-bit sharded == unsharded: {same3}, optimizer wrapper == unsharded optimizer: {same4})", flush=True)
+      f"16-bit sharded == unsharded: {same3}, optimizer wrapper == unsharded optimizer: {same4}, "
+      f"step_from_host == copy then step: {same5})", flush=True)
 dist.destroy_process_group()
