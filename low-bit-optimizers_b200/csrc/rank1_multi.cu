@@ -574,12 +574,7 @@ __global__ void __launch_bounds__(R2T, 1) r1_update2_kernel(const __grid_constan
 using namespace lpmm_b200;
 
 // Host side.  `ts`: n tensors that all satisfy lpmm_b200_rank1_multi_ok.  Not part of the public header: called
-// by lpmm_b200_adamw4bit_unfused_step_many.  The descriptors travel in the launch parameters: `table` is unused
-// (kept for the callers' signature) and lpmm_b200_rank1_multi_table_bytes is 0.
-extern "C" int64_t lpmm_b200_rank1_multi_table_bytes(int n) {
-  (void)n;
-  return 0;
-}
+// by lpmm_b200_adamw4bit_unfused_step_many.  The descriptors travel in the launch parameters: no scratch is needed.
 
 extern "C" int lpmm_b200_rank1_multi_ok(const lpmm_b200_step_tensor* t) {
   if (!t || t->first || t->numel <= 0 || t->ndim != 2) return 0;
@@ -734,10 +729,8 @@ static int r1_window(const lpmm_b200_step_tensor* const* ts, int n, const float*
 
 extern "C" int lpmm_b200_rank1_multi_step(const lpmm_b200_step_tensor* const* ts, int n, const float* qmap_m,
                                           const float* qmap_v, double beta1, double beta2, double lr,
-                                          double weight_decay, double eps, double step, void* table,
-                                          int64_t table_bytes, void* stream, int arith, int apx) {
-  (void)table;
-  (void)table_bytes;
+                                          double weight_decay, double eps, double step, void* stream, int arith,
+                                          int apx) {
   if (n <= 0) return LPMM_B200_OK;
   if (!ts || !qmap_m || !qmap_v) return LPMM_B200_ERR_NULL_POINTER;
   for (int i = 0; i < n; ++i)

@@ -1594,12 +1594,11 @@ extern "C" int lpmm_b200_unfused_multi_tensor_apx(const lpmm_b200_tensor* ts, in
                                                   double weight_decay, double eps, double step, void* stream);
 
 // rank1_multi.cu: all rank-1 matrices of a list in three launches (internal to the library)
-extern "C" int64_t lpmm_b200_rank1_multi_table_bytes(int n);
 extern "C" int lpmm_b200_rank1_multi_ok(const lpmm_b200_step_tensor* t);
 extern "C" int lpmm_b200_rank1_multi_step(const lpmm_b200_step_tensor* const* ts, int n, const float* qmap_m,
                                           const float* qmap_v, double beta1, double beta2, double lr,
-                                          double weight_decay, double eps, double step, void* table,
-                                          int64_t table_bytes, void* stream, int arith, int apx);
+                                          double weight_decay, double eps, double step, void* stream, int arith,
+                                          int apx);
 
 // factored_multi.cu: all factored matrices of a list in four launches (internal to the library)
 extern "C" int lpmm_b200_factored_multi_ok(const lpmm_b200_step_tensor* t);
@@ -1643,7 +1642,6 @@ extern "C" int64_t lpmm_b200_unfused_step_many_scratch_bytes(const lpmm_b200_ste
   if (n < 0 || (n > 0 && !tensors)) return LPMM_B200_ERR_BAD_SIZE;
   std::vector<const lpmm_b200_step_tensor*> fmv;
   int64_t max_need = 0;
-  int r1n = 0;
   for (int i = 0; i < n; ++i) {
     const lpmm_b200_step_tensor* t = tensors[i];
     if (!t) return LPMM_B200_ERR_NULL_POINTER;
@@ -1654,11 +1652,9 @@ extern "C" int64_t lpmm_b200_unfused_step_many_scratch_bytes(const lpmm_b200_ste
       probe.first = 0;  // sized for the steady state
       if (lpmm_b200_factored_multi_ok(&probe)) fmv.push_back(t);
     }
-    if (t->v_mode == LPMM_B200_STATE_RANK1_4) ++r1n;
   }
   int64_t total = (int64_t)SIDE_STREAMS * ((max_need + 255) & ~(int64_t)255);
   if (fmv.size() >= 2) total += (lpmm_b200_factored_multi_scratch_bytes(fmv.data(), (int)fmv.size()) + 511) & ~(int64_t)255;
-  total += (lpmm_b200_rank1_multi_table_bytes(r1n) + 511) & ~(int64_t)255;
   return total + 1024;
 }
 
@@ -1700,8 +1696,6 @@ static int step_many(const lpmm_b200_step_tensor* const* tensors, int n, const f
       r1.push_back(tensors[i]);
     }
   }
-  void* r1_table = nullptr;
-  const int64_t r1_bytes = 0;
   if (r1.size() < 2) r1.clear();
   auto in_r1 = [&](const lpmm_b200_step_tensor* t, double s) {
     return !r1.empty() && s == r1_step && lpmm_b200_rank1_multi_ok(t);
@@ -1797,7 +1791,7 @@ static int step_many(const lpmm_b200_step_tensor* const* tensors, int n, const f
   }
   if (rc == LPMM_B200_OK && !r1.empty())
     rc = lpmm_b200_rank1_multi_step(r1.data(), (int)r1.size(), qmap_m, qmap_v, beta1, beta2, lr, weight_decay, eps,
-                                    r1_step, r1_table, r1_bytes, user, arith, apx);
+                                    r1_step, user, arith, apx);
   if (rc == LPMM_B200_OK && !fm.empty())
     rc = lpmm_b200_factored_multi_step(fm.data(), (int)fm.size(), qmap_m, beta1, beta2, lr, weight_decay, eps, fm_step,
                                        fm_scratch, fm_bytes, user, apx);
