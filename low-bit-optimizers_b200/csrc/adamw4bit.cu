@@ -459,7 +459,9 @@ static bool fast_math_ok(const lpmm_b200_hyper& h) {
   if (!(h.beta1 >= 0.0f && h.beta1 < 1.0f && h.beta2 >= 0.0f && h.beta2 < 1.0f && h.step >= 1.0f)) return false;
   const double dmin = (double)h.eps * (1.0 - (double)h.beta1);
   const double c2s_min = sqrt(1.0 - (double)h.beta2);
-  return dmin >= 0x1p-50 && h.eps <= 0x1p30f && c2s_min >= 0x1p-20;
+  // eps * c2s >= 2^-37: the square root of a denormal second moment (below 2^-63, where the short sequence is far
+  // off) divided by c2s stays under half a unit in the last place of eps, so the denominator is eps either way
+  return dmin >= 0x1p-50 && h.eps <= 0x1p30f && c2s_min >= 0x1p-20 && (double)h.eps * c2s_min >= 0x1p-37;
 }
 // The tolerance-mode parameter update folds 1 / -lr into its constants.
 static bool approx_math_ok(const lpmm_b200_hyper& h) {

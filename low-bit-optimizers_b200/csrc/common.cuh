@@ -183,8 +183,9 @@ __device__ __forceinline__ float udiv(float x, float d, float r) {
 
 // ---------------------------------------------------------------------------------------------
 // Short sequences for sqrt and division, each equal to the IEEE result on its stated domain.
-// sqrt_rn_fast: every v >= 2^-102 and v == 0 (exhaustively checked against sqrt.rn.f32); below
-//   2^-102 the residual underflows and the last bit may differ.
+// sqrt_rn_fast: every v >= 2^-102 and v == 0 (exhaustively checked against sqrt.rn.f32); in [2^-126, 2^-102)
+//   the residual underflows and the last bit may differ; a denormal v gives v * 2^63 (at most 2^-63, like the
+//   true root).  The hosts select it only when both cases vanish against eps or change it by a last bit.
 // div_rn_fast: 2^-60 <= d <= 2^60, 2^-60 <= |m| <= 2^30 or m == 0 (2.4e10 random and adversarial
 //   pairs against div.rn.f32); a denormal quotient may differ in the last bit.
 // ---------------------------------------------------------------------------------------------

@@ -159,7 +159,9 @@ static inline UConsts make_consts(double beta1, double beta2, double lr, double 
   c.inv_bc2s = (float)(1.0 / sqrt(bc2));  // torch divides by a host scalar as x * float(1.0 / s)
   c.eps = (float)eps;
   c.alpha = (float)(-step_size);
-  c.fast = (eps >= 0x1p-40 && eps <= 0x1p30 && bc2 >= 0x1p-40);
+  // eps * sqrt(bc2) >= 2^-37: the square root of a denormal second moment (below 2^-63, where the short sequence is
+  // far off) times 1 / sqrt(bc2) stays under half a unit in the last place of eps: the denominator is eps either way
+  c.fast = (eps >= 0x1p-40 && eps <= 0x1p30 && bc2 >= 0x1p-40 && eps * sqrt(bc2) >= 0x1p-37);
   // fused-kernel flavour: everything a float, as the reference's binding passes it
   c.f_beta1 = (float)beta1;
   c.f_beta2 = (float)beta2;
@@ -173,7 +175,8 @@ static inline UConsts make_consts(double beta1, double beta2, double lr, double 
   // the short sequences need the denominator, at least eps * (1 - beta1), inside [2^-60, 2^60]
   c.f_fast = (c.f_beta1 >= 0.0f && c.f_beta1 < 1.0f && c.f_beta2 >= 0.0f && c.f_beta2 < 1.0f && c.f_step >= 1.0f &&
               (double)c.f_eps * (1.0 - (double)c.f_beta1) >= 0x1p-50 && c.f_eps <= 0x1p30f &&
-              sqrt(1.0 - (double)c.f_beta2) >= 0x1p-20);
+              sqrt(1.0 - (double)c.f_beta2) >= 0x1p-20 &&
+              (double)c.f_eps * sqrt(1.0 - (double)c.f_beta2) >= 0x1p-37);
   return c;
 }
 

@@ -94,6 +94,45 @@ def test_fused_matches_reference_kernels(qmaps, case):
         assert_same(p_my, st_my, p_ref, st_ref, f"{name} step {s}")
 
 
+@pytest.mark.parametrize("eps", [1e-8, 1e-13])
+def test_second_moments_below_the_domain_of_the_short_square_root(qmaps, eps):
+    """Gradients of 1e-22 ... 1e-15 with no history: the second moments lie in (0, 2^-102), where the short square-root
+    sequence is not the IEEE one (last bit in [2^-126, 2^-102); far off for denormals, which are below 2^-63 either
+    way).  With eps = 1e-8 the short sequences are selected: a denormal's root vanishes against eps by construction of
+    the host's selection, and a last-bit difference of the root can move the denominator only when the sum lands
+    within 2^-19 of a rounding boundary -- so codes and scales are identical and at most a handful of the 2^20
+    parameters may differ, by one unit in the last place.  With eps = 1e-13 the host selects the IEEE instantiation and
+    everything is identical."""
+    ref = load_reference_extension("fused_adamw")
+    if ref is None:
+        pytest.skip("oracle/_ref was not built")
+    N = _lib()
+    qm, qv, _ = device_qmaps(qmaps)
+    n = 1 << 20
+    h = dict(HYPER, eps=eps)
+    torch.manual_seed(5)
+    p_ref = torch.randn(n, device=device()) * 0.02
+    p_my = p_ref.clone()
+    st_ref, st_my = fused_state(n), fused_state(n)
+    worst = 0
+    for s in range(1, 4):
+        gen = torch.Generator(device=device())
+        gen.manual_seed(900 + s)
+        mag = torch.pow(10.0, -22.0 + 7.0 * torch.rand(n, generator=gen, device=device()))
+        sign = torch.where(torch.rand(n, generator=gen, device=device()) < 0.5, -1.0, 1.0)
+        g = (mag * sign).contiguous()
+        mine_step(N, p_my, g, st_my, qm, qv, s, h)
+        ref_step(ref, p_ref, g, st_ref, qm, qv, s, h)
+        torch.cuda.synchronize()
+        for k in range(4):
+            assert torch.equal(st_my[k].view(torch.uint8).view(-1), st_ref[k].view(torch.uint8).view(-1)), f"step {s}: state {k}"
+        diff = (p_my.view(torch.int32) - p_ref.view(torch.int32)).abs()
+        assert int(diff.max()) <= 1, f"step {s}: a parameter differs by more than one unit in the last place"
+        worst = max(worst, int((diff != 0).sum()))
+        p_my.copy_(p_ref)  # keep the two runs on the same trajectory
+    assert worst <= (8 if eps == 1e-8 else 0), f"{worst} parameters differ"
+
+
 def test_fused_nonlinear_second_moment_map(qmaps):
     """A second-moment map other than the linear one takes the table path instead of the closed form."""
     ref = load_reference_extension("fused_adamw")
