@@ -532,6 +532,61 @@ class ZeroAdamW(torch.optim.Optimizer):
         eng._gather()
         return loss
 
+    @torch.no_grad()
+    def step_from_host(self, host_grads, chunk_bytes=256 << 20):
+        """One step whose (already reduced) gradients arrive from host memory: ``host_grads`` holds one CPU tensor per
+        parameter (pinned, for the copies to be asynchronous), in the order of ``param_groups``.  Only this rank's
+        slices are copied into ``p.grad`` (allocated here if missing; the rest of a ``p.grad`` is left as it is), on a
+        copy stream, and every ``chunk_bytes`` that have landed are followed by a launch over just those groups, so
+        update and peer stores overlap the remaining copies.  Results are those of ``step()`` on the same gradients."""
+        eng = self.engine
+        host = list(host_grads)
+        if len(host) != len(self._plist):
+            raise ValueError(f"expected {len(self._plist)} host gradients, got {len(host)}")
+        grads = []
+        for p, h in zip(self._plist, host):
+            if h is None:
+                raise RuntimeError("ZeroAdamW needs a gradient for every parameter")
+            if h.numel() != p.numel() or h.dtype != p.dtype:
+                raise RuntimeError("a host gradient must have its parameter's size and dtype")
+            if p.grad is None:
+                p.grad = torch.empty_like(p, memory_format=torch.contiguous_format)
+            grads.append(p.grad)
+        eng.use_full_grads(grads)
+        owner = [gi for gi, g in enumerate(self.param_groups) for _ in g["params"]]
+        pieces = owned_pieces(eng.numels, eng.gstart, eng.lo, eng.hi)
+        cuda = eng.device.type == "cuda"
+        eng.step_count += 1
+        eng._pre_step_barrier()
+        if cuda:
+            main = torch.cuda.current_stream(eng.device)
+            if getattr(eng, "_copy_stream", None) is None:
+                eng._copy_stream = torch.cuda.Stream(device=eng.device)
+            cs = eng._copy_stream
+            cs.wait_stream(main)  # launches already enqueued may still read the gradients
+        run_lo, run_hi, pending = None, None, 0
+        for k, (i, a, b) in enumerate(pieces):
+            e0, e1 = a * GROUP, min(b * GROUP, eng.numels[i])
+            dst, src = grads[i].view(-1)[e0:e1], host[i].view(-1)[e0:e1]
+            if cuda:
+                with torch.cuda.stream(cs):
+                    dst.copy_(src, non_blocking=True)
+            else:
+                dst.copy_(src)
+            if run_lo is None:
+                run_lo = eng.gstart[i] + a
+            run_hi = eng.gstart[i] + b
+            pending += (e1 - e0) * eng.esize
+            last = k + 1 == len(pieces)
+            if last or pending >= chunk_bytes or owner[pieces[k + 1][0]] != owner[i]:  # a launch stays inside one group
+                if cuda:
+                    ev = torch.cuda.Event()
+                    ev.record(cs)
+                    main.wait_event(ev)
+                eng._update(run_lo, run_hi, hyper=self.param_groups[owner[i]])
+                run_lo, pending = None, 0
+        eng._gather()
+
     def state_dict(self):
         """Collective.  The unsharded optimizer's ``state_dict()``: every rank returns the full state."""
         eng = self.engine

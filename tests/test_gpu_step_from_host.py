@@ -90,3 +90,22 @@ def test_zero1_engine_step_from_host_equals_copy_then_step(dtype, chunk):
         assert torch.equal(getattr(za, name).view(torch.uint8), getattr(zb, name).view(torch.uint8)), name
     with pytest.raises(RuntimeError):
         za.step_from_host(host[:-1])
+
+
+@pytest.mark.parametrize("chunk", [1 << 12, 256 << 20])
+def test_zero_wrapper_step_from_host_equals_step(chunk):
+    """``lpmm.optim.ZeroAdamW.step_from_host`` on one rank, two parameter groups (a launch never spans two groups)."""
+    import lpmm
+    kw = dict(lr=1e-3, betas=(0.9, 0.999), eps=1e-8)
+    groups = lambda ps: [dict(params=ps[:3], weight_decay=0.01), dict(params=ps[3:], weight_decay=0.1, lr=2e-3)]
+    pa, pb = _model(), _model()
+    za, zb = lpmm.optim.ZeroAdamW(groups(pa), **kw), lpmm.optim.ZeroAdamW(groups(pb), **kw)
+    for s in range(1, 5):
+        hg = _host_grads(s)
+        za.step_from_host(hg, chunk_bytes=chunk)
+        for p, h in zip(pb, hg):
+            p.grad = h.to(device())
+        zb.step()
+    _same(pa, pb, za, zb)
+    with pytest.raises(ValueError):
+        za.step_from_host(hg[:-1])

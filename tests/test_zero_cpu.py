@@ -230,9 +230,11 @@ def test_sharded_state_gathers_to_the_unsharded_layout_and_reloads(golden_dir, t
 
 
 # ---- the optimizer wrapper: parameters adopted into the flat buffer, parameter groups, state_dict ------------------
-def _wrapper_run(qm, qv, steps=3, resume_from=None):
+def _wrapper_run(qm, qv, steps=3, resume_from=None, from_host=False):
     """A small model stepped by ``lpmm.optim.ZeroAdamW`` (engine = the C oracle): two parameter groups with different
-    weight decay, the learning rate of the second halved at step 2.  Returns (optimizer, parameters)."""
+    weight decay, the learning rate of the second halved at step 2.  ``from_host``: the gradients are handed to
+    ``step_from_host`` (tiny chunks: several launches per parameter group) instead of being put into ``p.grad``.
+    Returns (optimizer, parameters)."""
     import lpmm
     torch.manual_seed(0)
     params = [torch.nn.Parameter(torch.randn(s) * 0.02) for s in SHAPES]
@@ -247,6 +249,9 @@ def _wrapper_run(qm, qv, steps=3, resume_from=None):
     for step in range(first, steps + 1):
         if step == 2:
             opt.param_groups[1]["lr"] = 1e-3
+        if from_host:
+            opt.step_from_host(_grads(step), chunk_bytes=4096)
+            continue
         for p, g in zip(params, _grads(step)):
             p.grad = g
         opt.step()
@@ -260,8 +265,9 @@ def _wrapper_worker(rank, world, port, golden_dir, out_dir):
     opt, params = _wrapper_run(z["m"], z["v"], steps=2)
     sd = opt.state_dict()                                   # collective
     pvals = [p.detach().clone() for p in params]
-    # resume in a fresh wrapper from the gathered dict and take step 3; and take step 3 directly
-    opt2, params2 = _wrapper_run(z["m"], z["v"], steps=3, resume_from=(sd, pvals, 3))
+    # resume in a fresh wrapper from the gathered dict and take step 3 (gradients through step_from_host); and take
+    # step 3 directly
+    opt2, params2 = _wrapper_run(z["m"], z["v"], steps=3, resume_from=(sd, pvals, 3), from_host=True)
     for p, g in zip(params, _grads(3)):
         p.grad = g
     opt.step()

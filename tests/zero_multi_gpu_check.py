@@ -116,6 +116,20 @@ for step in range(1, 4):
     sa.step_from_host(host, chunk_bytes=1 << 16)
 torch.cuda.synchronize(); dist.barrier()
 same5 = bool(torch.equal(sa.flat.view(torch.int32), sb.flat.view(torch.int32)))
+# the same through the optimizer wrapper: every rank copies only its own slices of the host gradients
+wc = [torch.nn.Parameter(p.detach().clone()) for p in wa]
+wd = [torch.nn.Parameter(p.detach().clone()) for p in wa]
+zc = lpmm.optim.ZeroAdamW(grp(wc), lr=1e-3, gather="fused")
+zd = lpmm.optim.ZeroAdamW(grp(wd), lr=1e-3, gather="nccl")
+for step in range(1, 4):
+    hg = []
+    for i, x in enumerate(wc):
+        g = torch.Generator(device=dev); g.manual_seed(step * 100003 + 17 * i)
+        hg.append((torch.randn(x.shape, generator=g, device=dev) * 1e-3).cpu().pin_memory())
+    for y, h in zip(wd, hg): y.grad = h.to(dev)
+    zc.step_from_host(hg, chunk_bytes=1 << 16); zd.step()
+torch.cuda.synchronize(); dist.barrier()
+same5 = same5 and all(bool(torch.equal(x.detach().view(torch.int32), y.detach().view(torch.int32))) for x, y in zip(wc, wd))
 ok = ok and same3 and same4 and same5
 print(f"rank {rank}: {'OK' if ok else 'MISMATCH'} (fused == nccl: {same}, in-kernel gradient reduction == summed gradients: {same2}, "
       f"16-bit sharded == unsharded: {same3}, optimizer wrapper == unsharded optimizer: {same4}, "
