@@ -15,8 +15,10 @@ own arm      one step = ``lpmm.optim.AdamW(fused=True).step()`` over the whole l
              inside the timed region; ``copy_then_step_ms`` is the plain sequence timed beside it.  ``tolerance_mode``: the same
              step with ``exact_params=False`` (codes and scales bit-identical, parameters within 1e-6).
              With N > 1 the list is ZeRO-1 sharded by whole 128-element groups (``lpmm.zero``); the updated
-             parameters reach the other ranks by NVLink stores inside the update kernel (``--gather fused``,
-             the default) or by an NCCL all-gather after it (``--gather nccl``).  The whole step is timed
+             parameters reach the other ranks by copy-engine peer copies of every updated 1 GB range while the
+             next range is updated (``--gather copy``, the default: the fastest of the three here), by NVLink
+             stores inside the update kernel (``--gather fused``, timed beside it as ``gather_fused``) or by an
+             NCCL all-gather after the update (``--gather nccl``).  The whole step is timed
              (``"scaling": "strong"``: the list is fixed, the ranks share it); extra keys give the check that
              the sharded step equals the unsharded one (``zero1_check``), the update alone per GPU
              (``local_update``), the same list with bf16 parameters (``params_bf16``) and the
@@ -464,9 +466,13 @@ def run_own(args):
         else:
             student_t_(opt.grad_shard.view(-1), 100003 + rank, rows_outliers=False)
 
+        from lpmm.zero import COPY_CHUNK_BYTES
+        shard_bytes = 4 * (opt.hi - opt.lo) * 128
+        ranges_per_step = -(-shard_bytes // COPY_CHUNK_BYTES) if args.gather == "copy" else 1
+
         def step():
             opt.step()
-            launches[0] += (len(shapes) + 399) // 400
+            launches[0] += ranges_per_step * ((len(shapes) + 399) // 400)
 
     def barrier():
         if world > 1:
@@ -506,7 +512,7 @@ def run_own(args):
         k_ms = sum(ks) / len(ks)
         k_bytes = alg_bytes
     else:
-        k_ms, k_bytes = opt.time_update_only(max(3, min(args.steps, 10)))
+        k_ms, k_bytes = opt.time_update_only(max(3, min(args.steps, 10)), peers=args.gather != "copy")
         extra.update(opt.breakdown(max(3, min(args.steps, 10))))
     peak, peak_kind = measured_peak()
     if world > 1:
@@ -544,6 +550,19 @@ def run_own(args):
                          "peak_kind": f"of {peak_kind}", "launch_ms": t_ms, "launch_ms_min_max": [min(tks), max(tks)],
                          "frac_of_nominal_8000": t_ach / 8000.0}}
         roofline["frac_of_nominal_8000"] = achieved / 8000.0
+    if world > 1 and args.gather == "copy":
+        # update kernel on ranges of the shard, each range then copied to every peer by the copy engines while the next
+        # is updated: the step is bound by the bytes a rank must receive over NVLink; the kernel itself is `local_update`
+        link_bytes = 4.0 * opt.shard_groups * 128 * (world - 1)
+        link_peak = 770.0
+        t_hbm, t_link = k_bytes / (peak * 1e9), link_bytes / (link_peak * 1e9)
+        roofline = {"bound": "nvlink" if t_link >= t_hbm else "hbm", "achieved": link_bytes / (ms_per_step * 1e-3) / 1e9,
+                    "peak": link_peak, "unit": "GB/s", "frac": max(t_hbm, t_link) / (ms_per_step * 1e-3), "traffic": None,
+                    "peak_kind": "measured peer-copy rate of this pool (770 GB/s per direction); HBM side of measured",
+                    "kernel": "adamw4bit_multi_kernel on 1 GB ranges + copy-engine peer copies of each finished range",
+                    "launch_ms": k_ms, "step_ms": ms_per_step, "algorithmic_bytes_per_launch": k_bytes,
+                    "nvlink_bytes_sent_per_rank_per_step": link_bytes,
+                    "nvlink_bytes_received_per_rank_per_step": link_bytes, "target_ms": max(t_hbm, t_link) * 1e3}
     if world > 1 and args.gather == "fused":
         # fused update + peer stores: the target time is the slower of HBM and NVLink; this kernel is NVLink-bound
         link_bytes = 4.0 * opt.shard_groups * 128 * (world - 1)      # sent (and received) per rank per launch
@@ -655,6 +674,11 @@ def run_own(args):
             extra["params_bf16"] = sharded_step_line(shapes, dev, args.gather, torch.bfloat16, n_x, world)
         except Exception as e:  # an extra must not cost the headline line
             extra["params_bf16"] = {"error": repr(e)[:200]}
+        other = "fused" if args.gather == "copy" else "copy"
+        try:  # the same list with the other in-process exchange (stores inside the update kernel / copy engines)
+            extra[f"gather_{other}"] = sharded_step_line(shapes, dev, other, torch.float32, n_x, world)
+        except Exception as e:
+            extra[f"gather_{other}"] = {"error": repr(e)[:200]}
         if args.model == "7b":
             try:
                 s13 = llama7b_shapes(layers=40, hidden=5120, inter=13824)
@@ -680,7 +704,9 @@ def run_own(args):
                        "params_4bit": nq, "params_fp32_state": nf, "layers": n_layers,
                        "parallelism": "single GPU" if world == 1 else (
                            f"ZeRO-1 over {world} GPUs, group-aligned shards, fp32 params reach the peers by "
-                           + ("NVLink stores inside the update kernel" if args.gather == "fused" else "an NCCL all-gather after the update")
+                           + {"fused": "NVLink stores inside the update kernel",
+                              "copy": "copy-engine peer copies of each updated 1 GB range, overlapped with the update of the next",
+                              "nccl": "an NCCL all-gather after the update"}[args.gather]
                            + ("; gradients of all ranks summed by NVLink loads inside the same kernel" if args.reduce_grads else "")),
                        "l2": "inputs (>= 90 GB touched per step) exceed the 126 MB L2; no explicit flush"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": n_launch, "roofline": roofline, "cpu_baseline": cpu,
@@ -706,9 +732,12 @@ def main():
     ap.add_argument("--reduce-grads", action="store_true",
                     help="N > 1, --gather fused: every rank holds full local gradients and the update kernel also sums "
                          "them over the ranks (reduce-scatter inside the step); no e2e figure in this mode")
-    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
-                    help="N > 1: parameters reach the peers by stores inside the update kernel, or by an NCCL all-gather after it")
+    ap.add_argument("--gather", default="copy", choices=["copy", "fused", "nccl"],
+                    help="N > 1: parameters reach the peers by copy-engine peer copies of every updated range (overlapped "
+                         "with the update of the next), by stores inside the update kernel, or by an NCCL all-gather after it")
     args = ap.parse_args()
+    if args.reduce_grads:
+        args.gather = "fused"  # the gradient reduction lives in the update kernel
     if args.impl == "reference":
         run_reference(args)
     else:

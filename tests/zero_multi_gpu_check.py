@@ -1,6 +1,6 @@
 """Run under torch.distributed.run on 2 or more GPUs (tests/test_gpu_zero_multi.py does): the ZeRO-1 step
-with parameters pushed to the peers by stores inside the update kernel equals the ZeRO-1 step followed by an
-NCCL all-gather, bit for bit, and every rank ends with the same parameter buffer; and the step that also
+with parameters pushed to the peers by stores inside the update kernel, or by copy-engine peer copies of the updated
+ranges, equals the ZeRO-1 step followed by an NCCL all-gather, bit for bit, and every rank ends with the same parameter buffer; and the step that also
 reduces the gradients of all ranks inside the update kernel equals the step on gradients summed beforehand;
 16-bit parameters, the optimizer wrapper and the step fed from pinned host memory likewise.
 Prints one OK line per rank."""
@@ -13,7 +13,7 @@ torch.cuda.set_device(lr_); dev = torch.device("cuda", lr_)
 dist.init_process_group("nccl", device_id=dev)
 shapes = [(300, 128), (4096,), (5000,), (77, 129), (128,), (64, 64, 3), (2048, 1024)]
 H = dict(lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01)
-opts = {g: Zero1FusedAdamW(shapes, dev, gather=g, **H) for g in ("nccl", "fused")}
+opts = {g: Zero1FusedAdamW(shapes, dev, gather=g, **H) for g in ("nccl", "fused", "copy")}
 for o in opts.values(): o.init_params_normal_(0.02, seed=0)
 for step in range(1, 5):
     grads = []
@@ -25,6 +25,7 @@ for step in range(1, 5):
 torch.cuda.synchronize(); dist.barrier()
 a, b = opts["nccl"].flat, opts["fused"].flat
 same = bool(torch.equal(a.view(torch.int32), b.view(torch.int32)))
+same = same and bool(torch.equal(a.view(torch.int32), opts["copy"].flat.view(torch.int32)))  # copy-engine peer copies
 chk = torch.tensor([float(b.double().sum())], device=dev, dtype=torch.float64); lst = [torch.zeros_like(chk) for _ in range(world)]
 dist.all_gather(lst, chk)
 ok = same and all(float(x) == float(lst[0]) for x in lst)
@@ -60,7 +61,7 @@ import lpmm
 from lpmm import _kernels as K
 same3 = True
 for dt in (torch.bfloat16, torch.float16):
-    zs = {g: Zero1FusedAdamW(shapes, dev, gather=g, dtype=dt, **H) for g in ("nccl", "fused")}
+    zs = {g: Zero1FusedAdamW(shapes, dev, gather=g, dtype=dt, **H) for g in ("nccl", "fused", "copy")}
     for o in zs.values(): o.init_params_normal_(0.02, seed=0)
     torch.manual_seed(0)
     plain = [torch.nn.Parameter(v.detach().clone()) for v in zs["nccl"].params]
@@ -76,7 +77,7 @@ for dt in (torch.bfloat16, torch.float16):
         po.step()
     torch.cuda.synchronize(); dist.barrier()
     a, b = zs["nccl"].flat.view(torch.int16), zs["fused"].flat.view(torch.int16)
-    same3 = same3 and bool(torch.equal(a, b))
+    same3 = same3 and bool(torch.equal(a, b)) and bool(torch.equal(a, zs["copy"].flat.view(torch.int16)))
     for v, p in zip(zs["fused"].params, plain):
         same3 = same3 and bool(torch.equal(v.view(-1).view(torch.int16), p.detach().view(-1).view(torch.int16)))
     del zs
@@ -119,7 +120,7 @@ same5 = bool(torch.equal(sa.flat.view(torch.int32), sb.flat.view(torch.int32)))
 # the same through the optimizer wrapper: every rank copies only its own slices of the host gradients
 wc = [torch.nn.Parameter(p.detach().clone()) for p in wa]
 wd = [torch.nn.Parameter(p.detach().clone()) for p in wa]
-zc = lpmm.optim.ZeroAdamW(grp(wc), lr=1e-3, gather="fused")
+zc = lpmm.optim.ZeroAdamW(grp(wc), lr=1e-3, gather="copy")
 zd = lpmm.optim.ZeroAdamW(grp(wd), lr=1e-3, gather="nccl")
 for step in range(1, 4):
     hg = []
