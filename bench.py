@@ -468,7 +468,8 @@ def run_own(args):
 
         from lpmm.zero import COPY_CHUNK_BYTES
         shard_bytes = 4 * (opt.hi - opt.lo) * 128
-        ranges_per_step = -(-shard_bytes // COPY_CHUNK_BYTES) if args.gather == "copy" else 1
+        # gather="copy": a first range of an eighth of COPY_CHUNK_BYTES, then full ones
+        ranges_per_step = (1 + -(-max(shard_bytes - COPY_CHUNK_BYTES // 8, 0) // COPY_CHUNK_BYTES)) if args.gather == "copy" else 1
 
         def step():
             opt.step()

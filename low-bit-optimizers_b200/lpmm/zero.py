@@ -312,8 +312,11 @@ class Zero1FusedAdamW:
         if self.gather != "copy":
             return self._update(lo, hi, hyper=hyper)
         per = max(1, COPY_CHUNK_BYTES // (GROUP * self.esize))
-        for a in range(lo, hi, per):
-            self._update(a, min(a + per, hi), hyper=hyper)
+        a, n = lo, max(1, per // 8)  # a short first range: the copy engines start early
+        while a < hi:
+            b = min(a + n, hi)
+            self._update(a, b, hyper=hyper)
+            a, n = b, per
 
     def _pre_step_barrier(self):
         """gather="fused": the launch stores into every peer's parameter buffer, so no rank may start it while another
@@ -511,11 +514,11 @@ class ZeroAdamW(torch.optim.Optimizer):
 
     The model's parameters are adopted into one flat buffer (``p.data`` becomes a view that starts on a
     128-element group boundary; with ``gather="fused"`` the buffer lives in symmetric memory and the update kernel
-    writes every rank's copy).  Every rank must construct it from identical parameters (a replicated model) and must
+    writes every rank's copy, with ``gather="copy"`` the copy engines do while the next range is updated).  Every rank must construct it from identical parameters (a replicated model) and must
     call ``step()`` with identical, already reduced gradients in ``p.grad`` (what data-parallel backward with an
     all-reduce leaves): each rank reads only its own groups out of them, nothing is copied.  Parameter groups keep
     their own ``lr`` / ``betas`` / ``eps`` / ``weight_decay``, read at every step (schedulers work), one launch per
-    group.  ``state_dict()`` gathers the shards into exactly what the unsharded optimizer's ``state_dict()`` holds
+    group (per 1 GB range of a group with ``gather="copy"``).  ``state_dict()`` gathers the shards into exactly what the unsharded optimizer's ``state_dict()`` holds
     (the reference's fused layout, lpmm/optim/adamw.py:508-523: ``int8[(numel + 1) // 2]`` codes, fp32 group
     maxima in ``overhead['max1']``, fp32 moments for tensors of at most 4096 elements) and ``load_state_dict`` takes
     such a dict, so checkpoints move freely between the two.  Both are collective calls.
