@@ -306,7 +306,7 @@ extern "C" int lpmm_b200_adamw4bit_unfused_multi_tensor(const lpmm_b200_tensor* 
 
 // The same launch with the tolerance-mode parameter update (flags & LPMM_B200_FLAG_PARAMS_WITHIN_TOLERANCE); internal
 // to the library, reached through lpmm_b200_adamw4bit_unfused_step_many_flags.
-extern "C" int lpmm_b200_unfused_multi_tensor_apx(const lpmm_b200_tensor* ts, int n, const float* qmap_m,
+LPMM_INTERNAL int lpmm_b200_unfused_multi_tensor_apx(const lpmm_b200_tensor* ts, int n, const float* qmap_m,
                                                   const float* qmap_v, double beta1, double beta2, double lr,
                                                   double weight_decay, double eps, double step, void* stream) {
   return um_step(ts, n, qmap_m, qmap_v, beta1, beta2, lr, weight_decay, eps, step, 0, -1, stream, 0, 1);
@@ -314,7 +314,7 @@ extern "C" int lpmm_b200_unfused_multi_tensor_apx(const lpmm_b200_tensor* ts, in
 
 // The same launch with the fused kernel's arithmetic on these (padded) states; internal to the library,
 // reached through lpmm_b200_adamw4bit_fused_arith_step_many.
-extern "C" int lpmm_b200_fused_arith_multi_tensor(const lpmm_b200_tensor* ts, int n, const float* qmap_m,
+LPMM_INTERNAL int lpmm_b200_fused_arith_multi_tensor(const lpmm_b200_tensor* ts, int n, const float* qmap_m,
                                                   const float* qmap_v, double beta1, double beta2, double lr,
                                                   double weight_decay, double eps, double step, void* stream) {
   return um_step(ts, n, qmap_m, qmap_v, beta1, beta2, lr, weight_decay, eps, step, 0, -1, stream, 1, 0);

@@ -7,6 +7,9 @@
 
 #include "lpmm_b200.h"
 
+// Functions shared between the library's translation units but not part of its C ABI: C linkage, not exported.
+#define LPMM_INTERNAL extern "C" __attribute__((visibility("hidden")))
+
 namespace lpmm_b200 {
 
 // ---------------------------------------------------------------------------------------------

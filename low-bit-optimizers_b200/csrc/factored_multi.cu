@@ -465,7 +465,7 @@ static inline int64_t f_align(int64_t x) { return (x + 63) & ~(int64_t)63; }  //
 using namespace lpmm_b200;
 
 // Host side; internal to the library (called by lpmm_b200_adamw4bit_unfused_step_many).
-extern "C" int lpmm_b200_factored_multi_ok(const lpmm_b200_step_tensor* t) {
+LPMM_INTERNAL int lpmm_b200_factored_multi_ok(const lpmm_b200_step_tensor* t) {
   if (!t || t->first || t->numel <= 0 || t->ndim != 2 || t->v_mode != LPMM_B200_STATE_FACTORED) return 0;
   if (t->m_mode != LPMM_B200_STATE_FP32 && t->m_mode != LPMM_B200_STATE_GROUP4) return 0;
   if (t->m_mode == LPMM_B200_STATE_GROUP4) {
@@ -481,7 +481,7 @@ extern "C" int lpmm_b200_factored_multi_ok(const lpmm_b200_step_tensor* t) {
 
 // Bytes of device scratch the list needs: one row-mean slot per tensor and the partial sums (column partials for
 // tiles of at least F_MIN_ROWS rows, row partials per 256-column segment).
-extern "C" int64_t lpmm_b200_factored_multi_scratch_bytes(const lpmm_b200_step_tensor* const* ts, int n) {
+LPMM_INTERNAL int64_t lpmm_b200_factored_multi_scratch_bytes(const lpmm_b200_step_tensor* const* ts, int n) {
   int64_t floats = 0;
   for (int i = 0; i < n; ++i) {
     const int64_t R = ts[i]->shape[0], C = ts[i]->shape[1];
@@ -624,7 +624,7 @@ static int f_window(const lpmm_b200_step_tensor* const* ts, int n, const float* 
   return LPMM_B200_OK;
 }
 
-extern "C" int lpmm_b200_factored_multi_step(const lpmm_b200_step_tensor* const* ts, int n, const float* qmap_m,
+LPMM_INTERNAL int lpmm_b200_factored_multi_step(const lpmm_b200_step_tensor* const* ts, int n, const float* qmap_m,
                                              double beta1, double beta2, double lr, double weight_decay, double eps,
                                              double step, void* scratch, int64_t scratch_bytes, void* stream, int apx) {
   if (n <= 0) return LPMM_B200_OK;

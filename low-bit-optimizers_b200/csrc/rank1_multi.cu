@@ -576,7 +576,7 @@ using namespace lpmm_b200;
 // Host side.  `ts`: n tensors that all satisfy lpmm_b200_rank1_multi_ok.  Not part of the public header: called
 // by lpmm_b200_adamw4bit_unfused_step_many.  The descriptors travel in the launch parameters: no scratch is needed.
 
-extern "C" int lpmm_b200_rank1_multi_ok(const lpmm_b200_step_tensor* t) {
+LPMM_INTERNAL int lpmm_b200_rank1_multi_ok(const lpmm_b200_step_tensor* t) {
   if (!t || t->first || t->numel <= 0 || t->ndim != 2) return 0;
   if (t->m_mode != LPMM_B200_STATE_GROUP4 || t->v_mode != LPMM_B200_STATE_RANK1_4) return 0;
   if ((t->m_bits != 0 && t->m_bits != 4) || (t->v_bits != 0 && t->v_bits != 4)) return 0;
@@ -727,7 +727,7 @@ static int r1_window(const lpmm_b200_step_tensor* const* ts, int n, const float*
   return LPMM_B200_OK;
 }
 
-extern "C" int lpmm_b200_rank1_multi_step(const lpmm_b200_step_tensor* const* ts, int n, const float* qmap_m,
+LPMM_INTERNAL int lpmm_b200_rank1_multi_step(const lpmm_b200_step_tensor* const* ts, int n, const float* qmap_m,
                                           const float* qmap_v, double beta1, double beta2, double lr,
                                           double weight_decay, double eps, double step, void* stream, int arith,
                                           int apx) {

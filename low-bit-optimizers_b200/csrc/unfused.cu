@@ -1585,25 +1585,25 @@ extern "C" int lpmm_b200_adamw4bit_fused_arith_step(const lpmm_b200_step_tensor*
 }
 
 // adamw_unfused_multi.cu: the shared launch with the fused kernel's arithmetic (internal to the library)
-extern "C" int lpmm_b200_fused_arith_multi_tensor(const lpmm_b200_tensor* ts, int n, const float* qmap_m,
+LPMM_INTERNAL int lpmm_b200_fused_arith_multi_tensor(const lpmm_b200_tensor* ts, int n, const float* qmap_m,
                                                   const float* qmap_v, double beta1, double beta2, double lr,
                                                   double weight_decay, double eps, double step, void* stream);
 // the shared launch of the torch-operation arithmetic with the tolerance-mode parameter update
-extern "C" int lpmm_b200_unfused_multi_tensor_apx(const lpmm_b200_tensor* ts, int n, const float* qmap_m,
+LPMM_INTERNAL int lpmm_b200_unfused_multi_tensor_apx(const lpmm_b200_tensor* ts, int n, const float* qmap_m,
                                                   const float* qmap_v, double beta1, double beta2, double lr,
                                                   double weight_decay, double eps, double step, void* stream);
 
 // rank1_multi.cu: all rank-1 matrices of a list in three launches (internal to the library)
-extern "C" int lpmm_b200_rank1_multi_ok(const lpmm_b200_step_tensor* t);
-extern "C" int lpmm_b200_rank1_multi_step(const lpmm_b200_step_tensor* const* ts, int n, const float* qmap_m,
+LPMM_INTERNAL int lpmm_b200_rank1_multi_ok(const lpmm_b200_step_tensor* t);
+LPMM_INTERNAL int lpmm_b200_rank1_multi_step(const lpmm_b200_step_tensor* const* ts, int n, const float* qmap_m,
                                           const float* qmap_v, double beta1, double beta2, double lr,
                                           double weight_decay, double eps, double step, void* stream, int arith,
                                           int apx);
 
 // factored_multi.cu: all factored matrices of a list in four launches (internal to the library)
-extern "C" int lpmm_b200_factored_multi_ok(const lpmm_b200_step_tensor* t);
-extern "C" int64_t lpmm_b200_factored_multi_scratch_bytes(const lpmm_b200_step_tensor* const* ts, int n);
-extern "C" int lpmm_b200_factored_multi_step(const lpmm_b200_step_tensor* const* ts, int n, const float* qmap_m,
+LPMM_INTERNAL int lpmm_b200_factored_multi_ok(const lpmm_b200_step_tensor* t);
+LPMM_INTERNAL int64_t lpmm_b200_factored_multi_scratch_bytes(const lpmm_b200_step_tensor* const* ts, int n);
+LPMM_INTERNAL int lpmm_b200_factored_multi_step(const lpmm_b200_step_tensor* const* ts, int n, const float* qmap_m,
                                              double beta1, double beta2, double lr, double weight_decay, double eps,
                                              double step, void* scratch, int64_t scratch_bytes, void* stream,
                                              int apx);

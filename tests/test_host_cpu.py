@@ -23,6 +23,13 @@ def test_library_exports_every_declared_symbol():
         assert hasattr(lib, name), f"{name} is declared in include/lpmm_b200.h but not exported"
     assert declared == set(N.SIGNATURES), "the ctypes table and the header disagree"
     assert N.lib.lpmm_b200_abi_version() == 3
+    # and nothing else under the library's prefix is exported: helpers shared between its translation units stay hidden
+    import shutil
+    import subprocess
+    if shutil.which("nm"):
+        out = subprocess.run(["nm", "-D", "--defined-only", N._LIB_PATH], capture_output=True, text=True).stdout
+        exported = set(re.findall(r" T (lpmm_b200_[a-z0-9_]+)", out))
+        assert exported == declared, f"exported but not declared: {sorted(exported - declared)}"
 
 
 def test_argument_validation_without_a_gpu():
