@@ -16,7 +16,7 @@ ranges of equal length S = ceil(G / world) and rank r
   by group and only a barrier follows; or -- ``gather="copy"`` -- the range is updated in pieces of 1 GB and the
   copy engines write every finished piece into the peers' buffers while the next piece is updated (on this
   hardware the copy engines move 770 GB/s per direction where stores from the SMs reach 660-690, so this is the
-  fastest of the three; measured 18.0 / 32.3 ms per step of the 7B list on 2 / 8 GPUs against 20.0 / 35.4).
+  fastest of the three; measured 18.2 / 31.7 ms per step of the 7B list on 2 / 8 GPUs against 20.0 / 35.4).
 
 With ``reduce_grads=True`` the gradient reduce-scatter moves into the launch as well: every rank keeps
 its full local gradients in a peer-mapped buffer and the update kernel sums, for each element of the
