@@ -15,7 +15,7 @@ own arm      one step = ``lpmm.optim.AdamW(fused=True).step()`` over the whole l
              inside the timed region; ``copy_then_step_ms`` is the plain sequence timed beside it.  ``tolerance_mode``: the same
              step with ``exact_params=False`` (codes and scales bit-identical, parameters within 1e-6).
              With N > 1 the list is ZeRO-1 sharded by whole 128-element groups (``lpmm.zero``); the updated
-             parameters reach the other ranks by copy-engine peer copies of every updated 1 GB range while the
+             parameters reach the other ranks by copy-engine peer copies of every updated 1-2 GB range while the
              next range is updated (``--gather copy``, the default: the fastest of the three here), by NVLink
              stores inside the update kernel (``--gather fused``, timed beside it as ``gather_fused``) or by an
              NCCL all-gather after the update (``--gather nccl``).  The whole step is timed
@@ -466,10 +466,10 @@ def run_own(args):
         else:
             student_t_(opt.grad_shard.view(-1), 100003 + rank, rows_outliers=False)
 
-        from lpmm.zero import COPY_CHUNK_BYTES
-        shard_bytes = 4 * (opt.hi - opt.lo) * 128
-        # gather="copy": a first range of an eighth of COPY_CHUNK_BYTES, then full ones
-        ranges_per_step = (1 + -(-max(shard_bytes - COPY_CHUNK_BYTES // 8, 0) // COPY_CHUNK_BYTES)) if args.gather == "copy" else 1
+        from lpmm.zero import copy_chunk_bytes
+        shard_bytes, chunk_bytes = 4 * (opt.hi - opt.lo) * 128, copy_chunk_bytes(world)
+        # gather="copy": a first range of an eighth of the chunk, then full ones
+        ranges_per_step = (1 + -(-max(shard_bytes - chunk_bytes // 8, 0) // chunk_bytes)) if args.gather == "copy" else 1
 
         def step():
             opt.step()
@@ -560,7 +560,7 @@ def run_own(args):
         roofline = {"bound": "nvlink" if t_link >= t_hbm else "hbm", "achieved": link_bytes / (ms_per_step * 1e-3) / 1e9,
                     "peak": link_peak, "unit": "GB/s", "frac": max(t_hbm, t_link) / (ms_per_step * 1e-3), "traffic": None,
                     "peak_kind": "measured peer-copy rate of this pool (770 GB/s per direction); HBM side of measured",
-                    "kernel": "adamw4bit_multi_kernel on 1 GB ranges + copy-engine peer copies of each finished range",
+                    "kernel": "adamw4bit_multi_kernel on 1-2 GB ranges + copy-engine peer copies of each finished range",
                     "launch_ms": k_ms, "step_ms": ms_per_step, "algorithmic_bytes_per_launch": k_bytes,
                     "nvlink_bytes_sent_per_rank_per_step": link_bytes,
                     "nvlink_bytes_received_per_rank_per_step": link_bytes, "target_ms": max(t_hbm, t_link) * 1e3}
@@ -706,7 +706,7 @@ def run_own(args):
                        "parallelism": "single GPU" if world == 1 else (
                            f"ZeRO-1 over {world} GPUs, group-aligned shards, fp32 params reach the peers by "
                            + {"fused": "NVLink stores inside the update kernel",
-                              "copy": "copy-engine peer copies of each updated 1 GB range, overlapped with the update of the next",
+                              "copy": "copy-engine peer copies of each updated 1-2 GB range, overlapped with the update of the next",
                               "nccl": "an NCCL all-gather after the update"}[args.gather]
                            + ("; gradients of all ranks summed by NVLink loads inside the same kernel" if args.reduce_grads else "")),
                        "l2": "inputs (>= 90 GB touched per step) exceed the 126 MB L2; no explicit flush"},

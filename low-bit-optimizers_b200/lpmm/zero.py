@@ -13,10 +13,10 @@ ranges of equal length S = ceil(G / world) and rank r
   flat parameter buffer after the launch (``gather="nccl"``), or -- ``gather="fused"`` -- the launch
   itself stores every updated parameter into all peers' buffers through peer-mapped symmetric
   memory (plain vectorised stores over NVLink, no multicast), so transfer and update overlap group
-  by group and only a barrier follows; or -- ``gather="copy"`` -- the range is updated in pieces of 1 GB and the
+  by group and only a barrier follows; or -- ``gather="copy"`` -- the range is updated in pieces of 1-2 GB and the
   copy engines write every finished piece into the peers' buffers while the next piece is updated (on this
   hardware the copy engines move 770 GB/s per direction where stores from the SMs reach 660-690, so this is the
-  fastest of the three; measured 18.2 / 31.7 ms per step of the 7B list on 2 / 8 GPUs against 20.0 / 35.4).
+  fastest of the three; measured 18.2 / 27.5 / 31.2 ms per step of the 7B list on 2 / 4 / 8 GPUs against 20.0 / 30.2 / 35.4).
 
 With ``reduce_grads=True`` the gradient reduce-scatter moves into the launch as well: every rank keeps
 its full local gradients in a peer-mapped buffer and the update kernel sums, for each element of the
@@ -35,8 +35,12 @@ GROUP = 128
 THRESHOLD = 4096
 
 
-# gather="copy": bytes of parameters per update launch / round of peer copies (large rounds keep the ranks in step)
-COPY_CHUNK_BYTES = 1 << 30
+def copy_chunk_bytes(world):
+    """gather="copy": bytes of parameters per update launch / round of peer copies.  Large rounds keep the ranks in
+    step (one sender per receiver at a time); with a single peer shorter rounds fill the pipeline sooner.  Measured on
+    the 7B list: 2 GPUs 18.2 / 18.7 / 19.8 ms with 1 / 2 / 4 GB, 4 GPUs 33.3 / 28.6 / 27.4 / 27.4 ms with 0.5 / 1 / 2 GB /
+    the whole shard."""
+    return (1 << 30) if world <= 2 else (2 << 30)
 
 
 def groups_of(numel):
@@ -307,11 +311,11 @@ class Zero1FusedAdamW:
                 peer[e0:e1].copy_(self.flat[e0:e1], non_blocking=True)
 
     def _update_in_chunks(self, lo, hi, hyper=None):
-        """``_update`` of ``[lo, hi)``; with gather="copy" in ranges of ``COPY_CHUNK_BYTES`` so that the copies of one
-        range run while the next is being updated."""
+        """``_update`` of ``[lo, hi)``; with gather="copy" in ranges of ``copy_chunk_bytes(world)`` so that the copies of
+        one range run while the next is being updated."""
         if self.gather != "copy":
             return self._update(lo, hi, hyper=hyper)
-        per = max(1, COPY_CHUNK_BYTES // (GROUP * self.esize))
+        per = max(1, copy_chunk_bytes(self.world) // (GROUP * self.esize))
         a, n = lo, max(1, per // 8)  # a short first range: the copy engines start early
         while a < hi:
             b = min(a + n, hi)
@@ -518,7 +522,7 @@ class ZeroAdamW(torch.optim.Optimizer):
     call ``step()`` with identical, already reduced gradients in ``p.grad`` (what data-parallel backward with an
     all-reduce leaves): each rank reads only its own groups out of them, nothing is copied.  Parameter groups keep
     their own ``lr`` / ``betas`` / ``eps`` / ``weight_decay``, read at every step (schedulers work), one launch per
-    group (per 1 GB range of a group with ``gather="copy"``).  ``state_dict()`` gathers the shards into exactly what the unsharded optimizer's ``state_dict()`` holds
+    group (per 1-2 GB range of a group with ``gather="copy"``).  ``state_dict()`` gathers the shards into exactly what the unsharded optimizer's ``state_dict()`` holds
     (the reference's fused layout, lpmm/optim/adamw.py:508-523: ``int8[(numel + 1) // 2]`` codes, fp32 group
     maxima in ``overhead['max1']``, fp32 moments for tensors of at most 4096 elements) and ``load_state_dict`` takes
     such a dict, so checkpoints move freely between the two.  Both are collective calls.
