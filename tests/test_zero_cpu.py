@@ -340,3 +340,34 @@ def test_step_from_host_without_a_gpu_is_copy_then_step(golden_dir):
     assert np.array_equal(a.flat.numpy().view(np.int32), b.flat.numpy().view(np.int32))
     with pytest.raises(RuntimeError):
         a.step_from_host(host[:-1])
+
+
+def test_copy_exchange_cuts_the_owned_range_into_a_short_first_range_and_full_ones():
+    """gather="copy": ``_update_in_chunks`` must cover ``[lo, hi)`` exactly once, in order, with a first range of an
+    eighth of ``copy_chunk_bytes(world)`` (the copy engines start early) and full ranges after it; other modes take
+    one launch.  The launches are recorded instead of run."""
+    from lpmm import zero as Z
+
+    class Recorder(Z.Zero1FusedAdamW):
+        def __init__(self):  # no buffers: only the fields the chunking reads
+            self.calls, self.esize = [], 4
+
+        def _update(self, lo, hi, hyper=None, peers=True):
+            self.calls.append((lo, hi))
+
+    assert Z.copy_chunk_bytes(2) == 1 << 30 and Z.copy_chunk_bytes(4) == Z.copy_chunk_bytes(8) == 2 << 30
+    for world in (2, 4, 8):
+        per = Z.copy_chunk_bytes(world) // (Z.GROUP * 4)
+        for lo, hi in ((0, 1), (5, 5 + per // 8), (7, 7 + per // 8 + 1), (100, 100 + 3 * per + 17)):
+            r = Recorder()
+            r.gather, r.world = "copy", world
+            r._update_in_chunks(lo, hi)
+            assert r.calls[0][0] == lo and r.calls[-1][1] == hi
+            assert all(a[1] == b[0] for a, b in zip(r.calls, r.calls[1:])), "ranges must follow each other"
+            assert r.calls[0][1] - r.calls[0][0] <= max(1, per // 8)
+            assert all(b - a <= per for a, b in r.calls[1:])
+            assert len(r.calls) == 1 + max(0, -(-(hi - lo - max(1, per // 8)) // per))
+    r = Recorder()
+    r.gather, r.world = "fused", 8
+    r._update_in_chunks(3, 10 ** 9)
+    assert r.calls == [(3, 10 ** 9)]
