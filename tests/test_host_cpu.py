@@ -264,3 +264,20 @@ def test_reference_arm_of_the_bench_prints_its_line(tmp_path):
     from oracle import build_ref
     if build_ref.have_python() or build_ref.reference_root() is not None:
         assert d["cpu_baseline"]["kind"] == "reference-python"
+
+
+def test_step_from_host_checks_its_arguments_before_touching_a_gpu():
+    """``AdamW.step_from_host``: one entry per parameter, sizes and dtypes checked; an all-``None`` list is a no-op."""
+    import torch
+    import lpmm
+    ps = [torch.nn.Parameter(torch.zeros(8, 4)), torch.nn.Parameter(torch.zeros(5))]
+    opt = lpmm.optim.AdamW(ps, fused=True)
+    with pytest.raises(ValueError):
+        opt.step_from_host([None])
+    with pytest.raises(RuntimeError):
+        opt.step_from_host([torch.zeros(31), None])
+    with pytest.raises(RuntimeError):
+        opt.step_from_host([torch.zeros(32, dtype=torch.float64), None])
+    ps[0].grad = torch.ones(8, 4)
+    opt.step_from_host([None, None])          # nobody steps; a skipped parameter loses its gradient
+    assert ps[0].grad is None and len(opt.state) == 0
