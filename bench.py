@@ -370,12 +370,13 @@ def local_update_rate(opt, iters, peak, world):
             "hbm_gb_per_s_per_gpu": gbs, "frac_of_measured_hbm_peak": gbs / peak}
 
 
-def sharded_step_line(shapes, dev, gather, dtype, iters, world):
-    """Whole sharded step (update + exchange) of another list / element type, timed like the headline: max over ranks."""
+def sharded_step_line(shapes, dev, gather, dtype, iters, world, replica_dtype=None):
+    """Whole sharded step (update + exchange) of another list / element type, timed like the headline: max over ranks.
+    ``replica_dtype``: fp32 master parameters kept per shard, 16-bit replicas published to the peers."""
     import torch
     import torch.distributed as dist
     from lpmm.zero import Zero1FusedAdamW
-    z = Zero1FusedAdamW(shapes, dev, gather=gather, dtype=dtype, **HYPER)
+    z = Zero1FusedAdamW(shapes, dev, gather=gather, dtype=dtype, replica_dtype=replica_dtype, **HYPER)
     z.init_params_normal_(0.02, seed=0)
     tmp = torch.empty(min(z.grad_shard.numel(), 1 << 26), device=dev)
     student_t_(tmp, 100003 + dist.get_rank(), rows_outliers=False)
@@ -398,8 +399,10 @@ def sharded_step_line(shapes, dev, gather, dtype, iters, world):
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item())
     total = sum(numel(s) for s in shapes)
-    sent = float(z.esize) * z.shard_groups * 128 * (world - 1)
-    out = {"params": total, "dtype": str(dtype).replace("torch.", ""), "ms_per_step": ms, "value": total / (ms * 1e-3), "unit": UNIT,
+    sent = float(z.xsize) * z.shard_groups * 128 * (world - 1)
+    out = {"params": total, "dtype": str(dtype).replace("torch.", "") + (
+               "" if replica_dtype is None else " master, " + str(replica_dtype).replace("torch.", "") + " replicas"),
+           "ms_per_step": ms, "value": total / (ms * 1e-3), "unit": UNIT,
            "steps": iters, "nvlink_bytes_sent_per_rank_per_step": sent, "nvlink_gb_per_s_per_rank": sent / (ms * 1e-3) / 1e9}
     del z
     torch.cuda.empty_cache()
@@ -675,6 +678,12 @@ def run_own(args):
             extra["params_bf16"] = sharded_step_line(shapes, dev, args.gather, torch.bfloat16, n_x, world)
         except Exception as e:  # an extra must not cost the headline line
             extra["params_bf16"] = {"error": repr(e)[:200]}
+        if args.gather == "copy":
+            try:  # fp32 master parameters per shard, bf16 replicas for the model: the exchange carries 2 B per parameter
+                extra["fp32_master_bf16_replicas"] = sharded_step_line(shapes, dev, "copy", torch.float32, n_x, world,
+                                                                       replica_dtype=torch.bfloat16)
+            except Exception as e:
+                extra["fp32_master_bf16_replicas"] = {"error": repr(e)[:200]}
         other = "fused" if args.gather == "copy" else "copy"
         try:  # the same list with the other in-process exchange (stores inside the update kernel / copy engines)
             extra[f"gather_{other}"] = sharded_step_line(shapes, dev, other, torch.float32, n_x, world)

@@ -399,6 +399,12 @@ int lpmm_b200_adamw4bit_fused_arith_step_many_flags(const lpmm_b200_step_tensor*
                                                     const double* steps, void* scratch, int64_t scratch_bytes,
                                                     void* stream, uint32_t flags);
 
+/* fp32 -> bf16 / fp16 copy of `numel` elements, round to nearest even (dtype = LPMM_B200_DTYPE_*): the 16-bit replicas
+ * of fp32 master parameters in a sharded step (a rank keeps fp32 parameters for its own range and publishes them at
+ * half the bytes).  src 4-byte, dst 2-byte aligned; 256-bit loads / 128-bit stores where both are 32- / 16-byte aligned
+ * at the same element.  No counterpart in the reference (torch's `.to(dtype)` gives the same values). */
+int lpmm_b200_narrow_fp32(const float* src, void* dst, int64_t numel, int dtype, void* stream);
+
 /* One momentum-SGD step of one tensor with the arithmetic of _single_tensor_sgd4bit
  * (lpmm/optim/sgd.py:133-187).  buf_mode FP32 or GROUP4; first != 0: the buffer is created from
  * the (decayed) gradient.  momentum == 0 ignores the buffer. */

@@ -138,6 +138,7 @@ def _load():
                                                       + [ctypes.POINTER(d), vp, i64, vp]),
         "lpmm_b200_factored_scratch_bytes": (i64, [ctypes.POINTER(i64), i32]),
         "lpmm_b200_adamw4bit_factored_step_noalloc": (i32, [ctypes.POINTER(StepTensor), vp] + [d] * 6 + [vp]),
+        "lpmm_b200_narrow_fp32": (i32, [vp, vp, i64, i32, vp]),
         "lpmm_b200_test_exactness": (i32, [i32, vp, ctypes.c_uint64, i64, vp, vp]),
         "lpmm_b200_sgd4bit_step": (i32, [vp, vp, i64, vp, vp, i32, i32, vp, d, d, d, d, i32, i32, vp]),
     }

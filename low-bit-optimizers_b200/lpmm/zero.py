@@ -86,10 +86,13 @@ class Zero1FusedAdamW:
 
     def __init__(self, shapes, device, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=1e-2, process_group=None,
                  rank=None, world=None, gather="nccl", reduce_grads=False, grad_scale=None, dtype=torch.float32,
-                 exact_params=True):
+                 exact_params=True, replica_dtype=None):
         """``dtype``: element type of parameters and gradients, fp32 or bf16 / fp16 (the 16-bit fused step; half the
         bytes over NVLink).  ``exact_params=False``: the tolerance mode of the fused step (codes and scales as
-        always, parameters within 1e-6 relative)."""
+        always, parameters within 1e-6 relative).  ``replica_dtype`` (bf16 / fp16; fp32 parameters, gather="copy"): fp32
+        MASTER parameters with 16-bit replicas -- a rank keeps fp32 parameters only for its own range (the rest of
+        ``flat`` is never refreshed), narrows every updated range into ``replica`` and the copy engines publish that
+        to the peers: the exchange carries 2 bytes per parameter and the model computes on ``replica_params``."""
         from .functional import create_general_qmap
         if dtype not in (torch.float32, torch.bfloat16, torch.float16):
             raise ValueError("dtype must be float32, bfloat16 or float16")
@@ -132,6 +135,24 @@ class Zero1FusedAdamW:
             self.flat = torch.zeros(self.world * S * GROUP, dtype=self.dtype, device=self.device)
         self.params = [self.flat[gs * GROUP: gs * GROUP + n].view(s)
                        for s, n, gs in zip(self.shapes, self.numels, self.gstart)]
+        self.replica = None
+        if replica_dtype is not None:
+            if self.dtype != torch.float32 or replica_dtype not in (torch.bfloat16, torch.float16):
+                raise ValueError("replica_dtype is bfloat16 or float16, next to float32 parameters")
+            if self.world > 1 and self.gather != "copy":
+                raise ValueError("replica_dtype needs gather='copy'")
+            if self.world > 1:
+                import torch.distributed._symmetric_memory as symm_mem
+                self.replica = symm_mem.empty(self.world * S * GROUP, dtype=replica_dtype, device=self.device)
+                self.replica.zero_()
+                self._rsymm = symm_mem.rendezvous(self.replica, process_group if process_group is not None else dist.group.WORLD)
+                order = [(self.rank + k) % self.world for k in range(1, self.world)]
+                self._peer_replicas = [self._rsymm.get_buffer(r, (self.world * S * GROUP,), replica_dtype) for r in order]
+            else:
+                self.replica = torch.zeros(self.world * S * GROUP, dtype=replica_dtype, device=self.device)
+            self.replica_params = [self.replica[gs * GROUP: gs * GROUP + n].view(s)
+                                   for s, n, gs in zip(self.shapes, self.numels, self.gstart)]
+        self.xsize = 2 if self.replica is not None else self.esize  # bytes per parameter that reach the peers
         self.grad_shard = torch.zeros(S * GROUP, dtype=self.dtype, device=self.device)
         # reduce_grads: every rank holds a FULL flat gradient buffer (its local gradients, as data-parallel
         # backward leaves them) in symmetric memory, ``self.grads[i]`` its views; the update kernel of a rank
@@ -202,6 +223,8 @@ class Zero1FusedAdamW:
         for lo in range(0, self.flat.numel(), chunk):
             hi = min(lo + chunk, self.flat.numel())
             self.flat[lo:hi].normal_(0, std, generator=g)
+            if self.replica is not None:
+                self.replica[lo:hi].copy_(self.flat[lo:hi])
 
     def set_grad_shard_from_full(self, grads):
         """Copy this rank's slice out of a full gradient list (tests / single-process use)."""
@@ -296,19 +319,35 @@ class Zero1FusedAdamW:
                 N.check(N.lib.lpmm_b200_adamw4bit_multi_tensor_flags(self._tl, nt, qm, qv, h, lo, hi, flags, st))
         if peers and self.gather == "copy":
             self._push_to_peers(lo, hi)
+        elif peers and self.replica is not None:
+            self._narrow(lo, hi)
+
+    def _narrow(self, lo, hi):
+        """The 16-bit replica of groups ``[lo, hi)`` from the fp32 master parameters, on the current stream."""
+        from . import _native as N
+        e0, n = lo * GROUP, (hi - lo) * GROUP
+        dt = N.DTYPE_BF16 if self.replica.dtype == torch.bfloat16 else N.DTYPE_FP16
+        with torch.cuda.device(self.device):
+            N.check(N.lib.lpmm_b200_narrow_fp32(ctypes.c_void_p(self.flat.data_ptr() + 4 * e0),
+                                                ctypes.c_void_p(self.replica.data_ptr() + 2 * e0), n, dt,
+                                                ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
 
     def _push_to_peers(self, lo, hi):
         """gather="copy": once the launches enqueued so far have finished, the copy engines write groups ``[lo, hi)``
         of the flat buffer into every peer's copy (one stream, peers in rank order starting after this rank, so that
         ranks in step send to different peers); the caller's stream goes on with the next range meanwhile."""
         main = torch.cuda.current_stream(self.device)
+        src, peers = self.flat, self._peer_flats
+        if self.replica is not None:  # fp32 master parameters stay here; the peers get the 16-bit replica of the range
+            self._narrow(lo, hi)
+            src, peers = self.replica, self._peer_replicas
         ev = torch.cuda.Event()
         ev.record(main)
         self._peer_stream.wait_event(ev)
         e0, e1 = lo * GROUP, hi * GROUP
         with torch.cuda.stream(self._peer_stream):
-            for peer in self._peer_flats:
-                peer[e0:e1].copy_(self.flat[e0:e1], non_blocking=True)
+            for peer in peers:
+                peer[e0:e1].copy_(src[e0:e1], non_blocking=True)
 
     def _update_in_chunks(self, lo, hi, hyper=None):
         """``_update`` of ``[lo, hi)``; with gather="copy" in ranges of ``copy_chunk_bytes(world)`` so that the copies of
@@ -490,7 +529,7 @@ class Zero1FusedAdamW:
         dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.pg)
         upd_ms, ag_ms = float(t[0]), float(t[1])
         total = sum(self.numels)
-        recv = float(self.esize) * self.shard_groups * GROUP * (self.world - 1)
+        recv = float(self.xsize) * self.shard_groups * GROUP * (self.world - 1)
         if self.gather == "fused":
             return {"update_with_peer_stores": {"ms": upd_ms, "aggregate_params_per_s": total / (upd_ms * 1e-3),
                                                 "nvlink_bytes_sent_per_rank": recv,

@@ -109,3 +109,50 @@ def test_zero_wrapper_step_from_host_equals_step(chunk):
     _same(pa, pb, za, zb)
     with pytest.raises(ValueError):
         za.step_from_host(hg[:-1])
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_narrowing_kernel_equals_torch_conversion(dtype):
+    """``lpmm_b200_narrow_fp32`` through the C ABI on aligned and unaligned views, sizes around the vector width,
+    values that need rounding, infinities and NaN: bit-identical to ``.to(dtype)``."""
+    import ctypes
+    from lpmm import _native as N
+    dt = N.DTYPE_BF16 if dtype == torch.bfloat16 else N.DTYPE_FP16
+    torch.manual_seed(3)
+    base = torch.randn(1 << 16, device=device()) * 3.0
+    base[::97] = float("inf")
+    base[1::193] = float("nan")
+    base[2::389] = 1e-30
+    out = torch.zeros((1 << 16) + 16, dtype=dtype, device=device())
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    for off_s, off_d, n in ((0, 0, 1 << 16), (1, 0, 1000), (3, 5, 4097), (8, 8, 12345), (0, 1, 77), (5, 0, 7), (0, 0, 0)):
+        src, dst = base[off_s:off_s + n], out[off_d:off_d + n]
+        dst.zero_()
+        N.check(N.lib.lpmm_b200_narrow_fp32(ctypes.c_void_p(src.data_ptr()), ctypes.c_void_p(dst.data_ptr()), n, dt, st))
+        torch.cuda.synchronize()
+        want = src.to(dtype)
+        nan = torch.isnan(want)
+        assert torch.equal(torch.isnan(dst), nan), (off_s, off_d, n)     # a NaN stays a NaN (payload not compared)
+        assert torch.equal(dst.view(torch.int16)[~nan], want.view(torch.int16)[~nan]), (off_s, off_d, n)
+    assert N.lib.lpmm_b200_narrow_fp32(None, None, 5, dt, st) == -1
+    assert N.lib.lpmm_b200_narrow_fp32(None, None, 5, 9, st) == -3
+
+
+def test_one_rank_engine_with_fp32_master_and_bf16_replicas():
+    from lpmm.zero import Zero1FusedAdamW
+    kw = dict(lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01, rank=0, world=1)
+    za = Zero1FusedAdamW(SHAPES, device(), replica_dtype=torch.bfloat16, **kw)
+    zb = Zero1FusedAdamW(SHAPES, device(), **kw)
+    za.init_params_normal_(0.02, seed=0)
+    zb.init_params_normal_(0.02, seed=0)
+    for s in range(1, 4):
+        grads = [student_t(sh, 100003 * s + i) for i, sh in enumerate(SHAPES)]
+        for z in (za, zb):
+            z.set_grad_shard_from_full(grads)
+            z.step()
+    torch.cuda.synchronize()
+    assert torch.equal(za.flat.view(torch.int32), zb.flat.view(torch.int32))
+    assert torch.equal(za.replica.view(torch.int16), zb.flat.to(torch.bfloat16).view(torch.int16))
+    assert za.replica_params[3].shape == tuple(SHAPES[3])
+    with pytest.raises(ValueError):
+        Zero1FusedAdamW(SHAPES, device(), dtype=torch.bfloat16, replica_dtype=torch.bfloat16, **kw)

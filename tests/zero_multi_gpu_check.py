@@ -131,8 +131,24 @@ for step in range(1, 4):
     zc.step_from_host(hg, chunk_bytes=1 << 16); zd.step()
 torch.cuda.synchronize(); dist.barrier()
 same5 = same5 and all(bool(torch.equal(x.detach().view(torch.int32), y.detach().view(torch.int32))) for x, y in zip(wc, wd))
-ok = ok and same3 and same4 and same5
+# ---- fp32 master parameters per shard with bf16 replicas: the replica equals the narrowed parameters of the plain
+# sharded step on every rank, and a rank's own range of master parameters equals that step's fp32 parameters
+ma = Zero1FusedAdamW(shapes, dev, gather="copy", replica_dtype=torch.bfloat16, **H)
+mb = Zero1FusedAdamW(shapes, dev, gather="nccl", **H)
+ma.init_params_normal_(0.02, seed=0); mb.init_params_normal_(0.02, seed=0)
+for step in range(1, 4):
+    grads = []
+    for i, s in enumerate(shapes):
+        g = torch.Generator(device=dev); g.manual_seed(step * 100003 + 19 * i)
+        grads.append(torch.randn(s, generator=g, device=dev) * 1e-3)
+    for o in (ma, mb):
+        o.set_grad_shard_from_full(grads); o.step()
+torch.cuda.synchronize(); dist.barrier()
+own = slice(ma.lo * 128, ma.hi * 128)
+same6 = bool(torch.equal(ma.replica.view(torch.int16), mb.flat.to(torch.bfloat16).view(torch.int16)))
+same6 = same6 and bool(torch.equal(ma.flat[own].view(torch.int32), mb.flat[own].view(torch.int32)))
+ok = ok and same3 and same4 and same5 and same6
 print(f"rank {rank}: {'OK' if ok else 'MISMATCH'} (fused == nccl: {same}, in-kernel gradient reduction == summed gradients: {same2}, "
       f"16-bit sharded == unsharded: {same3}, optimizer wrapper == unsharded optimizer: {same4}, "
-      f"step_from_host == copy then step: {same5})", flush=True)
+      f"step_from_host == copy then step: {same5}, fp32 master + bf16 replicas == narrowed parameters: {same6})", flush=True)
 dist.destroy_process_group()
